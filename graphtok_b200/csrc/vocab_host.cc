@@ -1,0 +1,316 @@
+// tokenizer.json -> HostVocab.  See vocab_host.h for the contract.
+#include "vocab_host.h"
+#include "json_min.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <fstream>
+#include <sstream>
+#include <unordered_map>
+
+namespace gtok {
+
+namespace {
+
+// The exact Split patterns of the two regex-driven families
+// (reference: src/vocab.cc:124-131).  GPT-2's pattern is built into the
+// ByteLevel pre-tokenizer and never appears in the file.
+const char* const kLlama3Pattern =
+    "(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\r\\n\\p{L}\\p{N}]?\\p{L}+|"
+    "\\p{N}{1,3}| ?[^\\s\\p{L}\\p{N}]+[\\r\\n]*|\\s*[\\r\\n]+|"
+    "\\s+(?!\\S)|\\s+";
+const char* const kQwen25Pattern =
+    "(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\r\\n\\p{L}\\p{N}]?\\p{L}+|"
+    "\\p{N}| ?[^\\s\\p{L}\\p{N}]+[\\r\\n]*|\\s*[\\r\\n]+|"
+    "\\s+(?!\\S)|\\s+";
+
+struct ByteMaps {
+    uint32_t b2u[256];
+    int u2b[0x200];
+    ByteMaps() {
+        for (int& x : u2b) x = -1;
+        bool printable[256] = {};
+        for (int b = 0x21; b <= 0x7E; ++b) printable[b] = true;
+        for (int b = 0xA1; b <= 0xAC; ++b) printable[b] = true;
+        for (int b = 0xAE; b <= 0xFF; ++b) printable[b] = true;
+        uint32_t extra = 0;
+        for (int b = 0; b < 256; ++b) b2u[b] = printable[b] ? static_cast<uint32_t>(b) : 256u + extra++;
+        for (int b = 0; b < 256; ++b) u2b[b2u[b]] = b;
+    }
+};
+const ByteMaps& maps() { static const ByteMaps m; return m; }
+
+using json::Value;
+
+bool str_is(const Value* obj, const char* key, const char* want) {
+    if (!obj) return false;
+    const Value* v = obj->find(key);
+    return v && v->is_string() && v->str == want;
+}
+// Field equals `want`; an absent field counts as `dflt`.
+bool bool_is(const Value* obj, const char* key, bool want, bool dflt) {
+    const Value* v = obj ? obj->find(key) : nullptr;
+    if (!v) return dflt == want;
+    return v->is_bool() && v->b == want;
+}
+bool null_or_absent(const Value* obj, const char* key) {
+    const Value* v = obj->find(key);
+    return !v || v->is_null();
+}
+bool empty_or_absent(const Value* obj, const char* key) {
+    const Value* v = obj->find(key);
+    return !v || v->is_null() || (v->is_string() && v->str.empty());
+}
+bool is_split(const Value& step, const char* pattern) {
+    if (!step.is_object() || !str_is(&step, "type", "Split") || !str_is(&step, "behavior", "Isolated") ||
+        !bool_is(&step, "invert", false, false))
+        return false;
+    const Value* pat = step.find("pattern");
+    return pat && pat->is_object() && str_is(pat, "Regex", pattern);
+}
+bool is_bytelevel(const Value& step, bool trim_offsets, bool use_regex) {
+    return step.is_object() && str_is(&step, "type", "ByteLevel") &&
+           bool_is(&step, "add_prefix_space", false, false) &&
+           bool_is(&step, "trim_offsets", trim_offsets, true) &&
+           bool_is(&step, "use_regex", use_regex, true);
+}
+
+// Token string in the byte-level alphabet -> raw bytes.  A codepoint outside
+// the 256-entry alphabet contributes its low byte, as the reference does
+// (src/vocab.cc:103-109).
+std::string decode_token(const std::string& s) {
+    std::string out;
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(s.data());
+    size_t n = s.size(), i = 0;
+    while (i < n) {
+        uint32_t cp;
+        size_t adv;
+        unsigned char c = p[i];
+        if (c < 0x80) { cp = c; adv = 1; }
+        else if ((c & 0xE0) == 0xC0 && i + 1 < n) { cp = ((c & 0x1Fu) << 6) | (p[i + 1] & 0x3Fu); adv = 2; }
+        else if ((c & 0xF0) == 0xE0 && i + 2 < n) { cp = ((c & 0x0Fu) << 12) | ((p[i + 1] & 0x3Fu) << 6) | (p[i + 2] & 0x3Fu); adv = 3; }
+        else if ((c & 0xF8) == 0xF0 && i + 3 < n) {
+            cp = ((c & 0x07u) << 18) | ((p[i + 1] & 0x3Fu) << 12) | ((p[i + 2] & 0x3Fu) << 6) | (p[i + 3] & 0x3Fu);
+            adv = 4;
+        } else { cp = c; adv = 1; }
+        int b = unicode_to_byte(cp);
+        out.push_back(static_cast<char>(b >= 0 ? b : static_cast<int>(cp & 0xFF)));
+        i += adv;
+    }
+    return out;
+}
+
+std::string utf8_of(uint32_t cp) {
+    std::string s;
+    if (cp < 0x80) s.push_back(static_cast<char>(cp));
+    else if (cp < 0x800) { s.push_back(static_cast<char>(0xC0 | (cp >> 6))); s.push_back(static_cast<char>(0x80 | (cp & 0x3F))); }
+    else { s.push_back(static_cast<char>(0xE0 | (cp >> 12))); s.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F))); s.push_back(static_cast<char>(0x80 | (cp & 0x3F))); }
+    return s;
+}
+
+}  // namespace
+
+const uint32_t* byte_to_unicode() { return maps().b2u; }
+int unicode_to_byte(uint32_t cp) { return cp < 0x200 ? maps().u2b[cp] : -1; }
+
+const char* family_name(Family f) {
+    switch (f) {
+        case Family::GPT2: return "GPT2";
+        case Family::Llama3: return "Llama3";
+        case Family::Qwen25: return "Qwen25";
+    }
+    return "?";
+}
+
+bool load_tokenizer_json(const std::string& path, HostVocab& out, std::string& err) {
+    std::ifstream f(path, std::ios::binary);
+    if (!f.is_open()) { err = "cannot open " + path; return false; }
+    std::stringstream ss;
+    ss << f.rdbuf();
+    const std::string text = ss.str();
+    Value root;
+    {
+        json::Parser parser(text.data(), text.size());
+        std::string perr;
+        if (!parser.parse(root, perr)) { err = "JSON parse error: " + perr; return false; }
+    }
+    if (!root.is_object()) { err = "top level is not an object"; return false; }
+    const Value* model = root.find("model");
+    if (!model || !model->is_object()) { err = "top-level 'model' missing"; return false; }
+    if (const Value* t = model->find("type")) {
+        if (!t->is_string() || t->str != "BPE") { err = "unsupported model.type"; return false; }
+    }
+    const Value* vocab = model->find("vocab");
+    const Value* merges = model->find("merges");
+    if (!vocab || !vocab->is_object() || !merges || !merges->is_array()) {
+        err = "model.vocab or model.merges missing";
+        return false;
+    }
+
+    // ---- family by exact structural match -------------------------------
+    const Value* norm = root.find("normalizer");
+    const Value* pt = root.find("pre_tokenizer");
+    const bool norm_null = !norm || norm->is_null();
+    bool matched = false;
+    out.nfc = false;
+    if (pt && norm_null && is_bytelevel(*pt, /*trim_offsets=*/true, /*use_regex=*/true)) {
+        out.family = Family::GPT2;
+        matched = true;
+    } else if (pt && pt->is_object() && str_is(pt, "type", "Sequence")) {
+        const Value* seq = pt->find("pretokenizers");
+        if (seq && seq->is_array() && seq->arr.size() == 2) {
+            if (norm_null && is_split(seq->arr[0], kLlama3Pattern) && is_bytelevel(seq->arr[1], true, false)) {
+                out.family = Family::Llama3;
+                matched = true;
+            } else if (norm && norm->is_object() && str_is(norm, "type", "NFC") &&
+                       is_split(seq->arr[0], kQwen25Pattern) && is_bytelevel(seq->arr[1], false, false)) {
+                out.family = Family::Qwen25;
+                out.nfc = true;
+                matched = true;
+            }
+        }
+    }
+    if (!matched) {
+        err = "unsupported pre_tokenizer/normalizer pipeline (only the exact GPT-2, Llama-3 and Qwen2.5 shapes load)";
+        return false;
+    }
+    // ---- model options ---------------------------------------------------
+    const bool llama = out.family == Family::Llama3;
+    if (!null_or_absent(model, "dropout") || !empty_or_absent(model, "continuing_subword_prefix") ||
+        !empty_or_absent(model, "end_of_word_suffix") || !bool_is(model, "byte_fallback", false, false) ||
+        !bool_is(model, "fuse_unk", false, false) || !bool_is(model, "ignore_merges", llama, false) ||
+        !null_or_absent(model, "unk_token")) {
+        err = "unsupported BPE model options for this family";
+        return false;
+    }
+    out.ignore_merges = llama;
+
+    // ---- vocab -----------------------------------------------------------
+    std::unordered_map<std::string, uint32_t> id_of;
+    id_of.reserve(vocab->obj.size() * 2);
+    out.token_bytes.clear();
+    out.token_bytes.resize(vocab->obj.size());
+    for (const json::Member& m : vocab->obj) {
+        if (!m.second.is_number() || !m.second.is_int || m.second.inum < 0 || m.second.inum > 0x7FFFFFFF) {
+            err = "vocab id is not a non-negative integer";
+            return false;
+        }
+        uint32_t id = static_cast<uint32_t>(m.second.inum);
+        if (id >= out.token_bytes.size()) {
+            if (id > (1u << 24)) { err = "vocab id too large"; return false; }
+            out.token_bytes.resize(id + 1);
+        }
+        out.token_bytes[id] = decode_token(m.first);
+        id_of[m.first] = id;    // a repeated key keeps its last id, like a JSON object
+    }
+    for (int b = 0; b < 256; ++b) {
+        auto it = id_of.find(utf8_of(byte_to_unicode()[b]));
+        if (it == id_of.end()) {
+            char buf[64];
+            std::snprintf(buf, sizeof buf, "missing single-byte token for byte 0x%02x", b);
+            err = buf;
+            return false;
+        }
+        out.byte_to_id[b] = it->second;
+    }
+
+    // ---- merges ----------------------------------------------------------
+    out.merges.clear();
+    out.merges.reserve(merges->arr.size());
+    if (merges->arr.size() >= (1u << 26)) { err = "more than 2^26 merges"; return false; }
+    for (const Value& m : merges->arr) {
+        std::string l, r;
+        if (m.is_string()) {
+            size_t sp = m.str.find(' ');
+            if (sp == std::string::npos) { err = "malformed merge entry"; return false; }
+            l = m.str.substr(0, sp);
+            r = m.str.substr(sp + 1);
+        } else if (m.is_array() && m.arr.size() == 2 && m.arr[0].is_string() && m.arr[1].is_string()) {
+            l = m.arr[0].str;
+            r = m.arr[1].str;
+        } else {
+            err = "unexpected merge entry type";
+            return false;
+        }
+        auto li = id_of.find(l), ri = id_of.find(r);
+        if (li == id_of.end() || ri == id_of.end()) { err = "merge references unknown token"; return false; }
+        auto ci = id_of.find(l + r);
+        if (ci == id_of.end()) { err = "merge product missing from vocab"; return false; }
+        out.merges.push_back({li->second, ri->second, ci->second});
+    }
+
+    // ---- added tokens ----------------------------------------------------
+    out.added.clear();
+    out.added_max_bytes = 0;
+    if (const Value* at = root.find("added_tokens"); at && at->is_array()) {
+        std::unordered_map<std::string, uint32_t> seen;
+        for (const Value& t : at->arr) {
+            if (!t.is_object()) { err = "added token is not an object"; return false; }
+            if (!bool_is(&t, "single_word", false, false) || !bool_is(&t, "lstrip", false, false) ||
+                !bool_is(&t, "rstrip", false, false)) {
+                err = "added token uses unsupported single_word/lstrip/rstrip matching";
+                return false;
+            }
+            const Value* idv = t.find("id");
+            const Value* cv = t.find("content");
+            uint32_t id = (idv && idv->is_number() && idv->inum >= 0) ? static_cast<uint32_t>(idv->inum) : 0u;
+            std::string content = (cv && cv->is_string()) ? cv->str : std::string();
+            const Value* nv = t.find("normalized");
+            bool normalized = nv && nv->is_bool() && nv->b;
+            if (normalized && out.nfc) { err = "normalized added tokens with an NFC normalizer are not supported"; return false; }
+            if (content.empty()) continue;
+            auto dup = seen.find(content);
+            if (dup != seen.end()) {
+                if (dup->second != id) { err = "added token content assigned to two ids"; return false; }
+                continue;
+            }
+            seen.emplace(content, id);
+            if (id >= out.token_bytes.size()) {
+                if (id > (1u << 24)) { err = "added token id too large"; return false; }
+                out.token_bytes.resize(static_cast<size_t>(id) + 1);
+            }
+            if (out.token_bytes[id].empty()) {
+                out.token_bytes[id] = content;
+            } else {
+                // The id already names a model token: its spelling must be this literal.
+                bool same = false;
+                for (const json::Member& m : vocab->obj)
+                    if (static_cast<uint32_t>(m.second.inum) == id && m.first == content) { same = true; break; }
+                if (!same) { err = "added token id conflicts with model-vocab content"; return false; }
+            }
+            if (out.nfc) {
+                for (unsigned char c : content)
+                    if (c >= 0x80) { err = "non-ASCII added token under an NFC normalizer is not supported"; return false; }
+            }
+            out.added.push_back({id, content});
+            out.added_max_bytes = std::max<uint32_t>(out.added_max_bytes, static_cast<uint32_t>(content.size()));
+        }
+        // On-device matching looks at each candidate start on its own, which is
+        // only sound when no literal contains another literal's first byte
+        // after its own first position (reference: src/vocab.cc:812-825).
+        bool root_byte[256] = {};
+        for (const AddedToken& a : out.added) root_byte[static_cast<unsigned char>(a.content[0])] = true;
+        for (const AddedToken& a : out.added)
+            for (size_t i = 1; i < a.content.size(); ++i)
+                if (root_byte[static_cast<unsigned char>(a.content[i])]) {
+                    err = "added-token literals can overlap (a literal contains another literal's first byte)";
+                    return false;
+                }
+    }
+    out.vocab_size = static_cast<uint32_t>(out.token_bytes.size());
+
+    // ---- rank monotonicity ------------------------------------------------
+    {
+        std::vector<uint32_t> last_made(out.vocab_size, 0);   // 1 + highest rank producing the id
+        out.monotone = true;
+        for (uint32_t k = 0; k < out.merges.size(); ++k)
+            last_made[out.merges[k].result] = k + 1;
+        for (uint32_t k = 0; k < out.merges.size() && out.monotone; ++k) {
+            const MergeRule& m = out.merges[k];
+            if (last_made[m.left] > k || last_made[m.right] > k) out.monotone = false;
+        }
+    }
+    return true;
+}
+
+}  // namespace gtok
