@@ -1,0 +1,65 @@
+"""Builds the native pieces in-tree:
+
+  graphtok_b200/lib/libgtok.so      CUDA kernels + engine + C ABI, sm_100a only
+  graphtok_b200/datagen/datagen     synthetic text / vocabulary generator (host only)
+
+nvcc cross-compiles without a GPU.  Run as `python -m graphtok_b200.build`.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB_DIR = os.path.join(HERE, "lib")
+LIB = os.path.join(LIB_DIR, "libgtok.so")
+DATAGEN = os.path.join(HERE, "datagen", "datagen")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
+    "-Xcompiler", "-fPIC", "--shared",
+    "-Xlinker", "--version-script=" + os.path.join(CSRC, "gtok.map"),
+]
+SOURCES = ["encode_kernels.cu", "engine.cu", "gtok_abi.cc", "vocab_host.cc", "tables_build.cc"]
+
+
+def _newer(target, deps):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def _nvcc():
+    return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+
+
+def build_lib(force=False, verbose=False):
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "gtok.h")]
+    if not force and not _newer(LIB, deps):
+        return LIB
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+def build_datagen(force=False):
+    src = [os.path.join(HERE, "datagen", f) for f in ("datagen.cc", "seqsplit.h")] + [os.path.join(CSRC, "unicode_class_table.h")]
+    if not force and not _newer(DATAGEN, src):
+        return DATAGEN
+    subprocess.run(["g++", "-std=c++17", "-O2", "-o", DATAGEN, src[0]], check=True)
+    return DATAGEN
+
+
+def main():
+    force = "--force" in sys.argv
+    build_lib(force=force, verbose="-v" in sys.argv)
+    build_datagen(force=force)
+    print(LIB)
+    print(DATAGEN)
+
+
+if __name__ == "__main__":
+    main()

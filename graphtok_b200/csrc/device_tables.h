@@ -1,0 +1,88 @@
+// Layout of the vocabulary tables the encode kernels read.  One definition is
+// shared by the host builder (tables_build.cc, which fills plain host vectors)
+// and the kernels (which see the same arrays in device memory).
+//
+// All tables are read-only during an encode and small enough to stay resident
+// in the B200's L2 (tens of MB at most): the merge table is 16 B per slot, the
+// whole-word table 32 B per slot.
+#pragma once
+#include <stdint.h>
+
+namespace gtok {
+
+constexpr uint32_t kNoRank = 0xFFFFFFFFu;
+constexpr uint32_t kEmptyKey = 0xFFFFFFFFu;
+constexpr uint32_t kNoToken = 0xFFFFFFFFu;
+constexpr int kWordKeyMax = 15;        // longest pre-token the inline-key word table holds
+constexpr int kProbeLimit = 64;        // every table is built so that no probe chain is longer
+
+// Merge rule table: open addressing, linear probing, one 16-byte slot per rule.
+//   x = left id, y = right id, z = rank, w = result id;  x == kEmptyKey marks a free slot.
+// Replaces the reference's Slot64 / Slot128 pair (src/vocab.h:162-201): the
+// key and the value arrive in a single 128-bit load.
+struct MergeSlot { uint32_t left, right, rank, result; };
+
+// Whole-word table: pre-token bytes (at most 15) -> token id, for pre-tokens whose
+// encoding is known to be that single token.  Under ignore_merges (Llama-3) this
+// is every vocabulary token, which is the reference's direct table
+// (src/vocab.cc:1134-1171); otherwise only tokens whose own bytes merge back to
+// themselves, which makes the table a precomputed memo of the merge loop.
+//   k0,k1 = bytes 0..7 and 8..15 little-endian, zero padded, with the length in
+//   the top byte of k1;  id == kNoToken marks a free slot.
+struct WordSlot { uint64_t k0, k1; uint32_t id; uint32_t pad[3]; };
+
+// Long-token table (ignore_merges only): tokens of 16 bytes or more, found by
+// a 64-bit hash and confirmed byte for byte against `long_blob`.
+struct LongSlot { uint64_t hash; uint32_t id, off, len, pad; };
+
+// Added-token (special-token) trie.  Node i owns edges [first[i], first[i]+count[i]),
+// sorted by byte; an edge is (next_node << 8) | byte.  terminal[i] is the token id
+// ending at node i or kNoToken.  root[b] is the node after first byte b, or kNoToken.
+struct DeviceTables {
+    const MergeSlot* merge;     uint32_t merge_mask;
+    const WordSlot* word;       uint32_t word_mask;
+    const LongSlot* longtab;    uint32_t long_mask;
+    const uint8_t* long_blob;   uint32_t long_max_len;
+    const uint32_t* byte_to_id;          // [256]
+    const uint16_t* uc_stage1;           // unicode class table, see unicode_class_table.h
+    const uint32_t* uc_stage2;
+    const uint32_t* trie_root;           // [256]
+    const uint32_t* trie_first;
+    const uint16_t* trie_count;
+    const uint32_t* trie_terminal;
+    const uint32_t* trie_edges;
+    uint32_t added_max_bytes;            // 0 when the vocabulary has no added tokens
+    uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5
+    uint32_t ignore_merges;
+    uint32_t monotone;
+};
+
+// ---- hashes (host and device) ------------------------------------------------
+#if defined(__CUDACC__)
+#define GTOK_HD __host__ __device__ __forceinline__
+#else
+#define GTOK_HD inline
+#endif
+
+GTOK_HD uint32_t merge_hash(uint32_t l, uint32_t r) {
+    uint64_t x = (static_cast<uint64_t>(l) << 32) | r;
+    x ^= x >> 31; x *= 0x7fb5d329728ea185ULL;
+    x ^= x >> 27; x *= 0x81dadef4bc2dd44dULL;
+    x ^= x >> 33;
+    return static_cast<uint32_t>(x);
+}
+GTOK_HD uint32_t word_hash(uint64_t k0, uint64_t k1) {
+    uint64_t x = k0 * 0x9E3779B185EBCA87ULL + (k1 ^ (k1 >> 29)) * 0xC2B2AE3D27D4EB4FULL;
+    x ^= x >> 32; x *= 0xD6E8FEB86659FD93ULL;
+    x ^= x >> 32;
+    return static_cast<uint32_t>(x);
+}
+// FNV-1a over the bytes, folded with the length; used for the long-token table.
+GTOK_HD uint64_t long_hash_step(uint64_t h, uint8_t b) { return (h ^ b) * 1099511628211ULL; }
+constexpr uint64_t kLongHashSeed = 1469598103934665603ULL;
+GTOK_HD uint64_t long_hash_finish(uint64_t h, uint32_t len) {
+    h ^= len; h *= 0x9E3779B185EBCA87ULL; h ^= h >> 32;
+    return h;
+}
+
+}  // namespace gtok

@@ -1,0 +1,1211 @@
+// The encode path, tile by tile: pre-tokenization (boundary bits), per-pre-token
+// BPE merging and output assembly.  Two tile programs:
+//
+//   pretok_tile : text bytes -> one boundary bit per byte (a set bit = a
+//                 pre-token starts here) plus one "added token starts here" bit.
+//   merge_tile  : boundary bits + text -> token ids, written straight to their
+//                 final place in the output (tile base found by a single-pass
+//                 decoupled look-back over tile totals).
+//
+// Both are written against a small "thread block" interface (Blk):
+//     blk.par(f)                run f(tid) for every thread, then barrier
+//     blk.excl_scan(arr,total)  in-place exclusive scan of arr[kThreads]
+// so that the CUDA kernels in encode_kernels.cu (one real thread per tid) and a
+// serial emulation used by the CPU tests execute the very same logic.  Nothing
+// outside a par() body may depend on the order in which tids run, and no par()
+// body may read what another tid writes in the same par().
+//
+// Reference for behaviour (not structure): the boundary predicates restate the
+// regular expressions' semantics as the reference does in
+// src/pretok_boundary.h:221-297 (GPT-2) and :511-671 (Llama-3 / Qwen2.5), in the
+// byte domain instead of over dense codepoint arrays; the merge loop is the
+// greedy lowest-rank-first rule of src/tokenizer.cu:360-580 / src/host_encode.cc:617-648;
+// the batched rounds for long pre-tokens follow the idea of src/tokenizer.cu:754-791.
+#pragma once
+#include <stdint.h>
+
+#include "device_tables.h"
+
+#if defined(__CUDACC__)
+#define GTOK_DEV __device__ __forceinline__
+#define GTOK_DEV_NOINLINE static __device__ __noinline__
+#else
+#define GTOK_DEV inline
+#define GTOK_DEV_NOINLINE inline
+#endif
+
+namespace gtok {
+
+constexpr int kTile = 4096;        // bytes per tile
+constexpr int kThreads = 256;      // threads per block
+constexpr int kPer = kTile / kThreads;   // 16 bytes per thread
+constexpr int kHaloL = 128;
+constexpr int kHaloR = 64;
+constexpr int kWin = kHaloL + kTile + kHaloR;
+constexpr int kTileWords = kTile / 32;
+
+constexpr uint32_t kInvalidTok = 0xFFFFFFFFu;
+constexpr uint32_t kLongRef = 0x80000000u;      // tok[] entry that stands for a whole long pre-token
+constexpr uint32_t kDirty = 0xFFFFFFFEu;
+constexpr uint32_t kReprobe = 0xFFFFFFFEu;
+
+constexpr int kThreadWordMax = 16;   // longest pre-token merged by a single thread
+constexpr int kWarpWordMax = 256;    // longest pre-token merged by a warp in shared memory
+constexpr int kRows = 128;           // single-thread merge rows per batch
+constexpr int kWsWords = kRows * kThreadWordMax * 3;   // 6144 u32 = 24 KB, shared by all merge paths
+constexpr int kBlockWordSmemMax = kWsWords / 3;        // 2048 symbols
+constexpr int kMaxTeam = 256;        // long pre-tokens starting in one tile (a tile holds < 4096/17 of them)
+
+// Error bits accumulated in ctl[2] and reported to the host.
+enum : uint32_t {
+    kErrOutputFull = 1u,      // more tokens than the output buffer holds
+    kErrWaitExpired = 2u,     // a look-back wait gave up
+    kErrProbeLimit = 4u,      // a table probe ran past its limit (corrupt table)
+    kErrInternal = 8u,
+};
+
+// Per-byte attribute (shared memory, pretok only).
+enum : uint8_t {
+    A_L = 0, A_N = 1, A_S = 2, A_O = 3, A_CONT = 4, A_ADDED = 5, A_OUT = 7, A_CLS = 7,
+    A_CRLF = 8, A_SP = 16, A_DOC = 32,
+};
+
+struct EncodeArgs {
+    const uint8_t* text;          // padded; readable kTile + kWin bytes past the capacity
+    const uint32_t* meta;         // [0] = n_bytes, [1] = n_docs
+    const uint32_t* doc_off;      // [n_docs + 1] byte offsets (batch) or nullptr
+    const uint32_t* docmask;      // one bit per byte, set at document starts (batch) or nullptr
+    uint32_t* bmask;              // boundary bits, 1 per byte
+    uint32_t* amask;              // added-token-start bits
+    uint32_t* tile_nb;            // boundaries per tile
+    unsigned long long* st1;      // pretok look-back state per tile
+    unsigned long long* st2;      // merge look-back state per tile
+    uint32_t* ctl;                // [0] pretok ticket, [1] merge ticket, [2] error bits
+    uint32_t* gstage;             // u32 per byte: ids of long pre-tokens
+    uint32_t* gwork_rk;           // u32 per byte: rank workspace for very long pre-tokens
+    uint32_t* gwork_nw;           // u32 per byte: result workspace for very long pre-tokens
+    uint32_t* out_tokens;
+    uint32_t out_cap;
+    uint32_t* out_doc_tok;        // [n_docs + 1] token offsets (batch) or nullptr
+    uint32_t* status;             // [0] total tokens, [1] error bits (host-visible)
+    DeviceTables tb;
+};
+
+// ---- small portable helpers ---------------------------------------------------
+template <class T>
+GTOK_DEV T ldg(const T* p) {
+#if defined(__CUDA_ARCH__)
+    return __ldg(p);
+#else
+    return *p;
+#endif
+}
+GTOK_DEV int popc32(uint32_t x) {
+#if defined(__CUDA_ARCH__)
+    return __popc(x);
+#else
+    return __builtin_popcount(x);
+#endif
+}
+GTOK_DEV int ffs32(uint32_t x) {   // index of lowest set bit, x != 0
+#if defined(__CUDA_ARCH__)
+    return __ffs(x) - 1;
+#else
+    return __builtin_ctz(x);
+#endif
+}
+GTOK_DEV int fls32(uint32_t x) {   // index of highest set bit, x != 0
+#if defined(__CUDA_ARCH__)
+    return 31 - __clz(x);
+#else
+    return 31 - __builtin_clz(x);
+#endif
+}
+GTOK_DEV uint32_t shared_add(uint32_t* p, uint32_t v) {
+#if defined(__CUDA_ARCH__)
+    return atomicAdd(p, v);
+#else
+    uint32_t o = *p; *p = o + v; return o;
+#endif
+}
+GTOK_DEV void global_or(uint32_t* p, uint32_t v) {
+#if defined(__CUDA_ARCH__)
+    atomicOr(p, v);
+#else
+    *p |= v;
+#endif
+}
+GTOK_DEV unsigned long long load_state(const unsigned long long* p) {
+#if defined(__CUDA_ARCH__)
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+#else
+    return *p;
+#endif
+}
+GTOK_DEV void store_state(unsigned long long* p, unsigned long long v) {
+#if defined(__CUDA_ARCH__)
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+#else
+    *p = v;
+#endif
+}
+GTOK_DEV void backoff() {
+#if defined(__CUDA_ARCH__)
+    __nanosleep(40);
+#endif
+}
+
+constexpr unsigned long long kStAgg = 1ull << 62;     // value covers this tile only
+constexpr unsigned long long kStFinal = 2ull << 62;   // value needs nothing from earlier tiles
+constexpr int kWaitLimit = 1 << 22;                   // polls before a wait gives up
+
+// Waits for tile j's state to be published.  Returns 0 (and raises the error
+// bit) when the limit runs out, which the host reports as a failed call.
+GTOK_DEV unsigned long long wait_state(const unsigned long long* st, int j, uint32_t* ctl) {
+    for (int it = 0; it < kWaitLimit; ++it) {
+        unsigned long long v = load_state(st + j);
+        if (v >> 62) return v;
+        backoff();
+    }
+    global_or(ctl + 2, kErrWaitExpired);
+    return kStFinal;
+}
+
+// ---- merge-rule probe ----------------------------------------------------------
+struct RankRes { uint32_t rank, res; };
+GTOK_DEV RankRes probe_rule(const DeviceTables& tb, uint32_t l, uint32_t r) {
+    uint32_t h = merge_hash(l, r) & tb.merge_mask;
+    for (int i = 0; i < kProbeLimit; ++i) {
+#if defined(__CUDA_ARCH__)
+        uint4 s = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h);
+        if (s.x == l && s.y == r) return RankRes{s.z, s.w};
+        if (s.x == kEmptyKey) break;
+#else
+        const MergeSlot& s = tb.merge[h];
+        if (s.left == l && s.right == r) return RankRes{s.rank, s.result};
+        if (s.left == kEmptyKey) break;
+#endif
+        h = (h + 1) & tb.merge_mask;
+    }
+    return RankRes{kNoRank, 0};
+}
+
+GTOK_DEV uint32_t probe_word(const DeviceTables& tb, uint64_t k0, uint64_t k1) {
+    uint32_t h = word_hash(k0, k1) & tb.word_mask;
+    for (int i = 0; i < kProbeLimit; ++i) {
+#if defined(__CUDA_ARCH__)
+        const uint4* sp = reinterpret_cast<const uint4*>(tb.word + h);
+        uint4 a = __ldg(sp);
+        uint4 b = __ldg(sp + 1);
+        uint64_t s0 = (static_cast<uint64_t>(a.y) << 32) | a.x, s1 = (static_cast<uint64_t>(a.w) << 32) | a.z;
+        uint32_t id = b.x;
+#else
+        uint64_t s0 = tb.word[h].k0, s1 = tb.word[h].k1;
+        uint32_t id = tb.word[h].id;
+#endif
+        if (id == kNoToken) return kNoToken;
+        if (s0 == k0 && s1 == k1) return id;
+        h = (h + 1) & tb.word_mask;
+    }
+    return kNoToken;
+}
+
+// Whole pre-token of 16 bytes or more, present in the vocabulary?  (ignore_merges)
+GTOK_DEV uint32_t probe_long(const DeviceTables& tb, const uint8_t* text, uint32_t g, uint32_t len) {
+    if (len > tb.long_max_len) return kNoToken;
+    uint64_t h = kLongHashSeed;
+    for (uint32_t i = 0; i < len; ++i) h = long_hash_step(h, ldg(text + g + i));
+    h = long_hash_finish(h, len);
+    uint32_t at = static_cast<uint32_t>(h) & tb.long_mask;
+    for (int i = 0; i < kProbeLimit; ++i) {
+        LongSlot s = tb.longtab[at];
+        if (s.id == kNoToken) return kNoToken;
+        if (s.hash == h && s.len == len) {
+            bool same = true;
+            for (uint32_t k = 0; k < len && same; ++k) same = ldg(tb.long_blob + s.off + k) == ldg(text + g + k);
+            if (same) return s.id;
+        }
+        at = (at + 1) & tb.long_mask;
+    }
+    return kNoToken;
+}
+
+// ---- document-start bits ---------------------------------------------------------
+GTOK_DEV bool is_docstart_global(const EncodeArgs& a, int p) {
+    if (p == 0) return true;
+    if (!a.docmask) return false;
+    return (ldg(a.docmask + (p >> 5)) >> (p & 31)) & 1u;
+}
+
+// ==================================================================================
+//                                   PRE-TOKENIZATION
+// ==================================================================================
+struct PretokSmem {
+    alignas(16) uint8_t txt[kWin + 16];
+    alignas(16) uint8_t attr[kWin + 16];
+    uint32_t dsw[kWin / 32 + 2];             // document-start bits of the window
+    uint16_t bnd16[kThreads + 2], add16[kThreads + 2], pend16[kThreads + 2];
+    uint16_t lead16[kThreads + 2], nlead16[kThreads + 2], nstart16[kThreads + 2];
+    uint32_t carry[kTileWords + 1];
+    uint32_t sum_has[32], sum_cnt[32];
+    uint32_t scan[kThreads];
+    uint32_t misc[8];
+};
+
+// View of one tile's window for the predicate code.
+struct Win {
+    const PretokSmem* sm;
+    const EncodeArgs* a;
+    int lo;        // global position of window byte 0 (may be negative)
+    int vlo, vhi;  // positions in [vlo, vhi) have a trustworthy shared-memory attribute
+    int n;
+};
+
+// Longest added-token literal starting at global position s, clamped to the
+// document of s.  Returns its byte length (0 = none) and its id.
+template <class GetByte>
+GTOK_DEV uint32_t match_literal(const EncodeArgs& a, int s, int n, GetByte byte_at, uint32_t* id_out) {
+    const DeviceTables& tb = a.tb;
+    uint32_t node = ldg(tb.trie_root + byte_at(s));
+    if (node == kNoToken) return 0;
+    uint32_t best = 0;
+    int q = s + 1;
+    for (;;) {
+        uint32_t term = ldg(tb.trie_terminal + node);
+        if (term != kNoToken) { best = static_cast<uint32_t>(q - s); *id_out = term; }
+        if (q >= n || static_cast<uint32_t>(q - s) >= tb.added_max_bytes) break;
+        if (a.docmask && is_docstart_global(a, q)) break;
+        uint32_t want = byte_at(q);
+        uint32_t first = ldg(tb.trie_first + node), cnt = ldg(tb.trie_count + node);
+        uint32_t next = kNoToken;
+        for (uint32_t e = 0; e < cnt; ++e) {
+            uint32_t ed = ldg(tb.trie_edges + first + e);
+            if ((ed & 0xFF) == want) { next = ed >> 8; break; }
+        }
+        if (next == kNoToken) break;
+        node = next;
+        ++q;
+    }
+    return best;
+}
+
+// Class + flags of a byte, ignoring added tokens.  `byte_at(q)` must be valid for
+// q in [p, p+3] when those are below n.
+template <class GetByte, class IsDoc>
+GTOK_DEV uint8_t plain_attr(const EncodeArgs& a, int p, int n, GetByte byte_at, IsDoc is_doc) {
+    uint32_t b = byte_at(p);
+    uint8_t flags = is_doc(p) ? A_DOC : 0;
+    if ((b & 0xC0u) == 0x80u) return static_cast<uint8_t>(A_CONT | flags);
+    uint32_t cp = b;
+    if (b >= 0x80u) {
+        // Lenient decode: the lead byte decides the width if that many bytes
+        // remain in the document; continuation bytes are taken on trust.
+        int avail = n - p;
+        if (avail > 4) avail = 4;
+        for (int k = 1; k < avail; ++k) if (is_doc(p + k)) { avail = k; break; }
+        if ((b & 0xE0u) == 0xC0u && avail >= 2) cp = ((b & 0x1Fu) << 6) | (byte_at(p + 1) & 0x3Fu);
+        else if ((b & 0xF0u) == 0xE0u && avail >= 3) cp = ((b & 0x0Fu) << 12) | ((byte_at(p + 1) & 0x3Fu) << 6) | (byte_at(p + 2) & 0x3Fu);
+        else if ((b & 0xF8u) == 0xF0u && avail >= 4)
+            cp = ((b & 0x07u) << 18) | ((byte_at(p + 1) & 0x3Fu) << 12) | ((byte_at(p + 2) & 0x3Fu) << 6) | (byte_at(p + 3) & 0x3Fu);
+    }
+    uint32_t cls;
+    if (cp > 0x10FFFFu) cls = A_O;
+    else {
+        uint32_t leaf = ldg(a.tb.uc_stage1 + (cp >> 7));
+        uint32_t w = ldg(a.tb.uc_stage2 + leaf * 8u + ((cp & 127u) >> 4));
+        cls = (w >> ((cp & 15u) * 2u)) & 3u;
+    }
+    if (b == 0x0Au || b == 0x0Du) flags |= A_CRLF;
+    if (b == 0x20u) flags |= A_SP;
+    return static_cast<uint8_t>(cls | flags);
+}
+
+// Attribute of an arbitrary position straight from global memory (slow path for
+// walks that leave the window).
+GTOK_DEV_NOINLINE uint8_t attr_global(const EncodeArgs& a, int p, int n) {
+    if (p < 0 || p >= n) return A_OUT;
+    auto byte_at = [&](int q) -> uint32_t { return ldg(a.text + q); };
+    auto is_doc = [&](int q) -> bool { return is_docstart_global(a, q); };
+    if (a.tb.added_max_bytes) {
+        // Only the nearest literal-start byte at or before p can own p: a literal
+        // never contains another literal's first byte past its own first position.
+        int lim = p - static_cast<int>(a.tb.added_max_bytes) + 1;
+        if (lim < 0) lim = 0;
+        for (int s = p; s >= lim; --s) {
+            if (ldg(a.tb.trie_root + byte_at(s)) != kNoToken) {
+                uint32_t id;
+                uint32_t ml = match_literal(a, s, n, byte_at, &id);
+                if (ml && s + static_cast<int>(ml) > p) {
+                    uint8_t flags = is_doc(p) ? A_DOC : 0;
+                    return static_cast<uint8_t>((s == p ? A_ADDED : A_CONT) | flags);
+                }
+                break;
+            }
+            if (s < p && is_doc(s + 1)) break;   // never look into the previous document
+        }
+    }
+    return plain_attr(a, p, n, byte_at, is_doc);
+}
+
+GTOK_DEV uint8_t attr_at(const Win& w, int p) {
+    if (p >= w.vlo && p < w.vhi) return w.sm->attr[p - w.lo];
+    return attr_global(*w.a, p, w.n);
+}
+GTOK_DEV uint32_t text_at(const Win& w, int p) {   // p in [0, n)
+    if (p >= w.vlo && p < w.vhi) return w.sm->txt[p - w.lo];
+    return ldg(w.a->text + p);
+}
+
+// Lead position of the codepoint before the one starting at p (p itself not a
+// document start).  Returns -1 when p is the first codepoint of its document.
+GTOK_DEV int prev_lead(const Win& w, int p) {
+    int q = p - 1;
+    for (;;) {
+        if (q < 0) return -1;
+        uint8_t a = attr_at(w, q);
+        if ((a & A_CLS) != A_CONT) return q;
+        if (a & A_DOC) return -1;     // stray continuation bytes open the document: dropped
+        --q;
+    }
+}
+// Lead position of the codepoint after the one starting at p, or -1 at the end
+// of the document.
+GTOK_DEV int next_lead(const Win& w, int p) {
+    int q = p + 1;
+    for (;;) {
+        if (q >= w.n) return -1;
+        uint8_t a = attr_at(w, q);
+        if (a & A_DOC) return -1;
+        if ((a & A_CLS) != A_CONT) return q;
+        ++q;
+    }
+}
+// Class of the codepoint at lead q for its neighbours: L/N/S/O, or -1 for "nothing
+// there" (q < 0, or an added token, which behaves like the edge of the text).
+GTOK_DEV int ncls(uint8_t a) {
+    int c = a & A_CLS;
+    return c <= A_O ? c : -1;
+}
+
+// First byte of the codepoint at lead q as the contraction rule sees it:
+// lower-cased ASCII and U+017F read as 's' when the family matches case-insensitively.
+GTOK_DEV int tail_byte(const Win& w, int q, bool ci) {
+    if (q < 0) return -1;
+    uint8_t a = attr_at(w, q);
+    if ((a & A_CLS) > A_O) return -1;
+    int b = static_cast<int>(text_at(w, q));
+    if (ci) {
+        if (b >= 'A' && b <= 'Z') b += 32;
+        else if (b == 0xC5 && q + 1 < w.n && !(attr_at(w, q + 1) & A_DOC) && text_at(w, q + 1) == 0xBF) b = 's';
+    }
+    return b;
+}
+
+// Does a contraction ('s 't 'm 'd -> 1, 're 've 'll -> 2) start at the apostrophe
+// at lead k?  It does when the letters follow and the regex cursor can be at k:
+// at the start of the document, or after anything but punctuation or a literal space.
+GTOK_DEV int contraction_at(const Win& w, int k, uint8_t ak, bool ci) {
+    if ((ak & A_CLS) != A_O || text_at(w, k) != 0x27u) return 0;
+    int r1 = next_lead(w, k);
+    if (r1 < 0) return 0;
+    int x = tail_byte(w, r1, ci), tl = 0;
+    if (x == 'r' || x == 'v' || x == 'l') {
+        int r2 = next_lead(w, r1);
+        int y = r2 < 0 ? -1 : tail_byte(w, r2, ci);
+        if ((x == 'l' && y == 'l') || (x != 'l' && y == 'e')) tl = 2;
+    } else if (x == 's' || x == 't' || x == 'm' || x == 'd') tl = 1;
+    if (!tl) return 0;
+    if (ak & A_DOC) return tl;
+    int q = prev_lead(w, k);
+    if (q < 0) return tl;
+    uint8_t aq = attr_at(w, q);
+    if ((aq & A_CLS) == A_O) return 0;
+    if ((aq & A_CLS) == A_S && (aq & A_SP)) return 0;
+    return tl;
+}
+GTOK_DEV int contraction_at(const Win& w, int k, bool ci) {
+    if (k < 0) return 0;
+    return contraction_at(w, k, attr_at(w, k), ci);
+}
+
+// Boundary decision for the lead byte at p with attribute a0 (class L/N/S/O).
+// Sets *pending for a Llama-3 digit inside a digit run, whose answer depends on
+// its index in the run and is filled in later.
+GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool* pending, bool* nstart) {
+    *pending = false;
+    const int cur = a0 & A_CLS;
+    const bool ci = family != 0;
+    int q1 = (a0 & A_DOC) ? -1 : prev_lead(w, p);
+    if (cur == A_N) *nstart = true;
+    if (q1 < 0) return true;                       // first codepoint of its document
+    const uint8_t a1 = attr_at(w, q1);
+    const int prev = ncls(a1);
+    if (cur == A_N && prev == A_N) *nstart = false;
+
+    if (cur == A_L) {
+        // Inside a contraction tail?
+        int c1 = contraction_at(w, q1, a1, ci);
+        if (c1 >= 1) return false;
+        if (prev == A_L) {
+            int q2 = (a1 & A_DOC) ? -1 : prev_lead(w, q1);
+            if (q2 >= 0) {
+                int c2 = contraction_at(w, q2, ci);
+                if (c2 == 2) return false;          // second letter of 're 've 'll
+                if (c2 == 1) return true;           // letter right after a finished 's 't 'm 'd
+                uint8_t a2 = attr_at(w, q2);
+                int q3 = (a2 & A_DOC) ? -1 : prev_lead(w, q2);
+                if (q3 >= 0 && contraction_at(w, q3, ci) == 2) return true;   // after a finished 're 've 'll
+            }
+            return false;                            // inside a run of letters
+        }
+    } else if (cur == A_O) {
+        if (contraction_at(w, p, a0, ci)) return true;
+    }
+
+    if (family == 0) {   // ---------------------------------------------- GPT-2
+        if (prev == A_S && (a1 & A_SP) && cur != A_S) return false;      // " x": the space leads the token
+        if (cur == A_S) {
+            if (prev != A_S) return true;
+            // Last whitespace before a non-space splits off (\s+(?!\S)).
+            int r1 = next_lead(w, p);
+            if (r1 < 0) return false;
+            int nx = ncls(attr_at(w, r1));
+            return nx >= 0 && nx != A_S;
+        }
+        return cur != prev;
+    }
+
+    // ----------------------------------------------------------- Llama-3 / Qwen2.5
+    if (cur == A_S) {
+        if (a0 & A_CRLF) return prev == A_L || prev == A_N || prev < 0;   // else absorbed (O) or inside a run (S)
+        if (prev != A_S) return true;                                     // the run starts here
+        if (!(a1 & A_CRLF)) {
+            // Plain whitespace after plain whitespace: only the run's last char,
+            // with something other than the end of the text after it, splits off.
+            int r1 = next_lead(w, p);
+            if (r1 < 0) return false;
+            int nx = ncls(attr_at(w, r1));
+            return nx >= 0 && nx != A_S;
+        }
+        // Previous char is CR/LF.  If that newline stretch hangs off a punctuation
+        // token ( ?[^\s\p{L}\p{N}]+[\r\n]*), the whitespace run starts here.
+        int q = q1;
+        for (;;) {
+            uint8_t aq = attr_at(w, q);
+            if (!((aq & A_CLS) == A_S && (aq & A_CRLF))) { if ((aq & A_CLS) == A_O) return true; break; }
+            if (aq & A_DOC) break;
+            q = prev_lead(w, q);
+            if (q < 0) break;
+        }
+        // Otherwise p follows a newline inside the run: it starts the remainder
+        // only if no later newline in the run pulls it into \s*[\r\n]+.
+        int r = p;
+        for (;;) {
+            r = next_lead(w, r);
+            if (r < 0) return true;
+            uint8_t ar = attr_at(w, r);
+            if ((ar & A_CLS) != A_S) return true;
+            if (ar & A_CRLF) return false;
+        }
+    }
+    if (cur == A_L) {
+        if (prev == A_S) return (a1 & A_CRLF) != 0;     // any non-newline whitespace leads the word
+        if (prev == A_O) {
+            // One punctuation char leads the word if the cursor can be at it.
+            if (a1 & A_DOC) return false;
+            int q2 = prev_lead(w, q1);
+            if (q2 < 0) return false;
+            uint8_t a2 = attr_at(w, q2);
+            if ((a2 & A_CLS) == A_O) return true;
+            if ((a2 & A_CLS) == A_S && (a2 & A_SP)) return true;
+            return false;
+        }
+        return true;
+    }
+    if (cur == A_N) {
+        if (family == 2 || prev != A_N) return true;
+        *pending = true;
+        return false;
+    }
+    // cur == A_O
+    if (prev == A_O) return false;
+    if (prev == A_S && (a1 & A_SP)) return false;
+    return true;
+}
+
+// One tile of pre-tokenization.
+template <class Blk>
+GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int tile) {
+    const int n = static_cast<int>(ldg(a.meta));
+    const int t0 = tile * kTile;
+    const int lo = t0 - kHaloL;
+    const uint32_t family = a.tb.family;
+    const int n_chunks = kWin / 16;
+
+    // ---- P0: stage the window ----
+    blk.par([&](int tid) {
+        for (int c = tid; c < n_chunks; c += kThreads) {
+            int p = lo + c * 16;
+            uint32_t* dst = reinterpret_cast<uint32_t*>(sm.txt + c * 16);
+            if (p >= 0 && p < n) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(a.text + p);
+#if defined(__CUDA_ARCH__)
+                uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+                *reinterpret_cast<uint4*>(dst) = v;
+#else
+                for (int k = 0; k < 4; ++k) dst[k] = src[k];
+#endif
+            } else {
+                dst[0] = dst[1] = dst[2] = dst[3] = 0;
+            }
+        }
+        for (int wd = tid; wd < kWin / 32 + 2; wd += kThreads) {
+            int gw = (lo >> 5) + wd;                 // lo is a multiple of 32
+            uint32_t v = 0;
+            if (gw >= 0 && gw * 32 < n) {
+                if (a.docmask) v = ldg(a.docmask + gw);
+                if (gw == 0) v |= 1u;
+            }
+            sm.dsw[wd] = v;
+        }
+    });
+
+    auto sm_is_doc = [&](int p) -> bool {   // p within [lo, lo + kWin + 64)
+        int i = p - lo;
+        return (sm.dsw[i >> 5] >> (i & 31)) & 1u;
+    };
+    auto byte_any = [&](int q) -> uint32_t {
+        int i = q - lo;
+        return (i >= 0 && i < kWin) ? sm.txt[i] : ldg(a.text + q);
+    };
+
+    // ---- P1: per-byte class and flags ----
+    blk.par([&](int tid) {
+        for (int c = tid; c < n_chunks; c += kThreads) {
+            for (int k = 0; k < 16; ++k) {
+                int i = c * 16 + k, p = lo + i;
+                uint8_t v = A_OUT;
+                if (p >= 0 && p < n) v = plain_attr(a, p, n, byte_any, sm_is_doc);
+                sm.attr[i] = v;
+            }
+        }
+    });
+
+    // ---- P2: paint added-token literals ----
+    if (a.tb.added_max_bytes) {
+        blk.par([&](int tid) {
+            for (int c = tid; c < n_chunks; c += kThreads) {
+                for (int k = 0; k < 16; ++k) {
+                    int i = c * 16 + k, p = lo + i;
+                    if (p < 0 || p >= n) continue;
+                    if (ldg(a.tb.trie_root + sm.txt[i]) == kNoToken) continue;
+                    uint32_t id;
+                    uint32_t ml = match_literal(a, p, n, byte_any, &id);
+                    if (!ml) continue;
+                    sm.attr[i] = static_cast<uint8_t>(A_ADDED | (sm.attr[i] & A_DOC));
+                    for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kWin; ++j)
+                        sm.attr[i + j] = static_cast<uint8_t>(A_CONT | (sm.attr[i + j] & A_DOC));
+                }
+            }
+        });
+    }
+
+    Win w;
+    w.sm = &sm; w.a = &a; w.lo = lo; w.n = n;
+    w.vlo = lo < 0 ? 0 : lo + static_cast<int>(a.tb.added_max_bytes);
+    w.vhi = lo + kWin < n ? lo + kWin : n;
+
+    // ---- P3: boundary bits for the tile's own bytes ----
+    blk.par([&](int tid) {
+        uint32_t bnd = 0, add = 0, pend = 0, lead = 0, nlead = 0, nstart = 0;
+        for (int k = 0; k < kPer; ++k) {
+            int i = kHaloL + tid * kPer + k, p = lo + i;
+            if (p >= n) break;
+            uint8_t a0 = sm.attr[i];
+            int cls = a0 & A_CLS;
+            if (cls == A_CONT) { if (a0 & A_DOC) bnd |= 1u << k; continue; }
+            lead |= 1u << k;
+            if (cls == A_ADDED) { bnd |= 1u << k; add |= 1u << k; continue; }
+            bool pending = false, ns = false;
+            bool b = is_boundary(w, p, a0, family, &pending, &ns);
+            if (b) bnd |= 1u << k;
+            if (pending) pend |= 1u << k;
+            if (cls == A_N) { nlead |= 1u << k; if (ns) nstart |= 1u << k; }
+        }
+        sm.bnd16[tid] = static_cast<uint16_t>(bnd);
+        sm.add16[tid] = static_cast<uint16_t>(add);
+        sm.pend16[tid] = static_cast<uint16_t>(pend);
+        sm.lead16[tid] = static_cast<uint16_t>(lead);
+        sm.nlead16[tid] = static_cast<uint16_t>(nlead);
+        sm.nstart16[tid] = static_cast<uint16_t>(nstart);
+    });
+
+    // ---- P4: index of each digit in its run (Llama-3 \p{N}{1,3}) ----
+    if (family == 1) {
+        const uint32_t* leadw = reinterpret_cast<const uint32_t*>(sm.lead16);
+        const uint32_t* nleadw = reinterpret_cast<const uint32_t*>(sm.nlead16);
+        const uint32_t* nstartw = reinterpret_cast<const uint32_t*>(sm.nstart16);
+        // (has, cnt): "a run start was seen" and "digits since the last run start".
+        blk.par([&](int tid) {
+            if (tid >= 32) return;
+            uint32_t has = 0, cnt = 0;
+            for (int k = 0; k < kTileWords / 32; ++k) {
+                int wd = tid * (kTileWords / 32) + k;
+                uint32_t nl = nleadw[wd], st = nstartw[wd];
+                if (st) { has = 1; cnt = popc32(nl & ~((1u << fls32(st)) - 1u)); }
+                else cnt += popc32(nl);
+            }
+            sm.sum_has[tid] = has;
+            sm.sum_cnt[tid] = cnt;
+        });
+        blk.par([&](int tid) {
+            if (tid != 0) return;
+            // Tile summary, published before anything that waits.
+            uint32_t has = 0, cnt = 0, any_lead = 0, last_is_n = 0;
+            for (int l = 0; l < 32; ++l) {
+                if (sm.sum_has[l]) { has = 1; cnt = sm.sum_cnt[l]; } else cnt += sm.sum_cnt[l];
+            }
+            for (int wd = kTileWords - 1; wd >= 0; --wd) {
+                if (leadw[wd]) { any_lead = 1; last_is_n = (nleadw[wd] >> fls32(leadw[wd])) & 1u; break; }
+            }
+            bool pass = !any_lead || (last_is_n && !has);     // the run (if any) is still open and began earlier
+            uint32_t first_needs = 0;                          // first digit of the tile continues an earlier run
+            for (int wd = 0; wd < kTileWords; ++wd) {
+                if (nleadw[wd]) { int b = ffs32(nleadw[wd]); first_needs = !((nstartw[wd] >> b) & 1u); break; }
+            }
+            unsigned long long mine;
+            if (!pass) mine = kStFinal | ((last_is_n && any_lead) ? cnt : 0u);
+            else mine = kStAgg | cnt;
+            if (tile == 0 && pass) mine = kStFinal | cnt;
+            store_state(a.st1 + tile, mine);
+            uint32_t carry_in = 0;
+            if ((pass || first_needs) && tile > 0) {
+                for (int j = tile - 1; j >= 0; --j) {
+                    unsigned long long v = wait_state(a.st1, j, a.ctl);
+                    carry_in += static_cast<uint32_t>(v);
+                    if ((v >> 62) == 2) break;
+                }
+                if (pass) store_state(a.st1 + tile, kStFinal | (carry_in + cnt));
+            }
+            sm.misc[0] = carry_in;
+        });
+        blk.par([&](int tid) {
+            if (tid >= 32) return;
+            // Exclusive (has, cnt) over the 32 lane summaries, seeded with the carry.
+            uint32_t cnt = sm.misc[0];
+            for (int l = 0; l < tid; ++l) { if (sm.sum_has[l]) cnt = sm.sum_cnt[l]; else cnt += sm.sum_cnt[l]; }
+            for (int k = 0; k < kTileWords / 32; ++k) {
+                int wd = tid * (kTileWords / 32) + k;
+                sm.carry[wd] = cnt;
+                uint32_t nl = nleadw[wd], st = nstartw[wd];
+                if (st) cnt = popc32(nl & ~((1u << fls32(st)) - 1u));
+                else cnt += popc32(nl);
+            }
+        });
+        blk.par([&](int tid) {
+            uint32_t pend = sm.pend16[tid];
+            if (!pend) return;
+            int wd = tid >> 1, shift = (tid & 1) * 16;
+            uint32_t nl = nleadw[wd], st = nstartw[wd], bnd = sm.bnd16[tid];
+            while (pend) {
+                int k = ffs32(pend);
+                pend &= pend - 1;
+                int bit = shift + k;
+                uint32_t below = (1u << bit) - 1u;     // bit >= 1 never needed at 0: a pending digit is not the word's first lead... but may be
+                uint32_t idx;
+                uint32_t st_below = st & below;
+                if (st_below) idx = popc32(nl & below & ~((1u << fls32(st_below)) - 1u));
+                else idx = sm.carry[wd] + popc32(nl & below);
+                if (idx % 3u == 0u) bnd |= 1u << k;
+            }
+            sm.bnd16[tid] = static_cast<uint16_t>(bnd);
+        });
+    }
+
+    // ---- P5: write the bit masks, count boundaries ----
+    blk.par([&](int tid) {
+        uint32_t cnt = 0;
+        if (tid < kTileWords) {
+            uint32_t bw = reinterpret_cast<const uint32_t*>(sm.bnd16)[tid];
+            a.bmask[tile * kTileWords + tid] = bw;
+            if (a.tb.added_max_bytes) a.amask[tile * kTileWords + tid] = reinterpret_cast<const uint32_t*>(sm.add16)[tid];
+            cnt = popc32(bw);
+        }
+        sm.scan[tid] = cnt;
+    });
+    uint32_t total = 0;
+    blk.excl_scan(sm.scan, &total);
+    blk.par([&](int tid) { if (tid == 0) a.tile_nb[tile] = total; });
+}
+
+// ==================================================================================
+//                                   MERGE + ASSEMBLY
+// ==================================================================================
+struct MergeSmem {
+    alignas(16) uint8_t txt[kTile + 64];
+    uint32_t bm[kTileWords + 4];
+    uint32_t am[kTileWords + 4];
+    uint32_t tok[kTile + 16];
+    uint16_t miss[kTile];
+    uint32_t team_g[kMaxTeam], team_len[kMaxTeam], team_cnt[kMaxTeam];
+    uint32_t b2i[256];
+    uint32_t scan[kThreads];
+    uint32_t ws[kWsWords];
+    uint32_t red[kThreads + 8];
+    uint32_t ctr[16];
+};
+enum { C_NMISS = 0, C_NTEAM = 1, C_TEAMNEXT = 2, C_NBLOCK = 3, C_BASE = 4, C_TOTAL = 5, C_TMP = 6, C_TMP2 = 7 };
+
+// Greedy BPE of one short pre-token by a single thread; symbols, ranks and
+// results live in shared-memory rows laid out [slot][row] so that threads
+// working on the same slot hit different banks.
+GTOK_DEV uint32_t bpe_thread(const EncodeArgs& a, const uint32_t* b2i, const uint8_t* bytes, uint32_t len,
+                             uint32_t* ws, int row, uint32_t* out) {
+    uint32_t* ids = ws + row;
+    uint32_t* rk = ws + kRows * kThreadWordMax + row;
+    uint32_t* nw = ws + 2 * kRows * kThreadWordMax + row;
+    uint32_t m = len;
+    for (uint32_t i = 0; i < m; ++i) ids[i * kRows] = b2i[bytes[i]];
+    for (uint32_t i = 0; i + 1 < m; ++i) {
+        RankRes r = probe_rule(a.tb, ids[i * kRows], ids[(i + 1) * kRows]);
+        rk[i * kRows] = r.rank;
+        nw[i * kRows] = r.res;
+    }
+    while (m > 1) {
+        uint32_t best = kNoRank, bi = 0;
+        for (uint32_t i = 0; i + 1 < m; ++i) {
+            uint32_t r = rk[i * kRows];
+            if (r < best) { best = r; bi = i; }
+        }
+        if (best == kNoRank) break;
+        ids[bi * kRows] = nw[bi * kRows];
+        for (uint32_t i = bi + 1; i + 1 < m; ++i) {
+            ids[i * kRows] = ids[(i + 1) * kRows];
+            rk[i * kRows] = rk[(i + 1) * kRows];
+            nw[i * kRows] = nw[(i + 1) * kRows];
+        }
+        --m;
+        if (bi + 1 < m) {
+            RankRes r = probe_rule(a.tb, ids[bi * kRows], ids[(bi + 1) * kRows]);
+            rk[bi * kRows] = r.rank; nw[bi * kRows] = r.res;
+        } else rk[bi * kRows] = kNoRank;
+        if (bi > 0) {
+            RankRes r = probe_rule(a.tb, ids[(bi - 1) * kRows], ids[bi * kRows]);
+            rk[(bi - 1) * kRows] = r.rank; nw[(bi - 1) * kRows] = r.res;
+        }
+    }
+    for (uint32_t i = 0; i < m; ++i) out[i] = ids[i * kRows];
+    return m;
+}
+
+// Team (warp or whole block) BPE over arrays ids/rk/nw of n symbols, which may live
+// in shared or global memory.  `Team` supplies:
+//     kSize, par(f), excl_scan(arr[kSize], &total), reduce_min(arr[kSize]) -> value
+//     keep(lane, k)   three words per lane that survive from one par() to the next
+// and `scratch` is shared memory of at least 3*kSize + 16 words owned by the team.
+//
+// For vocabularies whose rule ranks are monotone (a rule's operands are made by
+// earlier rules only) all pairs of the current lowest rank are merged in one
+// round: a merge can then only create pairs of higher rank, so the set of
+// lowest-rank pairs is fixed for the round, and the only interaction among them
+// is inside a stretch of overlapping equal pairs (x x x x ...), where the greedy
+// left-to-right order takes every other pair starting from the left.
+// Otherwise one merge is applied per round, exactly as the scalar loop would.
+template <class Team>
+GTOK_DEV uint32_t team_bpe(Team& tm, const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint32_t n, uint32_t* scratch) {
+    constexpr int T = Team::kSize;
+    uint32_t* s_a = scratch;            // [T]
+    uint32_t* s_b = scratch + T;        // [T]
+    uint32_t* s_c = scratch + 2 * T;    // [T]
+    uint32_t* s_m = scratch + 3 * T;    // [T / 32 + 1]
+    tm.par([&](int lane) {
+        for (uint32_t i = lane; i < n; i += T) {
+            if (i + 1 < n) { RankRes r = probe_rule(a.tb, ids[i], ids[i + 1]); rk[i] = r.rank; nw[i] = r.res; }
+            else { rk[i] = kNoRank; nw[i] = 0; }
+        }
+    });
+    for (;;) {
+        if (n < 2) break;
+        tm.par([&](int lane) {
+            uint32_t best = kNoRank;
+            for (uint32_t i = lane; i < n; i += T) { uint32_t r = rk[i]; if (r < best) best = r; }
+            s_a[lane] = best;
+        });
+        const uint32_t m = tm.reduce_min(s_a);
+        if (m == kNoRank) break;
+        if (!a.tb.monotone) {
+            // One merge, by lane 0: the leftmost pair of rank m.
+            tm.par([&](int lane) {
+                if (lane != 0) return;
+                uint32_t bi = 0;
+                while (rk[bi] != m) ++bi;
+                ids[bi] = nw[bi];
+                for (uint32_t i = bi + 1; i + 1 < n; ++i) { ids[i] = ids[i + 1]; rk[i] = rk[i + 1]; nw[i] = nw[i + 1]; }
+                uint32_t nn = n - 1;
+                rk[nn - 1] = kNoRank;
+                if (bi + 1 < nn) { RankRes r = probe_rule(a.tb, ids[bi], ids[bi + 1]); rk[bi] = r.rank; nw[bi] = r.res; }
+                else rk[bi] = kNoRank;
+                if (bi > 0) { RankRes r = probe_rule(a.tb, ids[bi - 1], ids[bi]); rk[bi - 1] = r.rank; nw[bi - 1] = r.res; }
+            });
+            --n;
+            continue;
+        }
+        // ---- one round: merge every selected pair of rank m, compacting in place ----
+        uint32_t out_base = 0;      // symbols written so far
+        uint32_t carry_run = 0;     // length of the stretch of rank-m pairs ending just before this chunk
+        uint32_t prev_sel = 0;      // was the last element of the previous chunk a selected pair
+        for (uint32_t base = 0; base < n; base += T) {
+            // (a) flags
+            tm.par([&](int lane) {
+                uint32_t e = base + lane;
+                s_a[lane] = (e < n && rk[e] == m) ? 1u : 0u;
+            });
+            // (b) stretch position within the lane's group of 32
+            tm.par([&](int lane) {
+                int g0 = lane & ~31;
+                uint32_t k = 0;
+                int j = lane - 1;
+                while (j >= g0 && s_a[j]) { ++k; --j; }
+                s_b[lane] = k | (j < g0 ? 0x80000000u : 0u);    // high bit: the stretch reaches the group start
+            });
+            // (c) carry across groups of 32 (one thread; T/32 groups)
+            tm.par([&](int lane) {
+                if (lane != 0) return;
+                uint32_t run = carry_run;
+                for (int g = 0; g < T / 32; ++g) {
+                    s_m[g] = run;
+                    uint32_t last = s_b[g * 32 + 31];
+                    uint32_t trail = s_a[g * 32 + 31] ? (last & 0x7FFFFFFFu) + 1u : 0u;
+                    bool all = s_a[g * 32 + 31] && (last & 0x80000000u);   // 32 flags set
+                    run = all ? run + 32u : trail;
+                }
+                s_m[T / 32] = run;
+            });
+            // (d) selection, survival, and the values to move
+            uint32_t alive_total = 0;
+            tm.par([&](int lane) {
+                uint32_t kb = s_b[lane];
+                uint32_t k = (kb & 0x7FFFFFFFu) + ((kb & 0x80000000u) ? s_m[lane >> 5] : 0u);
+                uint32_t sel = (s_a[lane] && !(k & 1u)) ? 1u : 0u;
+                s_c[lane] = sel;
+            });
+            tm.par([&](int lane) {
+                uint32_t e = base + lane;
+                uint32_t dead = lane ? s_c[lane - 1] : prev_sel;
+                s_b[lane] = (e < n && !dead) ? 1u : 0u;        // alive
+            });
+            // values must be read before anything is overwritten
+            tm.par([&](int lane) {
+                uint32_t e = base + lane;
+                if (e < n && s_b[lane]) {
+                    uint32_t sel = s_c[lane];
+                    tm.keep(lane, 0) = sel ? nw[e] : ids[e];
+                    tm.keep(lane, 1) = sel ? kDirty : rk[e];
+                    tm.keep(lane, 2) = nw[e];
+                }
+            });
+            const uint32_t last_sel = s_c[T - 1];
+            const uint32_t run_out = s_m[T / 32];
+            // s_a is free now: reuse it for the scan of alive flags
+            tm.par([&](int lane) { s_a[lane] = s_b[lane]; });
+            tm.excl_scan(s_a, &alive_total);
+            tm.par([&](int lane) {
+                if (s_b[lane]) {
+                    uint32_t d = out_base + s_a[lane];
+                    ids[d] = tm.keep(lane, 0);
+                    rk[d] = tm.keep(lane, 1);
+                    nw[d] = tm.keep(lane, 2);
+                }
+            });
+            out_base += alive_total;
+            carry_run = run_out;
+            prev_sel = last_sel;
+        }
+        n = out_base;
+        // ---- re-probe the pairs next to a merge ----
+        tm.par([&](int lane) {
+            for (uint32_t p = lane; p < n; p += T) {
+                bool d0 = rk[p] == kDirty, d1 = p + 1 < n && rk[p + 1] == kDirty;
+                if (d0 || d1) nw[p] = kReprobe;
+            }
+        });
+        tm.par([&](int lane) {
+            for (uint32_t p = lane; p < n; p += T) {
+                if (nw[p] != kReprobe) continue;
+                if (p + 1 < n) { RankRes r = probe_rule(a.tb, ids[p], ids[p + 1]); rk[p] = r.rank; nw[p] = r.res; }
+                else { rk[p] = kNoRank; nw[p] = 0; }
+            }
+        });
+    }
+    return n;
+}
+
+// End (exclusive, global byte position) of the pre-token starting at g, found by
+// scanning the boundary bits; tiles without any boundary are skipped in one step.
+GTOK_DEV uint32_t find_word_end(const EncodeArgs& a, uint32_t g, uint32_t n) {
+    uint32_t wi = g >> 5;
+    uint32_t n_words = ((n + kTile - 1) / kTile) * kTileWords;
+    uint32_t bits = ldg(a.bmask + wi) & ~((2u << (g & 31)) - 1u);
+    if ((g & 31) == 31) bits = 0;
+    for (;;) {
+        if (bits) { uint32_t e = wi * 32 + ffs32(bits); return e < n ? e : n; }
+        ++wi;
+        if (wi >= n_words) return n;
+        if ((wi % kTileWords) == 0) {
+            while (wi < n_words && ldg(a.tile_nb + wi / kTileWords) == 0) wi += kTileWords;
+            if (wi >= n_words) return n;
+        }
+        bits = ldg(a.bmask + wi);
+    }
+}
+
+template <class Blk>
+struct BlockTeam {
+    static constexpr int kSize = kThreads;
+    Blk& blk;
+    uint32_t* keepbuf;   // [3 * kThreads] in shared memory
+    GTOK_DEV BlockTeam(Blk& b, uint32_t* kb) : blk(b), keepbuf(kb) {}
+    template <class F> GTOK_DEV void par(F f) { blk.par(f); }
+    GTOK_DEV void excl_scan(uint32_t* arr, uint32_t* total) { blk.excl_scan(arr, total); }
+    GTOK_DEV uint32_t reduce_min(uint32_t* arr) { return blk.reduce_min(arr); }
+    GTOK_DEV uint32_t& keep(int lane, int k) { return keepbuf[k * kThreads + lane]; }
+};
+
+// One tile of merging and output assembly.
+template <class Blk>
+GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile) {
+    const uint32_t n = ldg(a.meta);
+    const uint32_t n_docs = ldg(a.meta + 1);
+    const uint32_t t0 = static_cast<uint32_t>(tile) * kTile;
+    const uint32_t n_tiles = (n + kTile - 1) / kTile;
+    const uint32_t n_words = n_tiles * kTileWords;
+    const DeviceTables& tb = a.tb;
+
+    // ---- Q0: stage text, bit masks, byte ids ----
+    blk.par([&](int tid) {
+        for (int c = tid; c < (kTile + 64) / 16; c += kThreads) {
+            uint32_t p = t0 + c * 16;
+            uint32_t* dst = reinterpret_cast<uint32_t*>(sm.txt + c * 16);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(a.text + p);
+#if defined(__CUDA_ARCH__)
+            *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+#else
+            for (int k = 0; k < 4; ++k) dst[k] = src[k];
+#endif
+        }
+        for (int wd = tid; wd < kTileWords + 4; wd += kThreads) {
+            uint32_t gw = tile * kTileWords + wd;
+            sm.bm[wd] = gw < n_words ? ldg(a.bmask + gw) : 0u;
+            sm.am[wd] = (tb.added_max_bytes && gw < n_words) ? ldg(a.amask + gw) : 0u;
+        }
+        sm.b2i[tid] = ldg(tb.byte_to_id + tid);
+        for (int i = tid; i < kTile + 16; i += kThreads) sm.tok[i] = kInvalidTok;
+        if (tid < 16) sm.ctr[tid] = 0;
+    });
+
+    // ---- Q1: every pre-token that starts in this tile ----
+    blk.par([&](int tid) {
+        uint32_t bits = (sm.bm[tid >> 1] >> ((tid & 1) * 16)) & 0xFFFFu;
+        while (bits) {
+            int k = ffs32(bits);
+            bits &= bits - 1;
+            uint32_t o = tid * kPer + k;          // offset in tile
+            uint32_t g = t0 + o;
+            if (g >= n) break;
+            // next boundary within the staged bits (tile + 64 bytes)
+            uint32_t e_off = 0;                   // 0 = not found
+            {
+                uint32_t wi = (o + 1) >> 5;
+                uint32_t bb = (o + 1) & 31 ? sm.bm[wi] & ~((1u << ((o + 1) & 31)) - 1u) : sm.bm[wi];
+                for (;;) {
+                    if (bb) { e_off = wi * 32 + ffs32(bb); break; }
+                    if (++wi >= kTileWords + 2) break;
+                    bb = sm.bm[wi];
+                }
+            }
+            uint32_t len = 0;                     // 0 = longer than the staged window
+            if (e_off) len = e_off - o;
+            if (e_off == 0 && t0 + kTile + 64 >= n) len = n - g;
+            if (len && g + len > n) len = n - g;
+            if ((sm.txt[o] & 0xC0u) == 0x80u) continue;      // stray continuation bytes opening a document
+            if ((sm.am[o >> 5] >> (o & 31)) & 1u) {
+                uint32_t id = 0;
+                auto byte_at = [&](int q) -> uint32_t { return ldg(a.text + q); };
+                match_literal(a, static_cast<int>(g), static_cast<int>(n), byte_at, &id);
+                sm.tok[o] = id;
+                continue;
+            }
+            if (len == 0 || len > kThreadWordMax) {
+                uint32_t slot = shared_add(&sm.ctr[C_NTEAM], 1u);
+                if (slot < kMaxTeam) { sm.team_g[slot] = g; sm.team_len[slot] = len; sm.team_cnt[slot] = 0; sm.tok[o] = kLongRef | slot; }
+                continue;
+            }
+            if (len <= kWordKeyMax) {
+                uint64_t k0 = 0, k1 = 0;
+                for (uint32_t i = 0; i < len && i < 8; ++i) k0 |= static_cast<uint64_t>(sm.txt[o + i]) << (8 * i);
+                for (uint32_t i = 8; i < len; ++i) k1 |= static_cast<uint64_t>(sm.txt[o + i]) << (8 * (i - 8));
+                k1 |= static_cast<uint64_t>(len) << 56;
+                uint32_t id = probe_word(tb, k0, k1);
+                if (id != kNoToken) { sm.tok[o] = id; continue; }
+            } else if (tb.ignore_merges) {
+                uint32_t id = probe_long(tb, a.text, g, len);
+                if (id != kNoToken) { sm.tok[o] = id; continue; }
+            }
+            if (len == 1) { sm.tok[o] = sm.b2i[sm.txt[o]]; continue; }
+            uint32_t slot = shared_add(&sm.ctr[C_NMISS], 1u);
+            sm.miss[slot] = static_cast<uint16_t>(o | ((len - 1) << 12));
+        }
+    });
+
+    // ---- Q2: merge loop for the short pre-tokens the table did not know ----
+    {
+        const uint32_t n_miss = sm.ctr[C_NMISS];
+        for (uint32_t base = 0; base < n_miss; base += kRows) {
+            blk.par([&](int tid) {
+                if (tid >= kRows || base + tid >= n_miss) return;
+                uint32_t mv = sm.miss[base + tid];
+                uint32_t o = mv & 0xFFFu, len = (mv >> 12) + 1u;
+                bpe_thread(a, sm.b2i, sm.txt + o, len, sm.ws, tid, sm.tok + o);
+            });
+        }
+    }
+
+    // ---- Q3: long pre-tokens, one at a time, by the whole block ----
+    {
+        uint32_t n_team = sm.ctr[C_NTEAM];
+        if (n_team > kMaxTeam) n_team = kMaxTeam;
+        for (uint32_t ti = 0; ti < n_team; ++ti) {
+            const uint32_t g = sm.team_g[ti];
+            blk.par([&](int tid) {
+                if (tid != 0) return;
+                uint32_t len = sm.team_len[ti];
+                if (len == 0) len = find_word_end(a, g, n) - g;
+                uint32_t id = kNoToken;
+                if (tb.ignore_merges) id = probe_long(tb, a.text, g, len);
+                sm.ctr[C_TMP] = len;
+                sm.ctr[C_TMP2] = id;
+            });
+            const uint32_t len = sm.ctr[C_TMP];
+            const uint32_t hit = sm.ctr[C_TMP2];
+            if (hit != kNoToken) {
+                blk.par([&](int tid) { if (tid == 0) { a.gstage[g] = hit; sm.team_cnt[ti] = 1; } });
+                continue;
+            }
+            // Workspace: shared memory when the pre-token fits beside the team's own
+            // scratch, else the per-byte global arrays (disjoint per pre-token).
+            constexpr uint32_t kScratch = 6 * kThreads + 16;                 // team scratch + keep buffer
+            constexpr uint32_t kFit = (kWsWords - kScratch) / 3;
+            uint32_t* scratch = sm.ws;
+            uint32_t* keepbuf = sm.ws + 3 * kThreads + 16;
+            uint32_t *ids, *rk, *nw;
+            if (len <= kFit) { ids = sm.ws + kScratch; rk = ids + kFit; nw = rk + kFit; }
+            else { ids = a.gstage + g; rk = a.gwork_rk + g; nw = a.gwork_nw + g; }
+            blk.par([&](int tid) {
+                for (uint32_t i = tid; i < len; i += kThreads) ids[i] = sm.b2i[ldg(a.text + g + i)];
+            });
+            BlockTeam<Blk> team(blk, keepbuf);
+            uint32_t cnt = team_bpe(team, a, ids, rk, nw, len, scratch);
+            blk.par([&](int tid) {
+                if (ids != a.gstage + g)
+                    for (uint32_t i = tid; i < cnt; i += kThreads) a.gstage[g + i] = ids[i];
+                if (tid == 0) sm.team_cnt[ti] = cnt;
+            });
+        }
+    }
+
+    // ---- Q4: how many tokens does each thread's stretch of tok[] stand for ----
+    blk.par([&](int tid) {
+        uint32_t sum = 0;
+        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? 16 : 0);
+        for (int i = lo; i < hi; ++i) {
+            uint32_t v = sm.tok[i];
+            if (v == kInvalidTok) continue;
+            sum += (v & kLongRef) ? sm.team_cnt[v & ~kLongRef] : 1u;
+        }
+        sm.scan[tid] = sum;
+        sm.red[tid] = sum;    // kept: the scan below overwrites sm.scan
+    });
+    uint32_t total = 0;
+    blk.excl_scan(sm.scan, &total);
+
+    // ---- Q5: tile base by decoupled look-back ----
+    blk.par([&](int tid) {
+        if (tid != 0) return;
+        unsigned long long mine = (tile == 0 ? kStFinal : kStAgg) | total;
+        store_state(a.st2 + tile, mine);
+        uint32_t base = 0;
+        for (int j = tile - 1; j >= 0; --j) {
+            unsigned long long v = wait_state(a.st2, j, a.ctl);
+            base += static_cast<uint32_t>(v);
+            if ((v >> 62) == 2) break;
+        }
+        if (tile > 0) store_state(a.st2 + tile, kStFinal | (base + total));
+        sm.ctr[C_BASE] = base;
+    });
+    const uint32_t base = sm.ctr[C_BASE];
+
+    // ---- Q6: tokens to their final place ----
+    blk.par([&](int tid) {
+        uint32_t at = base + sm.scan[tid];
+        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? 16 : 0);
+        for (int i = lo; i < hi; ++i) {
+            uint32_t v = sm.tok[i];
+            if (v == kInvalidTok) continue;
+            if (v & kLongRef) { uint32_t ti = v & ~kLongRef; sm.team_len[ti] = at; at += sm.team_cnt[ti]; continue; }
+            if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + 2, kErrOutputFull);
+            ++at;
+        }
+    });
+    {
+        uint32_t n_team = sm.ctr[C_NTEAM];
+        if (n_team > kMaxTeam) n_team = kMaxTeam;
+        if (n_team) {
+            blk.par([&](int tid) {
+                for (uint32_t ti = 0; ti < n_team; ++ti) {
+                    uint32_t g = sm.team_g[ti], cnt = sm.team_cnt[ti], at = sm.team_len[ti];
+                    for (uint32_t i = tid; i < cnt; i += kThreads) {
+                        if (at + i < a.out_cap) a.out_tokens[at + i] = a.gstage[g + i];
+                        else { global_or(a.ctl + 2, kErrOutputFull); break; }
+                    }
+                }
+            });
+        }
+    }
+
+    // ---- Q7: per-document token offsets; totals ----
+    if (a.out_doc_tok) {
+        blk.par([&](int tid) {
+            // documents whose first byte lies in this tile
+            uint32_t lo = 0, hi = n_docs + 1;
+            while (lo < hi) { uint32_t mid = (lo + hi) >> 1; if (ldg(a.doc_off + mid) < t0) lo = mid + 1; else hi = mid; }
+            uint32_t t1 = t0 + kTile;
+            for (uint32_t d = lo + tid; d <= n_docs; d += kThreads) {
+                uint32_t off = ldg(a.doc_off + d);
+                if (off >= t1 || off >= n) break;
+                uint32_t o = off - t0, owner = o / kPer;
+                uint32_t cnt = sm.scan[owner];
+                for (uint32_t i = owner * kPer; i < o; ++i) {
+                    uint32_t v = sm.tok[i];
+                    if (v == kInvalidTok) continue;
+                    cnt += (v & kLongRef) ? sm.team_cnt[v & ~kLongRef] : 1u;
+                }
+                a.out_doc_tok[d] = base + cnt;
+            }
+            if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
+                uint32_t lo2 = 0, hi2 = n_docs + 1;
+                while (lo2 < hi2) { uint32_t mid = (lo2 + hi2) >> 1; if (ldg(a.doc_off + mid) < n) lo2 = mid + 1; else hi2 = mid; }
+                for (uint32_t d = lo2 + tid; d <= n_docs; d += kThreads) a.out_doc_tok[d] = base + total;
+            }
+        });
+    }
+    if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
+        blk.par([&](int tid) {
+            if (tid != 0) return;
+            a.status[0] = base + total;
+        });
+    }
+}
+
+}  // namespace gtok

@@ -1,0 +1,392 @@
+// See engine.h.
+#include "engine.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "encode_core.h"
+#include "encode_kernels.h"
+#include "tables_build.h"
+#include "unicode_class_table.h"
+
+namespace gtok {
+
+namespace {
+
+// Every CUDA call is checked; a failure becomes a message and a false/-1 return,
+// never an abort, so that no error crosses the C ABI as anything but a code.
+#define GTOK_CUDA(call)                                                                        \
+    do {                                                                                       \
+        cudaError_t e_ = (call);                                                               \
+        if (e_ != cudaSuccess) {                                                               \
+            err = std::string(#call) + ": " + cudaGetErrorString(e_);                          \
+            return false;                                                                      \
+        }                                                                                      \
+    } while (0)
+
+template <class T>
+bool upload(const std::vector<T>& v, const T** dst, std::vector<void*>& owned, std::string& err) {
+    void* p = nullptr;
+    size_t bytes = std::max<size_t>(v.size() * sizeof(T), 16);
+    GTOK_CUDA(cudaMalloc(&p, bytes));
+    owned.push_back(p);
+    if (!v.empty()) GTOK_CUDA(cudaMemcpy(p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+    *dst = static_cast<const T*>(p);
+    return true;
+}
+
+constexpr size_t kTextPad = kTile + kWin + 256;
+constexpr uint32_t kHdrWords = 4;     // meta occupies the first 4 words of the header; offsets follow
+
+struct Ctx {
+    uint32_t cap_bytes = 0, cap_docs = 0, n_tiles_cap = 0;
+    bool batch = false;
+    uint8_t* d_text = nullptr;
+    uint32_t* d_hdr = nullptr;
+    uint32_t* d_docmask = nullptr;
+    uint32_t *d_bmask = nullptr, *d_amask = nullptr, *d_tile_nb = nullptr;
+    unsigned char* d_ctrl = nullptr;
+    size_t ctrl_bytes = 0;
+    uint32_t *d_gstage = nullptr, *d_grk = nullptr, *d_gnw = nullptr;
+    uint32_t *d_out = nullptr, *d_doc_tok = nullptr;
+    uint32_t *h_status = nullptr, *d_status = nullptr;
+    uint8_t* h_text = nullptr;
+    uint32_t* h_hdr = nullptr;
+    uint32_t* h_out = nullptr;
+    size_t h_out_words = 0;
+    cudaStream_t stream = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    EncodeArgs args;
+    uint32_t staged_docs = 0, staged_len = 0;
+
+    ~Ctx() {
+        if (exec) cudaGraphExecDestroy(exec);
+        if (graph) cudaGraphDestroy(graph);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+        if (stream) cudaStreamDestroy(stream);
+        cudaFree(d_text); cudaFree(d_hdr); cudaFree(d_docmask); cudaFree(d_bmask); cudaFree(d_amask);
+        cudaFree(d_tile_nb); cudaFree(d_ctrl); cudaFree(d_gstage); cudaFree(d_grk); cudaFree(d_gnw);
+        cudaFree(d_out); cudaFree(d_doc_tok);
+        if (h_status) cudaFreeHost(h_status);
+        if (h_text) cudaFreeHost(h_text);
+        if (h_hdr) cudaFreeHost(h_hdr);
+        if (h_out) cudaFreeHost(h_out);
+    }
+};
+
+}  // namespace
+
+struct Engine::Impl {
+    int device = 0;
+    int sm_count = 0;
+    HostTables ht;
+    DeviceTables dt{};
+    std::vector<void*> owned;
+    std::unique_ptr<Ctx> single, batch;
+    Ctx* staged = nullptr;
+    int pretok_per_sm = 1, merge_per_sm = 1;
+
+    ~Impl() {
+        single.reset();
+        batch.reset();
+        for (void* p : owned) cudaFree(p);
+    }
+
+    bool upload_tables(std::string& err) {
+        std::vector<uint16_t> s1(gtok_uc_stage1_init, gtok_uc_stage1_init + GTOK_UC_STAGE1_LEN);
+        std::vector<uint32_t> s2(gtok_uc_stage2_init, gtok_uc_stage2_init + GTOK_UC_STAGE2_LEN);
+        if (!upload(ht.merge, &dt.merge, owned, err) || !upload(ht.word, &dt.word, owned, err) ||
+            !upload(ht.longtab, &dt.longtab, owned, err) || !upload(ht.long_blob, &dt.long_blob, owned, err) ||
+            !upload(ht.byte_to_id, &dt.byte_to_id, owned, err) || !upload(s1, &dt.uc_stage1, owned, err) ||
+            !upload(s2, &dt.uc_stage2, owned, err) || !upload(ht.trie_root, &dt.trie_root, owned, err) ||
+            !upload(ht.trie_first, &dt.trie_first, owned, err) || !upload(ht.trie_count, &dt.trie_count, owned, err) ||
+            !upload(ht.trie_terminal, &dt.trie_terminal, owned, err) || !upload(ht.trie_edges, &dt.trie_edges, owned, err))
+            return false;
+        dt.merge_mask = static_cast<uint32_t>(ht.merge.size() - 1);
+        dt.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
+        dt.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
+        dt.long_max_len = ht.long_max_len;
+        dt.added_max_bytes = ht.added_max_bytes;
+        dt.family = ht.family;
+        dt.ignore_merges = ht.ignore_merges;
+        dt.monotone = ht.monotone;
+        return true;
+    }
+
+    bool build_ctx(std::unique_ptr<Ctx>& slot, uint32_t cap_bytes, uint32_t cap_docs, bool batch_mode, std::string& err) {
+        std::unique_ptr<Ctx> c(new Ctx());
+        c->cap_bytes = cap_bytes;
+        c->cap_docs = cap_docs;
+        c->batch = batch_mode;
+        c->n_tiles_cap = (cap_bytes + kTile - 1) / kTile + 1;
+        const size_t tile_bytes = static_cast<size_t>(c->n_tiles_cap) * kTile;
+        const size_t mask_words = static_cast<size_t>(c->n_tiles_cap) * kTileWords + 8;
+        const size_t hdr_words = kHdrWords + static_cast<size_t>(cap_docs) + 2;
+        GTOK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        GTOK_CUDA(cudaEventCreate(&c->ev0));
+        GTOK_CUDA(cudaEventCreate(&c->ev1));
+        GTOK_CUDA(cudaMalloc(&c->d_text, tile_bytes + kTextPad));
+        GTOK_CUDA(cudaMemset(c->d_text, 0, tile_bytes + kTextPad));
+        GTOK_CUDA(cudaMalloc(&c->d_hdr, hdr_words * 4));
+        GTOK_CUDA(cudaMemset(c->d_hdr, 0, hdr_words * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_bmask, mask_words * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_amask, mask_words * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_tile_nb, (c->n_tiles_cap + 1) * 4));
+        if (batch_mode) GTOK_CUDA(cudaMalloc(&c->d_docmask, mask_words * 4));
+        c->ctrl_bytes = 64 + static_cast<size_t>(c->n_tiles_cap + 1) * 16;
+        GTOK_CUDA(cudaMalloc(&c->d_ctrl, c->ctrl_bytes));
+        GTOK_CUDA(cudaMemset(c->d_ctrl, 0, c->ctrl_bytes));
+        GTOK_CUDA(cudaMalloc(&c->d_gstage, (tile_bytes + 64) * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_grk, (tile_bytes + 64) * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_gnw, (tile_bytes + 64) * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_out, (static_cast<size_t>(cap_bytes) + 16) * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_doc_tok, (static_cast<size_t>(cap_docs) + 2) * 4));
+        GTOK_CUDA(cudaHostAlloc(&c->h_status, 64, cudaHostAllocMapped));
+        std::memset(c->h_status, 0, 64);
+        GTOK_CUDA(cudaHostGetDevicePointer(&c->d_status, c->h_status, 0));
+        GTOK_CUDA(cudaHostAlloc(&c->h_text, static_cast<size_t>(cap_bytes) + 64, cudaHostAllocDefault));
+        GTOK_CUDA(cudaHostAlloc(&c->h_hdr, hdr_words * 4, cudaHostAllocDefault));
+
+        EncodeArgs& a = c->args;
+        std::memset(&a, 0, sizeof a);
+        a.text = c->d_text;
+        a.meta = c->d_hdr;
+        a.doc_off = batch_mode ? c->d_hdr + kHdrWords : nullptr;
+        a.docmask = batch_mode ? c->d_docmask : nullptr;
+        a.bmask = c->d_bmask;
+        a.amask = c->d_amask;
+        a.tile_nb = c->d_tile_nb;
+        a.ctl = reinterpret_cast<uint32_t*>(c->d_ctrl);
+        a.st1 = reinterpret_cast<unsigned long long*>(c->d_ctrl + 64);
+        a.st2 = a.st1 + (c->n_tiles_cap + 1);
+        a.gstage = c->d_gstage;
+        a.gwork_rk = c->d_grk;
+        a.gwork_nw = c->d_gnw;
+        a.out_tokens = c->d_out;
+        a.out_cap = cap_bytes + 16;
+        a.out_doc_tok = batch_mode ? c->d_doc_tok : nullptr;
+        a.status = c->d_status;
+        a.tb = dt;
+
+        // Capture: control block reset, [document mask], pretok, merge.
+        const int pretok_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * pretok_per_sm));
+        const int merge_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * merge_per_sm));
+        GTOK_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+        cudaMemsetAsync(c->d_ctrl, 0, c->ctrl_bytes, c->stream);
+        if (batch_mode) {
+            cudaMemsetAsync(c->d_docmask, 0, mask_words * 4, c->stream);
+            launch_docmask(a, c->d_docmask, std::max(1, std::min<int>(sm_count, static_cast<int>((cap_docs + 256) / 256))), c->stream);
+        }
+        launch_pretok(a, pretok_blocks, c->stream);
+        launch_merge(a, merge_blocks, c->stream);
+        GTOK_CUDA(cudaStreamEndCapture(c->stream, &c->graph));
+        GTOK_CUDA(cudaGraphInstantiate(&c->exec, c->graph, 0));
+        GTOK_CUDA(cudaGetLastError());
+        slot = std::move(c);
+        return true;
+    }
+
+    // Context able to take `need_bytes` (and `need_docs`); built or rebuilt on demand.
+    Ctx* ctx_for(bool batch_mode, uint32_t need_bytes, uint32_t need_docs, uint32_t cap_hint, std::string& err) {
+        std::unique_ptr<Ctx>& slot = batch_mode ? batch : single;
+        if (slot && slot->cap_bytes >= need_bytes && slot->cap_docs >= need_docs) return slot.get();
+        uint32_t cap = std::max<uint32_t>(std::max<uint32_t>(need_bytes, cap_hint), 4096);
+        if (slot) cap = std::max(cap, slot->cap_bytes);
+        uint32_t docs = 1;
+        if (batch_mode) {
+            docs = slot ? slot->cap_docs : 256;
+            while (docs < need_docs) {
+                if (docs > (0xFFFFFFFFu >> 1)) { err = "document capacity overflow"; return nullptr; }
+                docs <<= 1;
+            }
+        }
+        if (staged == slot.get()) staged = nullptr;
+        std::unique_ptr<Ctx> fresh;
+        if (!build_ctx(fresh, cap, docs, batch_mode, err)) return nullptr;
+        slot = std::move(fresh);
+        return slot.get();
+    }
+
+    bool grow_host_out(Ctx* c, size_t words, std::string& err) {
+        if (c->h_out_words >= words) return true;
+        if (c->h_out) cudaFreeHost(c->h_out);
+        c->h_out = nullptr;
+        c->h_out_words = 0;
+        size_t want = std::max<size_t>(words, 1 << 16);
+        GTOK_CUDA(cudaHostAlloc(&c->h_out, want * 4, cudaHostAllocDefault));
+        c->h_out_words = want;
+        return true;
+    }
+
+    // Host -> pinned -> device, for the text and the header.
+    bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err) {
+        if (len) std::memcpy(c->h_text, bytes, len);
+        c->h_hdr[0] = len;
+        c->h_hdr[1] = n_docs;
+        c->h_hdr[2] = c->h_hdr[3] = 0;
+        size_t hdr_words = kHdrWords;
+        if (doc_off) {
+            std::memcpy(c->h_hdr + kHdrWords, doc_off, (static_cast<size_t>(n_docs) + 1) * 4);
+            hdr_words += static_cast<size_t>(n_docs) + 1;
+        }
+        if (len) GTOK_CUDA(cudaMemcpyAsync(c->d_text, c->h_text, (static_cast<size_t>(len) + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream));
+        GTOK_CUDA(cudaMemcpyAsync(c->d_hdr, c->h_hdr, hdr_words * 4, cudaMemcpyHostToDevice, c->stream));
+        c->staged_len = len;
+        c->staged_docs = n_docs;
+        return true;
+    }
+
+    // One replay; returns the total token count or -1.
+    int64_t replay(Ctx* c, bool timed, float* ms, std::string& err) {
+        c->h_status[0] = 0;
+        c->h_status[1] = 0;
+        if (c->staged_len == 0) { if (ms) *ms = 0.f; return 0; }
+        auto fail = [&](cudaError_t e, const char* what) { err = std::string(what) + ": " + cudaGetErrorString(e); return int64_t(-1); };
+        cudaError_t e;
+        if (timed && (e = cudaEventRecord(c->ev0, c->stream)) != cudaSuccess) return fail(e, "cudaEventRecord");
+        if ((e = cudaGraphLaunch(c->exec, c->stream)) != cudaSuccess) return fail(e, "cudaGraphLaunch");
+        if (timed && (e = cudaEventRecord(c->ev1, c->stream)) != cudaSuccess) return fail(e, "cudaEventRecord");
+        if ((e = cudaStreamSynchronize(c->stream)) != cudaSuccess) return fail(e, "cudaStreamSynchronize");
+        if (timed && ms) cudaEventElapsedTime(ms, c->ev0, c->ev1);
+        uint32_t errs = reinterpret_cast<volatile uint32_t*>(c->h_status)[1];
+        if (errs) {
+            char buf[96];
+            std::snprintf(buf, sizeof buf, "encode kernels reported error bits 0x%x", errs);
+            err = buf;
+            return (errs & kErrOutputFull) ? -2 : -1;
+        }
+        return reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
+    }
+};
+
+Engine::~Engine() = default;
+
+Engine* Engine::create(const std::string& path, std::string& err) {
+    std::unique_ptr<Engine> e(new Engine());
+    if (!load_tokenizer_json(path, e->hv_, err)) return nullptr;
+    e->impl_.reset(new Impl());
+    Impl& im = *e->impl_;
+    if (!build_host_tables(e->hv_, im.ht, err)) return nullptr;
+    int n_dev = 0;
+    cudaError_t ce = cudaGetDeviceCount(&n_dev);
+    if (ce != cudaSuccess || n_dev == 0) {
+        err = std::string("no CUDA device: ") + (ce != cudaSuccess ? cudaGetErrorString(ce) : "device count is 0") +
+              " (this library has no CPU path)";
+        return nullptr;
+    }
+    int dev = 0;
+    if (const char* env = std::getenv("GTOK_DEVICE")) dev = std::atoi(env);
+    else cudaGetDevice(&dev);
+    if (cudaSetDevice(dev) != cudaSuccess) { err = "cudaSetDevice failed"; return nullptr; }
+    im.device = dev;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { err = "cudaGetDeviceProperties failed"; return nullptr; }
+    im.sm_count = prop.multiProcessorCount;
+    if (prop.major < 10) {
+        err = "this build targets sm_100a (B200); found compute capability " + std::to_string(prop.major) + "." + std::to_string(prop.minor);
+        return nullptr;
+    }
+    if (configure_kernels() != cudaSuccess) { err = std::string("kernel configuration failed: ") + cudaGetErrorString(cudaGetLastError()); return nullptr; }
+    im.pretok_per_sm = pretok_blocks_per_sm();
+    im.merge_per_sm = merge_blocks_per_sm();
+    if (!im.upload_tables(err)) return nullptr;
+    return e.release();
+}
+
+void Engine::table_bytes(uint64_t* merge, uint64_t* word, uint64_t* other) const {
+    const HostTables& ht = impl_->ht;
+    *merge = ht.merge.size() * sizeof(MergeSlot);
+    *word = ht.word.size() * sizeof(WordSlot);
+    *other = ht.longtab.size() * sizeof(LongSlot) + ht.long_blob.size() + 1024 + GTOK_UC_STAGE1_LEN * 2 + GTOK_UC_STAGE2_LEN * 4;
+}
+
+int64_t Engine::encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, uint32_t* out, uint32_t max_out, bool out_on_device) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    if (len == 0) return 0;
+    Ctx* c = im.ctx_for(false, len, 1, cap_bytes, last_error_);
+    if (!c) return -1;
+    if (!im.stage_input(c, text, len, nullptr, 1, last_error_)) return -1;
+    int64_t total = im.replay(c, false, nullptr, last_error_);
+    if (total < 0) return total;
+    if (static_cast<uint64_t>(total) > max_out) return -2;
+    if (total == 0) return 0;
+    cudaError_t e;
+    if (out_on_device) {
+        e = cudaMemcpyAsync(out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    } else {
+        if (!im.grow_host_out(c, static_cast<size_t>(total), last_error_)) return -1;
+        e = cudaMemcpyAsync(c->h_out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToHost, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e == cudaSuccess) std::memcpy(out, c->h_out, static_cast<size_t>(total) * 4);
+    }
+    if (e != cudaSuccess) { last_error_ = std::string("token copy: ") + cudaGetErrorString(e); return -1; }
+    return total;
+}
+
+int64_t Engine::encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes,
+                             uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_tok) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    const uint32_t len = doc_off[n_docs];
+    if (len == 0) { for (uint32_t d = 0; d <= n_docs; ++d) out_doc_tok[d] = 0; return 0; }
+    Ctx* c = im.ctx_for(true, len, n_docs, cap_bytes, last_error_);
+    if (!c) return -4;
+    if (!im.stage_input(c, bytes, len, doc_off, n_docs, last_error_)) return -1;
+    int64_t total = im.replay(c, false, nullptr, last_error_);
+    if (total < 0) return total;
+    if (static_cast<uint64_t>(total) > out_cap) return -2;
+    if (!im.grow_host_out(c, static_cast<size_t>(total) + n_docs + 2, last_error_)) return -1;
+    cudaError_t e = cudaSuccess;
+    if (total) e = cudaMemcpyAsync(c->h_out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(c->h_out + total, c->d_doc_tok, (static_cast<size_t>(n_docs) + 1) * 4, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { last_error_ = std::string("token copy: ") + cudaGetErrorString(e); return -1; }
+    if (total) std::memcpy(out_tokens, c->h_out, static_cast<size_t>(total) * 4);
+    std::memcpy(out_doc_tok, c->h_out + total, (static_cast<size_t>(n_docs) + 1) * 4);
+    return total;
+}
+
+int Engine::stage(const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    const bool batch_mode = doc_off != nullptr;
+    Ctx* c = im.ctx_for(batch_mode, len, batch_mode ? n_docs : 1, cap_bytes, last_error_);
+    if (!c) return -1;
+    if (!im.stage_input(c, bytes, len, doc_off, batch_mode ? n_docs : 1, last_error_)) return -1;
+    if (cudaStreamSynchronize(c->stream) != cudaSuccess) { last_error_ = "stage: stream synchronize failed"; return -1; }
+    im.staged = c;
+    return 0;
+}
+
+int64_t Engine::replay_staged(float* ms_out) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    if (!im.staged) { last_error_ = "nothing staged"; return -1; }
+    return im.replay(im.staged, true, ms_out, last_error_);
+}
+
+int64_t Engine::read_staged(uint32_t* out, uint32_t max_out, uint32_t* out_doc_tok) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    Ctx* c = im.staged;
+    if (!c) { last_error_ = "nothing staged"; return -1; }
+    uint32_t total = reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
+    if (total > max_out) return -2;
+    if (total && cudaMemcpy(out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (out_doc_tok && c->batch &&
+        cudaMemcpy(out_doc_tok, c->d_doc_tok, (static_cast<size_t>(c->staged_docs) + 1) * 4, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return -1;
+    return total;
+}
+
+}  // namespace gtok

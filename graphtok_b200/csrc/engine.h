@@ -1,0 +1,51 @@
+// Host-side engine behind the libgtok C ABI: owns the vocabulary tables in device
+// memory and, per capacity, a context with its workspaces, pinned staging
+// buffers and the captured CUDA graph (memset -> [document mask] -> pretok ->
+// merge).  Plays the role of the reference's TokenizerCtx
+// (src/tokenizer.cuh:132-548, launch_graph_core at src/tokenizer.cu:4654-4773),
+// with work proportional to the input length rather than to the capacity.
+#pragma once
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "vocab_host.h"
+
+namespace gtok {
+
+class Engine {
+public:
+    // Returns nullptr and a reason on failure (bad file, no usable GPU, ...).
+    static Engine* create(const std::string& tokenizer_json, std::string& err);
+    ~Engine();
+
+    // Return codes follow the C ABI: >= 0 token count, -1 error, -2 output too small.
+    // `text` is host memory.  When `out_on_device` the ids are copied device-to-device.
+    int64_t encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, uint32_t* out, uint32_t max_out, bool out_on_device);
+    // Documents are concatenated in `bytes`; `doc_off` has n_docs + 1 ascending offsets.
+    int64_t encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes,
+                         uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_tok);
+
+    // Measurement entry points (the reference's stage_input / launch_graph_sync,
+    // src/tokenizer.cuh:252-279): stage once, then time graph replays alone.
+    int stage(const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes);
+    int64_t replay_staged(float* ms_out);                 // one replay; CUDA-event time of the graph
+    int64_t read_staged(uint32_t* out, uint32_t max_out, uint32_t* out_doc_tok);
+
+    const HostVocab& vocab() const { return hv_; }
+    uint32_t vocab_size() const { return hv_.vocab_size; }
+    std::string last_error() const { return last_error_; }
+    // Number of kernel launches one replay makes (for reporting).
+    int launches_per_replay(bool batch) const { return batch ? 3 : 2; }
+    void table_bytes(uint64_t* merge, uint64_t* word, uint64_t* other) const;
+
+private:
+    Engine() = default;
+    struct Impl;
+    std::unique_ptr<Impl> impl_;
+    HostVocab hv_;
+    std::string last_error_;
+};
+
+}  // namespace gtok

@@ -1,0 +1,180 @@
+// extern "C" boundary of libgtok.so; see include/gtok.h for the contract.
+#include "../../include/gtok.h"
+
+#include <chrono>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "engine.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+struct Handle {
+    std::unique_ptr<gtok::Engine> engine;
+    uint32_t cap_bytes = 4096;
+    std::vector<uint32_t> rebased;     // scratch for batch offsets
+};
+
+struct Dispatcher {
+    Handle handle;
+    std::mutex mu;
+    uint32_t max_batch_bytes = 0, max_batch_docs = 0;
+    uint64_t stats[5] = {0, 0, 0, 0, 0};
+};
+
+bool open_handle(Handle& h, const char* path, uint32_t max_bytes) {
+    if (!path) { g_last_error = "null vocabulary path"; return false; }
+    std::string err;
+    h.engine.reset(gtok::Engine::create(path, err));
+    if (!h.engine) { g_last_error = err; return false; }
+    h.cap_bytes = max_bytes < 4096 ? 4096 : max_bytes;
+    return true;
+}
+
+int32_t do_encode(Handle* h, const uint8_t* text, uint32_t len, uint32_t* out, uint32_t max_out, bool dev) {
+    if (!text && len) return -1;
+    if (len > h->cap_bytes) return -3;
+    int64_t n = h->engine->encode(text, len, h->cap_bytes, out, max_out, dev);
+    if (n < 0) g_last_error = h->engine->last_error();
+    return static_cast<int32_t>(n);
+}
+
+}  // namespace
+
+extern "C" {
+
+void* gtok_create(const char* vocab_json_path, uint32_t max_bytes) {
+    try {
+        std::unique_ptr<Handle> h(new Handle());
+        if (!open_handle(*h, vocab_json_path, max_bytes)) return nullptr;
+        return h.release();
+    } catch (const std::exception& e) { g_last_error = e.what(); return nullptr; } catch (...) { return nullptr; }
+}
+
+int32_t gtok_encode(void* handle, const uint8_t* text, uint32_t len, uint32_t* out, uint32_t max_out) {
+    if (!handle) return -1;
+    try { return do_encode(static_cast<Handle*>(handle), text, len, out, max_out, false); } catch (...) { return -1; }
+}
+
+int32_t gtok_encode_to_device(void* handle, const uint8_t* text, uint32_t len, void* out_dev, uint32_t max_out) {
+    if (!handle || !out_dev) return -1;
+    try { return do_encode(static_cast<Handle*>(handle), text, len, static_cast<uint32_t*>(out_dev), max_out, true); } catch (...) { return -1; }
+}
+
+int32_t gtok_encode_batch(void* handle, const uint8_t* concat_bytes, const uint32_t* doc_byte_offsets, uint32_t n_docs,
+                          uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets) {
+    if (!handle || !concat_bytes || !doc_byte_offsets || !out_tokens || !out_doc_offsets || n_docs == 0) return -1;
+    try {
+        Handle* h = static_cast<Handle*>(handle);
+        for (uint32_t i = 0; i < n_docs; ++i)
+            if (doc_byte_offsets[i + 1] < doc_byte_offsets[i]) return -1;
+        const uint32_t first = doc_byte_offsets[0];
+        const uint64_t total = static_cast<uint64_t>(doc_byte_offsets[n_docs]) - first;
+        if (total > h->cap_bytes) return -3;
+        const uint32_t* offs = doc_byte_offsets;
+        if (first != 0) {
+            h->rebased.resize(static_cast<size_t>(n_docs) + 1);
+            for (uint32_t i = 0; i <= n_docs; ++i) h->rebased[i] = doc_byte_offsets[i] - first;
+            offs = h->rebased.data();
+        }
+        int64_t n = h->engine->encode_batch(concat_bytes + first, offs, n_docs, h->cap_bytes, out_tokens, out_cap, out_doc_offsets);
+        if (n < 0) g_last_error = h->engine->last_error();
+        return static_cast<int32_t>(n);
+    } catch (...) { return -1; }
+}
+
+uint32_t gtok_cpu_max_bytes(void*) { return 0u; }
+void gtok_set_cpu_max_bytes(void*, uint32_t) {}
+const char* gtok_cpu_backend(void*) { return "off"; }
+
+void* gtok_dispatcher_create(const char* vocab_json_path, uint32_t /*cpu_workers*/, uint32_t max_batch_bytes,
+                             uint32_t max_batch_docs, uint32_t policy) {
+    if (!vocab_json_path || policy > 2) return nullptr;
+    try {
+        std::unique_ptr<Dispatcher> d(new Dispatcher());
+        d->max_batch_bytes = max_batch_bytes ? max_batch_bytes : (8u << 20);
+        d->max_batch_docs = max_batch_docs ? max_batch_docs : 256;
+        if (!open_handle(d->handle, vocab_json_path, d->max_batch_bytes)) return nullptr;
+        return d.release();
+    } catch (...) { return nullptr; }
+}
+
+int32_t gtok_dispatch_encode(void* dispatcher, const uint8_t* text, uint32_t len, uint32_t* out, uint32_t max_out) {
+    if (!dispatcher || (!text && len)) return -1;
+    try {
+        Dispatcher* d = static_cast<Dispatcher*>(dispatcher);
+        std::lock_guard<std::mutex> lock(d->mu);
+        if (len > d->handle.cap_bytes) d->handle.cap_bytes = len;    // large requests grow the context
+        const auto t0 = std::chrono::steady_clock::now();
+        int32_t n = do_encode(&d->handle, text, len, out, max_out, false);
+        d->stats[1] += 1;
+        d->stats[2] += 1;
+        if (len > d->max_batch_bytes) d->stats[3] += 1;
+        d->stats[4] += static_cast<uint64_t>(std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count());
+        return n;
+    } catch (...) { return -1; }
+}
+
+void gtok_dispatcher_stats(void* dispatcher, uint64_t* out5) {
+    if (!dispatcher || !out5) return;
+    Dispatcher* d = static_cast<Dispatcher*>(dispatcher);
+    std::lock_guard<std::mutex> lock(d->mu);
+    std::memcpy(out5, d->stats, sizeof d->stats);
+}
+
+void gtok_dispatcher_destroy(void* dispatcher) { delete static_cast<Dispatcher*>(dispatcher); }
+
+uint32_t gtok_vocab_size(void* handle) { return handle ? static_cast<Handle*>(handle)->engine->vocab_size() : 0u; }
+
+void gtok_destroy(void* handle) { delete static_cast<Handle*>(handle); }
+
+const char* gtok_x_last_error(void) { return g_last_error.c_str(); }
+
+uint32_t gtok_x_family(void* handle) {
+    if (!handle) return 0xFFFFFFFFu;
+    const gtok::HostVocab& hv = static_cast<Handle*>(handle)->engine->vocab();
+    return static_cast<uint32_t>(hv.family) | (hv.nfc ? 0x100u : 0u);
+}
+
+int32_t gtok_x_stage(void* handle, const uint8_t* bytes, uint32_t len, const uint32_t* doc_byte_offsets, uint32_t n_docs) {
+    if (!handle || (!bytes && len)) return -1;
+    try {
+        Handle* h = static_cast<Handle*>(handle);
+        if (len > h->cap_bytes) return -3;
+        int r = h->engine->stage(bytes, len, doc_byte_offsets, n_docs, h->cap_bytes);
+        if (r < 0) g_last_error = h->engine->last_error();
+        return r;
+    } catch (...) { return -1; }
+}
+
+int32_t gtok_x_replay(void* handle, float* ms_out) {
+    if (!handle) return -1;
+    try {
+        Handle* h = static_cast<Handle*>(handle);
+        int64_t n = h->engine->replay_staged(ms_out);
+        if (n < 0) g_last_error = h->engine->last_error();
+        return static_cast<int32_t>(n);
+    } catch (...) { return -1; }
+}
+
+int32_t gtok_x_read(void* handle, uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets) {
+    if (!handle) return -1;
+    try { return static_cast<int32_t>(static_cast<Handle*>(handle)->engine->read_staged(out_tokens, out_cap, out_doc_offsets)); } catch (...) { return -1; }
+}
+
+void gtok_x_table_bytes(void* handle, uint64_t* out3) {
+    if (!handle || !out3) return;
+    static_cast<Handle*>(handle)->engine->table_bytes(&out3[0], &out3[1], &out3[2]);
+}
+
+int32_t gtok_x_launches_per_replay(void* handle, int32_t batch) {
+    if (!handle) return -1;
+    return static_cast<Handle*>(handle)->engine->launches_per_replay(batch != 0);
+}
+
+}  // extern "C"

@@ -1,0 +1,193 @@
+// See tables_build.h.
+#include "tables_build.h"
+
+#include <algorithm>
+#include <map>
+#include <unordered_map>
+
+namespace gtok {
+
+namespace {
+
+uint32_t pow2_at_least(uint64_t x) {
+    uint32_t p = 16;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+struct RuleMap {
+    std::unordered_map<uint64_t, uint64_t> m;
+    bool find(uint32_t l, uint32_t r, uint32_t& rank, uint32_t& res) const {
+        auto it = m.find((static_cast<uint64_t>(l) << 32) | r);
+        if (it == m.end()) return false;
+        rank = static_cast<uint32_t>(it->second >> 32);
+        res = static_cast<uint32_t>(it->second);
+        return true;
+    }
+};
+
+// Plain greedy BPE of a short byte string; used once per vocabulary token at
+// load time to decide which tokens may enter the whole-word table.
+bool merges_to_self(const HostVocab& hv, const RuleMap& rules, const std::string& bytes, uint32_t id) {
+    std::vector<uint32_t> sym;
+    for (unsigned char c : bytes) sym.push_back(hv.byte_to_id[c]);
+    for (;;) {
+        uint32_t best = kNoRank, bi = 0, bres = 0;
+        for (size_t i = 0; i + 1 < sym.size(); ++i) {
+            uint32_t rk, res;
+            if (rules.find(sym[i], sym[i + 1], rk, res) && rk < best) { best = rk; bi = static_cast<uint32_t>(i); bres = res; }
+        }
+        if (best == kNoRank) break;
+        sym[bi] = bres;
+        sym.erase(sym.begin() + bi + 1);
+    }
+    return sym.size() == 1 && sym[0] == id;
+}
+
+}  // namespace
+
+bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
+    out.family = static_cast<uint32_t>(hv.family);
+    out.ignore_merges = hv.ignore_merges ? 1u : 0u;
+    out.monotone = hv.monotone ? 1u : 0u;
+    out.byte_to_id.assign(hv.byte_to_id, hv.byte_to_id + 256);
+
+    // ---- merge rules ----------------------------------------------------
+    RuleMap rules;
+    rules.m.reserve(hv.merges.size() * 2);
+    for (uint32_t k = 0; k < hv.merges.size(); ++k) {
+        const MergeRule& m = hv.merges[k];
+        // The first rule for a pair wins; a later duplicate is unreachable in
+        // the reference's table too (src/vocab.cc:745-795).
+        rules.m.emplace((static_cast<uint64_t>(m.left) << 32) | m.right, (static_cast<uint64_t>(k) << 32) | m.result);
+    }
+    for (uint32_t cap = pow2_at_least(static_cast<uint64_t>(hv.merges.size()) * 2);; cap <<= 1) {
+        if (cap > (1u << 30)) { err = "merge table cannot be built within its probe limit"; return false; }
+        out.merge.assign(cap, MergeSlot{kEmptyKey, kEmptyKey, kNoRank, 0});
+        const uint32_t mask = cap - 1;
+        bool ok = true;
+        for (uint32_t k = 0; k < hv.merges.size() && ok; ++k) {
+            const MergeRule& m = hv.merges[k];
+            uint32_t h = merge_hash(m.left, m.right) & mask;
+            int steps = 0;
+            for (;; h = (h + 1) & mask) {
+                MergeSlot& s = out.merge[h];
+                if (s.left == kEmptyKey) { s = MergeSlot{m.left, m.right, k, m.result}; break; }
+                if (s.left == m.left && s.right == m.right) break;   // duplicate pair: keep the first
+                if (++steps >= kProbeLimit - 1) { ok = false; break; }
+            }
+        }
+        if (ok) break;
+    }
+
+    // ---- whole-word table -------------------------------------------------
+    std::vector<std::pair<std::string, uint32_t>> entries;   // (bytes, id)
+    {
+        std::map<std::string, uint32_t> lowest;   // the lowest id wins for a repeated spelling
+        for (uint32_t id = 0; id < hv.token_bytes.size(); ++id) {
+            const std::string& b = hv.token_bytes[id];
+            if (b.empty()) continue;
+            if (!hv.ignore_merges) {
+                if (b.size() > static_cast<size_t>(kWordKeyMax)) continue;
+                if (!merges_to_self(hv, rules, b, id)) continue;
+            }
+            lowest.emplace(b, id);
+        }
+        entries.assign(lowest.begin(), lowest.end());
+    }
+    size_t n_short = 0;
+    for (const auto& e : entries) if (e.first.size() <= static_cast<size_t>(kWordKeyMax)) ++n_short;
+    for (uint32_t cap = pow2_at_least(n_short * 2);; cap <<= 1) {
+        if (cap > (1u << 28)) { err = "word table cannot be built within its probe limit"; return false; }
+        out.word.assign(cap, WordSlot{0, 0, kNoToken, {0, 0, 0}});
+        const uint32_t mask = cap - 1;
+        bool ok = true;
+        for (const auto& e : entries) {
+            if (e.first.size() > static_cast<size_t>(kWordKeyMax)) continue;
+            uint64_t k0, k1;
+            make_word_key(reinterpret_cast<const uint8_t*>(e.first.data()), static_cast<uint32_t>(e.first.size()), k0, k1);
+            uint32_t h = word_hash(k0, k1) & mask;
+            int steps = 0;
+            for (;; h = (h + 1) & mask) {
+                WordSlot& s = out.word[h];
+                if (s.id == kNoToken) { s.k0 = k0; s.k1 = k1; s.id = e.second; break; }
+                if (++steps >= kProbeLimit - 1) { ok = false; break; }
+            }
+            if (!ok) break;
+        }
+        if (ok) break;
+    }
+
+    // ---- long-token table (ignore_merges) ---------------------------------
+    out.longtab.clear();
+    out.long_blob.clear();
+    out.long_max_len = 0;
+    if (hv.ignore_merges) {
+        size_t n_long = entries.size() - n_short;
+        for (uint32_t cap = pow2_at_least(n_long * 2);; cap <<= 1) {
+            if (cap > (1u << 28)) { err = "long-token table cannot be built within its probe limit"; return false; }
+            out.longtab.assign(cap, LongSlot{0, kNoToken, 0, 0, 0});
+            out.long_blob.clear();
+            const uint32_t mask = cap - 1;
+            bool ok = true;
+            for (const auto& e : entries) {
+                if (e.first.size() <= static_cast<size_t>(kWordKeyMax)) continue;
+                uint64_t h = kLongHashSeed;
+                for (unsigned char c : e.first) h = long_hash_step(h, c);
+                h = long_hash_finish(h, static_cast<uint32_t>(e.first.size()));
+                uint32_t at = static_cast<uint32_t>(h) & mask;
+                int steps = 0;
+                for (;; at = (at + 1) & mask) {
+                    LongSlot& s = out.longtab[at];
+                    if (s.id == kNoToken) {
+                        s.hash = h; s.id = e.second; s.off = static_cast<uint32_t>(out.long_blob.size());
+                        s.len = static_cast<uint32_t>(e.first.size());
+                        out.long_blob.insert(out.long_blob.end(), e.first.begin(), e.first.end());
+                        out.long_max_len = std::max(out.long_max_len, s.len);
+                        break;
+                    }
+                    if (++steps >= kProbeLimit - 1) { ok = false; break; }
+                }
+                if (!ok) break;
+            }
+            if (ok) break;
+        }
+    }
+    if (out.long_blob.empty()) out.long_blob.push_back(0);
+    if (out.longtab.empty()) out.longtab.assign(16, LongSlot{0, kNoToken, 0, 0, 0});
+
+    // ---- added-token trie ---------------------------------------------------
+    out.added_max_bytes = hv.added_max_bytes;
+    if (hv.added_max_bytes > kMaxAddedBytes) {
+        err = "an added-token literal is longer than the on-device matcher supports";
+        return false;
+    }
+    struct Node { std::map<uint8_t, uint32_t> next; uint32_t terminal = kNoToken; };
+    std::vector<Node> nodes(1);
+    for (const AddedToken& a : hv.added) {
+        uint32_t at = 0;
+        for (unsigned char c : a.content) {
+            auto it = nodes[at].next.find(c);
+            if (it == nodes[at].next.end()) {
+                uint32_t fresh = static_cast<uint32_t>(nodes.size());
+                nodes[at].next.emplace(c, fresh);
+                nodes.emplace_back();
+                at = fresh;
+            } else at = it->second;
+        }
+        nodes[at].terminal = a.id;
+    }
+    out.trie_root.assign(256, kNoToken);
+    for (const auto& e : nodes[0].next) out.trie_root[e.first] = e.second;
+    out.trie_first.clear(); out.trie_count.clear(); out.trie_terminal.clear(); out.trie_edges.clear();
+    for (const Node& nd : nodes) {
+        out.trie_first.push_back(static_cast<uint32_t>(out.trie_edges.size()));
+        out.trie_count.push_back(static_cast<uint16_t>(nd.next.size()));
+        out.trie_terminal.push_back(nd.terminal);
+        for (const auto& e : nd.next) out.trie_edges.push_back((e.second << 8) | e.first);
+    }
+    if (out.trie_edges.empty()) out.trie_edges.push_back(0);
+    return true;
+}
+
+}  // namespace gtok

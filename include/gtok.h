@@ -1,0 +1,86 @@
+/* libgtok C ABI: text -> token ids for byte-level BPE tokenizers on one B200.
+ *
+ * The first thirteen entry points are the reference's own C ABI
+ * (src/gtok_shim.cc:133-399, exported through src/gtok.map:4-7) with the same
+ * names, argument meaning and return codes, so that its ctypes / dlopen callers
+ * (python/gpu_bpe_tokenizer/vllm.py:87-121, integrations/dynamo) bind unchanged.
+ * The gtok_x_* entry points are additions for measurement and diagnostics.
+ *
+ * Ownership: the caller owns every input and output buffer; a handle owns its
+ * device and pinned memory.  No exception crosses this boundary: failures are
+ * negative return codes (or NULL).  A tokenizer handle is not thread-safe; a
+ * dispatcher handle is.
+ *
+ * This library has no CPU route: gtok_cpu_backend() is always "off" (a state the
+ * reference also has, src/cpu_route.cc:68-74) and every encode runs on the GPU;
+ * creation fails when no sm_100 device is present.
+ */
+#ifndef GTOK_H
+#define GTOK_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* src/gtok_shim.cc:138-155.  Loads an HF tokenizer.json; max_bytes is the largest
+ * input a call may carry (raised to 4096).  GPU contexts are built on first use.
+ * NULL on failure (see gtok_x_last_error). */
+void* gtok_create(const char* vocab_json_path, uint32_t max_bytes);
+
+/* src/gtok_shim.cc:160-202.  Returns the token count, -1 on error, -2 if `out` is too
+ * small, -3 if the (normalised) input exceeds the handle's byte cap. */
+int32_t gtok_encode(void* handle, const uint8_t* text, uint32_t len, uint32_t* out, uint32_t max_out);
+
+/* src/gtok_shim.cc:209-236.  As gtok_encode, ids copied device-to-device into out_dev. */
+int32_t gtok_encode_to_device(void* handle, const uint8_t* text, uint32_t len, void* out_dev, uint32_t max_out);
+
+/* src/gtok_shim.cc:246-318.  n_docs documents concatenated in concat_bytes with
+ * n_docs+1 byte offsets; one graph replay; result equals per-document gtok_encode
+ * concatenated.  out_doc_offsets gets n_docs+1 running token counts.  Returns the
+ * total, -1 error, -2 out_tokens too small, -3 bytes exceed the cap, -4 document
+ * capacity could not grow. */
+int32_t gtok_encode_batch(void* handle, const uint8_t* concat_bytes, const uint32_t* doc_byte_offsets, uint32_t n_docs,
+                          uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets);
+
+/* src/gtok_shim.cc:325-335.  CPU-route controls; the route does not exist here:
+ * the limit reads 0, setting it is accepted and ignored, the backend is "off". */
+uint32_t gtok_cpu_max_bytes(void* handle);
+void gtok_set_cpu_max_bytes(void* handle, uint32_t max_bytes);
+const char* gtok_cpu_backend(void* handle);
+
+/* src/gtok_shim.cc:346-390.  One dispatcher is shared by all request threads;
+ * gtok_dispatch_encode is thread-safe and blocking.  policy: 0 adaptive, 1 GPU,
+ * 2 CPU (accepted; every request still runs on the GPU).  Stats: [cpu_requests,
+ * gpu_requests, gpu_batches, gpu_large, gpu_batch_ns]. */
+void* gtok_dispatcher_create(const char* vocab_json_path, uint32_t cpu_workers, uint32_t max_batch_bytes,
+                             uint32_t max_batch_docs, uint32_t policy);
+int32_t gtok_dispatch_encode(void* dispatcher, const uint8_t* text, uint32_t len, uint32_t* out, uint32_t max_out);
+void gtok_dispatcher_stats(void* dispatcher, uint64_t* out5);
+void gtok_dispatcher_destroy(void* dispatcher);
+
+/* src/gtok_shim.cc:392-399. */
+uint32_t gtok_vocab_size(void* handle);
+void gtok_destroy(void* handle);
+
+/* ---- additions (no counterpart in the reference's C ABI) -------------------- */
+
+/* Last failure message of this thread's most recent failing call ("" if none). */
+const char* gtok_x_last_error(void);
+/* 0 GPT-2, 1 Llama-3, 2 Qwen2.5; bit 8 set when the vocabulary asks for NFC. */
+uint32_t gtok_x_family(void* handle);
+/* Measurement, after the reference's stage_input / launch_graph_sync / read_staged_batch
+ * (src/tokenizer.cuh:252-279): copy the input to the device once, then time graph
+ * replays on their own.  doc_byte_offsets may be NULL for a single document.
+ * gtok_x_replay returns the token count and writes the CUDA-event time of the replay. */
+int32_t gtok_x_stage(void* handle, const uint8_t* bytes, uint32_t len, const uint32_t* doc_byte_offsets, uint32_t n_docs);
+int32_t gtok_x_replay(void* handle, float* ms_out);
+int32_t gtok_x_read(void* handle, uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets);
+/* Sizes in bytes of the merge table, the whole-word table and the remaining tables. */
+void gtok_x_table_bytes(void* handle, uint64_t* out3);
+/* Kernel launches one graph replay performs (single document / batch). */
+int32_t gtok_x_launches_per_replay(void* handle, int32_t batch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,124 @@
+// Serial CPU emulation of the encode kernels' thread blocks, for tests only.
+// The tile programs in graphtok_b200/csrc/encode_core.h are templates over a
+// "block" object; here that object runs the 256 logical threads of a block one
+// after the other (forwards or backwards, so that a dependence on thread order
+// shows up as a difference between the two), and the tiles in order.  This lets
+// the CPU test suite check the kernels' logic against the oracle without a GPU.
+// It is not part of the shipped library and not a fallback: libgtok has no CPU path.
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../graphtok_b200/csrc/encode_core.h"
+#include "../../graphtok_b200/csrc/tables_build.h"
+#include "../../graphtok_b200/csrc/unicode_class_table.h"
+#include "../../graphtok_b200/csrc/vocab_host.h"
+
+namespace {
+
+struct CpuBlk {
+    bool reverse = false;
+    template <class F> void par(F f) {
+        if (!reverse) for (int t = 0; t < gtok::kThreads; ++t) f(t);
+        else for (int t = gtok::kThreads - 1; t >= 0; --t) f(t);
+    }
+    void excl_scan(uint32_t* arr, uint32_t* total) {
+        uint32_t acc = 0;
+        for (int i = 0; i < gtok::kThreads; ++i) { uint32_t v = arr[i]; arr[i] = acc; acc += v; }
+        *total = acc;
+    }
+    uint32_t reduce_min(uint32_t* arr) {
+        uint32_t m = 0xFFFFFFFFu;
+        for (int i = 0; i < gtok::kThreads; ++i) if (arr[i] < m) m = arr[i];
+        return m;
+    }
+};
+
+struct Emul {
+    gtok::HostVocab hv;
+    gtok::HostTables ht;
+    gtok::DeviceTables tb;
+    std::vector<uint16_t> s1;
+    std::vector<uint32_t> s2;
+};
+
+}  // namespace
+
+extern "C" {
+
+void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
+    Emul* e = new Emul();
+    std::string msg;
+    if (!gtok::load_tokenizer_json(path, e->hv, msg) || !gtok::build_host_tables(e->hv, e->ht, msg)) {
+        if (err && err_cap) { std::strncpy(err, msg.c_str(), err_cap - 1); err[err_cap - 1] = 0; }
+        delete e;
+        return nullptr;
+    }
+    e->s1.assign(gtok_uc_stage1_init, gtok_uc_stage1_init + GTOK_UC_STAGE1_LEN);
+    e->s2.assign(gtok_uc_stage2_init, gtok_uc_stage2_init + GTOK_UC_STAGE2_LEN);
+    gtok::DeviceTables& tb = e->tb;
+    const gtok::HostTables& ht = e->ht;
+    tb.merge = ht.merge.data(); tb.merge_mask = static_cast<uint32_t>(ht.merge.size() - 1);
+    tb.word = ht.word.data(); tb.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
+    tb.longtab = ht.longtab.data(); tb.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
+    tb.long_blob = ht.long_blob.data(); tb.long_max_len = ht.long_max_len;
+    tb.byte_to_id = ht.byte_to_id.data();
+    tb.uc_stage1 = e->s1.data(); tb.uc_stage2 = e->s2.data();
+    tb.trie_root = ht.trie_root.data(); tb.trie_first = ht.trie_first.data(); tb.trie_count = ht.trie_count.data();
+    tb.trie_terminal = ht.trie_terminal.data(); tb.trie_edges = ht.trie_edges.data();
+    tb.added_max_bytes = ht.added_max_bytes; tb.family = ht.family; tb.ignore_merges = ht.ignore_merges;
+    tb.monotone = ht.monotone;
+    return e;
+}
+
+void gtok_emul_destroy(void* h) { delete static_cast<Emul*>(h); }
+
+// force_monotone: 0 keep, 1 treat the vocabulary as non-monotone (exercises the one-merge-per-round path)
+// Returns the token count, or -(error bits) when the kernels flagged an error.
+int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_t* doc_off, uint32_t n_docs,
+                         uint32_t* out, uint32_t cap, uint32_t* out_doc_tok, uint32_t* bmask_out, int reverse,
+                         int force_non_monotone) {
+    Emul* e = static_cast<Emul*>(h);
+    using namespace gtok;
+    const uint32_t n_tiles = (n + kTile - 1) / kTile;
+    if (n == 0) { if (out_doc_tok) for (uint32_t d = 0; d <= n_docs; ++d) out_doc_tok[d] = 0; return 0; }
+    std::vector<uint8_t> buf(static_cast<size_t>(n_tiles) * kTile + kTile + kWin + 64, 0xAA);   // junk past n
+    std::memcpy(buf.data(), text, n);
+    uint32_t meta[2] = {n, n_docs};
+    std::vector<uint32_t> docmask, bmask(n_tiles * kTileWords + 8, 0xDEADBEEF), amask(n_tiles * kTileWords + 8, 0xDEADBEEF), tile_nb(n_tiles + 1, 0);
+    std::vector<unsigned long long> st1(n_tiles + 1, 0), st2(n_tiles + 1, 0);
+    uint32_t ctl[4] = {0, 0, 0, 0}, status[4] = {0, 0, 0, 0};
+    std::vector<uint32_t> gstage(static_cast<size_t>(n_tiles) * kTile + 64), grk(gstage.size()), gnw(gstage.size());
+    EncodeArgs a;
+    std::memset(&a, 0, sizeof a);
+    a.text = buf.data(); a.meta = meta;
+    if (doc_off) {
+        docmask.assign(n_tiles * kTileWords + 8, 0);
+        for (uint32_t d = 0; d <= n_docs; ++d) if (doc_off[d] < n) docmask[doc_off[d] >> 5] |= 1u << (doc_off[d] & 31);
+        a.doc_off = doc_off; a.docmask = docmask.data(); a.out_doc_tok = out_doc_tok;
+    }
+    a.bmask = bmask.data(); a.amask = amask.data(); a.tile_nb = tile_nb.data();
+    a.st1 = st1.data(); a.st2 = st2.data(); a.ctl = ctl;
+    a.gstage = gstage.data(); a.gwork_rk = grk.data(); a.gwork_nw = gnw.data();
+    a.out_tokens = out; a.out_cap = cap; a.status = status;
+    a.tb = e->tb;
+    if (force_non_monotone) a.tb.monotone = 0;
+    CpuBlk blk;
+    blk.reverse = reverse != 0;
+    {
+        PretokSmem* sm = new PretokSmem();
+        for (uint32_t t = 0; t < n_tiles; ++t) { std::memset(sm, 0xCD, sizeof *sm); pretok_tile(blk, a, *sm, static_cast<int>(t)); }
+        delete sm;
+    }
+    if (bmask_out) std::memcpy(bmask_out, bmask.data(), static_cast<size_t>(n_tiles) * kTileWords * 4);
+    {
+        MergeSmem* sm = new MergeSmem();
+        for (uint32_t t = 0; t < n_tiles; ++t) { std::memset(sm, 0xCD, sizeof *sm); merge_tile(blk, a, *sm, static_cast<int>(t)); }
+        delete sm;
+    }
+    if (ctl[2]) return -static_cast<int64_t>(ctl[2]);
+    return status[0];
+}
+
+}  // extern "C"
