@@ -1,0 +1,305 @@
+#!/usr/bin/env python3
+"""Benchmark of the encode path (text -> token ids) on 1..8 B200s of one box.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (libgtok, CUDA)
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU encoder on host cores
+
+A step is one encode of the workload document: the Llama-3-shaped configuration
+(seeded synthetic vocabulary of 127,744 merges + 256 special tokens, one ~4.5 MB
+document of ~0.9 M tokens; stands in for the real vocabulary and corpus, which are
+not available offline).  With N > 1 every rank encodes its own document of that
+configuration (weak scaling; documents are independent, the only cross-GPU step
+is an all-gather of the per-rank token counts for the global offsets).
+
+`value` is input MB/s (1e6 bytes) with the text already in device memory, timed
+with CUDA events around each graph replay on the stream that launches it, L2
+flushed between replays; `e2e` is the same through gtok_encode with host buffers
+(pinned H2D, replay, D2H inside the timed region).  One JSON line on stdout.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "encode_throughput_1M_token_doc"
+UNIT = "MB/s"
+WORKLOAD = "config1: Llama-3-shaped BPE (127744 merges, 256 specials), one ~4.5 MB / ~0.9M-token synthetic document"
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(mx))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def workload(rank):
+    """(tokenizer.json path, document bytes) for this rank."""
+    from graphtok_b200 import synth
+    path = synth.vocab_path("cfg1")
+    vocab, tcfg, seed, nbytes = synth.DOCS[1]
+    doc = synth.text(tcfg, seed + 1000 * rank, nbytes)
+    return path, doc
+
+
+def cpu_encoder(path):
+    """The reference's own host encoder when it was built from its sources, else the oracle port."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    if os.path.exists(oracle_lib.REF_SO):
+        return oracle_lib.Reference(path), "reference"
+    return oracle_lib.Oracle(path), "port"
+
+
+def time_cpu(enc, doc, budget_s=12.0, max_reps=8):
+    """Encodes `doc` repeatedly (at least twice) within the budget: returns (best seconds, runs, tokens)."""
+    times, n_tok = [], 0
+    t_all = time.perf_counter()
+    while len(times) < 2 or (time.perf_counter() - t_all < budget_s and len(times) < max_reps):
+        t = time.perf_counter()
+        ids = enc.encode_normalized(doc)
+        times.append(time.perf_counter() - t)
+        n_tok = len(ids)
+    return min(times), len(times), n_tok
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    path, doc = workload(0)
+    enc, kind = cpu_encoder(path)
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        enc.encode_normalized(doc)
+    ts = []
+    n_tok = 0
+    for _ in range(args.steps):
+        t = time.perf_counter()
+        n_tok = len(enc.encode_normalized(doc))
+        ts.append(time.perf_counter() - t)
+    per = float(np.mean(ts))
+    val = len(doc) / per / 1e6
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8/u32 integer", "data": "synthetic", "tokens_per_s": n_tok / per,
+        "config": {"workload": WORKLOAD, "bytes": len(doc), "tokens": n_tok},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": 1, "kind": kind,
+                         "sample": "the whole workload document per step, one host thread (the reference's host encoder is single-threaded per engine)"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="gtok", choices=["gtok", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "gtok" else args.warmup
+
+    rank = env_int("RANK", 0)
+    local_rank = env_int("LOCAL_RANK", 0)
+    world = env_int("WORLD_SIZE", 1)
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the encode path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    os.environ["GTOK_DEVICE"] = str(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from graphtok_b200 import GTok
+    path, doc = workload(rank)
+    g = GTok(path, max_bytes=len(doc) + 4096)
+    n_bytes = len(doc)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput ------------------------------------
+    g.stage(doc)
+    for _ in range(args.warmup):
+        flush.zero_()
+        torch.cuda.synchronize()
+        n_tok, _ = g.replay()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    dev_ms = []
+    wall0 = time.perf_counter()
+    for _ in range(args.steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        n_tok, ms = g.replay()
+        dev_ms.append(ms)
+    barrier()
+    wall = time.perf_counter() - wall0
+    step_ms = float(np.sum(dev_ms)) / args.steps
+
+    # per-kernel times (same kernels launched one by one with events between them)
+    prof = []
+    for _ in range(max(5, min(args.steps, 20))):
+        flush.zero_()
+        torch.cuda.synchronize()
+        prof.append(g.profile()[1:])
+    prof = np.array(prof)
+    pretok_ms, merge_ms = float(np.mean(prof[:, 0])), float(np.mean(prof[:, 1]))
+
+    # ---- end to end through the C ABI ------------------------------------
+    for _ in range(3):
+        ids = g.encode(doc)
+    out = np.empty(n_bytes + 16, dtype=np.uint32)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        n_e2e = g.lib.gtok_encode(g.handle, doc, n_bytes, out.ctypes.data, out.size)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    clocks = sampler.stop()
+
+    # ---- reduce over ranks ---------------------------------------------------
+    stats = torch.tensor([step_ms, e2e_s * 1e3, float(n_bytes), float(n_tok), pretok_ms, merge_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        # the path's one exchange step: per-rank token counts -> global offsets
+        counts = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([n_tok], dtype=torch.int64, device="cuda"))
+        offsets = np.concatenate([[0], np.cumsum([int(c.item()) for c in counts])])
+        step_ms, e2e_ms = float(mx[0]), float(mx[1])
+        tot_bytes, tot_tok = float(sm[2]), float(sm[3])
+        pretok_ms, merge_ms = float(mx[4]), float(mx[5])
+    else:
+        e2e_ms = e2e_s * 1e3
+        tot_bytes, tot_tok = float(n_bytes), float(n_tok)
+        offsets = np.array([0, n_tok])
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        tm, tw, to = g.table_bytes()
+        # Algorithmic bytes of the dominant (merge) kernel per launch: the text, its
+        # boundary bits, the ids written, and the tables it probes (merge + whole-word + rest).
+        algo = n_bytes + n_bytes / 8.0 + 4.0 * n_tok + tm + tw + to
+        achieved = algo / (merge_ms * 1e-3) / 1e9
+        whole = (n_bytes + 4.0 * n_tok + tm + tw + to) / (step_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": tot_bytes / (step_ms * 1e-3) / 1e6, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8/u32 integer", "data": "synthetic",
+            "tokens_per_s": tot_tok / (step_ms * 1e-3),
+            "config": {"workload": WORKLOAD, "bytes_per_gpu": n_bytes, "tokens_per_gpu": int(n_tok), "l2": "flushed between steps (256 MB write)",
+                       "parallelism": "documents sharded across ranks; all_gather of token counts only"},
+            "e2e": {"value": tot_bytes / (e2e_ms * 1e-3) / 1e6, "unit": UNIT, "h2d_bytes_per_step": n_bytes + 16, "d2h_bytes_per_step": int(4 * n_tok + 8),
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": 2 * args.steps * world,
+            "kernels_ms": {"pretok_kernel": pretok_ms, "merge_kernel": merge_ms},
+            "roofline": {"bound": "hbm", "kernel": "merge_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_kind, "traffic": None, "algorithmic_bytes": algo,
+                         "whole_replay": {"achieved": whole, "frac": whole / peak}},
+            "clocks": clocks,
+            "wall_s_timed_region": wall,
+            "global_token_offsets": [int(x) for x in offsets],
+        }
+        # CPU baseline on this box's host cores (reported, not a target).
+        try:
+            enc, kind = cpu_encoder(path)
+            best, runs, cpu_tok = time_cpu(enc, doc)
+            line["cpu_baseline"] = {"value": n_bytes / best / 1e6, "unit": UNIT, "cores": 1, "kind": kind,
+                                    "sample": "whole workload document, best of %d runs, one host thread" % runs, "tokens_match": bool(cpu_tok == n_tok)}
+        except Exception as e:   # the baseline is a report, never a reason to lose the GPU number
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "unavailable", "sample": str(e)[:200]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

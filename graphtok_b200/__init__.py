@@ -16,6 +16,15 @@ LIB_PATH = os.path.join(_HERE, "lib", "libgtok.so")
 _lib = None
 
 
+def plan_documents(offsets, n_parts):
+    """Contiguous document ranges of about equal bytes: n_parts + 1 document indices."""
+    offsets = np.ascontiguousarray(offsets, dtype=np.uint32)
+    out = np.zeros(n_parts + 1, dtype=np.uint32)
+    if load_lib().gtok_x_plan_documents(offsets.ctypes.data, offsets.size - 1, n_parts, out.ctypes.data) != 0:
+        raise RuntimeError("gtok_x_plan_documents failed")
+    return out
+
+
 def load_lib():
     """ctypes handle on libgtok.so with argument/return types declared."""
     global _lib
@@ -61,6 +70,12 @@ def load_lib():
     lib.gtok_x_replay.argtypes = [vp, vp]
     lib.gtok_x_read.restype = i32
     lib.gtok_x_read.argtypes = [vp, vp, u32, vp]
+    lib.gtok_x_profile.restype = i32
+    lib.gtok_x_profile.argtypes = [vp, vp]
+    lib.gtok_x_plan_chunks.restype = i32
+    lib.gtok_x_plan_chunks.argtypes = [vp, vp, ctypes.c_uint64, u32, vp]
+    lib.gtok_x_plan_documents.restype = i32
+    lib.gtok_x_plan_documents.argtypes = [vp, u32, u32, vp]
     lib.gtok_x_table_bytes.restype = None
     lib.gtok_x_table_bytes.argtypes = [vp, vp]
     lib.gtok_x_launches_per_replay.restype = i32
@@ -144,6 +159,21 @@ class GTok:
         if n < 0:
             self._fail("gtok_x_read", n)
         return out[:n].copy(), (doc if n_docs else None)
+
+    def profile(self):
+        """Staged input, kernel by kernel: (tokens, pretok ms, merge ms, sequence ms)."""
+        ms = (ctypes.c_float * 3)()
+        n = self.lib.gtok_x_profile(self.handle, ms)
+        if n < 0:
+            self._fail("gtok_x_profile", n)
+        return n, ms[0], ms[1], ms[2]
+
+    def plan_chunks(self, data, n_parts):
+        data = bytes(data)
+        out = np.zeros(n_parts + 1, dtype=np.uint64)
+        if self.lib.gtok_x_plan_chunks(self.handle, data, len(data), n_parts, out.ctypes.data) != 0:
+            raise GTokError("gtok_x_plan_chunks failed")
+        return out
 
     def table_bytes(self):
         t = (ctypes.c_uint64 * 3)()

@@ -61,7 +61,9 @@ struct Ctx {
     cudaStream_t stream = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr, ev3 = nullptr;
+    int pretok_blocks = 1, merge_blocks = 1, docmask_blocks = 1;
+    size_t mask_words = 0;
     EncodeArgs args;
     uint32_t staged_docs = 0, staged_len = 0;
 
@@ -70,6 +72,8 @@ struct Ctx {
         if (graph) cudaGraphDestroy(graph);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
+        if (ev2) cudaEventDestroy(ev2);
+        if (ev3) cudaEventDestroy(ev3);
         if (stream) cudaStreamDestroy(stream);
         cudaFree(d_text); cudaFree(d_hdr); cudaFree(d_docmask); cudaFree(d_bmask); cudaFree(d_amask);
         cudaFree(d_tile_nb); cudaFree(d_ctrl); cudaFree(d_gstage); cudaFree(d_grk); cudaFree(d_gnw);
@@ -132,6 +136,8 @@ struct Engine::Impl {
         GTOK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
         GTOK_CUDA(cudaEventCreate(&c->ev0));
         GTOK_CUDA(cudaEventCreate(&c->ev1));
+        GTOK_CUDA(cudaEventCreate(&c->ev2));
+        GTOK_CUDA(cudaEventCreate(&c->ev3));
         GTOK_CUDA(cudaMalloc(&c->d_text, tile_bytes + kTextPad));
         GTOK_CUDA(cudaMemset(c->d_text, 0, tile_bytes + kTextPad));
         GTOK_CUDA(cudaMalloc(&c->d_hdr, hdr_words * 4));
@@ -178,11 +184,15 @@ struct Engine::Impl {
         // Capture: control block reset, [document mask], pretok, merge.
         const int pretok_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * pretok_per_sm));
         const int merge_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * merge_per_sm));
+        c->pretok_blocks = pretok_blocks;
+        c->merge_blocks = merge_blocks;
+        c->docmask_blocks = std::max(1, std::min<int>(sm_count, static_cast<int>((cap_docs + 256) / 256)));
+        c->mask_words = mask_words;
         GTOK_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
         cudaMemsetAsync(c->d_ctrl, 0, c->ctrl_bytes, c->stream);
         if (batch_mode) {
             cudaMemsetAsync(c->d_docmask, 0, mask_words * 4, c->stream);
-            launch_docmask(a, c->d_docmask, std::max(1, std::min<int>(sm_count, static_cast<int>((cap_docs + 256) / 256))), c->stream);
+            launch_docmask(a, c->d_docmask, c->docmask_blocks, c->stream);
         }
         launch_pretok(a, pretok_blocks, c->stream);
         launch_merge(a, merge_blocks, c->stream);
@@ -373,6 +383,35 @@ int64_t Engine::replay_staged(float* ms_out) {
     cudaSetDevice(im.device);
     if (!im.staged) { last_error_ = "nothing staged"; return -1; }
     return im.replay(im.staged, true, ms_out, last_error_);
+}
+
+int64_t Engine::profile_staged(float* ms_out) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    Ctx* c = im.staged;
+    if (!c) { last_error_ = "nothing staged"; return -1; }
+    c->h_status[0] = 0;
+    c->h_status[1] = 0;
+    ms_out[0] = ms_out[1] = ms_out[2] = 0.f;
+    if (c->staged_len == 0) return 0;
+    cudaEventRecord(c->ev0, c->stream);
+    cudaMemsetAsync(c->d_ctrl, 0, c->ctrl_bytes, c->stream);
+    if (c->batch) {
+        cudaMemsetAsync(c->d_docmask, 0, c->mask_words * 4, c->stream);
+        launch_docmask(c->args, c->d_docmask, c->docmask_blocks, c->stream);
+    }
+    cudaEventRecord(c->ev1, c->stream);
+    launch_pretok(c->args, c->pretok_blocks, c->stream);
+    cudaEventRecord(c->ev2, c->stream);
+    launch_merge(c->args, c->merge_blocks, c->stream);
+    cudaEventRecord(c->ev3, c->stream);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { last_error_ = std::string("profile: ") + cudaGetErrorString(e); return -1; }
+    cudaEventElapsedTime(&ms_out[0], c->ev1, c->ev2);
+    cudaEventElapsedTime(&ms_out[1], c->ev2, c->ev3);
+    cudaEventElapsedTime(&ms_out[2], c->ev0, c->ev3);
+    if (reinterpret_cast<volatile uint32_t*>(c->h_status)[1]) { last_error_ = "encode kernels reported an error"; return -1; }
+    return reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
 }
 
 int64_t Engine::read_staged(uint32_t* out, uint32_t max_out, uint32_t* out_doc_tok) {

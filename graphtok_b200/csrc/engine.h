@@ -32,6 +32,9 @@ public:
     int stage(const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes);
     int64_t replay_staged(float* ms_out);                 // one replay; CUDA-event time of the graph
     int64_t read_staged(uint32_t* out, uint32_t max_out, uint32_t* out_doc_tok);
+    // Same work as one replay, launched kernel by kernel with an event between them:
+    // ms_out[0] = pretok kernel, ms_out[1] = merge kernel, ms_out[2] = whole sequence.
+    int64_t profile_staged(float* ms_out);
 
     const HostVocab& vocab() const { return hv_; }
     uint32_t vocab_size() const { return hv_.vocab_size; }

@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "engine.h"
+#include "shard_plan.h"
 
 namespace {
 
@@ -162,6 +163,16 @@ int32_t gtok_x_replay(void* handle, float* ms_out) {
     } catch (...) { return -1; }
 }
 
+int32_t gtok_x_profile(void* handle, float* ms_out3) {
+    if (!handle || !ms_out3) return -1;
+    try {
+        Handle* h = static_cast<Handle*>(handle);
+        int64_t n = h->engine->profile_staged(ms_out3);
+        if (n < 0) g_last_error = h->engine->last_error();
+        return static_cast<int32_t>(n);
+    } catch (...) { return -1; }
+}
+
 int32_t gtok_x_read(void* handle, uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets) {
     if (!handle) return -1;
     try { return static_cast<int32_t>(static_cast<Handle*>(handle)->engine->read_staged(out_tokens, out_cap, out_doc_offsets)); } catch (...) { return -1; }
@@ -175,6 +186,26 @@ void gtok_x_table_bytes(void* handle, uint64_t* out3) {
 int32_t gtok_x_launches_per_replay(void* handle, int32_t batch) {
     if (!handle) return -1;
     return static_cast<Handle*>(handle)->engine->launches_per_replay(batch != 0);
+}
+
+int32_t gtok_x_plan_chunks(void* handle, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out_offsets) {
+    if (!handle || (!text && len) || !n_parts || !out_offsets) return -1;
+    try {
+        std::vector<uint64_t> cuts;
+        gtok::plan_chunks(static_cast<Handle*>(handle)->engine->vocab(), text, len, n_parts, cuts);
+        std::memcpy(out_offsets, cuts.data(), cuts.size() * sizeof(uint64_t));
+        return 0;
+    } catch (...) { return -1; }
+}
+
+int32_t gtok_x_plan_documents(const uint32_t* doc_byte_offsets, uint32_t n_docs, uint32_t n_parts, uint32_t* out_doc_index) {
+    if (!doc_byte_offsets || !n_parts || !out_doc_index) return -1;
+    try {
+        std::vector<uint32_t> cuts;
+        gtok::plan_documents(doc_byte_offsets, n_docs, n_parts, cuts);
+        std::memcpy(out_doc_index, cuts.data(), cuts.size() * sizeof(uint32_t));
+        return 0;
+    } catch (...) { return -1; }
 }
 
 }  // extern "C"

@@ -75,10 +75,24 @@ uint32_t gtok_x_family(void* handle);
 int32_t gtok_x_stage(void* handle, const uint8_t* bytes, uint32_t len, const uint32_t* doc_byte_offsets, uint32_t n_docs);
 int32_t gtok_x_replay(void* handle, float* ms_out);
 int32_t gtok_x_read(void* handle, uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets);
+/* The staged input once more, launched kernel by kernel with CUDA events between:
+ * ms_out3 = {pre-tokenization kernel, merge kernel, whole sequence}. */
+int32_t gtok_x_profile(void* handle, float* ms_out3);
 /* Sizes in bytes of the merge table, the whole-word table and the remaining tables. */
 void gtok_x_table_bytes(void* handle, uint64_t* out3);
 /* Kernel launches one graph replay performs (single document / batch). */
 int32_t gtok_x_launches_per_replay(void* handle, int32_t batch);
+
+/* Partitioning over the GPUs of one box (no counterpart in the reference, which is
+ * single-GPU).  gtok_x_plan_chunks cuts one document into n_parts pieces at
+ * positions where a pre-token starts whatever precedes it (letter | space letter),
+ * so that the pieces' ids concatenate to the ids of the whole; out_offsets gets
+ * n_parts+1 byte offsets.  gtok_x_plan_documents cuts a batch into n_parts
+ * contiguous document ranges of about equal bytes; out_doc_index gets n_parts+1
+ * document indices.  Each part is then encoded by one GPU with gtok_encode /
+ * gtok_encode_batch; only the parts' token counts cross GPUs. */
+int32_t gtok_x_plan_chunks(void* handle, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out_offsets);
+int32_t gtok_x_plan_documents(const uint32_t* doc_byte_offsets, uint32_t n_docs, uint32_t n_parts, uint32_t* out_doc_index);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,78 @@
+"""Seeded input generators shared by the CPU and GPU parity tests."""
+import random
+
+import numpy as np
+
+TILE = 4096
+
+POOLS = {
+    "mixed": list("ab cd\r\n1.'sXY tlrevmTLREVM\t") + ["é", "日", "ſ", " ", "2", "'ll", "'RE", "\n\n", "  ", "!!"],
+    "space": list("a \n\r.") + [" ", " ", "　", "\t"],
+    "digit": list("0123456789 a.") + ["٣", "५"],
+    "apos": list("'stdmlrve ") + ["ſ", "'"],
+}
+
+
+def fuzz_strings(seed, special, per_pool=300, lengths=(1, 2, 3, 5, 8, 13, 40, 120, 700)):
+    rng = random.Random(seed)
+    out = []
+    for name, pool in POOLS.items():
+        pool = list(pool)
+        if special:
+            pool += [special, "<", "|", "<|"]
+        for _ in range(per_pool):
+            n = rng.randint(1, rng.choice(lengths))
+            out.append("".join(rng.choice(pool) for _ in range(n)))
+    return out
+
+
+def malformed_bytes(seed, count=300):
+    rng = random.Random(seed)
+    alphabet = [0x61, 0x20, 0x80, 0xBF, 0xC3, 0xE4, 0xF0, 0xA9, 0x0A, 0x27, 0x73, 0x31, 0xFF, 0xC5, 0x2E]
+    return [bytes(rng.choice(alphabet) for _ in range(rng.randint(1, 60))) for _ in range(count)]
+
+
+def tile_crossers(special):
+    """Inputs whose interesting structure sits on tile edges (4096-byte tiles, 128/64-byte halos)."""
+    out = []
+    for pad in (TILE - 70, TILE - 3, TILE - 2, TILE - 1, TILE, TILE + 1, 2 * TILE - 1):
+        base = ("ab " * (pad // 3 + 1))[:pad]
+        for mid in (" " * 300, "\n" * 300, " \n" * 150, "\n " * 150, "." + "\n" * 200 + " x", "7" * 500, "7" * 9000, "x" * 20, "x" * 5000,
+                    "don't", "'ll", " 's", "é" * 100, "日本語" * 50, ".\r\n\r\n  \r\n y", "a" + " " * 129 + "\n" + " " * 200 + "b", "\t" * 70 + "z",
+                    "=" * 200 + "\n\n\n" + "w", "1 2 3 4 5 6 7 8 9 " * 30):
+            out.append(base + mid + " tail end.")
+            if special:
+                out.append(base + special + mid + special + special + " t")
+    out.append("z" * (3 * TILE + 17))
+    out.append("9" * (2 * TILE + 5) + " " + "8" * 100)
+    out.append((" " * (TILE + 100)) + "x")
+    out.append(("\n" * (TILE + 100)) + "x")
+    out.append("ab" * 1100 + " q")
+    out.append("abcde" * 2500)
+    return out
+
+
+def length_ladder():
+    out = []
+    for n in (1, 2, 15, 16, 17, 18, 31, 32, 33, 63, 64, 65, 129, 257, 513, 1025, 1529, 1530, 1531, 2048, 2049, 4095, 4096, 4097, 9000):
+        out += ["a" * n, "ab" * (n // 2 + 1), ("the" * (n // 3 + 1))[:n], "x " + "q" * n + " y"]
+    return out
+
+
+def make_batch(seed, docs_text):
+    """Concatenation + uint32 offsets, with a few empty documents mixed in."""
+    rng = random.Random(seed)
+    blobs, offs = [], [0]
+    for t in docs_text:
+        b = t if isinstance(t, bytes) else t.encode("utf-8")
+        if rng.random() < 0.15:
+            offs.append(offs[-1])      # an empty document first
+        blobs.append(b)
+        offs.append(offs[-1] + len(b))
+    return b"".join(blobs), np.array(offs, dtype=np.uint32)
+
+
+SEAM_DOCS = [
+    "123", "456", "12", "3456789", " ", "  ", "a ", " b", "\n", "\r", "\n\n", "x\r", "\ny", "don", "'t", "'", "s", "it'", "ll go",
+    ".", "\n.", ".\n", "\n", "a.", "\n\nb", "é", "e", "́", "日本", "語", "x  ", "  y", "\t", "\tz", "", "", "end",
+]

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "../../graphtok_b200/csrc/encode_core.h"
+#include "../../graphtok_b200/csrc/shard_plan.h"
 #include "../../graphtok_b200/csrc/tables_build.h"
 #include "../../graphtok_b200/csrc/unicode_class_table.h"
 #include "../../graphtok_b200/csrc/vocab_host.h"
@@ -119,6 +120,14 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     }
     if (ctl[2]) return -static_cast<int64_t>(ctl[2]);
     return status[0];
+}
+
+// The shard planner of libgtok (gtok_x_plan_chunks), reachable without a GPU handle.
+int gtok_emul_plan_chunks(void* h, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out) {
+    std::vector<uint64_t> cuts;
+    gtok::plan_chunks(static_cast<Emul*>(h)->hv, text, len, n_parts, cuts);
+    std::memcpy(out, cuts.data(), cuts.size() * sizeof(uint64_t));
+    return 0;
 }
 
 }  // extern "C"

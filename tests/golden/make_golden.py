@@ -1,0 +1,81 @@
+#!/usr/bin/env python3
+"""Regenerates the golden vectors in this directory.
+
+Vocabularies: tiny_{gpt2,llama3,qwen25}.json, written by the in-tree generator
+(graphtok_b200.synth.vocab_path("tiny_*"): seeded corpus + greedy BPE trainer) and
+committed here because the expected ids are only meaningful for these exact files.
+
+Expected ids: Hugging Face `tokenizers` (the reference's own test oracle,
+tests/test_encode_batch.py:69-84 there) on every case string:
+    Tokenizer.from_file(vocab).encode(text, add_special_tokens=False).ids
+For the Qwen2.5-shaped vocabulary that call includes the file's NFC normaliser.
+
+The case list follows the shapes of the reference's tests: document-seam strings
+(tests/seam_corpus.py), pre-token lengths around the bucket cut-overs
+(tests/test_exactness_targeted.py:39,83-88), equal-rank runs (:104-124),
+added-token edge strings (tests/test_host_fast_path.py:107-128), a small-alphabet
+fuzz (:132-141) and the named NFC cases (tests/test_nfc_normalization.py).
+
+Run:  python tests/golden/make_golden.py        (needs `tokenizers`; offline)
+"""
+import json
+import os
+import random
+
+from tokenizers import Tokenizer
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def cases(family, special):
+    c = [
+        "", " ", "  ", "\n", "\r\n", "a", "Hello, world! It's 2026", "don't DON'T can't he'll we're I've I'm she'd 'tis",
+        "x'sy 'll 'LL ''s .'s  's \t's a'", "'s", "'", "''", "a'\nb", "1'st 2'nd",
+        "tabs\tand\t\tmore \t mixed", "trailing spaces   ", "   leading", "line1\nline2\n\nline4\r\n\r\nline6",
+        "code:\n    if (x == 1) {\n        return y[i];\n    }\n", "a.\n\nb", "a.\r\n \r\n b", "x !\n\n  y", "x;\n\t\ty",
+        "1 12 123 1234 12345 123456 1234567 12345678901234567890", "3.14159 1,000,000 0x1F 1e-9", "٣٤٥٦٧ ५६७८ ①②③④",
+        "ünïcödé Ωmega привет мир Ελληνικά", "日本語のテキスト 中文文本 한국어", "emoji 🙂🙃 👍🏽 done", "a\u00a0b\u2003c\u3000d\u2028e",
+        "ſ 'ſ x'ſy İstanbul ǅ", "(word) -word --word \"quoted\" [x]{y}<z>", "a+b=c; d->e; f::g; #h @i $j %k ^l &m *n",
+        "aaaaaaaaaaaaaaa", "a" * 16, "a" * 17, "a" * 31, "a" * 32, "a" * 33, "a" * 63, "a" * 64, "a" * 65, "a" * 129, "a" * 257,
+        "a" * 513, "a" * 1025, "ab" * 600, "abc" * 700, " " * 100, "\n" * 100, " \n" * 60, "x" + " " * 70 + "y", "x" + "\n" * 70 + "y",
+        "." * 90, ".\n" * 50, "=" * 300, "9" * 400, "z" * 2100, "mn" * 2600,
+        "the quick brown fox jumps over the lazy dog " * 40,
+        "https://example.com/a/b/c?d=e&f=g#h user@example.org C:\\path\\file.txt",
+        "supercalifragilisticexpialidocious antidisestablishmentarianism pneumonoultramicroscopicsilicovolcanoconiosis",
+        "中" * 40, "日本" * 300, "é" * 50, "e\u0301" * 50, "🙂" * 30,
+    ]
+    if special:
+        s = special
+        c += [s, s + s, "a" + s + "b", " " + s + " ", s + "'s", "x" + s + "\n\n" + s + " y", "<" + s, s[:-1], s[:-1] + " " + s,
+              "<|" + s, "12" + s + "345", "a " + s + "  " + s + " b", s + "é", "\n" + s + "\n"]
+    rng = random.Random(20260101)
+    pools = [list("ab cd\r\n1.'sXY"), list("'stdmlrve LRVE\t"), list("0123456789 ,."), list(" \n\r\t.x")]
+    for pool in pools:
+        for _ in range(120):
+            c.append("".join(rng.choice(pool) for _ in range(rng.randint(1, 48))))
+    if family == "qwen25":
+        c += ["e\u0301", "a\u0308o\u0308u\u0308", "\u0041\u030a", "\u212b", "\u1e9b\u0323", "q\u0307\u0323", "\uac00", "\u1100\u1161\u11a8",
+              "\u0958", "\u0b47\u0b56", "x\u0301\u0301\u0301", "\u0301a", "caf\u0065\u0301 na\u0069\u0308ve", "\ufb01 \u00bd \u2126",
+              "a\u0323\u0302", "\u0f73", "\u1f71", "\u2000\u2001", "\u0344", "D\u0307\u0323", "\u1ebf", "e\u0302\u0301", "\u09cb", "\u09c7\u09be"]
+    seen, out = set(), []
+    for s in c:
+        if s not in seen:
+            seen.add(s)
+            out.append(s)
+    return out
+
+
+def main():
+    for family, special in (("gpt2", None), ("llama3", "<|reserved_special_token_3|>"), ("qwen25", "<|qwen_special_1|>")):
+        vocab = os.path.join(HERE, "tiny_%s.json" % family)
+        tok = Tokenizer.from_file(vocab)
+        rows = []
+        for s in cases(family, special):
+            rows.append({"text": s, "ids": tok.encode(s, add_special_tokens=False).ids})
+        with open(os.path.join(HERE, "golden_%s.json" % family), "w") as f:
+            json.dump({"vocab": "tiny_%s.json" % family, "source": "tokenizers " + __import__("tokenizers").__version__, "cases": rows}, f, ensure_ascii=True)
+        print(family, len(rows), "cases")
+
+
+if __name__ == "__main__":
+    main()

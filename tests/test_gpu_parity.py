@@ -1,0 +1,177 @@
+"""Parity proper: libgtok on a B200, called through its C ABI, against the oracle and the
+golden vectors.  Ids are integers: every comparison is exact."""
+import ctypes
+import json
+import os
+import threading
+
+import numpy as np
+import pytest
+
+import oracle_lib
+from conftest import FAMILIES, GOLDEN, SPECIAL, tiny_vocab
+import cases
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gtoks(built):
+    from graphtok_b200 import GTok
+    hs = {f: GTok(tiny_vocab(f), max_bytes=1 << 20) for f in FAMILIES}
+    yield hs
+    for h in hs.values():
+        h.close()
+
+
+def norm(o, b):
+    return oracle_lib.nfc(b) if o.needs_nfc else b
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_golden_vectors(gtoks, oracles, family):
+    data = json.load(open(os.path.join(GOLDEN, "golden_%s.json" % family)))
+    g, o = gtoks[family], oracles[family]
+    for row in data["cases"]:
+        b = norm(o, row["text"].encode("utf-8"))
+        assert g.encode(b).tolist() == row["ids"], repr(row["text"][:40])
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_fuzz_malformed_edges_and_lengths(gtoks, oracles, family):
+    g, o = gtoks[family], oracles[family]
+    texts = [t.encode() for t in cases.fuzz_strings(41, SPECIAL[family], per_pool=150)]
+    texts += cases.malformed_bytes(43, 200)
+    texts += [t.encode() for t in cases.tile_crossers(SPECIAL[family])]
+    texts += [t.encode() for t in cases.length_ladder()]
+    for b in texts:
+        b = norm(o, b) if b.decode("utf-8", "ignore").encode() == b else b
+        assert np.array_equal(g.encode(b), o.encode_normalized(b)), repr(b[:60])
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_batch_equals_per_document(gtoks, oracles, family):
+    g, o = gtoks[family], oracles[family]
+    docs = [norm(o, d.encode()) for d in cases.SEAM_DOCS] + [("word " * 900).encode(), b"\x80\x80abc", b"q" * 5000, ("7" * 4200).encode()]
+    blob, offs = cases.make_batch(3, docs)
+    ids, doc = g.encode_batch(blob, offs)
+    want_ids, want_doc = [], [0]
+    for i in range(len(offs) - 1):
+        t = o.encode_normalized(blob[int(offs[i]):int(offs[i + 1])])
+        want_ids.append(t)
+        want_doc.append(want_doc[-1] + len(t))
+    assert np.array_equal(ids, np.concatenate(want_ids))
+    assert doc.tolist() == want_doc
+    # the same handle keeps answering single documents identically afterwards
+    assert np.array_equal(g.encode(b"after the batch"), o.encode_normalized(b"after the batch"))
+
+
+def test_return_codes(gtoks):
+    g = gtoks["gpt2"]
+    lib = g.lib
+    out = np.zeros(4, dtype=np.uint32)
+    text = b"many words in a row " * 50
+    assert lib.gtok_encode(g.handle, text, len(text), out.ctypes.data, 4) == -2
+    big = b"x" * ((1 << 20) + 1)
+    assert lib.gtok_encode(g.handle, big, len(big), out.ctypes.data, 4) == -3
+    assert lib.gtok_encode(g.handle, b"", 0, out.ctypes.data, 4) == 0
+    assert lib.gtok_encode(None, b"a", 1, out.ctypes.data, 4) == -1
+    offs = np.array([0, 3, 2], dtype=np.uint32)
+    doc = np.zeros(3, dtype=np.uint32)
+    assert lib.gtok_encode_batch(g.handle, b"abcd", offs.ctypes.data, 2, out.ctypes.data, 4, doc.ctypes.data) == -1
+    assert lib.gtok_vocab_size(g.handle) > 256
+    assert lib.gtok_cpu_backend(g.handle) == b"off"
+    # a failed call leaves the handle usable
+    assert g.encode(b"still fine").size > 0
+
+
+def test_encode_to_device_matches_host(gtoks, oracles):
+    import torch
+    g, o = gtoks["llama3"], oracles["llama3"]
+    text = ("device side output " * 200).encode()
+    buf = torch.zeros(len(text), dtype=torch.int32, device="cuda")
+    n = g.lib.gtok_encode_to_device(g.handle, text, len(text), ctypes.c_void_p(buf.data_ptr()), buf.numel())
+    assert n > 0
+    torch.cuda.synchronize()
+    assert np.array_equal(buf[:n].cpu().numpy().astype(np.uint32), o.encode_normalized(text))
+
+
+def test_sizes_change_between_calls_on_one_handle(gtoks, oracles):
+    g, o = gtoks["llama3"], oracles["llama3"]
+    from graphtok_b200 import synth
+    doc = synth.text(4, 5, 900000)
+    for n in (900000, 17, 4096, 300000, 1, 4097, 65536, 899999, 5):
+        b = doc[:n].decode("utf-8", "ignore").encode()
+        assert np.array_equal(g.encode(b), o.encode_normalized(b)), n
+
+
+def test_dispatcher_threads(built, oracles):
+    from graphtok_b200 import load_lib
+    lib = load_lib()
+    d = lib.gtok_dispatcher_create(os.fsencode(tiny_vocab("gpt2")), 0, 1 << 20, 64, 0)
+    assert d
+    o = oracles["gpt2"]
+    texts = [("request %d says hello %s" % (i, "again " * (i % 37))).encode() for i in range(200)]
+    want = [o.encode_normalized(t) for t in texts]
+    errors = []
+
+    def worker(k):
+        out = np.zeros(4096, dtype=np.uint32)
+        for i in range(k, len(texts), 8):
+            n = lib.gtok_dispatch_encode(d, texts[i], len(texts[i]), out.ctypes.data, out.size)
+            if n < 0 or not np.array_equal(out[:n], want[i]):
+                errors.append(i)
+
+    ts = [threading.Thread(target=worker, args=(k,)) for k in range(8)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    stats = (ctypes.c_uint64 * 5)()
+    lib.gtok_dispatcher_stats(d, stats)
+    lib.gtok_dispatcher_destroy(d)
+    assert not errors
+    assert stats[1] == len(texts)
+
+
+@pytest.mark.parametrize("config", (0, 1, 3))
+def test_benchmark_configurations_full_size(built, config):
+    """Configurations 0, 1 and 3 at their full sizes against the oracle."""
+    from graphtok_b200 import GTok, synth
+    path, doc = synth.config_doc(config)
+    o = oracle_lib.Oracle(path)
+    b = norm(o, doc)
+    g = GTok(path, max_bytes=len(b) + 4096)
+    try:
+        assert np.array_equal(g.encode(b), o.encode_normalized(b))
+    finally:
+        g.close()
+
+
+def test_configuration_4_prefix_and_chunk_property(built):
+    """Adversarial document: an 8 MB prefix against the oracle, and at the full 32 MB the
+    size-independent property that planned chunks concatenate to the whole."""
+    from graphtok_b200 import GTok, synth
+    path, doc = synth.config_doc(4)
+    o = oracle_lib.Oracle(path)
+    g = GTok(path, max_bytes=len(doc) + 4096)
+    try:
+        pre = doc[:8 << 20].decode("utf-8", "ignore").encode()
+        assert np.array_equal(g.encode(pre), o.encode_normalized(pre))
+        whole = g.encode(doc)
+        cuts = g.plan_chunks(doc, 8)
+        parts = [g.encode(doc[int(cuts[k]):int(cuts[k + 1])]) for k in range(8)]
+        assert np.array_equal(np.concatenate(parts), whole)
+    finally:
+        g.close()
+
+
+def test_configuration_2_batch(built):
+    from graphtok_b200 import GTok, synth
+    path, blob, offs = synth.config_batch(2048)
+    o = oracle_lib.Oracle(path)
+    g = GTok(path, max_bytes=len(blob) + 4096)
+    try:
+        ids, doc = g.encode_batch(blob, offs)
+        want_ids, want_doc = o.encode_batch(blob, offs)
+        assert np.array_equal(ids, want_ids) and np.array_equal(doc, want_doc)
+    finally:
+        g.close()
