@@ -70,6 +70,8 @@ def load_lib():
     lib.gtok_x_replay.argtypes = [vp, vp]
     lib.gtok_x_read.restype = i32
     lib.gtok_x_read.argtypes = [vp, vp, u32, vp]
+    lib.gtok_x_read_boundaries.restype = i32
+    lib.gtok_x_read_boundaries.argtypes = [vp, vp, u32]
     lib.gtok_x_profile.restype = i32
     lib.gtok_x_profile.argtypes = [vp, vp]
     lib.gtok_x_plan_chunks.restype = i32
@@ -159,6 +161,15 @@ class GTok:
         if n < 0:
             self._fail("gtok_x_read", n)
         return out[:n].copy(), (doc if n_docs else None)
+
+    def boundaries(self, n_bytes):
+        """Byte offsets at which pre-tokens start, for the staged input after a replay."""
+        words = np.zeros((n_bytes + 31) // 32 + 1, dtype=np.uint32)
+        r = self.lib.gtok_x_read_boundaries(self.handle, words.ctypes.data, words.size)
+        if r < 0:
+            self._fail("gtok_x_read_boundaries", r)
+        bits = np.unpackbits(words.view(np.uint8), bitorder="little")[:n_bytes]
+        return np.nonzero(bits)[0].astype(np.uint32)
 
     def profile(self):
         """Staged input, kernel by kernel: (tokens, pretok ms, merge ms, sequence ms)."""

@@ -414,6 +414,20 @@ int64_t Engine::profile_staged(float* ms_out) {
     return reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
 }
 
+int64_t Engine::read_boundaries(uint32_t* out_words, uint32_t max_words) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    Ctx* c = im.staged;
+    if (!c) { last_error_ = "nothing staged"; return -1; }
+    uint32_t words = (c->staged_len + 31) / 32;
+    if (words > max_words) return -2;
+    if (words && cudaMemcpy(out_words, c->d_bmask, static_cast<size_t>(words) * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return words;
+}
+
+const DeviceTables* Engine::device_tables() const { return &impl_->dt; }
+int Engine::device_index() const { return impl_->device; }
+
 int64_t Engine::read_staged(uint32_t* out, uint32_t max_out, uint32_t* out_doc_tok) {
     Impl& im = *impl_;
     cudaSetDevice(im.device);

@@ -35,6 +35,12 @@ public:
     // Same work as one replay, launched kernel by kernel with an event between them:
     // ms_out[0] = pretok kernel, ms_out[1] = merge kernel, ms_out[2] = whole sequence.
     int64_t profile_staged(float* ms_out);
+    // Boundary bits of the staged input as left by the last replay: one bit per byte,
+    // set where a pre-token starts; writes (len + 31) / 32 words.
+    int64_t read_boundaries(uint32_t* out_words, uint32_t max_words);
+    // Device-side table block for callers inside the library (no-allocation entry point).
+    const struct DeviceTables* device_tables() const;
+    int device_index() const;
 
     const HostVocab& vocab() const { return hv_; }
     uint32_t vocab_size() const { return hv_.vocab_size; }

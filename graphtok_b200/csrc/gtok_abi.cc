@@ -173,6 +173,11 @@ int32_t gtok_x_profile(void* handle, float* ms_out3) {
     } catch (...) { return -1; }
 }
 
+int32_t gtok_x_read_boundaries(void* handle, uint32_t* out_words, uint32_t max_words) {
+    if (!handle || !out_words) return -1;
+    try { return static_cast<int32_t>(static_cast<Handle*>(handle)->engine->read_boundaries(out_words, max_words)); } catch (...) { return -1; }
+}
+
 int32_t gtok_x_read(void* handle, uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets) {
     if (!handle) return -1;
     try { return static_cast<int32_t>(static_cast<Handle*>(handle)->engine->read_staged(out_tokens, out_cap, out_doc_offsets)); } catch (...) { return -1; }

@@ -75,6 +75,9 @@ uint32_t gtok_x_family(void* handle);
 int32_t gtok_x_stage(void* handle, const uint8_t* bytes, uint32_t len, const uint32_t* doc_byte_offsets, uint32_t n_docs);
 int32_t gtok_x_replay(void* handle, float* ms_out);
 int32_t gtok_x_read(void* handle, uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets);
+/* Boundary bits of the staged input after a replay: bit i of the stream is set where a
+ * pre-token starts at byte i.  Writes (len + 31) / 32 words; returns that count. */
+int32_t gtok_x_read_boundaries(void* handle, uint32_t* out_words, uint32_t max_words);
 /* The staged input once more, launched kernel by kernel with CUDA events between:
  * ms_out3 = {pre-tokenization kernel, merge kernel, whole sequence}. */
 int32_t gtok_x_profile(void* handle, float* ms_out3);

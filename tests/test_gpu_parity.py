@@ -66,6 +66,19 @@ def test_batch_equals_per_document(gtoks, oracles, family):
     assert np.array_equal(g.encode(b"after the batch"), o.encode_normalized(b"after the batch"))
 
 
+@pytest.mark.parametrize("family", FAMILIES)
+def test_boundary_bits_match_oracle_starts(gtoks, oracles, family):
+    g, o = gtoks[family], oracles[family]
+    for t in cases.fuzz_strings(51, SPECIAL[family], per_pool=40) + cases.tile_crossers(SPECIAL[family])[:30]:
+        b = norm(o, t.encode())
+        if not b:
+            continue
+        g.stage(b)
+        g.replay()
+        _, want = o.encode_normalized(b, want_starts=True)
+        assert np.array_equal(g.boundaries(len(b)), want), repr(t[:60])
+
+
 def test_return_codes(gtoks):
     g = gtoks["gpt2"]
     lib = g.lib
