@@ -9,6 +9,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <string>
+
 #include "encode_core.h"
 #include "encode_kernels.h"
 
@@ -110,7 +113,81 @@ __global__ void docmask_kernel(const uint32_t* meta, const uint32_t* doc_off, ui
     }
 }
 
+// ---- boundaries without any allocation --------------------------------------------
+// Working memory of boundaries_noalloc(): the pre-tokenization kernel's ticket and error
+// words, its per-tile look-back states, the per-tile boundary counts, the added-token
+// bits and the byte count the kernel reads.  It lives in the library's device image:
+// every GPU that loads the library holds these ~0.5 MB until the process exits.
+struct NoAllocScratch {
+    uint32_t ctl[16];
+    uint32_t meta[16];
+    unsigned long long st1[kNoAllocTiles + 1];
+    uint32_t tile_nb[kNoAllocTiles + 1];
+    uint32_t amask[kNoAllocTiles * kTileWords + 8];
+};
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+__global__ void noalloc_set_meta(uint32_t* meta, uint32_t n) { meta[0] = n; meta[1] = 1; }
+
 }  // namespace
+
+int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev, uint32_t len, void* out_bits_dev,
+                       cudaStream_t stream, std::string& err) {
+    if (len > kNoAllocMaxBytes) {
+        err = "boundaries_noalloc: input of " + std::to_string(len) + " bytes exceeds the fixed working memory (limit " +
+              std::to_string(kNoAllocMaxBytes) + " bytes)";
+        return -3;
+    }
+    if (!text_dev || !out_bits_dev) { err = "boundaries_noalloc: null device pointer"; return -1; }
+    if (reinterpret_cast<uintptr_t>(text_dev) & 15u) { err = "boundaries_noalloc: text must be 16-byte aligned"; return -1; }
+    if (len == 0) return 0;
+    // Device address of the scratch array, looked up once per device with that device
+    // current.  In host code the array's name is only a handle for this lookup.
+    static std::mutex mu;
+    static NoAllocScratch* scratch_of[64] = {};
+    static int sm_of[64] = {};
+    if (device < 0 || device >= 64) { err = "boundaries_noalloc: device index out of range"; return -1; }
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) { err = std::string("cudaSetDevice: ") + cudaGetErrorString(e); return -1; }
+    NoAllocScratch* sc;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!scratch_of[device]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p) { err = std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e); return -1; }
+            int sms = 0;
+            e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+            if (e != cudaSuccess || sms <= 0) { err = std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e); return -1; }
+            sm_of[device] = sms;
+            scratch_of[device] = static_cast<NoAllocScratch*>(p);
+        }
+        sc = scratch_of[device];
+    }
+    EncodeArgs a;
+    memset(&a, 0, sizeof a);
+    a.text = static_cast<const uint8_t*>(text_dev);
+    a.meta = sc->meta;
+    a.bmask = static_cast<uint32_t*>(out_bits_dev);
+    a.amask = sc->amask;
+    a.tile_nb = sc->tile_nb;
+    a.st1 = sc->st1;
+    a.ctl = sc->ctl;
+    a.tb = tb;
+    const uint32_t n_tiles = (len + kTile - 1) / kTile;
+    // The array keeps whatever the previous call left: ticket, error word and the
+    // look-back states of the tiles this call uses must start at zero.
+    e = cudaMemsetAsync(sc->ctl, 0, sizeof sc->ctl, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(sc->st1, 0, sizeof(unsigned long long) * (n_tiles + 1), stream);
+    if (e != cudaSuccess) { err = std::string("cudaMemsetAsync: ") + cudaGetErrorString(e); return -1; }
+    noalloc_set_meta<<<1, 1, 0, stream>>>(sc->meta, len);
+    const int blocks = static_cast<int>(n_tiles < static_cast<uint32_t>(sm_of[device] * 4) ? n_tiles : sm_of[device] * 4);
+    pretok_kernel<<<blocks, kThreads, 0, stream>>>(a);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) { err = std::string("boundaries_noalloc: ") + cudaGetErrorString(e); return -1; }
+    return 0;
+}
 
 size_t merge_smem_bytes() { return sizeof(MergeSmem); }
 

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#include <string>
+
 #include "encode_core.h"
 
 namespace gtok {
@@ -14,5 +16,15 @@ int merge_blocks_per_sm();
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_merge(const EncodeArgs& a, int blocks, cudaStream_t s);
+
+
+// Largest input of boundaries_noalloc(), fixed by its statically reserved working memory.
+constexpr uint32_t kNoAllocMaxBytes = 4u << 20;
+constexpr uint32_t kNoAllocTiles = kNoAllocMaxBytes / kTile;
+// Boundary bits of `len` bytes of single-document text already in device memory, written
+// to a caller-supplied device buffer, using only working memory reserved inside the
+// library image.  See gtok_x_boundaries_noalloc in include/gtok.h for the contract.
+int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev, uint32_t len, void* out_bits_dev,
+                       cudaStream_t stream, std::string& err);
 
 }  // namespace gtok

@@ -8,6 +8,8 @@
 #include <string>
 #include <vector>
 
+#include "device_tables.h"
+#include "encode_kernels.h"
 #include "engine.h"
 #include "shard_plan.h"
 
@@ -191,6 +193,18 @@ void gtok_x_table_bytes(void* handle, uint64_t* out3) {
 int32_t gtok_x_launches_per_replay(void* handle, int32_t batch) {
     if (!handle) return -1;
     return static_cast<Handle*>(handle)->engine->launches_per_replay(batch != 0);
+}
+
+int32_t gtok_x_boundaries_noalloc(void* handle, const void* text_dev, uint32_t len, void* out_bits_dev, void* cuda_stream) {
+    if (!handle) return -1;
+    try {
+        Handle* h = static_cast<Handle*>(handle);
+        std::string err;
+        int r = gtok::boundaries_noalloc(*h->engine->device_tables(), h->engine->device_index(), text_dev, len, out_bits_dev,
+                                         static_cast<cudaStream_t>(cuda_stream), err);
+        if (r < 0) g_last_error = err;
+        return r;
+    } catch (...) { return -1; }
 }
 
 int32_t gtok_x_plan_chunks(void* handle, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out_offsets) {
