@@ -55,6 +55,7 @@ struct DeviceTables {
     uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5
     uint32_t ignore_merges;
     uint32_t monotone;
+    uint32_t added_ws;                   // some added-token literal contains a space, CR or LF
 };
 
 // ---- hashes (host and device) ------------------------------------------------

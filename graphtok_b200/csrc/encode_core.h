@@ -10,6 +10,7 @@
 // Both are written against a small "thread block" interface (Blk):
 //     blk.par(f)                run f(tid) for every thread, then barrier
 //     blk.excl_scan(arr,total)  in-place exclusive scan of arr[kThreads]
+//     blk.lookback(st,tile,total,ctl)  publish this tile's total, return the sum of all earlier tiles'
 // so that the CUDA kernels in encode_kernels.cu (one real thread per tid) and a
 // serial emulation used by the CPU tests execute the very same logic.  Nothing
 // outside a par() body may depend on the order in which tids run, and no par()
@@ -50,7 +51,9 @@ constexpr uint32_t kDirty = 0xFFFFFFFEu;
 constexpr uint32_t kReprobe = 0xFFFFFFFEu;
 
 constexpr int kThreadWordMax = 16;   // longest pre-token merged by a single thread
-constexpr int kWarpWordMax = 256;    // longest pre-token merged by a warp in shared memory
+constexpr int kMedWordMax = 64;      // longest pre-token merged by a single thread (second pass, fewer rows)
+constexpr int kMedRows = 32;
+constexpr int kTokExtra = 64;        // token slots past the tile for pre-tokens that start in it
 constexpr int kRows = 128;           // single-thread merge rows per batch
 constexpr int kWsWords = kRows * kThreadWordMax * 3;   // 6144 u32 = 24 KB, shared by all merge paths
 constexpr int kBlockWordSmemMax = kWsWords / 3;        // 2048 symbols
@@ -242,9 +245,26 @@ GTOK_DEV bool is_docstart_global(const EncodeArgs& a, int p) {
 // ==================================================================================
 //                                   PRE-TOKENIZATION
 // ==================================================================================
+// One-hot byte used to build bit planes: bit c for class c (L,N,S,O,CONT,ADDED), then flags.
+enum : uint8_t { kOhL = 1, kOhN = 2, kOhS = 4, kOhO = 8, kOhC = 16, kOhAdded = 32, kOhCrlf = 64, kOhSp = 128 };
+enum { PL_L = 0, PL_N, PL_S, PL_O, PL_C, PL_AD, PL_CRLF, PL_SP, PL_AP, kPlanes };
+
+GTOK_DEV uint8_t onehot_of(uint8_t at) {
+    int c = at & A_CLS;
+    uint8_t oh = c <= A_ADDED ? static_cast<uint8_t>(1u << c) : 0;
+    if (at & A_CRLF) oh |= kOhCrlf;
+    if (at & A_SP) oh |= kOhSp;
+    return oh;
+}
+// Bit k of each of the four bytes of w, gathered into the low four bits.
+GTOK_DEV uint32_t gather_bit4(uint32_t w, int k) { return (((w >> k) & 0x01010101u) * 0x01020408u) >> 24; }
+
 struct PretokSmem {
     alignas(16) uint8_t txt[kWin + 16];
     alignas(16) uint8_t attr[kWin + 16];
+    alignas(16) uint8_t oh[kWin + 16];       // one-hot class + flags per byte (see kOh*)
+    alignas(4) uint16_t plane[kPlanes][kWin / 16 + 4];   // bit planes of the window, 16 bytes per entry
+    uint16_t lut[128];                       // ASCII byte -> attr | one-hot << 8
     uint32_t dsw[kWin / 32 + 2];             // document-start bits of the window
     uint16_t bnd16[kThreads + 2], add16[kThreads + 2], pend16[kThreads + 2];
     uint16_t lead16[kThreads + 2], nlead16[kThreads + 2], nstart16[kThreads + 2];
@@ -389,6 +409,50 @@ GTOK_DEV int ncls(uint8_t a) {
     return c <= A_O ? c : -1;
 }
 
+// Fast forms of the two run walks for positions outside the window, where every
+// attribute would have to be rebuilt from global memory.  They only step over bytes
+// whose meaning is certain from the byte alone (CR/LF going back, 0x20 going forward;
+// never when an added-token literal could contain such a byte, never across a document
+// start) and leave the deciding position to the general code.
+GTOK_DEV bool no_docstart_in4(const EncodeArgs& a, int q) {     // q..q+3 within one mask word (q % 4 == 0)
+    if (!a.docmask) return q != 0;
+    if (q == 0) return false;
+    return ((ldg(a.docmask + (q >> 5)) >> (q & 31)) & 0xFu) == 0;
+}
+// q is a CR/LF byte: position of the first byte before the newline stretch that is not
+// CR/LF, or the CR/LF that opens its document (the caller's test then ends the walk).
+GTOK_DEV int skip_back_newlines(const Win& w, int q) {
+    const EncodeArgs& a = *w.a;
+    if (a.tb.added_ws) return q;
+    for (;;) {
+        if (q < 0) return q;
+        if ((q & 3) == 3 && q >= 7) {
+            uint32_t v = ldg(reinterpret_cast<const uint32_t*>(a.text + q - 3));
+            if ((v == 0x0A0A0A0Au || v == 0x0A0D0A0Du || v == 0x0D0A0D0Au || v == 0x0D0D0D0Du) && no_docstart_in4(a, q - 3)) { q -= 4; continue; }
+        }
+        uint32_t b = ldg(a.text + q);
+        if (b != 0x0Au && b != 0x0Du) return q;
+        if (is_docstart_global(a, q)) return q;
+        --q;
+    }
+}
+// r is a lead at or past the window end: first position at or after r that is not a
+// plain space of the same document, or -1 at the end of the document.
+GTOK_DEV int skip_forward_spaces(const Win& w, int r) {
+    const EncodeArgs& a = *w.a;
+    if (a.tb.added_ws) return r;
+    for (;;) {
+        if (r >= w.n) return -1;
+        if ((r & 3) == 0 && r + 4 <= w.n) {
+            uint32_t v = ldg(reinterpret_cast<const uint32_t*>(a.text + r));
+            if (v == 0x20202020u && no_docstart_in4(a, r)) { r += 4; continue; }
+        }
+        if (is_docstart_global(a, r)) return -1;
+        if (ldg(a.text + r) != 0x20u) return r;
+        ++r;
+    }
+}
+
 // First byte of the codepoint at lead q as the contraction rule sees it:
 // lower-cased ASCII and U+017F read as 's' when the family matches case-insensitively.
 GTOK_DEV int tail_byte(const Win& w, int q, bool ci) {
@@ -493,6 +557,8 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
         // token ( ?[^\s\p{L}\p{N}]+[\r\n]*), the whitespace run starts here.
         int q = q1;
         for (;;) {
+            if (q < w.vlo) q = skip_back_newlines(w, q);      // long runs: raw bytes, four at a time
+            if (q < 0) break;
             uint8_t aq = attr_at(w, q);
             if (!((aq & A_CLS) == A_S && (aq & A_CRLF))) { if ((aq & A_CLS) == A_O) return true; break; }
             if (aq & A_DOC) break;
@@ -505,6 +571,7 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
         for (;;) {
             r = next_lead(w, r);
             if (r < 0) return true;
+            if (r >= w.vhi) { r = skip_forward_spaces(w, r); if (r < 0) return true; }
             uint8_t ar = attr_at(w, r);
             if ((ar & A_CLS) != A_S) return true;
             if (ar & A_CRLF) return false;
@@ -544,7 +611,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     const uint32_t family = a.tb.family;
     const int n_chunks = kWin / 16;
 
-    // ---- P0: stage the window ----
+    // ---- P0: stage the window; ASCII lookup table ----
     blk.par([&](int tid) {
         for (int c = tid; c < n_chunks; c += kThreads) {
             int p = lo + c * 16;
@@ -570,6 +637,14 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             }
             sm.dsw[wd] = v;
         }
+        if (tid < 128) {
+            uint32_t leaf = ldg(a.tb.uc_stage1);                       // codepoints 0..127 share stage-1 entry 0
+            uint32_t wv = ldg(a.tb.uc_stage2 + leaf * 8u + (static_cast<uint32_t>(tid) >> 4));
+            uint8_t at = static_cast<uint8_t>((wv >> ((tid & 15) * 2)) & 3u);
+            if (tid == 0x0A || tid == 0x0D) at |= A_CRLF;
+            if (tid == 0x20) at |= A_SP;
+            sm.lut[tid] = static_cast<uint16_t>(at | (onehot_of(at) << 8));
+        }
     });
 
     auto sm_is_doc = [&](int p) -> bool {   // p within [lo, lo + kWin + 64)
@@ -581,14 +656,30 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         return (i >= 0 && i < kWin) ? sm.txt[i] : ldg(a.text + q);
     };
 
-    // ---- P1: per-byte class and flags ----
+    // ---- P1: per-byte class and flags (ASCII through the table, the rest decoded) ----
     blk.par([&](int tid) {
         for (int c = tid; c < n_chunks; c += kThreads) {
-            for (int k = 0; k < 16; ++k) {
-                int i = c * 16 + k, p = lo + i;
-                uint8_t v = A_OUT;
-                if (p >= 0 && p < n) v = plain_attr(a, p, n, byte_any, sm_is_doc);
-                sm.attr[i] = v;
+            const uint32_t* tw = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
+            uint32_t* aw = reinterpret_cast<uint32_t*>(sm.attr + c * 16);
+            uint32_t* ow = reinterpret_cast<uint32_t*>(sm.oh + c * 16);
+            const int i0 = c * 16, p0 = lo + i0;
+            const uint32_t ds = (sm.dsw[i0 >> 5] >> (i0 & 31)) & 0xFFFFu;
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t t = tw[j];
+                uint32_t av = 0, ov = 0;
+                for (int k = 0; k < 4; ++k) {
+                    const int i = j * 4 + k, p = p0 + i;
+                    const uint32_t bt = (t >> (8 * k)) & 0xFFu;
+                    uint32_t at, oh;
+                    if (p < 0 || p >= n) { at = A_OUT; oh = 0; }
+                    else if (bt < 0x80u) { uint32_t v = sm.lut[bt]; at = v & 0xFFu; oh = v >> 8; if ((ds >> i) & 1u) at |= A_DOC; }
+                    else if ((bt & 0xC0u) == 0x80u) { at = A_CONT | (((ds >> i) & 1u) ? A_DOC : 0); oh = kOhC; }
+                    else { at = plain_attr(a, p, n, byte_any, sm_is_doc); oh = onehot_of(static_cast<uint8_t>(at)); }
+                    av |= at << (8 * k);
+                    ov |= oh << (8 * k);
+                }
+                aw[j] = av;
+                ow[j] = ov;
             }
         }
     });
@@ -605,41 +696,129 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     uint32_t ml = match_literal(a, p, n, byte_any, &id);
                     if (!ml) continue;
                     sm.attr[i] = static_cast<uint8_t>(A_ADDED | (sm.attr[i] & A_DOC));
-                    for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kWin; ++j)
+                    sm.oh[i] = kOhAdded;
+                    for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kWin; ++j) {
                         sm.attr[i + j] = static_cast<uint8_t>(A_CONT | (sm.attr[i + j] & A_DOC));
+                        sm.oh[i + j] = kOhC;
+                    }
                 }
             }
         });
     }
+
+    // ---- P2b: bit planes, 16 bytes per entry ----
+    blk.par([&](int tid) {
+        for (int c = tid; c < n_chunks; c += kThreads) {
+            const uint32_t* ow = reinterpret_cast<const uint32_t*>(sm.oh + c * 16);
+            const uint32_t* tw = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
+            const uint32_t o0 = ow[0], o1 = ow[1], o2 = ow[2], o3 = ow[3];
+            for (int k = 0; k < 8; ++k)
+                sm.plane[k][c] = static_cast<uint16_t>(gather_bit4(o0, k) | (gather_bit4(o1, k) << 4) | (gather_bit4(o2, k) << 8) | (gather_bit4(o3, k) << 12));
+            uint32_t ap = 0;
+            for (int j = 0; j < 4; ++j) {
+                uint32_t x = tw[j] ^ 0x27272727u;                      // a zero byte marks an apostrophe
+                uint32_t z = (x - 0x01010101u) & ~x & 0x80808080u;
+                // the borrow trick can flag a byte above a true zero; apostrophes are rare, so check exactly
+                if (z) for (int k = 0; k < 4; ++k) if (((tw[j] >> (8 * k)) & 0xFFu) == 0x27u) ap |= 1u << (j * 4 + k);
+            }
+            sm.plane[PL_AP][c] = static_cast<uint16_t>(ap);
+        }
+    });
 
     Win w;
     w.sm = &sm; w.a = &a; w.lo = lo; w.n = n;
     w.vlo = lo < 0 ? 0 : lo + static_cast<int>(a.tb.added_max_bytes);
     w.vhi = lo + kWin < n ? lo + kWin : n;
 
-    // ---- P3: boundary bits for the tile's own bytes ----
+    // ---- P3: boundary bits, 32 bytes per thread as 64-bit planes with 16-bit margins ----
+    // Bit i of a plane is byte i; "<< 1" moves a fact from a byte to the byte after it.
+    // Cases the plane algebra does not cover are marked uncertain and decided one by one
+    // by is_boundary(): anything within three bytes after an apostrophe (contractions),
+    // plain whitespace right after a newline (needs run walks), and words holding stray
+    // continuation bytes or added-token literals.
     blk.par([&](int tid) {
-        uint32_t bnd = 0, add = 0, pend = 0, lead = 0, nlead = 0, nstart = 0;
-        for (int k = 0; k < kPer; ++k) {
-            int i = kHaloL + tid * kPer + k, p = lo + i;
-            if (p >= n) break;
-            uint8_t a0 = sm.attr[i];
-            int cls = a0 & A_CLS;
-            if (cls == A_CONT) { if (a0 & A_DOC) bnd |= 1u << k; continue; }
-            lead |= 1u << k;
-            if (cls == A_ADDED) { bnd |= 1u << k; add |= 1u << k; continue; }
-            bool pending = false, ns = false;
-            bool b = is_boundary(w, p, a0, family, &pending, &ns);
-            if (b) bnd |= 1u << k;
-            if (pending) pend |= 1u << k;
-            if (cls == A_N) { nlead |= 1u << k; if (ns) nstart |= 1u << k; }
+        if (tid >= kTileWords) return;
+        const int ww = kHaloL / 32 + tid;
+        auto load = [&](int k) -> uint64_t {
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(sm.plane[k]);
+            return (static_cast<uint64_t>(pw[ww - 1]) >> 16) | (static_cast<uint64_t>(pw[ww]) << 16) | (static_cast<uint64_t>(pw[ww + 1]) << 48);
+        };
+        const uint64_t OWN = 0x0000FFFFFFFF0000ull;
+        const uint64_t L = load(PL_L), N = load(PL_N), S = load(PL_S), O = load(PL_O), C = load(PL_C), AD = load(PL_AD);
+        const uint64_t CR = load(PL_CRLF), SP = load(PL_SP), AP = load(PL_AP);
+        const uint64_t DOC = (static_cast<uint64_t>(sm.dsw[ww - 1]) >> 16) | (static_cast<uint64_t>(sm.dsw[ww]) << 16) | (static_cast<uint64_t>(sm.dsw[ww + 1]) << 48);
+        const uint64_t LEAD = L | N | S | O | AD;
+        auto fill = [&](uint64_t x) -> uint64_t {      // spread a lead's bit over its continuation bytes
+            x |= (x << 1) & C; x |= (x << 1) & C; x |= (x << 1) & C;
+            return x;
+        };
+        auto prevcp = [&](uint64_t x) -> uint64_t {    // at each lead: x of the codepoint before it (0 at a document start)
+            return (fill(x) << 1) & LEAD & ~DOC;
+        };
+        auto nextcp = [&](uint64_t x) -> uint64_t {    // at each lead: x of the codepoint after it (0 at a document end)
+            uint64_t y = (x & ~DOC) >> 1;              // lands on the last byte of the codepoint before
+            y |= (y & C) >> 1; y |= (y & C) >> 1; y |= (y & C) >> 1;
+            return y & LEAD;
+        };
+        const uint64_t pL = prevcp(L), pN = prevcp(N), pS = prevcp(S), pO = prevcp(O);
+        const uint64_t pSP = prevcp(SP), pCR = prevcp(CR);
+        const uint64_t pNone = LEAD & ~(pL | pN | pS | pO);
+        uint64_t bnd = 0, pend = 0, unc = 0;
+        // words the algebra cannot be trusted on
+        // (a continuation byte right after an apostrophe stretches a contraction past three bytes)
+        const bool messy = (C & (C << 1) & (C << 2) & (C << 3)) != 0 || (DOC & C) != 0 || AD != 0 ||
+                           (((AP << 1) | (AP << 2) | (AP << 3)) & C) != 0;
+        if (messy) unc = LEAD;
+        unc |= (AP | (AP << 1) | (AP << 2) | (AP << 3)) & LEAD;
+        bnd |= AD | (DOC & C) | pNone;
+        if (family == 0) {
+            const uint64_t nNonS = nextcp(L | N | O);
+            bnd |= S & (~pS | nNonS);
+            const uint64_t rest = (L | N | O) & ~pSP;          // a literal space before leads the token
+            bnd |= rest & ((L & ~pL) | (N & ~pN) | (O & ~pO));
+        } else {
+            const uint64_t nNonS = nextcp(L | N | O);
+            const uint64_t Scr = S & CR, Spl = S & ~CR;
+            bnd |= Scr & (pL | pN);
+            bnd |= Spl & ~pS;
+            bnd |= Spl & pS & ~pCR & nNonS;
+            unc |= Spl & pS & pCR;
+            const uint64_t ppOorSP = prevcp(pO | pSP);         // prev-prev is punctuation or a literal space
+            bnd |= L & ((pS & pCR) | (pO & ppOorSP) | pN);
+            if (family == 2) bnd |= N;
+            else { bnd |= N & ~pN; pend = N & pN; }
+            bnd |= O & ~pO & ~pSP;
         }
-        sm.bnd16[tid] = static_cast<uint16_t>(bnd);
-        sm.add16[tid] = static_cast<uint16_t>(add);
-        sm.pend16[tid] = static_cast<uint16_t>(pend);
-        sm.lead16[tid] = static_cast<uint16_t>(lead);
-        sm.nlead16[tid] = static_cast<uint16_t>(nlead);
-        sm.nstart16[tid] = static_cast<uint16_t>(nstart);
+        bnd &= ~unc;
+        pend &= ~unc;
+        uint64_t nstart = N & ~pN;
+        // one-by-one decisions
+        uint64_t todo = unc & OWN;
+        while (todo) {
+#if defined(__CUDA_ARCH__)
+            const int bit = __ffsll(static_cast<long long>(todo)) - 1;
+#else
+            const int bit = __builtin_ctzll(todo);
+#endif
+            todo &= todo - 1;
+            const int i = ww * 32 + bit - 16, p = lo + i;
+            const uint8_t a0 = sm.attr[i];
+            const uint64_t m = 1ull << bit;
+            if ((a0 & A_CLS) == A_ADDED) { bnd |= m; continue; }
+            bool pending = false, ns = false;
+            const bool bb = is_boundary(w, p, a0, family, &pending, &ns);
+            if (bb) bnd |= m; else bnd &= ~m;
+            if (pending) pend |= m; else pend &= ~m;
+            if ((a0 & A_CLS) == A_N) { if (ns) nstart |= m; else nstart &= ~m; }
+        }
+        uint32_t* bndw = reinterpret_cast<uint32_t*>(sm.bnd16);
+        reinterpret_cast<uint32_t*>(sm.bnd16)[tid] = static_cast<uint32_t>((bnd & OWN) >> 16);
+        reinterpret_cast<uint32_t*>(sm.add16)[tid] = static_cast<uint32_t>((AD & OWN) >> 16);
+        reinterpret_cast<uint32_t*>(sm.pend16)[tid] = static_cast<uint32_t>((pend & OWN) >> 16);
+        reinterpret_cast<uint32_t*>(sm.lead16)[tid] = static_cast<uint32_t>((LEAD & OWN) >> 16);
+        reinterpret_cast<uint32_t*>(sm.nlead16)[tid] = static_cast<uint32_t>((N & OWN) >> 16);
+        reinterpret_cast<uint32_t*>(sm.nstart16)[tid] = static_cast<uint32_t>((nstart & OWN) >> 16);
+        (void)bndw;
     });
 
     // ---- P4: index of each digit in its run (Llama-3 \p{N}{1,3}) ----
@@ -747,7 +926,8 @@ struct MergeSmem {
     alignas(16) uint8_t txt[kTile + 64];
     uint32_t bm[kTileWords + 4];
     uint32_t am[kTileWords + 4];
-    uint32_t tok[kTile + 16];
+    uint32_t tok[kTile + kTokExtra];
+    uint32_t med[kMaxTeam];
     uint16_t miss[kTile];
     uint32_t team_g[kMaxTeam], team_len[kMaxTeam], team_cnt[kMaxTeam];
     uint32_t b2i[256];
@@ -756,7 +936,7 @@ struct MergeSmem {
     uint32_t red[kThreads + 8];
     uint32_t ctr[16];
 };
-enum { C_NMISS = 0, C_NTEAM = 1, C_TEAMNEXT = 2, C_NBLOCK = 3, C_BASE = 4, C_TOTAL = 5, C_TMP = 6, C_TMP2 = 7 };
+enum { C_NMISS = 0, C_NTEAM = 1, C_NMED = 2, C_NBLOCK = 3, C_BASE = 4, C_TOTAL = 5, C_TMP = 6, C_TMP2 = 7 };
 
 // Greedy BPE of one short pre-token by a single thread; symbols, ranks and
 // results live in shared-memory rows laid out [slot][row] so that threads
@@ -798,6 +978,55 @@ GTOK_DEV uint32_t bpe_thread(const EncodeArgs& a, const uint32_t* b2i, const uin
     }
     for (uint32_t i = 0; i < m; ++i) out[i] = ids[i * kRows];
     return m;
+}
+
+// The same greedy loop for pre-tokens of up to 64 bytes.  Merged-away symbols are
+// marked dead in place instead of shifting the tail down, so a step costs one pass
+// over the slots plus two probes; rows are laid out [slot][row] with 32 rows.
+GTOK_DEV uint32_t bpe_thread_med(const EncodeArgs& a, const uint32_t* b2i, const uint8_t* bytes, uint32_t len,
+                                 uint32_t* ws, uint32_t row, uint32_t* out) {
+    constexpr uint32_t kDead = 0xFFFFFFFFu;
+    uint32_t* ids = ws + row;
+    uint32_t* rk = ws + kMedRows * kMedWordMax + row;
+    uint32_t* nw = ws + 2 * kMedRows * kMedWordMax + row;
+    for (uint32_t i = 0; i < len; ++i) ids[i * kMedRows] = b2i[bytes[i]];
+    for (uint32_t i = 0; i + 1 < len; ++i) {
+        RankRes r = probe_rule(a.tb, ids[i * kMedRows], ids[(i + 1) * kMedRows]);
+        rk[i * kMedRows] = r.rank;
+        nw[i * kMedRows] = r.res;
+    }
+    rk[(len - 1) * kMedRows] = kNoRank;
+    for (;;) {
+        uint32_t best = kNoRank, bi = 0;
+        for (uint32_t i = 0; i < len; ++i) {
+            uint32_t r = rk[i * kMedRows];
+            if (r < best) { best = r; bi = i; }
+        }
+        if (best == kNoRank) break;
+        uint32_t j = bi + 1;
+        while (ids[j * kMedRows] == kDead) ++j;
+        uint32_t k = j + 1;
+        while (k < len && ids[k * kMedRows] == kDead) ++k;
+        ids[bi * kMedRows] = nw[bi * kMedRows];
+        ids[j * kMedRows] = kDead;
+        rk[j * kMedRows] = kNoRank;
+        if (k < len) {
+            RankRes r = probe_rule(a.tb, ids[bi * kMedRows], ids[k * kMedRows]);
+            rk[bi * kMedRows] = r.rank; nw[bi * kMedRows] = r.res;
+        } else rk[bi * kMedRows] = kNoRank;
+        int p = static_cast<int>(bi) - 1;
+        while (p >= 0 && ids[p * kMedRows] == kDead) --p;
+        if (p >= 0) {
+            RankRes r = probe_rule(a.tb, ids[p * kMedRows], ids[bi * kMedRows]);
+            rk[p * kMedRows] = r.rank; nw[p * kMedRows] = r.res;
+        }
+    }
+    uint32_t c = 0;
+    for (uint32_t i = 0; i < len; ++i) {
+        uint32_t v = ids[i * kMedRows];
+        if (v != kDead) out[c++] = v;
+    }
+    return c;
 }
 
 // Team (warp or whole block) BPE over arrays ids/rk/nw of n symbols, which may live
@@ -1001,7 +1230,7 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
             sm.am[wd] = (tb.added_max_bytes && gw < n_words) ? ldg(a.amask + gw) : 0u;
         }
         sm.b2i[tid] = ldg(tb.byte_to_id + tid);
-        for (int i = tid; i < kTile + 16; i += kThreads) sm.tok[i] = kInvalidTok;
+        for (int i = tid; i < kTile + kTokExtra; i += kThreads) sm.tok[i] = kInvalidTok;
         if (tid < 16) sm.ctr[tid] = 0;
     });
 
@@ -1037,7 +1266,12 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
                 sm.tok[o] = id;
                 continue;
             }
-            if (len == 0 || len > kThreadWordMax) {
+            if (len > kThreadWordMax && len <= kMedWordMax) {
+                uint32_t slot = shared_add(&sm.ctr[C_NMED], 1u);
+                sm.med[slot] = o | (len << 16);
+                continue;
+            }
+            if (len == 0 || len > kMedWordMax) {
                 uint32_t slot = shared_add(&sm.ctr[C_NTEAM], 1u);
                 if (slot < kMaxTeam) { sm.team_g[slot] = g; sm.team_len[slot] = len; sm.team_cnt[slot] = 0; sm.tok[o] = kLongRef | slot; }
                 continue;
@@ -1068,6 +1302,26 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
                 uint32_t mv = sm.miss[base + tid];
                 uint32_t o = mv & 0xFFFu, len = (mv >> 12) + 1u;
                 bpe_thread(a, sm.b2i, sm.txt + o, len, sm.ws, tid, sm.tok + o);
+            });
+        }
+    }
+
+    // ---- Q2b: pre-tokens of 17..64 bytes, still one thread each, 32 at a time ----
+    {
+        const uint32_t n_med = sm.ctr[C_NMED];
+        for (uint32_t base = 0; base < n_med; base += kMedRows) {
+            blk.par([&](int tid) {
+                // four lanes of each warp work, so the eight warps share the rows
+                if ((tid & 31) >= kMedRows / 8) return;
+                uint32_t row = (tid & 31) * 8 + (tid >> 5);
+                if (base + row >= n_med) return;
+                uint32_t mv = sm.med[base + row];
+                uint32_t o = mv & 0xFFFFu, len = mv >> 16;
+                if (tb.ignore_merges) {
+                    uint32_t id = probe_long(tb, a.text, t0 + o, len);
+                    if (id != kNoToken) { sm.tok[o] = id; return; }
+                }
+                bpe_thread_med(a, sm.b2i, sm.txt + o, len, sm.ws, row, sm.tok + o);
             });
         }
     }
@@ -1118,7 +1372,7 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
     // ---- Q4: how many tokens does each thread's stretch of tok[] stand for ----
     blk.par([&](int tid) {
         uint32_t sum = 0;
-        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? 16 : 0);
+        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? kTokExtra : 0);
         for (int i = lo; i < hi; ++i) {
             uint32_t v = sm.tok[i];
             if (v == kInvalidTok) continue;
@@ -1131,25 +1385,12 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
     blk.excl_scan(sm.scan, &total);
 
     // ---- Q5: tile base by decoupled look-back ----
-    blk.par([&](int tid) {
-        if (tid != 0) return;
-        unsigned long long mine = (tile == 0 ? kStFinal : kStAgg) | total;
-        store_state(a.st2 + tile, mine);
-        uint32_t base = 0;
-        for (int j = tile - 1; j >= 0; --j) {
-            unsigned long long v = wait_state(a.st2, j, a.ctl);
-            base += static_cast<uint32_t>(v);
-            if ((v >> 62) == 2) break;
-        }
-        if (tile > 0) store_state(a.st2 + tile, kStFinal | (base + total));
-        sm.ctr[C_BASE] = base;
-    });
-    const uint32_t base = sm.ctr[C_BASE];
+    const uint32_t base = blk.lookback(a.st2, tile, total, a.ctl);
 
     // ---- Q6: tokens to their final place ----
     blk.par([&](int tid) {
         uint32_t at = base + sm.scan[tid];
-        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? 16 : 0);
+        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? kTokExtra : 0);
         for (int i = lo; i < hi; ++i) {
             uint32_t v = sm.tok[i];
             if (v == kInvalidTok) continue;

@@ -49,6 +49,41 @@ struct GpuBlk {
         *total = tot;
         __syncthreads();
     }
+    // Publishes this tile's total and returns the sum of all earlier tiles' totals: warp 0
+    // reads 32 predecessors' states at a time, adds them up to the nearest one whose value
+    // already includes everything before it.
+    __device__ __forceinline__ uint32_t lookback(unsigned long long* st, int tile, uint32_t total, uint32_t* ctl) {
+        __shared__ uint32_t s_base;
+        if (threadIdx.x < 32) {
+            const int lane = threadIdx.x;
+            if (lane == 0) store_state(st + tile, (tile == 0 ? kStFinal : kStAgg) | total);
+            uint32_t base = 0;
+            int hi = tile - 1;
+            bool done = tile == 0;
+            while (!done) {
+                const int j = hi - lane;
+                unsigned long long v = kStFinal;
+                if (j >= 0) v = wait_state(st, j, ctl);
+                const unsigned fin = __ballot_sync(0xFFFFFFFFu, (v >> 62) == 2);
+                uint32_t val = static_cast<uint32_t>(v);
+                if (fin) {
+                    const int first = __ffs(fin) - 1;
+                    if (lane > first) val = 0;
+                    done = true;
+                }
+                base += __reduce_add_sync(0xFFFFFFFFu, val);
+                hi -= 32;
+            }
+            if (lane == 0) {
+                if (tile > 0) store_state(st + tile, kStFinal | (base + total));
+                s_base = base;
+            }
+        }
+        __syncthreads();
+        const uint32_t b = s_base;
+        __syncthreads();
+        return b;
+    }
     __device__ __forceinline__ uint32_t reduce_min(uint32_t* arr) {
         __shared__ uint32_t wmin[kThreads / 32];
         const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;

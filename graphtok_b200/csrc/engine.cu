@@ -121,6 +121,7 @@ struct Engine::Impl {
         dt.family = ht.family;
         dt.ignore_merges = ht.ignore_merges;
         dt.monotone = ht.monotone;
+        dt.added_ws = ht.added_ws;
         return true;
     }
 

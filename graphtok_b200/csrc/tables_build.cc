@@ -158,6 +158,9 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
 
     // ---- added-token trie ---------------------------------------------------
     out.added_max_bytes = hv.added_max_bytes;
+    out.added_ws = 0;
+    for (const AddedToken& a : hv.added)
+        for (unsigned char c : a.content) if (c == 0x20 || c == 0x0A || c == 0x0D) out.added_ws = 1;
     if (hv.added_max_bytes > kMaxAddedBytes) {
         err = "an added-token literal is longer than the on-device matcher supports";
         return false;

@@ -21,7 +21,7 @@ struct HostTables {
     std::vector<uint32_t> trie_root, trie_first, trie_terminal, trie_edges;
     std::vector<uint16_t> trie_count;
     uint32_t added_max_bytes = 0;
-    uint32_t family = 0, ignore_merges = 0, monotone = 1;
+    uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0;
 };
 
 // Returns false (with a reason) when a table cannot be built within its probe

@@ -43,6 +43,15 @@ def tile_crossers(special):
             out.append(base + mid + " tail end.")
             if special:
                 out.append(base + special + mid + special + special + " t")
+    # run walks that leave the tile window (plain whitespace right after a very long newline stretch,
+    # and a very long stretch of spaces right after a newline)
+    for head in ("a", ".", "1", ""):
+        out.append("lead " + head + "\n" * 9000 + "  x")
+        out.append("lead " + head + "\r\n" * 4500 + " \tx")
+    out.append("k\n" + " " * 9000 + "x")
+    out.append("k\n" + " " * 9000 + "\n x")
+    out.append("k\n" + " " * 9000)
+    out.append("k\n" + " " * 5000 + "\t" + " " * 5000 + "\n\nq")
     out.append("z" * (3 * TILE + 17))
     out.append("9" * (2 * TILE + 5) + " " + "8" * 100)
     out.append((" " * (TILE + 100)) + "x")

@@ -29,6 +29,15 @@ struct CpuBlk {
         for (int i = 0; i < gtok::kThreads; ++i) { uint32_t v = arr[i]; arr[i] = acc; acc += v; }
         *total = acc;
     }
+    uint32_t lookback(unsigned long long* st, int tile, uint32_t total, uint32_t*) {
+        uint32_t base = 0;
+        for (int j = tile - 1; j >= 0; --j) {
+            base += static_cast<uint32_t>(st[j]);
+            if ((st[j] >> 62) == 2) break;
+        }
+        st[tile] = gtok::kStFinal | (base + total);
+        return base;
+    }
     uint32_t reduce_min(uint32_t* arr) {
         uint32_t m = 0xFFFFFFFFu;
         for (int i = 0; i < gtok::kThreads; ++i) if (arr[i] < m) m = arr[i];
@@ -70,6 +79,7 @@ void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
     tb.trie_terminal = ht.trie_terminal.data(); tb.trie_edges = ht.trie_edges.data();
     tb.added_max_bytes = ht.added_max_bytes; tb.family = ht.family; tb.ignore_merges = ht.ignore_merges;
     tb.monotone = ht.monotone;
+    tb.added_ws = ht.added_ws;
     return e;
 }
 
