@@ -50,12 +50,9 @@ constexpr uint32_t kLongRef = 0x80000000u;      // tok[] entry that stands for a
 constexpr uint32_t kDirty = 0xFFFFFFFEu;
 constexpr uint32_t kReprobe = 0xFFFFFFFEu;
 
-constexpr int kThreadWordMax = 16;   // longest pre-token merged by a single thread
-constexpr int kMedWordMax = 64;      // longest pre-token merged by a single thread (second pass, fewer rows)
-constexpr int kMedRows = 32;
+constexpr int kMedWordMax = 64;      // longest pre-token merged by a single thread
 constexpr int kTokExtra = 64;        // token slots past the tile for pre-tokens that start in it
-constexpr int kRows = 128;           // single-thread merge rows per batch
-constexpr int kWsWords = kRows * kThreadWordMax * 3;   // 6144 u32 = 24 KB, shared by all merge paths
+constexpr int kWsWords = 6144;       // u32 words (24 KB) shared by all merge paths: a 2048-symbol arena of ids, ranks, results
 constexpr int kBlockWordSmemMax = kWsWords / 3;        // 2048 symbols
 constexpr int kMaxTeam = 256;        // long pre-tokens starting in one tile (a tile holds < 4096/17 of them)
 
@@ -91,6 +88,7 @@ struct EncodeArgs {
     uint32_t out_cap;
     uint32_t* out_doc_tok;        // [n_docs + 1] token offsets (batch) or nullptr
     uint32_t* status;             // [0] total tokens, [1] error bits (host-visible)
+    unsigned long long* phase_clk; // optional: cycles spent per phase, summed over blocks (diagnostics)
     DeviceTables tb;
 };
 
@@ -152,6 +150,20 @@ GTOK_DEV void store_state(unsigned long long* p, unsigned long long v) {
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 #else
     *p = v;
+#endif
+}
+GTOK_DEV unsigned long long cycle_now() {
+#if defined(__CUDA_ARCH__)
+    return clock64();
+#else
+    return 0;
+#endif
+}
+GTOK_DEV void add_cycles(unsigned long long* p, unsigned long long v) {
+#if defined(__CUDA_ARCH__)
+    atomicAdd(p, v);
+#else
+    *p += v;
 #endif
 }
 GTOK_DEV void backoff() {
@@ -235,6 +247,51 @@ GTOK_DEV uint32_t probe_long(const DeviceTables& tb, const uint8_t* text, uint32
     return kNoToken;
 }
 
+// Same lookup with the bytes at hand (shared memory).
+GTOK_DEV uint32_t probe_long_bytes(const DeviceTables& tb, const uint8_t* bytes, uint32_t len) {
+    if (len > tb.long_max_len) return kNoToken;
+    uint64_t h = kLongHashSeed;
+    for (uint32_t i = 0; i < len; ++i) h = long_hash_step(h, bytes[i]);
+    h = long_hash_finish(h, len);
+    uint32_t at = static_cast<uint32_t>(h) & tb.long_mask;
+    for (int i = 0; i < kProbeLimit; ++i) {
+        LongSlot s = tb.longtab[at];
+        if (s.id == kNoToken) return kNoToken;
+        if (s.hash == h && s.len == len) {
+            bool same = true;
+            for (uint32_t k = 0; k < len && same; ++k) same = ldg(tb.long_blob + s.off + k) == bytes[k];
+            if (same) return s.id;
+        }
+        at = (at + 1) & tb.long_mask;
+    }
+    return kNoToken;
+}
+
+// Two independent rule probes whose first loads are issued back to back, so that the
+// pair costs one memory round trip instead of two.
+GTOK_DEV void probe_rule2(const DeviceTables& tb, bool want1, uint32_t l1, uint32_t r1, RankRes* o1,
+                          bool want2, uint32_t l2, uint32_t r2, RankRes* o2) {
+    *o1 = RankRes{kNoRank, 0};
+    *o2 = RankRes{kNoRank, 0};
+#if defined(__CUDA_ARCH__)
+    const uint32_t h1 = merge_hash(l1, r1) & tb.merge_mask, h2 = merge_hash(l2, r2) & tb.merge_mask;
+    uint4 s1 = make_uint4(kEmptyKey, 0, 0, 0), s2 = make_uint4(kEmptyKey, 0, 0, 0);
+    if (want1) s1 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h1);
+    if (want2) s2 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h2);
+    if (want1) {
+        if (s1.x == l1 && s1.y == r1) *o1 = RankRes{s1.z, s1.w};
+        else if (s1.x != kEmptyKey) *o1 = probe_rule(tb, l1, r1);
+    }
+    if (want2) {
+        if (s2.x == l2 && s2.y == r2) *o2 = RankRes{s2.z, s2.w};
+        else if (s2.x != kEmptyKey) *o2 = probe_rule(tb, l2, r2);
+    }
+#else
+    if (want1) *o1 = probe_rule(tb, l1, r1);
+    if (want2) *o2 = probe_rule(tb, l2, r2);
+#endif
+}
+
 // ---- document-start bits ---------------------------------------------------------
 GTOK_DEV bool is_docstart_global(const EncodeArgs& a, int p) {
     if (p == 0) return true;
@@ -272,6 +329,7 @@ struct PretokSmem {
     uint32_t sum_has[32], sum_cnt[32];
     uint32_t scan[kThreads];
     uint32_t misc[8];
+    unsigned long long clk_last;
 };
 
 // View of one tile's window for the predicate code.
@@ -610,6 +668,17 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     const int lo = t0 - kHaloL;
     const uint32_t family = a.tb.family;
     const int n_chunks = kWin / 16;
+    // Diagnostics only: cycles between phase ends, block-summed into phase_clk[slot].
+    auto mark = [&](int slot) {
+        if (!a.phase_clk) return;
+        blk.par([&](int tid) {
+            if (tid != 0) return;
+            unsigned long long t = cycle_now();
+            if (slot >= 0) add_cycles(a.phase_clk + slot, t - sm.clk_last);
+            sm.clk_last = t;
+        });
+    };
+    mark(-1);
 
     // ---- P0: stage the window; ASCII lookup table ----
     blk.par([&](int tid) {
@@ -647,6 +716,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         }
     });
 
+    mark(0);
     auto sm_is_doc = [&](int p) -> bool {   // p within [lo, lo + kWin + 64)
         int i = p - lo;
         return (sm.dsw[i >> 5] >> (i & 31)) & 1u;
@@ -684,6 +754,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         }
     });
 
+    mark(1);
     // ---- P2: paint added-token literals ----
     if (a.tb.added_max_bytes) {
         blk.par([&](int tid) {
@@ -706,6 +777,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         });
     }
 
+    mark(2);
     // ---- P2b: bit planes, 16 bytes per entry ----
     blk.par([&](int tid) {
         for (int c = tid; c < n_chunks; c += kThreads) {
@@ -725,6 +797,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         }
     });
 
+    mark(3);
     Win w;
     w.sm = &sm; w.a = &a; w.lo = lo; w.n = n;
     w.vlo = lo < 0 ? 0 : lo + static_cast<int>(a.tb.added_max_bytes);
@@ -821,6 +894,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         (void)bndw;
     });
 
+    mark(4);
     // ---- P4: index of each digit in its run (Llama-3 \p{N}{1,3}) ----
     if (family == 1) {
         const uint32_t* leadw = reinterpret_cast<const uint32_t*>(sm.lead16);
@@ -903,6 +977,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         });
     }
 
+    mark(5);
     // ---- P5: write the bit masks, count boundaries ----
     blk.par([&](int tid) {
         uint32_t cnt = 0;
@@ -917,6 +992,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     uint32_t total = 0;
     blk.excl_scan(sm.scan, &total);
     blk.par([&](int tid) { if (tid == 0) a.tile_nb[tile] = total; });
+    mark(6);
 }
 
 // ==================================================================================
@@ -927,103 +1003,51 @@ struct MergeSmem {
     uint32_t bm[kTileWords + 4];
     uint32_t am[kTileWords + 4];
     uint32_t tok[kTile + kTokExtra];
-    uint32_t med[kMaxTeam];
-    uint16_t miss[kTile];
+    uint16_t wl[kTile + 8];            // offsets in the tile of the pre-token starts, in order; then the end sentinel
+    uint32_t miss[kTile / 2];          // pre-tokens of 2..64 bytes the table did not know: offset | len << 12
+    uint32_t aoff[kThreads];           // arena offset of each pre-token of the current batch
     uint32_t team_g[kMaxTeam], team_len[kMaxTeam], team_cnt[kMaxTeam];
     uint32_t b2i[256];
     uint32_t scan[kThreads];
     uint32_t ws[kWsWords];
     uint32_t red[kThreads + 8];
     uint32_t ctr[16];
+    unsigned long long clk_last;
 };
-enum { C_NMISS = 0, C_NTEAM = 1, C_NMED = 2, C_NBLOCK = 3, C_BASE = 4, C_TOTAL = 5, C_TMP = 6, C_TMP2 = 7 };
+enum { C_NMISS = 0, C_NTEAM = 1, C_NWORDS = 2, C_USED = 3, C_BASE = 4, C_TOTAL = 5, C_TMP = 6, C_TMP2 = 7 };
 
-// Greedy BPE of one short pre-token by a single thread; symbols, ranks and
-// results live in shared-memory rows laid out [slot][row] so that threads
-// working on the same slot hit different banks.
-GTOK_DEV uint32_t bpe_thread(const EncodeArgs& a, const uint32_t* b2i, const uint8_t* bytes, uint32_t len,
-                             uint32_t* ws, int row, uint32_t* out) {
-    uint32_t* ids = ws + row;
-    uint32_t* rk = ws + kRows * kThreadWordMax + row;
-    uint32_t* nw = ws + 2 * kRows * kThreadWordMax + row;
-    uint32_t m = len;
-    for (uint32_t i = 0; i < m; ++i) ids[i * kRows] = b2i[bytes[i]];
-    for (uint32_t i = 0; i + 1 < m; ++i) {
-        RankRes r = probe_rule(a.tb, ids[i * kRows], ids[(i + 1) * kRows]);
-        rk[i * kRows] = r.rank;
-        nw[i * kRows] = r.res;
-    }
-    while (m > 1) {
-        uint32_t best = kNoRank, bi = 0;
-        for (uint32_t i = 0; i + 1 < m; ++i) {
-            uint32_t r = rk[i * kRows];
-            if (r < best) { best = r; bi = i; }
-        }
-        if (best == kNoRank) break;
-        ids[bi * kRows] = nw[bi * kRows];
-        for (uint32_t i = bi + 1; i + 1 < m; ++i) {
-            ids[i * kRows] = ids[(i + 1) * kRows];
-            rk[i * kRows] = rk[(i + 1) * kRows];
-            nw[i * kRows] = nw[(i + 1) * kRows];
-        }
-        --m;
-        if (bi + 1 < m) {
-            RankRes r = probe_rule(a.tb, ids[bi * kRows], ids[(bi + 1) * kRows]);
-            rk[bi * kRows] = r.rank; nw[bi * kRows] = r.res;
-        } else rk[bi * kRows] = kNoRank;
-        if (bi > 0) {
-            RankRes r = probe_rule(a.tb, ids[(bi - 1) * kRows], ids[bi * kRows]);
-            rk[(bi - 1) * kRows] = r.rank; nw[(bi - 1) * kRows] = r.res;
-        }
-    }
-    for (uint32_t i = 0; i < m; ++i) out[i] = ids[i * kRows];
-    return m;
-}
-
-// The same greedy loop for pre-tokens of up to 64 bytes.  Merged-away symbols are
-// marked dead in place instead of shifting the tail down, so a step costs one pass
-// over the slots plus two probes; rows are laid out [slot][row] with 32 rows.
-GTOK_DEV uint32_t bpe_thread_med(const EncodeArgs& a, const uint32_t* b2i, const uint8_t* bytes, uint32_t len,
-                                 uint32_t* ws, uint32_t row, uint32_t* out) {
+// Greedy BPE of one pre-token by a single thread (lowest rank first, leftmost among
+// equals, src/host_encode.cc:617-648).  ids/rk/nw are the pre-token's stretch of the
+// block's symbol arena with the pair ranks already probed; merged-away symbols are
+// marked dead in place, so a step is one pass over the slots plus one round trip for
+// the two new pairs.
+GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint32_t len, uint32_t* out) {
     constexpr uint32_t kDead = 0xFFFFFFFFu;
-    uint32_t* ids = ws + row;
-    uint32_t* rk = ws + kMedRows * kMedWordMax + row;
-    uint32_t* nw = ws + 2 * kMedRows * kMedWordMax + row;
-    for (uint32_t i = 0; i < len; ++i) ids[i * kMedRows] = b2i[bytes[i]];
-    for (uint32_t i = 0; i + 1 < len; ++i) {
-        RankRes r = probe_rule(a.tb, ids[i * kMedRows], ids[(i + 1) * kMedRows]);
-        rk[i * kMedRows] = r.rank;
-        nw[i * kMedRows] = r.res;
-    }
-    rk[(len - 1) * kMedRows] = kNoRank;
     for (;;) {
         uint32_t best = kNoRank, bi = 0;
         for (uint32_t i = 0; i < len; ++i) {
-            uint32_t r = rk[i * kMedRows];
+            uint32_t r = rk[i];
             if (r < best) { best = r; bi = i; }
         }
         if (best == kNoRank) break;
         uint32_t j = bi + 1;
-        while (ids[j * kMedRows] == kDead) ++j;
+        while (ids[j] == kDead) ++j;
         uint32_t k = j + 1;
-        while (k < len && ids[k * kMedRows] == kDead) ++k;
-        ids[bi * kMedRows] = nw[bi * kMedRows];
-        ids[j * kMedRows] = kDead;
-        rk[j * kMedRows] = kNoRank;
-        if (k < len) {
-            RankRes r = probe_rule(a.tb, ids[bi * kMedRows], ids[k * kMedRows]);
-            rk[bi * kMedRows] = r.rank; nw[bi * kMedRows] = r.res;
-        } else rk[bi * kMedRows] = kNoRank;
+        while (k < len && ids[k] == kDead) ++k;
         int p = static_cast<int>(bi) - 1;
-        while (p >= 0 && ids[p * kMedRows] == kDead) --p;
-        if (p >= 0) {
-            RankRes r = probe_rule(a.tb, ids[p * kMedRows], ids[bi * kMedRows]);
-            rk[p * kMedRows] = r.rank; nw[p * kMedRows] = r.res;
-        }
+        while (p >= 0 && ids[p] == kDead) --p;
+        const uint32_t merged = nw[bi];
+        ids[bi] = merged;
+        ids[j] = kDead;
+        rk[j] = kNoRank;
+        RankRes right, left;
+        probe_rule2(a.tb, k < len, merged, k < len ? ids[k] : 0u, &right, p >= 0, p >= 0 ? ids[p] : 0u, merged, &left);
+        rk[bi] = right.rank; nw[bi] = right.res;
+        if (p >= 0) { rk[p] = left.rank; nw[p] = left.res; }
     }
     uint32_t c = 0;
     for (uint32_t i = 0; i < len; ++i) {
-        uint32_t v = ids[i * kMedRows];
+        uint32_t v = ids[i];
         if (v != kDead) out[c++] = v;
     }
     return c;
@@ -1212,6 +1236,16 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
     const uint32_t n_words = n_tiles * kTileWords;
     const DeviceTables& tb = a.tb;
 
+    auto mark = [&](int slot) {
+        if (!a.phase_clk) return;
+        blk.par([&](int tid) {
+            if (tid != 0) return;
+            unsigned long long t = cycle_now();
+            if (slot >= 0) add_cycles(a.phase_clk + slot, t - sm.clk_last);
+            sm.clk_last = t;
+        });
+    };
+    mark(-1);
     // ---- Q0: stage text, bit masks, byte ids ----
     blk.par([&](int tid) {
         for (int c = tid; c < (kTile + 64) / 16; c += kThreads) {
@@ -1234,98 +1268,168 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
         if (tid < 16) sm.ctr[tid] = 0;
     });
 
-    // ---- Q1: every pre-token that starts in this tile ----
+    mark(8);
+    // ---- Q1a: the tile's pre-token starts as an ordered list ----
     blk.par([&](int tid) {
         uint32_t bits = (sm.bm[tid >> 1] >> ((tid & 1) * 16)) & 0xFFFFu;
+        sm.scan[tid] = popc32(bits);
+    });
+    uint32_t n_starts = 0;
+    blk.excl_scan(sm.scan, &n_starts);
+    blk.par([&](int tid) {
+        uint32_t bits = (sm.bm[tid >> 1] >> ((tid & 1) * 16)) & 0xFFFFu;
+        uint32_t at = sm.scan[tid];
         while (bits) {
             int k = ffs32(bits);
             bits &= bits - 1;
-            uint32_t o = tid * kPer + k;          // offset in tile
-            uint32_t g = t0 + o;
-            if (g >= n) break;
-            // next boundary within the staged bits (tile + 64 bytes)
-            uint32_t e_off = 0;                   // 0 = not found
-            {
-                uint32_t wi = (o + 1) >> 5;
-                uint32_t bb = (o + 1) & 31 ? sm.bm[wi] & ~((1u << ((o + 1) & 31)) - 1u) : sm.bm[wi];
-                for (;;) {
-                    if (bb) { e_off = wi * 32 + ffs32(bb); break; }
-                    if (++wi >= kTileWords + 2) break;
-                    bb = sm.bm[wi];
-                }
-            }
-            uint32_t len = 0;                     // 0 = longer than the staged window
-            if (e_off) len = e_off - o;
-            if (e_off == 0 && t0 + kTile + 64 >= n) len = n - g;
-            if (len && g + len > n) len = n - g;
-            if ((sm.txt[o] & 0xC0u) == 0x80u) continue;      // stray continuation bytes opening a document
-            if ((sm.am[o >> 5] >> (o & 31)) & 1u) {
-                uint32_t id = 0;
-                auto byte_at = [&](int q) -> uint32_t { return ldg(a.text + q); };
-                match_literal(a, static_cast<int>(g), static_cast<int>(n), byte_at, &id);
-                sm.tok[o] = id;
-                continue;
-            }
-            if (len > kThreadWordMax && len <= kMedWordMax) {
-                uint32_t slot = shared_add(&sm.ctr[C_NMED], 1u);
-                sm.med[slot] = o | (len << 16);
-                continue;
-            }
-            if (len == 0 || len > kMedWordMax) {
-                uint32_t slot = shared_add(&sm.ctr[C_NTEAM], 1u);
-                if (slot < kMaxTeam) { sm.team_g[slot] = g; sm.team_len[slot] = len; sm.team_cnt[slot] = 0; sm.tok[o] = kLongRef | slot; }
-                continue;
-            }
-            if (len <= kWordKeyMax) {
-                uint64_t k0 = 0, k1 = 0;
-                for (uint32_t i = 0; i < len && i < 8; ++i) k0 |= static_cast<uint64_t>(sm.txt[o + i]) << (8 * i);
-                for (uint32_t i = 8; i < len; ++i) k1 |= static_cast<uint64_t>(sm.txt[o + i]) << (8 * (i - 8));
-                k1 |= static_cast<uint64_t>(len) << 56;
-                uint32_t id = probe_word(tb, k0, k1);
-                if (id != kNoToken) { sm.tok[o] = id; continue; }
-            } else if (tb.ignore_merges) {
-                uint32_t id = probe_long(tb, a.text, g, len);
-                if (id != kNoToken) { sm.tok[o] = id; continue; }
-            }
-            if (len == 1) { sm.tok[o] = sm.b2i[sm.txt[o]]; continue; }
-            uint32_t slot = shared_add(&sm.ctr[C_NMISS], 1u);
-            sm.miss[slot] = static_cast<uint16_t>(o | ((len - 1) << 12));
+            sm.wl[at++] = static_cast<uint16_t>(tid * kPer + k);
+        }
+        if (tid == 0) {
+            // end of the last pre-token: the first boundary in the 64 staged bytes past the tile, if any
+            uint32_t e = 0xFFFFu;
+            if (sm.bm[kTileWords]) e = kTile + ffs32(sm.bm[kTileWords]);
+            else if (sm.bm[kTileWords + 1]) e = kTile + 32 + ffs32(sm.bm[kTileWords + 1]);
+            sm.wl[n_starts] = static_cast<uint16_t>(e);
         }
     });
 
-    // ---- Q2: merge loop for the short pre-tokens the table did not know ----
-    {
-        const uint32_t n_miss = sm.ctr[C_NMISS];
-        for (uint32_t base = 0; base < n_miss; base += kRows) {
-            blk.par([&](int tid) {
-                if (tid >= kRows || base + tid >= n_miss) return;
-                uint32_t mv = sm.miss[base + tid];
-                uint32_t o = mv & 0xFFFu, len = (mv >> 12) + 1u;
-                bpe_thread(a, sm.b2i, sm.txt + o, len, sm.ws, tid, sm.tok + o);
-            });
-        }
-    }
-
-    // ---- Q2b: pre-tokens of 17..64 bytes, still one thread each, 32 at a time ----
-    {
-        const uint32_t n_med = sm.ctr[C_NMED];
-        for (uint32_t base = 0; base < n_med; base += kMedRows) {
-            blk.par([&](int tid) {
-                // four lanes of each warp work, so the eight warps share the rows
-                if ((tid & 31) >= kMedRows / 8) return;
-                uint32_t row = (tid & 31) * 8 + (tid >> 5);
-                if (base + row >= n_med) return;
-                uint32_t mv = sm.med[base + row];
-                uint32_t o = mv & 0xFFFFu, len = mv >> 16;
-                if (tb.ignore_merges) {
-                    uint32_t id = probe_long(tb, a.text, t0 + o, len);
-                    if (id != kNoToken) { sm.tok[o] = id; return; }
+    // ---- Q1b: one table probe per pre-token, four in flight per thread ----
+    blk.par([&](int tid) {
+        for (uint32_t base = tid; base < n_starts; base += kThreads * 4) {
+            uint32_t wo[4], wlen[4], wh[4];
+            uint64_t wk0[4], wk1[4];
+            bool wp[4];
+#if defined(__CUDA_ARCH__)
+            uint4 sa[4], sb[4];
+#endif
+            for (int u = 0; u < 4; ++u) {
+                wp[u] = false;
+                const uint32_t i = base + u * kThreads;
+                if (i >= n_starts) continue;
+                const uint32_t o = sm.wl[i], g = t0 + o;
+                if (g >= n) continue;
+                const uint32_t e = sm.wl[i + 1];
+                uint32_t len = 0;                     // 0 = runs past the staged window
+                if (e != 0xFFFFu) len = e - o;
+                else if (t0 + kTile + 64 >= n) len = n - g;
+                if (len && g + len > n) len = n - g;
+                if ((sm.txt[o] & 0xC0u) == 0x80u) continue;      // stray continuation bytes opening a document
+                if ((sm.am[o >> 5] >> (o & 31)) & 1u) {
+                    uint32_t id = 0;
+                    auto byte_at = [&](int q) -> uint32_t { return ldg(a.text + q); };
+                    match_literal(a, static_cast<int>(g), static_cast<int>(n), byte_at, &id);
+                    sm.tok[o] = id;
+                    continue;
                 }
-                bpe_thread_med(a, sm.b2i, sm.txt + o, len, sm.ws, row, sm.tok + o);
+                if (len == 0 || len > kMedWordMax) {
+                    uint32_t slot = shared_add(&sm.ctr[C_NTEAM], 1u);
+                    if (slot < kMaxTeam) { sm.team_g[slot] = g; sm.team_len[slot] = len; sm.team_cnt[slot] = 0; sm.tok[o] = kLongRef | slot; }
+                    continue;
+                }
+                if (len > kWordKeyMax) {
+                    uint32_t slot = shared_add(&sm.ctr[C_NMISS], 1u);
+                    sm.miss[slot] = o | (len << 12);
+                    continue;
+                }
+                uint64_t k0 = 0, k1 = 0;
+                for (uint32_t b = 0; b < len && b < 8; ++b) k0 |= static_cast<uint64_t>(sm.txt[o + b]) << (8 * b);
+                for (uint32_t b = 8; b < len; ++b) k1 |= static_cast<uint64_t>(sm.txt[o + b]) << (8 * (b - 8));
+                k1 |= static_cast<uint64_t>(len) << 56;
+                wo[u] = o; wlen[u] = len; wk0[u] = k0; wk1[u] = k1;
+                wh[u] = word_hash(k0, k1) & tb.word_mask;
+                wp[u] = true;
+#if defined(__CUDA_ARCH__)
+                const uint4* sp = reinterpret_cast<const uint4*>(tb.word + wh[u]);
+                sa[u] = __ldg(sp);
+                sb[u] = __ldg(sp + 1);
+#endif
+            }
+            for (int u = 0; u < 4; ++u) {
+                if (!wp[u]) continue;
+                uint32_t id;
+#if defined(__CUDA_ARCH__)
+                const uint64_t s0 = (static_cast<uint64_t>(sa[u].y) << 32) | sa[u].x, s1 = (static_cast<uint64_t>(sa[u].w) << 32) | sa[u].z;
+                if (sb[u].x == kNoToken) id = kNoToken;
+                else if (s0 == wk0[u] && s1 == wk1[u]) id = sb[u].x;
+                else id = probe_word(tb, wk0[u], wk1[u]);
+#else
+                id = probe_word(tb, wk0[u], wk1[u]);
+#endif
+                const uint32_t o = wo[u], len = wlen[u];
+                if (id != kNoToken) { sm.tok[o] = id; continue; }
+                if (len == 1) { sm.tok[o] = sm.b2i[sm.txt[o]]; continue; }
+                uint32_t slot = shared_add(&sm.ctr[C_NMISS], 1u);
+                sm.miss[slot] = o | (len << 12);
+            }
+        }
+    });
+
+    mark(9);
+    // ---- Q2: merge loop for the pre-tokens of 2..64 bytes the table did not know ----
+    // A batch takes as many of them as fit the symbol arena (at most one per thread):
+    // the owner lays out the symbols, all threads probe the pairs, the owner merges.
+    {
+        constexpr uint32_t kArena = kWsWords / 3;
+        constexpr uint32_t kPending = 0xFFFFFFFDu;
+        uint32_t* ids = sm.ws;
+        uint32_t* rk = sm.ws + kArena;
+        uint32_t* nw = sm.ws + 2 * kArena;
+        const uint32_t n_miss = sm.ctr[C_NMISS];
+        uint32_t done = 0;
+        while (done < n_miss) {
+            blk.par([&](int tid) {
+                uint32_t idx = done + tid;
+                sm.scan[tid] = idx < n_miss ? (sm.miss[idx] >> 12) : 0u;
             });
+            uint32_t tot = 0;
+            blk.excl_scan(sm.scan, &tot);
+            blk.par([&](int tid) {
+                uint32_t idx = done + tid;
+                uint32_t len = idx < n_miss ? (sm.miss[idx] >> 12) : 0u;
+                bool fits = idx < n_miss && sm.scan[tid] + len <= kArena;
+                sm.red[tid] = fits ? 0xFFFFFFFFu : static_cast<uint32_t>(tid);
+            });
+            uint32_t nb = blk.reduce_min(sm.red);
+            if (nb == 0xFFFFFFFFu) nb = kThreads;
+            blk.par([&](int tid) {
+                if (static_cast<uint32_t>(tid) >= nb) return;
+                const uint32_t mv = sm.miss[done + tid];
+                const uint32_t o = mv & 0xFFFu, len = mv >> 12, at = sm.scan[tid];
+                if (static_cast<uint32_t>(tid) + 1 == nb) sm.ctr[C_USED] = at + len;
+                bool resolved = false;
+                if (tb.ignore_merges && len > kWordKeyMax) {
+                    uint32_t id = probe_long_bytes(tb, sm.txt + o, len);
+                    if (id != kNoToken) { sm.tok[o] = id; resolved = true; }
+                }
+                for (uint32_t i = 0; i < len; ++i) {
+                    ids[at + i] = sm.b2i[sm.txt[o + i]];
+                    rk[at + i] = (!resolved && i + 1 < len) ? kPending : kNoRank;
+                }
+                sm.aoff[tid] = resolved ? 0xFFFFFFFFu : at;
+            });
+            const uint32_t used = sm.ctr[C_USED];
+            blk.par([&](int tid) {
+                for (uint32_t sidx = tid; sidx < used; sidx += kThreads) {
+                    if (rk[sidx] != kPending) continue;
+                    RankRes r = probe_rule(tb, ids[sidx], ids[sidx + 1]);
+                    rk[sidx] = r.rank;
+                    nw[sidx] = r.res;
+                }
+            });
+            blk.par([&](int tid) {
+                if (static_cast<uint32_t>(tid) >= nb) return;
+                const uint32_t at = sm.aoff[tid];
+                if (at == 0xFFFFFFFFu) return;
+                const uint32_t mv = sm.miss[done + tid];
+                const uint32_t o = mv & 0xFFFu, len = mv >> 12;
+                bpe_arena(a, ids + at, rk + at, nw + at, len, sm.tok + o);
+            });
+            done += nb;
         }
     }
+    mark(10);
 
+    mark(11);
     // ---- Q3: long pre-tokens, one at a time, by the whole block ----
     {
         uint32_t n_team = sm.ctr[C_NTEAM];
@@ -1369,34 +1473,54 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
         }
     }
 
+    mark(12);
     // ---- Q4: how many tokens does each thread's stretch of tok[] stand for ----
     blk.par([&](int tid) {
         uint32_t sum = 0;
-        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? kTokExtra : 0);
+        int lo = tid * kPer, hi = lo + kPer;
         for (int i = lo; i < hi; ++i) {
             uint32_t v = sm.tok[i];
             if (v == kInvalidTok) continue;
             sum += (v & kLongRef) ? sm.team_cnt[v & ~kLongRef] : 1u;
         }
         sm.scan[tid] = sum;
-        sm.red[tid] = sum;    // kept: the scan below overwrites sm.scan
+        // slots past the tile (ids of pre-tokens that start in its last bytes): plain ids only
+        if (tid < kTokExtra / kPer) {
+            uint32_t ex = 0;
+            for (int i = kTile + tid * kPer; i < kTile + (tid + 1) * kPer; ++i) ex += sm.tok[i] != kInvalidTok;
+            sm.red[kThreads + tid] = ex;
+        }
     });
-    uint32_t total = 0;
-    blk.excl_scan(sm.scan, &total);
+    uint32_t total_main = 0;
+    blk.excl_scan(sm.scan, &total_main);
+    uint32_t total = total_main;
+    for (int t = 0; t < kTokExtra / kPer; ++t) total += sm.red[kThreads + t];
 
+    mark(13);
     // ---- Q5: tile base by decoupled look-back ----
     const uint32_t base = blk.lookback(a.st2, tile, total, a.ctl);
 
+    mark(14);
     // ---- Q6: tokens to their final place ----
     blk.par([&](int tid) {
         uint32_t at = base + sm.scan[tid];
-        int lo = tid * kPer, hi = lo + kPer + (tid == kThreads - 1 ? kTokExtra : 0);
+        int lo = tid * kPer, hi = lo + kPer;
         for (int i = lo; i < hi; ++i) {
             uint32_t v = sm.tok[i];
             if (v == kInvalidTok) continue;
             if (v & kLongRef) { uint32_t ti = v & ~kLongRef; sm.team_len[ti] = at; at += sm.team_cnt[ti]; continue; }
             if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + 2, kErrOutputFull);
             ++at;
+        }
+        if (tid < kTokExtra / kPer) {
+            at = base + total_main;
+            for (int t = 0; t < tid; ++t) at += sm.red[kThreads + t];
+            for (int i = kTile + tid * kPer; i < kTile + (tid + 1) * kPer; ++i) {
+                uint32_t v = sm.tok[i];
+                if (v == kInvalidTok) continue;
+                if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + 2, kErrOutputFull);
+                ++at;
+            }
         }
     });
     {
@@ -1415,6 +1539,7 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
         }
     }
 
+    mark(15);
     // ---- Q7: per-document token offsets; totals ----
     if (a.out_doc_tok) {
         blk.par([&](int tid) {

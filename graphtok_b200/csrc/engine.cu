@@ -54,6 +54,7 @@ struct Ctx {
     uint32_t *d_gstage = nullptr, *d_grk = nullptr, *d_gnw = nullptr;
     uint32_t *d_out = nullptr, *d_doc_tok = nullptr;
     uint32_t *h_status = nullptr, *d_status = nullptr;
+    unsigned long long* d_phase = nullptr;
     uint8_t* h_text = nullptr;
     uint32_t* h_hdr = nullptr;
     uint32_t* h_out = nullptr;
@@ -77,7 +78,7 @@ struct Ctx {
         if (stream) cudaStreamDestroy(stream);
         cudaFree(d_text); cudaFree(d_hdr); cudaFree(d_docmask); cudaFree(d_bmask); cudaFree(d_amask);
         cudaFree(d_tile_nb); cudaFree(d_ctrl); cudaFree(d_gstage); cudaFree(d_grk); cudaFree(d_gnw);
-        cudaFree(d_out); cudaFree(d_doc_tok);
+        cudaFree(d_out); cudaFree(d_doc_tok); cudaFree(d_phase);
         if (h_status) cudaFreeHost(h_status);
         if (h_text) cudaFreeHost(h_text);
         if (h_hdr) cudaFreeHost(h_hdr);
@@ -180,6 +181,11 @@ struct Engine::Impl {
         a.out_cap = cap_bytes + 16;
         a.out_doc_tok = batch_mode ? c->d_doc_tok : nullptr;
         a.status = c->d_status;
+        if (std::getenv("GTOK_PHASE_CLOCKS")) {
+            GTOK_CUDA(cudaMalloc(&c->d_phase, 32 * sizeof(unsigned long long)));
+            GTOK_CUDA(cudaMemset(c->d_phase, 0, 32 * sizeof(unsigned long long)));
+            a.phase_clk = c->d_phase;
+        }
         a.tb = dt;
 
         // Capture: control block reset, [document mask], pretok, merge.
@@ -424,6 +430,16 @@ int64_t Engine::read_boundaries(uint32_t* out_words, uint32_t max_words) {
     if (words > max_words) return -2;
     if (words && cudaMemcpy(out_words, c->d_bmask, static_cast<size_t>(words) * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return words;
+}
+
+int Engine::read_phase_clocks(unsigned long long* out32, bool reset) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    Ctx* c = im.staged;
+    if (!c || !c->d_phase) return -1;
+    if (cudaMemcpy(out32, c->d_phase, 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (reset) cudaMemset(c->d_phase, 0, 32 * sizeof(unsigned long long));
+    return 0;
 }
 
 const DeviceTables* Engine::device_tables() const { return &impl_->dt; }

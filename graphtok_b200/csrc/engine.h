@@ -39,6 +39,8 @@ public:
     // set where a pre-token starts; writes (len + 31) / 32 words.
     int64_t read_boundaries(uint32_t* out_words, uint32_t max_words);
     // Device-side table block for callers inside the library (no-allocation entry point).
+    // Diagnostics (contexts created with GTOK_PHASE_CLOCKS set): cycles per kernel phase, summed over blocks.
+    int read_phase_clocks(unsigned long long* out32, bool reset);
     const struct DeviceTables* device_tables() const;
     int device_index() const;
 

@@ -207,6 +207,11 @@ int32_t gtok_x_boundaries_noalloc(void* handle, const void* text_dev, uint32_t l
     } catch (...) { return -1; }
 }
 
+int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset) {
+    if (!handle || !out32) return -1;
+    try { return static_cast<Handle*>(handle)->engine->read_phase_clocks(reinterpret_cast<unsigned long long*>(out32), reset != 0); } catch (...) { return -1; }
+}
+
 int32_t gtok_x_plan_chunks(void* handle, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out_offsets) {
     if (!handle || (!text && len) || !n_parts || !out_offsets) return -1;
     try {

@@ -81,6 +81,10 @@ int32_t gtok_x_read_boundaries(void* handle, uint32_t* out_words, uint32_t max_w
 /* The staged input once more, launched kernel by kernel with CUDA events between:
  * ms_out3 = {pre-tokenization kernel, merge kernel, whole sequence}. */
 int32_t gtok_x_profile(void* handle, float* ms_out3);
+/* Diagnostics: when the environment variable GTOK_PHASE_CLOCKS was set as the staged
+ * context was created, SM cycles spent in each phase of the two kernels, summed over
+ * thread blocks since the last reset (slots 0-6 pre-tokenization, 8-15 merge).  -1 if off. */
+int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset);
 /* Sizes in bytes of the merge table, the whole-word table and the remaining tables. */
 void gtok_x_table_bytes(void* handle, uint64_t* out3);
 /* Kernel launches one graph replay performs (single document / batch). */
