@@ -16,7 +16,8 @@ constexpr uint32_t kNoToken = 0xFFFFFFFFu;
 constexpr int kWordKeyMax = 15;        // longest pre-token the inline-key word table holds
 constexpr int kProbeLimit = 64;        // every table is built so that no probe chain is longer
 
-// Merge rule table: open addressing, linear probing, one 16-byte slot per rule.
+// Merge rule table: open addressing over buckets of two 16-byte slots (one 32-byte
+// sector per probe), linear probing over buckets; merge_mask = buckets - 1.
 //   x = left id, y = right id, z = rank, w = result id;  x == kEmptyKey marks a free slot.
 // Replaces the reference's Slot64 / Slot128 pair (src/vocab.h:162-201): the
 // key and the value arrive in a single 128-bit load.

@@ -190,21 +190,29 @@ GTOK_DEV unsigned long long wait_state(const unsigned long long* st, int j, uint
 
 // ---- merge-rule probe ----------------------------------------------------------
 struct RankRes { uint32_t rank, res; };
-GTOK_DEV RankRes probe_rule(const DeviceTables& tb, uint32_t l, uint32_t r) {
-    uint32_t h = merge_hash(l, r) & tb.merge_mask;
+// The merge table is probed a bucket (two slots, one 32-byte sector) at a time: both
+// slots arrive together, a bucket with a free slot ends the search.
+GTOK_DEV RankRes probe_rule_from(const DeviceTables& tb, uint32_t l, uint32_t r, uint32_t bucket) {
     for (int i = 0; i < kProbeLimit; ++i) {
 #if defined(__CUDA_ARCH__)
-        uint4 s = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h);
-        if (s.x == l && s.y == r) return RankRes{s.z, s.w};
-        if (s.x == kEmptyKey) break;
+        const uint4* bp = reinterpret_cast<const uint4*>(tb.merge) + 2 * bucket;
+        uint4 s0 = __ldg(bp), s1 = __ldg(bp + 1);
+        if (s0.x == l && s0.y == r) return RankRes{s0.z, s0.w};
+        if (s1.x == l && s1.y == r) return RankRes{s1.z, s1.w};
+        if (s1.x == kEmptyKey) break;
 #else
-        const MergeSlot& s = tb.merge[h];
-        if (s.left == l && s.right == r) return RankRes{s.rank, s.result};
-        if (s.left == kEmptyKey) break;
+        const MergeSlot& s0 = tb.merge[2 * bucket];
+        const MergeSlot& s1 = tb.merge[2 * bucket + 1];
+        if (s0.left == l && s0.right == r) return RankRes{s0.rank, s0.result};
+        if (s1.left == l && s1.right == r) return RankRes{s1.rank, s1.result};
+        if (s1.left == kEmptyKey) break;
 #endif
-        h = (h + 1) & tb.merge_mask;
+        bucket = (bucket + 1) & tb.merge_mask;
     }
     return RankRes{kNoRank, 0};
+}
+GTOK_DEV RankRes probe_rule(const DeviceTables& tb, uint32_t l, uint32_t r) {
+    return probe_rule_from(tb, l, r, merge_hash(l, r) & tb.merge_mask);
 }
 
 GTOK_DEV uint32_t probe_word(const DeviceTables& tb, uint64_t k0, uint64_t k1) {
@@ -274,17 +282,21 @@ GTOK_DEV void probe_rule2(const DeviceTables& tb, bool want1, uint32_t l1, uint3
     *o1 = RankRes{kNoRank, 0};
     *o2 = RankRes{kNoRank, 0};
 #if defined(__CUDA_ARCH__)
-    const uint32_t h1 = merge_hash(l1, r1) & tb.merge_mask, h2 = merge_hash(l2, r2) & tb.merge_mask;
-    uint4 s1 = make_uint4(kEmptyKey, 0, 0, 0), s2 = make_uint4(kEmptyKey, 0, 0, 0);
-    if (want1) s1 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h1);
-    if (want2) s2 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h2);
+    const uint32_t b1 = merge_hash(l1, r1) & tb.merge_mask, b2 = merge_hash(l2, r2) & tb.merge_mask;
+    const uint4* p1 = reinterpret_cast<const uint4*>(tb.merge) + 2 * b1;
+    const uint4* p2 = reinterpret_cast<const uint4*>(tb.merge) + 2 * b2;
+    uint4 x0 = make_uint4(kEmptyKey, 0, 0, 0), x1 = x0, y0 = x0, y1 = x0;
+    if (want1) { x0 = __ldg(p1); x1 = __ldg(p1 + 1); }
+    if (want2) { y0 = __ldg(p2); y1 = __ldg(p2 + 1); }
     if (want1) {
-        if (s1.x == l1 && s1.y == r1) *o1 = RankRes{s1.z, s1.w};
-        else if (s1.x != kEmptyKey) *o1 = probe_rule(tb, l1, r1);
+        if (x0.x == l1 && x0.y == r1) *o1 = RankRes{x0.z, x0.w};
+        else if (x1.x == l1 && x1.y == r1) *o1 = RankRes{x1.z, x1.w};
+        else if (x1.x != kEmptyKey) *o1 = probe_rule_from(tb, l1, r1, (b1 + 1) & tb.merge_mask);
     }
     if (want2) {
-        if (s2.x == l2 && s2.y == r2) *o2 = RankRes{s2.z, s2.w};
-        else if (s2.x != kEmptyKey) *o2 = probe_rule(tb, l2, r2);
+        if (y0.x == l2 && y0.y == r2) *o2 = RankRes{y0.z, y0.w};
+        else if (y1.x == l2 && y1.y == r2) *o2 = RankRes{y1.z, y1.w};
+        else if (y1.x != kEmptyKey) *o2 = probe_rule_from(tb, l2, r2, (b2 + 1) & tb.merge_mask);
     }
 #else
     if (want1) *o1 = probe_rule(tb, l1, r1);
@@ -322,6 +334,7 @@ struct PretokSmem {
     alignas(16) uint8_t oh[kWin + 16];       // one-hot class + flags per byte (see kOh*)
     alignas(4) uint16_t plane[kPlanes][kWin / 16 + 4];   // bit planes of the window, 16 bytes per entry
     uint16_t lut[128];                       // ASCII byte -> attr | one-hot << 8
+    uint32_t rootbits[8];                    // bytes that can start an added-token literal
     uint32_t dsw[kWin / 32 + 2];             // document-start bits of the window
     uint16_t bnd16[kThreads + 2], add16[kThreads + 2], pend16[kThreads + 2];
     uint16_t lead16[kThreads + 2], nlead16[kThreads + 2], nstart16[kThreads + 2];
@@ -714,6 +727,11 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             if (tid == 0x20) at |= A_SP;
             sm.lut[tid] = static_cast<uint16_t>(at | (onehot_of(at) << 8));
         }
+        if (tid >= 128 && tid < 136 && a.tb.added_max_bytes) {
+            uint32_t bits = 0;
+            for (int k = 0; k < 32; ++k) if (ldg(a.tb.trie_root + (tid - 128) * 32 + k) != kNoToken) bits |= 1u << k;
+            sm.rootbits[tid - 128] = bits;
+        }
     });
 
     mark(0);
@@ -726,7 +744,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         return (i >= 0 && i < kWin) ? sm.txt[i] : ldg(a.text + q);
     };
 
-    // ---- P1: per-byte class and flags (ASCII through the table, the rest decoded) ----
+    // ---- P1: per-byte class and flags (ASCII through the table, the rest decoded after) ----
     blk.par([&](int tid) {
         for (int c = tid; c < n_chunks; c += kThreads) {
             const uint32_t* tw = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
@@ -734,6 +752,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             uint32_t* ow = reinterpret_cast<uint32_t*>(sm.oh + c * 16);
             const int i0 = c * 16, p0 = lo + i0;
             const uint32_t ds = (sm.dsw[i0 >> 5] >> (i0 & 31)) & 0xFFFFu;
+            uint32_t slow = 0;                                  // non-ASCII lead bytes, decoded below
             for (int j = 0; j < 4; ++j) {
                 const uint32_t t = tw[j];
                 uint32_t av = 0, ov = 0;
@@ -742,14 +761,41 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     const uint32_t bt = (t >> (8 * k)) & 0xFFu;
                     uint32_t at, oh;
                     if (p < 0 || p >= n) { at = A_OUT; oh = 0; }
-                    else if (bt < 0x80u) { uint32_t v = sm.lut[bt]; at = v & 0xFFu; oh = v >> 8; if ((ds >> i) & 1u) at |= A_DOC; }
-                    else if ((bt & 0xC0u) == 0x80u) { at = A_CONT | (((ds >> i) & 1u) ? A_DOC : 0); oh = kOhC; }
-                    else { at = plain_attr(a, p, n, byte_any, sm_is_doc); oh = onehot_of(static_cast<uint8_t>(at)); }
+                    else if (bt < 0x80u) { uint32_t v = sm.lut[bt]; at = v & 0xFFu; oh = v >> 8; }
+                    else if ((bt & 0xC0u) == 0x80u) { at = A_CONT; oh = kOhC; }
+                    else { at = A_O; oh = kOhO; slow |= 1u << i; }
+                    if ((ds >> i) & 1u) at |= A_DOC;
                     av |= at << (8 * k);
                     ov |= oh << (8 * k);
                 }
                 aw[j] = av;
                 ow[j] = ov;
+            }
+            while (slow) {
+                const int i = ffs32(slow);
+                slow &= slow - 1;
+                const int wi = i0 + i, p = p0 + i;
+                const uint32_t b = sm.txt[wi];
+                int avail = n - p;
+                if (avail > 4) avail = 4;
+                if (a.docmask) for (int k = 1; k < avail; ++k) if (sm_is_doc(p + k)) { avail = k; break; }
+                uint32_t b1, b2, b3;
+                if (wi + 3 < kWin) { b1 = sm.txt[wi + 1]; b2 = sm.txt[wi + 2]; b3 = sm.txt[wi + 3]; }
+                else { b1 = avail > 1 ? byte_any(p + 1) : 0; b2 = avail > 2 ? byte_any(p + 2) : 0; b3 = avail > 3 ? byte_any(p + 3) : 0; }
+                // lenient decode (src/pretok_boundary.h:43-57): the lead byte decides the width when
+                // that many bytes remain in the document; anything else is a one-byte codepoint
+                uint32_t cp = b;
+                if ((b & 0xE0u) == 0xC0u && avail >= 2) cp = ((b & 0x1Fu) << 6) | (b1 & 0x3Fu);
+                else if ((b & 0xF0u) == 0xE0u && avail >= 3) cp = ((b & 0x0Fu) << 12) | ((b1 & 0x3Fu) << 6) | (b2 & 0x3Fu);
+                else if ((b & 0xF8u) == 0xF0u && avail >= 4) cp = ((b & 0x07u) << 18) | ((b1 & 0x3Fu) << 12) | ((b2 & 0x3Fu) << 6) | (b3 & 0x3Fu);
+                uint32_t cls = A_O;
+                if (cp <= 0x10FFFFu) {
+                    uint32_t leaf = ldg(a.tb.uc_stage1 + (cp >> 7));
+                    uint32_t wv = ldg(a.tb.uc_stage2 + leaf * 8u + ((cp & 127u) >> 4));
+                    cls = (wv >> ((cp & 15u) * 2u)) & 3u;
+                }
+                sm.attr[wi] = static_cast<uint8_t>(cls | (sm.attr[wi] & A_DOC));
+                sm.oh[wi] = static_cast<uint8_t>(1u << cls);
             }
         }
     });
@@ -762,7 +808,8 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                 for (int k = 0; k < 16; ++k) {
                     int i = c * 16 + k, p = lo + i;
                     if (p < 0 || p >= n) continue;
-                    if (ldg(a.tb.trie_root + sm.txt[i]) == kNoToken) continue;
+                    const uint32_t bt = sm.txt[i];
+                    if (!((sm.rootbits[bt >> 5] >> (bt & 31)) & 1u)) continue;
                     uint32_t id;
                     uint32_t ml = match_literal(a, p, n, byte_any, &id);
                     if (!ml) continue;

@@ -114,7 +114,7 @@ struct Engine::Impl {
             !upload(ht.trie_first, &dt.trie_first, owned, err) || !upload(ht.trie_count, &dt.trie_count, owned, err) ||
             !upload(ht.trie_terminal, &dt.trie_terminal, owned, err) || !upload(ht.trie_edges, &dt.trie_edges, owned, err))
             return false;
-        dt.merge_mask = static_cast<uint32_t>(ht.merge.size() - 1);
+        dt.merge_mask = static_cast<uint32_t>(ht.merge.size() / 2 - 1);
         dt.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
         dt.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
         dt.long_max_len = ht.long_max_len;

@@ -61,19 +61,24 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
         // the reference's table too (src/vocab.cc:745-795).
         rules.m.emplace((static_cast<uint64_t>(m.left) << 32) | m.right, (static_cast<uint64_t>(k) << 32) | m.result);
     }
-    for (uint32_t cap = pow2_at_least(static_cast<uint64_t>(hv.merges.size()) * 2);; cap <<= 1) {
-        if (cap > (1u << 30)) { err = "merge table cannot be built within its probe limit"; return false; }
-        out.merge.assign(cap, MergeSlot{kEmptyKey, kEmptyKey, kNoRank, 0});
-        const uint32_t mask = cap - 1;
+    // Buckets of two slots; at least two buckets per rule keeps the load at or below a quarter.
+    for (uint32_t nb = pow2_at_least(static_cast<uint64_t>(hv.merges.size()) * 2);; nb <<= 1) {
+        if (nb > (1u << 29)) { err = "merge table cannot be built within its probe limit"; return false; }
+        out.merge.assign(static_cast<size_t>(nb) * 2, MergeSlot{kEmptyKey, kEmptyKey, kNoRank, 0});
+        const uint32_t mask = nb - 1;
         bool ok = true;
         for (uint32_t k = 0; k < hv.merges.size() && ok; ++k) {
             const MergeRule& m = hv.merges[k];
-            uint32_t h = merge_hash(m.left, m.right) & mask;
+            uint32_t bkt = merge_hash(m.left, m.right) & mask;
             int steps = 0;
-            for (;; h = (h + 1) & mask) {
-                MergeSlot& s = out.merge[h];
-                if (s.left == kEmptyKey) { s = MergeSlot{m.left, m.right, k, m.result}; break; }
-                if (s.left == m.left && s.right == m.right) break;   // duplicate pair: keep the first
+            for (;; bkt = (bkt + 1) & mask) {
+                MergeSlot* s = &out.merge[2 * static_cast<size_t>(bkt)];
+                bool placed = false, dup = false;
+                for (int w = 0; w < 2; ++w) {
+                    if (s[w].left == m.left && s[w].right == m.right) { dup = true; break; }   // duplicate pair: keep the first
+                    if (s[w].left == kEmptyKey) { s[w] = MergeSlot{m.left, m.right, k, m.result}; placed = true; break; }
+                }
+                if (placed || dup) break;
                 if (++steps >= kProbeLimit - 1) { ok = false; break; }
             }
         }
@@ -97,7 +102,7 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
     }
     size_t n_short = 0;
     for (const auto& e : entries) if (e.first.size() <= static_cast<size_t>(kWordKeyMax)) ++n_short;
-    for (uint32_t cap = pow2_at_least(n_short * 2);; cap <<= 1) {
+    for (uint32_t cap = pow2_at_least(n_short * 4);; cap <<= 1) {
         if (cap > (1u << 28)) { err = "word table cannot be built within its probe limit"; return false; }
         out.word.assign(cap, WordSlot{0, 0, kNoToken, {0, 0, 0}});
         const uint32_t mask = cap - 1;
