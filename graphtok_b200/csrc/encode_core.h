@@ -52,7 +52,7 @@ constexpr uint32_t kReprobe = 0xFFFFFFFEu;
 
 constexpr int kMedWordMax = 64;      // longest pre-token merged by a single thread
 constexpr int kTokExtra = 64;        // token slots past the tile for pre-tokens that start in it
-constexpr int kWsWords = 6144;       // u32 words (24 KB) shared by all merge paths: a 2048-symbol arena of ids, ranks, results
+constexpr int kWsWords = 4608;       // u32 words (18 KB) shared by all merge paths: a 1536-symbol arena of ids, ranks, results
 constexpr int kBlockWordSmemMax = kWsWords / 3;        // 2048 symbols
 constexpr int kMaxTeam = 256;        // long pre-tokens starting in one tile (a tile holds < 4096/17 of them)
 
@@ -1050,13 +1050,12 @@ struct MergeSmem {
     uint32_t bm[kTileWords + 4];
     uint32_t am[kTileWords + 4];
     uint32_t tok[kTile + kTokExtra];
-    uint16_t wl[kTile + 8];            // offsets in the tile of the pre-token starts, in order; then the end sentinel
     uint32_t miss[kTile / 2];          // pre-tokens of 2..64 bytes the table did not know: offset | len << 12
     uint32_t aoff[kThreads];           // arena offset of each pre-token of the current batch
     uint32_t team_g[kMaxTeam], team_len[kMaxTeam], team_cnt[kMaxTeam];
     uint32_t b2i[256];
     uint32_t scan[kThreads];
-    uint32_t ws[kWsWords];
+    uint32_t ws[kWsWords];             // merge workspace; before that, the ordered list of pre-token starts (u16)
     uint32_t red[kThreads + 8];
     uint32_t ctr[16];
     unsigned long long clk_last;
@@ -1317,6 +1316,7 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
 
     mark(8);
     // ---- Q1a: the tile's pre-token starts as an ordered list ----
+    uint16_t* const wl = reinterpret_cast<uint16_t*>(sm.ws);   // kTile + 1 entries; dead before the workspace is used
     blk.par([&](int tid) {
         uint32_t bits = (sm.bm[tid >> 1] >> ((tid & 1) * 16)) & 0xFFFFu;
         sm.scan[tid] = popc32(bits);
@@ -1329,14 +1329,14 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
         while (bits) {
             int k = ffs32(bits);
             bits &= bits - 1;
-            sm.wl[at++] = static_cast<uint16_t>(tid * kPer + k);
+            wl[at++] = static_cast<uint16_t>(tid * kPer + k);
         }
         if (tid == 0) {
             // end of the last pre-token: the first boundary in the 64 staged bytes past the tile, if any
             uint32_t e = 0xFFFFu;
             if (sm.bm[kTileWords]) e = kTile + ffs32(sm.bm[kTileWords]);
             else if (sm.bm[kTileWords + 1]) e = kTile + 32 + ffs32(sm.bm[kTileWords + 1]);
-            sm.wl[n_starts] = static_cast<uint16_t>(e);
+            wl[n_starts] = static_cast<uint16_t>(e);
         }
     });
 
@@ -1353,9 +1353,9 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
                 wp[u] = false;
                 const uint32_t i = base + u * kThreads;
                 if (i >= n_starts) continue;
-                const uint32_t o = sm.wl[i], g = t0 + o;
+                const uint32_t o = wl[i], g = t0 + o;
                 if (g >= n) continue;
-                const uint32_t e = sm.wl[i + 1];
+                const uint32_t e = wl[i + 1];
                 uint32_t len = 0;                     // 0 = runs past the staged window
                 if (e != 0xFFFFu) len = e - o;
                 else if (t0 + kTile + 64 >= n) len = n - g;

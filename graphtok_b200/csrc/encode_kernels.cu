@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(kThreads) pretok_kernel(const EncodeArgs a) {
     }
 }
 
-__global__ void __launch_bounds__(kThreads) merge_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) merge_kernel(const EncodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem_raw);
     __shared__ int s_tile;
@@ -227,7 +227,12 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
 size_t merge_smem_bytes() { return sizeof(MergeSmem); }
 
 cudaError_t configure_kernels() {
-    return cudaFuncSetAttribute(merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(MergeSmem)));
+    cudaError_t e = cudaFuncSetAttribute(merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(MergeSmem)));
+    // Both kernels live on shared memory, not L1: ask for the largest carve-out so that
+    // as many blocks as the register file allows are resident.
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(merge_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return e;
 }
 
 int pretok_blocks_per_sm() {
