@@ -228,7 +228,7 @@ def main():
         torch.cuda.synchronize()
         prof.append(g.profile()[1:])
     prof = np.array(prof)
-    pretok_ms, merge_ms = float(np.mean(prof[:, 0])), float(np.mean(prof[:, 1]))
+    kern_ms = [float(x) for x in prof[:, :4].mean(axis=0)]     # pretok, words, miss, assemble
 
     # ---- end to end through the C ABI ------------------------------------
     for _ in range(3):
@@ -243,7 +243,7 @@ def main():
     clocks = sampler.stop()
 
     # ---- reduce over ranks ---------------------------------------------------
-    stats = torch.tensor([step_ms, e2e_s * 1e3, float(n_bytes), float(n_tok), pretok_ms, merge_ms], dtype=torch.float64, device="cuda")
+    stats = torch.tensor([step_ms, e2e_s * 1e3, float(n_bytes), float(n_tok)] + kern_ms, dtype=torch.float64, device="cuda")
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -255,7 +255,7 @@ def main():
         offsets = np.concatenate([[0], np.cumsum([int(c.item()) for c in counts])])
         step_ms, e2e_ms = float(mx[0]), float(mx[1])
         tot_bytes, tot_tok = float(sm[2]), float(sm[3])
-        pretok_ms, merge_ms = float(mx[4]), float(mx[5])
+        kern_ms = [float(mx[4 + i]) for i in range(4)]
     else:
         e2e_ms = e2e_s * 1e3
         tot_bytes, tot_tok = float(n_bytes), float(n_tok)
@@ -264,10 +264,21 @@ def main():
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         tm, tw, to = g.table_bytes()
-        # Algorithmic bytes of the dominant (merge) kernel per launch: the text, its
-        # boundary bits, the ids written, and the tables it probes (merge + whole-word + rest).
-        algo = n_bytes + n_bytes / 8.0 + 4.0 * n_tok + tm + tw + to
-        achieved = algo / (merge_ms * 1e-3) / 1e9
+        # Algorithmic bytes per launch of each kernel (what it must read and write once):
+        #   pretok   : text in, boundary + added-token bits out, class tables
+        #   words    : text + bits in, one u32 slot per byte out, whole-word table
+        #   miss     : the unknown pre-tokens' bytes in, their ids out, merge table
+        #   assemble : one u32 slot per byte in, ids out
+        names = ["pretok_kernel", "words_kernel", "miss_kernel", "assemble_kernel"]
+        algo_of = {
+            "pretok_kernel": n_bytes + 2 * n_bytes / 8.0 + to,
+            "words_kernel": n_bytes + 2 * n_bytes / 8.0 + 4.0 * n_bytes + tw,
+            "miss_kernel": n_bytes * 0.25 + 4.0 * n_tok * 0.25 + tm,
+            "assemble_kernel": 4.0 * n_bytes + 4.0 * n_tok,
+        }
+        dom = int(np.argmax(kern_ms))
+        algo = algo_of[names[dom]]
+        achieved = algo / (kern_ms[dom] * 1e-3) / 1e9
         whole = (n_bytes + 4.0 * n_tok + tm + tw + to) / (step_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": tot_bytes / (step_ms * 1e-3) / 1e6, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -278,9 +289,9 @@ def main():
                        "parallelism": "documents sharded across ranks; all_gather of token counts only"},
             "e2e": {"value": tot_bytes / (e2e_ms * 1e-3) / 1e6, "unit": UNIT, "h2d_bytes_per_step": n_bytes + 16, "d2h_bytes_per_step": int(4 * n_tok + 8),
                     "ms_per_step": e2e_ms},
-            "gpu_launches": 2 * args.steps * world,
-            "kernels_ms": {"pretok_kernel": pretok_ms, "merge_kernel": merge_ms},
-            "roofline": {"bound": "hbm", "kernel": "merge_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "gpu_launches": 4 * args.steps * world,
+            "kernels_ms": dict(zip(names, kern_ms)),
+            "roofline": {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind, "traffic": None, "algorithmic_bytes": algo,
                          "whole_replay": {"achieved": whole, "frac": whole / peak}},
             "clocks": clocks,

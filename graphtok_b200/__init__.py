@@ -176,12 +176,12 @@ class GTok:
         return np.nonzero(bits)[0].astype(np.uint32)
 
     def profile(self):
-        """Staged input, kernel by kernel: (tokens, pretok ms, merge ms, sequence ms)."""
-        ms = (ctypes.c_float * 3)()
+        """Staged input, kernel by kernel: (tokens, pretok ms, words ms, miss ms, assemble ms, sequence ms)."""
+        ms = (ctypes.c_float * 5)()
         n = self.lib.gtok_x_profile(self.handle, ms)
         if n < 0:
             self._fail("gtok_x_profile", n)
-        return n, ms[0], ms[1], ms[2]
+        return (n,) + tuple(ms)
 
     def plan_chunks(self, data, n_parts):
         data = bytes(data)

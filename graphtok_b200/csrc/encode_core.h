@@ -52,9 +52,6 @@ constexpr uint32_t kReprobe = 0xFFFFFFFEu;
 
 constexpr int kMedWordMax = 64;      // longest pre-token merged by a single thread
 constexpr int kTokExtra = 64;        // token slots past the tile for pre-tokens that start in it
-constexpr int kWsWords = 4608;       // u32 words (18 KB) shared by all merge paths: a 1536-symbol arena of ids, ranks, results
-constexpr int kBlockWordSmemMax = kWsWords / 3;        // 2048 symbols
-constexpr int kMaxTeam = 256;        // long pre-tokens starting in one tile (a tile holds < 4096/17 of them)
 
 // Error bits accumulated in ctl[2] and reported to the host.
 enum : uint32_t {
@@ -80,10 +77,17 @@ struct EncodeArgs {
     uint32_t* tile_nb;            // boundaries per tile
     unsigned long long* st1;      // pretok look-back state per tile
     unsigned long long* st2;      // merge look-back state per tile
-    uint32_t* ctl;                // [0] pretok ticket, [1] merge ticket, [2] error bits
+    uint32_t* ctl;                // [0] pretok ticket, [1] assemble ticket, [2] error bits, [3] exit counter,
+                                  // [4] unknown pre-tokens, [5] long pre-tokens, [6] batch ticket, [7] long ticket
     uint32_t* gstage;             // u32 per byte: ids of long pre-tokens
     uint32_t* gwork_rk;           // u32 per byte: rank workspace for very long pre-tokens
     uint32_t* gwork_nw;           // u32 per byte: result workspace for very long pre-tokens
+    uint32_t* stage;              // u32 per byte: id stored at the byte where its pre-token starts (+k for its k-th id), else invalid
+    uint32_t* ovf;                // kTokExtra u32 per tile: ids of a tile's last pre-token that do not fit before the tile's end
+    unsigned long long* gmiss;    // pre-tokens of 2..64 bytes the whole-word table did not know: position | len << 32
+    uint32_t* glong_g;            // pre-tokens longer than 64 bytes: position, length (0 = not known yet), id count
+    uint32_t* glong_len;
+    uint32_t* glong_cnt;
     uint32_t* out_tokens;
     uint32_t out_cap;
     uint32_t* out_doc_tok;        // [n_docs + 1] token offsets (batch) or nullptr
@@ -889,7 +893,36 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         const bool messy = (C & (C << 1) & (C << 2) & (C << 3)) != 0 || (DOC & C) != 0 || AD != 0 ||
                            (((AP << 1) | (AP << 2) | (AP << 3)) & C) != 0;
         if (messy) unc = LEAD;
-        unc |= (AP | (AP << 1) | (AP << 2) | (AP << 3)) & LEAD;
+        // Contractions: 's 't 'm 'd (tail 1) and 're 've 'll (tail 2), when the regex cursor can be
+        // at the apostrophe (anything but punctuation or a literal space before it).  The few
+        // apostrophes of a word are looked at one by one; what follows them is ASCII or the case
+        // goes to the one-by-one path.
+        uint64_t cs1 = 0, cs2 = 0;
+        if (!messy && AP) {
+            const bool ci = family != 0;
+            uint64_t aps = AP & LEAD & ~(pO | pSP);
+            while (aps) {
+#if defined(__CUDA_ARCH__)
+                const int bit = __ffsll(static_cast<long long>(aps)) - 1;
+#else
+                const int bit = __builtin_ctzll(aps);
+#endif
+                aps &= aps - 1;
+                const uint64_t m = 1ull << bit;
+                if (bit > 59) { unc |= m; continue; }                   // tail would leave the window
+                const int i = ww * 32 + bit - 16;
+                uint32_t x = sm.txt[i + 1], y = sm.txt[i + 2];
+                if (x >= 0x80u || ((DOC >> (bit + 1)) & 3u)) { unc |= (m | (m << 1) | (m << 2) | (m << 3) | (m << 4)) & LEAD; continue; }
+                if (ci) { if (x >= 'A' && x <= 'Z') x += 32; if (y >= 'A' && y <= 'Z') y += 32; }
+                // the second letter must be a letter of this document too (an added-token literal is not)
+                const bool y_ok = ((L >> (bit + 2)) & 1u) != 0;
+                if (!((L >> (bit + 1)) & 1u)) continue;
+                if ((x == 'r' || x == 'v') && y == 'e' && y_ok) cs2 |= m;
+                else if (x == 'l' && y == 'l' && y_ok) cs2 |= m;
+                else if (x == 's' || x == 't' || x == 'm' || x == 'd') cs1 |= m;
+            }
+        }
+        if (messy) unc |= (AP | (AP << 1) | (AP << 2) | (AP << 3)) & LEAD;
         bnd |= AD | (DOC & C) | pNone;
         if (family == 0) {
             const uint64_t nNonS = nextcp(L | N | O);
@@ -908,6 +941,11 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             if (family == 2) bnd |= N;
             else { bnd |= N & ~pN; pend = N & pN; }
             bnd |= O & ~pO & ~pSP;
+        }
+        {
+            const uint64_t in_tail = ((cs1 | cs2) << 1) | (cs2 << 2);
+            const uint64_t after_tail = (cs1 << 2) | (cs2 << 3);
+            bnd = (bnd & ~in_tail) | cs1 | cs2 | (after_tail & L & pL);
         }
         bnd &= ~unc;
         pend &= ~unc;
@@ -1045,22 +1083,42 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 // ==================================================================================
 //                                   MERGE + ASSEMBLY
 // ==================================================================================
-struct MergeSmem {
+constexpr int kMissBatch = kThreads;           // unknown pre-tokens per batch of the miss kernel, one per thread
+constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB)
+constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
+enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7 };
+
+struct WordsSmem {
     alignas(16) uint8_t txt[kTile + 64];
     uint32_t bm[kTileWords + 4];
     uint32_t am[kTileWords + 4];
-    uint32_t tok[kTile + kTokExtra];
-    uint32_t miss[kTile / 2];          // pre-tokens of 2..64 bytes the table did not know: offset | len << 12
-    uint32_t aoff[kThreads];           // arena offset of each pre-token of the current batch
-    uint32_t team_g[kMaxTeam], team_len[kMaxTeam], team_cnt[kMaxTeam];
+    alignas(16) uint32_t tok[kTile + kTokExtra];
+    uint16_t wl[kTile + 8];            // offsets in the tile of the pre-token starts, in order; then the end sentinel
+    uint32_t miss[kTile / 2];          // offset | len << 12
+    uint32_t lng_o[kLongPerTile], lng_len[kLongPerTile];
     uint32_t b2i[256];
     uint32_t scan[kThreads];
-    uint32_t ws[kWsWords];             // merge workspace; before that, the ordered list of pre-token starts (u16)
-    uint32_t red[kThreads + 8];
-    uint32_t ctr[16];
+    uint32_t ctr[8];
     unsigned long long clk_last;
 };
-enum { C_NMISS = 0, C_NTEAM = 1, C_NWORDS = 2, C_USED = 3, C_BASE = 4, C_TOTAL = 5, C_TMP = 6, C_TMP2 = 7 };
+struct MissSmem {
+    uint32_t ws[3 * kArenaSyms];       // arena: ids, ranks, results (also the long pre-token workspace)
+    uint32_t b2i[256];
+    uint32_t scan[kThreads];
+    uint32_t red[kThreads + 8];
+    uint32_t aoff[kThreads];
+    unsigned long long word[kThreads]; // this batch's entries of the global list
+    uint32_t ctr[8];
+    unsigned long long clk_last;
+};
+struct AsmSmem {
+    uint32_t scan[kThreads];
+    uint32_t ex[8];
+    uint32_t lref_idx[kLongPerTile], lref_at[kLongPerTile];
+    uint32_t ctr[8];
+    unsigned long long clk_last;
+};
+enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7 };
 
 // Greedy BPE of one pre-token by a single thread (lowest rank first, leftmost among
 // equals, src/host_encode.cc:617-648).  ids/rk/nw are the pre-token's stretch of the
@@ -1272,16 +1330,17 @@ struct BlockTeam {
     GTOK_DEV uint32_t& keep(int lane, int k) { return keepbuf[k * kThreads + lane]; }
 };
 
-// One tile of merging and output assembly.
+// ---- kernel 2: every pre-token of a tile against the whole-word table ----------------
+// Known pre-tokens get their id at once; the others are appended to the global lists that
+// the miss kernel works through.  The tile's slots go to `stage` (and the few ids that
+// spill past the tile's end to `ovf`), so that nothing here waits on a merge loop.
 template <class Blk>
-GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile) {
+GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile) {
     const uint32_t n = ldg(a.meta);
-    const uint32_t n_docs = ldg(a.meta + 1);
     const uint32_t t0 = static_cast<uint32_t>(tile) * kTile;
     const uint32_t n_tiles = (n + kTile - 1) / kTile;
     const uint32_t n_words = n_tiles * kTileWords;
     const DeviceTables& tb = a.tb;
-
     auto mark = [&](int slot) {
         if (!a.phase_clk) return;
         blk.par([&](int tid) {
@@ -1292,7 +1351,7 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
         });
     };
     mark(-1);
-    // ---- Q0: stage text, bit masks, byte ids ----
+    // ---- W0: stage text, bit masks, byte ids ----
     blk.par([&](int tid) {
         for (int c = tid; c < (kTile + 64) / 16; c += kThreads) {
             uint32_t p = t0 + c * 16;
@@ -1311,12 +1370,10 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
         }
         sm.b2i[tid] = ldg(tb.byte_to_id + tid);
         for (int i = tid; i < kTile + kTokExtra; i += kThreads) sm.tok[i] = kInvalidTok;
-        if (tid < 16) sm.ctr[tid] = 0;
+        if (tid < 8) sm.ctr[tid] = 0;
     });
-
     mark(8);
-    // ---- Q1a: the tile's pre-token starts as an ordered list ----
-    uint16_t* const wl = reinterpret_cast<uint16_t*>(sm.ws);   // kTile + 1 entries; dead before the workspace is used
+    // ---- W1: the tile's pre-token starts as an ordered list ----
     blk.par([&](int tid) {
         uint32_t bits = (sm.bm[tid >> 1] >> ((tid & 1) * 16)) & 0xFFFFu;
         sm.scan[tid] = popc32(bits);
@@ -1329,18 +1386,18 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
         while (bits) {
             int k = ffs32(bits);
             bits &= bits - 1;
-            wl[at++] = static_cast<uint16_t>(tid * kPer + k);
+            sm.wl[at++] = static_cast<uint16_t>(tid * kPer + k);
         }
         if (tid == 0) {
             // end of the last pre-token: the first boundary in the 64 staged bytes past the tile, if any
             uint32_t e = 0xFFFFu;
             if (sm.bm[kTileWords]) e = kTile + ffs32(sm.bm[kTileWords]);
             else if (sm.bm[kTileWords + 1]) e = kTile + 32 + ffs32(sm.bm[kTileWords + 1]);
-            wl[n_starts] = static_cast<uint16_t>(e);
+            sm.wl[n_starts] = static_cast<uint16_t>(e);
         }
     });
-
-    // ---- Q1b: one table probe per pre-token, four in flight per thread ----
+    mark(9);
+    // ---- W2: one table probe per pre-token, four in flight per thread ----
     blk.par([&](int tid) {
         for (uint32_t base = tid; base < n_starts; base += kThreads * 4) {
             uint32_t wo[4], wlen[4], wh[4];
@@ -1353,9 +1410,9 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
                 wp[u] = false;
                 const uint32_t i = base + u * kThreads;
                 if (i >= n_starts) continue;
-                const uint32_t o = wl[i], g = t0 + o;
+                const uint32_t o = sm.wl[i], g = t0 + o;
                 if (g >= n) continue;
-                const uint32_t e = wl[i + 1];
+                const uint32_t e = sm.wl[i + 1];
                 uint32_t len = 0;                     // 0 = runs past the staged window
                 if (e != 0xFFFFu) len = e - o;
                 else if (t0 + kTile + 64 >= n) len = n - g;
@@ -1370,7 +1427,8 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
                 }
                 if (len == 0 || len > kMedWordMax) {
                     uint32_t slot = shared_add(&sm.ctr[C_NTEAM], 1u);
-                    if (slot < kMaxTeam) { sm.team_g[slot] = g; sm.team_len[slot] = len; sm.team_cnt[slot] = 0; sm.tok[o] = kLongRef | slot; }
+                    if (slot < kLongPerTile) { sm.lng_o[slot] = o; sm.lng_len[slot] = len; }
+                    else global_or(a.ctl + CTL_ERR, kErrInternal);
                     continue;
                 }
                 if (len > kWordKeyMax) {
@@ -1410,184 +1468,257 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
             }
         }
     });
-
-    mark(9);
-    // ---- Q2: merge loop for the pre-tokens of 2..64 bytes the table did not know ----
-    // A batch takes as many of them as fit the symbol arena (at most one per thread):
-    // the owner lays out the symbols, all threads probe the pairs, the owner merges.
-    {
-        constexpr uint32_t kArena = kWsWords / 3;
-        constexpr uint32_t kPending = 0xFFFFFFFDu;
-        uint32_t* ids = sm.ws;
-        uint32_t* rk = sm.ws + kArena;
-        uint32_t* nw = sm.ws + 2 * kArena;
-        const uint32_t n_miss = sm.ctr[C_NMISS];
-        uint32_t done = 0;
-        while (done < n_miss) {
-            blk.par([&](int tid) {
-                uint32_t idx = done + tid;
-                sm.scan[tid] = idx < n_miss ? (sm.miss[idx] >> 12) : 0u;
-            });
-            uint32_t tot = 0;
-            blk.excl_scan(sm.scan, &tot);
-            blk.par([&](int tid) {
-                uint32_t idx = done + tid;
-                uint32_t len = idx < n_miss ? (sm.miss[idx] >> 12) : 0u;
-                bool fits = idx < n_miss && sm.scan[tid] + len <= kArena;
-                sm.red[tid] = fits ? 0xFFFFFFFFu : static_cast<uint32_t>(tid);
-            });
-            uint32_t nb = blk.reduce_min(sm.red);
-            if (nb == 0xFFFFFFFFu) nb = kThreads;
-            blk.par([&](int tid) {
-                if (static_cast<uint32_t>(tid) >= nb) return;
-                const uint32_t mv = sm.miss[done + tid];
-                const uint32_t o = mv & 0xFFFu, len = mv >> 12, at = sm.scan[tid];
-                if (static_cast<uint32_t>(tid) + 1 == nb) sm.ctr[C_USED] = at + len;
-                bool resolved = false;
-                if (tb.ignore_merges && len > kWordKeyMax) {
-                    uint32_t id = probe_long_bytes(tb, sm.txt + o, len);
-                    if (id != kNoToken) { sm.tok[o] = id; resolved = true; }
-                }
-                for (uint32_t i = 0; i < len; ++i) {
-                    ids[at + i] = sm.b2i[sm.txt[o + i]];
-                    rk[at + i] = (!resolved && i + 1 < len) ? kPending : kNoRank;
-                }
-                sm.aoff[tid] = resolved ? 0xFFFFFFFFu : at;
-            });
-            const uint32_t used = sm.ctr[C_USED];
-            blk.par([&](int tid) {
-                for (uint32_t sidx = tid; sidx < used; sidx += kThreads) {
-                    if (rk[sidx] != kPending) continue;
-                    RankRes r = probe_rule(tb, ids[sidx], ids[sidx + 1]);
-                    rk[sidx] = r.rank;
-                    nw[sidx] = r.res;
-                }
-            });
-            blk.par([&](int tid) {
-                if (static_cast<uint32_t>(tid) >= nb) return;
-                const uint32_t at = sm.aoff[tid];
-                if (at == 0xFFFFFFFFu) return;
-                const uint32_t mv = sm.miss[done + tid];
-                const uint32_t o = mv & 0xFFFu, len = mv >> 12;
-                bpe_arena(a, ids + at, rk + at, nw + at, len, sm.tok + o);
-            });
-            done += nb;
-        }
-    }
     mark(10);
-
-    mark(11);
-    // ---- Q3: long pre-tokens, one at a time, by the whole block ----
-    {
-        uint32_t n_team = sm.ctr[C_NTEAM];
-        if (n_team > kMaxTeam) n_team = kMaxTeam;
-        for (uint32_t ti = 0; ti < n_team; ++ti) {
-            const uint32_t g = sm.team_g[ti];
-            blk.par([&](int tid) {
-                if (tid != 0) return;
-                uint32_t len = sm.team_len[ti];
-                if (len == 0) len = find_word_end(a, g, n) - g;
-                uint32_t id = kNoToken;
-                if (tb.ignore_merges) id = probe_long(tb, a.text, g, len);
-                sm.ctr[C_TMP] = len;
-                sm.ctr[C_TMP2] = id;
-            });
-            const uint32_t len = sm.ctr[C_TMP];
-            const uint32_t hit = sm.ctr[C_TMP2];
-            if (hit != kNoToken) {
-                blk.par([&](int tid) { if (tid == 0) { a.gstage[g] = hit; sm.team_cnt[ti] = 1; } });
-                continue;
-            }
-            // Workspace: shared memory when the pre-token fits beside the team's own
-            // scratch, else the per-byte global arrays (disjoint per pre-token).
-            constexpr uint32_t kScratch = 6 * kThreads + 16;                 // team scratch + keep buffer
-            constexpr uint32_t kFit = (kWsWords - kScratch) / 3;
-            uint32_t* scratch = sm.ws;
-            uint32_t* keepbuf = sm.ws + 3 * kThreads + 16;
-            uint32_t *ids, *rk, *nw;
-            if (len <= kFit) { ids = sm.ws + kScratch; rk = ids + kFit; nw = rk + kFit; }
-            else { ids = a.gstage + g; rk = a.gwork_rk + g; nw = a.gwork_nw + g; }
-            blk.par([&](int tid) {
-                for (uint32_t i = tid; i < len; i += kThreads) ids[i] = sm.b2i[ldg(a.text + g + i)];
-            });
-            BlockTeam<Blk> team(blk, keepbuf);
-            uint32_t cnt = team_bpe(team, a, ids, rk, nw, len, scratch);
-            blk.par([&](int tid) {
-                if (ids != a.gstage + g)
-                    for (uint32_t i = tid; i < cnt; i += kThreads) a.gstage[g + i] = ids[i];
-                if (tid == 0) sm.team_cnt[ti] = cnt;
-            });
-        }
-    }
-
-    mark(12);
-    // ---- Q4: how many tokens does each thread's stretch of tok[] stand for ----
+    // ---- W3: hand the unknown and the long pre-tokens to the global lists; write the slots out ----
     blk.par([&](int tid) {
+        if (tid != 0) return;
+        uint32_t nm = sm.ctr[C_NMISS], nl = sm.ctr[C_NTEAM];
+        if (nl > kLongPerTile) nl = kLongPerTile;
+        sm.ctr[C_NTEAM] = nl;
+#if defined(__CUDA_ARCH__)
+        sm.ctr[C_BASEM] = nm ? atomicAdd(a.ctl + CTL_NMISS, nm) : 0u;
+        sm.ctr[C_BASEL] = nl ? atomicAdd(a.ctl + CTL_NLONG, nl) : 0u;
+#else
+        sm.ctr[C_BASEM] = a.ctl[CTL_NMISS]; a.ctl[CTL_NMISS] += nm;
+        sm.ctr[C_BASEL] = a.ctl[CTL_NLONG]; a.ctl[CTL_NLONG] += nl;
+#endif
+    });
+    {
+        const uint32_t nm = sm.ctr[C_NMISS], nl = sm.ctr[C_NTEAM], bm0 = sm.ctr[C_BASEM], bl0 = sm.ctr[C_BASEL];
+        blk.par([&](int tid) {
+            for (uint32_t i = tid; i < nm; i += kThreads) {
+                uint32_t mv = sm.miss[i];
+                a.gmiss[bm0 + i] = static_cast<unsigned long long>(t0 + (mv & 0xFFFu)) | (static_cast<unsigned long long>(mv >> 12) << 32);
+            }
+            for (uint32_t i = tid; i < nl; i += kThreads) {
+                a.glong_g[bl0 + i] = t0 + sm.lng_o[i];
+                a.glong_len[bl0 + i] = sm.lng_len[i];
+                a.glong_cnt[bl0 + i] = 0;
+                sm.tok[sm.lng_o[i]] = kLongRef | (bl0 + i);
+            }
+        });
+        blk.par([&](int tid) {
+#if defined(__CUDA_ARCH__)
+            for (int c = tid; c < kTile / 4; c += kThreads)
+                reinterpret_cast<uint4*>(a.stage + t0)[c] = reinterpret_cast<const uint4*>(sm.tok)[c];
+#else
+            for (int i = tid; i < kTile; i += kThreads) a.stage[t0 + i] = sm.tok[i];
+#endif
+            if (tid < kTokExtra) a.ovf[static_cast<size_t>(tile) * kTokExtra + tid] = sm.tok[kTile + tid];
+        });
+    }
+    mark(11);
+}
+
+// Stores the k-th id of the pre-token that starts at byte g.
+GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
+    const uint32_t tile = g / kTile, t1 = (tile + 1) * kTile;
+    if (g + k < t1) a.stage[g + k] = id;
+    else a.ovf[static_cast<size_t>(tile) * kTokExtra + (g + k - t1)] = id;
+}
+
+// ---- kernel 3a: one batch of unknown pre-tokens (2..64 bytes), one per thread ----------
+// The owner lays its symbols out in the block's arena, all threads probe the pairs, the
+// owner merges (lowest rank first) and stores the ids.
+template <class Blk>
+GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t first, uint32_t n_miss) {
+    const DeviceTables& tb = a.tb;
+    constexpr uint32_t kPending = 0xFFFFFFFDu;
+    uint32_t* ids = sm.ws;
+    uint32_t* rk = sm.ws + kArenaSyms;
+    uint32_t* nw = sm.ws + 2 * kArenaSyms;
+    const uint32_t n_here = n_miss - first < static_cast<uint32_t>(kMissBatch) ? n_miss - first : static_cast<uint32_t>(kMissBatch);
+    blk.par([&](int tid) {
+        if (static_cast<uint32_t>(tid) < n_here) sm.word[tid] = a.gmiss[first + tid];
+    });
+    uint32_t done = 0;
+    while (done < n_here) {
+        blk.par([&](int tid) {
+            uint32_t idx = done + tid;
+            sm.scan[tid] = idx < n_here ? static_cast<uint32_t>(sm.word[idx] >> 32) : 0u;
+        });
+        uint32_t tot = 0;
+        blk.excl_scan(sm.scan, &tot);
+        blk.par([&](int tid) {
+            uint32_t idx = done + tid;
+            uint32_t len = idx < n_here ? static_cast<uint32_t>(sm.word[idx] >> 32) : 0u;
+            bool fits = idx < n_here && sm.scan[tid] + len <= static_cast<uint32_t>(kArenaSyms);
+            sm.red[tid] = fits ? 0xFFFFFFFFu : static_cast<uint32_t>(tid);
+        });
+        uint32_t nb = blk.reduce_min(sm.red);
+        if (nb == 0xFFFFFFFFu) nb = kThreads;
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= nb) return;
+            const unsigned long long wv = sm.word[done + tid];
+            const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32), at = sm.scan[tid];
+            if (static_cast<uint32_t>(tid) + 1 == nb) sm.ctr[C_USED] = at + len;
+            bool resolved = false;
+            if (tb.ignore_merges && len > kWordKeyMax) {
+                uint32_t id = probe_long(tb, a.text, g, len);
+                if (id != kNoToken) { put_id(a, g, 0, id); resolved = true; }
+            }
+            for (uint32_t i = 0; i < len; ++i) {
+                ids[at + i] = sm.b2i[ldg(a.text + g + i)];
+                rk[at + i] = (!resolved && i + 1 < len) ? kPending : kNoRank;
+            }
+            sm.aoff[tid] = resolved ? 0xFFFFFFFFu : at;
+        });
+        const uint32_t used = sm.ctr[C_USED];
+        blk.par([&](int tid) {
+            for (uint32_t sidx = tid; sidx < used; sidx += kThreads) {
+                if (rk[sidx] != kPending) continue;
+                RankRes r = probe_rule(tb, ids[sidx], ids[sidx + 1]);
+                rk[sidx] = r.rank;
+                nw[sidx] = r.res;
+            }
+        });
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= nb) return;
+            const uint32_t at = sm.aoff[tid];
+            if (at == 0xFFFFFFFFu) return;
+            const unsigned long long wv = sm.word[done + tid];
+            const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
+            // merge in place, then the ids (the arena stretch is free again) go to their slots
+            uint32_t cnt = bpe_arena(a, ids + at, rk + at, nw + at, len, nw + at);
+            for (uint32_t k = 0; k < cnt; ++k) put_id(a, g, k, nw[at + k]);
+        });
+        done += nb;
+    }
+}
+
+// ---- kernel 3b: one pre-token longer than 64 bytes, by the whole block ------------------
+template <class Blk>
+GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li) {
+    const uint32_t n = ldg(a.meta);
+    const DeviceTables& tb = a.tb;
+    const uint32_t g = ldg(a.glong_g + li);
+    blk.par([&](int tid) {
+        if (tid != 0) return;
+        uint32_t len = ldg(a.glong_len + li);
+        if (len == 0) len = find_word_end(a, g, n) - g;
+        uint32_t id = kNoToken;
+        if (tb.ignore_merges) id = probe_long(tb, a.text, g, len);
+        sm.ctr[C_TMP] = len;
+        sm.ctr[C_TMP2] = id;
+    });
+    const uint32_t len = sm.ctr[C_TMP];
+    const uint32_t hit = sm.ctr[C_TMP2];
+    if (hit != kNoToken) {
+        blk.par([&](int tid) { if (tid == 0) { a.gstage[g] = hit; a.glong_cnt[li] = 1; } });
+        return;
+    }
+    // Workspace: shared memory when the pre-token fits beside the team's own scratch,
+    // else the per-byte global arrays (disjoint per pre-token).
+    constexpr uint32_t kScratch = 6 * kThreads + 16;                 // team scratch + keep buffer
+    constexpr uint32_t kFit = (3 * kArenaSyms - kScratch) / 3;
+    uint32_t* scratch = sm.ws;
+    uint32_t* keepbuf = sm.ws + 3 * kThreads + 16;
+    uint32_t *ids, *rk, *nw;
+    if (len <= kFit) { ids = sm.ws + kScratch; rk = ids + kFit; nw = rk + kFit; }
+    else { ids = a.gstage + g; rk = a.gwork_rk + g; nw = a.gwork_nw + g; }
+    blk.par([&](int tid) {
+        for (uint32_t i = tid; i < len; i += kThreads) ids[i] = sm.b2i[ldg(a.text + g + i)];
+    });
+    BlockTeam<Blk> team(blk, keepbuf);
+    uint32_t cnt = team_bpe(team, a, ids, rk, nw, len, scratch);
+    blk.par([&](int tid) {
+        if (ids != a.gstage + g)
+            for (uint32_t i = tid; i < cnt; i += kThreads) a.gstage[g + i] = ids[i];
+        if (tid == 0) a.glong_cnt[li] = cnt;
+    });
+}
+
+// ---- kernel 4: output assembly ------------------------------------------------------------
+// Counts the ids each tile's slots stand for, finds the tile's base by a single-pass
+// decoupled look-back over the tile totals, and writes the ids to their final place,
+// together with the per-document offsets and the total.
+template <class Blk>
+GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile) {
+    const uint32_t n = ldg(a.meta);
+    const uint32_t n_docs = ldg(a.meta + 1);
+    const uint32_t t0 = static_cast<uint32_t>(tile) * kTile;
+    const uint32_t n_tiles = (n + kTile - 1) / kTile;
+    const uint32_t* ovf = a.ovf + static_cast<size_t>(tile) * kTokExtra;
+    auto mark = [&](int slot) {
+        if (!a.phase_clk) return;
+        blk.par([&](int tid) {
+            if (tid != 0) return;
+            unsigned long long t = cycle_now();
+            if (slot >= 0) add_cycles(a.phase_clk + slot, t - sm.clk_last);
+            sm.clk_last = t;
+        });
+    };
+    mark(-1);
+    auto weight = [&](uint32_t v) -> uint32_t {
+        if (v == kInvalidTok) return 0u;
+        return (v & kLongRef) ? ldg(a.glong_cnt + (v & ~kLongRef)) : 1u;
+    };
+    // ---- A0: ids per thread ----
+    blk.par([&](int tid) {
+        if (tid == 0) sm.ctr[C_NLREF] = 0;
         uint32_t sum = 0;
-        int lo = tid * kPer, hi = lo + kPer;
-        for (int i = lo; i < hi; ++i) {
-            uint32_t v = sm.tok[i];
-            if (v == kInvalidTok) continue;
-            sum += (v & kLongRef) ? sm.team_cnt[v & ~kLongRef] : 1u;
-        }
+        const uint32_t* sp = a.stage + t0 + tid * kPer;
+        for (int i = 0; i < kPer; ++i) sum += weight(sp[i]);
         sm.scan[tid] = sum;
-        // slots past the tile (ids of pre-tokens that start in its last bytes): plain ids only
         if (tid < kTokExtra / kPer) {
             uint32_t ex = 0;
-            for (int i = kTile + tid * kPer; i < kTile + (tid + 1) * kPer; ++i) ex += sm.tok[i] != kInvalidTok;
-            sm.red[kThreads + tid] = ex;
+            for (int i = 0; i < kPer; ++i) ex += ovf[tid * kPer + i] != kInvalidTok;
+            sm.ex[tid] = ex;
         }
     });
     uint32_t total_main = 0;
     blk.excl_scan(sm.scan, &total_main);
     uint32_t total = total_main;
-    for (int t = 0; t < kTokExtra / kPer; ++t) total += sm.red[kThreads + t];
-
-    mark(13);
-    // ---- Q5: tile base by decoupled look-back ----
+    for (int t = 0; t < kTokExtra / kPer; ++t) total += sm.ex[t];
+    mark(12);
+    // ---- A1: tile base by decoupled look-back ----
     const uint32_t base = blk.lookback(a.st2, tile, total, a.ctl);
-
-    mark(14);
-    // ---- Q6: tokens to their final place ----
+    mark(13);
+    // ---- A2: ids to their final place ----
     blk.par([&](int tid) {
         uint32_t at = base + sm.scan[tid];
-        int lo = tid * kPer, hi = lo + kPer;
-        for (int i = lo; i < hi; ++i) {
-            uint32_t v = sm.tok[i];
+        const uint32_t* sp = a.stage + t0 + tid * kPer;
+        for (int i = 0; i < kPer; ++i) {
+            uint32_t v = sp[i];
             if (v == kInvalidTok) continue;
-            if (v & kLongRef) { uint32_t ti = v & ~kLongRef; sm.team_len[ti] = at; at += sm.team_cnt[ti]; continue; }
-            if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + 2, kErrOutputFull);
+            if (v & kLongRef) {
+                uint32_t li = v & ~kLongRef, slot = shared_add(&sm.ctr[C_NLREF], 1u);
+                if (slot < kLongPerTile) { sm.lref_idx[slot] = li; sm.lref_at[slot] = at; }
+                at += ldg(a.glong_cnt + li);
+                continue;
+            }
+            if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + CTL_ERR, kErrOutputFull);
             ++at;
         }
         if (tid < kTokExtra / kPer) {
             at = base + total_main;
-            for (int t = 0; t < tid; ++t) at += sm.red[kThreads + t];
-            for (int i = kTile + tid * kPer; i < kTile + (tid + 1) * kPer; ++i) {
-                uint32_t v = sm.tok[i];
+            for (int t = 0; t < tid; ++t) at += sm.ex[t];
+            for (int i = 0; i < kPer; ++i) {
+                uint32_t v = ovf[tid * kPer + i];
                 if (v == kInvalidTok) continue;
-                if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + 2, kErrOutputFull);
+                if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + CTL_ERR, kErrOutputFull);
                 ++at;
             }
         }
     });
     {
-        uint32_t n_team = sm.ctr[C_NTEAM];
-        if (n_team > kMaxTeam) n_team = kMaxTeam;
-        if (n_team) {
+        uint32_t n_ref = sm.ctr[C_NLREF];
+        if (n_ref > kLongPerTile) n_ref = kLongPerTile;
+        if (n_ref) {
             blk.par([&](int tid) {
-                for (uint32_t ti = 0; ti < n_team; ++ti) {
-                    uint32_t g = sm.team_g[ti], cnt = sm.team_cnt[ti], at = sm.team_len[ti];
+                for (uint32_t r = 0; r < n_ref; ++r) {
+                    const uint32_t li = sm.lref_idx[r], at = sm.lref_at[r];
+                    const uint32_t g = ldg(a.glong_g + li), cnt = ldg(a.glong_cnt + li);
                     for (uint32_t i = tid; i < cnt; i += kThreads) {
                         if (at + i < a.out_cap) a.out_tokens[at + i] = a.gstage[g + i];
-                        else { global_or(a.ctl + 2, kErrOutputFull); break; }
+                        else { global_or(a.ctl + CTL_ERR, kErrOutputFull); break; }
                     }
                 }
             });
         }
     }
-
-    mark(15);
-    // ---- Q7: per-document token offsets; totals ----
+    mark(14);
+    // ---- A3: per-document token offsets; totals ----
     if (a.out_doc_tok) {
         blk.par([&](int tid) {
             // documents whose first byte lies in this tile
@@ -1599,11 +1730,7 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
                 if (off >= t1 || off >= n) break;
                 uint32_t o = off - t0, owner = o / kPer;
                 uint32_t cnt = sm.scan[owner];
-                for (uint32_t i = owner * kPer; i < o; ++i) {
-                    uint32_t v = sm.tok[i];
-                    if (v == kInvalidTok) continue;
-                    cnt += (v & kLongRef) ? sm.team_cnt[v & ~kLongRef] : 1u;
-                }
+                for (uint32_t i = owner * kPer; i < o; ++i) cnt += weight(a.stage[t0 + i]);
                 a.out_doc_tok[d] = base + cnt;
             }
             if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
@@ -1619,6 +1746,7 @@ GTOK_DEV void merge_tile(Blk& blk, const EncodeArgs& a, MergeSmem& sm, int tile)
             a.status[0] = base + total;
         });
     }
+    mark(15);
 }
 
 }  // namespace gtok

@@ -2,10 +2,10 @@
 // tile programs of encode_core.h, plus the launch helpers the engine captures into
 // its CUDA graph.
 //
-// Both kernels are persistent: a fixed grid (a multiple of the SM count) pulls tile
-// numbers from a ticket counter, so the work done depends on the byte count that
-// sits in device memory, not on the capacity the graph was captured for, and a tile
-// never waits on a tile that has not been handed to a running block.
+// The kernels are persistent: a fixed grid (a multiple of the SM count) walks the tiles,
+// so the work done depends on the byte count that sits in device memory, not on the
+// capacity the graph was captured for.  Where a tile waits on earlier tiles (look-back)
+// tiles are handed out by a ticket counter, so a tile never waits on one no block has started.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -114,27 +114,66 @@ __global__ void __launch_bounds__(kThreads) pretok_kernel(const EncodeArgs a) {
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 4) merge_kernel(const EncodeArgs a) {
+// Kernel 2: whole-word table lookups, tile by tile (tiles are independent here).
+__global__ void __launch_bounds__(kThreads, 4) words_kernel(const EncodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem_raw);
+    WordsSmem& sm = *reinterpret_cast<WordsSmem*>(smem_raw);
+    GpuBlk blk;
+    const uint32_t n = a.meta[0];
+    const int n_tiles = static_cast<int>((n + kTile - 1) / kTile);
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) words_tile(blk, a, sm, tile);
+}
+
+// Kernel 3: merge loops for what the table did not know, batch by batch, then the
+// pre-tokens longer than 64 bytes one by one.
+__global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    MissSmem& sm = *reinterpret_cast<MissSmem*>(smem_raw);
+    __shared__ uint32_t s_pick;
+    GpuBlk blk;
+    const uint32_t n_miss = a.ctl[CTL_NMISS], n_long = a.ctl[CTL_NLONG];
+    sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
+    __syncthreads();
+    for (;;) {
+        if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_BATCH, 1u);
+        __syncthreads();
+        const uint32_t first = s_pick * kMissBatch;
+        __syncthreads();
+        if (first >= n_miss) break;
+        miss_batch(blk, a, sm, first, n_miss);
+    }
+    for (;;) {
+        if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);
+        __syncthreads();
+        const uint32_t li = s_pick;
+        __syncthreads();
+        if (li >= n_long) break;
+        long_word(blk, a, sm, li);
+    }
+}
+
+// Kernel 4: output assembly; tiles are handed out in order because a tile's base is the
+// sum of all earlier tiles' counts.
+__global__ void __launch_bounds__(kThreads) assemble_kernel(const EncodeArgs a) {
+    __shared__ AsmSmem sm;
     __shared__ int s_tile;
     GpuBlk blk;
     const uint32_t n = a.meta[0];
     const int n_tiles = static_cast<int>((n + kTile - 1) / kTile);
     for (;;) {
-        if (threadIdx.x == 0) s_tile = static_cast<int>(atomicAdd(a.ctl + 1, 1u));
+        if (threadIdx.x == 0) s_tile = static_cast<int>(atomicAdd(a.ctl + CTL_ASM, 1u));
         __syncthreads();
         const int tile = s_tile;
         __syncthreads();
         if (tile >= n_tiles) break;
-        merge_tile(blk, a, sm, tile);
+        assemble_tile(blk, a, sm, tile);
     }
     // The last block to leave mirrors the error word where the host can read it.
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(a.ctl + 3, 1u) == gridDim.x - 1) {
+        if (atomicAdd(a.ctl + CTL_EXIT, 1u) == gridDim.x - 1) {
             __threadfence();
-            a.status[1] = *reinterpret_cast<volatile uint32_t*>(a.ctl + 2);
+            a.status[1] = *reinterpret_cast<volatile uint32_t*>(a.ctl + CTL_ERR);
         }
     }
 }
@@ -224,34 +263,33 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
     return 0;
 }
 
-size_t merge_smem_bytes() { return sizeof(MergeSmem); }
-
 cudaError_t configure_kernels() {
-    cudaError_t e = cudaFuncSetAttribute(merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(MergeSmem)));
-    // Both kernels live on shared memory, not L1: ask for the largest carve-out so that
-    // as many blocks as the register file allows are resident.
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(merge_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaError_t e = cudaFuncSetAttribute(words_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(WordsSmem)));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(miss_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(MissSmem)));
+    // The kernels live on shared memory, not L1: ask for the largest carve-out so that as
+    // many blocks as the register file allows are resident.
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(words_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(miss_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     return e;
 }
 
-int pretok_blocks_per_sm() {
+static int blocks_per_sm(const void* fn, size_t smem) {
     int nb = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, pretok_kernel, kThreads, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, kThreads, smem);
     return nb > 0 ? nb : 1;
 }
-int merge_blocks_per_sm() {
-    int nb = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, merge_kernel, kThreads, sizeof(MergeSmem));
-    return nb > 0 ? nb : 1;
-}
+int pretok_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(pretok_kernel), 0); }
+int words_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(words_kernel), sizeof(WordsSmem)); }
+int miss_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(miss_kernel), sizeof(MissSmem)); }
+int assemble_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(assemble_kernel), 0); }
 
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s) {
     docmask_kernel<<<blocks, 256, 0, s>>>(a.meta, a.doc_off, docmask);
 }
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, 0, s>>>(a); }
-void launch_merge(const EncodeArgs& a, int blocks, cudaStream_t s) {
-    merge_kernel<<<blocks, kThreads, sizeof(MergeSmem), s>>>(a);
-}
+void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s) { words_kernel<<<blocks, kThreads, sizeof(WordsSmem), s>>>(a); }
+void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s) { miss_kernel<<<blocks, kThreads, sizeof(MissSmem), s>>>(a); }
+void launch_assemble(const EncodeArgs& a, int blocks, cudaStream_t s) { assemble_kernel<<<blocks, kThreads, 0, s>>>(a); }
 
 }  // namespace gtok

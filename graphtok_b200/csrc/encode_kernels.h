@@ -9,13 +9,16 @@
 
 namespace gtok {
 
-size_t merge_smem_bytes();
 cudaError_t configure_kernels();     // once per device, before the first launch
 int pretok_blocks_per_sm();
-int merge_blocks_per_sm();
+int words_blocks_per_sm();
+int miss_blocks_per_sm();
+int assemble_blocks_per_sm();
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s);
-void launch_merge(const EncodeArgs& a, int blocks, cudaStream_t s);
+void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s);
+void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s);
+void launch_assemble(const EncodeArgs& a, int blocks, cudaStream_t s);
 
 
 // Largest input of boundaries_noalloc(), fixed by its statically reserved working memory.

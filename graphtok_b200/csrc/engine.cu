@@ -52,6 +52,8 @@ struct Ctx {
     unsigned char* d_ctrl = nullptr;
     size_t ctrl_bytes = 0;
     uint32_t *d_gstage = nullptr, *d_grk = nullptr, *d_gnw = nullptr;
+    uint32_t *d_stage = nullptr, *d_ovf = nullptr, *d_glong = nullptr;
+    unsigned long long* d_gmiss = nullptr;
     uint32_t *d_out = nullptr, *d_doc_tok = nullptr;
     uint32_t *h_status = nullptr, *d_status = nullptr;
     unsigned long long* d_phase = nullptr;
@@ -62,8 +64,8 @@ struct Ctx {
     cudaStream_t stream = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr, ev3 = nullptr;
-    int pretok_blocks = 1, merge_blocks = 1, docmask_blocks = 1;
+    cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int pretok_blocks = 1, words_blocks = 1, miss_blocks = 1, asm_blocks = 1, docmask_blocks = 1;
     size_t mask_words = 0;
     EncodeArgs args;
     uint32_t staged_docs = 0, staged_len = 0;
@@ -71,14 +73,12 @@ struct Ctx {
     ~Ctx() {
         if (exec) cudaGraphExecDestroy(exec);
         if (graph) cudaGraphDestroy(graph);
-        if (ev0) cudaEventDestroy(ev0);
-        if (ev1) cudaEventDestroy(ev1);
-        if (ev2) cudaEventDestroy(ev2);
-        if (ev3) cudaEventDestroy(ev3);
+        for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
         cudaFree(d_text); cudaFree(d_hdr); cudaFree(d_docmask); cudaFree(d_bmask); cudaFree(d_amask);
         cudaFree(d_tile_nb); cudaFree(d_ctrl); cudaFree(d_gstage); cudaFree(d_grk); cudaFree(d_gnw);
         cudaFree(d_out); cudaFree(d_doc_tok); cudaFree(d_phase);
+        cudaFree(d_stage); cudaFree(d_ovf); cudaFree(d_glong); cudaFree(d_gmiss);
         if (h_status) cudaFreeHost(h_status);
         if (h_text) cudaFreeHost(h_text);
         if (h_hdr) cudaFreeHost(h_hdr);
@@ -96,7 +96,7 @@ struct Engine::Impl {
     std::vector<void*> owned;
     std::unique_ptr<Ctx> single, batch;
     Ctx* staged = nullptr;
-    int pretok_per_sm = 1, merge_per_sm = 1;
+    int pretok_per_sm = 1, words_per_sm = 1, miss_per_sm = 1, asm_per_sm = 1;
 
     ~Impl() {
         single.reset();
@@ -136,10 +136,7 @@ struct Engine::Impl {
         const size_t mask_words = static_cast<size_t>(c->n_tiles_cap) * kTileWords + 8;
         const size_t hdr_words = kHdrWords + static_cast<size_t>(cap_docs) + 2;
         GTOK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
-        GTOK_CUDA(cudaEventCreate(&c->ev0));
-        GTOK_CUDA(cudaEventCreate(&c->ev1));
-        GTOK_CUDA(cudaEventCreate(&c->ev2));
-        GTOK_CUDA(cudaEventCreate(&c->ev3));
+        for (cudaEvent_t& e : c->ev) GTOK_CUDA(cudaEventCreate(&e));
         GTOK_CUDA(cudaMalloc(&c->d_text, tile_bytes + kTextPad));
         GTOK_CUDA(cudaMemset(c->d_text, 0, tile_bytes + kTextPad));
         GTOK_CUDA(cudaMalloc(&c->d_hdr, hdr_words * 4));
@@ -154,6 +151,10 @@ struct Engine::Impl {
         GTOK_CUDA(cudaMalloc(&c->d_gstage, (tile_bytes + 64) * 4));
         GTOK_CUDA(cudaMalloc(&c->d_grk, (tile_bytes + 64) * 4));
         GTOK_CUDA(cudaMalloc(&c->d_gnw, (tile_bytes + 64) * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_stage, (tile_bytes + 64) * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_ovf, static_cast<size_t>(c->n_tiles_cap) * kTokExtra * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_gmiss, (tile_bytes / 2 + 64) * 8));
+        GTOK_CUDA(cudaMalloc(&c->d_glong, static_cast<size_t>(c->n_tiles_cap) * kLongPerTile * 3 * 4));
         GTOK_CUDA(cudaMalloc(&c->d_out, (static_cast<size_t>(cap_bytes) + 16) * 4));
         GTOK_CUDA(cudaMalloc(&c->d_doc_tok, (static_cast<size_t>(cap_docs) + 2) * 4));
         GTOK_CUDA(cudaHostAlloc(&c->h_status, 64, cudaHostAllocMapped));
@@ -177,6 +178,12 @@ struct Engine::Impl {
         a.gstage = c->d_gstage;
         a.gwork_rk = c->d_grk;
         a.gwork_nw = c->d_gnw;
+        a.stage = c->d_stage;
+        a.ovf = c->d_ovf;
+        a.gmiss = c->d_gmiss;
+        a.glong_g = c->d_glong;
+        a.glong_len = c->d_glong + static_cast<size_t>(c->n_tiles_cap) * kLongPerTile;
+        a.glong_cnt = c->d_glong + static_cast<size_t>(c->n_tiles_cap) * kLongPerTile * 2;
         a.out_tokens = c->d_out;
         a.out_cap = cap_bytes + 16;
         a.out_doc_tok = batch_mode ? c->d_doc_tok : nullptr;
@@ -190,9 +197,13 @@ struct Engine::Impl {
 
         // Capture: control block reset, [document mask], pretok, merge.
         const int pretok_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * pretok_per_sm));
-        const int merge_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * merge_per_sm));
+        const int words_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * words_per_sm));
+        const int miss_blocks = std::max(1, sm_count * miss_per_sm);
+        const int asm_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * asm_per_sm));
         c->pretok_blocks = pretok_blocks;
-        c->merge_blocks = merge_blocks;
+        c->words_blocks = words_blocks;
+        c->miss_blocks = miss_blocks;
+        c->asm_blocks = asm_blocks;
         c->docmask_blocks = std::max(1, std::min<int>(sm_count, static_cast<int>((cap_docs + 256) / 256)));
         c->mask_words = mask_words;
         GTOK_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
@@ -202,7 +213,9 @@ struct Engine::Impl {
             launch_docmask(a, c->d_docmask, c->docmask_blocks, c->stream);
         }
         launch_pretok(a, pretok_blocks, c->stream);
-        launch_merge(a, merge_blocks, c->stream);
+        launch_words(a, words_blocks, c->stream);
+        launch_miss(a, miss_blocks, c->stream);
+        launch_assemble(a, asm_blocks, c->stream);
         GTOK_CUDA(cudaStreamEndCapture(c->stream, &c->graph));
         GTOK_CUDA(cudaGraphInstantiate(&c->exec, c->graph, 0));
         GTOK_CUDA(cudaGetLastError());
@@ -267,11 +280,11 @@ struct Engine::Impl {
         if (c->staged_len == 0) { if (ms) *ms = 0.f; return 0; }
         auto fail = [&](cudaError_t e, const char* what) { err = std::string(what) + ": " + cudaGetErrorString(e); return int64_t(-1); };
         cudaError_t e;
-        if (timed && (e = cudaEventRecord(c->ev0, c->stream)) != cudaSuccess) return fail(e, "cudaEventRecord");
+        if (timed && (e = cudaEventRecord(c->ev[0], c->stream)) != cudaSuccess) return fail(e, "cudaEventRecord");
         if ((e = cudaGraphLaunch(c->exec, c->stream)) != cudaSuccess) return fail(e, "cudaGraphLaunch");
-        if (timed && (e = cudaEventRecord(c->ev1, c->stream)) != cudaSuccess) return fail(e, "cudaEventRecord");
+        if (timed && (e = cudaEventRecord(c->ev[1], c->stream)) != cudaSuccess) return fail(e, "cudaEventRecord");
         if ((e = cudaStreamSynchronize(c->stream)) != cudaSuccess) return fail(e, "cudaStreamSynchronize");
-        if (timed && ms) cudaEventElapsedTime(ms, c->ev0, c->ev1);
+        if (timed && ms) cudaEventElapsedTime(ms, c->ev[0], c->ev[1]);
         uint32_t errs = reinterpret_cast<volatile uint32_t*>(c->h_status)[1];
         if (errs) {
             char buf[96];
@@ -312,7 +325,9 @@ Engine* Engine::create(const std::string& path, std::string& err) {
     }
     if (configure_kernels() != cudaSuccess) { err = std::string("kernel configuration failed: ") + cudaGetErrorString(cudaGetLastError()); return nullptr; }
     im.pretok_per_sm = pretok_blocks_per_sm();
-    im.merge_per_sm = merge_blocks_per_sm();
+    im.words_per_sm = words_blocks_per_sm();
+    im.miss_per_sm = miss_blocks_per_sm();
+    im.asm_per_sm = assemble_blocks_per_sm();
     if (!im.upload_tables(err)) return nullptr;
     return e.release();
 }
@@ -399,24 +414,27 @@ int64_t Engine::profile_staged(float* ms_out) {
     if (!c) { last_error_ = "nothing staged"; return -1; }
     c->h_status[0] = 0;
     c->h_status[1] = 0;
-    ms_out[0] = ms_out[1] = ms_out[2] = 0.f;
+    for (int i = 0; i < 5; ++i) ms_out[i] = 0.f;
     if (c->staged_len == 0) return 0;
-    cudaEventRecord(c->ev0, c->stream);
+    cudaEventRecord(c->ev[0], c->stream);
     cudaMemsetAsync(c->d_ctrl, 0, c->ctrl_bytes, c->stream);
     if (c->batch) {
         cudaMemsetAsync(c->d_docmask, 0, c->mask_words * 4, c->stream);
         launch_docmask(c->args, c->d_docmask, c->docmask_blocks, c->stream);
     }
-    cudaEventRecord(c->ev1, c->stream);
+    cudaEventRecord(c->ev[1], c->stream);
     launch_pretok(c->args, c->pretok_blocks, c->stream);
-    cudaEventRecord(c->ev2, c->stream);
-    launch_merge(c->args, c->merge_blocks, c->stream);
-    cudaEventRecord(c->ev3, c->stream);
+    cudaEventRecord(c->ev[2], c->stream);
+    launch_words(c->args, c->words_blocks, c->stream);
+    cudaEventRecord(c->ev[3], c->stream);
+    launch_miss(c->args, c->miss_blocks, c->stream);
+    cudaEventRecord(c->ev[4], c->stream);
+    launch_assemble(c->args, c->asm_blocks, c->stream);
+    cudaEventRecord(c->ev[5], c->stream);
     cudaError_t e = cudaStreamSynchronize(c->stream);
     if (e != cudaSuccess) { last_error_ = std::string("profile: ") + cudaGetErrorString(e); return -1; }
-    cudaEventElapsedTime(&ms_out[0], c->ev1, c->ev2);
-    cudaEventElapsedTime(&ms_out[1], c->ev2, c->ev3);
-    cudaEventElapsedTime(&ms_out[2], c->ev0, c->ev3);
+    for (int i = 0; i < 4; ++i) cudaEventElapsedTime(&ms_out[i], c->ev[i + 1], c->ev[i + 2]);
+    cudaEventElapsedTime(&ms_out[4], c->ev[0], c->ev[5]);
     if (reinterpret_cast<volatile uint32_t*>(c->h_status)[1]) { last_error_ = "encode kernels reported an error"; return -1; }
     return reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
 }

@@ -33,7 +33,7 @@ public:
     int64_t replay_staged(float* ms_out);                 // one replay; CUDA-event time of the graph
     int64_t read_staged(uint32_t* out, uint32_t max_out, uint32_t* out_doc_tok);
     // Same work as one replay, launched kernel by kernel with an event between them:
-    // ms_out[0] = pretok kernel, ms_out[1] = merge kernel, ms_out[2] = whole sequence.
+    // ms_out[0..3] = pretok, words, miss, assemble kernels, ms_out[4] = whole sequence.
     int64_t profile_staged(float* ms_out);
     // Boundary bits of the staged input as left by the last replay: one bit per byte,
     // set where a pre-token starts; writes (len + 31) / 32 words.
@@ -48,7 +48,7 @@ public:
     uint32_t vocab_size() const { return hv_.vocab_size; }
     std::string last_error() const { return last_error_; }
     // Number of kernel launches one replay makes (for reporting).
-    int launches_per_replay(bool batch) const { return batch ? 3 : 2; }
+    int launches_per_replay(bool batch) const { return batch ? 5 : 4; }
     void table_bytes(uint64_t* merge, uint64_t* word, uint64_t* other) const;
 
 private:

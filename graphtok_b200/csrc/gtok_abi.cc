@@ -165,7 +165,8 @@ int32_t gtok_x_replay(void* handle, float* ms_out) {
     } catch (...) { return -1; }
 }
 
-int32_t gtok_x_profile(void* handle, float* ms_out3) {
+int32_t gtok_x_profile(void* handle, float* ms_out5) {
+    float* ms_out3 = ms_out5;
     if (!handle || !ms_out3) return -1;
     try {
         Handle* h = static_cast<Handle*>(handle);

@@ -99,7 +99,7 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     uint32_t meta[2] = {n, n_docs};
     std::vector<uint32_t> docmask, bmask(n_tiles * kTileWords + 8, 0xDEADBEEF), amask(n_tiles * kTileWords + 8, 0xDEADBEEF), tile_nb(n_tiles + 1, 0);
     std::vector<unsigned long long> st1(n_tiles + 1, 0), st2(n_tiles + 1, 0);
-    uint32_t ctl[4] = {0, 0, 0, 0}, status[4] = {0, 0, 0, 0};
+    uint32_t ctl[16] = {0}, status[4] = {0, 0, 0, 0};
     std::vector<uint32_t> gstage(static_cast<size_t>(n_tiles) * kTile + 64), grk(gstage.size()), gnw(gstage.size());
     EncodeArgs a;
     std::memset(&a, 0, sizeof a);
@@ -112,6 +112,12 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     a.bmask = bmask.data(); a.amask = amask.data(); a.tile_nb = tile_nb.data();
     a.st1 = st1.data(); a.st2 = st2.data(); a.ctl = ctl;
     a.gstage = gstage.data(); a.gwork_rk = grk.data(); a.gwork_nw = gnw.data();
+    std::vector<uint32_t> stage(gstage.size(), 0xABABABAB), ovf(static_cast<size_t>(n_tiles + 1) * kTokExtra, 0xABABABAB);
+    std::vector<unsigned long long> gmiss(gstage.size() / 2 + 64);
+    std::vector<uint32_t> glong(static_cast<size_t>(n_tiles + 1) * kLongPerTile * 3, 0xABABABAB);
+    a.stage = stage.data(); a.ovf = ovf.data(); a.gmiss = gmiss.data();
+    a.glong_g = glong.data(); a.glong_len = glong.data() + static_cast<size_t>(n_tiles + 1) * kLongPerTile;
+    a.glong_cnt = glong.data() + static_cast<size_t>(n_tiles + 1) * kLongPerTile * 2;
     a.out_tokens = out; a.out_cap = cap; a.status = status;
     a.tb = e->tb;
     if (force_non_monotone) a.tb.monotone = 0;
@@ -124,8 +130,23 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     }
     if (bmask_out) std::memcpy(bmask_out, bmask.data(), static_cast<size_t>(n_tiles) * kTileWords * 4);
     {
-        MergeSmem* sm = new MergeSmem();
-        for (uint32_t t = 0; t < n_tiles; ++t) { std::memset(sm, 0xCD, sizeof *sm); merge_tile(blk, a, *sm, static_cast<int>(t)); }
+        WordsSmem* sm = new WordsSmem();
+        // tiles of this kernel are independent: run them last to first to show it
+        for (uint32_t t = n_tiles; t-- > 0;) { std::memset(sm, 0xCD, sizeof *sm); words_tile(blk, a, *sm, static_cast<int>(t)); }
+        delete sm;
+    }
+    {
+        MissSmem* sm = new MissSmem();
+        std::memset(sm, 0xCD, sizeof *sm);
+        for (int i = 0; i < 256; ++i) sm->b2i[i] = a.tb.byte_to_id[i];
+        const uint32_t n_miss = ctl[CTL_NMISS], n_long = ctl[CTL_NLONG];
+        for (uint32_t first = 0; first < n_miss; first += kMissBatch) miss_batch(blk, a, *sm, first, n_miss);
+        for (uint32_t li = 0; li < n_long; ++li) long_word(blk, a, *sm, li);
+        delete sm;
+    }
+    {
+        AsmSmem* sm = new AsmSmem();
+        for (uint32_t t = 0; t < n_tiles; ++t) { std::memset(sm, 0xCD, sizeof *sm); assemble_tile(blk, a, *sm, static_cast<int>(t)); }
         delete sm;
     }
     if (ctl[2]) return -static_cast<int64_t>(ctl[2]);
