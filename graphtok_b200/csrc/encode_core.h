@@ -126,6 +126,16 @@ GTOK_DEV int fls32(uint32_t x) {   // index of highest set bit, x != 0
     return 31 - __builtin_clz(x);
 #endif
 }
+GTOK_DEV uint64_t brev64(uint64_t x) {
+#if defined(__CUDA_ARCH__)
+    return __brevll(x);
+#else
+    x = ((x >> 1) & 0x5555555555555555ull) | ((x & 0x5555555555555555ull) << 1);
+    x = ((x >> 2) & 0x3333333333333333ull) | ((x & 0x3333333333333333ull) << 2);
+    x = ((x >> 4) & 0x0F0F0F0F0F0F0F0Full) | ((x & 0x0F0F0F0F0F0F0F0Full) << 4);
+    return __builtin_bswap64(x);
+#endif
+}
 GTOK_DEV uint32_t shared_add(uint32_t* p, uint32_t v) {
 #if defined(__CUDA_ARCH__)
     return atomicAdd(p, v);
@@ -489,21 +499,26 @@ GTOK_DEV int ncls(uint8_t a) {
 // whose meaning is certain from the byte alone (CR/LF going back, 0x20 going forward;
 // never when an added-token literal could contain such a byte, never across a document
 // start) and leave the deciding position to the general code.
-GTOK_DEV bool no_docstart_in4(const EncodeArgs& a, int q) {     // q..q+3 within one mask word (q % 4 == 0)
-    if (!a.docmask) return q != 0;
-    if (q == 0) return false;
-    return ((ldg(a.docmask + (q >> 5)) >> (q & 31)) & 0xFu) == 0;
-}
 // q is a CR/LF byte: position of the first byte before the newline stretch that is not
 // CR/LF, or the CR/LF that opens its document (the caller's test then ends the walk).
+GTOK_DEV bool all_bytes_in(uint32_t v, uint32_t x, uint32_t y) {   // every byte of v equals x or y
+    for (int k = 0; k < 4; ++k) { uint32_t b = (v >> (8 * k)) & 0xFFu; if (b != x && b != y) return false; }
+    return true;
+}
+GTOK_DEV bool no_docstart_in16(const EncodeArgs& a, int q) {    // q..q+15 within one mask word (q % 16 == 0)
+    if (q == 0) return false;
+    if (!a.docmask) return true;
+    return ((ldg(a.docmask + (q >> 5)) >> (q & 31)) & 0xFFFFu) == 0;
+}
 GTOK_DEV int skip_back_newlines(const Win& w, int q) {
     const EncodeArgs& a = *w.a;
     if (a.tb.added_ws) return q;
     for (;;) {
         if (q < 0) return q;
-        if ((q & 3) == 3 && q >= 7) {
-            uint32_t v = ldg(reinterpret_cast<const uint32_t*>(a.text + q - 3));
-            if ((v == 0x0A0A0A0Au || v == 0x0A0D0A0Du || v == 0x0D0A0D0Au || v == 0x0D0D0D0Du) && no_docstart_in4(a, q - 3)) { q -= 4; continue; }
+        if ((q & 15) == 15 && q >= 31 && no_docstart_in16(a, q - 15)) {
+            const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + q - 15);
+            uint32_t v0 = ldg(p4), v1 = ldg(p4 + 1), v2 = ldg(p4 + 2), v3 = ldg(p4 + 3);
+            if (all_bytes_in(v0, 0x0Au, 0x0Du) && all_bytes_in(v1, 0x0Au, 0x0Du) && all_bytes_in(v2, 0x0Au, 0x0Du) && all_bytes_in(v3, 0x0Au, 0x0Du)) { q -= 16; continue; }
         }
         uint32_t b = ldg(a.text + q);
         if (b != 0x0Au && b != 0x0Du) return q;
@@ -518,9 +533,9 @@ GTOK_DEV int skip_forward_spaces(const Win& w, int r) {
     if (a.tb.added_ws) return r;
     for (;;) {
         if (r >= w.n) return -1;
-        if ((r & 3) == 0 && r + 4 <= w.n) {
-            uint32_t v = ldg(reinterpret_cast<const uint32_t*>(a.text + r));
-            if (v == 0x20202020u && no_docstart_in4(a, r)) { r += 4; continue; }
+        if ((r & 15) == 0 && r + 16 <= w.n && no_docstart_in16(a, r)) {
+            const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + r);
+            if (ldg(p4) == 0x20202020u && ldg(p4 + 1) == 0x20202020u && ldg(p4 + 2) == 0x20202020u && ldg(p4 + 3) == 0x20202020u) { r += 16; continue; }
         }
         if (is_docstart_global(a, r)) return -1;
         if (ldg(a.text + r) != 0x20u) return r;
@@ -935,7 +950,25 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             bnd |= Scr & (pL | pN);
             bnd |= Spl & ~pS;
             bnd |= Spl & pS & ~pCR & nNonS;
-            unc |= Spl & pS & pCR;
+            // Plain whitespace right after a newline: it opens the rest of the run when the newline
+            // stretch before it hangs off a punctuation token, or when no later newline in the run
+            // pulls it into \s*[\r\n]+.  Both are floods along a stretch of bits (carry of an
+            // addition); a stretch that leaves the window is decided one by one instead.
+            const uint64_t cand = Spl & pS & pCR;
+            if (cand) {
+                const uint64_t Mcr = CR & ~DOC;                              // newline bytes, stretches cut at document starts
+                const uint64_t rs = CR & (~(CR << 1) | DOC);                 // first byte of each stretch
+                const uint64_t absorbed = ((Mcr + (rs & pO & Mcr)) ^ Mcr) & Mcr;
+                const uint64_t from_edge = (Mcr & 1ull) ? (((Mcr + 1ull) ^ Mcr) & Mcr) : 0ull;   // stretch whose start is not visible
+                const uint64_t SplF = fill(Spl) & ~DOC;
+                const uint64_t top_nl = SplF & ((CR & ~DOC) >> 1);           // whitespace byte directly before a newline
+                const uint64_t rM = brev64(SplF), rT = brev64(top_nl);
+                const uint64_t later_nl = brev64(((rM + rT) ^ rM) & rM);     // whitespace stretches that end in a newline
+                const uint64_t to_edge = (rM & 1ull) ? brev64(((rM + 1ull) ^ rM) & rM) : 0ull;  // stretch that reaches the window's end
+                const uint64_t unknown = cand & ((from_edge << 1) | to_edge);
+                bnd |= cand & ~unknown & ((absorbed << 1) | ~later_nl);
+                unc |= unknown;
+            }
             const uint64_t ppOorSP = prevcp(pO | pSP);         // prev-prev is punctuation or a literal space
             bnd |= L & ((pS & pCR) | (pO & ppOorSP) | pN);
             if (family == 2) bnd |= N;
@@ -1083,8 +1116,8 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 // ==================================================================================
 //                                   MERGE + ASSEMBLY
 // ==================================================================================
-constexpr int kMissBatch = kThreads;           // unknown pre-tokens per batch of the miss kernel, one per thread
-constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB)
+constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch of the miss kernel
+constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB); owners fit a byte
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
 enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7 };
 
@@ -1108,10 +1141,13 @@ struct MissSmem {
     uint32_t red[kThreads + 8];
     uint32_t aoff[kThreads];
     unsigned long long word[kThreads]; // this batch's entries of the global list
+    uint8_t owner[kArenaSyms];         // which of the batch's pre-tokens an arena slot belongs to
+    uint8_t rawb[kArenaSyms];          // the slot's text byte
     uint32_t ctr[8];
     unsigned long long clk_last;
 };
 struct AsmSmem {
+    alignas(16) uint32_t tok[kTile + kTokExtra];   // the tile's slots, then its overflow slots
     uint32_t scan[kThreads];
     uint32_t ex[8];
     uint32_t lref_idx[kLongPerTile], lref_at[kLongPerTile];
@@ -1547,22 +1583,43 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t f
         });
         uint32_t nb = blk.reduce_min(sm.red);
         if (nb == 0xFFFFFFFFu) nb = kThreads;
+        // owner: which slots are mine (shared memory only)
         blk.par([&](int tid) {
             if (static_cast<uint32_t>(tid) >= nb) return;
-            const unsigned long long wv = sm.word[done + tid];
-            const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32), at = sm.scan[tid];
+            const uint32_t len = static_cast<uint32_t>(sm.word[done + tid] >> 32), at = sm.scan[tid];
             if (static_cast<uint32_t>(tid) + 1 == nb) sm.ctr[C_USED] = at + len;
-            bool resolved = false;
-            if (tb.ignore_merges && len > kWordKeyMax) {
-                uint32_t id = probe_long(tb, a.text, g, len);
-                if (id != kNoToken) { put_id(a, g, 0, id); resolved = true; }
-            }
-            for (uint32_t i = 0; i < len; ++i) {
-                ids[at + i] = sm.b2i[ldg(a.text + g + i)];
-                rk[at + i] = (!resolved && i + 1 < len) ? kPending : kNoRank;
-            }
-            sm.aoff[tid] = resolved ? 0xFFFFFFFFu : at;
+            for (uint32_t i = 0; i < len; ++i) sm.owner[at + i] = static_cast<uint8_t>(tid);
+            sm.aoff[tid] = at;
         });
+        // all threads: fetch the bytes, one slot each, so the loads overlap
+        {
+            const uint32_t used0 = sm.ctr[C_USED];
+            blk.par([&](int tid) {
+                for (uint32_t sidx = tid; sidx < used0; sidx += kThreads) {
+                    const uint32_t w = sm.owner[sidx];
+                    const unsigned long long wv = sm.word[done + w];
+                    const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32), at = sm.scan[w];
+                    const uint32_t bt = ldg(a.text + g + (sidx - at));
+                    sm.rawb[sidx] = static_cast<uint8_t>(bt);
+                    ids[sidx] = sm.b2i[bt];
+                    rk[sidx] = (sidx + 1 < at + len) ? kPending : kNoRank;
+                }
+            });
+        }
+        // owner: a pre-token of 16 bytes or more that is itself in the vocabulary (ignore_merges)
+        if (tb.ignore_merges) {
+            blk.par([&](int tid) {
+                if (static_cast<uint32_t>(tid) >= nb) return;
+                const unsigned long long wv = sm.word[done + tid];
+                const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32), at = sm.scan[tid];
+                if (len <= kWordKeyMax) return;
+                uint32_t id = probe_long_bytes(tb, sm.rawb + at, len);
+                if (id == kNoToken) return;
+                put_id(a, g, 0, id);
+                for (uint32_t i = 0; i < len; ++i) rk[at + i] = kNoRank;
+                sm.aoff[tid] = 0xFFFFFFFFu;
+            });
+        }
         const uint32_t used = sm.ctr[C_USED];
         blk.par([&](int tid) {
             for (uint32_t sidx = tid; sidx < used; sidx += kThreads) {
@@ -1653,16 +1710,25 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
         if (v == kInvalidTok) return 0u;
         return (v & kLongRef) ? ldg(a.glong_cnt + (v & ~kLongRef)) : 1u;
     };
-    // ---- A0: ids per thread ----
+    // ---- A0: the tile's slots into shared memory; ids per thread ----
     blk.par([&](int tid) {
         if (tid == 0) sm.ctr[C_NLREF] = 0;
+#if defined(__CUDA_ARCH__)
+        for (int c = tid; c < kTile / 4; c += kThreads)
+            reinterpret_cast<uint4*>(sm.tok)[c] = __ldg(reinterpret_cast<const uint4*>(a.stage + t0) + c);
+#else
+        for (int i = tid; i < kTile; i += kThreads) sm.tok[i] = a.stage[t0 + i];
+#endif
+        if (tid < kTokExtra) sm.tok[kTile + tid] = ovf[tid];
+    });
+    blk.par([&](int tid) {
         uint32_t sum = 0;
-        const uint32_t* sp = a.stage + t0 + tid * kPer;
+        const uint32_t* sp = sm.tok + tid * kPer;
         for (int i = 0; i < kPer; ++i) sum += weight(sp[i]);
         sm.scan[tid] = sum;
         if (tid < kTokExtra / kPer) {
             uint32_t ex = 0;
-            for (int i = 0; i < kPer; ++i) ex += ovf[tid * kPer + i] != kInvalidTok;
+            for (int i = 0; i < kPer; ++i) ex += sm.tok[kTile + tid * kPer + i] != kInvalidTok;
             sm.ex[tid] = ex;
         }
     });
@@ -1677,7 +1743,7 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
     // ---- A2: ids to their final place ----
     blk.par([&](int tid) {
         uint32_t at = base + sm.scan[tid];
-        const uint32_t* sp = a.stage + t0 + tid * kPer;
+        const uint32_t* sp = sm.tok + tid * kPer;
         for (int i = 0; i < kPer; ++i) {
             uint32_t v = sp[i];
             if (v == kInvalidTok) continue;
@@ -1694,7 +1760,7 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
             at = base + total_main;
             for (int t = 0; t < tid; ++t) at += sm.ex[t];
             for (int i = 0; i < kPer; ++i) {
-                uint32_t v = ovf[tid * kPer + i];
+                uint32_t v = sm.tok[kTile + tid * kPer + i];
                 if (v == kInvalidTok) continue;
                 if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + CTL_ERR, kErrOutputFull);
                 ++at;
@@ -1730,7 +1796,7 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
                 if (off >= t1 || off >= n) break;
                 uint32_t o = off - t0, owner = o / kPer;
                 uint32_t cnt = sm.scan[owner];
-                for (uint32_t i = owner * kPer; i < o; ++i) cnt += weight(a.stage[t0 + i]);
+                for (uint32_t i = owner * kPer; i < o; ++i) cnt += weight(sm.tok[i]);
                 a.out_doc_tok[d] = base + cnt;
             }
             if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
