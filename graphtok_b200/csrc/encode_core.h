@@ -905,7 +905,12 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         uint64_t bnd = 0, pend = 0, unc = 0;
         // words the algebra cannot be trusted on
         // (a continuation byte right after an apostrophe stretches a contraction past three bytes)
-        const bool messy = (C & (C << 1) & (C << 2) & (C << 3)) != 0 || (DOC & C) != 0 || AD != 0 ||
+        // An added-token literal is its start bit plus continuation bits; those long stretches are
+        // harmless to the algebra (the literal has no class, so its neighbours see "nothing").
+        const uint64_t lit1 = (AD << 1) & C;
+        const uint64_t lit = ((C + lit1) ^ C) & C;
+        const uint64_t Cg = C & ~lit;
+        const bool messy = (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 ||
                            (((AP << 1) | (AP << 2) | (AP << 3)) & C) != 0;
         if (messy) unc = LEAD;
         // Contractions: 's 't 'm 'd (tail 1) and 're 've 'll (tail 2), when the regex cursor can be
@@ -1164,9 +1169,20 @@ enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5
 GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint32_t len, uint32_t* out) {
     constexpr uint32_t kDead = 0xFFFFFFFFu;
     for (;;) {
+        // leftmost lowest rank; four slots per step so that the loads overlap
         uint32_t best = kNoRank, bi = 0;
-        for (uint32_t i = 0; i < len; ++i) {
-            uint32_t r = rk[i];
+        uint32_t i = 0;
+        for (; i + 4 <= len; i += 4) {
+            const uint32_t r0 = rk[i], r1 = rk[i + 1], r2 = rk[i + 2], r3 = rk[i + 3];
+            const uint32_t m01 = r1 < r0 ? r1 : r0, m23 = r3 < r2 ? r3 : r2;
+            const uint32_t m = m23 < m01 ? m23 : m01;
+            if (m < best) {
+                best = m;
+                bi = (r0 == m) ? i : (r1 == m) ? i + 1 : (r2 == m) ? i + 2 : i + 3;
+            }
+        }
+        for (; i < len; ++i) {
+            const uint32_t r = rk[i];
             if (r < best) { best = r; bi = i; }
         }
         if (best == kNoRank) break;
