@@ -84,7 +84,8 @@ struct EncodeArgs {
     uint32_t* gwork_nw;           // u32 per byte: result workspace for very long pre-tokens
     uint32_t* stage;              // u32 per byte: id stored at the byte where its pre-token starts (+k for its k-th id), else invalid
     uint32_t* ovf;                // kTokExtra u32 per tile: ids of a tile's last pre-token that do not fit before the tile's end
-    unsigned long long* gmiss;    // pre-tokens of 2..64 bytes the whole-word table did not know: position | len << 32
+    unsigned long long* gmiss;    // pre-tokens of 2..16 bytes the whole-word table did not know: position | len << 32
+    unsigned long long* gmed;     // the same for 17..64 bytes
     uint32_t* glong_g;            // pre-tokens longer than 64 bytes: position, length (0 = not known yet), id count
     uint32_t* glong_len;
     uint32_t* glong_cnt;
@@ -1124,7 +1125,9 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch of the miss kernel
 constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB); owners fit a byte
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
-enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7 };
+enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8 };
+constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
+constexpr int kMedBatch = 64;                  // so that the long merge chains of the latter start first and spread over more blocks
 
 struct WordsSmem {
     alignas(16) uint8_t txt[kTile + 64];
@@ -1132,7 +1135,8 @@ struct WordsSmem {
     uint32_t am[kTileWords + 4];
     alignas(16) uint32_t tok[kTile + kTokExtra];
     uint16_t wl[kTile + 8];            // offsets in the tile of the pre-token starts, in order; then the end sentinel
-    uint32_t miss[kTile / 2];          // offset | len << 12
+    uint32_t miss[kTile / 2];          // offset | len << 12, up to 16 bytes
+    uint32_t med[kTile / 16];          // offset | len << 12, 17..64 bytes
     uint32_t lng_o[kLongPerTile], lng_len[kLongPerTile];
     uint32_t b2i[256];
     uint32_t scan[kThreads];
@@ -1159,7 +1163,7 @@ struct AsmSmem {
     uint32_t ctr[8];
     unsigned long long clk_last;
 };
-enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7 };
+enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7, C_NMED = 5, C_BASED = 6 };
 
 // Greedy BPE of one pre-token by a single thread (lowest rank first, leftmost among
 // equals, src/host_encode.cc:617-648).  ids/rk/nw are the pre-token's stretch of the
@@ -1169,20 +1173,9 @@ enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5
 GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint32_t len, uint32_t* out) {
     constexpr uint32_t kDead = 0xFFFFFFFFu;
     for (;;) {
-        // leftmost lowest rank; four slots per step so that the loads overlap
         uint32_t best = kNoRank, bi = 0;
-        uint32_t i = 0;
-        for (; i + 4 <= len; i += 4) {
-            const uint32_t r0 = rk[i], r1 = rk[i + 1], r2 = rk[i + 2], r3 = rk[i + 3];
-            const uint32_t m01 = r1 < r0 ? r1 : r0, m23 = r3 < r2 ? r3 : r2;
-            const uint32_t m = m23 < m01 ? m23 : m01;
-            if (m < best) {
-                best = m;
-                bi = (r0 == m) ? i : (r1 == m) ? i + 1 : (r2 == m) ? i + 2 : i + 3;
-            }
-        }
-        for (; i < len; ++i) {
-            const uint32_t r = rk[i];
+        for (uint32_t i = 0; i < len; ++i) {
+            uint32_t r = rk[i];
             if (r < best) { best = r; bi = i; }
         }
         if (best == kNoRank) break;
@@ -1483,6 +1476,11 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                     else global_or(a.ctl + CTL_ERR, kErrInternal);
                     continue;
                 }
+                if (len > kShortWordMax) {
+                    uint32_t slot = shared_add(&sm.ctr[C_NMED], 1u);
+                    sm.med[slot] = o | (len << 12);
+                    continue;
+                }
                 if (len > kWordKeyMax) {
                     uint32_t slot = shared_add(&sm.ctr[C_NMISS], 1u);
                     sm.miss[slot] = o | (len << 12);
@@ -1528,19 +1526,28 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
         if (nl > kLongPerTile) nl = kLongPerTile;
         sm.ctr[C_NTEAM] = nl;
 #if defined(__CUDA_ARCH__)
+        const uint32_t nd = sm.ctr[C_NMED];
         sm.ctr[C_BASEM] = nm ? atomicAdd(a.ctl + CTL_NMISS, nm) : 0u;
         sm.ctr[C_BASEL] = nl ? atomicAdd(a.ctl + CTL_NLONG, nl) : 0u;
+        sm.ctr[C_BASED] = nd ? atomicAdd(a.ctl + CTL_NMED, nd) : 0u;
 #else
+        const uint32_t nd = sm.ctr[C_NMED];
         sm.ctr[C_BASEM] = a.ctl[CTL_NMISS]; a.ctl[CTL_NMISS] += nm;
         sm.ctr[C_BASEL] = a.ctl[CTL_NLONG]; a.ctl[CTL_NLONG] += nl;
+        sm.ctr[C_BASED] = a.ctl[CTL_NMED]; a.ctl[CTL_NMED] += nd;
 #endif
     });
     {
         const uint32_t nm = sm.ctr[C_NMISS], nl = sm.ctr[C_NTEAM], bm0 = sm.ctr[C_BASEM], bl0 = sm.ctr[C_BASEL];
+        const uint32_t nd = sm.ctr[C_NMED], bd0 = sm.ctr[C_BASED];
         blk.par([&](int tid) {
             for (uint32_t i = tid; i < nm; i += kThreads) {
                 uint32_t mv = sm.miss[i];
                 a.gmiss[bm0 + i] = static_cast<unsigned long long>(t0 + (mv & 0xFFFu)) | (static_cast<unsigned long long>(mv >> 12) << 32);
+            }
+            for (uint32_t i = tid; i < nd; i += kThreads) {
+                uint32_t mv = sm.med[i];
+                a.gmed[bd0 + i] = static_cast<unsigned long long>(t0 + (mv & 0xFFFu)) | (static_cast<unsigned long long>(mv >> 12) << 32);
             }
             for (uint32_t i = tid; i < nl; i += kThreads) {
                 a.glong_g[bl0 + i] = t0 + sm.lng_o[i];
@@ -1573,15 +1580,25 @@ GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
 // The owner lays its symbols out in the block's arena, all threads probe the pairs, the
 // owner merges (lowest rank first) and stores the ids.
 template <class Blk>
-GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t first, uint32_t n_miss) {
+GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, uint32_t first, uint32_t n_miss, uint32_t batch) {
     const DeviceTables& tb = a.tb;
     constexpr uint32_t kPending = 0xFFFFFFFDu;
     uint32_t* ids = sm.ws;
     uint32_t* rk = sm.ws + kArenaSyms;
     uint32_t* nw = sm.ws + 2 * kArenaSyms;
-    const uint32_t n_here = n_miss - first < static_cast<uint32_t>(kMissBatch) ? n_miss - first : static_cast<uint32_t>(kMissBatch);
+    const uint32_t n_here = n_miss - first < batch ? n_miss - first : batch;
+    auto mark = [&](int slot) {
+        if (!a.phase_clk) return;
+        blk.par([&](int tid) {
+            if (tid != 0) return;
+            unsigned long long t = cycle_now();
+            if (slot >= 0) add_cycles(a.phase_clk + slot, t - sm.clk_last);
+            sm.clk_last = t;
+        });
+    };
+    mark(-1);
     blk.par([&](int tid) {
-        if (static_cast<uint32_t>(tid) < n_here) sm.word[tid] = a.gmiss[first + tid];
+        if (static_cast<uint32_t>(tid) < n_here) sm.word[tid] = list[first + tid];
     });
     uint32_t done = 0;
     while (done < n_here) {
@@ -1599,6 +1616,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t f
         });
         uint32_t nb = blk.reduce_min(sm.red);
         if (nb == 0xFFFFFFFFu) nb = kThreads;
+        mark(16);
         // owner: which slots are mine (shared memory only)
         blk.par([&](int tid) {
             if (static_cast<uint32_t>(tid) >= nb) return;
@@ -1622,6 +1640,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t f
                 }
             });
         }
+        mark(17);
         // owner: a pre-token of 16 bytes or more that is itself in the vocabulary (ignore_merges)
         if (tb.ignore_merges) {
             blk.par([&](int tid) {
@@ -1636,6 +1655,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t f
                 sm.aoff[tid] = 0xFFFFFFFFu;
             });
         }
+        mark(18);
         const uint32_t used = sm.ctr[C_USED];
         blk.par([&](int tid) {
             for (uint32_t sidx = tid; sidx < used; sidx += kThreads) {
@@ -1645,6 +1665,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t f
                 nw[sidx] = r.res;
             }
         });
+        mark(19);
         blk.par([&](int tid) {
             if (static_cast<uint32_t>(tid) >= nb) return;
             const uint32_t at = sm.aoff[tid];
@@ -1655,6 +1676,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t f
             uint32_t cnt = bpe_arena(a, ids + at, rk + at, nw + at, len, nw + at);
             for (uint32_t k = 0; k < cnt; ++k) put_id(a, g, k, nw[at + k]);
         });
+        mark(20);
         done += nb;
     }
 }

@@ -131,16 +131,19 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
     MissSmem& sm = *reinterpret_cast<MissSmem*>(smem_raw);
     __shared__ uint32_t s_pick;
     GpuBlk blk;
-    const uint32_t n_miss = a.ctl[CTL_NMISS], n_long = a.ctl[CTL_NLONG];
+    const uint32_t n_miss = a.ctl[CTL_NMISS], n_med = a.ctl[CTL_NMED], n_long = a.ctl[CTL_NLONG];
+    const uint32_t med_batches = (n_med + kMedBatch - 1) / kMedBatch, short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
     sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
     __syncthreads();
+    // the batches of longer pre-tokens first: their merge chains decide when the kernel ends
     for (;;) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_BATCH, 1u);
         __syncthreads();
-        const uint32_t first = s_pick * kMissBatch;
+        const uint32_t t = s_pick;
         __syncthreads();
-        if (first >= n_miss) break;
-        miss_batch(blk, a, sm, first, n_miss);
+        if (t >= med_batches + short_batches) break;
+        if (t < med_batches) miss_batch(blk, a, sm, a.gmed, t * kMedBatch, n_med, kMedBatch);
+        else miss_batch(blk, a, sm, a.gmiss, (t - med_batches) * kMissBatch, n_miss, kMissBatch);
     }
     for (;;) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);
