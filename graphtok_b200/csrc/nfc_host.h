@@ -1,0 +1,18 @@
+// Unicode Normalization Form C on the host, for vocabularies whose tokenizer.json
+// declares {"type": "NFC"} (Qwen2.5).  Plays the role of the reference's host
+// normaliser (src/vocab.cc:1234-1668, normalize_view_for_vocab): a quick scan that leaves
+// already-normalised text untouched, and re-normalisation of the stretches around the
+// codepoints that can make a text non-NFC.  Tables: nfc_tables.h (Unicode 15.0).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+namespace gtok {
+
+// Returns false and leaves `out` untouched when `text` is already NFC (use the input as
+// is); otherwise writes the normalised bytes to `out` and returns true.  Bytes that are
+// not valid UTF-8 are passed through unchanged and act as barriers.
+bool nfc_normalize(const uint8_t* text, size_t len, std::string& out);
+
+}  // namespace gtok

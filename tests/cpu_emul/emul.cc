@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "../../graphtok_b200/csrc/encode_core.h"
+#include "../../graphtok_b200/csrc/nfc_host.h"
 #include "../../graphtok_b200/csrc/shard_plan.h"
 #include "../../graphtok_b200/csrc/tables_build.h"
 #include "../../graphtok_b200/csrc/unicode_class_table.h"
@@ -152,6 +153,15 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     }
     if (ctl[2]) return -static_cast<int64_t>(ctl[2]);
     return status[0];
+}
+
+// The library's host-side NFC (csrc/nfc_host.cc), reachable without a GPU handle.
+int64_t gtok_emul_nfc(const uint8_t* text, uint64_t len, uint8_t* out, uint64_t cap) {
+    std::string o;
+    if (!gtok::nfc_normalize(text, len, o)) { if (len > cap) return -1; std::memcpy(out, text, len); return static_cast<int64_t>(len); }
+    if (o.size() > cap) return -1;
+    std::memcpy(out, o.data(), o.size());
+    return static_cast<int64_t>(o.size());
 }
 
 // The shard planner of libgtok (gtok_x_plan_chunks), reachable without a GPU handle.

@@ -43,13 +43,24 @@ def build_emul():
     deps = [os.path.join(EMUL_DIR, "emul.cc")] + [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     if _stale(EMUL_SO, deps):
         subprocess.run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-o", EMUL_SO, os.path.join(EMUL_DIR, "emul.cc"),
-                        os.path.join(CSRC, "vocab_host.cc"), os.path.join(CSRC, "tables_build.cc")], check=True)
+                        os.path.join(CSRC, "vocab_host.cc"), os.path.join(CSRC, "tables_build.cc"), os.path.join(CSRC, "nfc_host.cc")], check=True)
     return EMUL_SO
 
 
 def nfc(data):
     """NFC of UTF-8 bytes (Python unicodedata, Unicode 15.0, which Hugging Face tokenizers agrees with)."""
     return unicodedata.normalize("NFC", data.decode("utf-8")).encode("utf-8")
+
+
+def lib_nfc(data):
+    """NFC by the library's own host code (csrc/nfc_host.cc), for checking it against `nfc`."""
+    lib = ctypes.CDLL(build_emul())
+    lib.gtok_emul_nfc.restype = ctypes.c_int64
+    lib.gtok_emul_nfc.argtypes = [ctypes.c_char_p, ctypes.c_uint64, ctypes.c_char_p, ctypes.c_uint64]
+    out = ctypes.create_string_buffer(len(data) * 3 + 16)
+    n = lib.gtok_emul_nfc(bytes(data), len(data), out, len(out))
+    assert n >= 0
+    return out.raw[:n]
 
 
 class Oracle:

@@ -112,6 +112,29 @@ def test_merges_as_pairs_are_accepted(built, oracles):
         os.remove(p)
 
 
+def test_host_nfc_matches_unicodedata(built):
+    """The library's NFC (used before the graph for Qwen2.5 vocabularies) against Python's, which
+    Hugging Face's normaliser agrees with: named cases, a small-alphabet fuzz, every codepoint once."""
+    import random
+    import unicodedata as ud
+    named = ["e\u0301", "a\u0308o\u0308", "A\u030a", "\u212b", "\u1e9b\u0323", "q\u0307\u0323", "\uac00", "\u1100\u1161\u11a8", "\u0958",
+             "\u0b47\u0b56", "x\u0301\u0301\u0301", "\u0301a", "\ufb01 \u00bd \u2126", "a\u0323\u0302", "\u0f73", "\u1f71", "\u0344", "D\u0307\u0323",
+             "\u09c7\u09be", "plain ascii", "", "\u65e5\u672c\u8a9e", "\U0001d15e", "\u0cc6\u0cc2\u0cd5"]
+    for s in named:
+        assert oracle_lib.lib_nfc(s.encode()) == ud.normalize("NFC", s).encode(), repr(s)
+    rng = random.Random(4)
+    pool = [chr(c) for c in list(range(0x41, 0x48)) + list(range(0x300, 0x370)) + [0xC0, 0xE9, 0x323, 0x1100, 0x1161, 0x11A8, 0xAC00, 0xAC01, 0x958, 0xB47,
+                                                                                     0xB56, 0xB3E, 0x344, 0x340, 0x20, 0x3099, 0x304B, 0x1E0A, 0x1D157, 0x1D165]]
+    for _ in range(20000):
+        s = "".join(rng.choice(pool) for _ in range(rng.randint(1, 9)))
+        assert oracle_lib.lib_nfc(s.encode()) == ud.normalize("NFC", s).encode(), [hex(ord(c)) for c in s]
+    blob = "".join("a" + chr(cp) + "b" for cp in range(0x80, 0x30000) if not 0xD800 <= cp <= 0xDFFF)
+    assert oracle_lib.lib_nfc(blob.encode()) == ud.normalize("NFC", blob).encode()
+    # bytes that are not UTF-8 pass through untouched
+    raw = b"ab\xcc\xff e\xcc\x81 \xe4\xb8"
+    assert oracle_lib.lib_nfc(raw) == b"ab\xcc\xff \xc3\xa9 \xe4\xb8"
+
+
 def test_document_plan_is_contiguous_and_balanced(built):
     import graphtok_b200
     rng = np.random.default_rng(0)

@@ -79,6 +79,19 @@ def test_boundary_bits_match_oracle_starts(gtoks, oracles, family):
         assert np.array_equal(g.boundaries(len(b)), want), repr(t[:60])
 
 
+def test_qwen_raw_text_is_normalised_inside_the_call(gtoks, oracles):
+    """gtok_encode applies the vocabulary's NFC itself: raw (decomposed) text gives the golden ids."""
+    data = json.load(open(os.path.join(GOLDEN, "golden_qwen25.json")))
+    g = gtoks["qwen25"]
+    for row in data["cases"]:
+        assert g.encode(row["text"].encode("utf-8")).tolist() == row["ids"], repr(row["text"][:40])
+    docs = ["cafe\u0301", "", "nai\u0308ve", "plain", "\u1100\u1161\u11a8 x"]
+    blob, offs = cases.make_batch(5, docs)
+    ids, doc = g.encode_batch(blob, offs)
+    want, want_doc = oracles["qwen25"].encode_batch(blob, offs)
+    assert np.array_equal(ids, want) and np.array_equal(doc, want_doc)
+
+
 def test_return_codes(gtoks):
     g = gtoks["gpt2"]
     lib = g.lib
