@@ -246,6 +246,15 @@ int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset) {
     try { return static_cast<Handle*>(handle)->engine->read_phase_clocks(reinterpret_cast<unsigned long long*>(out32), reset != 0); } catch (...) { return -1; }
 }
 
+int32_t gtok_x_token_bytes(void* handle, uint32_t id, uint8_t* out, uint32_t cap) {
+    if (!handle) return -1;
+    const gtok::HostVocab& hv = static_cast<Handle*>(handle)->engine->vocab();
+    if (id >= hv.token_bytes.size()) return -1;
+    const std::string& b = hv.token_bytes[id];
+    if (out && cap >= b.size() && !b.empty()) std::memcpy(out, b.data(), b.size());
+    return static_cast<int32_t>(b.size());
+}
+
 int32_t gtok_x_plan_chunks(void* handle, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out_offsets) {
     if (!handle || (!text && len) || !n_parts || !out_offsets) return -1;
     try {

@@ -115,6 +115,10 @@ int32_t gtok_x_launches_per_replay(void* handle, int32_t batch);
  * serialise them.  Returns 0, -1 on error, -3 when `len` exceeds the limit. */
 int32_t gtok_x_boundaries_noalloc(void* handle, const void* text_dev, uint32_t len, void* out_bits_dev, void* cuda_stream);
 
+/* Raw bytes of token `id` (the spelling the ids decode to); returns the length, -1 for an
+ * id outside the vocabulary.  Nothing is written when `cap` is too small. */
+int32_t gtok_x_token_bytes(void* handle, uint32_t id, uint8_t* out, uint32_t cap);
+
 /* Partitioning over the GPUs of one box (no counterpart in the reference, which is
  * single-GPU).  gtok_x_plan_chunks cuts one document into n_parts pieces at
  * positions where a pre-token starts whatever precedes it (letter | space letter),

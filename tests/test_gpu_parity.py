@@ -201,3 +201,35 @@ def test_configuration_2_batch(built):
         assert np.array_equal(ids, want_ids) and np.array_equal(doc, want_doc)
     finally:
         g.close()
+
+
+def test_python_module_surface(built, oracles):
+    """The reference's Python classes over this library: same calls, same return types."""
+    import graphtok_b200.gpu_bpe_tokenizer as gpu_bpe_tokenizer
+    tok = gpu_bpe_tokenizer.Tokenizer(tiny_vocab("llama3"), max_input_chars=4096)
+    o = oracles["llama3"]
+    text = "Hello, world! It's 2026 <|reserved_special_token_3|> done"
+    ids = tok.encode(text)
+    assert isinstance(ids, list) and ids == o.encode(text.encode()).tolist() == tok(text)
+    arr = tok.encode_numpy(text.encode())
+    assert arr.dtype == np.uint32 and arr.tolist() == ids
+    toks, offs = tok.encode_batch([text, "", "second doc"])
+    assert toks.dtype == np.uint32 and offs.dtype == np.uint32 and offs.tolist()[0] == 0 and len(offs) == 4
+    assert toks[offs[0]:offs[1]].tolist() == ids and offs[1] == offs[2]
+    e_t, e_o = tok.encode_batch([])
+    assert e_t.size == 0 and e_o.tolist() == [0]
+    assert tok.decode(ids) == text
+    long_text = "grow " * 5000                                  # beyond max_input_chars: capacity grows
+    assert tok.encode_numpy(long_text).tolist() == o.encode(long_text.encode()).tolist()
+    assert tok.active_capacity >= len(long_text) and tok.regex_kind == "Llama3" and tok.cpu_backend == "off" and tok.last_route == "gpu"
+    assert tok.vocab_size > 256 and tok.host_max_bytes == 0
+    dev = tok.encode_to_device(text)
+    assert dev.is_cuda and dev.cpu().numpy().astype(np.uint32).tolist() == ids
+    tok.bench_stage(text)
+    n, ms = tok.bench_run()
+    assert n == len(ids) and ms >= 0
+    with pytest.raises(ValueError):
+        gpu_bpe_tokenizer.Dispatcher(tiny_vocab("gpt2"), policy="sometimes")
+    d = gpu_bpe_tokenizer.Dispatcher(tiny_vocab("llama3"), cpu_workers=0, policy="gpu")
+    assert d.encode_numpy(text).tolist() == ids and d.stats()["gpu_requests"] == 1 and d.cpu_backend == "off"
+    d.close()
