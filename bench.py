@@ -276,6 +276,9 @@ def main():
             "miss_kernel": n_bytes * 0.25 + 4.0 * n_tok * 0.25 + tm,
             "assemble_kernel": 4.0 * n_bytes + 4.0 * n_tok,
         }
+        # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures of
+        # this workload summarised under profiles/*_kernel_config1.md
+        traffic_of = {"pretok_kernel": 4.76e6 + 8.35e6, "words_kernel": 11.43e6, "miss_kernel": 13.79e6 + 0.14e6, "assemble_kernel": 18.39e6}
         dom = int(np.argmax(kern_ms))
         algo = algo_of[names[dom]]
         achieved = algo / (kern_ms[dom] * 1e-3) / 1e9
@@ -292,7 +295,7 @@ def main():
             "gpu_launches": 4 * args.steps * world,
             "kernels_ms": dict(zip(names, kern_ms)),
             "roofline": {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_kind, "traffic": None, "algorithmic_bytes": algo,
+                         "peak_source": peak_kind, "traffic": traffic_of[names[dom]], "algorithmic_bytes": algo,
                          "whole_replay": {"achieved": whole, "frac": whole / peak}},
             "clocks": clocks,
             "wall_s_timed_region": wall,
