@@ -2,6 +2,8 @@
 #include "../../include/gtok.h"
 
 #include <chrono>
+#include <condition_variable>
+#include <deque>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -26,11 +28,29 @@ struct Handle {
     std::string norm_doc;
 };
 
+// Leader/follower batching (the reference's src/dispatcher.cc:133-205): a request thread
+// queues its text; whoever finds no batch in progress becomes the leader, takes everything
+// queued so far (up to the byte and document limits), encodes it as ONE batch replay and hands
+// each follower its slice.  A request larger than the batch limit runs alone.
+struct Request {
+    const uint8_t* text;
+    uint32_t len;
+    uint32_t* out;
+    uint32_t max_out;
+    int32_t result = 0;
+    bool done = false;
+};
 struct Dispatcher {
     Handle handle;
     std::mutex mu;
+    std::condition_variable cv;
+    std::deque<Request*> queue;
+    bool leader_active = false;
     uint32_t max_batch_bytes = 0, max_batch_docs = 0;
     uint64_t stats[5] = {0, 0, 0, 0, 0};
+    // leader scratch
+    std::vector<uint8_t> blob;
+    std::vector<uint32_t> offs, toks, doc_tok;
 };
 
 bool open_handle(Handle& h, const char* path, uint32_t max_bytes) {
@@ -53,6 +73,47 @@ int32_t do_encode(Handle* h, const uint8_t* text, uint32_t len, uint32_t* out, u
     }
     if (len > h->cap_bytes) return -3;
     int64_t n = h->engine->encode(text, len, h->cap_bytes, out, max_out, dev);
+    if (n < 0) g_last_error = h->engine->last_error();
+    return static_cast<int32_t>(n);
+}
+
+int32_t do_encode_batch(Handle* h, const uint8_t* concat_bytes, const uint32_t* doc_byte_offsets, uint32_t n_docs,
+                        uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets) {
+    for (uint32_t i = 0; i < n_docs; ++i)
+        if (doc_byte_offsets[i + 1] < doc_byte_offsets[i]) return -1;
+    const uint32_t first = doc_byte_offsets[0];
+    uint64_t total = static_cast<uint64_t>(doc_byte_offsets[n_docs]) - first;
+    const uint32_t* offs = doc_byte_offsets;
+    if (h->engine->vocab().nfc) {
+        // each document is normalised on its own; the blob is rebuilt only if one of them changes
+        bool any = false;
+        for (uint32_t i = 0; i < n_docs && !any; ++i)
+            any = gtok::nfc_normalize(concat_bytes + doc_byte_offsets[i], doc_byte_offsets[i + 1] - doc_byte_offsets[i], h->norm_doc);
+        if (any) {
+            h->norm.clear();
+            h->rebased.assign(static_cast<size_t>(n_docs) + 1, 0);
+            for (uint32_t i = 0; i < n_docs; ++i) {
+                const uint8_t* d = concat_bytes + doc_byte_offsets[i];
+                const uint32_t dl = doc_byte_offsets[i + 1] - doc_byte_offsets[i];
+                if (gtok::nfc_normalize(d, dl, h->norm_doc)) h->norm += h->norm_doc;
+                else h->norm.append(reinterpret_cast<const char*>(d), dl);
+                if (h->norm.size() > 0xFFFFFFFFull) return -3;
+                h->rebased[i + 1] = static_cast<uint32_t>(h->norm.size());
+            }
+            if (h->norm.size() > h->cap_bytes) return -3;
+            int64_t n = h->engine->encode_batch(reinterpret_cast<const uint8_t*>(h->norm.data()), h->rebased.data(), n_docs, h->cap_bytes,
+                                                out_tokens, out_cap, out_doc_offsets);
+            if (n < 0) g_last_error = h->engine->last_error();
+            return static_cast<int32_t>(n);
+        }
+    }
+    if (total > h->cap_bytes) return -3;
+    if (first != 0) {
+        h->rebased.resize(static_cast<size_t>(n_docs) + 1);
+        for (uint32_t i = 0; i <= n_docs; ++i) h->rebased[i] = doc_byte_offsets[i] - first;
+        offs = h->rebased.data();
+    }
+    int64_t n = h->engine->encode_batch(concat_bytes + first, offs, n_docs, h->cap_bytes, out_tokens, out_cap, out_doc_offsets);
     if (n < 0) g_last_error = h->engine->last_error();
     return static_cast<int32_t>(n);
 }
@@ -83,44 +144,7 @@ int32_t gtok_encode_batch(void* handle, const uint8_t* concat_bytes, const uint3
                           uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets) {
     if (!handle || !concat_bytes || !doc_byte_offsets || !out_tokens || !out_doc_offsets || n_docs == 0) return -1;
     try {
-        Handle* h = static_cast<Handle*>(handle);
-        for (uint32_t i = 0; i < n_docs; ++i)
-            if (doc_byte_offsets[i + 1] < doc_byte_offsets[i]) return -1;
-        const uint32_t first = doc_byte_offsets[0];
-        uint64_t total = static_cast<uint64_t>(doc_byte_offsets[n_docs]) - first;
-        const uint32_t* offs = doc_byte_offsets;
-        if (h->engine->vocab().nfc) {
-            // each document is normalised on its own; the blob is rebuilt only if one of them changes
-            bool any = false;
-            for (uint32_t i = 0; i < n_docs && !any; ++i)
-                any = gtok::nfc_normalize(concat_bytes + doc_byte_offsets[i], doc_byte_offsets[i + 1] - doc_byte_offsets[i], h->norm_doc);
-            if (any) {
-                h->norm.clear();
-                h->rebased.assign(static_cast<size_t>(n_docs) + 1, 0);
-                for (uint32_t i = 0; i < n_docs; ++i) {
-                    const uint8_t* d = concat_bytes + doc_byte_offsets[i];
-                    const uint32_t dl = doc_byte_offsets[i + 1] - doc_byte_offsets[i];
-                    if (gtok::nfc_normalize(d, dl, h->norm_doc)) h->norm += h->norm_doc;
-                    else h->norm.append(reinterpret_cast<const char*>(d), dl);
-                    if (h->norm.size() > 0xFFFFFFFFull) return -3;
-                    h->rebased[i + 1] = static_cast<uint32_t>(h->norm.size());
-                }
-                if (h->norm.size() > h->cap_bytes) return -3;
-                int64_t n = h->engine->encode_batch(reinterpret_cast<const uint8_t*>(h->norm.data()), h->rebased.data(), n_docs, h->cap_bytes,
-                                                    out_tokens, out_cap, out_doc_offsets);
-                if (n < 0) g_last_error = h->engine->last_error();
-                return static_cast<int32_t>(n);
-            }
-        }
-        if (total > h->cap_bytes) return -3;
-        if (first != 0) {
-            h->rebased.resize(static_cast<size_t>(n_docs) + 1);
-            for (uint32_t i = 0; i <= n_docs; ++i) h->rebased[i] = doc_byte_offsets[i] - first;
-            offs = h->rebased.data();
-        }
-        int64_t n = h->engine->encode_batch(concat_bytes + first, offs, n_docs, h->cap_bytes, out_tokens, out_cap, out_doc_offsets);
-        if (n < 0) g_last_error = h->engine->last_error();
-        return static_cast<int32_t>(n);
+        return do_encode_batch(static_cast<Handle*>(handle), concat_bytes, doc_byte_offsets, n_docs, out_tokens, out_cap, out_doc_offsets);
     } catch (...) { return -1; }
 }
 
@@ -144,15 +168,68 @@ int32_t gtok_dispatch_encode(void* dispatcher, const uint8_t* text, uint32_t len
     if (!dispatcher || (!text && len)) return -1;
     try {
         Dispatcher* d = static_cast<Dispatcher*>(dispatcher);
-        std::lock_guard<std::mutex> lock(d->mu);
-        if (len > d->handle.cap_bytes) d->handle.cap_bytes = len;    // large requests grow the context
-        const auto t0 = std::chrono::steady_clock::now();
-        int32_t n = do_encode(&d->handle, text, len, out, max_out, false);
+        Request me{text, len, out, max_out};
+        std::unique_lock<std::mutex> lock(d->mu);
         d->stats[1] += 1;
-        d->stats[2] += 1;
-        if (len > d->max_batch_bytes) d->stats[3] += 1;
-        d->stats[4] += static_cast<uint64_t>(std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count());
-        return n;
+        d->queue.push_back(&me);
+        for (;;) {
+            if (me.done) return me.result;
+            if (!d->leader_active) break;
+            d->cv.wait(lock);
+        }
+        // Leader: serve batches until this thread's own request has been answered.
+        d->leader_active = true;
+        while (!me.done) {
+            std::vector<Request*> batch;
+            uint64_t bytes = 0;
+            while (!d->queue.empty() && batch.size() < d->max_batch_docs) {
+                Request* r = d->queue.front();
+                if (!batch.empty() && bytes + r->len > d->max_batch_bytes) break;
+                batch.push_back(r);
+                bytes += r->len;
+                d->queue.pop_front();
+                if (r->len > d->max_batch_bytes) break;        // a large request runs alone
+            }
+            lock.unlock();
+            const auto t0 = std::chrono::steady_clock::now();
+            if (bytes > d->handle.cap_bytes) d->handle.cap_bytes = static_cast<uint32_t>(std::min<uint64_t>(bytes, 0xFFFFFFFFull));
+            if (batch.size() == 1) {
+                Request* r = batch[0];
+                r->result = do_encode(&d->handle, r->text, r->len, r->out, r->max_out, false);
+            } else {
+                d->blob.resize(bytes);
+                d->offs.assign(batch.size() + 1, 0);
+                uint32_t at = 0;
+                for (size_t i = 0; i < batch.size(); ++i) {
+                    if (batch[i]->len) std::memcpy(d->blob.data() + at, batch[i]->text, batch[i]->len);
+                    at += batch[i]->len;
+                    d->offs[i + 1] = at;
+                }
+                d->toks.resize(bytes * 2 + 64);                  // ids never outnumber (normalised) bytes
+                d->doc_tok.assign(batch.size() + 1, 0);
+                int32_t n = bytes ? do_encode_batch(&d->handle, d->blob.data(), d->offs.data(), static_cast<uint32_t>(batch.size()), d->toks.data(),
+                                                    static_cast<uint32_t>(d->toks.size()), d->doc_tok.data())
+                                  : 0;
+                for (size_t i = 0; i < batch.size(); ++i) {
+                    Request* r = batch[i];
+                    if (n < 0) { r->result = -1; continue; }
+                    uint32_t cnt = d->doc_tok[i + 1] - d->doc_tok[i];
+                    if (cnt > r->max_out) { r->result = -2; continue; }
+                    if (cnt) std::memcpy(r->out, d->toks.data() + d->doc_tok[i], static_cast<size_t>(cnt) * 4);
+                    r->result = static_cast<int32_t>(cnt);
+                }
+            }
+            const uint64_t ns = static_cast<uint64_t>(std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count());
+            lock.lock();
+            d->stats[2] += 1;
+            if (batch.size() == 1 && batch[0]->len > d->max_batch_bytes) d->stats[3] += 1;
+            d->stats[4] += ns;
+            for (Request* r : batch) r->done = true;
+            d->cv.notify_all();
+        }
+        d->leader_active = false;
+        d->cv.notify_all();            // a queued follower takes over as leader
+        return me.result;
     } catch (...) { return -1; }
 }
 
