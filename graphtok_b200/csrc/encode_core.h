@@ -1144,12 +1144,13 @@ struct WordsSmem {
     unsigned long long clk_last;
 };
 struct MissSmem {
-    uint32_t ws[3 * kArenaSyms];       // arena: ids, ranks, results (also the long pre-token workspace)
+    alignas(16) uint32_t ws[3 * kArenaSyms];   // arena: ids, ranks, results (also the long pre-token workspace)
     uint32_t b2i[256];
     uint32_t scan[kThreads];
     uint32_t red[kThreads + 8];
     uint32_t aoff[kThreads];
     unsigned long long word[kThreads]; // this batch's entries of the global list
+    alignas(16) uint16_t lnk[kArenaSyms];   // live-symbol chain of each pre-token (prev << 8 | next)
     uint8_t owner[kArenaSyms];         // which of the batch's pre-tokens an arena slot belongs to
     uint8_t rawb[kArenaSyms];          // the slot's text byte
     uint32_t ctr[8];
@@ -1170,35 +1171,43 @@ enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5
 // block's symbol arena with the pair ranks already probed; merged-away symbols are
 // marked dead in place, so a step is one pass over the slots plus one round trip for
 // the two new pairs.
-GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint32_t len, uint32_t* out) {
-    constexpr uint32_t kDead = 0xFFFFFFFFu;
+GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint16_t* lnk, uint32_t len, uint32_t* out) {
+    // The stretch starts on a 4-slot boundary and is padded to a multiple of 4 with rank-less
+    // slots, so the rank scan reads four slots per load.  lnk[i] = prev << 8 | next (slot numbers
+    // within the stretch, 0xFF = none) keeps the live symbols chained.
+    const uint32_t len4 = (len + 3u) & ~3u;
     for (;;) {
         uint32_t best = kNoRank, bi = 0;
-        for (uint32_t i = 0; i < len; ++i) {
-            uint32_t r = rk[i];
-            if (r < best) { best = r; bi = i; }
+        for (uint32_t i = 0; i < len4; i += 4) {
+#if defined(__CUDA_ARCH__)
+            const uint4 v = *reinterpret_cast<const uint4*>(rk + i);
+            const uint32_t r0 = v.x, r1 = v.y, r2 = v.z, r3 = v.w;
+#else
+            const uint32_t r0 = rk[i], r1 = rk[i + 1], r2 = rk[i + 2], r3 = rk[i + 3];
+#endif
+            const uint32_t m01 = r1 < r0 ? r1 : r0, m23 = r3 < r2 ? r3 : r2;
+            const uint32_t m = m23 < m01 ? m23 : m01;
+            if (m < best) {
+                best = m;
+                bi = i + (r0 == m ? 0u : r1 == m ? 1u : r2 == m ? 2u : 3u);
+            }
         }
         if (best == kNoRank) break;
-        uint32_t j = bi + 1;
-        while (ids[j] == kDead) ++j;
-        uint32_t k = j + 1;
-        while (k < len && ids[k] == kDead) ++k;
-        int p = static_cast<int>(bi) - 1;
-        while (p >= 0 && ids[p] == kDead) --p;
+        const uint32_t l = lnk[bi];
+        const uint32_t j = l & 0xFFu, p = l >> 8;
+        const uint32_t k = lnk[j] & 0xFFu;
         const uint32_t merged = nw[bi];
         ids[bi] = merged;
-        ids[j] = kDead;
         rk[j] = kNoRank;
+        lnk[bi] = static_cast<uint16_t>((p << 8) | k);
+        if (k != 0xFFu) lnk[k] = static_cast<uint16_t>((bi << 8) | (lnk[k] & 0xFFu));
         RankRes right, left;
-        probe_rule2(a.tb, k < len, merged, k < len ? ids[k] : 0u, &right, p >= 0, p >= 0 ? ids[p] : 0u, merged, &left);
+        probe_rule2(a.tb, k != 0xFFu, merged, k != 0xFFu ? ids[k] : 0u, &right, p != 0xFFu, p != 0xFFu ? ids[p] : 0u, merged, &left);
         rk[bi] = right.rank; nw[bi] = right.res;
-        if (p >= 0) { rk[p] = left.rank; nw[p] = left.res; }
+        if (p != 0xFFu) { rk[p] = left.rank; nw[p] = left.res; }
     }
     uint32_t c = 0;
-    for (uint32_t i = 0; i < len; ++i) {
-        uint32_t v = ids[i];
-        if (v != kDead) out[c++] = v;
-    }
+    for (uint32_t i = 0; i != 0xFFu; i = lnk[i] & 0xFFu) out[c++] = ids[i];
     return c;
 }
 
@@ -1604,13 +1613,13 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     while (done < n_here) {
         blk.par([&](int tid) {
             uint32_t idx = done + tid;
-            sm.scan[tid] = idx < n_here ? static_cast<uint32_t>(sm.word[idx] >> 32) : 0u;
+            sm.scan[tid] = idx < n_here ? ((static_cast<uint32_t>(sm.word[idx] >> 32) + 3u) & ~3u) : 0u;   // stretches of whole 4-slot groups
         });
         uint32_t tot = 0;
         blk.excl_scan(sm.scan, &tot);
         blk.par([&](int tid) {
             uint32_t idx = done + tid;
-            uint32_t len = idx < n_here ? static_cast<uint32_t>(sm.word[idx] >> 32) : 0u;
+            uint32_t len = idx < n_here ? ((static_cast<uint32_t>(sm.word[idx] >> 32) + 3u) & ~3u) : 0u;
             bool fits = idx < n_here && sm.scan[tid] + len <= static_cast<uint32_t>(kArenaSyms);
             sm.red[tid] = fits ? 0xFFFFFFFFu : static_cast<uint32_t>(tid);
         });
@@ -1620,7 +1629,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
         // owner: which slots are mine (shared memory only)
         blk.par([&](int tid) {
             if (static_cast<uint32_t>(tid) >= nb) return;
-            const uint32_t len = static_cast<uint32_t>(sm.word[done + tid] >> 32), at = sm.scan[tid];
+            const uint32_t len = (static_cast<uint32_t>(sm.word[done + tid] >> 32) + 3u) & ~3u, at = sm.scan[tid];
             if (static_cast<uint32_t>(tid) + 1 == nb) sm.ctr[C_USED] = at + len;
             for (uint32_t i = 0; i < len; ++i) sm.owner[at + i] = static_cast<uint8_t>(tid);
             sm.aoff[tid] = at;
@@ -1633,10 +1642,13 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
                     const uint32_t w = sm.owner[sidx];
                     const unsigned long long wv = sm.word[done + w];
                     const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32), at = sm.scan[w];
-                    const uint32_t bt = ldg(a.text + g + (sidx - at));
+                    const uint32_t r = sidx - at;
+                    if (r >= len) { rk[sidx] = kNoRank; ids[sidx] = 0; sm.rawb[sidx] = 0; sm.lnk[sidx] = 0xFFFFu; continue; }   // padding
+                    const uint32_t bt = ldg(a.text + g + r);
                     sm.rawb[sidx] = static_cast<uint8_t>(bt);
                     ids[sidx] = sm.b2i[bt];
-                    rk[sidx] = (sidx + 1 < at + len) ? kPending : kNoRank;
+                    rk[sidx] = (r + 1 < len) ? kPending : kNoRank;
+                    sm.lnk[sidx] = static_cast<uint16_t>(((r ? r - 1 : 0xFFu) << 8) | (r + 1 < len ? r + 1 : 0xFFu));
                 }
             });
         }
@@ -1673,7 +1685,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             const unsigned long long wv = sm.word[done + tid];
             const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
             // merge in place, then the ids (the arena stretch is free again) go to their slots
-            uint32_t cnt = bpe_arena(a, ids + at, rk + at, nw + at, len, nw + at);
+            uint32_t cnt = bpe_arena(a, ids + at, rk + at, nw + at, sm.lnk + at, len, nw + at);
             for (uint32_t k = 0; k < cnt; ++k) put_id(a, g, k, nw[at + k]);
         });
         mark(20);
