@@ -66,12 +66,13 @@ struct DeviceTables {
 #define GTOK_HD inline
 #endif
 
+// 32-bit arithmetic only: this sits on the critical path of every merge step.
 GTOK_HD uint32_t merge_hash(uint32_t l, uint32_t r) {
-    uint64_t x = (static_cast<uint64_t>(l) << 32) | r;
-    x ^= x >> 31; x *= 0x7fb5d329728ea185ULL;
-    x ^= x >> 27; x *= 0x81dadef4bc2dd44dULL;
-    x ^= x >> 33;
-    return static_cast<uint32_t>(x);
+    uint32_t x = l * 0x9E3779B1u ^ (r + 0x7F4A7C15u) * 0x85EBCA77u;
+    x ^= x >> 15; x *= 0x2C1B3C6Du;
+    x ^= x >> 13; x *= 0x297A2D39u;
+    x ^= x >> 16;
+    return x;
 }
 GTOK_HD uint32_t word_hash(uint64_t k0, uint64_t k1) {
     uint64_t x = k0 * 0x9E3779B185EBCA87ULL + (k1 ^ (k1 >> 29)) * 0xC2B2AE3D27D4EB4FULL;

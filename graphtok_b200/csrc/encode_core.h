@@ -837,7 +837,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     sm.oh[i] = kOhAdded;
                     for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kWin; ++j) {
                         sm.attr[i + j] = static_cast<uint8_t>(A_CONT | (sm.attr[i + j] & A_DOC));
-                        sm.oh[i + j] = kOhC;
+                        sm.oh[i + j] = kOhC | kOhAdded;          // both bits: inside a literal
                     }
                 }
             }
@@ -884,7 +884,8 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             return (static_cast<uint64_t>(pw[ww - 1]) >> 16) | (static_cast<uint64_t>(pw[ww]) << 16) | (static_cast<uint64_t>(pw[ww + 1]) << 48);
         };
         const uint64_t OWN = 0x0000FFFFFFFF0000ull;
-        const uint64_t L = load(PL_L), N = load(PL_N), S = load(PL_S), O = load(PL_O), C = load(PL_C), AD = load(PL_AD);
+        const uint64_t L = load(PL_L), N = load(PL_N), S = load(PL_S), O = load(PL_O), C = load(PL_C), ADraw = load(PL_AD);
+        const uint64_t AD = ADraw & ~C;      // first byte of an added-token literal; ADraw & C marks its other bytes
         const uint64_t CR = load(PL_CRLF), SP = load(PL_SP), AP = load(PL_AP);
         const uint64_t DOC = (static_cast<uint64_t>(sm.dsw[ww - 1]) >> 16) | (static_cast<uint64_t>(sm.dsw[ww]) << 16) | (static_cast<uint64_t>(sm.dsw[ww + 1]) << 48);
         const uint64_t LEAD = L | N | S | O | AD;
@@ -908,9 +909,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         // (a continuation byte right after an apostrophe stretches a contraction past three bytes)
         // An added-token literal is its start bit plus continuation bits; those long stretches are
         // harmless to the algebra (the literal has no class, so its neighbours see "nothing").
-        const uint64_t lit1 = (AD << 1) & C;
-        const uint64_t lit = ((C + lit1) ^ C) & C;
-        const uint64_t Cg = C & ~lit;
+        const uint64_t Cg = C & ~ADraw;
         const bool messy = (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 ||
                            (((AP << 1) | (AP << 2) | (AP << 3)) & C) != 0;
         if (messy) unc = LEAD;
