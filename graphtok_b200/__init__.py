@@ -125,6 +125,10 @@ class GTok:
         data = bytes(data)
         out = np.empty(len(data) + 16, dtype=np.uint32)
         n = self.lib.gtok_encode(self.handle, data, len(data), out.ctypes.data, out.size)
+        if n == -2:
+            # more ids than bytes: only text that its vocabulary's NFC lengthens (at most threefold)
+            out = np.empty(3 * len(data) + 64, dtype=np.uint32)
+            n = self.lib.gtok_encode(self.handle, data, len(data), out.ctypes.data, out.size)
         if n < 0:
             self._fail("gtok_encode", n)
         return out[:n].copy()
@@ -178,8 +182,9 @@ class GTok:
         return np.nonzero(bits)[0].astype(np.uint32)
 
     def profile(self):
-        """Staged input, kernel by kernel: (tokens, pretok ms, words ms, miss ms, assemble ms, sequence ms)."""
-        ms = (ctypes.c_float * 5)()
+        """Staged input, kernel by kernel: (tokens, pretok ms, words ms, miss ms, assemble ms, sequence ms,
+        ms of what runs before pretok: normalisation and document-bit kernels)."""
+        ms = (ctypes.c_float * 6)()
         n = self.lib.gtok_x_profile(self.handle, ms)
         if n < 0:
             self._fail("gtok_x_profile", n)

@@ -57,6 +57,13 @@ struct DeviceTables {
     uint32_t ignore_merges;
     uint32_t monotone;
     uint32_t added_ws;                   // some added-token literal contains a space, CR or LF
+    // Normalisation data (nfc_tables.h), uploaded only for vocabularies that declare NFC.
+    const uint32_t* nfc_attn_bits;       // one bit per BMP codepoint that can make a text non-NFC
+    const uint32_t* nfc_attn_sup;        // (lo, hi) ranges of such codepoints above the BMP
+    const uint32_t* nfc_ccc;             // (codepoint, combining class) pairs, ascending
+    const uint32_t* nfc_decomp;          // (codepoint, n, d0..d3) full canonical decompositions, ascending
+    const uint32_t* nfc_comp;            // (first, second, composite) primary composites, ascending
+    uint32_t nfc_attn_sup_n, nfc_ccc_n, nfc_decomp_n, nfc_comp_n;
 };
 
 // ---- hashes (host and device) ------------------------------------------------

@@ -59,6 +59,8 @@ enum : uint32_t {
     kErrWaitExpired = 2u,     // a look-back wait gave up
     kErrProbeLimit = 4u,      // a table probe ran past its limit (corrupt table)
     kErrInternal = 8u,
+    kErrNfcLong = 16u,        // a stretch to normalise holds more codepoints than one thread takes
+    kErrNfcFull = 32u,        // the normalised text does not fit the text buffer
 };
 
 // Per-byte attribute (shared memory, pretok only).
@@ -94,6 +96,16 @@ struct EncodeArgs {
     uint32_t* out_doc_tok;        // [n_docs + 1] token offsets (batch) or nullptr
     uint32_t* status;             // [0] total tokens, [1] error bits (host-visible)
     unsigned long long* phase_clk; // optional: cycles spent per phase, summed over blocks (diagnostics)
+    // Normalisation (vocabularies that declare NFC); raw == nullptr otherwise.
+    const uint8_t* raw;           // text as the caller gave it, padded like `text`
+    const uint32_t* raw_meta;     // [0] = bytes, [1] = documents, [2] = 1 when the text is normalised already
+    const uint32_t* raw_doc_off;  // [n_docs + 1] offsets into raw (batch) or nullptr
+    const uint32_t* raw_docmask;  // document-start bits over raw (batch) or nullptr
+    uint8_t* norm_text;           // = text, writable
+    uint32_t* norm_meta;          // = meta, writable
+    uint32_t* norm_doc_off;       // = doc_off, writable
+    unsigned long long* st0;      // normalisation look-back state per tile
+    uint32_t text_cap;            // bytes the text buffer holds
     DeviceTables tb;
 };
 
@@ -1124,7 +1136,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch of the miss kernel
 constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB); owners fit a byte
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
-enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8 };
+enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9 };
 constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
 constexpr int kMedBatch = 64;                  // so that the long merge chains of the latter start first and spread over more blocks
 

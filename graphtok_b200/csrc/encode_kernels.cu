@@ -14,6 +14,7 @@
 
 #include "encode_core.h"
 #include "encode_kernels.h"
+#include "nfc_core.h"
 
 namespace gtok {
 
@@ -111,6 +112,25 @@ __global__ void __launch_bounds__(kThreads) pretok_kernel(const EncodeArgs a) {
         __syncthreads();
         if (tile >= n_tiles) break;
         pretok_tile(blk, a, sm, tile);
+    }
+}
+
+// Kernel 0 (vocabularies that declare NFC): raw text -> normalised text, byte count and
+// document offsets; tiles in ticket order because a tile's place in the output is the sum of
+// the lengths of all earlier tiles.
+__global__ void __launch_bounds__(kThreads) nfc_kernel(const EncodeArgs a) {
+    __shared__ NfcSmem sm;
+    __shared__ int s_tile;
+    GpuBlk blk;
+    const uint32_t n = a.raw_meta[0];
+    const int n_tiles = static_cast<int>((n + kTile - 1) / kTile);
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = static_cast<int>(atomicAdd(a.ctl + CTL_NFC, 1u));
+        __syncthreads();
+        const int tile = s_tile;
+        __syncthreads();
+        if (tile >= n_tiles) break;
+        nfc_tile(blk, a, sm, tile);
     }
 }
 
@@ -285,11 +305,16 @@ static int blocks_per_sm(const void* fn, size_t smem) {
 int pretok_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(pretok_kernel), 0); }
 int words_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(words_kernel), sizeof(WordsSmem)); }
 int miss_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(miss_kernel), sizeof(MissSmem)); }
+int nfc_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(nfc_kernel), 0); }
 int assemble_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(assemble_kernel), 0); }
 
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s) {
     docmask_kernel<<<blocks, 256, 0, s>>>(a.meta, a.doc_off, docmask);
 }
+void launch_raw_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s) {
+    docmask_kernel<<<blocks, 256, 0, s>>>(a.raw_meta, a.raw_doc_off, docmask);
+}
+void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s) { words_kernel<<<blocks, kThreads, sizeof(WordsSmem), s>>>(a); }
 void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s) { miss_kernel<<<blocks, kThreads, sizeof(MissSmem), s>>>(a); }

@@ -14,7 +14,10 @@ int pretok_blocks_per_sm();
 int words_blocks_per_sm();
 int miss_blocks_per_sm();
 int assemble_blocks_per_sm();
+int nfc_blocks_per_sm();
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);
+void launch_raw_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);   // over raw_doc_off
+void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s);

@@ -10,6 +10,7 @@
 
 #include "encode_core.h"
 #include "encode_kernels.h"
+#include "nfc_host.h"
 #include "tables_build.h"
 #include "unicode_class_table.h"
 
@@ -48,6 +49,9 @@ struct Ctx {
     uint8_t* d_text = nullptr;
     uint32_t* d_hdr = nullptr;
     uint32_t* d_docmask = nullptr;
+    uint8_t* d_raw = nullptr;             // vocabularies that declare NFC: text as given, its header and document bits
+    uint32_t* d_rawhdr = nullptr;
+    uint32_t* d_docmask_raw = nullptr;
     uint32_t *d_bmask = nullptr, *d_amask = nullptr, *d_tile_nb = nullptr;
     unsigned char* d_ctrl = nullptr;
     size_t ctrl_bytes = 0;
@@ -65,7 +69,8 @@ struct Ctx {
     cudaStream_t stream = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
-    cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t ev[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int nfc_blocks = 1;
     int pretok_blocks = 1, words_blocks = 1, miss_blocks = 1, asm_blocks = 1, docmask_blocks = 1;
     size_t mask_words = 0;
     EncodeArgs args;
@@ -76,6 +81,7 @@ struct Ctx {
         if (graph) cudaGraphDestroy(graph);
         for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
+        cudaFree(d_raw); cudaFree(d_rawhdr); cudaFree(d_docmask_raw);
         cudaFree(d_text); cudaFree(d_hdr); cudaFree(d_docmask); cudaFree(d_bmask); cudaFree(d_amask);
         cudaFree(d_tile_nb); cudaFree(d_ctrl); cudaFree(d_gstage); cudaFree(d_grk); cudaFree(d_gnw);
         cudaFree(d_out); cudaFree(d_doc_tok); cudaFree(d_phase);
@@ -97,7 +103,12 @@ struct Engine::Impl {
     std::vector<void*> owned;
     std::unique_ptr<Ctx> single, batch;
     Ctx* staged = nullptr;
-    int pretok_per_sm = 1, words_per_sm = 1, miss_per_sm = 1, asm_per_sm = 1;
+    int pretok_per_sm = 1, words_per_sm = 1, miss_per_sm = 1, asm_per_sm = 1, nfc_per_sm = 1;
+    bool nfc = false;                    // the vocabulary declares NFC: the graph starts with the normalisation kernel
+    uint32_t last_err_bits = 0;
+    std::string norm;                    // host normalisation, used only after kErrNfcLong
+    std::string norm_doc;
+    std::vector<uint32_t> norm_off;
 
     ~Impl() {
         single.reset();
@@ -115,6 +126,18 @@ struct Engine::Impl {
             !upload(ht.trie_first, &dt.trie_first, owned, err) || !upload(ht.trie_count, &dt.trie_count, owned, err) ||
             !upload(ht.trie_terminal, &dt.trie_terminal, owned, err) || !upload(ht.trie_edges, &dt.trie_edges, owned, err))
             return false;
+        if (nfc) {
+            NfcWords w;
+            nfc_table_words(w);
+            if (!upload(w.attn_bits, &dt.nfc_attn_bits, owned, err) || !upload(w.attn_sup, &dt.nfc_attn_sup, owned, err) ||
+                !upload(w.ccc, &dt.nfc_ccc, owned, err) || !upload(w.decomp, &dt.nfc_decomp, owned, err) ||
+                !upload(w.comp, &dt.nfc_comp, owned, err))
+                return false;
+            dt.nfc_attn_sup_n = static_cast<uint32_t>(w.attn_sup.size() / 2);
+            dt.nfc_ccc_n = static_cast<uint32_t>(w.ccc.size() / 2);
+            dt.nfc_decomp_n = static_cast<uint32_t>(w.decomp.size() / 6);
+            dt.nfc_comp_n = static_cast<uint32_t>(w.comp.size() / 3);
+        }
         dt.merge_mask = static_cast<uint32_t>(ht.merge.size() / 2 - 1);
         dt.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
         dt.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
@@ -146,7 +169,14 @@ struct Engine::Impl {
         GTOK_CUDA(cudaMalloc(&c->d_amask, mask_words * 4));
         GTOK_CUDA(cudaMalloc(&c->d_tile_nb, (c->n_tiles_cap + 1) * 4));
         if (batch_mode) GTOK_CUDA(cudaMalloc(&c->d_docmask, mask_words * 4));
-        c->ctrl_bytes = 64 + static_cast<size_t>(c->n_tiles_cap + 1) * 16;
+        if (nfc) {
+            GTOK_CUDA(cudaMalloc(&c->d_raw, tile_bytes + kTextPad));
+            GTOK_CUDA(cudaMemset(c->d_raw, 0, tile_bytes + kTextPad));
+            GTOK_CUDA(cudaMalloc(&c->d_rawhdr, hdr_words * 4));
+            GTOK_CUDA(cudaMemset(c->d_rawhdr, 0, hdr_words * 4));
+            if (batch_mode) GTOK_CUDA(cudaMalloc(&c->d_docmask_raw, mask_words * 4));
+        }
+        c->ctrl_bytes = 64 + static_cast<size_t>(c->n_tiles_cap + 1) * 24;
         GTOK_CUDA(cudaMalloc(&c->d_ctrl, c->ctrl_bytes));
         GTOK_CUDA(cudaMemset(c->d_ctrl, 0, c->ctrl_bytes));
         GTOK_CUDA(cudaMalloc(&c->d_gstage, (tile_bytes + 64) * 4));
@@ -177,6 +207,17 @@ struct Engine::Impl {
         a.ctl = reinterpret_cast<uint32_t*>(c->d_ctrl);
         a.st1 = reinterpret_cast<unsigned long long*>(c->d_ctrl + 64);
         a.st2 = a.st1 + (c->n_tiles_cap + 1);
+        a.st0 = a.st2 + (c->n_tiles_cap + 1);
+        a.text_cap = cap_bytes;
+        if (nfc) {
+            a.raw = c->d_raw;
+            a.raw_meta = c->d_rawhdr;
+            a.raw_doc_off = batch_mode ? c->d_rawhdr + kHdrWords : nullptr;
+            a.raw_docmask = batch_mode ? c->d_docmask_raw : nullptr;
+            a.norm_text = c->d_text;
+            a.norm_meta = c->d_hdr;
+            a.norm_doc_off = batch_mode ? c->d_hdr + kHdrWords : nullptr;
+        }
         a.gstage = c->d_gstage;
         a.gwork_rk = c->d_grk;
         a.gwork_nw = c->d_gnw;
@@ -207,14 +248,12 @@ struct Engine::Impl {
         c->words_blocks = words_blocks;
         c->miss_blocks = miss_blocks;
         c->asm_blocks = asm_blocks;
+        c->nfc_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * nfc_per_sm));
         c->docmask_blocks = std::max(1, std::min<int>(sm_count, static_cast<int>((cap_docs + 256) / 256)));
         c->mask_words = mask_words;
         GTOK_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
         cudaMemsetAsync(c->d_ctrl, 0, c->ctrl_bytes, c->stream);
-        if (batch_mode) {
-            cudaMemsetAsync(c->d_docmask, 0, mask_words * 4, c->stream);
-            launch_docmask(a, c->d_docmask, c->docmask_blocks, c->stream);
-        }
+        launch_front(c.get());
         launch_pretok(a, pretok_blocks, c->stream);
         launch_words(a, words_blocks, c->stream);
         launch_miss(a, miss_blocks, c->stream);
@@ -224,6 +263,21 @@ struct Engine::Impl {
         GTOK_CUDA(cudaGetLastError());
         slot = std::move(c);
         return true;
+    }
+
+    // What precedes pre-tokenization: [raw document bits, normalisation], [document bits].
+    void launch_front(Ctx* c) {
+        if (nfc) {
+            if (c->batch) {
+                cudaMemsetAsync(c->d_docmask_raw, 0, c->mask_words * 4, c->stream);
+                launch_raw_docmask(c->args, c->d_docmask_raw, c->docmask_blocks, c->stream);
+            }
+            launch_nfc(c->args, c->nfc_blocks, c->stream);
+        }
+        if (c->batch) {
+            cudaMemsetAsync(c->d_docmask, 0, c->mask_words * 4, c->stream);
+            launch_docmask(c->args, c->d_docmask, c->docmask_blocks, c->stream);
+        }
     }
 
     // Context able to take `need_bytes` (and `need_docs`); built or rebuilt on demand.
@@ -259,27 +313,76 @@ struct Engine::Impl {
     }
 
     // Host -> pinned -> device, for the text and the header.
-    bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err) {
+    // With NFC the destination is the raw buffer; `normalised` tells the kernel to copy only.
+    bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err,
+                     bool normalised = false) {
         if (len) std::memcpy(c->h_text, bytes, len);
         c->h_hdr[0] = len;
         c->h_hdr[1] = n_docs;
-        c->h_hdr[2] = c->h_hdr[3] = 0;
+        c->h_hdr[2] = normalised ? 1u : 0u;
+        c->h_hdr[3] = 0;
         size_t hdr_words = kHdrWords;
         if (doc_off) {
             std::memcpy(c->h_hdr + kHdrWords, doc_off, (static_cast<size_t>(n_docs) + 1) * 4);
             hdr_words += static_cast<size_t>(n_docs) + 1;
         }
-        if (len) GTOK_CUDA(cudaMemcpyAsync(c->d_text, c->h_text, (static_cast<size_t>(len) + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream));
-        GTOK_CUDA(cudaMemcpyAsync(c->d_hdr, c->h_hdr, hdr_words * 4, cudaMemcpyHostToDevice, c->stream));
+        if (len) GTOK_CUDA(cudaMemcpyAsync(nfc ? c->d_raw : c->d_text, c->h_text, (static_cast<size_t>(len) + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream));
+        GTOK_CUDA(cudaMemcpyAsync(nfc ? c->d_rawhdr : c->d_hdr, c->h_hdr, hdr_words * 4, cudaMemcpyHostToDevice, c->stream));
         c->staged_len = len;
         c->staged_docs = n_docs;
         return true;
+    }
+
+    static constexpr int64_t kNoCtx = INT64_MIN;
+
+    // Stages the input and replays the graph.  With NFC two things can make the first replay
+    // give up, and each is retried once: a stretch longer than a thread normalises (the text is
+    // then normalised on the host and the kernel only copies it), and normalised text longer
+    // than the text buffer (the context is rebuilt larger; NFC grows a text at most threefold).
+    int64_t run(Ctx*& c, bool batch_mode, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs,
+                uint32_t cap_hint, std::string& err) {
+        c = ctx_for(batch_mode, len, n_docs, cap_hint, err);
+        if (!c) return kNoCtx;
+        if (!stage_input(c, bytes, len, doc_off, n_docs, err)) return -1;
+        int64_t total = replay(c, false, nullptr, err);
+        if (total >= 0 || !nfc || !(last_err_bits & (kErrNfcLong | kErrNfcFull))) return total;
+        if (last_err_bits & kErrNfcLong) {
+            norm.clear();
+            if (!batch_mode) {
+                if (!nfc_normalize(bytes, len, norm)) norm.assign(reinterpret_cast<const char*>(bytes), len);
+            } else {
+                norm_off.assign(static_cast<size_t>(n_docs) + 1, 0);
+                for (uint32_t i = 0; i < n_docs; ++i) {
+                    const uint8_t* d = bytes + doc_off[i];
+                    const uint32_t dl = doc_off[i + 1] - doc_off[i];
+                    if (nfc_normalize(d, dl, norm_doc)) norm += norm_doc;
+                    else norm.append(reinterpret_cast<const char*>(d), dl);
+                    if (norm.size() > 0xFFFFFF00ull) { err = "normalised text exceeds 4 GiB"; return -3; }
+                    norm_off[i + 1] = static_cast<uint32_t>(norm.size());
+                }
+            }
+            if (norm.size() > 0xFFFFFF00ull) { err = "normalised text exceeds 4 GiB"; return -3; }
+            if (norm.empty()) { c->h_status[0] = 0; c->h_status[2] = 0; return 0; }
+            const uint32_t nl = static_cast<uint32_t>(norm.size());
+            c = ctx_for(batch_mode, nl, n_docs, cap_hint, err);
+            if (!c) return kNoCtx;
+            if (!stage_input(c, reinterpret_cast<const uint8_t*>(norm.data()), nl, batch_mode ? norm_off.data() : nullptr, n_docs, err, true)) return -1;
+            return replay(c, false, nullptr, err);
+        }
+        const uint64_t want = static_cast<uint64_t>(len) * 3 + 64;
+        if (want > 0xFFFFFF00ull) { err = "normalised text may exceed 4 GiB"; return -3; }
+        c = ctx_for(batch_mode, static_cast<uint32_t>(want), n_docs, cap_hint, err);
+        if (!c) return kNoCtx;
+        if (!stage_input(c, bytes, len, doc_off, n_docs, err)) return -1;
+        return replay(c, false, nullptr, err);
     }
 
     // One replay; returns the total token count or -1.
     int64_t replay(Ctx* c, bool timed, float* ms, std::string& err) {
         c->h_status[0] = 0;
         c->h_status[1] = 0;
+        c->h_status[2] = c->staged_len;
+        last_err_bits = 0;
         if (c->staged_len == 0) { if (ms) *ms = 0.f; return 0; }
         auto fail = [&](cudaError_t e, const char* what) { err = std::string(what) + ": " + cudaGetErrorString(e); return int64_t(-1); };
         cudaError_t e;
@@ -290,6 +393,7 @@ struct Engine::Impl {
         if (timed && ms) cudaEventElapsedTime(ms, c->ev[0], c->ev[1]);
         uint32_t errs = reinterpret_cast<volatile uint32_t*>(c->h_status)[1];
         if (errs) {
+            last_err_bits = errs;
             char buf[96];
             std::snprintf(buf, sizeof buf, "encode kernels reported error bits 0x%x", errs);
             err = buf;
@@ -331,6 +435,8 @@ Engine* Engine::create(const std::string& path, std::string& err) {
     im.words_per_sm = words_blocks_per_sm();
     im.miss_per_sm = miss_blocks_per_sm();
     im.asm_per_sm = assemble_blocks_per_sm();
+    im.nfc_per_sm = nfc_blocks_per_sm();
+    im.nfc = e->hv_.nfc;
     if (!im.upload_tables(err)) return nullptr;
     return e.release();
 }
@@ -346,11 +452,11 @@ int64_t Engine::encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, ui
     Impl& im = *impl_;
     cudaSetDevice(im.device);
     if (len == 0) return 0;
-    Ctx* c = im.ctx_for(false, len, 1, cap_bytes, last_error_);
-    if (!c) return -1;
-    if (!im.stage_input(c, text, len, nullptr, 1, last_error_)) return -1;
-    int64_t total = im.replay(c, false, nullptr, last_error_);
+    Ctx* c = nullptr;
+    int64_t total = im.run(c, false, text, len, nullptr, 1, cap_bytes, last_error_);
+    if (total == Impl::kNoCtx) return -1;
     if (total < 0) return total;
+    if (im.nfc && c->h_status[2] > cap_bytes) return -3;
     if (static_cast<uint64_t>(total) > max_out) return -2;
     if (total == 0) return 0;
     cudaError_t e;
@@ -373,11 +479,11 @@ int64_t Engine::encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint
     cudaSetDevice(im.device);
     const uint32_t len = doc_off[n_docs];
     if (len == 0) { for (uint32_t d = 0; d <= n_docs; ++d) out_doc_tok[d] = 0; return 0; }
-    Ctx* c = im.ctx_for(true, len, n_docs, cap_bytes, last_error_);
-    if (!c) return -4;
-    if (!im.stage_input(c, bytes, len, doc_off, n_docs, last_error_)) return -1;
-    int64_t total = im.replay(c, false, nullptr, last_error_);
+    Ctx* c = nullptr;
+    int64_t total = im.run(c, true, bytes, len, doc_off, n_docs, cap_bytes, last_error_);
+    if (total == Impl::kNoCtx) return -4;
     if (total < 0) return total;
+    if (im.nfc && c->h_status[2] > cap_bytes) return -3;
     if (static_cast<uint64_t>(total) > out_cap) return -2;
     if (!im.grow_host_out(c, static_cast<size_t>(total) + n_docs + 2, last_error_)) return -1;
     cudaError_t e = cudaSuccess;
@@ -417,14 +523,12 @@ int64_t Engine::profile_staged(float* ms_out) {
     if (!c) { last_error_ = "nothing staged"; return -1; }
     c->h_status[0] = 0;
     c->h_status[1] = 0;
-    for (int i = 0; i < 5; ++i) ms_out[i] = 0.f;
+    for (int i = 0; i < 6; ++i) ms_out[i] = 0.f;
     if (c->staged_len == 0) return 0;
     cudaEventRecord(c->ev[0], c->stream);
     cudaMemsetAsync(c->d_ctrl, 0, c->ctrl_bytes, c->stream);
-    if (c->batch) {
-        cudaMemsetAsync(c->d_docmask, 0, c->mask_words * 4, c->stream);
-        launch_docmask(c->args, c->d_docmask, c->docmask_blocks, c->stream);
-    }
+    cudaEventRecord(c->ev[6], c->stream);
+    im.launch_front(c);
     cudaEventRecord(c->ev[1], c->stream);
     launch_pretok(c->args, c->pretok_blocks, c->stream);
     cudaEventRecord(c->ev[2], c->stream);
@@ -438,6 +542,7 @@ int64_t Engine::profile_staged(float* ms_out) {
     if (e != cudaSuccess) { last_error_ = std::string("profile: ") + cudaGetErrorString(e); return -1; }
     for (int i = 0; i < 4; ++i) cudaEventElapsedTime(&ms_out[i], c->ev[i + 1], c->ev[i + 2]);
     cudaEventElapsedTime(&ms_out[4], c->ev[0], c->ev[5]);
+    cudaEventElapsedTime(&ms_out[5], c->ev[6], c->ev[1]);
     if (reinterpret_cast<volatile uint32_t*>(c->h_status)[1]) { last_error_ = "encode kernels reported an error"; return -1; }
     return reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
 }
@@ -447,7 +552,8 @@ int64_t Engine::read_boundaries(uint32_t* out_words, uint32_t max_words) {
     cudaSetDevice(im.device);
     Ctx* c = im.staged;
     if (!c) { last_error_ = "nothing staged"; return -1; }
-    uint32_t words = (c->staged_len + 31) / 32;
+    const uint32_t text_bytes = im.nfc ? reinterpret_cast<volatile uint32_t*>(c->h_status)[2] : c->staged_len;
+    uint32_t words = (text_bytes + 31) / 32;
     if (words > max_words) return -2;
     if (words && cudaMemcpy(out_words, c->d_bmask, static_cast<size_t>(words) * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return words;

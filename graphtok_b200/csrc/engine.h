@@ -1,7 +1,7 @@
 // Host-side engine behind the libgtok C ABI: owns the vocabulary tables in device
 // memory and, per capacity, a context with its workspaces, pinned staging
-// buffers and the captured CUDA graph (memset -> [document mask] -> pretok ->
-// merge).  Plays the role of the reference's TokenizerCtx
+// buffers and the captured CUDA graph (memset -> [normalisation] -> [document mask] ->
+// pretok -> words -> miss -> assemble).  Plays the role of the reference's TokenizerCtx
 // (src/tokenizer.cuh:132-548, launch_graph_core at src/tokenizer.cu:4654-4773),
 // with work proportional to the input length rather than to the capacity.
 #pragma once
@@ -20,7 +20,9 @@ public:
     static Engine* create(const std::string& tokenizer_json, std::string& err);
     ~Engine();
 
-    // Return codes follow the C ABI: >= 0 token count, -1 error, -2 output too small.
+    // Return codes follow the C ABI: >= 0 token count, -1 error, -2 output too small, -3 text
+    // longer than cap_bytes (for a vocabulary that declares NFC: the normalised text, which the
+    // graph produces itself from the raw bytes given here).
     // `text` is host memory.  When `out_on_device` the ids are copied device-to-device.
     int64_t encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, uint32_t* out, uint32_t max_out, bool out_on_device);
     // Documents are concatenated in `bytes`; `doc_off` has n_docs + 1 ascending offsets.
@@ -33,7 +35,8 @@ public:
     int64_t replay_staged(float* ms_out);                 // one replay; CUDA-event time of the graph
     int64_t read_staged(uint32_t* out, uint32_t max_out, uint32_t* out_doc_tok);
     // Same work as one replay, launched kernel by kernel with an event between them:
-    // ms_out[0..3] = pretok, words, miss, assemble kernels, ms_out[4] = whole sequence.
+    // ms_out[0..3] = pretok, words, miss, assemble kernels, ms_out[4] = whole sequence,
+    // ms_out[5] = what runs before pretok (normalisation kernel, document-bit kernels).
     int64_t profile_staged(float* ms_out);
     // Boundary bits of the staged input as left by the last replay: one bit per byte,
     // set where a pre-token starts; writes (len + 31) / 32 words.
@@ -48,7 +51,7 @@ public:
     uint32_t vocab_size() const { return hv_.vocab_size; }
     std::string last_error() const { return last_error_; }
     // Number of kernel launches one replay makes (for reporting).
-    int launches_per_replay(bool batch) const { return batch ? 5 : 4; }
+    int launches_per_replay(bool batch) const { return (batch ? 5 : 4) + (hv_.nfc ? (batch ? 2 : 1) : 0); }
     void table_bytes(uint64_t* merge, uint64_t* word, uint64_t* other) const;
 
 private:

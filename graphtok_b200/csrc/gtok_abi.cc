@@ -13,7 +13,6 @@
 #include "device_tables.h"
 #include "encode_kernels.h"
 #include "engine.h"
-#include "nfc_host.h"
 #include "shard_plan.h"
 
 namespace {
@@ -24,8 +23,6 @@ struct Handle {
     std::unique_ptr<gtok::Engine> engine;
     uint32_t cap_bytes = 4096;
     std::vector<uint32_t> rebased;     // scratch for batch offsets
-    std::string norm;                  // scratch for normalised text (NFC vocabularies)
-    std::string norm_doc;
 };
 
 // Leader/follower batching (the reference's src/dispatcher.cc:133-205): a request thread
@@ -64,14 +61,10 @@ bool open_handle(Handle& h, const char* path, uint32_t max_bytes) {
 
 int32_t do_encode(Handle* h, const uint8_t* text, uint32_t len, uint32_t* out, uint32_t max_out, bool dev) {
     if (!text && len) return -1;
-    // The vocabulary's normaliser first (NFC for Qwen2.5), as the reference does before its graph
-    // (src/gtok_shim.cc:117-129); the byte cap applies to what comes out of it.
-    if (h->engine->vocab().nfc && len && gtok::nfc_normalize(text, len, h->norm)) {
-        text = reinterpret_cast<const uint8_t*>(h->norm.data());
-        if (h->norm.size() > 0xFFFFFFFFull) return -3;
-        len = static_cast<uint32_t>(h->norm.size());
-    }
-    if (len > h->cap_bytes) return -3;
+    // A vocabulary's normaliser (NFC for Qwen2.5) runs inside the graph, where the reference
+    // runs it on the host before its graph (src/gtok_shim.cc:117-129); as there, the byte cap
+    // applies to what comes out of it, so the raw length is not checked here for such vocabularies.
+    if (len > h->cap_bytes && (!h->engine->vocab().nfc || len > 3ull * h->cap_bytes)) return -3;   // NFC shrinks a text at most threefold
     int64_t n = h->engine->encode(text, len, h->cap_bytes, out, max_out, dev);
     if (n < 0) g_last_error = h->engine->last_error();
     return static_cast<int32_t>(n);
@@ -84,30 +77,8 @@ int32_t do_encode_batch(Handle* h, const uint8_t* concat_bytes, const uint32_t* 
     const uint32_t first = doc_byte_offsets[0];
     uint64_t total = static_cast<uint64_t>(doc_byte_offsets[n_docs]) - first;
     const uint32_t* offs = doc_byte_offsets;
-    if (h->engine->vocab().nfc) {
-        // each document is normalised on its own; the blob is rebuilt only if one of them changes
-        bool any = false;
-        for (uint32_t i = 0; i < n_docs && !any; ++i)
-            any = gtok::nfc_normalize(concat_bytes + doc_byte_offsets[i], doc_byte_offsets[i + 1] - doc_byte_offsets[i], h->norm_doc);
-        if (any) {
-            h->norm.clear();
-            h->rebased.assign(static_cast<size_t>(n_docs) + 1, 0);
-            for (uint32_t i = 0; i < n_docs; ++i) {
-                const uint8_t* d = concat_bytes + doc_byte_offsets[i];
-                const uint32_t dl = doc_byte_offsets[i + 1] - doc_byte_offsets[i];
-                if (gtok::nfc_normalize(d, dl, h->norm_doc)) h->norm += h->norm_doc;
-                else h->norm.append(reinterpret_cast<const char*>(d), dl);
-                if (h->norm.size() > 0xFFFFFFFFull) return -3;
-                h->rebased[i + 1] = static_cast<uint32_t>(h->norm.size());
-            }
-            if (h->norm.size() > h->cap_bytes) return -3;
-            int64_t n = h->engine->encode_batch(reinterpret_cast<const uint8_t*>(h->norm.data()), h->rebased.data(), n_docs, h->cap_bytes,
-                                                out_tokens, out_cap, out_doc_offsets);
-            if (n < 0) g_last_error = h->engine->last_error();
-            return static_cast<int32_t>(n);
-        }
-    }
-    if (total > h->cap_bytes) return -3;
+    if (total > 0xFFFFFF00ull) return -3;
+    if (total > h->cap_bytes && (!h->engine->vocab().nfc || total > 3ull * h->cap_bytes)) return -3;
     if (first != 0) {
         h->rebased.resize(static_cast<size_t>(n_docs) + 1);
         for (uint32_t i = 0; i <= n_docs; ++i) h->rebased[i] = doc_byte_offsets[i] - first;
@@ -275,8 +246,8 @@ int32_t gtok_x_replay(void* handle, float* ms_out) {
     } catch (...) { return -1; }
 }
 
-int32_t gtok_x_profile(void* handle, float* ms_out5) {
-    float* ms_out3 = ms_out5;
+int32_t gtok_x_profile(void* handle, float* ms_out6) {
+    float* ms_out3 = ms_out6;
     if (!handle || !ms_out3) return -1;
     try {
         Handle* h = static_cast<Handle*>(handle);

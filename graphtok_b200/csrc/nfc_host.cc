@@ -131,6 +131,30 @@ void normalize_stretch(std::vector<uint32_t>& cps, std::vector<uint32_t>& tmp) {
 
 }  // namespace
 
+void nfc_table_words(NfcWords& out) {
+    out.attn_bits.assign(2048, 0);
+    out.attn_sup.clear();
+    for (uint32_t r = 0; r < GTOK_NFC_ATTN_LEN; ++r) {
+        for (uint32_t cp = gtok_nfc_attn[r].lo; cp <= gtok_nfc_attn[r].hi && cp < 0x10000; ++cp) out.attn_bits[cp >> 5] |= 1u << (cp & 31);
+        if (gtok_nfc_attn[r].hi >= 0x10000) {
+            out.attn_sup.push_back(gtok_nfc_attn[r].lo < 0x10000 ? 0x10000 : gtok_nfc_attn[r].lo);
+            out.attn_sup.push_back(gtok_nfc_attn[r].hi);
+        }
+    }
+    out.ccc.clear();
+    for (uint32_t i = 0; i < GTOK_NFC_CCC_LEN; ++i) { out.ccc.push_back(gtok_nfc_ccc[i].cp); out.ccc.push_back(gtok_nfc_ccc[i].ccc); }
+    out.decomp.clear();
+    for (uint32_t i = 0; i < GTOK_NFC_DECOMP_LEN; ++i) {
+        out.decomp.push_back(gtok_nfc_decomp[i].cp);
+        out.decomp.push_back(gtok_nfc_decomp[i].n);
+        for (int k = 0; k < 4; ++k) out.decomp.push_back(gtok_nfc_decomp[i].d[k]);
+    }
+    out.comp.clear();
+    for (uint32_t i = 0; i < GTOK_NFC_COMP_LEN; ++i) {
+        out.comp.push_back(gtok_nfc_comp[i].first); out.comp.push_back(gtok_nfc_comp[i].second); out.comp.push_back(gtok_nfc_comp[i].composite);
+    }
+}
+
 bool nfc_normalize(const uint8_t* text, size_t len, std::string& out) {
     // Every codepoint that can make a text non-NFC is U+0300 or above: lead byte >= 0xCC.
     size_t i = 0;

@@ -7,6 +7,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <string>
+#include <vector>
 
 namespace gtok {
 
@@ -14,5 +15,12 @@ namespace gtok {
 // is); otherwise writes the normalised bytes to `out` and returns true.  Bytes that are
 // not valid UTF-8 are passed through unchanged and act as barriers.
 bool nfc_normalize(const uint8_t* text, size_t len, std::string& out);
+
+// The same tables as flat arrays of 32-bit words, for upload to the device
+// (layouts in device_tables.h).
+struct NfcWords {
+    std::vector<uint32_t> attn_bits, attn_sup, ccc, decomp, comp;
+};
+void nfc_table_words(NfcWords& out);
 
 }  // namespace gtok

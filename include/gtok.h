@@ -79,11 +79,13 @@ int32_t gtok_x_read(void* handle, uint32_t* out_tokens, uint32_t out_cap, uint32
  * pre-token starts at byte i.  Writes (len + 31) / 32 words; returns that count. */
 int32_t gtok_x_read_boundaries(void* handle, uint32_t* out_words, uint32_t max_words);
 /* The staged input once more, launched kernel by kernel with CUDA events between:
- * ms_out5 = {pre-tokenization, words, miss, assemble kernel, whole sequence}. */
-int32_t gtok_x_profile(void* handle, float* ms_out5);
+ * ms_out6 = {pre-tokenization, words, miss, assemble kernel, whole sequence, what runs before
+ * pre-tokenization (normalisation and document-bit kernels)}. */
+int32_t gtok_x_profile(void* handle, float* ms_out6);
 /* Diagnostics: when the environment variable GTOK_PHASE_CLOCKS was set as the staged
  * context was created, SM cycles spent in each phase of the two kernels, summed over
- * thread blocks since the last reset (slots 0-6 pre-tokenization, 8-11 words, 12-15 assemble).  -1 if off. */
+ * thread blocks since the last reset (slots 0-6 pre-tokenization, 8-11 words, 12-15 assemble,
+ * 16-20 miss, 24-26 normalisation).  -1 if off. */
 int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset);
 /* Sizes in bytes of the merge table, the whole-word table and the remaining tables. */
 void gtok_x_table_bytes(void* handle, uint64_t* out3);

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "../../graphtok_b200/csrc/encode_core.h"
+#include "../../graphtok_b200/csrc/nfc_core.h"
 #include "../../graphtok_b200/csrc/nfc_host.h"
 #include "../../graphtok_b200/csrc/shard_plan.h"
 #include "../../graphtok_b200/csrc/tables_build.h"
@@ -162,6 +163,45 @@ int64_t gtok_emul_nfc(const uint8_t* text, uint64_t len, uint8_t* out, uint64_t 
     if (o.size() > cap) return -1;
     std::memcpy(out, o.data(), o.size());
     return static_cast<int64_t>(o.size());
+}
+
+// The device normaliser (csrc/nfc_core.h) run tile by tile on the CPU.  Returns the
+// normalised length, or -(error bits).  `out` must hold `cap` bytes.
+int64_t gtok_emul_nfc_device(const uint8_t* text, uint32_t n, const uint32_t* doc_off, uint32_t n_docs, uint8_t* out, uint32_t cap,
+                             uint32_t* out_doc_off, int reverse, int already_normalised) {
+    using namespace gtok;
+    static NfcWords words;
+    if (words.attn_bits.empty()) nfc_table_words(words);
+    if (n == 0) { if (out_doc_off) for (uint32_t d = 0; d <= n_docs; ++d) out_doc_off[d] = 0; return 0; }
+    const uint32_t n_tiles = (n + kTile - 1) / kTile;
+    std::vector<uint8_t> raw(static_cast<size_t>(n_tiles) * kTile + kTile + kWin + 64, 0xCC);   // junk past n
+    std::memcpy(raw.data(), text, n);
+    std::vector<uint8_t> norm(static_cast<size_t>(cap) + 64, 0xEE);
+    uint32_t raw_meta[4] = {n, n_docs, already_normalised ? 1u : 0u, 0}, meta[4] = {0, 0, 0, 0}, ctl[16] = {0}, status[4] = {0, 0, 0, 0};
+    std::vector<uint32_t> docmask;
+    std::vector<unsigned long long> st0(n_tiles + 1, 0);
+    EncodeArgs a;
+    std::memset(&a, 0, sizeof a);
+    a.raw = raw.data(); a.raw_meta = raw_meta; a.norm_text = norm.data(); a.text = norm.data(); a.norm_meta = meta; a.meta = meta;
+    a.st0 = st0.data(); a.ctl = ctl; a.status = status; a.text_cap = cap;
+    if (doc_off) {
+        docmask.assign(n_tiles * kTileWords + 8, 0);
+        for (uint32_t d = 0; d <= n_docs; ++d) if (doc_off[d] < n) docmask[doc_off[d] >> 5] |= 1u << (doc_off[d] & 31);
+        a.raw_doc_off = doc_off; a.raw_docmask = docmask.data(); a.norm_doc_off = out_doc_off;
+    }
+    a.tb.nfc_attn_bits = words.attn_bits.data();
+    a.tb.nfc_attn_sup = words.attn_sup.data(); a.tb.nfc_attn_sup_n = static_cast<uint32_t>(words.attn_sup.size() / 2);
+    a.tb.nfc_ccc = words.ccc.data(); a.tb.nfc_ccc_n = static_cast<uint32_t>(words.ccc.size() / 2);
+    a.tb.nfc_decomp = words.decomp.data(); a.tb.nfc_decomp_n = static_cast<uint32_t>(words.decomp.size() / 6);
+    a.tb.nfc_comp = words.comp.data(); a.tb.nfc_comp_n = static_cast<uint32_t>(words.comp.size() / 3);
+    CpuBlk blk;
+    blk.reverse = reverse != 0;
+    NfcSmem* sm = new NfcSmem();
+    for (uint32_t t = 0; t < n_tiles; ++t) { std::memset(sm, 0xCD, sizeof *sm); nfc_tile(blk, a, *sm, static_cast<int>(t)); }
+    delete sm;
+    if (ctl[CTL_ERR]) return -static_cast<int64_t>(ctl[CTL_ERR]);
+    std::memcpy(out, norm.data(), meta[0]);
+    return meta[0];
 }
 
 // The shard planner of libgtok (gtok_x_plan_chunks), reachable without a GPU handle.

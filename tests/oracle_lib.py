@@ -63,6 +63,26 @@ def lib_nfc(data):
     return out.raw[:n]
 
 
+def device_nfc(data, doc_off=None, reverse=False, cap=None, already_normalised=False):
+    """NFC by the device normaliser's tile program (csrc/nfc_core.h) run on the CPU.  Returns the bytes, or
+    (bytes, new offsets) when `doc_off` is given; a negative kernel status is returned as an int."""
+    lib = ctypes.CDLL(build_emul())
+    f = lib.gtok_emul_nfc_device
+    f.restype = ctypes.c_int64
+    f.argtypes = [ctypes.c_char_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_char_p, ctypes.c_uint32,
+                  ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    data = bytes(data)
+    cap = len(data) * 3 + 64 if cap is None else cap
+    out = ctypes.create_string_buffer(cap + 64)
+    if doc_off is None:
+        n = f(data, len(data), None, 1, out, cap, None, int(reverse), int(already_normalised))
+        return out.raw[:n] if n >= 0 else int(n)
+    offs = (ctypes.c_uint32 * len(doc_off))(*doc_off)
+    new = (ctypes.c_uint32 * len(doc_off))()
+    n = f(data, len(data), offs, len(doc_off) - 1, out, cap, new, int(reverse), int(already_normalised))
+    return (out.raw[:n], list(new)) if n >= 0 else int(n)
+
+
 class Oracle:
     def __init__(self, tokenizer_json):
         self.lib = ctypes.CDLL(build_oracle())

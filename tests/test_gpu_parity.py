@@ -92,6 +92,45 @@ def test_qwen_raw_text_is_normalised_inside_the_call(gtoks, oracles):
     assert np.array_equal(ids, want) and np.array_equal(doc, want_doc)
 
 
+def test_qwen_normalisation_on_the_device_large_and_odd_cases(oracles):
+    """NFC runs as the graph's first kernel: decomposed text over many tiles, a batch whose documents cut
+    codepoints, a stretch too long for a thread (host normalisation, then a copy-only pass), text that NFC
+    lengthens past the context (rebuilt larger), and the byte cap applying to the normalised length."""
+    import unicodedata as ud
+    from graphtok_b200 import GTok
+    o = oracles["qwen25"]
+    g = GTok(tiny_vocab("qwen25"), max_bytes=1 << 16)
+    try:
+        base = "Vi\u1ec7t Nam c\u00f3 nhi\u1ec1u \ud55c\uad6d\uc5b4 na\u00efve caf\u00e9 \u65e5\u672c "
+        nfd = ud.normalize("NFD", base * 1000).encode()
+        assert len(nfd) > (1 << 16) >= len(ud.normalize("NFC", base * 1000).encode())      # raw over the cap, normalised under it
+        assert np.array_equal(g.encode(nfd), o.encode(nfd))
+        assert np.array_equal(g.encode(nfd), o.encode(nfd))
+        zalgo = ("z" + "\u0301\u0323\u0308" * 50 + " ok ").encode() * 3
+        assert np.array_equal(g.encode(zalgo), o.encode(zalgo))
+        docs = [ud.normalize("NFD", base * 3), "\u0301x", "", "e", "\u0301\u0323", zalgo.decode(), "tail e\u0301"]
+        blob, offs = cases.make_batch(9, docs)
+        ids, doc = g.encode_batch(blob, offs)
+        want, want_doc = o.encode_batch(blob, offs)
+        assert np.array_equal(ids, want) and np.array_equal(doc, want_doc)
+        raw = ud.normalize("NFD", base * 40).encode()
+        cuts = [0, 5, 6, 7, 100, 101, 1000, 1001, 1002, len(raw) // 2, len(raw)]
+        ids, doc = g.encode_batch(raw, np.array(cuts, dtype=np.uint32))
+        parts = [o.encode_normalized(oracle_lib.lib_nfc(raw[cuts[i]:cuts[i + 1]])) for i in range(len(cuts) - 1)]
+        assert np.array_equal(ids, np.concatenate(parts)) and doc.tolist() == np.cumsum([0] + [len(x) for x in parts]).tolist()
+    finally:
+        g.close()
+    small = GTok(tiny_vocab("qwen25"), max_bytes=4096)
+    try:
+        grows = ("\u0958 " * 1000).encode()                  # 4000 bytes that become 7000
+        out = np.zeros(8192, dtype=np.uint32)
+        assert small.lib.gtok_encode(small.handle, grows, len(grows), out.ctypes.data, out.size) == -3
+        ok = ("\u0958 " * 500).encode()                      # 2000 bytes that become 3500
+        assert np.array_equal(small.encode(ok), o.encode(ok))
+    finally:
+        small.close()
+
+
 def test_return_codes(gtoks):
     g = gtoks["gpt2"]
     lib = g.lib

@@ -110,3 +110,79 @@ def test_chunk_plan_concatenates(emuls, oracles, family):
         assert cuts[0] == 0 and cuts[-1] == len(doc) and np.all(np.diff(cuts.astype(np.int64)) >= 0)
         pieces = [o.encode_normalized(doc[int(cuts[k]):int(cuts[k + 1])]) for k in range(parts)]
         assert np.array_equal(np.concatenate(pieces), o.encode_normalized(doc))
+
+
+def _nfc_pool():
+    marks = [0x300, 0x301, 0x302, 0x308, 0x323, 0x327, 0x31B, 0x345, 0x334, 0x340, 0x341, 0x343, 0x344, 0x5B4, 0x64B, 0x651, 0x93C, 0x94D, 0x9BE, 0x9D7,
+             0xB3E, 0xB56, 0xB57, 0xBBE, 0xCC2, 0xCD5, 0xD3E, 0xDCA, 0xDCF, 0xF71, 0xF72, 0xF74, 0x102E, 0x1161, 0x1175, 0x11A8, 0x11C2, 0x1B35, 0x3099,
+             0x309A, 0x1D165, 0x1D16E, 0x110BA, 0x11127, 0x1133E, 0x114B0, 0x115AF, 0x11930]
+    bases = [ord(c) for c in "aeiouAEONcy =\n1."] + [0xE9, 0x1EA0, 0x1100, 0x1112, 0xAC00, 0xAC01, 0xD55C, 0x915, 0x9C7, 0xB47, 0xBC6, 0xCC6, 0xD46, 0xDD9,
+             0xF40, 0x1025, 0x1B05, 0x3046, 0x304B, 0x4E2D, 0x2126, 0x212B, 0xF900, 0xFB1D, 0xFB2A, 0x2000, 0x958, 0xFA30, 0x1D15E, 0x2F800, 0x1F600,
+             0x11099, 0x11131, 0x11347, 0x114B9, 0x115B8, 0x11935, 0x1E69, 0x3A9, 0x438, 0x5E9, 0x644, 0x1F80]
+    return marks, bases
+
+
+def test_device_normaliser_matches_unicodedata_and_host():
+    """The NFC tile program (csrc/nfc_core.h) on the CPU emulation, both thread orders, against Python's
+    unicodedata (well-formed text) and the library's host normaliser (any bytes)."""
+    import random
+    import unicodedata as ud
+    rng = random.Random(11)
+    marks, bases = _nfc_pool()
+
+    def rand_text(k):
+        out = []
+        for _ in range(k):
+            r = rng.random()
+            out.append(chr(rng.choice(bases)) if r < 0.5 else chr(rng.choice(marks)) if r < 0.9 else
+                       chr(rng.choice(bases)) * rng.randint(1, 20) if r < 0.95 else "plain words " * rng.randint(0, 3))
+        return "".join(out)
+
+    named = ["e\u0301", "\u212b", "\u1100\u1161\u11a8", "\u0958", "x\u0301\u0301\u0301", "\u0301a", "a\u0323\u0302", "\u0344", "", "ascii only",
+             "\u65e5\u672c\u8a9e", "\U0001d15e", "a" * 4095 + "\u0301", "a" * 4094 + "e\u0301", "e\u0301" * 3000, "\uac00\u11a8" * 2000]
+    for s in named:
+        for rev in (False, True):
+            assert oracle_lib.device_nfc(s.encode(), reverse=rev) == ud.normalize("NFC", s).encode(), repr(s[:20])
+    for it in range(250):
+        s = rand_text(rng.randint(0, 60) if it % 5 else rng.randint(500, 2500))
+        b = s.encode()
+        assert oracle_lib.device_nfc(b, reverse=bool(it & 1)) == ud.normalize("NFC", s).encode(), it
+        if it % 4 == 1 and b:      # the same with some bytes broken: the host normaliser defines the result
+            bl = bytearray(b)
+            for _ in range(rng.randint(1, 6)):
+                bl[rng.randrange(len(bl))] = rng.choice([0x80, 0xBF, 0xC0, 0xC3, 0xE2, 0xF0, 0xFF, 0xCC, 0x41])
+            assert oracle_lib.device_nfc(bytes(bl), reverse=bool(it & 2)) == oracle_lib.lib_nfc(bytes(bl)), it
+    blob = "".join("a" + chr(cp) + "b" for cp in range(0x80, 0x30000) if not 0xD800 <= cp <= 0xDFFF)
+    assert oracle_lib.device_nfc(blob.encode()) == ud.normalize("NFC", blob).encode()
+
+
+def test_device_normaliser_batches_documents_apart():
+    """Documents are normalised one by one (a mark at the start of one does not combine with the end of the
+    one before, a codepoint cut by a document boundary is left alone) and their offsets are rewritten."""
+    import random
+    rng = random.Random(12)
+    marks, bases = _nfc_pool()
+    for it in range(150):
+        s = "".join(chr(rng.choice(bases if rng.random() < 0.5 else marks)) for _ in range(rng.randint(1, 400)))
+        b = s.encode()
+        offs = [0] + sorted(rng.randrange(len(b) + 1) for _ in range(rng.randint(0, 7))) + [len(b)]
+        if it % 3 == 0:
+            offs.append(len(b))
+        want, want_offs = b"", [0]
+        for i in range(len(offs) - 1):
+            want += oracle_lib.lib_nfc(b[offs[i]:offs[i + 1]])
+            want_offs.append(len(want))
+        got = oracle_lib.device_nfc(b, doc_off=offs, reverse=bool(it & 1))
+        assert got == (want, want_offs), (it, offs)
+
+
+def test_device_normaliser_reports_what_it_cannot_do():
+    """A stretch of more codepoints than one thread takes and a result longer than the buffer set error
+    bits (the engine then normalises on the host, or retries with a larger buffer); text flagged as
+    normalised already is copied as it is."""
+    zalgo = ("a" + "\u0301\u0323" * 60).encode()
+    assert oracle_lib.device_nfc(zalgo) == -16
+    assert oracle_lib.device_nfc(zalgo, already_normalised=True) == zalgo
+    grows = ("\u0958 " * 100).encode()
+    assert oracle_lib.device_nfc(grows, cap=len(grows) + 10) == -32
+    assert oracle_lib.device_nfc(grows) == oracle_lib.nfc(grows)
