@@ -456,8 +456,8 @@ int64_t Engine::encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, ui
     int64_t total = im.run(c, false, text, len, nullptr, 1, cap_bytes, last_error_);
     if (total == Impl::kNoCtx) return -1;
     if (total < 0) return total;
-    if (im.nfc && c->h_status[2] > cap_bytes) return -3;
-    if (static_cast<uint64_t>(total) > max_out) return -2;
+    if (im.nfc && c->h_status[2] > cap_bytes) { last_error_ = "normalised text is longer than the handle's byte capacity"; return -3; }
+    if (static_cast<uint64_t>(total) > max_out) { last_error_ = "more token ids than the output buffer holds"; return -2; }
     if (total == 0) return 0;
     cudaError_t e;
     if (out_on_device) {
@@ -483,8 +483,8 @@ int64_t Engine::encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint
     int64_t total = im.run(c, true, bytes, len, doc_off, n_docs, cap_bytes, last_error_);
     if (total == Impl::kNoCtx) return -4;
     if (total < 0) return total;
-    if (im.nfc && c->h_status[2] > cap_bytes) return -3;
-    if (static_cast<uint64_t>(total) > out_cap) return -2;
+    if (im.nfc && c->h_status[2] > cap_bytes) { last_error_ = "normalised text is longer than the handle's byte capacity"; return -3; }
+    if (static_cast<uint64_t>(total) > out_cap) { last_error_ = "more token ids than the output buffer holds"; return -2; }
     if (!im.grow_host_out(c, static_cast<size_t>(total) + n_docs + 2, last_error_)) return -1;
     cudaError_t e = cudaSuccess;
     if (total) e = cudaMemcpyAsync(c->h_out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToHost, c->stream);
