@@ -4,9 +4,15 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
+#include <mutex>
+#include <thread>
 
 #include "encode_core.h"
 #include "encode_kernels.h"
@@ -40,6 +46,93 @@ bool upload(const std::vector<T>& v, const T** dst, std::vector<void*>& owned, s
     return true;
 }
 
+// A few host threads that share the staging copies of one call: text into pinned memory and
+// ids out of it move at memcpy speed, which one thread cannot keep near what PCIe carries.
+// The workers only run the job's function (plain memcpy); every CUDA call stays on the
+// calling thread.  start() publishes a job of `parts` pieces, take() hands out the next piece
+// (to workers and to the caller alike), finish() returns when all pieces are done.  Workers
+// spin for a short while after a job, so that the copy-out of a call finds them awake after
+// its copy-in, then sleep on a condition variable.
+class CopyPool {
+public:
+    explicit CopyPool(int workers) {
+        for (int i = 0; i < workers; ++i) threads_.emplace_back([this] { loop(); });
+    }
+    ~CopyPool() {
+        stop_.store(true);
+        { std::lock_guard<std::mutex> lk(mu_); }
+        cv_.notify_all();
+        for (std::thread& t : threads_) t.join();
+    }
+    void start(int parts, const std::function<void(int)>* fn) {
+        fn_ = fn;
+        parts_ = static_cast<uint32_t>(parts);
+        remaining_.store(parts);
+        const uint64_t gen = (state_.load() >> 32) + 1;
+        state_.store(gen << 32, std::memory_order_release);
+        if (sleepers_.load() > 0) { { std::lock_guard<std::mutex> lk(mu_); } cv_.notify_all(); }
+    }
+    // Next piece of the current job, or -1 when none is left.
+    int take() {
+        uint64_t s = state_.load(std::memory_order_acquire);
+        for (;;) {
+            const uint32_t next = static_cast<uint32_t>(s);
+            if (next >= parts_) return -1;
+            if (state_.compare_exchange_weak(s, s + 1, std::memory_order_acq_rel)) return static_cast<int>(next);
+        }
+    }
+    void done_one() { remaining_.fetch_sub(1, std::memory_order_acq_rel); }
+    void finish() {
+        while (remaining_.load(std::memory_order_acquire) != 0) cpu_relax();
+        state_.store((state_.load() & 0xFFFFFFFF00000000ull) | 0xFFFFFFFFull, std::memory_order_release);   // closed: no piece can be taken any more
+        while (active_.load(std::memory_order_acquire) != 0) cpu_relax();
+        fn_ = nullptr;
+    }
+    static void cpu_relax() {
+#if defined(__x86_64__) || defined(__i386__)
+        __builtin_ia32_pause();
+#else
+        std::this_thread::yield();
+#endif
+    }
+
+private:
+    void loop() {
+        uint64_t seen = 0;
+        for (;;) {
+            // wait for a job newer than `seen`: spin briefly, then sleep
+            auto t0 = std::chrono::steady_clock::now();
+            for (uint32_t spins = 0;; ++spins) {
+                if (stop_.load()) return;
+                if ((state_.load(std::memory_order_acquire) >> 32) != seen) break;
+                cpu_relax();
+                if ((spins & 255u) == 255u && std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(1500)) {
+                    std::unique_lock<std::mutex> lk(mu_);
+                    sleepers_.fetch_add(1);
+                    cv_.wait(lk, [&] { return stop_.load() || (state_.load(std::memory_order_acquire) >> 32) != seen; });
+                    sleepers_.fetch_sub(1);
+                    t0 = std::chrono::steady_clock::now();
+                }
+            }
+            active_.fetch_add(1, std::memory_order_acq_rel);
+            seen = state_.load(std::memory_order_acquire) >> 32;
+            for (int p; (p = take()) >= 0;) { (*fn_)(p); done_one(); }
+            active_.fetch_sub(1, std::memory_order_acq_rel);
+        }
+    }
+    std::vector<std::thread> threads_;
+    std::mutex mu_;
+    std::condition_variable cv_;
+    const std::function<void(int)>* fn_ = nullptr;
+    uint32_t parts_ = 0;
+    std::atomic<uint64_t> state_{0};            // job number << 32 | next piece (0xFFFFFFFF = closed)
+    std::atomic<int> remaining_{0}, active_{0}, sleepers_{0};
+    std::atomic<bool> stop_{false};
+};
+
+constexpr size_t kCopyPart = 256 << 10;      // bytes per staging step: small enough to overlap with the DMA of the one before
+constexpr int kCopyEvents = 64;
+
 constexpr size_t kTextPad = kTile + kWin + 256;
 constexpr uint32_t kHdrWords = 4;     // meta occupies the first 4 words of the header; offsets follow
 
@@ -70,6 +163,7 @@ struct Ctx {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     cudaEvent_t ev[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t out_ev[kCopyEvents] = {};
     int nfc_blocks = 1;
     int pretok_blocks = 1, words_blocks = 1, miss_blocks = 1, asm_blocks = 1, docmask_blocks = 1;
     size_t mask_words = 0;
@@ -80,6 +174,7 @@ struct Ctx {
         if (exec) cudaGraphExecDestroy(exec);
         if (graph) cudaGraphDestroy(graph);
         for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
+        for (cudaEvent_t e : out_ev) if (e) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
         cudaFree(d_raw); cudaFree(d_rawhdr); cudaFree(d_docmask_raw);
         cudaFree(d_text); cudaFree(d_hdr); cudaFree(d_docmask); cudaFree(d_bmask); cudaFree(d_amask);
@@ -109,6 +204,9 @@ struct Engine::Impl {
     std::string norm;                    // host normalisation, used only after kErrNfcLong
     std::string norm_doc;
     std::vector<uint32_t> norm_off;
+    std::unique_ptr<CopyPool> pool;      // staging copies of large inputs and outputs
+    std::unique_ptr<std::atomic<uint8_t>[]> part_done;
+    int part_done_n = 0;
 
     ~Impl() {
         single.reset();
@@ -316,7 +414,40 @@ struct Engine::Impl {
     // With NFC the destination is the raw buffer; `normalised` tells the kernel to copy only.
     bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err,
                      bool normalised = false) {
-        if (len) std::memcpy(c->h_text, bytes, len);
+        uint8_t* d_dst = nfc ? c->d_raw : c->d_text;
+        if (len && pool && len >= 4 * kCopyPart) {
+            // piece by piece: finished pieces go to the device while the rest is still being copied into pinned memory
+            const int parts = static_cast<int>((len + kCopyPart - 1) / kCopyPart);
+            if (part_done_n < parts) { part_done.reset(new std::atomic<uint8_t>[parts]); part_done_n = parts; }
+            for (int p = 0; p < parts; ++p) part_done[p].store(0, std::memory_order_relaxed);
+            const std::function<void(int)> fn = [&](int p) {
+                const size_t off = static_cast<size_t>(p) * kCopyPart;
+                std::memcpy(c->h_text + off, bytes + off, std::min(kCopyPart, static_cast<size_t>(len) - off));
+                part_done[p].store(1, std::memory_order_release);
+            };
+            pool->start(parts, &fn);
+            int issued = 0;
+            cudaError_t ce = cudaSuccess;
+            while (issued < parts) {
+                int upto = issued;
+                while (upto < parts && part_done[upto].load(std::memory_order_acquire)) ++upto;
+                if (upto > issued) {
+                    const size_t off = static_cast<size_t>(issued) * kCopyPart;
+                    const size_t end = std::min(static_cast<size_t>(upto) * kCopyPart, static_cast<size_t>(len));
+                    const cudaError_t e1 = cudaMemcpyAsync(d_dst + off, c->h_text + off, (end - off + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream);
+                    if (ce == cudaSuccess) ce = e1;
+                    issued = upto;
+                    continue;
+                }
+                const int p = pool->take();
+                if (p >= 0) { fn(p); pool->done_one(); } else CopyPool::cpu_relax();
+            }
+            pool->finish();
+            if (ce != cudaSuccess) { err = std::string("text copy: ") + cudaGetErrorString(ce); return false; }
+        } else if (len) {
+            std::memcpy(c->h_text, bytes, len);
+            GTOK_CUDA(cudaMemcpyAsync(d_dst, c->h_text, (static_cast<size_t>(len) + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream));
+        }
         c->h_hdr[0] = len;
         c->h_hdr[1] = n_docs;
         c->h_hdr[2] = normalised ? 1u : 0u;
@@ -326,10 +457,59 @@ struct Engine::Impl {
             std::memcpy(c->h_hdr + kHdrWords, doc_off, (static_cast<size_t>(n_docs) + 1) * 4);
             hdr_words += static_cast<size_t>(n_docs) + 1;
         }
-        if (len) GTOK_CUDA(cudaMemcpyAsync(nfc ? c->d_raw : c->d_text, c->h_text, (static_cast<size_t>(len) + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream));
         GTOK_CUDA(cudaMemcpyAsync(nfc ? c->d_rawhdr : c->d_hdr, c->h_hdr, hdr_words * 4, cudaMemcpyHostToDevice, c->stream));
         c->staged_len = len;
         c->staged_docs = n_docs;
+        return true;
+    }
+
+    // ids (and, for a batch, the document offsets behind them) from the device to the caller's
+    // memory through the pinned buffer; large outputs part by part, so that the copy out of
+    // pinned memory of one part overlaps with the DMA of the next ones.
+    bool copy_out(Ctx* c, uint32_t* out, size_t words, uint32_t* out_doc_tok, size_t doc_words, std::string& err) {
+        if (!grow_host_out(c, words + doc_words + 2, err)) return false;
+        const size_t bytes = words * 4;
+        if (pool && bytes >= 4 * kCopyPart) {
+            size_t part = kCopyPart;
+            while ((bytes + part - 1) / part > static_cast<size_t>(kCopyEvents)) part *= 2;
+            const int parts = static_cast<int>((bytes + part - 1) / part);
+            for (int p = 0; p < parts; ++p) {
+                if (!c->out_ev[p]) GTOK_CUDA(cudaEventCreateWithFlags(&c->out_ev[p], cudaEventDisableTiming));
+                const size_t off = static_cast<size_t>(p) * part, nb = std::min(part, bytes - off);
+                GTOK_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(c->h_out) + off, reinterpret_cast<const char*>(c->d_out) + off, nb, cudaMemcpyDeviceToHost, c->stream));
+                GTOK_CUDA(cudaEventRecord(c->out_ev[p], c->stream));
+            }
+            if (doc_words) GTOK_CUDA(cudaMemcpyAsync(c->h_out + words, c->d_doc_tok, doc_words * 4, cudaMemcpyDeviceToHost, c->stream));
+            // pieces arrive in order; this thread watches the events and publishes how many are in,
+            // every thread (this one too) copies arrived pieces out of pinned memory
+            std::atomic<int> ready{0};
+            std::atomic<int> failed{0};
+            const std::function<void(int)> fn = [&](int p) {
+                while (ready.load(std::memory_order_acquire) <= p && !failed.load(std::memory_order_relaxed)) CopyPool::cpu_relax();
+                if (failed.load(std::memory_order_relaxed)) return;
+                const size_t off = static_cast<size_t>(p) * part, nb = std::min(part, bytes - off);
+                std::memcpy(reinterpret_cast<char*>(out) + off, reinterpret_cast<const char*>(c->h_out) + off, nb);
+            };
+            pool->start(parts, &fn);
+            int in = 0;
+            cudaError_t ce = cudaSuccess;
+            while (in < parts) {
+                const cudaError_t q = cudaEventQuery(c->out_ev[in]);
+                if (q == cudaSuccess) { ready.store(++in, std::memory_order_release); continue; }
+                if (q != cudaErrorNotReady) { ce = q; failed.store(1); break; }
+                CopyPool::cpu_relax();
+            }
+            for (int p; (p = pool->take()) >= 0;) { fn(p); pool->done_one(); }
+            pool->finish();
+            if (ce != cudaSuccess) { err = std::string("token copy: ") + cudaGetErrorString(ce); return false; }
+            GTOK_CUDA(cudaStreamSynchronize(c->stream));
+        } else {
+            if (words) GTOK_CUDA(cudaMemcpyAsync(c->h_out, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
+            if (doc_words) GTOK_CUDA(cudaMemcpyAsync(c->h_out + words, c->d_doc_tok, doc_words * 4, cudaMemcpyDeviceToHost, c->stream));
+            GTOK_CUDA(cudaStreamSynchronize(c->stream));
+            if (words) std::memcpy(out, c->h_out, bytes);
+        }
+        if (doc_words) std::memcpy(out_doc_tok, c->h_out + words, doc_words * 4);
         return true;
     }
 
@@ -438,6 +618,15 @@ Engine* Engine::create(const std::string& path, std::string& err) {
     im.nfc_per_sm = nfc_blocks_per_sm();
     im.nfc = e->hv_.nfc;
     if (!im.upload_tables(err)) return nullptr;
+    {
+        // GTOK_COPY_THREADS = host threads that share one call's staging copies (1 = the caller alone)
+        int want = 4;
+        if (const char* env = std::getenv("GTOK_COPY_THREADS")) want = std::atoi(env);
+        const int hw = static_cast<int>(std::thread::hardware_concurrency());
+        if (hw > 0) want = std::min(want, std::max(1, hw / 2));
+        want = std::min(want, 16);
+        if (want > 1) im.pool.reset(new CopyPool(want - 1));
+    }
     return e.release();
 }
 
@@ -459,17 +648,11 @@ int64_t Engine::encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, ui
     if (im.nfc && c->h_status[2] > cap_bytes) { last_error_ = "normalised text is longer than the handle's byte capacity"; return -3; }
     if (static_cast<uint64_t>(total) > max_out) { last_error_ = "more token ids than the output buffer holds"; return -2; }
     if (total == 0) return 0;
-    cudaError_t e;
     if (out_on_device) {
-        e = cudaMemcpyAsync(out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToDevice, c->stream);
+        cudaError_t e = cudaMemcpyAsync(out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToDevice, c->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-    } else {
-        if (!im.grow_host_out(c, static_cast<size_t>(total), last_error_)) return -1;
-        e = cudaMemcpyAsync(c->h_out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToHost, c->stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-        if (e == cudaSuccess) std::memcpy(out, c->h_out, static_cast<size_t>(total) * 4);
-    }
-    if (e != cudaSuccess) { last_error_ = std::string("token copy: ") + cudaGetErrorString(e); return -1; }
+        if (e != cudaSuccess) { last_error_ = std::string("token copy: ") + cudaGetErrorString(e); return -1; }
+    } else if (!im.copy_out(c, out, static_cast<size_t>(total), nullptr, 0, last_error_)) return -1;
     return total;
 }
 
@@ -485,15 +668,7 @@ int64_t Engine::encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint
     if (total < 0) return total;
     if (im.nfc && c->h_status[2] > cap_bytes) { last_error_ = "normalised text is longer than the handle's byte capacity"; return -3; }
     if (static_cast<uint64_t>(total) > out_cap) { last_error_ = "more token ids than the output buffer holds"; return -2; }
-    if (!im.grow_host_out(c, static_cast<size_t>(total) + n_docs + 2, last_error_)) return -1;
-    cudaError_t e = cudaSuccess;
-    if (total) e = cudaMemcpyAsync(c->h_out, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToHost, c->stream);
-    if (e == cudaSuccess)
-        e = cudaMemcpyAsync(c->h_out + total, c->d_doc_tok, (static_cast<size_t>(n_docs) + 1) * 4, cudaMemcpyDeviceToHost, c->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-    if (e != cudaSuccess) { last_error_ = std::string("token copy: ") + cudaGetErrorString(e); return -1; }
-    if (total) std::memcpy(out_tokens, c->h_out, static_cast<size_t>(total) * 4);
-    std::memcpy(out_doc_tok, c->h_out + total, (static_cast<size_t>(n_docs) + 1) * 4);
+    if (!im.copy_out(c, out_tokens, static_cast<size_t>(total), out_doc_tok, static_cast<size_t>(n_docs) + 1, last_error_)) return -1;
     return total;
 }
 
