@@ -87,7 +87,8 @@ struct EncodeArgs {
     uint32_t* stage;              // u32 per byte: id stored at the byte where its pre-token starts (+k for its k-th id), else invalid
     uint32_t* ovf;                // kTokExtra u32 per tile: ids of a tile's last pre-token that do not fit before the tile's end
     unsigned long long* gmiss;    // pre-tokens of 2..16 bytes the whole-word table did not know: position | len << 32
-    unsigned long long* gmed;     // the same for 17..64 bytes
+    unsigned long long* gmed;     // the same for 33..64 bytes (from the front) and 17..32 bytes (from the back, downwards)
+    uint32_t gmed_cap;            // entries in gmed
     uint32_t* glong_g;            // pre-tokens longer than 64 bytes: position, length (0 = not known yet), id count
     uint32_t* glong_len;
     uint32_t* glong_cnt;
@@ -1136,9 +1137,14 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch of the miss kernel
 constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB); owners fit a byte
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
-enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9 };
+enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10 };
 constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
-constexpr int kMedBatch = 64;                  // so that the long merge chains of the latter start first and spread over more blocks
+// A batch lasts as long as its longest merge chain, so pre-tokens are batched by length class and
+// the classes are handed out longest first: 33..64 bytes, 17..32 bytes, then the short ones.
+// Batch sizes are such that a batch always fits the arena (48 * 64, 96 * 32 slots).
+constexpr int kMedSplit = 32;
+constexpr int kMedBatchA = 48;                 // 33..64 bytes
+constexpr int kMedBatchB = 96;                 // 17..32 bytes
 
 struct WordsSmem {
     alignas(16) uint8_t txt[kTile + 64];
@@ -1147,7 +1153,7 @@ struct WordsSmem {
     alignas(16) uint32_t tok[kTile + kTokExtra];
     uint16_t wl[kTile + 8];            // offsets in the tile of the pre-token starts, in order; then the end sentinel
     uint32_t miss[kTile / 2];          // offset | len << 12, up to 16 bytes
-    uint32_t med[kTile / 16];          // offset | len << 12, 17..64 bytes
+    uint32_t med[kTile / 16];          // offset | len << 12: 33..64 bytes from the front, 17..32 bytes from the back
     uint32_t lng_o[kLongPerTile], lng_len[kLongPerTile];
     uint32_t b2i[256];
     uint32_t scan[kThreads];
@@ -1175,35 +1181,37 @@ struct AsmSmem {
     uint32_t ctr[8];
     unsigned long long clk_last;
 };
-enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7, C_NMED = 5, C_BASED = 6 };
+enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7, C_NMED = 5, C_BASED = 6, C_NMED2 = 4, C_BASED2 = 7 };
 
 // Greedy BPE of one pre-token by a single thread (lowest rank first, leftmost among
 // equals, src/host_encode.cc:617-648).  ids/rk/nw are the pre-token's stretch of the
 // block's symbol arena with the pair ranks already probed; merged-away symbols are
 // marked dead in place, so a step is one pass over the slots plus one round trip for
 // the two new pairs.
+// What the arena keeps per pair is rank << 6 | slot (kNoRank when no rule joins the pair): the
+// lowest key is the lowest rank and, among equal ranks, the leftmost pair, so the search for the
+// next merge is a plain minimum.  Ranks stay below 2^26 - 1 (checked when the tables are built),
+// slots below 64.
+GTOK_DEV uint32_t rank_key(uint32_t rank, uint32_t slot) { return rank == kNoRank ? kNoRank : ((rank << 6) | slot); }
+
 GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint16_t* lnk, uint32_t len, uint32_t* out) {
     // The stretch starts on a 4-slot boundary and is padded to a multiple of 4 with rank-less
-    // slots, so the rank scan reads four slots per load.  lnk[i] = prev << 8 | next (slot numbers
+    // slots, so the scan reads four slots per load.  lnk[i] = prev << 8 | next (slot numbers
     // within the stretch, 0xFF = none) keeps the live symbols chained.
     const uint32_t len4 = (len + 3u) & ~3u;
     for (;;) {
-        uint32_t best = kNoRank, bi = 0;
-        for (uint32_t i = 0; i < len4; i += 4) {
+        uint32_t best = kNoRank;
 #if defined(__CUDA_ARCH__)
+#pragma unroll 4
+        for (uint32_t i = 0; i < len4; i += 4) {
             const uint4 v = *reinterpret_cast<const uint4*>(rk + i);
-            const uint32_t r0 = v.x, r1 = v.y, r2 = v.z, r3 = v.w;
-#else
-            const uint32_t r0 = rk[i], r1 = rk[i + 1], r2 = rk[i + 2], r3 = rk[i + 3];
-#endif
-            const uint32_t m01 = r1 < r0 ? r1 : r0, m23 = r3 < r2 ? r3 : r2;
-            const uint32_t m = m23 < m01 ? m23 : m01;
-            if (m < best) {
-                best = m;
-                bi = i + (r0 == m ? 0u : r1 == m ? 1u : r2 == m ? 2u : 3u);
-            }
+            best = min(best, min(min(v.x, v.y), min(v.z, v.w)));
         }
+#else
+        for (uint32_t i = 0; i < len4; ++i) if (rk[i] < best) best = rk[i];
+#endif
         if (best == kNoRank) break;
+        const uint32_t bi = best & 63u;
         const uint32_t l = lnk[bi];
         const uint32_t j = l & 0xFFu, p = l >> 8;
         const uint32_t k = lnk[j] & 0xFFu;
@@ -1214,8 +1222,8 @@ GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, ui
         if (k != 0xFFu) lnk[k] = static_cast<uint16_t>((bi << 8) | (lnk[k] & 0xFFu));
         RankRes right, left;
         probe_rule2(a.tb, k != 0xFFu, merged, k != 0xFFu ? ids[k] : 0u, &right, p != 0xFFu, p != 0xFFu ? ids[p] : 0u, merged, &left);
-        rk[bi] = right.rank; nw[bi] = right.res;
-        if (p != 0xFFu) { rk[p] = left.rank; nw[p] = left.res; }
+        rk[bi] = rank_key(right.rank, bi); nw[bi] = right.res;
+        if (p != 0xFFu) { rk[p] = rank_key(left.rank, p); nw[p] = left.res; }
     }
     uint32_t c = 0;
     for (uint32_t i = 0; i != 0xFFu; i = lnk[i] & 0xFFu) out[c++] = ids[i];
@@ -1470,6 +1478,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
             bool wp[4];
 #if defined(__CUDA_ARCH__)
             uint4 sa[4], sb[4];
+#pragma unroll
 #endif
             for (int u = 0; u < 4; ++u) {
                 wp[u] = false;
@@ -1497,8 +1506,9 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                     continue;
                 }
                 if (len > kShortWordMax) {
-                    uint32_t slot = shared_add(&sm.ctr[C_NMED], 1u);
-                    sm.med[slot] = o | (len << 12);
+                    const bool big = len > static_cast<uint32_t>(kMedSplit);
+                    const uint32_t slot = shared_add(&sm.ctr[big ? C_NMED : C_NMED2], 1u);
+                    sm.med[big ? slot : kTile / 16 - 1 - slot] = o | (len << 12);
                     continue;
                 }
                 if (len > kWordKeyMax) {
@@ -1519,6 +1529,9 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                 sb[u] = __ldg(sp + 1);
 #endif
             }
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
             for (int u = 0; u < 4; ++u) {
                 if (!wp[u]) continue;
                 uint32_t id;
@@ -1545,21 +1558,22 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
         uint32_t nm = sm.ctr[C_NMISS], nl = sm.ctr[C_NTEAM];
         if (nl > kLongPerTile) nl = kLongPerTile;
         sm.ctr[C_NTEAM] = nl;
+        const uint32_t nd = sm.ctr[C_NMED], nd2 = sm.ctr[C_NMED2];
 #if defined(__CUDA_ARCH__)
-        const uint32_t nd = sm.ctr[C_NMED];
         sm.ctr[C_BASEM] = nm ? atomicAdd(a.ctl + CTL_NMISS, nm) : 0u;
         sm.ctr[C_BASEL] = nl ? atomicAdd(a.ctl + CTL_NLONG, nl) : 0u;
         sm.ctr[C_BASED] = nd ? atomicAdd(a.ctl + CTL_NMED, nd) : 0u;
+        sm.ctr[C_BASED2] = nd2 ? atomicAdd(a.ctl + CTL_NMED2, nd2) : 0u;
 #else
-        const uint32_t nd = sm.ctr[C_NMED];
         sm.ctr[C_BASEM] = a.ctl[CTL_NMISS]; a.ctl[CTL_NMISS] += nm;
         sm.ctr[C_BASEL] = a.ctl[CTL_NLONG]; a.ctl[CTL_NLONG] += nl;
         sm.ctr[C_BASED] = a.ctl[CTL_NMED]; a.ctl[CTL_NMED] += nd;
+        sm.ctr[C_BASED2] = a.ctl[CTL_NMED2]; a.ctl[CTL_NMED2] += nd2;
 #endif
     });
     {
         const uint32_t nm = sm.ctr[C_NMISS], nl = sm.ctr[C_NTEAM], bm0 = sm.ctr[C_BASEM], bl0 = sm.ctr[C_BASEL];
-        const uint32_t nd = sm.ctr[C_NMED], bd0 = sm.ctr[C_BASED];
+        const uint32_t nd = sm.ctr[C_NMED], bd0 = sm.ctr[C_BASED], nd2 = sm.ctr[C_NMED2], bd2 = sm.ctr[C_BASED2];
         blk.par([&](int tid) {
             for (uint32_t i = tid; i < nm; i += kThreads) {
                 uint32_t mv = sm.miss[i];
@@ -1568,6 +1582,10 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
             for (uint32_t i = tid; i < nd; i += kThreads) {
                 uint32_t mv = sm.med[i];
                 a.gmed[bd0 + i] = static_cast<unsigned long long>(t0 + (mv & 0xFFFu)) | (static_cast<unsigned long long>(mv >> 12) << 32);
+            }
+            for (uint32_t i = tid; i < nd2; i += kThreads) {
+                uint32_t mv = sm.med[kTile / 16 - 1 - i];
+                a.gmed[a.gmed_cap - 1 - (bd2 + i)] = static_cast<unsigned long long>(t0 + (mv & 0xFFFu)) | (static_cast<unsigned long long>(mv >> 12) << 32);
             }
             for (uint32_t i = tid; i < nl; i += kThreads) {
                 a.glong_g[bl0 + i] = t0 + sm.lng_o[i];
@@ -1589,6 +1607,10 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
     mark(11);
 }
 
+// Arena slots a pre-token of `len` symbols takes: whole groups of four (the rank scan reads a
+// group per load).
+GTOK_DEV uint32_t arena_slots(uint32_t len) { return (len + 3u) & ~3u; }
+
 // Stores the k-th id of the pre-token that starts at byte g.
 GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
     const uint32_t tile = g / kTile, t1 = (tile + 1) * kTile;
@@ -1600,7 +1622,7 @@ GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
 // The owner lays its symbols out in the block's arena, all threads probe the pairs, the
 // owner merges (lowest rank first) and stores the ids.
 template <class Blk>
-GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, uint32_t first, uint32_t n_miss, uint32_t batch) {
+GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss, uint32_t batch) {
     const DeviceTables& tb = a.tb;
     constexpr uint32_t kPending = 0xFFFFFFFDu;
     uint32_t* ids = sm.ws;
@@ -1618,19 +1640,19 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     };
     mark(-1);
     blk.par([&](int tid) {
-        if (static_cast<uint32_t>(tid) < n_here) sm.word[tid] = list[first + tid];
+        if (static_cast<uint32_t>(tid) < n_here) sm.word[tid] = list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];   // dir = -1: a list that grows downwards
     });
     uint32_t done = 0;
     while (done < n_here) {
         blk.par([&](int tid) {
             uint32_t idx = done + tid;
-            sm.scan[tid] = idx < n_here ? ((static_cast<uint32_t>(sm.word[idx] >> 32) + 3u) & ~3u) : 0u;   // stretches of whole 4-slot groups
+            sm.scan[tid] = idx < n_here ? arena_slots(static_cast<uint32_t>(sm.word[idx] >> 32)) : 0u;
         });
         uint32_t tot = 0;
         blk.excl_scan(sm.scan, &tot);
         blk.par([&](int tid) {
             uint32_t idx = done + tid;
-            uint32_t len = idx < n_here ? ((static_cast<uint32_t>(sm.word[idx] >> 32) + 3u) & ~3u) : 0u;
+            uint32_t len = idx < n_here ? arena_slots(static_cast<uint32_t>(sm.word[idx] >> 32)) : 0u;
             bool fits = idx < n_here && sm.scan[tid] + len <= static_cast<uint32_t>(kArenaSyms);
             sm.red[tid] = fits ? 0xFFFFFFFFu : static_cast<uint32_t>(tid);
         });
@@ -1640,7 +1662,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
         // owner: which slots are mine (shared memory only)
         blk.par([&](int tid) {
             if (static_cast<uint32_t>(tid) >= nb) return;
-            const uint32_t len = (static_cast<uint32_t>(sm.word[done + tid] >> 32) + 3u) & ~3u, at = sm.scan[tid];
+            const uint32_t len = arena_slots(static_cast<uint32_t>(sm.word[done + tid] >> 32)), at = sm.scan[tid];
             if (static_cast<uint32_t>(tid) + 1 == nb) sm.ctr[C_USED] = at + len;
             for (uint32_t i = 0; i < len; ++i) sm.owner[at + i] = static_cast<uint8_t>(tid);
             sm.aoff[tid] = at;
@@ -1684,7 +1706,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             for (uint32_t sidx = tid; sidx < used; sidx += kThreads) {
                 if (rk[sidx] != kPending) continue;
                 RankRes r = probe_rule(tb, ids[sidx], ids[sidx + 1]);
-                rk[sidx] = r.rank;
+                rk[sidx] = rank_key(r.rank, sidx - sm.scan[sm.owner[sidx]]);
                 nw[sidx] = r.res;
             }
         });

@@ -151,19 +151,24 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
     MissSmem& sm = *reinterpret_cast<MissSmem*>(smem_raw);
     __shared__ uint32_t s_pick;
     GpuBlk blk;
-    const uint32_t n_miss = a.ctl[CTL_NMISS], n_med = a.ctl[CTL_NMED], n_long = a.ctl[CTL_NLONG];
-    const uint32_t med_batches = (n_med + kMedBatch - 1) / kMedBatch, short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
+    const uint32_t n_miss = a.ctl[CTL_NMISS], n_med = a.ctl[CTL_NMED], n_med2 = a.ctl[CTL_NMED2], n_long = a.ctl[CTL_NLONG];
+    const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med2_batches = (n_med2 + kMedBatchB - 1) / kMedBatchB;
+    const uint32_t short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
     sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
     __syncthreads();
-    // the batches of longer pre-tokens first: their merge chains decide when the kernel ends
+    // longest pre-tokens first: their merge chains decide when the kernel ends
     for (;;) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_BATCH, 1u);
         __syncthreads();
         const uint32_t t = s_pick;
         __syncthreads();
-        if (t >= med_batches + short_batches) break;
-        if (t < med_batches) miss_batch(blk, a, sm, a.gmed, t * kMedBatch, n_med, kMedBatch);
-        else miss_batch(blk, a, sm, a.gmiss, (t - med_batches) * kMissBatch, n_miss, kMissBatch);
+        if (t >= med_batches + med2_batches + short_batches) break;
+        const unsigned long long* list = a.gmiss;
+        int dir = 1;
+        uint32_t first = (t - med_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch;
+        if (t < med_batches) { list = a.gmed; first = t * kMedBatchA; count = n_med; batch = kMedBatchA; }
+        else if (t < med_batches + med2_batches) { list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches) * kMedBatchB; count = n_med2; batch = kMedBatchB; }
+        miss_batch(blk, a, sm, list, dir, first, count, batch);
     }
     for (;;) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);

@@ -323,6 +323,7 @@ struct Engine::Impl {
         a.ovf = c->d_ovf;
         a.gmiss = c->d_gmiss;
         a.gmed = c->d_gmed;
+        a.gmed_cap = static_cast<uint32_t>(tile_bytes / 16 + 64);
         a.glong_g = c->d_glong;
         a.glong_len = c->d_glong + static_cast<size_t>(c->n_tiles_cap) * kLongPerTile;
         a.glong_cnt = c->d_glong + static_cast<size_t>(c->n_tiles_cap) * kLongPerTile * 2;

@@ -53,6 +53,7 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
     out.byte_to_id.assign(hv.byte_to_id, hv.byte_to_id + 256);
 
     // ---- merge rules ----------------------------------------------------
+    if (hv.merges.size() >= (1u << 26) - 2u) { err = "more merge rules than the kernels' rank keys can hold (2^26)"; return false; }
     RuleMap rules;
     rules.m.reserve(hv.merges.size() * 2);
     for (uint32_t k = 0; k < hv.merges.size(); ++k) {

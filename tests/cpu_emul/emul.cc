@@ -57,6 +57,8 @@ struct Emul {
 
 }  // namespace
 
+static uint32_t g_last_ctl[16];
+
 extern "C" {
 
 void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
@@ -117,7 +119,7 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     std::vector<uint32_t> stage(gstage.size(), 0xABABABAB), ovf(static_cast<size_t>(n_tiles + 1) * kTokExtra, 0xABABABAB);
     std::vector<unsigned long long> gmiss(gstage.size() / 2 + 64), gmed(gstage.size() / 16 + 64);
     std::vector<uint32_t> glong(static_cast<size_t>(n_tiles + 1) * kLongPerTile * 3, 0xABABABAB);
-    a.stage = stage.data(); a.ovf = ovf.data(); a.gmiss = gmiss.data(); a.gmed = gmed.data();
+    a.stage = stage.data(); a.ovf = ovf.data(); a.gmiss = gmiss.data(); a.gmed = gmed.data(); a.gmed_cap = static_cast<uint32_t>(gmed.size());
     a.glong_g = glong.data(); a.glong_len = glong.data() + static_cast<size_t>(n_tiles + 1) * kLongPerTile;
     a.glong_cnt = glong.data() + static_cast<size_t>(n_tiles + 1) * kLongPerTile * 2;
     a.out_tokens = out; a.out_cap = cap; a.status = status;
@@ -141,9 +143,10 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
         MissSmem* sm = new MissSmem();
         std::memset(sm, 0xCD, sizeof *sm);
         for (int i = 0; i < 256; ++i) sm->b2i[i] = a.tb.byte_to_id[i];
-        const uint32_t n_miss = ctl[CTL_NMISS], n_med = ctl[CTL_NMED], n_long = ctl[CTL_NLONG];
-        for (uint32_t first = 0; first < n_med; first += kMedBatch) miss_batch(blk, a, *sm, a.gmed, first, n_med, kMedBatch);
-        for (uint32_t first = 0; first < n_miss; first += kMissBatch) miss_batch(blk, a, *sm, a.gmiss, first, n_miss, kMissBatch);
+        const uint32_t n_miss = ctl[CTL_NMISS], n_med = ctl[CTL_NMED], n_med2 = ctl[CTL_NMED2], n_long = ctl[CTL_NLONG];
+        for (uint32_t first = 0; first < n_med; first += kMedBatchA) miss_batch(blk, a, *sm, a.gmed, 1, first, n_med, kMedBatchA);
+        for (uint32_t first = 0; first < n_med2; first += kMedBatchB) miss_batch(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, n_med2, kMedBatchB);
+        for (uint32_t first = 0; first < n_miss; first += kMissBatch) miss_batch(blk, a, *sm, a.gmiss, 1, first, n_miss, kMissBatch);
         for (uint32_t li = 0; li < n_long; ++li) long_word(blk, a, *sm, li);
         delete sm;
     }
@@ -152,9 +155,13 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
         for (uint32_t t = 0; t < n_tiles; ++t) { std::memset(sm, 0xCD, sizeof *sm); assemble_tile(blk, a, *sm, static_cast<int>(t)); }
         delete sm;
     }
+    std::memcpy(g_last_ctl, ctl, sizeof ctl);
     if (ctl[2]) return -static_cast<int64_t>(ctl[2]);
     return status[0];
 }
+
+// Control words of the last gtok_emul_encode (list sizes, error bits), for inspection.
+const uint32_t* gtok_emul_last_ctl() { return g_last_ctl; }
 
 // The library's host-side NFC (csrc/nfc_host.cc), reachable without a GPU handle.
 int64_t gtok_emul_nfc(const uint8_t* text, uint64_t len, uint8_t* out, uint64_t cap) {
