@@ -16,8 +16,10 @@ constexpr uint32_t kNoToken = 0xFFFFFFFFu;
 constexpr int kWordKeyMax = 15;        // longest pre-token the inline-key word table holds
 constexpr int kProbeLimit = 64;        // every table is built so that no probe chain is longer
 
-// Merge rule table: open addressing over buckets of two 16-byte slots (one 32-byte
-// sector per probe), linear probing over buckets; merge_mask = buckets - 1.
+// Merge rule table: two-choice (cuckoo) hashing over 16-byte slots.  A rule sits in one of
+// the two slots merge_slots() names, so a lookup is always exactly two independent 128-bit
+// loads issued together, hit or miss: one memory round trip per merge step, never a second
+// one for an unlucky lane of the warp.  At least four slots per rule.
 //   x = left id, y = right id, z = rank, w = result id;  x == kEmptyKey marks a free slot.
 // Replaces the reference's Slot64 / Slot128 pair (src/vocab.h:162-201): the
 // key and the value arrive in a single 128-bit load.
@@ -40,7 +42,7 @@ struct LongSlot { uint64_t hash; uint32_t id, off, len, pad; };
 // sorted by byte; an edge is (next_node << 8) | byte.  terminal[i] is the token id
 // ending at node i or kNoToken.  root[b] is the node after first byte b, or kNoToken.
 struct DeviceTables {
-    const MergeSlot* merge;     uint32_t merge_mask;
+    const MergeSlot* merge;     uint32_t merge_shift;     // slots = 2^(32 - merge_shift)
     const WordSlot* word;       uint32_t word_mask;
     const LongSlot* longtab;    uint32_t long_mask;
     const uint8_t* long_blob;   uint32_t long_max_len;
@@ -73,13 +75,13 @@ struct DeviceTables {
 #define GTOK_HD inline
 #endif
 
-// 32-bit arithmetic only: this sits on the critical path of every merge step.
-GTOK_HD uint32_t merge_hash(uint32_t l, uint32_t r) {
+// 32-bit arithmetic only: this sits on the critical path of every merge step.  The two slot
+// numbers are the top bits of two different multiples of one mixed word.
+GTOK_HD void merge_slots(uint32_t l, uint32_t r, uint32_t shift, uint32_t* s1, uint32_t* s2) {
     uint32_t x = l * 0x9E3779B1u ^ (r + 0x7F4A7C15u) * 0x85EBCA77u;
-    x ^= x >> 15; x *= 0x2C1B3C6Du;
-    x ^= x >> 13; x *= 0x297A2D39u;
-    x ^= x >> 16;
-    return x;
+    x ^= x >> 15;
+    *s1 = (x * 0x2C1B3C6Du) >> shift;
+    *s2 = *s1 ^ (((x * 0x297A2D39u + 0x68E31DA4u) >> shift) | 1u);      // never the same slot
 }
 GTOK_HD uint32_t word_hash(uint64_t k0, uint64_t k1) {
     uint64_t x = k0 * 0x9E3779B185EBCA87ULL + (k1 ^ (k1 >> 29)) * 0xC2B2AE3D27D4EB4FULL;

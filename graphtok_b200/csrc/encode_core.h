@@ -218,29 +218,21 @@ GTOK_DEV unsigned long long wait_state(const unsigned long long* st, int j, uint
 
 // ---- merge-rule probe ----------------------------------------------------------
 struct RankRes { uint32_t rank, res; };
-// The merge table is probed a bucket (two slots, one 32-byte sector) at a time: both
-// slots arrive together, a bucket with a free slot ends the search.
-GTOK_DEV RankRes probe_rule_from(const DeviceTables& tb, uint32_t l, uint32_t r, uint32_t bucket) {
-    for (int i = 0; i < kProbeLimit; ++i) {
-#if defined(__CUDA_ARCH__)
-        const uint4* bp = reinterpret_cast<const uint4*>(tb.merge) + 2 * bucket;
-        uint4 s0 = __ldg(bp), s1 = __ldg(bp + 1);
-        if (s0.x == l && s0.y == r) return RankRes{s0.z, s0.w};
-        if (s1.x == l && s1.y == r) return RankRes{s1.z, s1.w};
-        if (s1.x == kEmptyKey) break;
-#else
-        const MergeSlot& s0 = tb.merge[2 * bucket];
-        const MergeSlot& s1 = tb.merge[2 * bucket + 1];
-        if (s0.left == l && s0.right == r) return RankRes{s0.rank, s0.result};
-        if (s1.left == l && s1.right == r) return RankRes{s1.rank, s1.result};
-        if (s1.left == kEmptyKey) break;
-#endif
-        bucket = (bucket + 1) & tb.merge_mask;
-    }
-    return RankRes{kNoRank, 0};
-}
+// A rule is in one of its two slots or nowhere: both are loaded at once.
 GTOK_DEV RankRes probe_rule(const DeviceTables& tb, uint32_t l, uint32_t r) {
-    return probe_rule_from(tb, l, r, merge_hash(l, r) & tb.merge_mask);
+    uint32_t h1, h2;
+    merge_slots(l, r, tb.merge_shift, &h1, &h2);
+#if defined(__CUDA_ARCH__)
+    const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h1), s1 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h2);
+    if (s0.x == l && s0.y == r) return RankRes{s0.z, s0.w};
+    if (s1.x == l && s1.y == r) return RankRes{s1.z, s1.w};
+#else
+    const MergeSlot& s0 = tb.merge[h1];
+    const MergeSlot& s1 = tb.merge[h2];
+    if (s0.left == l && s0.right == r) return RankRes{s0.rank, s0.result};
+    if (s1.left == l && s1.right == r) return RankRes{s1.rank, s1.result};
+#endif
+    return RankRes{kNoRank, 0};
 }
 
 GTOK_DEV uint32_t probe_word(const DeviceTables& tb, uint64_t k0, uint64_t k1) {
@@ -303,28 +295,27 @@ GTOK_DEV uint32_t probe_long_bytes(const DeviceTables& tb, const uint8_t* bytes,
     return kNoToken;
 }
 
-// Two independent rule probes whose first loads are issued back to back, so that the
-// pair costs one memory round trip instead of two.
+// Two independent rule probes whose loads are all issued before the first compare, so that
+// the pair costs one memory round trip.
 GTOK_DEV void probe_rule2(const DeviceTables& tb, bool want1, uint32_t l1, uint32_t r1, RankRes* o1,
                           bool want2, uint32_t l2, uint32_t r2, RankRes* o2) {
     *o1 = RankRes{kNoRank, 0};
     *o2 = RankRes{kNoRank, 0};
 #if defined(__CUDA_ARCH__)
-    const uint32_t b1 = merge_hash(l1, r1) & tb.merge_mask, b2 = merge_hash(l2, r2) & tb.merge_mask;
-    const uint4* p1 = reinterpret_cast<const uint4*>(tb.merge) + 2 * b1;
-    const uint4* p2 = reinterpret_cast<const uint4*>(tb.merge) + 2 * b2;
+    uint32_t a1, a2, b1, b2;
+    merge_slots(l1, r1, tb.merge_shift, &a1, &a2);
+    merge_slots(l2, r2, tb.merge_shift, &b1, &b2);
+    const uint4* t = reinterpret_cast<const uint4*>(tb.merge);
     uint4 x0 = make_uint4(kEmptyKey, 0, 0, 0), x1 = x0, y0 = x0, y1 = x0;
-    if (want1) { x0 = __ldg(p1); x1 = __ldg(p1 + 1); }
-    if (want2) { y0 = __ldg(p2); y1 = __ldg(p2 + 1); }
+    if (want1) { x0 = __ldg(t + a1); x1 = __ldg(t + a2); }
+    if (want2) { y0 = __ldg(t + b1); y1 = __ldg(t + b2); }
     if (want1) {
         if (x0.x == l1 && x0.y == r1) *o1 = RankRes{x0.z, x0.w};
         else if (x1.x == l1 && x1.y == r1) *o1 = RankRes{x1.z, x1.w};
-        else if (x1.x != kEmptyKey) *o1 = probe_rule_from(tb, l1, r1, (b1 + 1) & tb.merge_mask);
     }
     if (want2) {
         if (y0.x == l2 && y0.y == r2) *o2 = RankRes{y0.z, y0.w};
         else if (y1.x == l2 && y1.y == r2) *o2 = RankRes{y1.z, y1.w};
-        else if (y1.x != kEmptyKey) *o2 = probe_rule_from(tb, l2, r2, (b2 + 1) & tb.merge_mask);
     }
 #else
     if (want1) *o1 = probe_rule(tb, l1, r1);

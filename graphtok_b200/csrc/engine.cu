@@ -236,7 +236,7 @@ struct Engine::Impl {
             dt.nfc_decomp_n = static_cast<uint32_t>(w.decomp.size() / 6);
             dt.nfc_comp_n = static_cast<uint32_t>(w.comp.size() / 3);
         }
-        dt.merge_mask = static_cast<uint32_t>(ht.merge.size() / 2 - 1);
+        dt.merge_shift = ht.merge_shift;
         dt.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
         dt.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
         dt.long_max_len = ht.long_max_len;

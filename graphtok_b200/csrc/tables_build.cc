@@ -62,25 +62,31 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
         // the reference's table too (src/vocab.cc:745-795).
         rules.m.emplace((static_cast<uint64_t>(m.left) << 32) | m.right, (static_cast<uint64_t>(k) << 32) | m.result);
     }
-    // Buckets of two slots; at least two buckets per rule keeps the load at or below a quarter.
-    for (uint32_t nb = pow2_at_least(static_cast<uint64_t>(hv.merges.size()) * 2);; nb <<= 1) {
-        if (nb > (1u << 29)) { err = "merge table cannot be built within its probe limit"; return false; }
-        out.merge.assign(static_cast<size_t>(nb) * 2, MergeSlot{kEmptyKey, kEmptyKey, kNoRank, 0});
-        const uint32_t mask = nb - 1;
+    // Two-choice table, at least four slots per rule.  A rule whose two slots are taken evicts
+    // one of the occupants to that one's other slot, and so on; a walk that does not end soon
+    // means a cycle, and the table is rebuilt at twice the size.
+    for (uint32_t bits = 4;; ++bits) {
+        if (bits > 30) { err = "merge table cannot be built"; return false; }
+        if ((1ull << bits) < static_cast<uint64_t>(hv.merges.size()) * 4) continue;
+        const uint32_t shift = 32 - bits;
+        out.merge.assign(size_t(1) << bits, MergeSlot{kEmptyKey, kEmptyKey, kNoRank, 0});
+        out.merge_shift = shift;
         bool ok = true;
         for (uint32_t k = 0; k < hv.merges.size() && ok; ++k) {
             const MergeRule& m = hv.merges[k];
-            uint32_t bkt = merge_hash(m.left, m.right) & mask;
-            int steps = 0;
-            for (;; bkt = (bkt + 1) & mask) {
-                MergeSlot* s = &out.merge[2 * static_cast<size_t>(bkt)];
-                bool placed = false, dup = false;
-                for (int w = 0; w < 2; ++w) {
-                    if (s[w].left == m.left && s[w].right == m.right) { dup = true; break; }   // duplicate pair: keep the first
-                    if (s[w].left == kEmptyKey) { s[w] = MergeSlot{m.left, m.right, k, m.result}; placed = true; break; }
-                }
-                if (placed || dup) break;
-                if (++steps >= kProbeLimit - 1) { ok = false; break; }
+            uint32_t s1, s2;
+            merge_slots(m.left, m.right, shift, &s1, &s2);
+            // a later duplicate of a pair is unreachable: keep the first
+            if ((out.merge[s1].left == m.left && out.merge[s1].right == m.right) || (out.merge[s2].left == m.left && out.merge[s2].right == m.right)) continue;
+            MergeSlot cur{m.left, m.right, k, m.result};
+            uint32_t at = out.merge[s1].left == kEmptyKey ? s1 : s2;
+            ok = false;
+            for (int kicks = 0; kicks < 512; ++kicks) {
+                std::swap(cur, out.merge[at]);
+                if (cur.left == kEmptyKey) { ok = true; break; }
+                // the evicted rule goes to its other slot
+                merge_slots(cur.left, cur.right, shift, &s1, &s2);
+                at = s1 == at ? s2 : s1;
             }
         }
         if (ok) break;

@@ -13,6 +13,7 @@ namespace gtok {
 
 struct HostTables {
     std::vector<MergeSlot> merge;
+    uint32_t merge_shift = 0;
     std::vector<WordSlot> word;
     std::vector<LongSlot> longtab;
     std::vector<uint8_t> long_blob;

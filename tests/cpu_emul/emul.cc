@@ -73,7 +73,7 @@ void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
     e->s2.assign(gtok_uc_stage2_init, gtok_uc_stage2_init + GTOK_UC_STAGE2_LEN);
     gtok::DeviceTables& tb = e->tb;
     const gtok::HostTables& ht = e->ht;
-    tb.merge = ht.merge.data(); tb.merge_mask = static_cast<uint32_t>(ht.merge.size() / 2 - 1);
+    tb.merge = ht.merge.data(); tb.merge_shift = ht.merge_shift;
     tb.word = ht.word.data(); tb.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
     tb.longtab = ht.longtab.data(); tb.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
     tb.long_blob = ht.long_blob.data(); tb.long_max_len = ht.long_max_len;
