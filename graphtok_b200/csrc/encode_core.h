@@ -1126,7 +1126,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 //                                   MERGE + ASSEMBLY
 // ==================================================================================
 constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch of the miss kernel
-constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB); owners fit a byte
+constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB)
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
 enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10 };
 constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
@@ -1154,13 +1154,9 @@ struct WordsSmem {
 struct MissSmem {
     alignas(16) uint32_t ws[3 * kArenaSyms];   // arena: ids, ranks, results (also the long pre-token workspace)
     uint32_t b2i[256];
-    uint32_t scan[kThreads];
-    uint32_t red[kThreads + 8];
-    uint32_t aoff[kThreads];
-    unsigned long long word[kThreads]; // this batch's entries of the global list
+    unsigned long long word[kThreads]; // this batch's entries of the global list (0 = none, or done already)
     alignas(16) uint16_t lnk[kArenaSyms];   // live-symbol chain of each pre-token (prev << 8 | next)
-    uint8_t owner[kArenaSyms];         // which of the batch's pre-tokens an arena slot belongs to
-    uint8_t rawb[kArenaSyms];          // the slot's text byte
+    uint8_t rawb[kArenaSyms];          // the pre-tokens' text bytes, max_len apart
     uint32_t ctr[8];
     unsigned long long clk_last;
 };
@@ -1185,39 +1181,56 @@ enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5
 // slots below 64.
 GTOK_DEV uint32_t rank_key(uint32_t rank, uint32_t slot) { return rank == kNoRank ? kNoRank : ((rank << 6) | slot); }
 
-GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint16_t* lnk, uint32_t len, uint32_t* out) {
-    // The stretch starts on a 4-slot boundary and is padded to a multiple of 4 with rank-less
-    // slots, so the scan reads four slots per load.  lnk[i] = prev << 8 | next (slot numbers
-    // within the stretch, 0xFF = none) keeps the live symbols chained.
-    const uint32_t len4 = (len + 3u) & ~3u;
+// The arena holds the batch's pre-tokens interleaved by groups of four slots: slot r of
+// pre-token w (of W in the batch) is element (r / 4 * W + w) * 4 + r % 4.  The threads of a
+// warp own consecutive pre-tokens, so when they all read their group g the 32 loads of 16
+// bytes are contiguous in shared memory (no bank conflict), however long each pre-token is.
+GTOK_DEV uint32_t arena_at(uint32_t w4, uint32_t stride, uint32_t r) { return (r >> 2) * stride + w4 + (r & 3u); }   // w4 = 4 * w, stride = 4 * W
+
+// ids/rk/nw/lnk are the arena's bases; the pre-token is number w4 / 4 of stride / 4; its k-th id
+// goes to the slot array by put(k, id).  Returns the number of ids.
+template <class Put>
+GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint16_t* lnk, uint32_t w4, uint32_t stride,
+                            uint32_t len, Put put) {
+    // lnk[slot] = prev << 8 | next (slot numbers within the pre-token, 0xFF = none) keeps the
+    // live symbols chained; slots past `len` in the last group hold no rank.
+    const uint32_t groups = (len + 3u) >> 2;
     for (;;) {
         uint32_t best = kNoRank;
 #if defined(__CUDA_ARCH__)
+        const uint4* rp = reinterpret_cast<const uint4*>(rk + w4);
+        const uint32_t gs = stride >> 2;
 #pragma unroll 4
-        for (uint32_t i = 0; i < len4; i += 4) {
-            const uint4 v = *reinterpret_cast<const uint4*>(rk + i);
+        for (uint32_t g = 0; g < groups; ++g) {
+            const uint4 v = rp[g * gs];
             best = min(best, min(min(v.x, v.y), min(v.z, v.w)));
         }
 #else
-        for (uint32_t i = 0; i < len4; ++i) if (rk[i] < best) best = rk[i];
+        for (uint32_t r = 0; r < groups * 4; ++r) { const uint32_t v = rk[arena_at(w4, stride, r)]; if (v < best) best = v; }
 #endif
         if (best == kNoRank) break;
-        const uint32_t bi = best & 63u;
-        const uint32_t l = lnk[bi];
+        const uint32_t bi = best & 63u, xb = arena_at(w4, stride, bi);
+        const uint32_t l = lnk[xb];
         const uint32_t j = l & 0xFFu, p = l >> 8;
-        const uint32_t k = lnk[j] & 0xFFu;
-        const uint32_t merged = nw[bi];
-        ids[bi] = merged;
-        rk[j] = kNoRank;
-        lnk[bi] = static_cast<uint16_t>((p << 8) | k);
-        if (k != 0xFFu) lnk[k] = static_cast<uint16_t>((bi << 8) | (lnk[k] & 0xFFu));
+        const uint32_t xj = arena_at(w4, stride, j);
+        const uint32_t k = lnk[xj] & 0xFFu;
+        const uint32_t merged = nw[xb];
+        ids[xb] = merged;
+        rk[xj] = kNoRank;
+        lnk[xb] = static_cast<uint16_t>((p << 8) | k);
+        const uint32_t xk = arena_at(w4, stride, k & 63u), xp = arena_at(w4, stride, p & 63u);
+        if (k != 0xFFu) lnk[xk] = static_cast<uint16_t>((bi << 8) | (lnk[xk] & 0xFFu));
         RankRes right, left;
-        probe_rule2(a.tb, k != 0xFFu, merged, k != 0xFFu ? ids[k] : 0u, &right, p != 0xFFu, p != 0xFFu ? ids[p] : 0u, merged, &left);
-        rk[bi] = rank_key(right.rank, bi); nw[bi] = right.res;
-        if (p != 0xFFu) { rk[p] = rank_key(left.rank, p); nw[p] = left.res; }
+        probe_rule2(a.tb, k != 0xFFu, merged, k != 0xFFu ? ids[xk] : 0u, &right, p != 0xFFu, p != 0xFFu ? ids[xp] : 0u, merged, &left);
+        rk[xb] = rank_key(right.rank, bi); nw[xb] = right.res;
+        if (p != 0xFFu) { rk[xp] = rank_key(left.rank, p); nw[xp] = left.res; }
     }
     uint32_t c = 0;
-    for (uint32_t i = 0; i != 0xFFu; i = lnk[i] & 0xFFu) out[c++] = ids[i];
+    for (uint32_t i = 0; i != 0xFFu;) {
+        const uint32_t x = arena_at(w4, stride, i);
+        put(c++, ids[x]);
+        i = lnk[x] & 0xFFu;
+    }
     return c;
 }
 
@@ -1598,10 +1611,6 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
     mark(11);
 }
 
-// Arena slots a pre-token of `len` symbols takes: whole groups of four (the rank scan reads a
-// group per load).
-GTOK_DEV uint32_t arena_slots(uint32_t len) { return (len + 3u) & ~3u; }
-
 // Stores the k-th id of the pre-token that starts at byte g.
 GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
     const uint32_t tile = g / kTile, t1 = (tile + 1) * kTile;
@@ -1610,16 +1619,21 @@ GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
 }
 
 // ---- kernel 3a: one batch of unknown pre-tokens (2..64 bytes), one per thread ----------
-// The owner lays its symbols out in the block's arena, all threads probe the pairs, the
-// owner merges (lowest rank first) and stores the ids.
+// All threads fetch the batch's bytes into the block's arena and probe the initial pairs, a
+// slot each; then the thread that owns a pre-token merges it (lowest rank first) and stores
+// the ids.  `max_len` is the longest pre-token of the batch's length class: batch * max_len
+// slots fit the arena.
 template <class Blk>
-GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss, uint32_t batch) {
+GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss,
+                         uint32_t batch, uint32_t max_len) {
     const DeviceTables& tb = a.tb;
     constexpr uint32_t kPending = 0xFFFFFFFDu;
     uint32_t* ids = sm.ws;
     uint32_t* rk = sm.ws + kArenaSyms;
     uint32_t* nw = sm.ws + 2 * kArenaSyms;
     const uint32_t n_here = n_miss - first < batch ? n_miss - first : batch;
+    const uint32_t stride = batch * 4u;                 // arena elements from one group of a pre-token to its next
+    const uint32_t slots = batch * max_len;
     auto mark = [&](int slot) {
         if (!a.phase_clk) return;
         blk.par([&](int tid) {
@@ -1631,90 +1645,59 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     };
     mark(-1);
     blk.par([&](int tid) {
-        if (static_cast<uint32_t>(tid) < n_here) sm.word[tid] = list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];   // dir = -1: a list that grows downwards
+        if (static_cast<uint32_t>(tid) < batch)
+            sm.word[tid] = static_cast<uint32_t>(tid) < n_here ? list[static_cast<long long>(dir) * static_cast<long long>(first + tid)] : 0ull;   // dir = -1: a list that grows downwards
     });
-    uint32_t done = 0;
-    while (done < n_here) {
-        blk.par([&](int tid) {
-            uint32_t idx = done + tid;
-            sm.scan[tid] = idx < n_here ? arena_slots(static_cast<uint32_t>(sm.word[idx] >> 32)) : 0u;
-        });
-        uint32_t tot = 0;
-        blk.excl_scan(sm.scan, &tot);
-        blk.par([&](int tid) {
-            uint32_t idx = done + tid;
-            uint32_t len = idx < n_here ? arena_slots(static_cast<uint32_t>(sm.word[idx] >> 32)) : 0u;
-            bool fits = idx < n_here && sm.scan[tid] + len <= static_cast<uint32_t>(kArenaSyms);
-            sm.red[tid] = fits ? 0xFFFFFFFFu : static_cast<uint32_t>(tid);
-        });
-        uint32_t nb = blk.reduce_min(sm.red);
-        if (nb == 0xFFFFFFFFu) nb = kThreads;
-        mark(16);
-        // owner: which slots are mine (shared memory only)
-        blk.par([&](int tid) {
-            if (static_cast<uint32_t>(tid) >= nb) return;
-            const uint32_t len = arena_slots(static_cast<uint32_t>(sm.word[done + tid] >> 32)), at = sm.scan[tid];
-            if (static_cast<uint32_t>(tid) + 1 == nb) sm.ctr[C_USED] = at + len;
-            for (uint32_t i = 0; i < len; ++i) sm.owner[at + i] = static_cast<uint8_t>(tid);
-            sm.aoff[tid] = at;
-        });
-        // all threads: fetch the bytes, one slot each, so the loads overlap
-        {
-            const uint32_t used0 = sm.ctr[C_USED];
-            blk.par([&](int tid) {
-                for (uint32_t sidx = tid; sidx < used0; sidx += kThreads) {
-                    const uint32_t w = sm.owner[sidx];
-                    const unsigned long long wv = sm.word[done + w];
-                    const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32), at = sm.scan[w];
-                    const uint32_t r = sidx - at;
-                    if (r >= len) { rk[sidx] = kNoRank; ids[sidx] = 0; sm.rawb[sidx] = 0; sm.lnk[sidx] = 0xFFFFu; continue; }   // padding
-                    const uint32_t bt = ldg(a.text + g + r);
-                    sm.rawb[sidx] = static_cast<uint8_t>(bt);
-                    ids[sidx] = sm.b2i[bt];
-                    rk[sidx] = (r + 1 < len) ? kPending : kNoRank;
-                    sm.lnk[sidx] = static_cast<uint16_t>(((r ? r - 1 : 0xFFu) << 8) | (r + 1 < len ? r + 1 : 0xFFu));
-                }
-            });
-        }
-        mark(17);
-        // owner: a pre-token of 16 bytes or more that is itself in the vocabulary (ignore_merges)
-        if (tb.ignore_merges) {
-            blk.par([&](int tid) {
-                if (static_cast<uint32_t>(tid) >= nb) return;
-                const unsigned long long wv = sm.word[done + tid];
-                const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32), at = sm.scan[tid];
-                if (len <= kWordKeyMax) return;
-                uint32_t id = probe_long_bytes(tb, sm.rawb + at, len);
-                if (id == kNoToken) return;
-                put_id(a, g, 0, id);
-                for (uint32_t i = 0; i < len; ++i) rk[at + i] = kNoRank;
-                sm.aoff[tid] = 0xFFFFFFFFu;
-            });
-        }
-        mark(18);
-        const uint32_t used = sm.ctr[C_USED];
-        blk.par([&](int tid) {
-            for (uint32_t sidx = tid; sidx < used; sidx += kThreads) {
-                if (rk[sidx] != kPending) continue;
-                RankRes r = probe_rule(tb, ids[sidx], ids[sidx + 1]);
-                rk[sidx] = rank_key(r.rank, sidx - sm.scan[sm.owner[sidx]]);
-                nw[sidx] = r.res;
-            }
-        });
-        mark(19);
-        blk.par([&](int tid) {
-            if (static_cast<uint32_t>(tid) >= nb) return;
-            const uint32_t at = sm.aoff[tid];
-            if (at == 0xFFFFFFFFu) return;
-            const unsigned long long wv = sm.word[done + tid];
+    mark(16);
+    // all threads: fetch the bytes, one slot each, so the loads overlap
+    blk.par([&](int tid) {
+        for (uint32_t x = tid; x < slots; x += kThreads) {
+            const uint32_t w = (x >> 2) % batch, r = ((x >> 2) / batch) * 4u + (x & 3u);
+            const unsigned long long wv = sm.word[w];
             const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
-            // merge in place, then the ids (the arena stretch is free again) go to their slots
-            uint32_t cnt = bpe_arena(a, ids + at, rk + at, nw + at, sm.lnk + at, len, nw + at);
-            for (uint32_t k = 0; k < cnt; ++k) put_id(a, g, k, nw[at + k]);
+            if (r >= ((len + 3u) & ~3u)) continue;                  // beyond the pre-token's last group: never read
+            if (r >= len) { rk[x] = kNoRank; continue; }            // padding of the last group
+            const uint32_t bt = ldg(a.text + g + r);
+            sm.rawb[w * max_len + r] = static_cast<uint8_t>(bt);
+            ids[x] = sm.b2i[bt];
+            rk[x] = (r + 1 < len) ? kPending : kNoRank;
+            sm.lnk[x] = static_cast<uint16_t>(((r ? r - 1 : 0xFFu) << 8) | (r + 1 < len ? r + 1 : 0xFFu));
+        }
+    });
+    mark(17);
+    // owner: a pre-token of 16 bytes or more that is itself in the vocabulary (ignore_merges)
+    if (tb.ignore_merges && max_len > static_cast<uint32_t>(kWordKeyMax)) {
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= n_here) return;
+            const unsigned long long wv = sm.word[tid];
+            const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
+            if (len <= kWordKeyMax) return;
+            uint32_t id = probe_long_bytes(tb, sm.rawb + tid * max_len, len);
+            if (id == kNoToken) return;
+            put_id(a, g, 0, id);
+            sm.word[tid] = 0ull;                                    // done
         });
-        mark(20);
-        done += nb;
     }
+    mark(18);
+    blk.par([&](int tid) {
+        for (uint32_t x = tid; x < slots; x += kThreads) {
+            const uint32_t w = (x >> 2) % batch, r = ((x >> 2) / batch) * 4u + (x & 3u);
+            const uint32_t len = static_cast<uint32_t>(sm.word[w] >> 32);
+            if (r + 1 >= len || rk[x] != kPending) continue;
+            RankRes q = probe_rule(tb, ids[x], ids[arena_at(4u * w, stride, r + 1)]);
+            rk[x] = rank_key(q.rank, r);
+            nw[x] = q.res;
+        }
+    });
+    mark(19);
+    blk.par([&](int tid) {
+        if (static_cast<uint32_t>(tid) >= n_here) return;
+        const unsigned long long wv = sm.word[tid];
+        const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
+        if (len == 0) return;
+        bpe_arena(a, ids, rk, nw, sm.lnk, 4u * tid, stride, len, [&](uint32_t k, uint32_t id) { put_id(a, g, k, id); });
+    });
+    mark(20);
 }
 
 // ---- kernel 3b: one pre-token longer than 64 bytes, by the whole block ------------------

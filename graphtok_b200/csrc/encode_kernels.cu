@@ -165,10 +165,12 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
         if (t >= med_batches + med2_batches + short_batches) break;
         const unsigned long long* list = a.gmiss;
         int dir = 1;
-        uint32_t first = (t - med_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch;
-        if (t < med_batches) { list = a.gmed; first = t * kMedBatchA; count = n_med; batch = kMedBatchA; }
-        else if (t < med_batches + med2_batches) { list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches) * kMedBatchB; count = n_med2; batch = kMedBatchB; }
-        miss_batch(blk, a, sm, list, dir, first, count, batch);
+        uint32_t first = (t - med_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch, max_len = kShortWordMax;
+        if (t < med_batches) { list = a.gmed; first = t * kMedBatchA; count = n_med; batch = kMedBatchA; max_len = kMedWordMax; }
+        else if (t < med_batches + med2_batches) {
+            list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches) * kMedBatchB; count = n_med2; batch = kMedBatchB; max_len = kMedSplit;
+        }
+        miss_batch(blk, a, sm, list, dir, first, count, batch, max_len);
     }
     for (;;) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);
@@ -294,11 +296,11 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
 cudaError_t configure_kernels() {
     cudaError_t e = cudaFuncSetAttribute(words_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(WordsSmem)));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(miss_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(MissSmem)));
-    // The kernels live on shared memory, not L1: ask for the largest carve-out so that as
-    // many blocks as the register file allows are resident.
+    // These two live on shared memory, not L1: ask for the largest carve-out so that as many
+    // blocks as the register file allows are resident.  (The pre-tokenization kernel reads its
+    // class tables through L1 and is better off with the default split.)
     if (e == cudaSuccess) e = cudaFuncSetAttribute(words_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(miss_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     return e;
 }
 
