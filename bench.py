@@ -67,9 +67,20 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                                         stdout=open(self.path, "w", buffering=1), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+
+    def wait_first_sample(self, timeout_s=8.0):
+        """nvidia-smi takes a moment to start: block until its first line is there."""
+        t0 = time.perf_counter()
+        while self.proc and time.perf_counter() - t0 < timeout_s:
+            try:
+                if os.path.getsize(self.path) > 0:
+                    return
+            except OSError:
+                return
+            time.sleep(0.05)
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
@@ -111,6 +122,37 @@ def workload(rank):
     vocab, tcfg, seed, nbytes = synth.DOCS[1]
     doc = synth.text(tcfg, seed + 1000 * rank, nbytes)
     return path, doc
+
+
+def prompt_latency(g, path, want_tokens=131072, reps=40):
+    """p50/p90 of gtok_encode (host buffers in and out) on the prefix of the adversarial long-context
+    document (configuration 4: base64 blocks, 1-64 KB character repeats, long digit strings, ordinary
+    text) that encodes to about 128k tokens."""
+    from graphtok_b200 import synth
+    _, long_doc = synth.config_doc(4)
+    lo, hi = 1 << 16, min(len(long_doc), 4 << 20)
+    out = np.empty(hi + 16, dtype=np.uint32)
+
+    def count(nb):
+        b = long_doc[:nb]
+        return g.lib.gtok_encode(g.handle, b, len(b), out.ctypes.data, out.size)
+
+    while hi - lo > 4096:                      # shortest prefix with at least want_tokens ids
+        mid = (lo + hi) // 2
+        if count(mid) >= want_tokens:
+            hi = mid
+        else:
+            lo = mid
+    prompt = long_doc[:hi]
+    n_tok = count(len(prompt))
+    ts = []
+    for _ in range(reps):
+        t = time.perf_counter()
+        g.lib.gtok_encode(g.handle, prompt, len(prompt), out.ctypes.data, out.size)
+        ts.append(time.perf_counter() - t)
+    ts.sort()
+    return {"p50_ms": ts[len(ts) // 2] * 1e3, "p90_ms": ts[int(len(ts) * 0.9)] * 1e3, "tokens": int(n_tok), "bytes": len(prompt),
+            "what": "gtok_encode with host buffers, prefix of the configuration-4 document (Llama-3-shaped vocabulary)"}
 
 
 def cpu_encoder(path):
@@ -167,6 +209,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="gtok", choices=["gtok", "reference"])
+    ap.add_argument("--quick", action="store_true", help="skip the CPU baseline and the prompt-latency section (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "gtok" else args.warmup
 
@@ -203,12 +246,13 @@ def main():
 
     # ---- device-resident throughput ------------------------------------
     g.stage(doc)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         flush.zero_()
         torch.cuda.synchronize()
         n_tok, _ = g.replay()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.wait_first_sample()
     barrier()
     dev_ms = []
     wall0 = time.perf_counter()
@@ -241,6 +285,11 @@ def main():
     barrier()
     e2e_s = (time.perf_counter() - t0) / args.steps
     clocks = sampler.stop()
+
+    # ---- latency of a 128k-token prompt (rank 0 of a 1-GPU run only) -------------
+    latency = None
+    if world == 1 and not args.quick:
+        latency = prompt_latency(g, path)
 
     # ---- reduce over ranks ---------------------------------------------------
     stats = torch.tensor([step_ms, e2e_s * 1e3, float(n_bytes), float(n_tok)] + kern_ms, dtype=torch.float64, device="cuda")
@@ -278,10 +327,14 @@ def main():
         }
         # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures of
         # this workload summarised under profiles/*_kernel_config1.md
-        traffic_of = {"pretok_kernel": 4.76e6 + 8.35e6, "words_kernel": 11.43e6, "miss_kernel": 13.79e6 + 0.14e6, "assemble_kernel": 18.39e6}
+        # (the pre-tokenization kernel's figure includes 43.5 MB of write-back that is not its own: it is the
+        # first kernel after the 256 MB L2 flush and the flush's dirty lines leave L2 while it runs)
+        traffic_of = {"pretok_kernel": 6.41e6 + 43.49e6, "words_kernel": 11.73e6, "miss_kernel": 13.79e6 + 0.15e6, "assemble_kernel": 18.39e6}
         dom = int(np.argmax(kern_ms))
         algo = algo_of[names[dom]]
         achieved = algo / (kern_ms[dom] * 1e-3) / 1e9
+        per_kernel = {k: {"ms": ms, "algorithmic_bytes": algo_of[k], "achieved_gbs": algo_of[k] / (ms * 1e-3) / 1e9,
+                          "frac": algo_of[k] / (ms * 1e-3) / 1e9 / peak, "dram_traffic": traffic_of[k]} for k, ms in zip(names, kern_ms)}
         whole = (n_bytes + 4.0 * n_tok + tm + tw + to) / (step_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": tot_bytes / (step_ms * 1e-3) / 1e6, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -294,15 +347,19 @@ def main():
                     "ms_per_step": e2e_ms},
             "gpu_launches": 4 * args.steps * world,
             "kernels_ms": dict(zip(names, kern_ms)),
+            "kernels_roofline": per_kernel,
             "roofline": {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind, "traffic": traffic_of[names[dom]], "algorithmic_bytes": algo,
                          "whole_replay": {"achieved": whole, "frac": whole / peak}},
             "clocks": clocks,
+            "latency_128k_prompt": latency,
             "wall_s_timed_region": wall,
             "global_token_offsets": [int(x) for x in offsets],
         }
         # CPU baseline on this box's host cores (reported, not a target).
         try:
+            if args.quick:
+                raise RuntimeError("skipped (--quick)")
             enc, kind = cpu_encoder(path)
             best, runs, cpu_tok = time_cpu(enc, doc)
             line["cpu_baseline"] = {"value": n_bytes / best / 1e6, "unit": UNIT, "cores": 1, "kind": kind,
