@@ -515,11 +515,44 @@ GTOK_DEV bool no_docstart_in16(const EncodeArgs& a, int q) {    // q..q+15 withi
     if (!a.docmask) return true;
     return ((ldg(a.docmask + (q >> 5)) >> (q & 31)) & 0xFFFFu) == 0;
 }
+// True when the 128 bytes at q (q % 128 == 0) repeat one 4-byte pattern whose bytes are all x
+// or y (CR/LF stretches: x = 0x0A, y = 0x0D; spaces: x = y = 0x20) and none of them opens a
+// document.  The eight loads are independent and the test is two operations per word, so a long
+// run is walked at about one memory round trip per 128 bytes.  (A stretch that mixes its two
+// bytes irregularly is not recognised here and is walked 16 bytes at a time.)
+GTOK_DEV bool run_of_128(const EncodeArgs& a, int q, uint32_t x, uint32_t y) {
+    if (a.docmask) {
+        const uint32_t* dm = a.docmask + (q >> 5);
+        if (ldg(dm) | ldg(dm + 1) | ldg(dm + 2) | ldg(dm + 3)) return false;
+    }
+    uint32_t all_and = 0xFFFFFFFFu, all_or = 0;
+#if defined(__CUDA_ARCH__)
+    const uint4* p = reinterpret_cast<const uint4*>(a.text + q);
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = __ldg(p + k);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        all_and &= v[k].x & v[k].y & v[k].z & v[k].w;
+        all_or |= v[k].x | v[k].y | v[k].z | v[k].w;
+    }
+#else
+    for (int k = 0; k < 32; ++k) {
+        const uint8_t* t = a.text + q + 4 * k;
+        const uint32_t w4 = static_cast<uint32_t>(t[0]) | (static_cast<uint32_t>(t[1]) << 8) | (static_cast<uint32_t>(t[2]) << 16) | (static_cast<uint32_t>(t[3]) << 24);
+        all_and &= w4;
+        all_or |= w4;
+    }
+#endif
+    if (all_and != all_or) return false;               // the 32 words are not all the same
+    return all_bytes_in(all_and, x, y);
+}
 GTOK_DEV int skip_back_newlines(const Win& w, int q) {
     const EncodeArgs& a = *w.a;
     if (a.tb.added_ws) return q;
     for (;;) {
         if (q < 0) return q;
+        if ((q & 127) == 127 && q >= 255 && run_of_128(a, q - 127, 0x0Au, 0x0Du)) { q -= 128; continue; }
         if ((q & 15) == 15 && q >= 31 && no_docstart_in16(a, q - 15)) {
             const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + q - 15);
             uint32_t v0 = ldg(p4), v1 = ldg(p4 + 1), v2 = ldg(p4 + 2), v3 = ldg(p4 + 3);
@@ -538,6 +571,7 @@ GTOK_DEV int skip_forward_spaces(const Win& w, int r) {
     if (a.tb.added_ws) return r;
     for (;;) {
         if (r >= w.n) return -1;
+        if ((r & 127) == 0 && r > 0 && r + 128 <= w.n && run_of_128(a, r, 0x20u, 0x20u)) { r += 128; continue; }
         if ((r & 15) == 0 && r + 16 <= w.n && no_docstart_in16(a, r)) {
             const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + r);
             if (ldg(p4) == 0x20202020u && ldg(p4 + 1) == 0x20202020u && ldg(p4 + 2) == 0x20202020u && ldg(p4 + 3) == 0x20202020u) { r += 16; continue; }
@@ -652,8 +686,14 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
         // token ( ?[^\s\p{L}\p{N}]+[\r\n]*), the whitespace run starts here.
         int q = q1;
         for (;;) {
-            if (q < w.vlo) q = skip_back_newlines(w, q);      // long runs: raw bytes, four at a time
+            if (q < w.vlo) q = skip_back_newlines(w, q);      // long runs: raw bytes, 128 or 16 at a time
             if (q < 0) break;
+            {
+                // inside the window: a 16-byte chunk of nothing but newline bytes of this document, from the bit planes
+                const int i = q - w.lo;
+                if ((i & 15) == 15 && q - 15 >= w.vlo && q < w.vhi && w.sm->plane[PL_CRLF][i >> 4] == 0xFFFFu &&
+                    ((w.sm->dsw[(i - 15) >> 5] >> ((i - 15) & 31)) & 0xFFFFu) == 0) { q -= 16; continue; }
+            }
             uint8_t aq = attr_at(w, q);
             if (!((aq & A_CLS) == A_S && (aq & A_CRLF))) { if ((aq & A_CLS) == A_O) return true; break; }
             if (aq & A_DOC) break;
@@ -666,6 +706,14 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
         for (;;) {
             r = next_lead(w, r);
             if (r < 0) return true;
+            for (;;) {
+                // inside the window: 16-byte chunks of plain (non-newline) one-byte whitespace of this document
+                const int i = r - w.lo;
+                if ((i & 15) != 0 || r < w.vlo || r + 16 > w.vhi || r + 16 >= w.n) break;
+                const uint32_t ws = w.sm->plane[PL_S][i >> 4] & ~static_cast<uint32_t>(w.sm->plane[PL_CRLF][i >> 4]);
+                if (ws != 0xFFFFu || ((w.sm->dsw[i >> 5] >> (i & 31)) & 0xFFFFu) != 0) break;
+                r += 16;
+            }
             if (r >= w.vhi) { r = skip_forward_spaces(w, r); if (r < 0) return true; }
             uint8_t ar = attr_at(w, r);
             if ((ar & A_CLS) != A_S) return true;
@@ -1700,6 +1748,120 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     mark(20);
 }
 
+// ---- run-length path for long pre-tokens made of a few byte runs ------------------------
+// A very long pre-token is, in practice, a run of one character (spaces, newlines, dashes,
+// '=' ...) or a few such runs.  Its symbol sequence is kept as (symbol, count) runs and a
+// round applies every occurrence of the lowest-rank pair at once: inside a run s^k the
+// pair (s, s) merges into t^(k/2) plus a left-over s, leftmost pairs first, and a pair
+// (l, r) across two runs takes one symbol from each.  For a vocabulary with monotone ranks
+// this is what the greedy loop does, one merge at a time (same argument as in team_bpe).
+// The number of runs stays tiny, so a round is one parallel batch of probes plus a few
+// hundred instructions by one thread, instead of passes over tens of thousands of symbols.
+// Returns false (nothing written) when the pre-token has too many runs, now or later.
+constexpr int kRleMax = 64;
+
+template <class Blk>
+GTOK_DEV bool rle_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li, uint32_t g, uint32_t len) {
+    uint32_t* w = sm.ws;
+    uint32_t* s_cnt = w;                      // [kThreads] scan scratch
+    uint32_t* sym = w + kThreads;             // run symbols, counts, and their rebuilt copies
+    uint32_t* cnt = sym + (kRleMax + 2);
+    uint32_t* sym2 = cnt + (kRleMax + 2);
+    uint32_t* cnt2 = sym2 + (kRleMax + 2);
+    uint32_t* r_self = cnt2 + (kRleMax + 2);  // rank / result of (s_i, s_i) and of (s_i, s_i+1)
+    uint32_t* t_self = r_self + (kRleMax + 2);
+    uint32_t* r_next = t_self + (kRleMax + 2);
+    uint32_t* t_next = r_next + (kRleMax + 2);
+    uint32_t* offs = t_next + (kRleMax + 2);
+    const uint32_t per = (len + kThreads - 1) / kThreads;
+    // ---- byte runs ----
+    blk.par([&](int tid) {
+        const uint32_t lo = tid * per, hi = lo + per < len ? lo + per : len;
+        uint32_t c = 0;
+        for (uint32_t i = lo; i < hi; ++i) c += (i == 0 || ldg(a.text + g + i) != ldg(a.text + g + i - 1)) ? 1u : 0u;
+        s_cnt[tid] = c;
+    });
+    uint32_t n_runs = 0;
+    blk.excl_scan(s_cnt, &n_runs);
+    if (n_runs > static_cast<uint32_t>(kRleMax)) return false;
+    blk.par([&](int tid) {
+        const uint32_t lo = tid * per, hi = lo + per < len ? lo + per : len;
+        uint32_t at = s_cnt[tid];
+        for (uint32_t i = lo; i < hi; ++i) {
+            const uint32_t b = ldg(a.text + g + i);
+            if (i == 0 || b != ldg(a.text + g + i - 1)) { sym[at] = sm.b2i[b]; offs[at] = i; ++at; }
+        }
+    });
+    blk.par([&](int tid) {
+        if (static_cast<uint32_t>(tid) < n_runs) cnt[tid] = (static_cast<uint32_t>(tid) + 1 < n_runs ? offs[tid + 1] : len) - offs[tid];
+        if (tid == 0) { sm.ctr[C_TMP] = n_runs; sm.ctr[C_TMP2] = 0; }
+    });
+    // ---- rounds ----
+    for (;;) {
+        const uint32_t R = sm.ctr[C_TMP];
+        blk.par([&](int tid) {
+            const uint32_t i = static_cast<uint32_t>(tid) >> 1;
+            if (i >= R) return;
+            if (!(tid & 1)) {
+                RankRes q{kNoRank, 0};
+                if (cnt[i] >= 2) q = probe_rule(a.tb, sym[i], sym[i]);
+                r_self[i] = q.rank; t_self[i] = q.res;
+            } else {
+                RankRes q{kNoRank, 0};
+                if (i + 1 < R) q = probe_rule(a.tb, sym[i], sym[i + 1]);
+                r_next[i] = q.rank; t_next[i] = q.res;
+            }
+        });
+        blk.par([&](int tid) {
+            if (tid != 0) return;
+            uint32_t m = kNoRank, l = 0, r = 0, t = 0;
+            for (uint32_t i = 0; i < R; ++i) {
+                if (r_self[i] < m) { m = r_self[i]; l = r = sym[i]; t = t_self[i]; }
+                if (r_next[i] < m) { m = r_next[i]; l = sym[i]; r = sym[i + 1]; t = t_next[i]; }
+            }
+            if (m == kNoRank) { sm.ctr[C_TMP2] = 1; return; }            // finished
+            uint32_t R2 = 0;
+            bool over = false;
+            auto emit = [&](uint32_t s, uint32_t c) {
+                if (c == 0) return;
+                if (R2 && sym2[R2 - 1] == s) { cnt2[R2 - 1] += c; return; }
+                if (R2 >= static_cast<uint32_t>(kRleMax)) { over = true; return; }
+                sym2[R2] = s; cnt2[R2] = c; ++R2;
+            };
+            for (uint32_t i = 0; i < R; ++i) {
+                const uint32_t s = sym[i], c = cnt[i];
+                if (l == r) {
+                    if (s == l && c >= 2) { emit(t, c >> 1); emit(l, c & 1u); }
+                    else emit(s, c);
+                } else if (s == l && i + 1 < R && sym[i + 1] == r && c >= 1 && cnt[i + 1] >= 1) {
+                    emit(l, c - 1); emit(t, 1); cnt[i + 1] -= 1;
+                } else emit(s, c);
+            }
+            if (over) { sm.ctr[C_TMP2] = 2; return; }
+            for (uint32_t i = 0; i < R2; ++i) { sym[i] = sym2[i]; cnt[i] = cnt2[i]; }
+            sm.ctr[C_TMP] = R2;
+        });
+        const uint32_t state = sm.ctr[C_TMP2];
+        if (state == 2) return false;
+        if (state == 1) break;
+    }
+    // ---- expand the runs into ids ----
+    const uint32_t R = sm.ctr[C_TMP];
+    blk.par([&](int tid) {
+        if (tid != 0) return;
+        uint32_t acc = 0;
+        for (uint32_t i = 0; i < R; ++i) { offs[i] = acc; acc += cnt[i]; }
+        a.glong_cnt[li] = acc;
+    });
+    blk.par([&](int tid) {
+        for (uint32_t i = 0; i < R; ++i) {
+            const uint32_t s = sym[i], c = cnt[i], o = g + offs[i];
+            for (uint32_t k = tid; k < c; k += kThreads) a.gstage[o + k] = s;
+        }
+    });
+    return true;
+}
+
 // ---- kernel 3b: one pre-token longer than 64 bytes, by the whole block ------------------
 template <class Blk>
 GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li) {
@@ -1721,6 +1883,7 @@ GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li
         blk.par([&](int tid) { if (tid == 0) { a.gstage[g] = hit; a.glong_cnt[li] = 1; } });
         return;
     }
+    if (tb.monotone && rle_word(blk, a, sm, li, g, len)) return;
     // Workspace: shared memory when the pre-token fits beside the team's own scratch,
     // else the per-byte global arrays (disjoint per pre-token).
     constexpr uint32_t kScratch = 6 * kThreads + 16;                 // team scratch + keep buffer

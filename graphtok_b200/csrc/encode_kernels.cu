@@ -99,7 +99,7 @@ struct GpuBlk {
     }
 };
 
-__global__ void __launch_bounds__(kThreads) pretok_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const EncodeArgs a) {
     __shared__ PretokSmem sm;
     __shared__ int s_tile;
     GpuBlk blk;

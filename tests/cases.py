@@ -48,6 +48,7 @@ def tile_crossers(special):
     for head in ("a", ".", "1", ""):
         out.append("lead " + head + "\n" * 9000 + "  x")
         out.append("lead " + head + "\r\n" * 4500 + " \tx")
+        out.append("lead " + head + "\n" * 9000 + " " * 9000 + "x")
     out.append("k\n" + " " * 9000 + "x")
     out.append("k\n" + " " * 9000 + "\n x")
     out.append("k\n" + " " * 9000)
