@@ -38,9 +38,12 @@ struct WordSlot { uint64_t k0, k1; uint32_t id; uint32_t pad[3]; };
 // a 64-bit hash and confirmed byte for byte against `long_blob`.
 struct LongSlot { uint64_t hash; uint32_t id, off, len, pad; };
 
-// Added-token (special-token) trie.  Node i owns edges [first[i], first[i]+count[i]),
-// sorted by byte; an edge is (next_node << 8) | byte.  terminal[i] is the token id
-// ending at node i or kNoToken.  root[b] is the node after first byte b, or kNoToken.
+// Added-token (special-token) trie, path-compressed.  root[b] is the node after first byte b,
+// or kNoToken.  On arriving at node i the bytes blob[skip[i] >> 8 ...] (skip[i] & 0xFF of them)
+// must follow in the text (a chain of single-child nodes folded into one, so that the long
+// common stems of literals like <|reserved_special_token_N|> cost one node instead of one
+// node per byte); then terminal[i] is the token id ending there or kNoToken, and the node
+// owns edges [first[i], first[i]+count[i]), sorted by byte; an edge is (next_node << 8) | byte.
 struct DeviceTables {
     const MergeSlot* merge;     uint32_t merge_shift;     // slots = 2^(32 - merge_shift)
     const WordSlot* word;       uint32_t word_mask;
@@ -54,6 +57,8 @@ struct DeviceTables {
     const uint16_t* trie_count;
     const uint32_t* trie_terminal;
     const uint32_t* trie_edges;
+    const uint32_t* trie_skip;
+    const uint8_t* trie_blob;
     uint32_t added_max_bytes;            // 0 when the vocabulary has no added tokens
     uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5
     uint32_t ignore_merges;

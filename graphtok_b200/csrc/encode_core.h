@@ -383,6 +383,14 @@ GTOK_DEV uint32_t match_literal(const EncodeArgs& a, int s, int n, GetByte byte_
     uint32_t best = 0;
     int q = s + 1;
     for (;;) {
+        // the node's skip string: bytes that must follow before the node itself is reached
+        const uint32_t sk = ldg(tb.trie_skip + node);
+        bool off_path = false;
+        for (uint32_t j = 0, len = sk & 0xFFu; j < len; ++j, ++q) {
+            if (q >= n || static_cast<uint32_t>(q - s) >= tb.added_max_bytes || (a.docmask && is_docstart_global(a, q)) ||
+                byte_at(q) != ldg(tb.trie_blob + (sk >> 8) + j)) { off_path = true; break; }
+        }
+        if (off_path) break;
         uint32_t term = ldg(tb.trie_terminal + node);
         if (term != kNoToken) { best = static_cast<uint32_t>(q - s); *id_out = term; }
         if (q >= n || static_cast<uint32_t>(q - s) >= tb.added_max_bytes) break;
@@ -885,6 +893,8 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     uint32_t id;
                     uint32_t ml = match_literal(a, p, n, byte_any, &id);
                     if (!ml) continue;
+                    // the id goes to the literal's slot at once, so that the next kernel need not walk the trie again
+                    if (a.stage && p >= t0 && p < t0 + kTile) a.stage[p] = id;
                     sm.attr[i] = static_cast<uint8_t>(A_ADDED | (sm.attr[i] & A_DOC));
                     sm.oh[i] = kOhAdded;
                     for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kWin; ++j) {
@@ -1545,10 +1555,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                 if (len && g + len > n) len = n - g;
                 if ((sm.txt[o] & 0xC0u) == 0x80u) continue;      // stray continuation bytes opening a document
                 if ((sm.am[o >> 5] >> (o & 31)) & 1u) {
-                    uint32_t id = 0;
-                    auto byte_at = [&](int q) -> uint32_t { return ldg(a.text + q); };
-                    match_literal(a, static_cast<int>(g), static_cast<int>(n), byte_at, &id);
-                    sm.tok[o] = id;
+                    sm.tok[o] = a.stage[g];                 // an added token: its id was left here when the literal was matched
                     continue;
                 }
                 if (len == 0 || len > kMedWordMax) {

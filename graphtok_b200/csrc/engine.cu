@@ -222,7 +222,8 @@ struct Engine::Impl {
             !upload(ht.byte_to_id, &dt.byte_to_id, owned, err) || !upload(s1, &dt.uc_stage1, owned, err) ||
             !upload(s2, &dt.uc_stage2, owned, err) || !upload(ht.trie_root, &dt.trie_root, owned, err) ||
             !upload(ht.trie_first, &dt.trie_first, owned, err) || !upload(ht.trie_count, &dt.trie_count, owned, err) ||
-            !upload(ht.trie_terminal, &dt.trie_terminal, owned, err) || !upload(ht.trie_edges, &dt.trie_edges, owned, err))
+            !upload(ht.trie_terminal, &dt.trie_terminal, owned, err) || !upload(ht.trie_edges, &dt.trie_edges, owned, err) ||
+            !upload(ht.trie_skip, &dt.trie_skip, owned, err) || !upload(ht.trie_blob, &dt.trie_blob, owned, err))
             return false;
         if (nfc) {
             NfcWords w;

@@ -192,15 +192,41 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
         }
         nodes[at].terminal = a.id;
     }
+    // Path compression: a node reached by an edge swallows the chain of single-child,
+    // non-terminal nodes below it as its skip string.
     out.trie_root.assign(256, kNoToken);
-    for (const auto& e : nodes[0].next) out.trie_root[e.first] = e.second;
     out.trie_first.clear(); out.trie_count.clear(); out.trie_terminal.clear(); out.trie_edges.clear();
-    for (const Node& nd : nodes) {
-        out.trie_first.push_back(static_cast<uint32_t>(out.trie_edges.size()));
-        out.trie_count.push_back(static_cast<uint16_t>(nd.next.size()));
-        out.trie_terminal.push_back(nd.terminal);
-        for (const auto& e : nd.next) out.trie_edges.push_back((e.second << 8) | e.first);
+    out.trie_skip.clear(); out.trie_blob.clear();
+    struct Pending { uint32_t plain, packed; };
+    std::vector<Pending> work;
+    auto add_packed = [&](uint32_t plain) -> uint32_t {
+        const uint32_t off = static_cast<uint32_t>(out.trie_blob.size());
+        uint32_t len = 0;
+        while (nodes[plain].terminal == kNoToken && nodes[plain].next.size() == 1) {
+            out.trie_blob.push_back(nodes[plain].next.begin()->first);
+            plain = nodes[plain].next.begin()->second;
+            ++len;
+        }
+        const uint32_t id = static_cast<uint32_t>(out.trie_skip.size());
+        out.trie_skip.push_back((off << 8) | len);          // len <= kMaxAddedBytes < 256
+        out.trie_terminal.push_back(nodes[plain].terminal);
+        out.trie_first.push_back(0);
+        out.trie_count.push_back(0);
+        work.push_back(Pending{plain, id});
+        return id;
+    };
+    for (const auto& e : nodes[0].next) out.trie_root[e.first] = add_packed(e.second);
+    for (size_t w = 0; w < work.size(); ++w) {
+        const Pending pd = work[w];
+        const Node& nd = nodes[pd.plain];
+        std::vector<uint32_t> edges;
+        for (const auto& e : nd.next) edges.push_back((add_packed(e.second) << 8) | e.first);
+        out.trie_first[pd.packed] = static_cast<uint32_t>(out.trie_edges.size());
+        out.trie_count[pd.packed] = static_cast<uint16_t>(edges.size());
+        out.trie_edges.insert(out.trie_edges.end(), edges.begin(), edges.end());
     }
+    if (out.trie_blob.empty()) out.trie_blob.push_back(0);
+    if (out.trie_skip.empty()) { out.trie_skip.push_back(0); out.trie_terminal.push_back(kNoToken); out.trie_first.push_back(0); out.trie_count.push_back(0); }
     if (out.trie_edges.empty()) out.trie_edges.push_back(0);
     return true;
 }

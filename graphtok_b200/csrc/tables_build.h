@@ -19,7 +19,8 @@ struct HostTables {
     std::vector<uint8_t> long_blob;
     uint32_t long_max_len = 0;
     std::vector<uint32_t> byte_to_id;
-    std::vector<uint32_t> trie_root, trie_first, trie_terminal, trie_edges;
+    std::vector<uint32_t> trie_root, trie_first, trie_terminal, trie_edges, trie_skip;
+    std::vector<uint8_t> trie_blob;
     std::vector<uint16_t> trie_count;
     uint32_t added_max_bytes = 0;
     uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0;

@@ -53,6 +53,12 @@ def tile_crossers(special):
     out.append("k\n" + " " * 9000 + "\n x")
     out.append("k\n" + " " * 9000)
     out.append("k\n" + " " * 5000 + "\t" + " " * 5000 + "\n\nq")
+    # long pre-tokens made of a few byte runs (run-length merge path) and of many (general path)
+    out.append("w " + "a" * 3000 + "b" * 3000 + "a" * 10 + " t")
+    out.append("w " + "=" * 700 + "-" * 65 + "=" * 2 + "~" * 9000 + " t")
+    out.append("w" + (" " * 70 + "\t" * 70) * 3 + "t")
+    out.append("w " + "ab" * 40 + " " + "abc" * 2000 + " t")
+    out.append("é" * 3000 + "日" * 2000 + "\U0001F600" * 500)
     out.append("z" * (3 * TILE + 17))
     out.append("9" * (2 * TILE + 5) + " " + "8" * 100)
     out.append((" " * (TILE + 100)) + "x")

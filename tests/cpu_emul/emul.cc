@@ -81,6 +81,7 @@ void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
     tb.uc_stage1 = e->s1.data(); tb.uc_stage2 = e->s2.data();
     tb.trie_root = ht.trie_root.data(); tb.trie_first = ht.trie_first.data(); tb.trie_count = ht.trie_count.data();
     tb.trie_terminal = ht.trie_terminal.data(); tb.trie_edges = ht.trie_edges.data();
+    tb.trie_skip = ht.trie_skip.data(); tb.trie_blob = ht.trie_blob.data();
     tb.added_max_bytes = ht.added_max_bytes; tb.family = ht.family; tb.ignore_merges = ht.ignore_merges;
     tb.monotone = ht.monotone;
     tb.added_ws = ht.added_ws;
