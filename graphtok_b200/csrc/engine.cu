@@ -624,7 +624,9 @@ Engine* Engine::create(const std::string& path, std::string& err) {
         // GTOK_COPY_THREADS = host threads that share one call's staging copies (1 = the caller alone)
         int want = 4;
         if (const char* env = std::getenv("GTOK_COPY_THREADS")) want = std::atoi(env);
-        const int hw = static_cast<int>(std::thread::hardware_concurrency());
+        int hw = static_cast<int>(std::thread::hardware_concurrency());
+        // one process per GPU (torchrun exports LOCAL_WORLD_SIZE): the host cores are shared by that many engines
+        if (const char* lws = std::getenv("LOCAL_WORLD_SIZE")) { const int k = std::atoi(lws); if (k > 1) hw /= k; }
         if (hw > 0) want = std::min(want, std::max(1, hw / 2));
         want = std::min(want, 16);
         if (want > 1) im.pool.reset(new CopyPool(want - 1));
