@@ -625,9 +625,12 @@ Engine* Engine::create(const std::string& path, std::string& err) {
         int want = 4;
         if (const char* env = std::getenv("GTOK_COPY_THREADS")) want = std::atoi(env);
         int hw = static_cast<int>(std::thread::hardware_concurrency());
-        // one process per GPU (torchrun exports LOCAL_WORLD_SIZE): the host cores are shared by that many engines
-        if (const char* lws = std::getenv("LOCAL_WORLD_SIZE")) { const int k = std::atoi(lws); if (k > 1) hw /= k; }
-        if (hw > 0) want = std::min(want, std::max(1, hw / 2));
+        if (hw > 0) {
+            // at most half the cores; with one process per GPU (torchrun exports LOCAL_WORLD_SIZE) this engine's share of them
+            int share = hw / 2;
+            if (const char* lws = std::getenv("LOCAL_WORLD_SIZE")) { const int k = std::atoi(lws); if (k > 1) share = hw / k; }
+            want = std::min(want, std::max(1, share));
+        }
         want = std::min(want, 16);
         if (want > 1) im.pool.reset(new CopyPool(want - 1));
     }
