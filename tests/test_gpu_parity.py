@@ -205,11 +205,24 @@ def test_benchmark_configurations_full_size(built, config):
     path, doc = synth.config_doc(config)
     o = oracle_lib.Oracle(path)
     b = norm(o, doc)
+    want = o.encode_normalized(b)
     g = GTok(path, max_bytes=len(b) + 4096)
     try:
-        assert np.array_equal(g.encode(b), o.encode_normalized(b))
+        assert np.array_equal(g.encode(b), want)
+        if o.needs_nfc:
+            assert np.array_equal(g.encode(doc), want)          # the raw document: the graph normalises it
     finally:
         g.close()
+    # the same with the staging copies on the calling thread alone
+    os.environ["GTOK_COPY_THREADS"] = "1"
+    try:
+        g1 = GTok(path, max_bytes=len(b) + 4096)
+        try:
+            assert np.array_equal(g1.encode(doc), want)
+        finally:
+            g1.close()
+    finally:
+        del os.environ["GTOK_COPY_THREADS"]
 
 
 def test_configuration_4_prefix_and_chunk_property(built):
