@@ -972,9 +972,14 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         // An added-token literal is its start bit plus continuation bits; those long stretches are
         // harmless to the algebra (the literal has no class, so its neighbours see "nothing").
         const uint64_t Cg = C & ~ADraw;
-        const bool messy = (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 ||
-                           (((AP << 1) | (AP << 2) | (AP << 3)) & C) != 0;
+        // (a stray continuation byte right after an apostrophe is glued to it and pushes the tail letters along)
+        const bool messy = (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 || ((AP << 1) & C) != 0;
         if (messy) unc = LEAD;
+        // An apostrophe with a continuation byte within the three bytes after it: what follows is not
+        // plain ASCII (U+017F counts as 's'), so this apostrophe and the three bytes after it, where a
+        // contraction and the letter after it would lie, are decided one by one; the word's other
+        // apostrophes stay with the algebra.
+        const uint64_t apC = AP & ((C >> 1) | (C >> 2) | (C >> 3));
         // Contractions: 's 't 'm 'd (tail 1) and 're 've 'll (tail 2), when the regex cursor can be
         // at the apostrophe (anything but punctuation or a literal space before it).  The few
         // apostrophes of a word are looked at one by one; what follows them is ASCII or the case
@@ -982,7 +987,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         uint64_t cs1 = 0, cs2 = 0;
         if (!messy && AP) {
             const bool ci = family != 0;
-            uint64_t aps = AP & LEAD & ~(pO | pSP);
+            uint64_t aps = AP & LEAD & ~(pO | pSP) & ~apC;
             while (aps) {
 #if defined(__CUDA_ARCH__)
                 const int bit = __ffsll(static_cast<long long>(aps)) - 1;
@@ -1004,7 +1009,10 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                 else if (x == 's' || x == 't' || x == 'm' || x == 'd') cs1 |= m;
             }
         }
-        if (messy) unc |= (AP | (AP << 1) | (AP << 2) | (AP << 3)) & LEAD;
+        {
+            const uint64_t x = messy ? AP : apC;
+            unc |= (x | (x << 1) | (x << 2) | (x << 3)) & LEAD;
+        }
         bnd |= AD | (DOC & C) | pNone;
         if (family == 0) {
             const uint64_t nNonS = nextcp(L | N | O);
