@@ -112,6 +112,38 @@ def test_merges_as_pairs_are_accepted(built, oracles):
         os.remove(p)
 
 
+def test_added_token_matcher_agrees_with_the_oracle(built):
+    """Added-token literals (path-compressed trie) against the oracle: literals that are prefixes of one
+    another, that share stems, of many different lengths, next to each other and at tile edges."""
+    import random
+    rng = random.Random(9)
+
+    def with_literals(lits):
+        def fn(j):
+            top = max(j["model"]["vocab"].values()) + 1
+            j["added_tokens"] = [{"id": top + i, "content": c, "single_word": False, "lstrip": False, "rstrip": False,
+                                  "normalized": False, "special": True} for i, c in enumerate(lits)]
+        return fn
+
+    # (the loader, like the reference's, refuses literals that contain a literal's first byte past their own start)
+    few = ["<|a|>", "<|ab|>", "<|a", "<|abc|>x", "[x]", "[xy", "<|reserved_7|>", "<|reserved_77|>", "\u00a7\u00e9"]
+    many = few + ["<" + "q" * k + ">" for k in range(1, 45)]
+    for fam in ("llama3", "gpt2"):
+        for lits in (few, many):
+            path = _mutate(fam, with_literals(lits))
+            try:
+                o, e = oracle_lib.Oracle(path), oracle_lib.Emul(path)
+                pool = lits + ["<|", "|>", "[", "<", "q", " word ", "x", "\n", "<|abc|", "\u00e9", "\u00a7", "7"]
+                for it in range(300):
+                    t = "".join(rng.choice(pool) for _ in range(rng.randint(1, 30)))
+                    if it % 5 == 0:
+                        t = "ab " * rng.randint(1300, 1400) + t + " tail"          # across a tile edge
+                    b = t.encode()
+                    assert np.array_equal(e.encode(b, reverse=bool(it & 1)), o.encode_normalized(b)), (fam, len(lits), t[-80:])
+            finally:
+                os.remove(path)
+
+
 def test_host_nfc_matches_unicodedata(built):
     """The library's NFC (used before the graph for Qwen2.5 vocabularies) against Python's, which
     Hugging Face's normaliser agrees with: named cases, a small-alphabet fuzz, every codepoint once."""
