@@ -138,6 +138,8 @@ def test_added_token_matcher_agrees_with_the_oracle(built):
                     t = "".join(rng.choice(pool) for _ in range(rng.randint(1, 30)))
                     if it % 5 == 0:
                         t = "ab " * rng.randint(1300, 1400) + t + " tail"          # across a tile edge
+                    if it == 7:
+                        t = "[x]" * 1500 + t + "<|a|>" * 70 + "w"                 # far more literals than a tile's list holds
                     b = t.encode()
                     assert np.array_equal(e.encode(b, reverse=bool(it & 1)), o.encode_normalized(b)), (fam, len(lits), t[-80:])
             finally:
