@@ -1202,6 +1202,7 @@ constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this 
 constexpr int kMedSplit = 32;
 constexpr int kMedBatchA = 48;                 // 33..64 bytes
 constexpr int kMedBatchB = 96;                 // 17..32 bytes
+constexpr int kMedTakeB = kThreads;            // list entries per call of that class under ignore_merges (most are whole tokens)
 
 struct WordsSmem {
     alignas(16) uint8_t txt[kTile + 64];
@@ -1221,6 +1222,7 @@ struct MissSmem {
     alignas(16) uint32_t ws[3 * kArenaSyms];   // arena: ids, ranks, results (also the long pre-token workspace)
     uint32_t b2i[256];
     unsigned long long word[kThreads]; // this batch's entries of the global list (0 = none, or done already)
+    unsigned long long cand[kThreads]; // list entries left over after the whole-token look-up
     alignas(16) uint16_t lnk[kArenaSyms];   // live-symbol chain of each pre-token (prev << 8 | next)
     uint8_t rawb[kArenaSyms];          // the pre-tokens' text bytes, max_len apart
     uint32_t ctr[8];
@@ -1688,13 +1690,17 @@ GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
 // slots fit the arena.
 template <class Blk>
 GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss,
-                         uint32_t batch, uint32_t max_len) {
+                         uint32_t batch, uint32_t max_len, uint32_t take) {
     const DeviceTables& tb = a.tb;
     constexpr uint32_t kPending = 0xFFFFFFFDu;
     uint32_t* ids = sm.ws;
     uint32_t* rk = sm.ws + kArenaSyms;
     uint32_t* nw = sm.ws + 2 * kArenaSyms;
-    const uint32_t n_here = n_miss - first < batch ? n_miss - first : batch;
+    // `take` list entries belong to this call.  take > batch: most entries are expected to be vocabulary
+    // tokens as they stand (ignore_merges), so every thread first looks one entry up as a whole, straight
+    // from the text, and only what is left enters the arena, `batch` pre-tokens at a time.
+    const uint32_t n_take = n_miss - first < take ? n_miss - first : take;
+    const bool filtered = take > batch;
     const uint32_t stride = batch * 4u;                 // arena elements from one group of a pre-token to its next
     const uint32_t slots = batch * max_len;
     auto mark = [&](int slot) {
@@ -1707,9 +1713,25 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
         });
     };
     mark(-1);
+    uint32_t n_cand = n_take;
+    if (filtered) {
+        blk.par([&](int tid) { if (tid == 0) sm.ctr[C_USED] = 0; });
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= n_take) return;
+            const unsigned long long wv = list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];
+            const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
+            const uint32_t id = probe_long(tb, a.text, g, len);
+            if (id != kNoToken) put_id(a, g, 0, id);
+            else sm.cand[shared_add(&sm.ctr[C_USED], 1u)] = wv;
+        });
+        n_cand = sm.ctr[C_USED];
+    }
+    for (uint32_t done = 0; done < n_cand; done += batch) {
+    const uint32_t n_here = n_cand - done < batch ? n_cand - done : batch;
     blk.par([&](int tid) {
         if (static_cast<uint32_t>(tid) < batch)
-            sm.word[tid] = static_cast<uint32_t>(tid) < n_here ? list[static_cast<long long>(dir) * static_cast<long long>(first + tid)] : 0ull;   // dir = -1: a list that grows downwards
+            sm.word[tid] = static_cast<uint32_t>(tid) >= n_here ? 0ull : filtered ? sm.cand[done + tid]
+                           : list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];   // dir = -1: a list that grows downwards
     });
     mark(16);
     // all threads: fetch the bytes, one slot each, so the loads overlap
@@ -1729,7 +1751,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     });
     mark(17);
     // owner: a pre-token of 16 bytes or more that is itself in the vocabulary (ignore_merges)
-    if (tb.ignore_merges && max_len > static_cast<uint32_t>(kWordKeyMax)) {
+    if (!filtered && tb.ignore_merges && max_len > static_cast<uint32_t>(kWordKeyMax)) {
         blk.par([&](int tid) {
             if (static_cast<uint32_t>(tid) >= n_here) return;
             const unsigned long long wv = sm.word[tid];
@@ -1761,6 +1783,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
         bpe_arena(a, ids, rk, nw, sm.lnk, 4u * tid, stride, len, [&](uint32_t k, uint32_t id) { put_id(a, g, k, id); });
     });
     mark(20);
+    }
 }
 
 // ---- run-length path for long pre-tokens made of a few byte runs ------------------------

@@ -152,7 +152,8 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
     __shared__ uint32_t s_pick;
     GpuBlk blk;
     const uint32_t n_miss = a.ctl[CTL_NMISS], n_med = a.ctl[CTL_NMED], n_med2 = a.ctl[CTL_NMED2], n_long = a.ctl[CTL_NLONG];
-    const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med2_batches = (n_med2 + kMedBatchB - 1) / kMedBatchB;
+    const uint32_t take_b = a.tb.ignore_merges ? kMedTakeB : kMedBatchB;      // list entries per call of the 17..32-byte class
+    const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med2_batches = (n_med2 + take_b - 1) / take_b;
     const uint32_t short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
     sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
     __syncthreads();
@@ -165,12 +166,12 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
         if (t >= med_batches + med2_batches + short_batches) break;
         const unsigned long long* list = a.gmiss;
         int dir = 1;
-        uint32_t first = (t - med_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch, max_len = kShortWordMax;
-        if (t < med_batches) { list = a.gmed; first = t * kMedBatchA; count = n_med; batch = kMedBatchA; max_len = kMedWordMax; }
+        uint32_t first = (t - med_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch, max_len = kShortWordMax, take = kMissBatch;
+        if (t < med_batches) { list = a.gmed; first = t * kMedBatchA; count = n_med; batch = kMedBatchA; max_len = kMedWordMax; take = kMedBatchA; }
         else if (t < med_batches + med2_batches) {
-            list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches) * kMedBatchB; count = n_med2; batch = kMedBatchB; max_len = kMedSplit;
+            list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches) * take_b; count = n_med2; batch = kMedBatchB; max_len = kMedSplit; take = take_b;
         }
-        miss_batch(blk, a, sm, list, dir, first, count, batch, max_len);
+        miss_batch(blk, a, sm, list, dir, first, count, batch, max_len, take);
     }
     for (;;) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);

@@ -145,9 +145,10 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
         std::memset(sm, 0xCD, sizeof *sm);
         for (int i = 0; i < 256; ++i) sm->b2i[i] = a.tb.byte_to_id[i];
         const uint32_t n_miss = ctl[CTL_NMISS], n_med = ctl[CTL_NMED], n_med2 = ctl[CTL_NMED2], n_long = ctl[CTL_NLONG];
-        for (uint32_t first = 0; first < n_med; first += kMedBatchA) miss_batch(blk, a, *sm, a.gmed, 1, first, n_med, kMedBatchA, kMedWordMax);
-        for (uint32_t first = 0; first < n_med2; first += kMedBatchB) miss_batch(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, n_med2, kMedBatchB, kMedSplit);
-        for (uint32_t first = 0; first < n_miss; first += kMissBatch) miss_batch(blk, a, *sm, a.gmiss, 1, first, n_miss, kMissBatch, kShortWordMax);
+        for (uint32_t first = 0; first < n_med; first += kMedBatchA) miss_batch(blk, a, *sm, a.gmed, 1, first, n_med, kMedBatchA, kMedWordMax, kMedBatchA);
+        const uint32_t take_b = a.tb.ignore_merges ? kMedTakeB : kMedBatchB;
+        for (uint32_t first = 0; first < n_med2; first += take_b) miss_batch(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, n_med2, kMedBatchB, kMedSplit, take_b);
+        for (uint32_t first = 0; first < n_miss; first += kMissBatch) miss_batch(blk, a, *sm, a.gmiss, 1, first, n_miss, kMissBatch, kShortWordMax, kMissBatch);
         for (uint32_t li = 0; li < n_long; ++li) long_word(blk, a, *sm, li);
         delete sm;
     }
