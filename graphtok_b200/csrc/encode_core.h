@@ -77,6 +77,7 @@ struct EncodeArgs {
     uint32_t* bmask;              // boundary bits, 1 per byte
     uint32_t* amask;              // added-token-start bits
     uint32_t* tile_nb;            // boundaries per tile
+    uint32_t* tile_tok;           // ids per tile (by the tile where their pre-token starts): set by words, added to by miss, summed by assemble
     unsigned long long* st1;      // pretok look-back state per tile
     unsigned long long* st2;      // merge look-back state per tile
     uint32_t* ctl;                // [0] pretok ticket, [1] assemble ticket, [2] error bits, [3] exit counter,
@@ -162,6 +163,13 @@ GTOK_DEV void global_or(uint32_t* p, uint32_t v) {
     atomicOr(p, v);
 #else
     *p |= v;
+#endif
+}
+GTOK_DEV void global_add(uint32_t* p, uint32_t v) {
+#if defined(__CUDA_ARCH__)
+    atomicAdd(p, v);
+#else
+    *p += v;
 #endif
 }
 GTOK_DEV unsigned long long load_state(const unsigned long long* p) {
@@ -1193,6 +1201,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 // ==================================================================================
 constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch of the miss kernel
 constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB)
+constexpr int kSumTiles = 16384;               // documents up to this many tiles (64 MiB): tile bases by direct summation
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
 enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10 };
 constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
@@ -1215,7 +1224,7 @@ struct WordsSmem {
     uint32_t lng_o[kLongPerTile], lng_len[kLongPerTile];
     uint32_t b2i[256];
     uint32_t scan[kThreads];
-    uint32_t ctr[8];
+    uint32_t ctr[12];
     unsigned long long clk_last;
 };
 struct MissSmem {
@@ -1231,12 +1240,13 @@ struct MissSmem {
 struct AsmSmem {
     alignas(16) uint32_t tok[kTile + kTokExtra];   // the tile's slots, then its overflow slots
     uint32_t scan[kThreads];
+    uint32_t sum[kThreads];
     uint32_t ex[8];
     uint32_t lref_idx[kLongPerTile], lref_at[kLongPerTile];
     uint32_t ctr[8];
     unsigned long long clk_last;
 };
-enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7, C_NMED = 5, C_BASED = 6, C_NMED2 = 4, C_BASED2 = 7 };
+enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7, C_NMED = 5, C_BASED = 6, C_NMED2 = 4, C_BASED2 = 7, C_NKNOWN = 8 };
 
 // Greedy BPE of one pre-token by a single thread (lowest rank first, leftmost among
 // equals, src/host_encode.cc:617-648).  ids/rk/nw are the pre-token's stretch of the
@@ -1515,7 +1525,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
         }
         sm.b2i[tid] = ldg(tb.byte_to_id + tid);
         for (int i = tid; i < kTile + kTokExtra; i += kThreads) sm.tok[i] = kInvalidTok;
-        if (tid < 8) sm.ctr[tid] = 0;
+        if (tid < 12) sm.ctr[tid] = 0;
     });
     mark(8);
     // ---- W1: the tile's pre-token starts as an ordered list ----
@@ -1544,6 +1554,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
     mark(9);
     // ---- W2: one table probe per pre-token, four in flight per thread ----
     blk.par([&](int tid) {
+        uint32_t known = 0;                                  // ids this thread settles here
         for (uint32_t base = tid; base < n_starts; base += kThreads * 4) {
             uint32_t wo[4], wlen[4], wh[4];
             uint64_t wk0[4], wk1[4];
@@ -1566,6 +1577,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                 if ((sm.txt[o] & 0xC0u) == 0x80u) continue;      // stray continuation bytes opening a document
                 if ((sm.am[o >> 5] >> (o & 31)) & 1u) {
                     sm.tok[o] = a.stage[g];                 // an added token: its id was left here when the literal was matched
+                    ++known;
                     continue;
                 }
                 if (len == 0 || len > kMedWordMax) {
@@ -1613,12 +1625,13 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                 id = probe_word(tb, wk0[u], wk1[u]);
 #endif
                 const uint32_t o = wo[u], len = wlen[u];
-                if (id != kNoToken) { sm.tok[o] = id; continue; }
-                if (len == 1) { sm.tok[o] = sm.b2i[sm.txt[o]]; continue; }
+                if (id != kNoToken) { sm.tok[o] = id; ++known; continue; }
+                if (len == 1) { sm.tok[o] = sm.b2i[sm.txt[o]]; ++known; continue; }
                 uint32_t slot = shared_add(&sm.ctr[C_NMISS], 1u);
                 sm.miss[slot] = o | (len << 12);
             }
         }
+        if (known) shared_add(&sm.ctr[C_NKNOWN], known);
     });
     mark(10);
     // ---- W3: hand the unknown and the long pre-tokens to the global lists; write the slots out ----
@@ -1628,6 +1641,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
         if (nl > kLongPerTile) nl = kLongPerTile;
         sm.ctr[C_NTEAM] = nl;
         const uint32_t nd = sm.ctr[C_NMED], nd2 = sm.ctr[C_NMED2];
+        a.tile_tok[tile] = sm.ctr[C_NKNOWN];            // the merge kernel adds what it settles
 #if defined(__CUDA_ARCH__)
         sm.ctr[C_BASEM] = nm ? atomicAdd(a.ctl + CTL_NMISS, nm) : 0u;
         sm.ctr[C_BASEL] = nl ? atomicAdd(a.ctl + CTL_NLONG, nl) : 0u;
@@ -1721,7 +1735,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             const unsigned long long wv = list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];
             const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
             const uint32_t id = probe_long(tb, a.text, g, len);
-            if (id != kNoToken) put_id(a, g, 0, id);
+            if (id != kNoToken) { put_id(a, g, 0, id); global_add(a.tile_tok + g / kTile, 1u); }
             else sm.cand[shared_add(&sm.ctr[C_USED], 1u)] = wv;
         });
         n_cand = sm.ctr[C_USED];
@@ -1760,6 +1774,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             uint32_t id = probe_long_bytes(tb, sm.rawb + tid * max_len, len);
             if (id == kNoToken) return;
             put_id(a, g, 0, id);
+            global_add(a.tile_tok + g / kTile, 1u);
             sm.word[tid] = 0ull;                                    // done
         });
     }
@@ -1780,7 +1795,8 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
         const unsigned long long wv = sm.word[tid];
         const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
         if (len == 0) return;
-        bpe_arena(a, ids, rk, nw, sm.lnk, 4u * tid, stride, len, [&](uint32_t k, uint32_t id) { put_id(a, g, k, id); });
+        const uint32_t cnt = bpe_arena(a, ids, rk, nw, sm.lnk, 4u * tid, stride, len, [&](uint32_t k, uint32_t id) { put_id(a, g, k, id); });
+        global_add(a.tile_tok + g / kTile, cnt);
     });
     mark(20);
     }
@@ -1890,6 +1906,7 @@ GTOK_DEV bool rle_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li,
         uint32_t acc = 0;
         for (uint32_t i = 0; i < R; ++i) { offs[i] = acc; acc += cnt[i]; }
         a.glong_cnt[li] = acc;
+        global_add(a.tile_tok + g / kTile, acc);
     });
     blk.par([&](int tid) {
         for (uint32_t i = 0; i < R; ++i) {
@@ -1918,7 +1935,7 @@ GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li
     const uint32_t len = sm.ctr[C_TMP];
     const uint32_t hit = sm.ctr[C_TMP2];
     if (hit != kNoToken) {
-        blk.par([&](int tid) { if (tid == 0) { a.gstage[g] = hit; a.glong_cnt[li] = 1; } });
+        blk.par([&](int tid) { if (tid == 0) { a.gstage[g] = hit; a.glong_cnt[li] = 1; global_add(a.tile_tok + g / kTile, 1u); } });
         return;
     }
     if (tb.monotone && rle_word(blk, a, sm, li, g, len)) return;
@@ -1939,7 +1956,7 @@ GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li
     blk.par([&](int tid) {
         if (ids != a.gstage + g)
             for (uint32_t i = tid; i < cnt; i += kThreads) a.gstage[g + i] = ids[i];
-        if (tid == 0) a.glong_cnt[li] = cnt;
+        if (tid == 0) { a.glong_cnt[li] = cnt; global_add(a.tile_tok + g / kTile, cnt); }
     });
 }
 
@@ -1996,7 +2013,21 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
     for (int t = 0; t < kTokExtra / kPer; ++t) total += sm.ex[t];
     mark(12);
     // ---- A1: tile base by decoupled look-back ----
-    const uint32_t base = blk.lookback(a.st2, tile, total, a.ctl);
+    // Every tile's total is known before this kernel starts (tile_tok), so up to kSumTiles tiles a
+    // block simply adds up the totals before its own; beyond that (the work is quadratic in the
+    // number of tiles) the totals are chained by look-back.
+    uint32_t base;
+    if (n_tiles <= static_cast<uint32_t>(kSumTiles)) {
+        blk.par([&](int tid) {
+            uint32_t acc = 0;
+            for (uint32_t j = tid; j < static_cast<uint32_t>(tile); j += kThreads) acc += ldg(a.tile_tok + j);
+            sm.sum[tid] = acc;
+        });
+        uint32_t before = 0;
+        blk.excl_scan(sm.sum, &before);
+        base = before;
+        if (ldg(a.tile_tok + tile) != total) blk.par([&](int tid) { if (tid == 0) global_or(a.ctl + CTL_ERR, kErrInternal); });   // the kernels disagree on a count
+    } else base = blk.lookback(a.st2, tile, total, a.ctl);
     mark(13);
     // ---- A2: ids to their final place ----
     blk.par([&](int tid) {

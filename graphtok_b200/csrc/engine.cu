@@ -275,7 +275,7 @@ struct Engine::Impl {
             GTOK_CUDA(cudaMemset(c->d_rawhdr, 0, hdr_words * 4));
             if (batch_mode) GTOK_CUDA(cudaMalloc(&c->d_docmask_raw, mask_words * 4));
         }
-        c->ctrl_bytes = 64 + static_cast<size_t>(c->n_tiles_cap + 1) * 24;
+        c->ctrl_bytes = 64 + static_cast<size_t>(c->n_tiles_cap + 1) * 28;     // control words, three look-back state arrays, ids per tile
         GTOK_CUDA(cudaMalloc(&c->d_ctrl, c->ctrl_bytes));
         GTOK_CUDA(cudaMemset(c->d_ctrl, 0, c->ctrl_bytes));
         GTOK_CUDA(cudaMalloc(&c->d_gstage, (tile_bytes + 64) * 4));
@@ -307,6 +307,7 @@ struct Engine::Impl {
         a.st1 = reinterpret_cast<unsigned long long*>(c->d_ctrl + 64);
         a.st2 = a.st1 + (c->n_tiles_cap + 1);
         a.st0 = a.st2 + (c->n_tiles_cap + 1);
+        a.tile_tok = reinterpret_cast<uint32_t*>(a.st0 + (c->n_tiles_cap + 1));
         a.text_cap = cap_bytes;
         if (nfc) {
             a.raw = c->d_raw;

@@ -114,7 +114,8 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
         for (uint32_t d = 0; d <= n_docs; ++d) if (doc_off[d] < n) docmask[doc_off[d] >> 5] |= 1u << (doc_off[d] & 31);
         a.doc_off = doc_off; a.docmask = docmask.data(); a.out_doc_tok = out_doc_tok;
     }
-    a.bmask = bmask.data(); a.amask = amask.data(); a.tile_nb = tile_nb.data();
+    std::vector<uint32_t> tile_tok(n_tiles + 1, 0);
+    a.bmask = bmask.data(); a.amask = amask.data(); a.tile_nb = tile_nb.data(); a.tile_tok = tile_tok.data();
     a.st1 = st1.data(); a.st2 = st2.data(); a.ctl = ctl;
     a.gstage = gstage.data(); a.gwork_rk = grk.data(); a.gwork_nw = gnw.data();
     std::vector<uint32_t> stage(gstage.size(), 0xABABABAB), ovf(static_cast<size_t>(n_tiles + 1) * kTokExtra, 0xABABABAB);
