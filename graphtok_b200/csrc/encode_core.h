@@ -77,6 +77,7 @@ struct EncodeArgs {
     uint32_t* bmask;              // boundary bits, 1 per byte
     uint32_t* amask;              // added-token-start bits
     uint32_t* tile_nb;            // boundaries per tile
+    uint32_t sum_tiles;           // documents of up to this many tiles get their tile bases by direct summation (kSumTiles; tests use 0)
     uint32_t* tile_tok;           // ids per tile (by the tile where their pre-token starts): set by words, added to by miss, summed by assemble
     unsigned long long* st1;      // pretok look-back state per tile
     unsigned long long* st2;      // merge look-back state per tile
@@ -2017,7 +2018,7 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
     // block simply adds up the totals before its own; beyond that (the work is quadratic in the
     // number of tiles) the totals are chained by look-back.
     uint32_t base;
-    if (n_tiles <= static_cast<uint32_t>(kSumTiles)) {
+    if (n_tiles <= a.sum_tiles) {
         blk.par([&](int tid) {
             uint32_t acc = 0;
             for (uint32_t j = tid; j < static_cast<uint32_t>(tile); j += kThreads) acc += ldg(a.tile_tok + j);

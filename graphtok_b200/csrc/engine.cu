@@ -308,6 +308,7 @@ struct Engine::Impl {
         a.st2 = a.st1 + (c->n_tiles_cap + 1);
         a.st0 = a.st2 + (c->n_tiles_cap + 1);
         a.tile_tok = reinterpret_cast<uint32_t*>(a.st0 + (c->n_tiles_cap + 1));
+        a.sum_tiles = kSumTiles;
         a.text_cap = cap_bytes;
         if (nfc) {
             a.raw = c->d_raw;

@@ -116,6 +116,7 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     }
     std::vector<uint32_t> tile_tok(n_tiles + 1, 0);
     a.bmask = bmask.data(); a.amask = amask.data(); a.tile_nb = tile_nb.data(); a.tile_tok = tile_tok.data();
+    a.sum_tiles = reverse ? 0u : static_cast<uint32_t>(kSumTiles);      // the reversed runs also take the look-back path of the assembly
     a.st1 = st1.data(); a.st2 = st2.data(); a.ctl = ctl;
     a.gstage = gstage.data(); a.gwork_rk = grk.data(); a.gwork_nw = gnw.data();
     std::vector<uint32_t> stage(gstage.size(), 0xABABABAB), ovf(static_cast<size_t>(n_tiles + 1) * kTokExtra, 0xABABABAB);
