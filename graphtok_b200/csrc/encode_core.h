@@ -244,8 +244,9 @@ GTOK_DEV RankRes probe_rule(const DeviceTables& tb, uint32_t l, uint32_t r) {
     return RankRes{kNoRank, 0};
 }
 
-GTOK_DEV uint32_t probe_word(const DeviceTables& tb, uint64_t k0, uint64_t k1) {
-    uint32_t h = word_hash(k0, k1) & tb.word_mask;
+// Probe chain of a key from slot h on (h = its home slot, or further along when the caller has
+// looked at the slots before).
+GTOK_DEV uint32_t probe_word_from(const DeviceTables& tb, uint64_t k0, uint64_t k1, uint32_t h) {
     for (int i = 0; i < kProbeLimit; ++i) {
 #if defined(__CUDA_ARCH__)
         const uint4* sp = reinterpret_cast<const uint4*>(tb.word + h);
@@ -262,6 +263,9 @@ GTOK_DEV uint32_t probe_word(const DeviceTables& tb, uint64_t k0, uint64_t k1) {
         h = (h + 1) & tb.word_mask;
     }
     return kNoToken;
+}
+GTOK_DEV uint32_t probe_word(const DeviceTables& tb, uint64_t k0, uint64_t k1) {
+    return probe_word_from(tb, k0, k1, word_hash(k0, k1) & tb.word_mask);
 }
 
 // Whole pre-token of 16 bytes or more, present in the vocabulary?  (ignore_merges)
@@ -1621,7 +1625,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                 const uint64_t s0 = (static_cast<uint64_t>(sa[u].y) << 32) | sa[u].x, s1 = (static_cast<uint64_t>(sa[u].w) << 32) | sa[u].z;
                 if (sb[u].x == kNoToken) id = kNoToken;
                 else if (s0 == wk0[u] && s1 == wk1[u]) id = sb[u].x;
-                else id = probe_word(tb, wk0[u], wk1[u]);
+                else id = probe_word_from(tb, wk0[u], wk1[u], (wh[u] + 1u) & tb.word_mask);     // the home slot holds another key: walk on from the next
 #else
                 id = probe_word(tb, wk0[u], wk1[u]);
 #endif

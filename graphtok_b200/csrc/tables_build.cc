@@ -109,7 +109,9 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
     }
     size_t n_short = 0;
     for (const auto& e : entries) if (e.first.size() <= static_cast<size_t>(kWordKeyMax)) ++n_short;
-    for (uint32_t cap = pow2_at_least(n_short * 4);; cap <<= 1) {
+    // eight slots per entry: one key in eight is then away from its home slot, and each of those
+    // costs its thread a further dependent load while the rest of the block waits
+    for (uint32_t cap = pow2_at_least(n_short * 8);; cap <<= 1) {
         if (cap > (1u << 28)) { err = "word table cannot be built within its probe limit"; return false; }
         out.word.assign(cap, WordSlot{0, 0, kNoToken, {0, 0, 0}});
         const uint32_t mask = cap - 1;
