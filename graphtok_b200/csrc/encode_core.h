@@ -91,6 +91,7 @@ struct EncodeArgs {
     unsigned long long* gmiss;    // pre-tokens of 2..16 bytes the whole-word table did not know: position | len << 32
     unsigned long long* gmed;     // the same for 33..64 bytes (from the front) and 17..32 bytes (from the back, downwards)
     uint32_t gmed_cap;            // entries in gmed
+    unsigned long long* gmed1;    // the same for 33..48 bytes
     uint32_t* glong_g;            // pre-tokens longer than 64 bytes: position, length (0 = not known yet), id count
     uint32_t* glong_len;
     uint32_t* glong_cnt;
@@ -1208,13 +1209,15 @@ constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch o
 constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB)
 constexpr int kSumTiles = 16384;               // documents up to this many tiles (64 MiB): tile bases by direct summation
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
-enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10 };
+enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10, CTL_NMED1 = 11 };
 constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
 // A batch lasts as long as its longest merge chain, so pre-tokens are batched by length class and
-// the classes are handed out longest first: 33..64 bytes, 17..32 bytes, then the short ones.
-// Batch sizes are such that a batch always fits the arena (48 * 64, 96 * 32 slots).
+// the classes are handed out longest first: 49..64 bytes, 33..48, 17..32, then the short ones.
+// Batch sizes are such that a batch always fits the arena (48 * 64, 64 * 48, 96 * 32 slots).
 constexpr int kMedSplit = 32;
-constexpr int kMedBatchA = 48;                 // 33..64 bytes
+constexpr int kMedSplit1 = 48;
+constexpr int kMedBatchA = 48;                 // 49..64 bytes
+constexpr int kMedBatchA1 = 64;                // 33..48 bytes
 constexpr int kMedBatchB = 96;                 // 17..32 bytes
 constexpr int kMedTakeB = kThreads;            // list entries per call of that class under ignore_merges (most are whole tokens)
 
@@ -1225,7 +1228,8 @@ struct WordsSmem {
     alignas(16) uint32_t tok[kTile + kTokExtra];
     uint16_t wl[kTile + 8];            // offsets in the tile of the pre-token starts, in order; then the end sentinel
     uint32_t miss[kTile / 2];          // offset | len << 12, up to 16 bytes
-    uint32_t med[kTile / 16];          // offset | len << 12: 33..64 bytes from the front, 17..32 bytes from the back
+    uint32_t med[kTile / 16];          // offset | len << 12: 49..64 bytes from the front, 17..32 bytes from the back
+    uint32_t med1[kTile / 32];         // offset | len << 12: 33..48 bytes
     uint32_t lng_o[kLongPerTile], lng_len[kLongPerTile];
     uint32_t b2i[256];
     uint32_t scan[kThreads];
@@ -1251,7 +1255,7 @@ struct AsmSmem {
     uint32_t ctr[8];
     unsigned long long clk_last;
 };
-enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7, C_NMED = 5, C_BASED = 6, C_NMED2 = 4, C_BASED2 = 7, C_NKNOWN = 8 };
+enum { C_NMISS = 0, C_NTEAM = 1, C_BASEM = 2, C_BASEL = 3, C_USED = 4, C_TMP = 5, C_TMP2 = 6, C_NLREF = 7, C_NMED = 5, C_BASED = 6, C_NMED2 = 4, C_BASED2 = 7, C_NKNOWN = 8, C_NMED1 = 9, C_BASED1 = 10 };
 
 // Greedy BPE of one pre-token by a single thread (lowest rank first, leftmost among
 // equals, src/host_encode.cc:617-648).  ids/rk/nw are the pre-token's stretch of the
@@ -1592,6 +1596,10 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                     continue;
                 }
                 if (len > kShortWordMax) {
+                    if (len > static_cast<uint32_t>(kMedSplit) && len <= static_cast<uint32_t>(kMedSplit1)) {
+                        sm.med1[shared_add(&sm.ctr[C_NMED1], 1u)] = o | (len << 12);
+                        continue;
+                    }
                     const bool big = len > static_cast<uint32_t>(kMedSplit);
                     const uint32_t slot = shared_add(&sm.ctr[big ? C_NMED : C_NMED2], 1u);
                     sm.med[big ? slot : kTile / 16 - 1 - slot] = o | (len << 12);
@@ -1645,23 +1653,26 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
         uint32_t nm = sm.ctr[C_NMISS], nl = sm.ctr[C_NTEAM];
         if (nl > kLongPerTile) nl = kLongPerTile;
         sm.ctr[C_NTEAM] = nl;
-        const uint32_t nd = sm.ctr[C_NMED], nd2 = sm.ctr[C_NMED2];
+        const uint32_t nd = sm.ctr[C_NMED], nd2 = sm.ctr[C_NMED2], nd1 = sm.ctr[C_NMED1];
         a.tile_tok[tile] = sm.ctr[C_NKNOWN];            // the merge kernel adds what it settles
 #if defined(__CUDA_ARCH__)
         sm.ctr[C_BASEM] = nm ? atomicAdd(a.ctl + CTL_NMISS, nm) : 0u;
         sm.ctr[C_BASEL] = nl ? atomicAdd(a.ctl + CTL_NLONG, nl) : 0u;
         sm.ctr[C_BASED] = nd ? atomicAdd(a.ctl + CTL_NMED, nd) : 0u;
         sm.ctr[C_BASED2] = nd2 ? atomicAdd(a.ctl + CTL_NMED2, nd2) : 0u;
+        sm.ctr[C_BASED1] = nd1 ? atomicAdd(a.ctl + CTL_NMED1, nd1) : 0u;
 #else
         sm.ctr[C_BASEM] = a.ctl[CTL_NMISS]; a.ctl[CTL_NMISS] += nm;
         sm.ctr[C_BASEL] = a.ctl[CTL_NLONG]; a.ctl[CTL_NLONG] += nl;
         sm.ctr[C_BASED] = a.ctl[CTL_NMED]; a.ctl[CTL_NMED] += nd;
         sm.ctr[C_BASED2] = a.ctl[CTL_NMED2]; a.ctl[CTL_NMED2] += nd2;
+        sm.ctr[C_BASED1] = a.ctl[CTL_NMED1]; a.ctl[CTL_NMED1] += nd1;
 #endif
     });
     {
         const uint32_t nm = sm.ctr[C_NMISS], nl = sm.ctr[C_NTEAM], bm0 = sm.ctr[C_BASEM], bl0 = sm.ctr[C_BASEL];
         const uint32_t nd = sm.ctr[C_NMED], bd0 = sm.ctr[C_BASED], nd2 = sm.ctr[C_NMED2], bd2 = sm.ctr[C_BASED2];
+        const uint32_t nd1 = sm.ctr[C_NMED1], bd1 = sm.ctr[C_BASED1];
         blk.par([&](int tid) {
             for (uint32_t i = tid; i < nm; i += kThreads) {
                 uint32_t mv = sm.miss[i];
@@ -1670,6 +1681,10 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
             for (uint32_t i = tid; i < nd; i += kThreads) {
                 uint32_t mv = sm.med[i];
                 a.gmed[bd0 + i] = static_cast<unsigned long long>(t0 + (mv & 0xFFFu)) | (static_cast<unsigned long long>(mv >> 12) << 32);
+            }
+            for (uint32_t i = tid; i < nd1; i += kThreads) {
+                uint32_t mv = sm.med1[i];
+                a.gmed1[bd1 + i] = static_cast<unsigned long long>(t0 + (mv & 0xFFFu)) | (static_cast<unsigned long long>(mv >> 12) << 32);
             }
             for (uint32_t i = tid; i < nd2; i += kThreads) {
                 uint32_t mv = sm.med[kTile / 16 - 1 - i];

@@ -151,9 +151,10 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
     MissSmem& sm = *reinterpret_cast<MissSmem*>(smem_raw);
     __shared__ uint32_t s_pick;
     GpuBlk blk;
-    const uint32_t n_miss = a.ctl[CTL_NMISS], n_med = a.ctl[CTL_NMED], n_med2 = a.ctl[CTL_NMED2], n_long = a.ctl[CTL_NLONG];
+    const uint32_t n_miss = a.ctl[CTL_NMISS], n_med = a.ctl[CTL_NMED], n_med1 = a.ctl[CTL_NMED1], n_med2 = a.ctl[CTL_NMED2], n_long = a.ctl[CTL_NLONG];
     const uint32_t take_b = a.tb.ignore_merges ? kMedTakeB : kMedBatchB;      // list entries per call of the 17..32-byte class
-    const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med2_batches = (n_med2 + take_b - 1) / take_b;
+    const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med1_batches = (n_med1 + kMedBatchA1 - 1) / kMedBatchA1;
+    const uint32_t med2_batches = (n_med2 + take_b - 1) / take_b;
     const uint32_t short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
     sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
     __syncthreads();
@@ -163,13 +164,14 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
         __syncthreads();
         const uint32_t t = s_pick;
         __syncthreads();
-        if (t >= med_batches + med2_batches + short_batches) break;
+        if (t >= med_batches + med1_batches + med2_batches + short_batches) break;
         const unsigned long long* list = a.gmiss;
         int dir = 1;
-        uint32_t first = (t - med_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch, max_len = kShortWordMax, take = kMissBatch;
+        uint32_t first = (t - med_batches - med1_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch, max_len = kShortWordMax, take = kMissBatch;
         if (t < med_batches) { list = a.gmed; first = t * kMedBatchA; count = n_med; batch = kMedBatchA; max_len = kMedWordMax; take = kMedBatchA; }
-        else if (t < med_batches + med2_batches) {
-            list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches) * take_b; count = n_med2; batch = kMedBatchB; max_len = kMedSplit; take = take_b;
+        else if (t < med_batches + med1_batches) { list = a.gmed1; first = (t - med_batches) * kMedBatchA1; count = n_med1; batch = kMedBatchA1; max_len = kMedSplit1; take = kMedBatchA1; }
+        else if (t < med_batches + med1_batches + med2_batches) {
+            list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches - med1_batches) * take_b; count = n_med2; batch = kMedBatchB; max_len = kMedSplit; take = take_b;
         }
         miss_batch(blk, a, sm, list, dir, first, count, batch, max_len, take);
     }

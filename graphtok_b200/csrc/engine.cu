@@ -152,6 +152,7 @@ struct Ctx {
     uint32_t *d_stage = nullptr, *d_ovf = nullptr, *d_glong = nullptr;
     unsigned long long* d_gmiss = nullptr;
     unsigned long long* d_gmed = nullptr;
+    unsigned long long* d_gmed1 = nullptr;
     uint32_t *d_out = nullptr, *d_doc_tok = nullptr;
     uint32_t *h_status = nullptr, *d_status = nullptr;
     unsigned long long* d_phase = nullptr;
@@ -180,7 +181,7 @@ struct Ctx {
         cudaFree(d_text); cudaFree(d_hdr); cudaFree(d_docmask); cudaFree(d_bmask); cudaFree(d_amask);
         cudaFree(d_tile_nb); cudaFree(d_ctrl); cudaFree(d_gstage); cudaFree(d_grk); cudaFree(d_gnw);
         cudaFree(d_out); cudaFree(d_doc_tok); cudaFree(d_phase);
-        cudaFree(d_stage); cudaFree(d_ovf); cudaFree(d_glong); cudaFree(d_gmiss); cudaFree(d_gmed);
+        cudaFree(d_stage); cudaFree(d_ovf); cudaFree(d_glong); cudaFree(d_gmiss); cudaFree(d_gmed); cudaFree(d_gmed1);
         if (h_status) cudaFreeHost(h_status);
         if (h_text) cudaFreeHost(h_text);
         if (h_hdr) cudaFreeHost(h_hdr);
@@ -285,6 +286,7 @@ struct Engine::Impl {
         GTOK_CUDA(cudaMalloc(&c->d_ovf, static_cast<size_t>(c->n_tiles_cap) * kTokExtra * 4));
         GTOK_CUDA(cudaMalloc(&c->d_gmiss, (tile_bytes / 2 + 64) * 8));
         GTOK_CUDA(cudaMalloc(&c->d_gmed, (tile_bytes / 16 + 64) * 8));
+        GTOK_CUDA(cudaMalloc(&c->d_gmed1, (tile_bytes / 32 + 64) * 8));
         GTOK_CUDA(cudaMalloc(&c->d_glong, static_cast<size_t>(c->n_tiles_cap) * kLongPerTile * 3 * 4));
         GTOK_CUDA(cudaMalloc(&c->d_out, (static_cast<size_t>(cap_bytes) + 16) * 4));
         GTOK_CUDA(cudaMalloc(&c->d_doc_tok, (static_cast<size_t>(cap_docs) + 2) * 4));
@@ -326,6 +328,7 @@ struct Engine::Impl {
         a.ovf = c->d_ovf;
         a.gmiss = c->d_gmiss;
         a.gmed = c->d_gmed;
+        a.gmed1 = c->d_gmed1;
         a.gmed_cap = static_cast<uint32_t>(tile_bytes / 16 + 64);
         a.glong_g = c->d_glong;
         a.glong_len = c->d_glong + static_cast<size_t>(c->n_tiles_cap) * kLongPerTile;

@@ -120,9 +120,9 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     a.st1 = st1.data(); a.st2 = st2.data(); a.ctl = ctl;
     a.gstage = gstage.data(); a.gwork_rk = grk.data(); a.gwork_nw = gnw.data();
     std::vector<uint32_t> stage(gstage.size(), 0xABABABAB), ovf(static_cast<size_t>(n_tiles + 1) * kTokExtra, 0xABABABAB);
-    std::vector<unsigned long long> gmiss(gstage.size() / 2 + 64), gmed(gstage.size() / 16 + 64);
+    std::vector<unsigned long long> gmiss(gstage.size() / 2 + 64), gmed(gstage.size() / 16 + 64), gmed1(gstage.size() / 32 + 64);
     std::vector<uint32_t> glong(static_cast<size_t>(n_tiles + 1) * kLongPerTile * 3, 0xABABABAB);
-    a.stage = stage.data(); a.ovf = ovf.data(); a.gmiss = gmiss.data(); a.gmed = gmed.data(); a.gmed_cap = static_cast<uint32_t>(gmed.size());
+    a.stage = stage.data(); a.ovf = ovf.data(); a.gmiss = gmiss.data(); a.gmed = gmed.data(); a.gmed_cap = static_cast<uint32_t>(gmed.size()); a.gmed1 = gmed1.data();
     a.glong_g = glong.data(); a.glong_len = glong.data() + static_cast<size_t>(n_tiles + 1) * kLongPerTile;
     a.glong_cnt = glong.data() + static_cast<size_t>(n_tiles + 1) * kLongPerTile * 2;
     a.out_tokens = out; a.out_cap = cap; a.status = status;
@@ -146,8 +146,9 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
         MissSmem* sm = new MissSmem();
         std::memset(sm, 0xCD, sizeof *sm);
         for (int i = 0; i < 256; ++i) sm->b2i[i] = a.tb.byte_to_id[i];
-        const uint32_t n_miss = ctl[CTL_NMISS], n_med = ctl[CTL_NMED], n_med2 = ctl[CTL_NMED2], n_long = ctl[CTL_NLONG];
+        const uint32_t n_miss = ctl[CTL_NMISS], n_med = ctl[CTL_NMED], n_med1 = ctl[CTL_NMED1], n_med2 = ctl[CTL_NMED2], n_long = ctl[CTL_NLONG];
         for (uint32_t first = 0; first < n_med; first += kMedBatchA) miss_batch(blk, a, *sm, a.gmed, 1, first, n_med, kMedBatchA, kMedWordMax, kMedBatchA);
+        for (uint32_t first = 0; first < n_med1; first += kMedBatchA1) miss_batch(blk, a, *sm, a.gmed1, 1, first, n_med1, kMedBatchA1, kMedSplit1, kMedBatchA1);
         const uint32_t take_b = a.tb.ignore_merges ? kMedTakeB : kMedBatchB;
         for (uint32_t first = 0; first < n_med2; first += take_b) miss_batch(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, n_med2, kMedBatchB, kMedSplit, take_b);
         for (uint32_t first = 0; first < n_miss; first += kMissBatch) miss_batch(blk, a, *sm, a.gmiss, 1, first, n_miss, kMissBatch, kShortWordMax, kMissBatch);
