@@ -327,9 +327,9 @@ def main():
         }
         # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures of
         # this workload summarised under profiles/*_kernel_config1.md
-        # (the pre-tokenization kernel's figure includes write-back that is not its own, 24.6 MB in this capture:
+        # (the pre-tokenization kernel's figure includes write-back that is not its own, 26.3 MB in this capture:
         # it is the first kernel after the 256 MB L2 flush and the flush's dirty lines leave L2 while it runs)
-        traffic_of = {"pretok_kernel": 5.21e6 + 24.65e6, "words_kernel": 11.47e6, "miss_kernel": 13.85e6 + 0.18e6, "assemble_kernel": 18.39e6}
+        traffic_of = {"pretok_kernel": 5.30e6 + 26.27e6, "words_kernel": 12.61e6, "miss_kernel": 13.89e6 + 0.21e6, "assemble_kernel": 18.39e6}
         dom = int(np.argmax(kern_ms))
         algo = algo_of[names[dom]]
         achieved = algo / (kern_ms[dom] * 1e-3) / 1e9
