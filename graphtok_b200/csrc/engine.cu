@@ -130,7 +130,7 @@ private:
     std::atomic<bool> stop_{false};
 };
 
-constexpr size_t kCopyPart = 256 << 10;      // bytes per staging step: small enough to overlap with the DMA of the one before
+constexpr size_t kCopyPart = 512 << 10;      // bytes per staging step: small enough to overlap with the DMA of the one before
 constexpr int kCopyEvents = 64;
 
 constexpr size_t kTextPad = kTile + kWin + 256;
