@@ -422,7 +422,7 @@ struct Engine::Impl {
     bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err,
                      bool normalised = false) {
         uint8_t* d_dst = nfc ? c->d_raw : c->d_text;
-        if (len && pool && len >= 4 * kCopyPart) {
+        if (len && pool && len >= 2 * kCopyPart) {
             // piece by piece: finished pieces go to the device while the rest is still being copied into pinned memory
             const int parts = static_cast<int>((len + kCopyPart - 1) / kCopyPart);
             if (part_done_n < parts) { part_done.reset(new std::atomic<uint8_t>[parts]); part_done_n = parts; }
@@ -476,7 +476,7 @@ struct Engine::Impl {
     bool copy_out(Ctx* c, uint32_t* out, size_t words, uint32_t* out_doc_tok, size_t doc_words, std::string& err) {
         if (!grow_host_out(c, words + doc_words + 2, err)) return false;
         const size_t bytes = words * 4;
-        if (pool && bytes >= 4 * kCopyPart) {
+        if (pool && bytes >= 2 * kCopyPart) {
             size_t part = kCopyPart;
             while ((bytes + part - 1) / part > static_cast<size_t>(kCopyEvents)) part *= 2;
             const int parts = static_cast<int>((bytes + part - 1) / part);
