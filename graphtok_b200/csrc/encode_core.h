@@ -1,13 +1,19 @@
-// The encode path, tile by tile: pre-tokenization (boundary bits), per-pre-token
-// BPE merging and output assembly.  Two tile programs:
+// The encode path, tile by tile (4096 bytes of text): pre-tokenization (boundary bits),
+// per-pre-token BPE merging and output assembly.  The tile programs, one per kernel:
 //
-//   pretok_tile : text bytes -> one boundary bit per byte (a set bit = a
-//                 pre-token starts here) plus one "added token starts here" bit.
-//   merge_tile  : boundary bits + text -> token ids, written straight to their
-//                 final place in the output (tile base found by a single-pass
-//                 decoupled look-back over tile totals).
+//   pretok_tile   : text bytes -> one boundary bit per byte (a set bit = a pre-token starts
+//                   here) plus one "added token starts here" bit; added-token ids go straight
+//                   to their slots.
+//   words_tile    : every pre-token of the tile against the whole-word table; known ones get
+//                   their id in the tile's slot array (one u32 per byte, id at the byte where the
+//                   pre-token starts), unknown ones go to global lists by length class.
+//   miss_batch    : a batch of unknown pre-tokens of one length class: greedy merge loop, one
+//                   thread per pre-token, over a shared-memory symbol arena.
+//   long_word     : one pre-token of more than 64 bytes, by a whole block (run-length merge for
+//                   runs of one character, round-batched merge otherwise).
+//   assemble_tile : the tile's slots -> ids at their final place in the output.
 //
-// Both are written against a small "thread block" interface (Blk):
+// All are written against a small "thread block" interface (Blk):
 //     blk.par(f)                run f(tid) for every thread, then barrier
 //     blk.excl_scan(arr,total)  in-place exclusive scan of arr[kThreads]
 //     blk.lookback(st,tile,total,ctl)  publish this tile's total, return the sum of all earlier tiles'

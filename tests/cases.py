@@ -70,7 +70,7 @@ def tile_crossers(special):
 
 def length_ladder():
     out = []
-    for n in (1, 2, 15, 16, 17, 18, 31, 32, 33, 63, 64, 65, 129, 257, 513, 1025, 1529, 1530, 1531, 2048, 2049, 4095, 4096, 4097, 9000):
+    for n in (1, 2, 15, 16, 17, 18, 31, 32, 33, 47, 48, 49, 50, 63, 64, 65, 129, 257, 513, 1025, 1529, 1530, 1531, 2048, 2049, 4095, 4096, 4097, 9000):
         out += ["a" * n, "ab" * (n // 2 + 1), ("the" * (n // 3 + 1))[:n], "x " + "q" * n + " y"]
     return out
 
