@@ -1215,7 +1215,7 @@ constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch o
 constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB)
 constexpr int kSumTiles = 16384;               // documents up to this many tiles (64 MiB): tile bases by direct summation
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
-enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10, CTL_NMED1 = 11 };
+enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10, CTL_NMED1 = 11, CTL_NFCFLAG = 12 };
 constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
 // A batch lasts as long as its longest merge chain, so pre-tokens are batched by length class and
 // the classes are handed out longest first: 49..64 bytes, 33..48, 17..32, then the short ones.

@@ -118,10 +118,40 @@ __global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const EncodeArgs a)
 // Kernel 0 (vocabularies that declare NFC): raw text -> normalised text, byte count and
 // document offsets; tiles in ticket order because a tile's place in the output is the sum of
 // the lengths of all earlier tiles.
+// Does the text need normalising at all?  Any codepoint that can make a text non-NFC raises the
+// flag.  (Launched with raw_docmask unset: document boundaries are ignored here, which can only
+// raise the flag once too often.)
+__global__ void __launch_bounds__(kThreads) nfc_check_kernel(const EncodeArgs a) {
+    const uint32_t n = a.raw_meta[0];
+    if (a.raw_meta[2]) return;                                   // the host says it is normalised already
+    const uint32_t chunks = (n + kPer - 1) / kPer;
+    uint32_t any = 0;
+    for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += gridDim.x * blockDim.x) {
+        uint32_t l, f;
+        nfc_chunk_masks(a, static_cast<long long>(c) * kPer, n, &l, &f);
+        any |= l;
+    }
+    if (__syncthreads_or(any != 0) && threadIdx.x == 0) atomicOr(a.ctl + CTL_NFCFLAG, 1u);
+}
+
+// Nothing to normalise (the usual case): the raw text and its header are the text and the header.
+__global__ void __launch_bounds__(kThreads) nfc_copy_kernel(const EncodeArgs a) {
+    if (a.ctl[CTL_NFCFLAG]) return;
+    const uint32_t n = a.raw_meta[0], n_docs = a.raw_meta[1];
+    const uint32_t quads = (n + 15) / 16;
+    const uint4* src = reinterpret_cast<const uint4*>(a.raw);
+    uint4* dst = reinterpret_cast<uint4*>(a.norm_text);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += gridDim.x * blockDim.x) dst[i] = src[i];
+    const uint32_t hdr = 4u + (a.raw_doc_off ? n_docs + 1u : 0u);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < hdr; i += gridDim.x * blockDim.x) a.norm_meta[i] = a.raw_meta[i];
+    if (blockIdx.x == 0 && threadIdx.x == 0) a.status[2] = n;
+}
+
 __global__ void __launch_bounds__(kThreads) nfc_kernel(const EncodeArgs a) {
     __shared__ NfcSmem sm;
     __shared__ int s_tile;
     GpuBlk blk;
+    if (!a.ctl[CTL_NFCFLAG]) return;                             // nothing to normalise: the copy kernel has moved the text over
     const uint32_t n = a.raw_meta[0];
     const int n_tiles = static_cast<int>((n + kTile - 1) / kTile);
     for (;;) {
@@ -324,6 +354,8 @@ void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStre
 void launch_raw_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s) {
     docmask_kernel<<<blocks, 256, 0, s>>>(a.raw_meta, a.raw_doc_off, docmask);
 }
+void launch_nfc_check(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_check_kernel<<<blocks, kThreads, 0, s>>>(a); }
+void launch_nfc_copy(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_copy_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s) { words_kernel<<<blocks, kThreads, sizeof(WordsSmem), s>>>(a); }

@@ -17,6 +17,9 @@ int assemble_blocks_per_sm();
 int nfc_blocks_per_sm();
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);
 void launch_raw_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);   // over raw_doc_off
+// check: the context's arguments with raw_docmask unset; copy and nfc: the context's own arguments
+void launch_nfc_check(const EncodeArgs& a, int blocks, cudaStream_t s);
+void launch_nfc_copy(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s);

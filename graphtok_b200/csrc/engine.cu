@@ -370,15 +370,24 @@ struct Engine::Impl {
         return true;
     }
 
-    // What precedes pre-tokenization: [raw document bits, normalisation], [document bits].
-    void launch_front(Ctx* c) {
-        if (nfc) {
-            if (c->batch) {
-                cudaMemsetAsync(c->d_docmask_raw, 0, c->mask_words * 4, c->stream);
-                launch_raw_docmask(c->args, c->d_docmask_raw, c->docmask_blocks, c->stream);
-            }
-            launch_nfc(c->args, c->nfc_blocks, c->stream);
+    // Normalisation, in three launches: look for codepoints that can make the raw text non-NFC; if
+    // there are none (the usual case) copy text and header over as they are; else normalise.  The
+    // second and third each return at once in the case that is not theirs.
+    void launch_normalise(Ctx* c) {
+        EncodeArgs chk = c->args;
+        chk.raw_docmask = nullptr;
+        const int wide = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap) * 2, sm_count * 8));
+        launch_nfc_check(chk, wide, c->stream);
+        launch_nfc_copy(c->args, wide, c->stream);
+        if (c->batch) {
+            cudaMemsetAsync(c->d_docmask_raw, 0, c->mask_words * 4, c->stream);
+            launch_raw_docmask(c->args, c->d_docmask_raw, c->docmask_blocks, c->stream);
         }
+        launch_nfc(c->args, c->nfc_blocks, c->stream);
+    }
+    // What precedes pre-tokenization: [normalisation], [document bits].
+    void launch_front(Ctx* c) {
+        if (nfc) launch_normalise(c);
         if (c->batch) {
             cudaMemsetAsync(c->d_docmask, 0, c->mask_words * 4, c->stream);
             launch_docmask(c->args, c->d_docmask, c->docmask_blocks, c->stream);
@@ -418,7 +427,7 @@ struct Engine::Impl {
     }
 
     // Host -> pinned -> device, for the text and the header.
-    // With NFC the destination is the raw buffer; `normalised` tells the kernel to copy only.
+    // With NFC the destination is the raw buffer; `normalised`: the text has been normalised on the host, the graph need not look.
     bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err,
                      bool normalised = false) {
         uint8_t* d_dst = nfc ? c->d_raw : c->d_text;

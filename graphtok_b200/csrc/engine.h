@@ -51,7 +51,7 @@ public:
     uint32_t vocab_size() const { return hv_.vocab_size; }
     std::string last_error() const { return last_error_; }
     // Number of kernel launches one replay makes (for reporting).
-    int launches_per_replay(bool batch) const { return (batch ? 5 : 4) + (hv_.nfc ? (batch ? 2 : 1) : 0); }
+    int launches_per_replay(bool batch) const { return (batch ? 5 : 4) + (hv_.nfc ? (batch ? 4 : 3) : 0); }
     void table_bytes(uint64_t* merge, uint64_t* word, uint64_t* other) const;
 
 private:
