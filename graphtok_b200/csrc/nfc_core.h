@@ -143,10 +143,33 @@ GTOK_DEV uint32_t utf8_width(uint32_t cp) { return cp < 0x80 ? 1u : cp < 0x800 ?
 // codepoint precedes the run).  Returns the length in bytes of the result and, when `out` is
 // given, writes it at out[at...] as far as it fits below `cap`.
 GTOK_DEV_NOINLINE uint32_t nfc_stretch(const EncodeArgs& a, uint32_t a0, uint32_t p, uint32_t n, uint8_t* out, uint32_t at, uint32_t cap) {
+    uint32_t cp = 0;
+    // By far the most common stretch, decided without the general machinery: an ASCII character,
+    // one combining mark of U+0300..U+036F that has no decomposition of its own, then something
+    // that needs no attention.  The pair either composes or stays as it is.
+    if (a0 + 1 == p) {
+        const int w1 = nfc_decode(a, p, n, &cp);
+        if (w1 == 2 && cp >= 0x300 && cp <= 0x36F && cp != 0x340 && cp != 0x341 && cp != 0x343 && cp != 0x344) {
+            const uint32_t q = p + 2;
+            uint32_t nx = 0;
+            const bool ends = q >= n || raw_docstart(a, q) || nfc_decode(a, q, n, &nx) == 0 || !nfc_attention(a.tb, nx);
+            if (ends) {
+                const uint32_t b0 = ldg(a.raw + a0);
+                const uint32_t m = nfc_compose(a.tb, b0, cp);
+                const uint32_t len = m ? utf8_width(m) : 3u;
+                if (out && at + len <= cap) {
+                    uint8_t* o = out + at;
+                    if (!m) { o[0] = static_cast<uint8_t>(b0); o[1] = static_cast<uint8_t>(0xC0 | (cp >> 6)); o[2] = static_cast<uint8_t>(0x80 | (cp & 0x3F)); }
+                    else if (len == 2) { o[0] = static_cast<uint8_t>(0xC0 | (m >> 6)); o[1] = static_cast<uint8_t>(0x80 | (m & 0x3F)); }
+                    else { o[0] = static_cast<uint8_t>(0xE0 | (m >> 12)); o[1] = static_cast<uint8_t>(0x80 | ((m >> 6) & 0x3F)); o[2] = static_cast<uint8_t>(0x80 | (m & 0x3F)); }
+                }
+                return len;
+            }
+        }
+    }
     NfcBuf b;
     b.n = 0;
     b.over = false;
-    uint32_t cp = 0;
     if (a0 < p) { nfc_decode(a, a0, n, &cp); nfc_push(a.tb, b, cp); }
     for (uint32_t q = p; q < n;) {
         const int w = nfc_decode(a, q, n, &cp);
