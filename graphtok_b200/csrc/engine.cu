@@ -482,9 +482,27 @@ struct Engine::Impl {
     // ids (and, for a batch, the document offsets behind them) from the device to the caller's
     // memory through the pinned buffer; large outputs part by part, so that the copy out of
     // pinned memory of one part overlaps with the DMA of the next ones.
+    // Is this host pointer page-locked memory the device can reach (cudaHostAlloc / cudaHostRegister)?
+    static bool is_pinned(const void* p) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+        return at.type == cudaMemoryTypeHost;
+    }
+
     bool copy_out(Ctx* c, uint32_t* out, size_t words, uint32_t* out_doc_tok, size_t doc_words, std::string& err) {
-        if (!grow_host_out(c, words + doc_words + 2, err)) return false;
         const size_t bytes = words * 4;
+        if (words && bytes >= kCopyPart && is_pinned(out)) {
+            // the caller's buffer is page-locked: the ids go there directly, no staging copy
+            GTOK_CUDA(cudaMemcpyAsync(out, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
+            if (doc_words) {
+                if (!grow_host_out(c, doc_words + 2, err)) return false;
+                GTOK_CUDA(cudaMemcpyAsync(c->h_out, c->d_doc_tok, doc_words * 4, cudaMemcpyDeviceToHost, c->stream));
+            }
+            GTOK_CUDA(cudaStreamSynchronize(c->stream));
+            if (doc_words) std::memcpy(out_doc_tok, c->h_out, doc_words * 4);
+            return true;
+        }
+        if (!grow_host_out(c, words + doc_words + 2, err)) return false;
         if (pool && bytes >= 2 * kCopyPart) {
             size_t part = kCopyPart;
             while ((bytes + part - 1) / part > static_cast<size_t>(kCopyEvents)) part *= 2;

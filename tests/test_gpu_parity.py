@@ -161,6 +161,25 @@ def test_encode_to_device_matches_host(gtoks, oracles):
     assert np.array_equal(buf[:n].cpu().numpy().astype(np.uint32), o.encode_normalized(text))
 
 
+def test_page_locked_output_buffer_is_written_directly(gtoks, oracles):
+    """A caller's page-locked buffer receives the ids without the staging copy: same ids as through a
+    pageable one, for a single document and for a batch (ids direct, document offsets staged)."""
+    import torch
+    g, o = gtoks["llama3"], oracles["llama3"]
+    text = ("page locked output, many ids to copy. " * 25000).encode()          # > 512 KB of ids, under the handle's 1 MiB
+    want = o.encode_normalized(text)
+    pinned = torch.zeros(len(text) + 16, dtype=torch.int32).pin_memory()
+    arr = pinned.numpy()
+    n = g.lib.gtok_encode(g.handle, text, len(text), arr.ctypes.data, arr.size)
+    assert n == len(want) and np.array_equal(arr[:n].view(np.uint32), want)
+    offs = np.array([0, 5, 5, len(text) // 2, len(text)], dtype=np.uint32)
+    docs = np.zeros(offs.size, dtype=np.uint32)
+    arr[:] = 0
+    n = g.lib.gtok_encode_batch(g.handle, text, offs.ctypes.data, offs.size - 1, arr.ctypes.data, arr.size, docs.ctypes.data)
+    want_ids, want_doc = o.encode_batch(text, offs)
+    assert n == len(want_ids) and np.array_equal(arr[:n].view(np.uint32), want_ids) and np.array_equal(docs, want_doc)
+
+
 def test_sizes_change_between_calls_on_one_handle(gtoks, oracles):
     g, o = gtoks["llama3"], oracles["llama3"]
     from graphtok_b200 import synth
