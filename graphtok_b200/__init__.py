@@ -78,6 +78,8 @@ def load_lib():
     lib.gtok_x_phase_clocks.argtypes = [vp, vp, i32]
     lib.gtok_x_token_bytes.restype = i32
     lib.gtok_x_token_bytes.argtypes = [vp, u32, vp, u32]
+    lib.gtok_x_decode.restype = ctypes.c_int64
+    lib.gtok_x_decode.argtypes = [vp, vp, u32, vp, ctypes.c_uint64, vp, vp]
     lib.gtok_x_profile.restype = i32
     lib.gtok_x_profile.argtypes = [vp, vp]
     lib.gtok_x_plan_chunks.restype = i32
@@ -189,6 +191,23 @@ class GTok:
         if n < 0:
             self._fail("gtok_x_profile", n)
         return (n,) + tuple(ms)
+
+    def decode(self, ids, out=None, want_ms=False):
+        """ids -> the bytes they spell, on the device (gtok_x_decode).  `out`: optional uint8 numpy
+        buffer to decode into (a page-locked one is written directly); returns bytes, or with
+        `want_ms` (bytes, CUDA-event ms of the decode graph)."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        need = ctypes.c_uint64(0)
+        ms = ctypes.c_float(0.0)
+        buf = out if out is not None else np.empty(16 * ids.size + 1024, dtype=np.uint8)
+        n = self.lib.gtok_x_decode(self.handle, ids.ctypes.data, ids.size, buf.ctypes.data, buf.size, ctypes.byref(need), ctypes.byref(ms))
+        if n == -2 and out is None:
+            buf = np.empty(need.value, dtype=np.uint8)
+            n = self.lib.gtok_x_decode(self.handle, ids.ctypes.data, ids.size, buf.ctypes.data, buf.size, ctypes.byref(need), ctypes.byref(ms))
+        if n < 0:
+            self._fail("gtok_x_decode", n)
+        data = buf[:n].tobytes()
+        return (data, ms.value) if want_ms else data
 
     def plan_chunks(self, data, n_parts):
         data = bytes(data)

@@ -13,6 +13,7 @@
 #include <string>
 
 #include "encode_core.h"
+#include "decode_core.h"
 #include "encode_kernels.h"
 #include "nfc_core.h"
 
@@ -337,6 +338,32 @@ cudaError_t configure_kernels() {
     return e;
 }
 
+// Decoding kernel: tiles of 2048 ids handed out in order (a tile's byte offset is the sum of
+// the earlier tiles' byte counts, found by look-back).
+__global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeArgs a) {
+    __shared__ DecodeSmem sm;
+    __shared__ int s_tile;
+    GpuBlk blk;
+    const uint32_t n = a.meta[0];
+    const int n_tiles = static_cast<int>((n + kDecIds - 1) / kDecIds);
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = static_cast<int>(atomicAdd(a.ctl + CTL_PRETOK, 1u));
+        __syncthreads();
+        const int tile = s_tile;
+        __syncthreads();
+        if (tile >= n_tiles) break;
+        decode_tile(blk, a, sm, tile);
+    }
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(a.ctl + CTL_EXIT, 1u) == gridDim.x - 1) {
+            __threadfence();
+            if (n == 0) a.status[0] = 0;
+            a.status[1] = *reinterpret_cast<volatile uint32_t*>(a.ctl + CTL_ERR);
+        }
+    }
+}
+
 static int blocks_per_sm(const void* fn, size_t smem) {
     int nb = 0;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, kThreads, smem);
@@ -346,6 +373,7 @@ int pretok_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(
 int words_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(words_kernel), sizeof(WordsSmem)); }
 int miss_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(miss_kernel), sizeof(MissSmem)); }
 int nfc_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(nfc_kernel), 0); }
+int decode_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(decode_kernel), 0); }
 int assemble_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(assemble_kernel), 0); }
 
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s) {
@@ -360,6 +388,7 @@ void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_kernel<<<
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s) { words_kernel<<<blocks, kThreads, sizeof(WordsSmem), s>>>(a); }
 void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s) { miss_kernel<<<blocks, kThreads, sizeof(MissSmem), s>>>(a); }
+void launch_decode(const DecodeArgs& a, int blocks, cudaStream_t s) { decode_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_assemble(const EncodeArgs& a, int blocks, cudaStream_t s) { assemble_kernel<<<blocks, kThreads, 0, s>>>(a); }
 
 }  // namespace gtok

@@ -5,6 +5,7 @@
 
 #include <string>
 
+#include "decode_core.h"
 #include "encode_core.h"
 
 namespace gtok {
@@ -15,6 +16,7 @@ int words_blocks_per_sm();
 int miss_blocks_per_sm();
 int assemble_blocks_per_sm();
 int nfc_blocks_per_sm();
+int decode_blocks_per_sm();
 void launch_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);
 void launch_raw_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cudaStream_t s);   // over raw_doc_off
 // check: the context's arguments with raw_docmask unset; copy and nfc: the context's own arguments
@@ -25,6 +27,7 @@ void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_assemble(const EncodeArgs& a, int blocks, cudaStream_t s);
+void launch_decode(const DecodeArgs& a, int blocks, cudaStream_t s);
 
 
 // Largest input of boundaries_noalloc(), fixed by its statically reserved working memory.

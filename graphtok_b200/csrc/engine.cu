@@ -191,6 +191,37 @@ struct Ctx {
 
 }  // namespace
 
+// Decoding context (ids -> bytes): its own stream and captured graph (control block reset ->
+// decode kernel), apart from the encode contexts, as in the reference
+// (src/tokenizer.cu:5225-5232).  Grows on demand.
+struct DecCtx {
+    uint32_t cap_ids = 0, n_tiles_cap = 0;
+    size_t cap_bytes = 0;
+    uint32_t* d_in = nullptr;             // [0] = number of ids, ids from word 4 on
+    uint8_t* d_out = nullptr;
+    unsigned char* d_ctrl = nullptr;
+    size_t ctrl_bytes = 0;
+    uint32_t *h_status = nullptr, *d_status = nullptr;
+    uint32_t* h_in = nullptr;
+    uint8_t* h_out = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    DecodeArgs args;
+
+    ~DecCtx() {
+        if (exec) cudaGraphExecDestroy(exec);
+        if (graph) cudaGraphDestroy(graph);
+        for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
+        if (stream) cudaStreamDestroy(stream);
+        cudaFree(d_in); cudaFree(d_out); cudaFree(d_ctrl);
+        if (h_status) cudaFreeHost(h_status);
+        if (h_in) cudaFreeHost(h_in);
+        if (h_out) cudaFreeHost(h_out);
+    }
+};
+
 struct Engine::Impl {
     int device = 0;
     int sm_count = 0;
@@ -198,6 +229,11 @@ struct Engine::Impl {
     DeviceTables dt{};
     std::vector<void*> owned;
     std::unique_ptr<Ctx> single, batch;
+    std::unique_ptr<DecCtx> dec;
+    const uint32_t* d_tok_off = nullptr;  // decoding tables, uploaded at the first decode
+    const uint8_t* d_tok_blob = nullptr;
+    uint32_t max_tok_len = 0;
+    int dec_per_sm = 1;
     Ctx* staged = nullptr;
     int pretok_per_sm = 1, words_per_sm = 1, miss_per_sm = 1, asm_per_sm = 1, nfc_per_sm = 1;
     bool nfc = false;                    // the vocabulary declares NFC: the graph starts with the normalisation kernel
@@ -212,6 +248,7 @@ struct Engine::Impl {
     ~Impl() {
         single.reset();
         batch.reset();
+        dec.reset();
         for (void* p : owned) cudaFree(p);
     }
 
@@ -247,6 +284,65 @@ struct Engine::Impl {
         dt.ignore_merges = ht.ignore_merges;
         dt.monotone = ht.monotone;
         dt.added_ws = ht.added_ws;
+        return true;
+    }
+
+    bool upload_decode_tables(const HostVocab& hv, std::string& err) {
+        if (d_tok_off) return true;
+        std::vector<uint32_t> off(static_cast<size_t>(hv.vocab_size) + 1, 0);
+        std::vector<uint8_t> blob;
+        for (uint32_t id = 0; id < hv.vocab_size; ++id) {
+            off[id] = static_cast<uint32_t>(blob.size());
+            if (id < hv.token_bytes.size()) {
+                const std::string& b = hv.token_bytes[id];
+                blob.insert(blob.end(), b.begin(), b.end());
+                max_tok_len = std::max<uint32_t>(max_tok_len, static_cast<uint32_t>(b.size()));
+            }
+        }
+        off[hv.vocab_size] = static_cast<uint32_t>(blob.size());
+        if (!upload(blob, &d_tok_blob, owned, err)) return false;
+        if (!upload(off, &d_tok_off, owned, err)) { d_tok_off = nullptr; return false; }
+        dec_per_sm = std::max(1, decode_blocks_per_sm());
+        return true;
+    }
+
+    bool build_dec(uint32_t cap_ids, size_t cap_bytes, uint32_t vocab_size, std::string& err) {
+        std::unique_ptr<DecCtx> c(new DecCtx());
+        c->cap_ids = cap_ids;
+        c->cap_bytes = cap_bytes;
+        c->n_tiles_cap = (cap_ids + kDecIds - 1) / kDecIds + 1;
+        GTOK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        for (cudaEvent_t& e : c->ev) GTOK_CUDA(cudaEventCreate(&e));
+        GTOK_CUDA(cudaMalloc(&c->d_in, (static_cast<size_t>(cap_ids) + 4 + kDecPer) * 4));
+        GTOK_CUDA(cudaMemset(c->d_in, 0, (static_cast<size_t>(cap_ids) + 4 + kDecPer) * 4));
+        GTOK_CUDA(cudaMalloc(&c->d_out, cap_bytes + 16));
+        c->ctrl_bytes = 64 + static_cast<size_t>(c->n_tiles_cap + 1) * 8;
+        GTOK_CUDA(cudaMalloc(&c->d_ctrl, c->ctrl_bytes));
+        GTOK_CUDA(cudaHostAlloc(&c->h_status, 64, cudaHostAllocMapped));
+        std::memset(c->h_status, 0, 64);
+        GTOK_CUDA(cudaHostGetDevicePointer(&c->d_status, c->h_status, 0));
+        GTOK_CUDA(cudaHostAlloc(&c->h_in, (static_cast<size_t>(cap_ids) + 4) * 4, cudaHostAllocDefault));
+        GTOK_CUDA(cudaHostAlloc(&c->h_out, cap_bytes + 16, cudaHostAllocDefault));
+        DecodeArgs& a = c->args;
+        std::memset(&a, 0, sizeof a);
+        a.meta = c->d_in;
+        a.ids = c->d_in + 4;
+        a.tok_off = d_tok_off;
+        a.blob = d_tok_blob;
+        a.vocab_size = vocab_size;
+        a.ctl = reinterpret_cast<uint32_t*>(c->d_ctrl);
+        a.st = reinterpret_cast<unsigned long long*>(c->d_ctrl + 64);
+        a.out = c->d_out;
+        a.out_cap = static_cast<uint32_t>(std::min<size_t>(cap_bytes, 0xFFFFFFF0u));
+        a.status = c->d_status;
+        const int blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * dec_per_sm));
+        GTOK_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+        cudaMemsetAsync(c->d_ctrl, 0, c->ctrl_bytes, c->stream);
+        launch_decode(a, blocks, c->stream);
+        GTOK_CUDA(cudaStreamEndCapture(c->stream, &c->graph));
+        GTOK_CUDA(cudaGraphInstantiate(&c->exec, c->graph, 0));
+        GTOK_CUDA(cudaGetLastError());
+        dec = std::move(c);
         return true;
     }
 
@@ -781,6 +877,57 @@ int Engine::read_phase_clocks(unsigned long long* out32, bool reset) {
     if (cudaMemcpy(out32, c->d_phase, 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     if (reset) cudaMemset(c->d_phase, 0, 32 * sizeof(unsigned long long));
     return 0;
+}
+
+// ids -> bytes on the device (the reference's TokenizerCtx::decode, src/tokenizer.cu:5499-5573).
+int64_t Engine::decode(const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t max_out, uint64_t* need, float* kernel_ms) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    if (need) *need = 0;
+    if (kernel_ms) *kernel_ms = 0.f;
+    if (n == 0) return 0;
+    if (!im.upload_decode_tables(hv_, last_error_)) return -1;
+    const uint64_t most = static_cast<uint64_t>(n) * std::max<uint32_t>(im.max_tok_len, 1);
+    if (most > 0xFFFFFFF0ull && max_out > 0xFFFFFFF0ull) max_out = 0xFFFFFFF0ull;    // byte offsets are 32-bit on the device
+    const uint64_t want = std::max<uint64_t>(std::min<uint64_t>(most, max_out), 1024);
+    if (!im.dec || im.dec->cap_ids < n || im.dec->cap_bytes < want) {
+        uint32_t cap_ids = 4096;
+        while (cap_ids < n && cap_ids < 0x80000000u) cap_ids <<= 1;
+        if (cap_ids < n) cap_ids = n;
+        size_t cap_bytes = 16384;
+        while (cap_bytes < want) cap_bytes <<= 1;
+        if (im.dec) { cap_ids = std::max(cap_ids, im.dec->cap_ids); cap_bytes = std::max(cap_bytes, im.dec->cap_bytes); }
+        im.dec.reset();
+        if (!im.build_dec(cap_ids, cap_bytes, hv_.vocab_size, last_error_)) { im.dec.reset(); return -1; }
+    }
+    DecCtx* c = im.dec.get();
+    c->h_in[0] = n;
+    c->h_in[1] = c->h_in[2] = c->h_in[3] = 0;
+    std::memcpy(c->h_in + 4, ids, static_cast<size_t>(n) * 4);
+    cudaError_t e = cudaMemcpyAsync(c->d_in, c->h_in, (static_cast<size_t>(n) + 4) * 4, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(c->ev[0], c->stream);
+    if (e == cudaSuccess) e = cudaGraphLaunch(c->exec, c->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(c->ev[1], c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { last_error_ = std::string("decode: ") + cudaGetErrorString(e); return -1; }
+    if (kernel_ms) cudaEventElapsedTime(kernel_ms, c->ev[0], c->ev[1]);
+    const uint32_t total = c->h_status[0], bits = c->h_status[1];
+    if (bits & kErrBadId) { last_error_ = "decode: an id is outside the vocabulary"; return -1; }
+    if (bits & kErrWaitExpired) { last_error_ = "decode: a wait on an earlier tile gave up"; return -1; }
+    if (need) *need = total;
+    if ((bits & kErrOutputFull) || total > max_out) { last_error_ = "decode: more bytes than the output buffer holds"; return -2; }
+    if (bits) { last_error_ = "decode: internal error"; return -1; }
+    if (total == 0) return 0;
+    if (im.is_pinned(out)) {
+        e = cudaMemcpyAsync(out, c->d_out, total, cudaMemcpyDeviceToHost, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    } else {
+        e = cudaMemcpyAsync(c->h_out, c->d_out, total, cudaMemcpyDeviceToHost, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e == cudaSuccess) std::memcpy(out, c->h_out, total);
+    }
+    if (e != cudaSuccess) { last_error_ = std::string("decode copy: ") + cudaGetErrorString(e); return -1; }
+    return total;
 }
 
 const DeviceTables* Engine::device_tables() const { return &impl_->dt; }

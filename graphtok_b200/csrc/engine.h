@@ -29,6 +29,11 @@ public:
     int64_t encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes,
                          uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_tok);
 
+    // ids -> the bytes they spell (host buffers).  Returns the byte count, -1 on error (an id outside
+    // the vocabulary included), -2 when `max_out` is too small; `need` (optional) receives the byte
+    // count in both cases, `kernel_ms` (optional) the CUDA-event time of the decode graph.
+    int64_t decode(const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t max_out, uint64_t* need, float* kernel_ms);
+
     // Measurement entry points (the reference's stage_input / launch_graph_sync,
     // src/tokenizer.cuh:252-279): stage once, then time graph replays alone.
     int stage(const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes);

@@ -303,6 +303,16 @@ int32_t gtok_x_token_bytes(void* handle, uint32_t id, uint8_t* out, uint32_t cap
     return static_cast<int32_t>(b.size());
 }
 
+int64_t gtok_x_decode(void* handle, const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t max_out, uint64_t* need_out, float* kernel_ms) {
+    if (!handle || (!ids && n) || (!out && max_out)) return -1;
+    try {
+        Handle* h = static_cast<Handle*>(handle);
+        int64_t r = h->engine->decode(ids, n, out, max_out, need_out, kernel_ms);
+        if (r < 0) g_last_error = h->engine->last_error();
+        return r;
+    } catch (const std::exception& e) { g_last_error = e.what(); return -1; } catch (...) { return -1; }
+}
+
 int32_t gtok_x_plan_chunks(void* handle, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out_offsets) {
     if (!handle || (!text && len) || !n_parts || !out_offsets) return -1;
     try {

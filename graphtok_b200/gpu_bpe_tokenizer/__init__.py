@@ -42,7 +42,6 @@ class Tokenizer:
         self._cap = max(4096, int(max_input_chars))
         self._g = GTok(self._path, max_bytes=self._cap)
         self._decode = bool(enable_decode)
-        self._bytes_of = {}
         self._staged_docs = None
 
     # ---- capacity ------------------------------------------------------------
@@ -93,27 +92,17 @@ class Tokenizer:
         toks, offs = self.encode_batch(texts)
         return torch.from_numpy(toks.astype(np.int32)).cuda(), torch.from_numpy(offs.astype(np.int32)).cuda()
 
-    # ---- decode (host side: ids -> the tokens' bytes) ---------------------------
-    def _token_bytes(self, tid):
-        b = self._bytes_of.get(tid)
-        if b is None:
-            lib = self._g.lib
-            n = lib.gtok_x_token_bytes(self._g.handle, int(tid), None, 0)
-            if n < 0:
-                raise ValueError("token id %d is outside the vocabulary" % tid)
-            buf = ctypes.create_string_buffer(max(n, 1))
-            lib.gtok_x_token_bytes(self._g.handle, int(tid), buf, n)
-            b = buf.raw[:n]
-            self._bytes_of[tid] = b
-        return b
-
+    # ---- decode (on the device: ids -> the tokens' bytes, gtok_x_decode) ---------
     def decode_bytes(self, ids):
         if not self._decode:
-            raise RuntimeError("this Tokenizer was created with enable_decode=False")
-        return b"".join(self._token_bytes(int(t)) for t in ids)
+            raise RuntimeError("decode() is disabled; construct Tokenizer(..., enable_decode=True)")
+        arr = np.asarray(ids)
+        if arr.size and (arr.min() < 0 or arr.max() > 0xFFFFFFFF):
+            raise ValueError("token ids must fit 32 unsigned bits")
+        return self._g.decode(arr.astype(np.uint32, copy=False))
 
     def decode(self, ids):
-        return self.decode_bytes(ids).decode("utf-8", errors="replace")
+        return self.decode_bytes(ids).decode("utf-8")          # strict, as the reference (PyUnicode_DecodeUTF8 "strict")
 
     # ---- measurement helpers (graph replays on staged input) --------------------
     def bench_stage(self, text):

@@ -121,6 +121,15 @@ int32_t gtok_x_boundaries_noalloc(void* handle, const void* text_dev, uint32_t l
  * id outside the vocabulary.  Nothing is written when `cap` is too small. */
 int32_t gtok_x_token_bytes(void* handle, uint32_t id, uint8_t* out, uint32_t cap);
 
+/* Decoding on the device: `n` token ids -> the bytes they spell, one pass (lengths, scan,
+ * gather) in a captured graph of its own.  Replaces the reference's TokenizerCtx::decode
+ * (src/tokenizer.cu:5499-5573, kernels :5225-5275) behind Tokenizer.decode / decode_bytes
+ * (src/python_bindings.cc:558-600); the reference's C ABI has no decode entry.  Host buffers.
+ * Returns the byte count; -1 on error (an id outside the vocabulary included); -2 when
+ * `max_out` is too small.  `need_out` (may be NULL) receives the byte count in both cases,
+ * `kernel_ms` (may be NULL) the CUDA-event time of the graph. */
+int64_t gtok_x_decode(void* handle, const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t max_out, uint64_t* need_out, float* kernel_ms);
+
 /* Partitioning over the GPUs of one box (no counterpart in the reference, which is
  * single-GPU).  gtok_x_plan_chunks cuts one document into n_parts pieces at
  * positions where a pre-token starts whatever precedes it (letter | space letter),

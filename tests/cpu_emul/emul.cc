@@ -7,9 +7,11 @@
 // It is not part of the shipped library and not a fallback: libgtok has no CPU path.
 #include <cstdint>
 #include <cstring>
+#include <memory>
 #include <string>
 #include <vector>
 
+#include "../../graphtok_b200/csrc/decode_core.h"
 #include "../../graphtok_b200/csrc/encode_core.h"
 #include "../../graphtok_b200/csrc/nfc_core.h"
 #include "../../graphtok_b200/csrc/nfc_host.h"
@@ -217,6 +219,54 @@ int64_t gtok_emul_nfc_device(const uint8_t* text, uint32_t n, const uint32_t* do
 }
 
 // The shard planner of libgtok (gtok_x_plan_chunks), reachable without a GPU handle.
+// The decode tile program (decode_core.h) on one serial "block", tiles in order.  Returns the byte
+// count (whatever `cap` is); *err_bits receives the error bits the kernel would report.
+int64_t gtok_emul_decode(void* h, const uint32_t* ids, uint32_t n, uint8_t* out, uint32_t cap, int reverse, uint32_t* err_bits) {
+    Emul* e = static_cast<Emul*>(h);
+    const gtok::HostVocab& hv = e->hv;
+    std::vector<uint32_t> off(static_cast<size_t>(hv.vocab_size) + 1, 0);
+    std::vector<uint8_t> blob;
+    for (uint32_t id = 0; id < hv.vocab_size; ++id) {
+        off[id] = static_cast<uint32_t>(blob.size());
+        if (id < hv.token_bytes.size()) blob.insert(blob.end(), hv.token_bytes[id].begin(), hv.token_bytes[id].end());
+    }
+    off[hv.vocab_size] = static_cast<uint32_t>(blob.size());
+    blob.resize(blob.size() + 16);
+    const uint32_t n_tiles = (n + gtok::kDecIds - 1) / gtok::kDecIds;
+    std::vector<uint32_t> in(static_cast<size_t>(n) + 4 + gtok::kDecPer, 0);
+    in[0] = n;
+    if (n) std::memcpy(in.data() + 4, ids, static_cast<size_t>(n) * 4);
+    std::vector<unsigned long long> st(n_tiles + 1, 0);
+    std::vector<uint8_t> obuf(static_cast<size_t>(cap) + 32, 0xEE);
+    uint8_t* o = obuf.data();
+    o += (16 - (reinterpret_cast<uintptr_t>(o) & 15)) & 15;
+    uint32_t ctl[16] = {0}, status[16] = {0};
+    gtok::DecodeArgs a;
+    std::memset(&a, 0, sizeof a);
+    a.meta = in.data();
+    a.ids = in.data() + 4;
+    a.tok_off = off.data();
+    a.blob = blob.data();
+    a.vocab_size = hv.vocab_size;
+    a.st = st.data();
+    a.ctl = ctl;
+    a.out = o;
+    a.out_cap = cap;
+    a.status = status;
+    std::unique_ptr<gtok::DecodeSmem> sm(new gtok::DecodeSmem());
+    CpuBlk blk;
+    blk.reverse = reverse != 0;
+    for (uint32_t t = 0; t < n_tiles; ++t) gtok::decode_tile(blk, a, *sm, static_cast<int>(t));
+    if (err_bits) *err_bits = ctl[gtok::CTL_ERR];
+    const uint32_t total = status[0];
+    if (total <= cap && !(ctl[gtok::CTL_ERR] & gtok::kErrOutputFull)) {
+        std::memcpy(out, o, total);
+        // nothing may be written past the end
+        for (uint32_t i = total; i < cap + 16 && o + i < obuf.data() + obuf.size(); ++i) if (o[i] != 0xEE) { if (err_bits) *err_bits |= 0x80000000u; break; }
+    }
+    return total;
+}
+
 int gtok_emul_plan_chunks(void* h, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out) {
     std::vector<uint64_t> cuts;
     gtok::plan_chunks(static_cast<Emul*>(h)->hv, text, len, n_parts, cuts);

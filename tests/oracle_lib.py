@@ -185,3 +185,40 @@ class Emul:
             bits = np.unpackbits(bm.view(np.uint8), bitorder="little")[:len(data)]
             res.append(np.nonzero(bits)[0].astype(np.uint32))
         return res[0] if len(res) == 1 else tuple(res)
+
+    def decode(self, ids, cap=None, reverse=False):
+        """decode_tile over the ids; returns (bytes or None when `cap` is too small, byte count, error bits)."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        f = self.lib.gtok_emul_decode
+        f.restype = ctypes.c_int64
+        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int, ctypes.c_void_p]
+        if cap is None:
+            cap = 64 * ids.size + 64
+        out = np.zeros(cap + 16, dtype=np.uint8)
+        bits = ctypes.c_uint32(0)
+        total = f(self.h, ids.ctypes.data, ids.size, out.ctypes.data, cap, int(reverse), ctypes.byref(bits))
+        ok = total <= cap and not (bits.value & 1)
+        return (out[:total].tobytes() if ok else None), int(total), bits.value
+
+
+def token_spellings(tokenizer_json):
+    """id -> raw bytes, straight from the tokenizer.json: model vocabulary strings mapped back
+    through the GPT-2 byte-to-unicode table (the reference's gpt2_token_decoded_bytes,
+    src/vocab.h:25-28), added tokens as their UTF-8 content.  Decoding oracle."""
+    import json
+    cs = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAC + 1)) + list(range(0xAE, 0xFF + 1))
+    back = {}
+    extra = 0
+    for b in range(256):
+        if b in cs:
+            back[chr(b)] = b
+        else:
+            back[chr(256 + extra)] = b
+            extra += 1
+    j = json.load(open(tokenizer_json, encoding="utf-8"))
+    table = {}
+    for tok, tid in j["model"]["vocab"].items():
+        table[tid] = bytes(back[ch] for ch in tok)
+    for at in j.get("added_tokens", []):
+        table[at["id"]] = at["content"].encode("utf-8")
+    return table

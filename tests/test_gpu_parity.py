@@ -275,6 +275,65 @@ def test_configuration_2_batch(built):
         g.close()
 
 
+@pytest.mark.parametrize("family", FAMILIES)
+def test_decode_on_the_device(gtoks, oracles, family):
+    """gtok_x_decode: random ids against the spellings read from the tokenizer.json, the golden
+    texts back from their ids, encode -> decode round trips, sizes changing between calls."""
+    g, o = gtoks[family], oracles[family]
+    table = oracle_lib.token_spellings(tiny_vocab(family))
+    known = np.array(sorted(table), dtype=np.uint32)
+    rng = np.random.default_rng(6)
+    for n in (1, 8, 9, 2047, 2048, 2049, 300000, 5, 70001):
+        ids = rng.choice(known, size=n)
+        assert g.decode(ids) == b"".join(table[int(t)] for t in ids), n
+    data = json.load(open(os.path.join(GOLDEN, "golden_%s.json" % family)))
+    for row in data["cases"]:
+        assert g.decode(row["ids"]) == norm(o, row["text"].encode("utf-8")), repr(row["text"][:40])
+    for t in cases.fuzz_strings(78, SPECIAL[family], per_pool=40):
+        b = norm(o, t.encode())
+        if b:
+            assert g.decode(g.encode(b)) == b, repr(t[:40])
+    assert g.decode(np.zeros(0, dtype=np.uint32)) == b""
+    longest = max(table, key=lambda t: len(table[t]))
+    assert g.decode(np.full(50000, longest, dtype=np.uint32)) == table[longest] * 50000
+
+
+def test_decode_return_codes_and_page_locked_output(gtoks):
+    import torch
+    g = gtoks["llama3"]
+    table = oracle_lib.token_spellings(tiny_vocab("llama3"))
+    ids = np.array(sorted(table)[:4000] * 10, dtype=np.uint32)
+    want = b"".join(table[int(t)] for t in ids)
+    need = ctypes.c_uint64(0)
+    small = np.zeros(len(want) - 1, dtype=np.uint8)
+    r = g.lib.gtok_x_decode(g.handle, ids.ctypes.data, ids.size, small.ctypes.data, small.size, ctypes.byref(need), None)
+    assert r == -2 and need.value == len(want)
+    exact = np.zeros(len(want), dtype=np.uint8)
+    r = g.lib.gtok_x_decode(g.handle, ids.ctypes.data, ids.size, exact.ctypes.data, exact.size, ctypes.byref(need), None)
+    assert r == len(want) and exact.tobytes() == want
+    pinned = torch.zeros(len(want) + 64, dtype=torch.uint8).pin_memory()
+    arr = pinned.numpy()
+    r = g.lib.gtok_x_decode(g.handle, ids.ctypes.data, ids.size, arr.ctypes.data, arr.size, None, None)
+    assert r == len(want) and arr[:r].tobytes() == want and not arr[r:].any()
+    bad = np.array([1, 2, 0x7FFFFFFF, 3], dtype=np.uint32)
+    r = g.lib.gtok_x_decode(g.handle, bad.ctypes.data, bad.size, arr.ctypes.data, arr.size, None, None)
+    assert r == -1 and b"outside the vocabulary" in g.lib.gtok_x_last_error()
+    assert g.decode(ids[:100]) == b"".join(table[int(t)] for t in ids[:100])       # the handle still works
+
+
+def test_decode_round_trip_full_size_configuration_1(built):
+    """encode -> decode gives the document back, at the benchmark's size."""
+    from graphtok_b200 import GTok, synth
+    path, doc = synth.config_doc(1)
+    g = GTok(path, max_bytes=len(doc) + 4096)
+    try:
+        ids = g.encode(doc)
+        out, ms = g.decode(ids, want_ms=True)
+        assert out == doc and 0 < ms < 50
+    finally:
+        g.close()
+
+
 def test_python_module_surface(built, oracles):
     """The reference's Python classes over this library: same calls, same return types."""
     import graphtok_b200.gpu_bpe_tokenizer as gpu_bpe_tokenizer
@@ -290,7 +349,7 @@ def test_python_module_surface(built, oracles):
     assert toks[offs[0]:offs[1]].tolist() == ids and offs[1] == offs[2]
     e_t, e_o = tok.encode_batch([])
     assert e_t.size == 0 and e_o.tolist() == [0]
-    assert tok.decode(ids) == text
+    assert tok.decode(ids) == text and tok.decode_bytes(np.array(ids)) == text.encode()
     long_text = "grow " * 5000                                  # beyond max_input_chars: capacity grows
     assert tok.encode_numpy(long_text).tolist() == o.encode(long_text.encode()).tolist()
     assert tok.active_capacity >= len(long_text) and tok.regex_kind == "Llama3" and tok.cpu_backend == "off" and tok.last_route == "gpu"

@@ -186,3 +186,49 @@ def test_device_normaliser_reports_what_it_cannot_do():
     grows = ("\u0958 " * 100).encode()
     assert oracle_lib.device_nfc(grows, cap=len(grows) + 10) == -32
     assert oracle_lib.device_nfc(grows) == oracle_lib.nfc(grows)
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_emul_decode_against_the_vocabulary_file_and_round_trip(emuls, oracles, family):
+    """decode_tile: random ids against a join of the spellings read from the tokenizer.json; the
+    golden texts back from their ids; encode -> decode round trips over several tiles."""
+    from conftest import tiny_vocab
+    e, o = emuls[family], oracles[family]
+    table = oracle_lib.token_spellings(tiny_vocab(family))
+    known = np.array(sorted(table), dtype=np.uint32)
+    rng = np.random.default_rng(5)
+    for i, n in enumerate((1, 7, 8, 9, 255, 2047, 2048, 2049, 5000, 12345)):
+        ids = rng.choice(known, size=n)
+        want = b"".join(table[int(t)] for t in ids)
+        got, total, bits = e.decode(ids, reverse=bool(i & 1))
+        assert bits == 0 and total == len(want) and got == want, n
+    data = json.load(open(os.path.join(GOLDEN, "golden_%s.json" % family)))
+    for row in data["cases"]:
+        got, _, bits = e.decode(row["ids"])
+        assert bits == 0 and got == norm(o, row["text"].encode("utf-8")), repr(row["text"][:40])
+    for t in list(cases.fuzz_strings(77, SPECIAL[family], per_pool=25)) + [("naïve café — 日本語 " * 900)]:
+        b = norm(o, t.encode())
+        ids = o.encode_normalized(b)
+        got, _, bits = e.decode(ids)
+        assert bits == 0 and got == b, repr(t[:40])
+    # one long token repeated: several rounds of the staging buffer per tile
+    longest = max(table, key=lambda t: len(table[t]))
+    ids = np.full(6000, longest, dtype=np.uint32)
+    got, total, bits = e.decode(ids, cap=len(table[longest]) * 6000 + 3)
+    assert bits == 0 and got == table[longest] * 6000
+
+
+def test_emul_decode_errors(emuls):
+    e = emuls["llama3"]
+    from conftest import tiny_vocab
+    table = oracle_lib.token_spellings(tiny_vocab("llama3"))
+    ids = np.array(sorted(table)[:3000], dtype=np.uint32)
+    want = b"".join(table[int(t)] for t in ids)
+    got, total, bits = e.decode(ids, cap=len(want) - 1)            # too small: the count is still reported
+    assert got is None and total == len(want) and bits & 1
+    got, total, bits = e.decode(ids, cap=len(want))                 # exact fit
+    assert got == want and bits == 0
+    got, total, bits = e.decode(np.array([1, 2, 0x7FFFFFFF, 3], dtype=np.uint32))
+    assert bits & 64                                                # an id outside the vocabulary
+    got, total, bits = e.decode(np.zeros(0, dtype=np.uint32))
+    assert total == 0 and bits == 0
