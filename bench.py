@@ -14,7 +14,8 @@ is an all-gather of the per-rank token counts for the global offsets).
 `value` is input MB/s (1e6 bytes) with the text already in device memory, timed
 with CUDA events around each graph replay on the stream that launches it, L2
 flushed between replays; `e2e` is the same through gtok_encode with host buffers
-(pinned H2D, replay, D2H inside the timed region).  One JSON line on stdout.
+(pinned H2D, replay, D2H inside the timed region).  `decode` (1 GPU) is the way back:
+the workload's ids through gtok_x_decode to its bytes.  One JSON line on stdout.
 """
 import argparse
 import ctypes
@@ -153,6 +154,40 @@ def prompt_latency(g, path, want_tokens=131072, reps=40):
     ts.sort()
     return {"p50_ms": ts[len(ts) // 2] * 1e3, "p90_ms": ts[int(len(ts) * 0.9)] * 1e3, "tokens": int(n_tok), "bytes": len(prompt),
             "what": "gtok_encode with host buffers, prefix of the configuration-4 document (Llama-3-shaped vocabulary)"}
+
+
+def decode_numbers(g, doc, flush, reps=20):
+    """Decoding of the workload's own ids back to its bytes through gtok_x_decode (host buffers):
+    CUDA-event time of the decode graph (control-block reset + one kernel) with L2 flushed before
+    each call, wall time of the whole call into a pageable and into a page-locked buffer."""
+    import ctypes
+    import torch
+    ids = g.encode(doc)
+    out = np.empty(len(doc) + 64, dtype=np.uint8)
+    pinned = torch.empty(len(doc) + 64, dtype=torch.uint8).pin_memory().numpy()
+    ms = ctypes.c_float(0.0)
+
+    def call(buf):
+        t = time.perf_counter()
+        n = g.lib.gtok_x_decode(g.handle, ids.ctypes.data, ids.size, buf.ctypes.data, buf.size, None, ctypes.byref(ms))
+        return n, (time.perf_counter() - t) * 1e3
+
+    n, _ = call(out)
+    if n != len(doc) or out[:n].tobytes() != bytes(doc):
+        raise SystemExit("decode(encode(document)) differs from the document")
+    graph, wall, wall_pin = [], [], []
+    for _ in range(reps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        wall.append(call(out)[1])
+        graph.append(ms.value)
+        wall_pin.append(call(pinned)[1])
+    gm = float(np.median(graph))
+    # algorithmic bytes: ids read (4 B each), the bytes written, 8 B of offsets and 16 B of spelling per id
+    algo = 4.0 * ids.size + len(doc) + 24.0 * ids.size
+    return {"what": "gtok_x_decode of the workload's ids back to its bytes (checked equal)", "ids": int(ids.size), "bytes": len(doc),
+            "graph_ms": gm, "ids_per_s": ids.size / (gm * 1e-3), "algorithmic_bytes": algo, "achieved_gbs": algo / (gm * 1e-3) / 1e9,
+            "e2e_ms_pageable_output": float(np.median(wall)), "e2e_ms_page_locked_output": float(np.median(wall_pin)), "gpu_launches_per_call": 1}
 
 
 def cpu_encoder(path):
@@ -304,6 +339,7 @@ def main():
     latency = None
     if world == 1 and not args.quick:
         latency = prompt_latency(g, path)
+    decode = decode_numbers(g, doc, flush) if world == 1 and not args.quick else None
 
     # ---- reduce over ranks ---------------------------------------------------
     stats = torch.tensor([step_ms, e2e_s * 1e3, float(n_bytes), float(n_tok)] + kern_ms, dtype=torch.float64, device="cuda")
@@ -368,6 +404,7 @@ def main():
                          "whole_replay": {"achieved": whole, "frac": whole / peak}},
             "clocks": clocks,
             "latency_128k_prompt": latency,
+            "decode": decode,
             "wall_s_timed_region": wall,
             "global_token_offsets": [int(x) for x in offsets],
         }

@@ -30,6 +30,7 @@ struct DecodeArgs {
     const uint32_t* meta;            // [0] = number of ids
     const uint32_t* tok_off;         // [vocab_size + 1] offsets of the spellings in `blob`
     const uint8_t* blob;
+    const uint32_t* tok16;           // [vocab_size][4]: the first 16 bytes of every spelling, one aligned load per id
     uint32_t vocab_size;
     unsigned long long* st;          // look-back state per tile
     uint32_t* ctl;                   // CTL_PRETOK = ticket, CTL_ERR, CTL_EXIT as in the encoder
@@ -40,7 +41,7 @@ struct DecodeArgs {
 
 struct DecodeSmem {
     uint32_t scan[kThreads];
-    uint32_t src[kDecIds];           // offset of each id's spelling in the blob
+    uint32_t id[kDecIds];            // the ids (those outside the vocabulary replaced by 0, with no bytes)
     uint32_t dst[kDecIds + 1];       // offset of each id's bytes in the tile's output
     alignas(16) uint8_t buf[kDecBuf + 16];
 };
@@ -77,7 +78,7 @@ GTOK_DEV void decode_tile(Blk& blk, const DecodeArgs& a, DecodeSmem& sm, int til
         uint32_t sum = 0;
 #pragma unroll
         for (int k = 0; k < kDecPer; ++k) {
-            sm.src[tid * kDecPer + k] = lo[k];
+            sm.id[tid * kDecPer + k] = id[k] < a.vocab_size ? id[k] : 0u;
             sm.dst[tid * kDecPer + k] = sum;      // relative to the thread's first byte for now
             sum += hi[k] - lo[k];
         }
@@ -113,13 +114,42 @@ GTOK_DEV void decode_tile(Blk& blk, const DecodeArgs& a, DecodeSmem& sm, int til
         blk.par([&](int tid) {
             const uint32_t f = tid * kDecPer;
             if (base + sm.dst[f + kDecPer] <= w0 || base + sm.dst[f] >= w1) return;
+            // Spellings of up to 16 bytes that lie inside this round come from the 16-byte table, all
+            // eight loads in flight together; the rest byte by byte from the blob.
+            uint32_t v[kDecPer][4];
+            uint32_t at[kDecPer], len[kDecPer];
+#pragma unroll
             for (int k = 0; k < kDecPer; ++k) {
-                uint32_t g = base + sm.dst[f + k];
-                const uint32_t ge = base + sm.dst[f + k + 1];
-                uint32_t s = sm.src[f + k];
-                if (g < w0) { s += w0 - g; g = w0; }
-                const uint32_t stop = ge < w1 ? ge : w1;
-                for (; g < stop; ++g, ++s) sm.buf[g - w0] = ldg(a.blob + s);
+                const uint32_t g = base + sm.dst[f + k], ge = base + sm.dst[f + k + 1];
+                at[k] = g - w0;
+                len[k] = ge - g;
+                const bool quick = len[k] - 1u < 16u && g >= w0 && ge <= w1;
+                if (!quick && len[k]) len[k] |= 0x80000000u;
+                v[k][0] = v[k][1] = v[k][2] = v[k][3] = 0;
+                if (quick) {
+                    const uint32_t* t = a.tok16 + static_cast<size_t>(sm.id[f + k]) * 4;
+#if defined(__CUDA_ARCH__)
+                    const uint4 x = __ldg(reinterpret_cast<const uint4*>(t));
+                    v[k][0] = x.x; v[k][1] = x.y; v[k][2] = x.z; v[k][3] = x.w;
+#else
+                    for (int q = 0; q < 4; ++q) v[k][q] = t[q];
+#endif
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kDecPer; ++k) {
+                if (len[k] & 0x80000000u) {
+                    uint32_t g = base + sm.dst[f + k];
+                    const uint32_t ge = base + sm.dst[f + k + 1];
+                    uint32_t s = ldg(a.tok_off + sm.id[f + k]);
+                    if (g < w0) { s += w0 - g; g = w0; }
+                    const uint32_t stop = ge < w1 ? ge : w1;
+                    for (; g < stop; ++g, ++s) sm.buf[g - w0] = ldg(a.blob + s);
+                    continue;
+                }
+#pragma unroll
+                for (int b = 0; b < 16; ++b)
+                    if (static_cast<uint32_t>(b) < len[k]) sm.buf[at[k] + b] = static_cast<uint8_t>(v[k][b >> 2] >> (8 * (b & 3)));
             }
         });
         blk.par([&](int tid) {

@@ -208,12 +208,14 @@ struct DecCtx {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     cudaEvent_t ev[2] = {nullptr, nullptr};
+    cudaEvent_t out_ev[kCopyEvents] = {};
     DecodeArgs args;
 
     ~DecCtx() {
         if (exec) cudaGraphExecDestroy(exec);
         if (graph) cudaGraphDestroy(graph);
         for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
+        for (cudaEvent_t e : out_ev) if (e) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
         cudaFree(d_in); cudaFree(d_out); cudaFree(d_ctrl);
         if (h_status) cudaFreeHost(h_status);
@@ -232,6 +234,7 @@ struct Engine::Impl {
     std::unique_ptr<DecCtx> dec;
     const uint32_t* d_tok_off = nullptr;  // decoding tables, uploaded at the first decode
     const uint8_t* d_tok_blob = nullptr;
+    const uint32_t* d_tok16 = nullptr;
     uint32_t max_tok_len = 0;
     int dec_per_sm = 1;
     Ctx* staged = nullptr;
@@ -291,16 +294,18 @@ struct Engine::Impl {
         if (d_tok_off) return true;
         std::vector<uint32_t> off(static_cast<size_t>(hv.vocab_size) + 1, 0);
         std::vector<uint8_t> blob;
+        std::vector<uint32_t> first16(static_cast<size_t>(hv.vocab_size) * 4 + 4, 0);
         for (uint32_t id = 0; id < hv.vocab_size; ++id) {
             off[id] = static_cast<uint32_t>(blob.size());
             if (id < hv.token_bytes.size()) {
                 const std::string& b = hv.token_bytes[id];
                 blob.insert(blob.end(), b.begin(), b.end());
+                std::memcpy(first16.data() + static_cast<size_t>(id) * 4, b.data(), std::min<size_t>(b.size(), 16));
                 max_tok_len = std::max<uint32_t>(max_tok_len, static_cast<uint32_t>(b.size()));
             }
         }
         off[hv.vocab_size] = static_cast<uint32_t>(blob.size());
-        if (!upload(blob, &d_tok_blob, owned, err)) return false;
+        if (!upload(blob, &d_tok_blob, owned, err) || !upload(first16, &d_tok16, owned, err)) return false;
         if (!upload(off, &d_tok_off, owned, err)) { d_tok_off = nullptr; return false; }
         dec_per_sm = std::max(1, decode_blocks_per_sm());
         return true;
@@ -321,7 +326,7 @@ struct Engine::Impl {
         GTOK_CUDA(cudaHostAlloc(&c->h_status, 64, cudaHostAllocMapped));
         std::memset(c->h_status, 0, 64);
         GTOK_CUDA(cudaHostGetDevicePointer(&c->d_status, c->h_status, 0));
-        GTOK_CUDA(cudaHostAlloc(&c->h_in, (static_cast<size_t>(cap_ids) + 4) * 4, cudaHostAllocDefault));
+        GTOK_CUDA(cudaHostAlloc(&c->h_in, (static_cast<size_t>(cap_ids) + 4 + kDecPer) * 4, cudaHostAllocDefault));
         GTOK_CUDA(cudaHostAlloc(&c->h_out, cap_bytes + 16, cudaHostAllocDefault));
         DecodeArgs& a = c->args;
         std::memset(&a, 0, sizeof a);
@@ -329,6 +334,7 @@ struct Engine::Impl {
         a.ids = c->d_in + 4;
         a.tok_off = d_tok_off;
         a.blob = d_tok_blob;
+        a.tok16 = d_tok16;
         a.vocab_size = vocab_size;
         a.ctl = reinterpret_cast<uint32_t*>(c->d_ctrl);
         a.st = reinterpret_cast<unsigned long long*>(c->d_ctrl + 64);
@@ -522,19 +528,16 @@ struct Engine::Impl {
         return true;
     }
 
-    // Host -> pinned -> device, for the text and the header.
-    // With NFC the destination is the raw buffer; `normalised`: the text has been normalised on the host, the graph need not look.
-    bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err,
-                     bool normalised = false) {
-        uint8_t* d_dst = nfc ? c->d_raw : c->d_text;
-        if (len && pool && len >= 2 * kCopyPart) {
-            // piece by piece: finished pieces go to the device while the rest is still being copied into pinned memory
+    // Host -> pinned -> device.  Large inputs piece by piece through the pool: finished pieces go to
+    // the device while the rest is still being copied into pinned memory.
+    bool host_to_device(uint8_t* d_dst, uint8_t* h_pin, const uint8_t* src, size_t len, cudaStream_t stream, std::string& err) {
+        if (pool && len >= 2 * kCopyPart) {
             const int parts = static_cast<int>((len + kCopyPart - 1) / kCopyPart);
             if (part_done_n < parts) { part_done.reset(new std::atomic<uint8_t>[parts]); part_done_n = parts; }
             for (int p = 0; p < parts; ++p) part_done[p].store(0, std::memory_order_relaxed);
             const std::function<void(int)> fn = [&](int p) {
                 const size_t off = static_cast<size_t>(p) * kCopyPart;
-                std::memcpy(c->h_text + off, bytes + off, std::min(kCopyPart, static_cast<size_t>(len) - off));
+                std::memcpy(h_pin + off, src + off, std::min(kCopyPart, len - off));
                 part_done[p].store(1, std::memory_order_release);
             };
             pool->start(parts, &fn);
@@ -545,8 +548,8 @@ struct Engine::Impl {
                 while (upto < parts && part_done[upto].load(std::memory_order_acquire)) ++upto;
                 if (upto > issued) {
                     const size_t off = static_cast<size_t>(issued) * kCopyPart;
-                    const size_t end = std::min(static_cast<size_t>(upto) * kCopyPart, static_cast<size_t>(len));
-                    const cudaError_t e1 = cudaMemcpyAsync(d_dst + off, c->h_text + off, (end - off + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream);
+                    const size_t end = std::min(static_cast<size_t>(upto) * kCopyPart, len);
+                    const cudaError_t e1 = cudaMemcpyAsync(d_dst + off, h_pin + off, (end - off + 15) & ~size_t(15), cudaMemcpyHostToDevice, stream);
                     if (ce == cudaSuccess) ce = e1;
                     issued = upto;
                     continue;
@@ -555,11 +558,20 @@ struct Engine::Impl {
                 if (p >= 0) { fn(p); pool->done_one(); } else CopyPool::cpu_relax();
             }
             pool->finish();
-            if (ce != cudaSuccess) { err = std::string("text copy: ") + cudaGetErrorString(ce); return false; }
-        } else if (len) {
-            std::memcpy(c->h_text, bytes, len);
-            GTOK_CUDA(cudaMemcpyAsync(d_dst, c->h_text, (static_cast<size_t>(len) + 15) & ~size_t(15), cudaMemcpyHostToDevice, c->stream));
+            if (ce != cudaSuccess) { err = std::string("copy to the device: ") + cudaGetErrorString(ce); return false; }
+        } else {
+            std::memcpy(h_pin, src, len);
+            GTOK_CUDA(cudaMemcpyAsync(d_dst, h_pin, (len + 15) & ~size_t(15), cudaMemcpyHostToDevice, stream));
         }
+        return true;
+    }
+
+    // Host -> pinned -> device, for the text and the header.
+    // With NFC the destination is the raw buffer; `normalised`: the text has been normalised on the host, the graph need not look.
+    bool stage_input(Ctx* c, const uint8_t* bytes, uint32_t len, const uint32_t* doc_off, uint32_t n_docs, std::string& err,
+                     bool normalised = false) {
+        uint8_t* d_dst = nfc ? c->d_raw : c->d_text;
+        if (len && !host_to_device(d_dst, c->h_text, bytes, len, c->stream, err)) return false;
         c->h_hdr[0] = len;
         c->h_hdr[1] = n_docs;
         c->h_hdr[2] = normalised ? 1u : 0u;
@@ -575,9 +587,50 @@ struct Engine::Impl {
         return true;
     }
 
-    // ids (and, for a batch, the document offsets behind them) from the device to the caller's
-    // memory through the pinned buffer; large outputs part by part, so that the copy out of
-    // pinned memory of one part overlaps with the DMA of the next ones.
+    // Device -> pinned -> the caller's memory, then the stream is idle.  Large outputs part by part,
+    // so that the copy out of pinned memory of one part overlaps with the DMA of the next ones.
+    bool device_to_host(void* out, void* h_pin, const void* d_src, size_t bytes, cudaStream_t stream, cudaEvent_t* evs, std::string& err) {
+        if (pool && bytes >= 2 * kCopyPart) {
+            size_t part = kCopyPart;
+            while ((bytes + part - 1) / part > static_cast<size_t>(kCopyEvents)) part *= 2;
+            const int parts = static_cast<int>((bytes + part - 1) / part);
+            for (int p = 0; p < parts; ++p) {
+                if (!evs[p]) GTOK_CUDA(cudaEventCreateWithFlags(&evs[p], cudaEventDisableTiming));
+                const size_t off = static_cast<size_t>(p) * part, nb = std::min(part, bytes - off);
+                GTOK_CUDA(cudaMemcpyAsync(static_cast<char*>(h_pin) + off, static_cast<const char*>(d_src) + off, nb, cudaMemcpyDeviceToHost, stream));
+                GTOK_CUDA(cudaEventRecord(evs[p], stream));
+            }
+            // pieces arrive in order; this thread watches the events and publishes how many are in,
+            // every thread (this one too) copies arrived pieces out of pinned memory
+            std::atomic<int> ready{0};
+            std::atomic<int> failed{0};
+            const std::function<void(int)> fn = [&](int p) {
+                while (ready.load(std::memory_order_acquire) <= p && !failed.load(std::memory_order_relaxed)) CopyPool::cpu_relax();
+                if (failed.load(std::memory_order_relaxed)) return;
+                const size_t off = static_cast<size_t>(p) * part, nb = std::min(part, bytes - off);
+                std::memcpy(static_cast<char*>(out) + off, static_cast<const char*>(h_pin) + off, nb);
+            };
+            pool->start(parts, &fn);
+            int in = 0;
+            cudaError_t ce = cudaSuccess;
+            while (in < parts) {
+                const cudaError_t q = cudaEventQuery(evs[in]);
+                if (q == cudaSuccess) { ready.store(++in, std::memory_order_release); continue; }
+                if (q != cudaErrorNotReady) { ce = q; failed.store(1); break; }
+                CopyPool::cpu_relax();
+            }
+            for (int p; (p = pool->take()) >= 0;) { fn(p); pool->done_one(); }
+            pool->finish();
+            if (ce != cudaSuccess) { err = std::string("copy from the device: ") + cudaGetErrorString(ce); return false; }
+            GTOK_CUDA(cudaStreamSynchronize(stream));
+        } else {
+            if (bytes) GTOK_CUDA(cudaMemcpyAsync(h_pin, d_src, bytes, cudaMemcpyDeviceToHost, stream));
+            GTOK_CUDA(cudaStreamSynchronize(stream));
+            if (bytes) std::memcpy(out, h_pin, bytes);
+        }
+        return true;
+    }
+
     // Is this host pointer page-locked memory the device can reach (cudaHostAlloc / cudaHostRegister)?
     static bool is_pinned(const void* p) {
         cudaPointerAttributes at;
@@ -585,6 +638,8 @@ struct Engine::Impl {
         return at.type == cudaMemoryTypeHost;
     }
 
+    // ids (and, for a batch, the document offsets behind them) from the device to the caller's
+    // memory: directly when that is page-locked, else through the pinned buffer.
     bool copy_out(Ctx* c, uint32_t* out, size_t words, uint32_t* out_doc_tok, size_t doc_words, std::string& err) {
         const size_t bytes = words * 4;
         if (words && bytes >= kCopyPart && is_pinned(out)) {
@@ -599,46 +654,8 @@ struct Engine::Impl {
             return true;
         }
         if (!grow_host_out(c, words + doc_words + 2, err)) return false;
-        if (pool && bytes >= 2 * kCopyPart) {
-            size_t part = kCopyPart;
-            while ((bytes + part - 1) / part > static_cast<size_t>(kCopyEvents)) part *= 2;
-            const int parts = static_cast<int>((bytes + part - 1) / part);
-            for (int p = 0; p < parts; ++p) {
-                if (!c->out_ev[p]) GTOK_CUDA(cudaEventCreateWithFlags(&c->out_ev[p], cudaEventDisableTiming));
-                const size_t off = static_cast<size_t>(p) * part, nb = std::min(part, bytes - off);
-                GTOK_CUDA(cudaMemcpyAsync(reinterpret_cast<char*>(c->h_out) + off, reinterpret_cast<const char*>(c->d_out) + off, nb, cudaMemcpyDeviceToHost, c->stream));
-                GTOK_CUDA(cudaEventRecord(c->out_ev[p], c->stream));
-            }
-            if (doc_words) GTOK_CUDA(cudaMemcpyAsync(c->h_out + words, c->d_doc_tok, doc_words * 4, cudaMemcpyDeviceToHost, c->stream));
-            // pieces arrive in order; this thread watches the events and publishes how many are in,
-            // every thread (this one too) copies arrived pieces out of pinned memory
-            std::atomic<int> ready{0};
-            std::atomic<int> failed{0};
-            const std::function<void(int)> fn = [&](int p) {
-                while (ready.load(std::memory_order_acquire) <= p && !failed.load(std::memory_order_relaxed)) CopyPool::cpu_relax();
-                if (failed.load(std::memory_order_relaxed)) return;
-                const size_t off = static_cast<size_t>(p) * part, nb = std::min(part, bytes - off);
-                std::memcpy(reinterpret_cast<char*>(out) + off, reinterpret_cast<const char*>(c->h_out) + off, nb);
-            };
-            pool->start(parts, &fn);
-            int in = 0;
-            cudaError_t ce = cudaSuccess;
-            while (in < parts) {
-                const cudaError_t q = cudaEventQuery(c->out_ev[in]);
-                if (q == cudaSuccess) { ready.store(++in, std::memory_order_release); continue; }
-                if (q != cudaErrorNotReady) { ce = q; failed.store(1); break; }
-                CopyPool::cpu_relax();
-            }
-            for (int p; (p = pool->take()) >= 0;) { fn(p); pool->done_one(); }
-            pool->finish();
-            if (ce != cudaSuccess) { err = std::string("token copy: ") + cudaGetErrorString(ce); return false; }
-            GTOK_CUDA(cudaStreamSynchronize(c->stream));
-        } else {
-            if (words) GTOK_CUDA(cudaMemcpyAsync(c->h_out, c->d_out, bytes, cudaMemcpyDeviceToHost, c->stream));
-            if (doc_words) GTOK_CUDA(cudaMemcpyAsync(c->h_out + words, c->d_doc_tok, doc_words * 4, cudaMemcpyDeviceToHost, c->stream));
-            GTOK_CUDA(cudaStreamSynchronize(c->stream));
-            if (words) std::memcpy(out, c->h_out, bytes);
-        }
+        if (doc_words) GTOK_CUDA(cudaMemcpyAsync(c->h_out + words, c->d_doc_tok, doc_words * 4, cudaMemcpyDeviceToHost, c->stream));
+        if (!device_to_host(out, c->h_out, c->d_out, bytes, c->stream, c->out_ev, err)) return false;
         if (doc_words) std::memcpy(out_doc_tok, c->h_out + words, doc_words * 4);
         return true;
     }
@@ -903,8 +920,10 @@ int64_t Engine::decode(const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t m
     DecCtx* c = im.dec.get();
     c->h_in[0] = n;
     c->h_in[1] = c->h_in[2] = c->h_in[3] = 0;
-    std::memcpy(c->h_in + 4, ids, static_cast<size_t>(n) * 4);
-    cudaError_t e = cudaMemcpyAsync(c->d_in, c->h_in, (static_cast<size_t>(n) + 4) * 4, cudaMemcpyHostToDevice, c->stream);
+    cudaError_t e = cudaMemcpyAsync(c->d_in, c->h_in, 16, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess && !im.host_to_device(reinterpret_cast<uint8_t*>(c->d_in + 4), reinterpret_cast<uint8_t*>(c->h_in + 4),
+                                               reinterpret_cast<const uint8_t*>(ids), static_cast<size_t>(n) * 4, c->stream, last_error_))
+        return -1;
     if (e == cudaSuccess) e = cudaEventRecord(c->ev[0], c->stream);
     if (e == cudaSuccess) e = cudaGraphLaunch(c->exec, c->stream);
     if (e == cudaSuccess) e = cudaEventRecord(c->ev[1], c->stream);
@@ -921,11 +940,7 @@ int64_t Engine::decode(const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t m
     if (im.is_pinned(out)) {
         e = cudaMemcpyAsync(out, c->d_out, total, cudaMemcpyDeviceToHost, c->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-    } else {
-        e = cudaMemcpyAsync(c->h_out, c->d_out, total, cudaMemcpyDeviceToHost, c->stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-        if (e == cudaSuccess) std::memcpy(out, c->h_out, total);
-    }
+    } else if (!im.device_to_host(out, c->h_out, c->d_out, total, c->stream, c->out_ev, last_error_)) return -1;
     if (e != cudaSuccess) { last_error_ = std::string("decode copy: ") + cudaGetErrorString(e); return -1; }
     return total;
 }

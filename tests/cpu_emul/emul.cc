@@ -226,9 +226,13 @@ int64_t gtok_emul_decode(void* h, const uint32_t* ids, uint32_t n, uint8_t* out,
     const gtok::HostVocab& hv = e->hv;
     std::vector<uint32_t> off(static_cast<size_t>(hv.vocab_size) + 1, 0);
     std::vector<uint8_t> blob;
+    std::vector<uint32_t> first16(static_cast<size_t>(hv.vocab_size) * 4 + 4, 0);
     for (uint32_t id = 0; id < hv.vocab_size; ++id) {
         off[id] = static_cast<uint32_t>(blob.size());
-        if (id < hv.token_bytes.size()) blob.insert(blob.end(), hv.token_bytes[id].begin(), hv.token_bytes[id].end());
+        if (id >= hv.token_bytes.size()) continue;
+        const std::string& b = hv.token_bytes[id];
+        blob.insert(blob.end(), b.begin(), b.end());
+        std::memcpy(first16.data() + static_cast<size_t>(id) * 4, b.data(), b.size() < 16 ? b.size() : 16);
     }
     off[hv.vocab_size] = static_cast<uint32_t>(blob.size());
     blob.resize(blob.size() + 16);
@@ -247,6 +251,7 @@ int64_t gtok_emul_decode(void* h, const uint32_t* ids, uint32_t n, uint8_t* out,
     a.ids = in.data() + 4;
     a.tok_off = off.data();
     a.blob = blob.data();
+    a.tok16 = first16.data();
     a.vocab_size = hv.vocab_size;
     a.st = st.data();
     a.ctl = ctl;
