@@ -244,6 +244,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="gtok", choices=["gtok", "reference"])
+    ap.add_argument("--decode-only", action="store_true", help="only the decode figures of the workload (1 GPU; profiling runs of decode_kernel)")
     ap.add_argument("--quick", action="store_true", help="skip the CPU baseline and the prompt-latency section (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "gtok" else args.warmup
@@ -272,6 +273,13 @@ def main():
     g = GTok(path, max_bytes=len(doc) + 4096)
     n_bytes = len(doc)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
+
+    if args.decode_only:
+        if world > 1:
+            raise SystemExit("bench.py --decode-only is a 1-GPU run")
+        print(json.dumps({"metric": "decode_of_the_workload_ids", "n_gpus": 1, "decode": decode_numbers(g, doc, flush, reps=max(args.steps, 1))}), flush=True)
+        g.close()
+        return
 
     def barrier():
         torch.cuda.synchronize()

@@ -296,6 +296,9 @@ def test_decode_on_the_device(gtoks, oracles, family):
     assert g.decode(np.zeros(0, dtype=np.uint32)) == b""
     longest = max(table, key=lambda t: len(table[t]))
     assert g.decode(np.full(50000, longest, dtype=np.uint32)) == table[longest] * 50000
+    # thousands of tiles: more than are resident at once, a long look-back chain
+    block = rng.choice(known, size=3001)
+    assert g.decode(np.tile(block, 3000)) == b"".join(table[int(t)] for t in block) * 3000
 
 
 def test_decode_return_codes_and_page_locked_output(gtoks):
