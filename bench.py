@@ -190,6 +190,33 @@ def decode_numbers(g, doc, flush, reps=20):
             "e2e_ms_pageable_output": float(np.median(wall)), "e2e_ms_page_locked_output": float(np.median(wall_pin)), "gpu_launches_per_call": 1}
 
 
+def small_input_latency(path, doc, reps=60):
+    """p50 of gtok_encode (host buffers) on short prefixes of the workload, on a handle created for
+    64 KB inputs: what a short prompt costs (launch and phase latency, not bandwidth)."""
+    from graphtok_b200 import GTok
+    g = GTok(path, max_bytes=64 << 10)
+    out = np.empty((64 << 10) + 16, dtype=np.uint32)
+    res = {}
+    try:
+        for nb in (64, 1024, 16384, 65536):
+            b = bytes(doc[:nb])
+            while b and (b[-1] & 0xC0) == 0x80:       # do not cut a codepoint
+                b = b[:-1]
+            for _ in range(5):
+                g.lib.gtok_encode(g.handle, b, len(b), out.ctypes.data, out.size)
+            ts = []
+            for _ in range(reps):
+                t = time.perf_counter()
+                n = g.lib.gtok_encode(g.handle, b, len(b), out.ctypes.data, out.size)
+                ts.append(time.perf_counter() - t)
+            ts.sort()
+            res["%d_bytes" % nb] = {"p50_us": ts[len(ts) // 2] * 1e6, "p90_us": ts[int(len(ts) * 0.9)] * 1e6, "tokens": int(n)}
+    finally:
+        g.close()
+    res["what"] = "gtok_encode with host buffers on prefixes of the workload document, handle created for 64 KB"
+    return res
+
+
 def cpu_encoder(path):
     """The reference's own host encoder when it was built from its sources, else the oracle port."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -348,6 +375,7 @@ def main():
     if world == 1 and not args.quick:
         latency = prompt_latency(g, path)
     decode = decode_numbers(g, doc, flush) if world == 1 and not args.quick else None
+    small = small_input_latency(path, doc) if world == 1 and not args.quick else None
 
     # ---- reduce over ranks ---------------------------------------------------
     stats = torch.tensor([step_ms, e2e_s * 1e3, float(n_bytes), float(n_tok)] + kern_ms, dtype=torch.float64, device="cuda")
@@ -387,7 +415,7 @@ def main():
         # this workload summarised under profiles/*_kernel_config1.md
         # (the pre-tokenization kernel's figure includes write-back that is not its own, 26.3 MB in this capture:
         # it is the first kernel after the 256 MB L2 flush and the flush's dirty lines leave L2 while it runs)
-        traffic_of = {"pretok_kernel": 5.30e6 + 26.27e6, "words_kernel": 12.61e6, "miss_kernel": 13.89e6 + 0.21e6, "assemble_kernel": 18.39e6}
+        traffic_of = {"pretok_kernel": 5.40e6 + 26.26e6, "words_kernel": 12.61e6, "miss_kernel": 13.88e6 + 0.21e6, "assemble_kernel": 18.39e6}
         dom = int(np.argmax(kern_ms))
         algo = algo_of[names[dom]]
         achieved = algo / (kern_ms[dom] * 1e-3) / 1e9
@@ -413,6 +441,7 @@ def main():
             "clocks": clocks,
             "latency_128k_prompt": latency,
             "decode": decode,
+            "latency_small_inputs": small,
             "wall_s_timed_region": wall,
             "global_token_offsets": [int(x) for x in offsets],
         }
