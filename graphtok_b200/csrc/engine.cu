@@ -906,31 +906,44 @@ int64_t Engine::decode(const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t m
     if (!im.upload_decode_tables(hv_, last_error_)) return -1;
     const uint64_t most = static_cast<uint64_t>(n) * std::max<uint32_t>(im.max_tok_len, 1);
     if (most > 0xFFFFFFF0ull && max_out > 0xFFFFFFF0ull) max_out = 0xFFFFFFF0ull;    // byte offsets are 32-bit on the device
-    const uint64_t want = std::max<uint64_t>(std::min<uint64_t>(most, max_out), 1024);
-    if (!im.dec || im.dec->cap_ids < n || im.dec->cap_bytes < want) {
-        uint32_t cap_ids = 4096;
-        while (cap_ids < n && cap_ids < 0x80000000u) cap_ids <<= 1;
-        if (cap_ids < n) cap_ids = n;
-        size_t cap_bytes = 16384;
-        while (cap_bytes < want) cap_bytes <<= 1;
-        if (im.dec) { cap_ids = std::max(cap_ids, im.dec->cap_ids); cap_bytes = std::max(cap_bytes, im.dec->cap_bytes); }
-        im.dec.reset();
-        if (!im.build_dec(cap_ids, cap_bytes, hv_.vocab_size, last_error_)) { im.dec.reset(); return -1; }
+    // The device buffer starts at 16 bytes per id (spellings average 4-5) and grows to the measured
+    // byte count when that was not enough, rather than to the caller's bound or the longest spelling
+    // times the count.
+    const uint64_t bound = std::max<uint64_t>(std::min<uint64_t>(most, max_out), 1024);
+    uint64_t want = std::min<uint64_t>(bound, 16ull * n + 4096);
+    DecCtx* c = nullptr;
+    uint32_t total = 0, bits = 0;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        if (!im.dec || im.dec->cap_ids < n || im.dec->cap_bytes < want) {
+            uint32_t cap_ids = 4096;
+            while (cap_ids < n && cap_ids < 0x80000000u) cap_ids <<= 1;
+            if (cap_ids < n) cap_ids = n;
+            size_t cap_bytes = 16384;
+            while (cap_bytes < want) cap_bytes <<= 1;
+            if (im.dec) { cap_ids = std::max(cap_ids, im.dec->cap_ids); cap_bytes = std::max(cap_bytes, im.dec->cap_bytes); }
+            im.dec.reset();
+            if (!im.build_dec(cap_ids, cap_bytes, hv_.vocab_size, last_error_)) { im.dec.reset(); return -1; }
+        }
+        c = im.dec.get();
+        c->h_in[0] = n;
+        c->h_in[1] = c->h_in[2] = c->h_in[3] = 0;
+        cudaError_t e = cudaMemcpyAsync(c->d_in, c->h_in, 16, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess && !im.host_to_device(reinterpret_cast<uint8_t*>(c->d_in + 4), reinterpret_cast<uint8_t*>(c->h_in + 4),
+                                                   reinterpret_cast<const uint8_t*>(ids), static_cast<size_t>(n) * 4, c->stream, last_error_))
+            return -1;
+        if (e == cudaSuccess) e = cudaEventRecord(c->ev[0], c->stream);
+        if (e == cudaSuccess) e = cudaGraphLaunch(c->exec, c->stream);
+        if (e == cudaSuccess) e = cudaEventRecord(c->ev[1], c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e != cudaSuccess) { last_error_ = std::string("decode: ") + cudaGetErrorString(e); return -1; }
+        if (kernel_ms) cudaEventElapsedTime(kernel_ms, c->ev[0], c->ev[1]);
+        total = c->h_status[0];
+        bits = c->h_status[1];
+        // the count is exact even when the buffer was too small: once more with room for it
+        if ((bits & kErrOutputFull) && !(bits & (kErrBadId | kErrWaitExpired)) && total > c->cap_bytes && total <= bound) { want = total; continue; }
+        break;
     }
-    DecCtx* c = im.dec.get();
-    c->h_in[0] = n;
-    c->h_in[1] = c->h_in[2] = c->h_in[3] = 0;
-    cudaError_t e = cudaMemcpyAsync(c->d_in, c->h_in, 16, cudaMemcpyHostToDevice, c->stream);
-    if (e == cudaSuccess && !im.host_to_device(reinterpret_cast<uint8_t*>(c->d_in + 4), reinterpret_cast<uint8_t*>(c->h_in + 4),
-                                               reinterpret_cast<const uint8_t*>(ids), static_cast<size_t>(n) * 4, c->stream, last_error_))
-        return -1;
-    if (e == cudaSuccess) e = cudaEventRecord(c->ev[0], c->stream);
-    if (e == cudaSuccess) e = cudaGraphLaunch(c->exec, c->stream);
-    if (e == cudaSuccess) e = cudaEventRecord(c->ev[1], c->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-    if (e != cudaSuccess) { last_error_ = std::string("decode: ") + cudaGetErrorString(e); return -1; }
-    if (kernel_ms) cudaEventElapsedTime(kernel_ms, c->ev[0], c->ev[1]);
-    const uint32_t total = c->h_status[0], bits = c->h_status[1];
+    cudaError_t e = cudaSuccess;
     if (bits & kErrBadId) { last_error_ = "decode: an id is outside the vocabulary"; return -1; }
     if (bits & kErrWaitExpired) { last_error_ = "decode: a wait on an earlier tile gave up"; return -1; }
     if (need) *need = total;

@@ -126,7 +126,8 @@ int32_t gtok_x_token_bytes(void* handle, uint32_t id, uint8_t* out, uint32_t cap
  * (src/tokenizer.cu:5499-5573, kernels :5225-5275) behind Tokenizer.decode / decode_bytes
  * (src/python_bindings.cc:558-600); the reference's C ABI has no decode entry.  Host buffers.
  * Returns the byte count; -1 on error (an id outside the vocabulary included); -2 when
- * `max_out` is too small.  `need_out` (may be NULL) receives the byte count in both cases,
+ * `max_out` is too small (out = NULL with max_out = 0 asks for the size).  `need_out` (may be NULL)
+ * receives the byte count in both cases,
  * `kernel_ms` (may be NULL) the CUDA-event time of the graph. */
 int64_t gtok_x_decode(void* handle, const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t max_out, uint64_t* need_out, float* kernel_ms);
 

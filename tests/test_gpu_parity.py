@@ -311,6 +311,8 @@ def test_decode_return_codes_and_page_locked_output(gtoks):
     small = np.zeros(len(want) - 1, dtype=np.uint8)
     r = g.lib.gtok_x_decode(g.handle, ids.ctypes.data, ids.size, small.ctypes.data, small.size, ctypes.byref(need), None)
     assert r == -2 and need.value == len(want)
+    r = g.lib.gtok_x_decode(g.handle, ids.ctypes.data, ids.size, None, 0, ctypes.byref(need), None)      # size query
+    assert r == -2 and need.value == len(want)
     exact = np.zeros(len(want), dtype=np.uint8)
     r = g.lib.gtok_x_decode(g.handle, ids.ctypes.data, ids.size, exact.ctypes.data, exact.size, ctypes.byref(need), None)
     assert r == len(want) and exact.tobytes() == want
