@@ -76,6 +76,8 @@ def load_lib():
     lib.gtok_x_boundaries_noalloc.argtypes = [vp, vp, u32, vp, vp]
     lib.gtok_x_phase_clocks.restype = i32
     lib.gtok_x_phase_clocks.argtypes = [vp, vp, i32]
+    lib.gtok_x_timeline.restype = i32
+    lib.gtok_x_timeline.argtypes = [vp, vp, u32]
     lib.gtok_x_token_bytes.restype = i32
     lib.gtok_x_token_bytes.argtypes = [vp, u32, vp, u32]
     lib.gtok_x_decode.restype = ctypes.c_int64

@@ -14,6 +14,7 @@ constexpr uint32_t kNoRank = 0xFFFFFFFFu;
 constexpr uint32_t kEmptyKey = 0xFFFFFFFFu;
 constexpr uint32_t kNoToken = 0xFFFFFFFFu;
 constexpr int kWordKeyMax = 15;        // longest pre-token the inline-key word table holds
+constexpr int kLitLens = 16;           // distinct added-token literal lengths the hashed matcher takes
 constexpr int kProbeLimit = 64;        // every table is built so that no probe chain is longer
 
 // Merge rule table: two-choice (cuckoo) hashing over 16-byte slots.  A rule sits in one of
@@ -60,6 +61,18 @@ struct DeviceTables {
     const uint32_t* trie_skip;
     const uint8_t* trie_blob;
     uint32_t added_max_bytes;            // 0 when the vocabulary has no added tokens
+    uint32_t lit1_bits[8];               // bytes that open an added-token literal (one bit per byte value)
+    uint32_t lit2_bits[8];               // bytes that come second in one
+    uint32_t lit_single;                 // some literal is a single byte
+    // The literals once more as a hash table keyed by their bytes (slots as in the long-token table,
+    // spellings 16-byte aligned in lit_blob), with the distinct literal lengths in ascending order:
+    // the longest literal at a position is then found with one pass over the text bytes and one
+    // round of independent probes instead of a walk down the trie.  lit_n_lens == 0 (more than
+    // kLitLens distinct lengths): only the trie is used.
+    const LongSlot* littab;     uint32_t lit_mask;
+    const uint8_t* lit_blob;
+    uint32_t lit_n_lens;
+    uint32_t lit_lens[16];
     uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5
     uint32_t ignore_merges;
     uint32_t monotone;

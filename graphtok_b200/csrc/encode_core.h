@@ -50,6 +50,23 @@ constexpr int kHaloL = 128;
 constexpr int kHaloR = 64;
 constexpr int kWin = kHaloL + kTile + kHaloR;
 constexpr int kTileWords = kTile / 32;
+// Pre-tokenization works on tiles of its own: a window of two 16-byte chunks per thread (halos
+// included), so that every thread has the same work in the chunk phases and a document of up to
+// about 4.7 MB is a single wave of blocks on a B200.
+constexpr int kPChunks = 2 * kThreads;
+constexpr int kPWin = kPChunks * 16;                    // 8192 bytes staged per tile
+constexpr int kPTile = kPWin - kHaloL - kHaloR;         // 8000 bytes of text per tile
+constexpr int kPTileWords = kPTile / 32;                // 250 mask words per tile
+constexpr int kUcStage1Bmp = 512;        // first-stage entries of the class table that cover U+0000..U+FFFF (128 codepoints each)
+constexpr int kUcStage2Words = 1664;     // words of its second stage (unicode_class_table.h; checked where the tables are uploaded)
+
+// Diagnostics (contexts created with GTOK_PHASE_CLOCKS set): 32 phase counters, then for each of the
+// four kernels and each of its first kTlBlocks blocks kTlSlots nanosecond stamps of the GPU's global
+// timer: [0] block started, [1] block finished, [2..] its first work items finished.
+constexpr int kPhaseWords = 32;
+constexpr int kTlBlocks = 1280;
+constexpr int kTlSlots = 8;
+constexpr int kTlWords = 6 * kTlBlocks * kTlSlots;     // tables 4 and 5: end of each pre-tokenization phase in a block's first and second tile
 
 constexpr uint32_t kInvalidTok = 0xFFFFFFFFu;
 constexpr uint32_t kLongRef = 0x80000000u;      // tok[] entry that stands for a whole long pre-token
@@ -105,7 +122,7 @@ struct EncodeArgs {
     uint32_t out_cap;
     uint32_t* out_doc_tok;        // [n_docs + 1] token offsets (batch) or nullptr
     uint32_t* status;             // [0] total tokens, [1] error bits (host-visible)
-    unsigned long long* phase_clk; // optional: cycles spent per phase, summed over blocks (diagnostics)
+    unsigned long long* phase_clk; // optional: cycles spent per phase, summed over blocks (diagnostics); from word kPhaseWords on, the block timeline
     // Normalisation (vocabularies that declare NFC); raw == nullptr otherwise.
     const uint8_t* raw;           // text as the caller gave it, padded like `text`
     const uint32_t* raw_meta;     // [0] = bytes, [1] = documents, [2] = 1 when the text is normalised already
@@ -164,6 +181,13 @@ GTOK_DEV uint32_t shared_add(uint32_t* p, uint32_t v) {
     return atomicAdd(p, v);
 #else
     uint32_t o = *p; *p = o + v; return o;
+#endif
+}
+GTOK_DEV void shared_or(uint32_t* p, uint32_t v) {
+#if defined(__CUDA_ARCH__)
+    atomicOr(p, v);
+#else
+    *p |= v;
 #endif
 }
 GTOK_DEV void global_or(uint32_t* p, uint32_t v) {
@@ -368,21 +392,38 @@ GTOK_DEV uint8_t onehot_of(uint8_t at) {
 GTOK_DEV uint32_t gather_bit4(uint32_t w, int k) { return (((w >> k) & 0x01010101u) * 0x01020408u) >> 24; }
 
 struct PretokSmem {
-    alignas(16) uint8_t txt[kWin + 16];
-    alignas(16) uint8_t attr[kWin + 16];
-    alignas(16) uint8_t oh[kWin + 16];       // one-hot class + flags per byte (see kOh*)
-    alignas(4) uint16_t plane[kPlanes][kWin / 16 + 4];   // bit planes of the window, 16 bytes per entry
-    uint16_t lut[128];                       // ASCII byte -> attr | one-hot << 8
-    uint32_t rootbits[8];                    // bytes that can start an added-token literal
-    uint32_t dsw[kWin / 32 + 2];             // document-start bits of the window
-    uint16_t bnd16[kThreads + 2], add16[kThreads + 2], pend16[kThreads + 2];
-    uint16_t lead16[kThreads + 2], nlead16[kThreads + 2], nstart16[kThreads + 2];
-    uint32_t carry[kTileWords + 1];
-    uint32_t sum_has[32], sum_cnt[32];
+    alignas(16) uint8_t txt[kPWin + 16];
+    alignas(16) uint8_t attr[kPWin + 16];
+    alignas(16) uint8_t oh[kPWin + 16];       // one-hot class + flags per byte (see kOh*)
+    alignas(4) uint16_t plane[kPlanes][kPWin / 16 + 4];   // bit planes of the window, 16 bytes per entry
+    uint32_t lut[256];                       // byte -> attr | one-hot << 8 | (opens an added-token literal) << 16: ASCII as classified, continuation bytes, lead bytes as "other" until decoded
+    uint16_t cand16[kPWin / 16 + 4];          // per 16-byte chunk: bytes that open an added-token literal
+    alignas(16) uint16_t ucs1[kUcStage1Bmp]; // the class table's first stage for the BMP and its whole second stage, copied once per block
+    alignas(16) uint32_t ucs2[kUcStage2Words];
+    uint32_t dirty[(kPWin / 16 + 31) / 32];   // chunks whose plane entries a painted literal has made stale
+    uint32_t dsw[kPWin / 32 + 2];             // document-start bits of the window
+    uint16_t bnd16[2 * kPTileWords + 4], add16[2 * kPTileWords + 4], pend16[2 * kPTileWords + 4];
+    uint16_t lead16[2 * kPTileWords + 4], nlead16[2 * kPTileWords + 4], nstart16[2 * kPTileWords + 4];
+    uint32_t carry[kPTileWords + 8];
+    uint32_t sum_has[32], sum_cnt[32], lane_last[32], lane_firstn[32];
     uint32_t scan[kThreads];
     uint32_t misc[8];
     unsigned long long clk_last;
 };
+
+// The nine plane entries of 16-byte chunk c from its one-hot bytes and its text.
+GTOK_DEV void chunk_planes(PretokSmem& sm, int c, const uint32_t* ow, const uint32_t* tw) {
+    for (int k = 0; k < 8; ++k)
+        sm.plane[k][c] = static_cast<uint16_t>(gather_bit4(ow[0], k) | (gather_bit4(ow[1], k) << 4) | (gather_bit4(ow[2], k) << 8) | (gather_bit4(ow[3], k) << 12));
+    uint32_t ap = 0;
+    for (int j = 0; j < 4; ++j) {
+        uint32_t x = tw[j] ^ 0x27272727u;                      // a zero byte marks an apostrophe
+        uint32_t z = (x - 0x01010101u) & ~x & 0x80808080u;
+        // the borrow trick can flag a byte above a true zero; apostrophes are rare, so check exactly
+        if (z) for (int k = 0; k < 4; ++k) if (((tw[j] >> (8 * k)) & 0xFFu) == 0x27u) ap |= 1u << (j * 4 + k);
+    }
+    sm.plane[PL_AP][c] = static_cast<uint16_t>(ap);
+}
 
 // View of one tile's window for the predicate code.
 struct Win {
@@ -427,6 +468,60 @@ GTOK_DEV uint32_t match_literal(const EncodeArgs& a, int s, int n, GetByte byte_
         ++q;
     }
     return best;
+}
+
+// The same answer from the hashed literal table: one pass over the text bytes keeps the running
+// hash; at every length some literal has the table is asked, and a slot whose hash and length
+// agree is confirmed against the literal's bytes, four at a time.  The longest confirmed literal
+// wins.  Everything stays in registers (no arrays: this runs with next to no L1 behind local memory).
+template <class GetByte>
+GTOK_DEV uint32_t match_literal_hashed(const EncodeArgs& a, int s, int n, GetByte byte_at, uint32_t* id_out) {
+    const DeviceTables& tb = a.tb;
+    uint32_t limit = static_cast<uint32_t>(n - s);
+    if (limit > tb.added_max_bytes) limit = tb.added_max_bytes;
+    if (a.docmask) for (uint32_t k = 1; k < limit; ++k) if (is_docstart_global(a, s + static_cast<int>(k))) { limit = k; break; }
+    uint32_t best = 0, li = 0;
+    uint64_t h = kLongHashSeed;
+    for (uint32_t len = 1; len <= limit && li < tb.lit_n_lens; ++len) {
+        h = long_hash_step(h, static_cast<uint8_t>(byte_at(s + static_cast<int>(len) - 1)));
+        if (len != tb.lit_lens[li]) continue;
+        ++li;
+        const uint64_t hf = long_hash_finish(h, len);
+        uint32_t at = static_cast<uint32_t>(hf) & tb.lit_mask;
+        for (int i = 0; i < kProbeLimit; ++i) {
+            const LongSlot& sl = tb.littab[at];
+            const uint32_t id = ldg(&sl.id);
+            if (id == kNoToken) break;
+            if (ldg(&sl.hash) == hf && ldg(&sl.len) == len) {
+                const uint32_t off = ldg(&sl.off);                 // 16-byte aligned, zero padded
+                uint32_t diff = 0;
+                for (uint32_t j = 0; j < len; j += 4) {
+                    const uint32_t lw = ldg(reinterpret_cast<const uint32_t*>(tb.lit_blob + off + j));
+                    uint32_t tw = 0;
+                    for (uint32_t b = 0; b < 4 && j + b < len; ++b) tw |= byte_at(s + static_cast<int>(j + b)) << (8 * b);
+                    diff |= lw ^ tw;
+                }
+                if (!diff) { best = len; *id_out = id; break; }
+            }
+            at = (at + 1) & tb.lit_mask;
+        }
+    }
+    return best;
+}
+template <class GetByte>
+GTOK_DEV uint32_t longest_literal(const EncodeArgs& a, int s, int n, GetByte byte_at, uint32_t* id_out) {
+    return a.tb.lit_n_lens ? match_literal_hashed(a, s, n, byte_at, id_out) : match_literal(a, s, n, byte_at, id_out);
+}
+
+// The literal at global position s as seen from a tile's window (text bytes in shared memory from
+// global position lo on, the rest from global memory).  A function of its own, not inlined: it runs
+// for a handful of bytes per tile and must not cost the tile program registers.
+GTOK_DEV_NOINLINE uint32_t literal_in_window(const EncodeArgs& a, const uint8_t* win_txt, int lo, int s, int n, uint32_t* id_out) {
+    auto byte_at = [&](int q) -> uint32_t {
+        const int i = q - lo;
+        return (i >= 0 && i < kPWin) ? win_txt[i] : ldg(a.text + q);
+    };
+    return longest_literal(a, s, n, byte_at, id_out);
 }
 
 // Class + flags of a byte, ignoring added tokens.  `byte_at(q)` must be valid for
@@ -474,7 +569,7 @@ GTOK_DEV_NOINLINE uint8_t attr_global(const EncodeArgs& a, int p, int n) {
         for (int s = p; s >= lim; --s) {
             if (ldg(a.tb.trie_root + byte_at(s)) != kNoToken) {
                 uint32_t id;
-                uint32_t ml = match_literal(a, s, n, byte_at, &id);
+                uint32_t ml = longest_literal(a, s, n, byte_at, &id);
                 if (ml && s + static_cast<int>(ml) > p) {
                     uint8_t flags = is_doc(p) ? A_DOC : 0;
                     return static_cast<uint8_t>((s == p ? A_ADDED : A_CONT) | flags);
@@ -773,14 +868,38 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
     return true;
 }
 
+// Once per block, before its first tile: the byte table and the block's copy of the class table.
+template <class Blk>
+GTOK_DEV void pretok_block_init(Blk& blk, const EncodeArgs& a, PretokSmem& sm) {
+    blk.par([&](int tid) {
+#if defined(__CUDA_ARCH__)
+        // 128-bit copies (both arrays are whole multiples of 16 bytes and 16-byte aligned in device memory)
+        for (int i = tid; i < kUcStage1Bmp / 8; i += kThreads) reinterpret_cast<uint4*>(sm.ucs1)[i] = __ldg(reinterpret_cast<const uint4*>(a.tb.uc_stage1) + i);
+        for (int i = tid; i < kUcStage2Words / 4; i += kThreads) reinterpret_cast<uint4*>(sm.ucs2)[i] = __ldg(reinterpret_cast<const uint4*>(a.tb.uc_stage2) + i);
+#else
+        for (int i = tid; i < kUcStage1Bmp; i += kThreads) sm.ucs1[i] = ldg(a.tb.uc_stage1 + i);
+        for (int i = tid; i < kUcStage2Words; i += kThreads) sm.ucs2[i] = ldg(a.tb.uc_stage2 + i);
+#endif
+        uint8_t at;
+        if (tid < 128) {
+            const uint32_t leaf = ldg(a.tb.uc_stage1);                       // codepoints 0..127 share stage-1 entry 0
+            const uint32_t wv = ldg(a.tb.uc_stage2 + leaf * 8u + (static_cast<uint32_t>(tid) >> 4));
+            at = static_cast<uint8_t>((wv >> ((tid & 15) * 2)) & 3u);
+            if (tid == 0x0A || tid == 0x0D) at |= A_CRLF;
+            if (tid == 0x20) at |= A_SP;
+        } else at = tid < 0xC0 ? A_CONT : A_O;
+        sm.lut[tid] = at | (static_cast<uint32_t>(onehot_of(at)) << 8) | (((a.tb.lit1_bits[tid >> 5] >> (tid & 31)) & 1u) << 16);
+    });
+}
+
 // One tile of pre-tokenization.
 template <class Blk>
 GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int tile) {
     const int n = static_cast<int>(ldg(a.meta));
-    const int t0 = tile * kTile;
+    const int t0 = tile * kPTile;
     const int lo = t0 - kHaloL;
     const uint32_t family = a.tb.family;
-    const int n_chunks = kWin / 16;
+    const int n_chunks = kPWin / 16;
     // Diagnostics only: cycles between phase ends, block-summed into phase_clk[slot].
     auto mark = [&](int slot) {
         if (!a.phase_clk) return;
@@ -789,28 +908,28 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             unsigned long long t = cycle_now();
             if (slot >= 0) add_cycles(a.phase_clk + slot, t - sm.clk_last);
             sm.clk_last = t;
+#if defined(__CUDA_ARCH__)
+            if (sm.misc[2] < 2u && blockIdx.x < kTlBlocks) {
+                unsigned long long ns;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+                a.phase_clk[kPhaseWords + (static_cast<size_t>(4 + sm.misc[2]) * kTlBlocks + blockIdx.x) * kTlSlots + (slot + 1)] = ns;
+            }
+#endif
         });
     };
     mark(-1);
 
-    // ---- P0: stage the window; ASCII lookup table ----
+    // ---- P0/P1: each thread fetches 16 bytes and classifies them at once ----
+    // Text, per-byte class and flags, the one-hot byte and the chunk's entries of the nine bit
+    // planes go to shared memory together; nothing here reads what another thread writes.
+    // ASCII and continuation bytes through the 256-entry table, the lead bytes of longer sequences
+    // decoded leniently (src/pretok_boundary.h:43-57: the lead byte decides the width when that
+    // many bytes remain in the document, anything else is a one-byte codepoint) and looked up in
+    // the block's copy of the class table.
     blk.par([&](int tid) {
-        for (int c = tid; c < n_chunks; c += kThreads) {
-            int p = lo + c * 16;
-            uint32_t* dst = reinterpret_cast<uint32_t*>(sm.txt + c * 16);
-            if (p >= 0 && p < n) {
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(a.text + p);
-#if defined(__CUDA_ARCH__)
-                uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
-                *reinterpret_cast<uint4*>(dst) = v;
-#else
-                for (int k = 0; k < 4; ++k) dst[k] = src[k];
-#endif
-            } else {
-                dst[0] = dst[1] = dst[2] = dst[3] = 0;
-            }
-        }
-        for (int wd = tid; wd < kWin / 32 + 2; wd += kThreads) {
+        if (tid == 0) sm.misc[1] = 0;
+        if (tid < static_cast<int>(sizeof(sm.dirty) / 4)) sm.dirty[tid] = 0;
+        for (int wd = tid; wd < kPWin / 32 + 2; wd += kThreads) {
             int gw = (lo >> 5) + wd;                 // lo is a multiple of 32
             uint32_t v = 0;
             if (gw >= 0 && gw * 32 < n) {
@@ -819,138 +938,191 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             }
             sm.dsw[wd] = v;
         }
-        if (tid < 128) {
-            uint32_t leaf = ldg(a.tb.uc_stage1);                       // codepoints 0..127 share stage-1 entry 0
-            uint32_t wv = ldg(a.tb.uc_stage2 + leaf * 8u + (static_cast<uint32_t>(tid) >> 4));
-            uint8_t at = static_cast<uint8_t>((wv >> ((tid & 15) * 2)) & 3u);
-            if (tid == 0x0A || tid == 0x0D) at |= A_CRLF;
-            if (tid == 0x20) at |= A_SP;
-            sm.lut[tid] = static_cast<uint16_t>(at | (onehot_of(at) << 8));
+        // both of the thread's chunks are requested before either is looked at
+        uint32_t both[kPChunks / kThreads][4];
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int h = 0; h < kPChunks / kThreads; ++h) {
+            const int p0 = lo + (tid + h * kThreads) * 16;
+            both[h][0] = both[h][1] = both[h][2] = both[h][3] = 0;
+            if (p0 >= 0 && p0 < n) {
+#if defined(__CUDA_ARCH__)
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.text + p0));
+                both[h][0] = v.x; both[h][1] = v.y; both[h][2] = v.z; both[h][3] = v.w;
+#else
+                for (int k = 0; k < 16; ++k) both[h][k >> 2] |= static_cast<uint32_t>(a.text[p0 + k]) << (8 * (k & 3));
+#endif
+            }
         }
-        if (tid >= 128 && tid < 136 && a.tb.added_max_bytes) {
-            uint32_t bits = 0;
-            for (int k = 0; k < 32; ++k) if (ldg(a.tb.trie_root + (tid - 128) * 32 + k) != kNoToken) bits |= 1u << k;
-            sm.rootbits[tid - 128] = bits;
-        }
-    });
-
-    mark(0);
-    auto sm_is_doc = [&](int p) -> bool {   // p within [lo, lo + kWin + 64)
-        int i = p - lo;
-        return (sm.dsw[i >> 5] >> (i & 31)) & 1u;
-    };
-    auto byte_any = [&](int q) -> uint32_t {
-        int i = q - lo;
-        return (i >= 0 && i < kWin) ? sm.txt[i] : ldg(a.text + q);
-    };
-
-    // ---- P1: per-byte class and flags (ASCII through the table, the rest decoded after) ----
-    blk.par([&](int tid) {
-        for (int c = tid; c < n_chunks; c += kThreads) {
-            const uint32_t* tw = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
-            uint32_t* aw = reinterpret_cast<uint32_t*>(sm.attr + c * 16);
-            uint32_t* ow = reinterpret_cast<uint32_t*>(sm.oh + c * 16);
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int h = 0; h < kPChunks / kThreads; ++h) {
+            const int c = tid + h * kThreads;
             const int i0 = c * 16, p0 = lo + i0;
-            const uint32_t ds = (sm.dsw[i0 >> 5] >> (i0 & 31)) & 0xFFFFu;
-            uint32_t slow = 0;                                  // non-ASCII lead bytes, decoded below
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t t = tw[j];
-                uint32_t av = 0, ov = 0;
-                for (int k = 0; k < 4; ++k) {
-                    const int i = j * 4 + k, p = p0 + i;
-                    const uint32_t bt = (t >> (8 * k)) & 0xFFu;
-                    uint32_t at, oh;
-                    if (p < 0 || p >= n) { at = A_OUT; oh = 0; }
-                    else if (bt < 0x80u) { uint32_t v = sm.lut[bt]; at = v & 0xFFu; oh = v >> 8; }
-                    else if ((bt & 0xC0u) == 0x80u) { at = A_CONT; oh = kOhC; }
-                    else { at = A_O; oh = kOhO; slow |= 1u << i; }
-                    if ((ds >> i) & 1u) at |= A_DOC;
-                    av |= at << (8 * k);
-                    ov |= oh << (8 * k);
-                }
-                aw[j] = av;
-                ow[j] = ov;
+            uint32_t tw[4] = {both[h][0], both[h][1], both[h][2], both[h][3]}, aw[4], ow[4];
+            if (p0 + 16 <= 0 || p0 >= n) {
+                // wholly outside the text
+                uint32_t* txw = reinterpret_cast<uint32_t*>(sm.txt + i0);
+                uint32_t* atw = reinterpret_cast<uint32_t*>(sm.attr + i0);
+                uint32_t* ohw = reinterpret_cast<uint32_t*>(sm.oh + i0);
+                for (int k = 0; k < 4; ++k) { txw[k] = 0; atw[k] = A_OUT * 0x01010101u; ohw[k] = 0; }
+                for (int k = 0; k < kPlanes; ++k) sm.plane[k][c] = 0;
+                sm.cand16[c] = 0;
+                continue;
             }
-            while (slow) {
-                const int i = ffs32(slow);
-                slow &= slow - 1;
-                const int wi = i0 + i, p = p0 + i;
-                const uint32_t b = sm.txt[wi];
-                int avail = n - p;
-                if (avail > 4) avail = 4;
-                if (a.docmask) for (int k = 1; k < avail; ++k) if (sm_is_doc(p + k)) { avail = k; break; }
-                uint32_t b1, b2, b3;
-                if (wi + 3 < kWin) { b1 = sm.txt[wi + 1]; b2 = sm.txt[wi + 2]; b3 = sm.txt[wi + 3]; }
-                else { b1 = avail > 1 ? byte_any(p + 1) : 0; b2 = avail > 2 ? byte_any(p + 2) : 0; b3 = avail > 3 ? byte_any(p + 3) : 0; }
-                // lenient decode (src/pretok_boundary.h:43-57): the lead byte decides the width when
-                // that many bytes remain in the document; anything else is a one-byte codepoint
-                uint32_t cp = b;
-                if ((b & 0xE0u) == 0xC0u && avail >= 2) cp = ((b & 0x1Fu) << 6) | (b1 & 0x3Fu);
-                else if ((b & 0xF0u) == 0xE0u && avail >= 3) cp = ((b & 0x0Fu) << 12) | ((b1 & 0x3Fu) << 6) | (b2 & 0x3Fu);
-                else if ((b & 0xF8u) == 0xF0u && avail >= 4) cp = ((b & 0x07u) << 18) | ((b1 & 0x3Fu) << 12) | ((b2 & 0x3Fu) << 6) | (b3 & 0x3Fu);
-                uint32_t cls = A_O;
-                if (cp <= 0x10FFFFu) {
-                    uint32_t leaf = ldg(a.tb.uc_stage1 + (cp >> 7));
-                    uint32_t wv = ldg(a.tb.uc_stage2 + leaf * 8u + ((cp & 127u) >> 4));
-                    cls = (wv >> ((cp & 15u) * 2u)) & 3u;
+            uint32_t ds = 0;
+            {
+                const int gw = p0 >> 5;
+                if (gw >= 0 && gw * 32 < n) {
+                    uint32_t v = a.docmask ? ldg(a.docmask + gw) : 0u;
+                    if (gw == 0) v |= 1u;
+                    ds = (v >> (p0 & 31)) & 0xFFFFu;
                 }
-                sm.attr[wi] = static_cast<uint8_t>(cls | (sm.attr[wi] & A_DOC));
-                sm.oh[wi] = static_cast<uint8_t>(1u << cls);
             }
+            uint32_t slow = 0;                                  // lead bytes of multi-byte sequences, decoded below
+            uint32_t cand = 0;                                  // bytes that open an added-token literal
+            if (p0 >= 0 && p0 + 16 <= n) {
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t t = tw[j];
+                    const uint32_t v0 = sm.lut[t & 0xFFu], v1 = sm.lut[(t >> 8) & 0xFFu], v2 = sm.lut[(t >> 16) & 0xFFu], v3 = sm.lut[t >> 24];
+                    aw[j] = (v0 & 0xFFu) | ((v1 & 0xFFu) << 8) | ((v2 & 0xFFu) << 16) | ((v3 & 0xFFu) << 24);
+                    ow[j] = ((v0 >> 8) & 0xFFu) | (v1 & 0xFF00u) | ((v2 & 0xFF00u) << 8) | ((v3 & 0xFF00u) << 16);
+                    cand |= (((v0 >> 16) & 1u) | ((v1 >> 15) & 2u) | ((v2 >> 14) & 4u) | ((v3 >> 13) & 8u)) << (4 * j);
+                    const uint32_t lead = t & (t << 1) & 0x80808080u;       // bytes 11xxxxxx
+                    slow |= (((lead >> 7) * 0x00204081u) >> 21 & 0xFu) << (4 * j);
+                }
+            } else {
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t av = 0, ov = 0;
+                    for (int k = 0; k < 4; ++k) {
+                        const int i = j * 4 + k, p = p0 + i;
+                        const uint32_t bt = (tw[j] >> (8 * k)) & 0xFFu;
+                        uint32_t at = A_OUT, oh = 0;
+                        if (p >= 0 && p < n) {
+                            const uint32_t v = sm.lut[bt];
+                            at = v & 0xFFu; oh = (v >> 8) & 0xFFu;
+                            cand |= ((v >> 16) & 1u) << i;
+                            if (bt >= 0xC0u) slow |= 1u << i;
+                        }
+                        av |= at << (8 * k);
+                        ov |= oh << (8 * k);
+                    }
+                    aw[j] = av;
+                    ow[j] = ov;
+                }
+            }
+            uint32_t* txw = reinterpret_cast<uint32_t*>(sm.txt + i0);
+            uint32_t* atw = reinterpret_cast<uint32_t*>(sm.attr + i0);
+            uint32_t* ohw = reinterpret_cast<uint32_t*>(sm.oh + i0);
+#if defined(__CUDA_ARCH__)
+            *reinterpret_cast<uint4*>(txw) = make_uint4(tw[0], tw[1], tw[2], tw[3]);
+            *reinterpret_cast<uint4*>(atw) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+            *reinterpret_cast<uint4*>(ohw) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+#else
+            for (int k = 0; k < 4; ++k) { txw[k] = tw[k]; atw[k] = aw[k]; ohw[k] = ow[k]; }
+#endif
+            if (ds | slow) {
+                // the rarer bytes are put right in shared memory (this thread's own chunk)
+                for (uint32_t d = ds; d;) {
+                    const int i = ffs32(d);
+                    d &= d - 1;
+                    sm.attr[i0 + i] |= A_DOC;
+                }
+                while (slow) {
+                    const int i = ffs32(slow);
+                    slow &= slow - 1;
+                    const int p = p0 + i;
+                    const uint32_t b = sm.txt[i0 + i];
+                    int avail = n - p;
+                    if (avail > 4) avail = 4;
+                    if (a.docmask) for (int k = 1; k < avail; ++k) if (is_docstart_global(a, p + k)) { avail = k; break; }
+                    const uint32_t b1 = avail > 1 ? ldg(a.text + p + 1) : 0u, b2 = avail > 2 ? ldg(a.text + p + 2) : 0u, b3 = avail > 3 ? ldg(a.text + p + 3) : 0u;
+                    uint32_t cp = b;
+                    if ((b & 0xE0u) == 0xC0u && avail >= 2) cp = ((b & 0x1Fu) << 6) | (b1 & 0x3Fu);
+                    else if ((b & 0xF0u) == 0xE0u && avail >= 3) cp = ((b & 0x0Fu) << 12) | ((b1 & 0x3Fu) << 6) | (b2 & 0x3Fu);
+                    else if ((b & 0xF8u) == 0xF0u && avail >= 4) cp = ((b & 0x07u) << 18) | ((b1 & 0x3Fu) << 12) | ((b2 & 0x3Fu) << 6) | (b3 & 0x3Fu);
+                    uint32_t cls = A_O;
+                    if (cp < 0x10000u) {
+                        const uint32_t leaf = sm.ucs1[cp >> 7];
+                        cls = (sm.ucs2[leaf * 8u + ((cp & 127u) >> 4)] >> ((cp & 15u) * 2u)) & 3u;
+                    } else if (cp <= 0x10FFFFu) {
+                        const uint32_t leaf = ldg(a.tb.uc_stage1 + (cp >> 7));
+                        cls = (ldg(a.tb.uc_stage2 + leaf * 8u + ((cp & 127u) >> 4)) >> ((cp & 15u) * 2u)) & 3u;
+                    }
+                    sm.attr[i0 + i] = static_cast<uint8_t>(cls | (sm.attr[i0 + i] & A_DOC));
+                    sm.oh[i0 + i] = static_cast<uint8_t>(1u << cls);
+                }
+                ow[0] = ohw[0]; ow[1] = ohw[1]; ow[2] = ohw[2]; ow[3] = ohw[3];
+            }
+            chunk_planes(sm, c, ow, tw);
+            sm.cand16[c] = static_cast<uint16_t>(cand);
         }
     });
 
     mark(1);
+    auto byte_any = [&](int q) -> uint32_t {
+        int i = q - lo;
+        return (i >= 0 && i < kPWin) ? sm.txt[i] : ldg(a.text + q);
+    };
     // ---- P2: paint added-token literals ----
+    // A literal can only start at a byte that opens one and is followed by a byte that is second in
+    // one (two 256-bit sets that come with the tables), so the trie is walked at next to no false starts.
     if (a.tb.added_max_bytes) {
         blk.par([&](int tid) {
             for (int c = tid; c < n_chunks; c += kThreads) {
-                for (int k = 0; k < 16; ++k) {
-                    int i = c * 16 + k, p = lo + i;
+                uint32_t cand = sm.cand16[c];
+                while (cand) {
+                    const int k = ffs32(cand);
+                    cand &= cand - 1;
+                    const int i = c * 16 + k, p = lo + i;
                     if (p < 0 || p >= n) continue;
-                    const uint32_t bt = sm.txt[i];
-                    if (!((sm.rootbits[bt >> 5] >> (bt & 31)) & 1u)) continue;
+                    if (!a.tb.lit_single) {                 // every literal has a second byte: it must follow
+                        if (p + 1 >= n) continue;
+                        const uint32_t b2 = byte_any(p + 1);
+                        if (!((a.tb.lit2_bits[b2 >> 5] >> (b2 & 31)) & 1u)) continue;
+                    }
                     uint32_t id;
-                    uint32_t ml = match_literal(a, p, n, byte_any, &id);
+                    uint32_t ml = literal_in_window(a, sm.txt, lo, p, n, &id);
                     if (!ml) continue;
                     // the id goes to the literal's slot at once, so that the next kernel need not walk the trie again
-                    if (a.stage && p >= t0 && p < t0 + kTile) a.stage[p] = id;
+                    if (a.stage && p >= t0 && p < t0 + kPTile) a.stage[p] = id;
                     sm.attr[i] = static_cast<uint8_t>(A_ADDED | (sm.attr[i] & A_DOC));
                     sm.oh[i] = kOhAdded;
-                    for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kWin; ++j) {
+                    for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kPWin; ++j) {
                         sm.attr[i + j] = static_cast<uint8_t>(A_CONT | (sm.attr[i + j] & A_DOC));
                         sm.oh[i + j] = kOhC | kOhAdded;          // both bits: inside a literal
                     }
+                    const int c_last = (i + static_cast<int>(ml) - 1 < kPWin ? i + static_cast<int>(ml) - 1 : kPWin - 1) >> 4;
+                    for (int cc = c; cc <= c_last; ++cc) shared_or(&sm.dirty[cc >> 5], 1u << (cc & 31));
+                    sm.misc[1] = 1;
                 }
             }
         });
-    }
-
-    mark(2);
-    // ---- P2b: bit planes, 16 bytes per entry ----
-    blk.par([&](int tid) {
-        for (int c = tid; c < n_chunks; c += kThreads) {
-            const uint32_t* ow = reinterpret_cast<const uint32_t*>(sm.oh + c * 16);
-            const uint32_t* tw = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
-            const uint32_t o0 = ow[0], o1 = ow[1], o2 = ow[2], o3 = ow[3];
-            for (int k = 0; k < 8; ++k)
-                sm.plane[k][c] = static_cast<uint16_t>(gather_bit4(o0, k) | (gather_bit4(o1, k) << 4) | (gather_bit4(o2, k) << 8) | (gather_bit4(o3, k) << 12));
-            uint32_t ap = 0;
-            for (int j = 0; j < 4; ++j) {
-                uint32_t x = tw[j] ^ 0x27272727u;                      // a zero byte marks an apostrophe
-                uint32_t z = (x - 0x01010101u) & ~x & 0x80808080u;
-                // the borrow trick can flag a byte above a true zero; apostrophes are rare, so check exactly
-                if (z) for (int k = 0; k < 4; ++k) if (((tw[j] >> (8 * k)) & 0xFFu) == 0x27u) ap |= 1u << (j * 4 + k);
-            }
-            sm.plane[PL_AP][c] = static_cast<uint16_t>(ap);
+        mark(2);
+        if (sm.misc[1]) {
+            // the planes of the chunks a literal was painted over
+            blk.par([&](int tid) {
+                for (int c = tid; c < n_chunks; c += kThreads) {
+                    if (!((sm.dirty[c >> 5] >> (c & 31)) & 1u)) continue;
+                    const uint32_t* owp = reinterpret_cast<const uint32_t*>(sm.oh + c * 16);
+                    const uint32_t* twp = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
+                    const uint32_t ow[4] = {owp[0], owp[1], owp[2], owp[3]}, tw[4] = {twp[0], twp[1], twp[2], twp[3]};
+                    chunk_planes(sm, c, ow, tw);
+                }
+            });
         }
-    });
+    }
 
     mark(3);
     Win w;
     w.sm = &sm; w.a = &a; w.lo = lo; w.n = n;
     w.vlo = lo < 0 ? 0 : lo + static_cast<int>(a.tb.added_max_bytes);
-    w.vhi = lo + kWin < n ? lo + kWin : n;
+    w.vhi = lo + kPWin < n ? lo + kPWin : n;
 
     // ---- P3: boundary bits, 32 bytes per thread as 64-bit planes with 16-bit margins ----
     // Bit i of a plane is byte i; "<< 1" moves a fact from a byte to the byte after it.
@@ -959,7 +1131,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     // plain whitespace right after a newline (needs run walks), and words holding stray
     // continuation bytes or added-token literals.
     blk.par([&](int tid) {
-        if (tid >= kTileWords) return;
+        if (tid >= kPTileWords) return;
         const int ww = kHaloL / 32 + tid;
         auto load = [&](int k) -> uint64_t {
             const uint32_t* pw = reinterpret_cast<const uint32_t*>(sm.plane[k]);
@@ -1114,17 +1286,23 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         const uint32_t* nleadw = reinterpret_cast<const uint32_t*>(sm.nlead16);
         const uint32_t* nstartw = reinterpret_cast<const uint32_t*>(sm.nstart16);
         // (has, cnt): "a run start was seen" and "digits since the last run start".
+        constexpr int kLaneWords = (kPTileWords + 31) / 32;
         blk.par([&](int tid) {
             if (tid >= 32) return;
-            uint32_t has = 0, cnt = 0;
-            for (int k = 0; k < kTileWords / 32; ++k) {
-                int wd = tid * (kTileWords / 32) + k;
+            uint32_t has = 0, cnt = 0, last = 0, firstn = 0;
+            for (int k = 0; k < kLaneWords; ++k) {
+                const int wd = tid * kLaneWords + k;
+                if (wd >= kPTileWords) break;
                 uint32_t nl = nleadw[wd], st = nstartw[wd];
                 if (st) { has = 1; cnt = popc32(nl & ~((1u << fls32(st)) - 1u)); }
                 else cnt += popc32(nl);
+                if (leadw[wd]) last = wd + 1;
+                if (nl && !firstn) firstn = wd + 1;
             }
             sm.sum_has[tid] = has;
             sm.sum_cnt[tid] = cnt;
+            sm.lane_last[tid] = last;          // 1 + the lane's last word holding a lead byte, 0 = none
+            sm.lane_firstn[tid] = firstn;      // 1 + its first word holding a digit
         });
         blk.par([&](int tid) {
             if (tid != 0) return;
@@ -1133,13 +1311,13 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             for (int l = 0; l < 32; ++l) {
                 if (sm.sum_has[l]) { has = 1; cnt = sm.sum_cnt[l]; } else cnt += sm.sum_cnt[l];
             }
-            for (int wd = kTileWords - 1; wd >= 0; --wd) {
-                if (leadw[wd]) { any_lead = 1; last_is_n = (nleadw[wd] >> fls32(leadw[wd])) & 1u; break; }
+            for (int l = 31; l >= 0; --l) {
+                if (sm.lane_last[l]) { const int wd = sm.lane_last[l] - 1; any_lead = 1; last_is_n = (nleadw[wd] >> fls32(leadw[wd])) & 1u; break; }
             }
             bool pass = !any_lead || (last_is_n && !has);     // the run (if any) is still open and began earlier
             uint32_t first_needs = 0;                          // first digit of the tile continues an earlier run
-            for (int wd = 0; wd < kTileWords; ++wd) {
-                if (nleadw[wd]) { int b = ffs32(nleadw[wd]); first_needs = !((nstartw[wd] >> b) & 1u); break; }
+            for (int l = 0; l < 32; ++l) {
+                if (sm.lane_firstn[l]) { const int wd = sm.lane_firstn[l] - 1; int b = ffs32(nleadw[wd]); first_needs = !((nstartw[wd] >> b) & 1u); break; }
             }
             unsigned long long mine;
             if (!pass) mine = kStFinal | ((last_is_n && any_lead) ? cnt : 0u);
@@ -1162,8 +1340,9 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             // Exclusive (has, cnt) over the 32 lane summaries, seeded with the carry.
             uint32_t cnt = sm.misc[0];
             for (int l = 0; l < tid; ++l) { if (sm.sum_has[l]) cnt = sm.sum_cnt[l]; else cnt += sm.sum_cnt[l]; }
-            for (int k = 0; k < kTileWords / 32; ++k) {
-                int wd = tid * (kTileWords / 32) + k;
+            for (int k = 0; k < kLaneWords; ++k) {
+                const int wd = tid * kLaneWords + k;
+                if (wd >= kPTileWords) break;
                 sm.carry[wd] = cnt;
                 uint32_t nl = nleadw[wd], st = nstartw[wd];
                 if (st) cnt = popc32(nl & ~((1u << fls32(st)) - 1u));
@@ -1171,37 +1350,55 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             }
         });
         blk.par([&](int tid) {
-            uint32_t pend = sm.pend16[tid];
-            if (!pend) return;
-            int wd = tid >> 1, shift = (tid & 1) * 16;
-            uint32_t nl = nleadw[wd], st = nstartw[wd], bnd = sm.bnd16[tid];
-            while (pend) {
-                int k = ffs32(pend);
-                pend &= pend - 1;
-                int bit = shift + k;
-                uint32_t below = (1u << bit) - 1u;     // bit >= 1 never needed at 0: a pending digit is not the word's first lead... but may be
-                uint32_t idx;
-                uint32_t st_below = st & below;
-                if (st_below) idx = popc32(nl & below & ~((1u << fls32(st_below)) - 1u));
-                else idx = sm.carry[wd] + popc32(nl & below);
-                if (idx % 3u == 0u) bnd |= 1u << k;
+            for (int h = tid; h < 2 * kPTileWords; h += kThreads) {
+                uint32_t pend = sm.pend16[h];
+                if (!pend) continue;
+                int wd = h >> 1, shift = (h & 1) * 16;
+                uint32_t nl = nleadw[wd], st = nstartw[wd], bnd = sm.bnd16[h];
+                while (pend) {
+                    int k = ffs32(pend);
+                    pend &= pend - 1;
+                    int bit = shift + k;
+                    uint32_t below = (1u << bit) - 1u;
+                    uint32_t idx;
+                    uint32_t st_below = st & below;
+                    if (st_below) idx = popc32(nl & below & ~((1u << fls32(st_below)) - 1u));
+                    else idx = sm.carry[wd] + popc32(nl & below);
+                    if (idx % 3u == 0u) bnd |= 1u << k;
+                }
+                sm.bnd16[h] = static_cast<uint16_t>(bnd);
             }
-            sm.bnd16[tid] = static_cast<uint16_t>(bnd);
         });
     }
 
     mark(5);
     // ---- P5: write the bit masks, count boundaries ----
-    blk.par([&](int tid) {
-        uint32_t cnt = 0;
-        if (tid < kTileWords) {
-            uint32_t bw = reinterpret_cast<const uint32_t*>(sm.bnd16)[tid];
-            a.bmask[tile * kTileWords + tid] = bw;
-            if (a.tb.added_max_bytes) a.amask[tile * kTileWords + tid] = reinterpret_cast<const uint32_t*>(sm.add16)[tid];
-            cnt = popc32(bw);
-        }
-        sm.scan[tid] = cnt;
-    });
+    // The masks are arrays of whole 4096-byte tiles' worth of words (what the kernels after this one
+    // read, and what a caller's buffer holds): nothing is written past that, and the last tile
+    // clears whatever lies between its own end and there.
+    {
+        const uint32_t lim = static_cast<uint32_t>((n + kTile - 1) / kTile) * kTileWords;
+        const bool last = t0 + kPTile >= n;
+        blk.par([&](int tid) {
+            uint32_t cnt = 0;
+            if (tid < kPTileWords) {
+                const uint32_t bw = reinterpret_cast<const uint32_t*>(sm.bnd16)[tid];
+                const uint32_t idx = static_cast<uint32_t>(tile) * kPTileWords + tid;
+                if (idx < lim) {
+                    a.bmask[idx] = bw;
+                    if (a.tb.added_max_bytes) a.amask[idx] = reinterpret_cast<const uint32_t*>(sm.add16)[tid];
+                }
+                cnt = popc32(bw);
+            }
+            if (last) {
+                for (uint32_t idx = static_cast<uint32_t>(tile + 1) * kPTileWords + tid; idx < lim; idx += kThreads) {
+                    a.bmask[idx] = 0;
+                    if (a.tb.added_max_bytes) a.amask[idx] = 0;
+                }
+            }
+            sm.scan[tid] = cnt;
+        });
+    }
     uint32_t total = 0;
     blk.excl_scan(sm.scan, &total);
     blk.par([&](int tid) { if (tid == 0) a.tile_nb[tile] = total; });
@@ -1253,10 +1450,10 @@ struct MissSmem {
     unsigned long long clk_last;
 };
 struct AsmSmem {
-    alignas(16) uint32_t tok[kTile + kTokExtra];   // the tile's slots, then its overflow slots
-    uint32_t scan[kThreads];
-    uint32_t sum[kThreads];
-    uint32_t ex[8];
+    uint32_t scan[kThreads];           // ids in each thread's sixteen slots, then their exclusive sums
+    uint32_t sum[kThreads];            // each thread's share of the earlier tiles' id counts
+    uint32_t ex[kTokExtra / 4];        // ids in each quad of the tile's overflow slots
+    uint32_t ovf[kTokExtra];           // the tile's overflow slots
     uint32_t lref_idx[kLongPerTile], lref_at[kLongPerTile];
     uint32_t ctr[8];
     unsigned long long clk_last;
@@ -1480,8 +1677,8 @@ GTOK_DEV uint32_t find_word_end(const EncodeArgs& a, uint32_t g, uint32_t n) {
         if (bits) { uint32_t e = wi * 32 + ffs32(bits); return e < n ? e : n; }
         ++wi;
         if (wi >= n_words) return n;
-        if ((wi % kTileWords) == 0) {
-            while (wi < n_words && ldg(a.tile_nb + wi / kTileWords) == 0) wi += kTileWords;
+        if ((wi % kPTileWords) == 0) {       // tile_nb counts per pre-tokenization tile
+            while (wi < n_words && ldg(a.tile_nb + wi / kPTileWords) == 0) wi += kPTileWords;
             if (wi >= n_words) return n;
         }
         bits = ldg(a.bmask + wi);
@@ -1987,9 +2184,10 @@ GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li
 }
 
 // ---- kernel 4: output assembly ------------------------------------------------------------
-// Counts the ids each tile's slots stand for, finds the tile's base by a single-pass
-// decoupled look-back over the tile totals, and writes the ids to their final place,
-// together with the per-document offsets and the total.
+// Each thread keeps its 16 slots in registers from the load to the store: the slots, the
+// tile's overflow slots and the earlier tiles' id counts (whose sum is the tile's base) are
+// all requested before anything waits, so a tile costs one memory round trip, one block scan
+// and the stores.  Beyond kSumTiles tiles the base comes from a look-back chain instead.
 template <class Blk>
 GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile) {
     const uint32_t n = ldg(a.meta);
@@ -1997,6 +2195,9 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
     const uint32_t t0 = static_cast<uint32_t>(tile) * kTile;
     const uint32_t n_tiles = (n + kTile - 1) / kTile;
     const uint32_t* ovf = a.ovf + static_cast<size_t>(tile) * kTokExtra;
+    const bool direct = n_tiles <= a.sum_tiles;
+    struct Slots { uint32_t v[kPer]; };
+    typename Blk::template Local<Slots> regs;
     auto mark = [&](int slot) {
         if (!a.phase_clk) return;
         blk.par([&](int tid) {
@@ -2011,56 +2212,74 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
         if (v == kInvalidTok) return 0u;
         return (v & kLongRef) ? ldg(a.glong_cnt + (v & ~kLongRef)) : 1u;
     };
-    // ---- A0: the tile's slots into shared memory; ids per thread ----
+    // ---- A0: slots into registers; ids per thread; partial sums of the earlier tiles' counts ----
     blk.par([&](int tid) {
-        if (tid == 0) sm.ctr[C_NLREF] = 0;
+        Slots& r = regs.at(tid);
+        uint32_t acc = 0;
+        if (direct) for (uint32_t j = tid; j < static_cast<uint32_t>(tile); j += kThreads) acc += ldg(a.tile_tok + j);
 #if defined(__CUDA_ARCH__)
-        for (int c = tid; c < kTile / 4; c += kThreads)
-            reinterpret_cast<uint4*>(sm.tok)[c] = __ldg(reinterpret_cast<const uint4*>(a.stage + t0) + c);
+        const uint4* src = reinterpret_cast<const uint4*>(a.stage + t0) + tid * (kPer / 4);
+#pragma unroll
+        for (int q = 0; q < kPer / 4; ++q) {
+            const uint4 w = __ldg(src + q);
+            r.v[4 * q] = w.x; r.v[4 * q + 1] = w.y; r.v[4 * q + 2] = w.z; r.v[4 * q + 3] = w.w;
+        }
 #else
-        for (int i = tid; i < kTile; i += kThreads) sm.tok[i] = a.stage[t0 + i];
+        for (int i = 0; i < kPer; ++i) r.v[i] = a.stage[t0 + tid * kPer + i];
 #endif
-        if (tid < kTokExtra) sm.tok[kTile + tid] = ovf[tid];
-    });
-    blk.par([&](int tid) {
         uint32_t sum = 0;
-        const uint32_t* sp = sm.tok + tid * kPer;
-        for (int i = 0; i < kPer; ++i) sum += weight(sp[i]);
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int i = 0; i < kPer; ++i) sum += weight(r.v[i]);
         sm.scan[tid] = sum;
-        if (tid < kTokExtra / kPer) {
+        sm.sum[tid] = acc;
+        if (tid < kTokExtra / 4) {
             uint32_t ex = 0;
-            for (int i = 0; i < kPer; ++i) ex += sm.tok[kTile + tid * kPer + i] != kInvalidTok;
+            for (int i = 0; i < 4; ++i) { const uint32_t x = ldg(ovf + tid * 4 + i); sm.ovf[tid * 4 + i] = x; ex += x != kInvalidTok; }
             sm.ex[tid] = ex;
         }
+        if (tid == 0) sm.ctr[C_NLREF] = 0;
     });
-    uint32_t total_main = 0;
-    blk.excl_scan(sm.scan, &total_main);
+    uint32_t total_main = 0, before = 0;
+    blk.excl_scan_and_sum(sm.scan, &total_main, sm.sum, &before);
     uint32_t total = total_main;
-    for (int t = 0; t < kTokExtra / kPer; ++t) total += sm.ex[t];
+    for (int t = 0; t < kTokExtra / 4; ++t) total += sm.ex[t];
     mark(12);
-    // ---- A1: tile base by decoupled look-back ----
+    // ---- A1: tile base ----
     // Every tile's total is known before this kernel starts (tile_tok), so up to kSumTiles tiles a
     // block simply adds up the totals before its own; beyond that (the work is quadratic in the
     // number of tiles) the totals are chained by look-back.
     uint32_t base;
-    if (n_tiles <= a.sum_tiles) {
-        blk.par([&](int tid) {
-            uint32_t acc = 0;
-            for (uint32_t j = tid; j < static_cast<uint32_t>(tile); j += kThreads) acc += ldg(a.tile_tok + j);
-            sm.sum[tid] = acc;
-        });
-        uint32_t before = 0;
-        blk.excl_scan(sm.sum, &before);
+    if (direct) {
         base = before;
         if (ldg(a.tile_tok + tile) != total) blk.par([&](int tid) { if (tid == 0) global_or(a.ctl + CTL_ERR, kErrInternal); });   // the kernels disagree on a count
     } else base = blk.lookback(a.st2, tile, total, a.ctl);
     mark(13);
-    // ---- A2: ids to their final place ----
+    // ---- A2: ids to their final place; per-document token offsets ----
     blk.par([&](int tid) {
+        const Slots& r = regs.at(tid);
         uint32_t at = base + sm.scan[tid];
-        const uint32_t* sp = sm.tok + tid * kPer;
+        uint32_t docbits = 0;
+        if (a.out_doc_tok) {
+            const uint32_t p0 = t0 + tid * kPer;
+            docbits = (ldg(a.docmask + (p0 >> 5)) >> (p0 & 31)) & 0xFFFFu;
+            if (p0 == 0) docbits |= 1u;
+        }
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
         for (int i = 0; i < kPer; ++i) {
-            uint32_t v = sp[i];
+            const uint32_t v = r.v[i];
+            if ((docbits >> i) & 1u) {
+                // documents that begin at this byte (several when some are empty): their first id is the next one written
+                const uint32_t p = t0 + tid * kPer + i;
+                if (p < n) {
+                    uint32_t lo = 0, hi = n_docs + 1;
+                    while (lo < hi) { uint32_t mid = (lo + hi) >> 1; if (ldg(a.doc_off + mid) < p) lo = mid + 1; else hi = mid; }
+                    for (uint32_t d = lo; d <= n_docs && ldg(a.doc_off + d) == p; ++d) a.out_doc_tok[d] = at;
+                }
+            }
             if (v == kInvalidTok) continue;
             if (v & kLongRef) {
                 uint32_t li = v & ~kLongRef, slot = shared_add(&sm.ctr[C_NLREF], 1u);
@@ -2071,11 +2290,11 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
             if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + CTL_ERR, kErrOutputFull);
             ++at;
         }
-        if (tid < kTokExtra / kPer) {
+        if (tid < kTokExtra / 4) {
             at = base + total_main;
             for (int t = 0; t < tid; ++t) at += sm.ex[t];
-            for (int i = 0; i < kPer; ++i) {
-                uint32_t v = sm.tok[kTile + tid * kPer + i];
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t v = sm.ovf[tid * 4 + i];
                 if (v == kInvalidTok) continue;
                 if (at < a.out_cap) a.out_tokens[at] = v; else global_or(a.ctl + CTL_ERR, kErrOutputFull);
                 ++at;
@@ -2099,32 +2318,15 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
         }
     }
     mark(14);
-    // ---- A3: per-document token offsets; totals ----
-    if (a.out_doc_tok) {
+    // ---- A3: offsets of the documents past the text's end; total ----
+    if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
         blk.par([&](int tid) {
-            // documents whose first byte lies in this tile
-            uint32_t lo = 0, hi = n_docs + 1;
-            while (lo < hi) { uint32_t mid = (lo + hi) >> 1; if (ldg(a.doc_off + mid) < t0) lo = mid + 1; else hi = mid; }
-            uint32_t t1 = t0 + kTile;
-            for (uint32_t d = lo + tid; d <= n_docs; d += kThreads) {
-                uint32_t off = ldg(a.doc_off + d);
-                if (off >= t1 || off >= n) break;
-                uint32_t o = off - t0, owner = o / kPer;
-                uint32_t cnt = sm.scan[owner];
-                for (uint32_t i = owner * kPer; i < o; ++i) cnt += weight(sm.tok[i]);
-                a.out_doc_tok[d] = base + cnt;
-            }
-            if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
+            if (a.out_doc_tok) {
                 uint32_t lo2 = 0, hi2 = n_docs + 1;
                 while (lo2 < hi2) { uint32_t mid = (lo2 + hi2) >> 1; if (ldg(a.doc_off + mid) < n) lo2 = mid + 1; else hi2 = mid; }
                 for (uint32_t d = lo2 + tid; d <= n_docs; d += kThreads) a.out_doc_tok[d] = base + total;
             }
-        });
-    }
-    if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
-        blk.par([&](int tid) {
-            if (tid != 0) return;
-            a.status[0] = base + total;
+            if (tid == 0) a.status[0] = base + total;
         });
     }
     mark(15);

@@ -22,6 +22,12 @@ namespace gtok {
 namespace {
 
 struct GpuBlk {
+    // Per-thread values that live from one par() to the next: registers here.
+    template <class T>
+    struct Local {
+        T v;
+        __device__ __forceinline__ T& at(int) { return v; }
+    };
     template <class F>
     __device__ __forceinline__ void par(F f) {
         f(static_cast<int>(threadIdx.x));
@@ -49,6 +55,34 @@ struct GpuBlk {
         }
         arr[tid] = off + x - v;
         *total = tot;
+        __syncthreads();
+    }
+    // excl_scan of arr[kThreads] and, in the same two barriers, the plain sum of other[kThreads].
+    __device__ __forceinline__ void excl_scan_and_sum(uint32_t* arr, uint32_t* total, const uint32_t* other, uint32_t* other_total) {
+        __shared__ uint32_t wsum2[kThreads / 32], osum2[kThreads / 32];
+        const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+        const uint32_t v = arr[tid];
+        uint32_t x = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t y = __shfl_up_sync(0xFFFFFFFFu, x, d);
+            if (lane >= d) x += y;
+        }
+        const uint32_t o = __reduce_add_sync(0xFFFFFFFFu, other[tid]);
+        if (lane == 31) wsum2[wid] = x;
+        if (lane == 0) osum2[wid] = o;
+        __syncthreads();
+        uint32_t off = 0, tot = 0, otot = 0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            uint32_t s = wsum2[w];
+            if (w < wid) off += s;
+            tot += s;
+            otot += osum2[w];
+        }
+        arr[tid] = off + x - v;
+        *total = tot;
+        *other_total = otot;
         __syncthreads();
     }
     // Publishes this tile's total and returns the sum of all earlier tiles' totals: warp 0
@@ -100,20 +134,34 @@ struct GpuBlk {
     }
 };
 
-__global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const EncodeArgs a) {
-    __shared__ PretokSmem sm;
+// Diagnostics: a stamp of the global nanosecond timer in this block's row of the timeline.
+__device__ __forceinline__ void tl_stamp(const EncodeArgs& a, int kernel, int slot) {
+    if (!a.phase_clk || threadIdx.x != 0 || blockIdx.x >= kTlBlocks || slot >= kTlSlots) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    a.phase_clk[kPhaseWords + (static_cast<size_t>(kernel) * kTlBlocks + blockIdx.x) * kTlSlots + slot] = t;
+}
+
+__global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const __grid_constant__ EncodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    PretokSmem& sm = *reinterpret_cast<PretokSmem*>(smem_raw);
     __shared__ int s_tile;
     GpuBlk blk;
     const uint32_t n = a.meta[0];
-    const int n_tiles = static_cast<int>((n + kTile - 1) / kTile);
-    for (;;) {
+    const int n_tiles = static_cast<int>((n + kPTile - 1) / kPTile);
+    tl_stamp(a, 0, 0);
+    pretok_block_init(blk, a, sm);
+    for (int done = 0;; ++done) {
         if (threadIdx.x == 0) s_tile = static_cast<int>(atomicAdd(a.ctl + 0, 1u));
         __syncthreads();
         const int tile = s_tile;
         __syncthreads();
         if (tile >= n_tiles) break;
+        if (threadIdx.x == 0) sm.misc[2] = static_cast<uint32_t>(done);      // diagnostics: which of the block's tiles this is
         pretok_tile(blk, a, sm, tile);
+        tl_stamp(a, 0, 2 + done);
     }
+    tl_stamp(a, 0, 1);
 }
 
 // Kernel 0 (vocabularies that declare NFC): raw text -> normalised text, byte count and
@@ -122,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const EncodeArgs a)
 // Does the text need normalising at all?  Any codepoint that can make a text non-NFC raises the
 // flag.  (Launched with raw_docmask unset: document boundaries are ignored here, which can only
 // raise the flag once too often.)
-__global__ void __launch_bounds__(kThreads) nfc_check_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads) nfc_check_kernel(const __grid_constant__ EncodeArgs a) {
     const uint32_t n = a.raw_meta[0];
     if (a.raw_meta[2]) return;                                   // the host says it is normalised already
     const uint32_t chunks = (n + kPer - 1) / kPer;
@@ -136,7 +184,7 @@ __global__ void __launch_bounds__(kThreads) nfc_check_kernel(const EncodeArgs a)
 }
 
 // Nothing to normalise (the usual case): the raw text and its header are the text and the header.
-__global__ void __launch_bounds__(kThreads) nfc_copy_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads) nfc_copy_kernel(const __grid_constant__ EncodeArgs a) {
     if (a.ctl[CTL_NFCFLAG]) return;
     const uint32_t n = a.raw_meta[0], n_docs = a.raw_meta[1];
     const uint32_t quads = (n + 15) / 16;
@@ -148,7 +196,7 @@ __global__ void __launch_bounds__(kThreads) nfc_copy_kernel(const EncodeArgs a) 
     if (blockIdx.x == 0 && threadIdx.x == 0) a.status[2] = n;
 }
 
-__global__ void __launch_bounds__(kThreads) nfc_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads) nfc_kernel(const __grid_constant__ EncodeArgs a) {
     __shared__ NfcSmem sm;
     __shared__ int s_tile;
     GpuBlk blk;
@@ -166,18 +214,21 @@ __global__ void __launch_bounds__(kThreads) nfc_kernel(const EncodeArgs a) {
 }
 
 // Kernel 2: whole-word table lookups, tile by tile (tiles are independent here).
-__global__ void __launch_bounds__(kThreads, 4) words_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) words_kernel(const __grid_constant__ EncodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     WordsSmem& sm = *reinterpret_cast<WordsSmem*>(smem_raw);
     GpuBlk blk;
     const uint32_t n = a.meta[0];
     const int n_tiles = static_cast<int>((n + kTile - 1) / kTile);
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) words_tile(blk, a, sm, tile);
+    tl_stamp(a, 1, 0);
+    int done = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) { words_tile(blk, a, sm, tile); tl_stamp(a, 1, 2 + done++); }
+    tl_stamp(a, 1, 1);
 }
 
 // Kernel 3: merge loops for what the table did not know, batch by batch, then the
 // pre-tokens longer than 64 bytes one by one.
-__global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) miss_kernel(const __grid_constant__ EncodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     MissSmem& sm = *reinterpret_cast<MissSmem*>(smem_raw);
     __shared__ uint32_t s_pick;
@@ -187,10 +238,11 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
     const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med1_batches = (n_med1 + kMedBatchA1 - 1) / kMedBatchA1;
     const uint32_t med2_batches = (n_med2 + take_b - 1) / take_b;
     const uint32_t short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
+    tl_stamp(a, 2, 0);
     sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
     __syncthreads();
     // longest pre-tokens first: their merge chains decide when the kernel ends
-    for (;;) {
+    for (int done = 0;; ++done) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_BATCH, 1u);
         __syncthreads();
         const uint32_t t = s_pick;
@@ -205,6 +257,7 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
             list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches - med1_batches) * take_b; count = n_med2; batch = kMedBatchB; max_len = kMedSplit; take = take_b;
         }
         miss_batch(blk, a, sm, list, dir, first, count, batch, max_len, take);
+        tl_stamp(a, 2, 2 + done);
     }
     for (;;) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);
@@ -214,24 +267,28 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const EncodeArgs a) {
         if (li >= n_long) break;
         long_word(blk, a, sm, li);
     }
+    tl_stamp(a, 2, 1);
 }
 
 // Kernel 4: output assembly; tiles are handed out in order because a tile's base is the
 // sum of all earlier tiles' counts.
-__global__ void __launch_bounds__(kThreads) assemble_kernel(const EncodeArgs a) {
+__global__ void __launch_bounds__(kThreads, 8) assemble_kernel(const __grid_constant__ EncodeArgs a) {
     __shared__ AsmSmem sm;
     __shared__ int s_tile;
     GpuBlk blk;
     const uint32_t n = a.meta[0];
     const int n_tiles = static_cast<int>((n + kTile - 1) / kTile);
-    for (;;) {
+    tl_stamp(a, 3, 0);
+    for (int done = 0;; ++done) {
         if (threadIdx.x == 0) s_tile = static_cast<int>(atomicAdd(a.ctl + CTL_ASM, 1u));
         __syncthreads();
         const int tile = s_tile;
         __syncthreads();
         if (tile >= n_tiles) break;
         assemble_tile(blk, a, sm, tile);
+        tl_stamp(a, 3, 2 + done);
     }
+    tl_stamp(a, 3, 1);
     // The last block to leave mirrors the error word where the host can read it.
     if (threadIdx.x == 0) {
         __threadfence();
@@ -312,7 +369,7 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
     a.st1 = sc->st1;
     a.ctl = sc->ctl;
     a.tb = tb;
-    const uint32_t n_tiles = (len + kTile - 1) / kTile;
+    const uint32_t n_tiles = (len + kPTile - 1) / kPTile;      // tiles of the pre-tokenization kernel
     // The array keeps whatever the previous call left: ticket, error word and the
     // look-back states of the tiles this call uses must start at zero.
     e = cudaMemsetAsync(sc->ctl, 0, sizeof sc->ctl, stream);
@@ -320,7 +377,7 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
     if (e != cudaSuccess) { err = std::string("cudaMemsetAsync: ") + cudaGetErrorString(e); return -1; }
     noalloc_set_meta<<<1, 1, 0, stream>>>(sc->meta, len);
     const int blocks = static_cast<int>(n_tiles < static_cast<uint32_t>(sm_of[device] * 4) ? n_tiles : sm_of[device] * 4);
-    pretok_kernel<<<blocks, kThreads, 0, stream>>>(a);
+    pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), stream>>>(a);
     e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) { err = std::string("boundaries_noalloc: ") + cudaGetErrorString(e); return -1; }
@@ -329,10 +386,13 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
 
 cudaError_t configure_kernels() {
     cudaError_t e = cudaFuncSetAttribute(words_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(WordsSmem)));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PretokSmem)));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(assemble_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(miss_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(MissSmem)));
-    // These two live on shared memory, not L1: ask for the largest carve-out so that as many
-    // blocks as the register file allows are resident.  (The pre-tokenization kernel reads its
-    // class tables through L1 and is better off with the default split.)
+    // All four kernels work out of shared memory, not L1: the largest carve-out for each, so that as
+    // many blocks as the register file allows are resident and the SMs keep one configuration
+    // from kernel to kernel of a replay.
     if (e == cudaSuccess) e = cudaFuncSetAttribute(words_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(miss_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     return e;
@@ -340,7 +400,7 @@ cudaError_t configure_kernels() {
 
 // Decoding kernel: tiles of 2048 ids handed out in order (a tile's byte offset is the sum of
 // the earlier tiles' byte counts, found by look-back).
-__global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) decode_kernel(const __grid_constant__ DecodeArgs a) {
     __shared__ DecodeSmem sm;
     __shared__ int s_tile;
     GpuBlk blk;
@@ -369,7 +429,7 @@ static int blocks_per_sm(const void* fn, size_t smem) {
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, kThreads, smem);
     return nb > 0 ? nb : 1;
 }
-int pretok_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(pretok_kernel), 0); }
+int pretok_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(pretok_kernel), sizeof(PretokSmem)); }
 int words_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(words_kernel), sizeof(WordsSmem)); }
 int miss_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(miss_kernel), sizeof(MissSmem)); }
 int nfc_blocks_per_sm() { return blocks_per_sm(reinterpret_cast<const void*>(nfc_kernel), 0); }
@@ -385,7 +445,7 @@ void launch_raw_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cuda
 void launch_nfc_check(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_check_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_nfc_copy(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_copy_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_kernel<<<blocks, kThreads, 0, s>>>(a); }
-void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, 0, s>>>(a); }
+void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), s>>>(a); }
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s) { words_kernel<<<blocks, kThreads, sizeof(WordsSmem), s>>>(a); }
 void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s) { miss_kernel<<<blocks, kThreads, sizeof(MissSmem), s>>>(a); }
 void launch_decode(const DecodeArgs& a, int blocks, cudaStream_t s) { decode_kernel<<<blocks, kThreads, 0, s>>>(a); }

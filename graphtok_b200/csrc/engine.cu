@@ -264,7 +264,8 @@ struct Engine::Impl {
             !upload(s2, &dt.uc_stage2, owned, err) || !upload(ht.trie_root, &dt.trie_root, owned, err) ||
             !upload(ht.trie_first, &dt.trie_first, owned, err) || !upload(ht.trie_count, &dt.trie_count, owned, err) ||
             !upload(ht.trie_terminal, &dt.trie_terminal, owned, err) || !upload(ht.trie_edges, &dt.trie_edges, owned, err) ||
-            !upload(ht.trie_skip, &dt.trie_skip, owned, err) || !upload(ht.trie_blob, &dt.trie_blob, owned, err))
+            !upload(ht.trie_skip, &dt.trie_skip, owned, err) || !upload(ht.trie_blob, &dt.trie_blob, owned, err) ||
+            !upload(ht.littab, &dt.littab, owned, err) || !upload(ht.lit_blob, &dt.lit_blob, owned, err))
             return false;
         if (nfc) {
             NfcWords w;
@@ -278,15 +279,8 @@ struct Engine::Impl {
             dt.nfc_decomp_n = static_cast<uint32_t>(w.decomp.size() / 6);
             dt.nfc_comp_n = static_cast<uint32_t>(w.comp.size() / 3);
         }
-        dt.merge_shift = ht.merge_shift;
-        dt.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
-        dt.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
-        dt.long_max_len = ht.long_max_len;
-        dt.added_max_bytes = ht.added_max_bytes;
-        dt.family = ht.family;
-        dt.ignore_merges = ht.ignore_merges;
-        dt.monotone = ht.monotone;
-        dt.added_ws = ht.added_ws;
+        static_assert(GTOK_UC_STAGE2_LEN == kUcStage2Words && GTOK_UC_STAGE1_LEN >= kUcStage1Bmp, "class table sizes the kernels copy to shared memory");
+        fill_table_scalars(ht, dt);
         return true;
     }
 
@@ -359,7 +353,7 @@ struct Engine::Impl {
         c->batch = batch_mode;
         c->n_tiles_cap = (cap_bytes + kTile - 1) / kTile + 1;
         const size_t tile_bytes = static_cast<size_t>(c->n_tiles_cap) * kTile;
-        const size_t mask_words = static_cast<size_t>(c->n_tiles_cap) * kTileWords + 8;
+        const size_t mask_words = static_cast<size_t>(c->n_tiles_cap) * kTileWords + 264;
         const size_t hdr_words = kHdrWords + static_cast<size_t>(cap_docs) + 2;
         GTOK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
         for (cudaEvent_t& e : c->ev) GTOK_CUDA(cudaEventCreate(&e));
@@ -440,14 +434,14 @@ struct Engine::Impl {
         a.out_doc_tok = batch_mode ? c->d_doc_tok : nullptr;
         a.status = c->d_status;
         if (std::getenv("GTOK_PHASE_CLOCKS")) {
-            GTOK_CUDA(cudaMalloc(&c->d_phase, 32 * sizeof(unsigned long long)));
-            GTOK_CUDA(cudaMemset(c->d_phase, 0, 32 * sizeof(unsigned long long)));
+            GTOK_CUDA(cudaMalloc(&c->d_phase, (kPhaseWords + kTlWords) * sizeof(unsigned long long)));
+            GTOK_CUDA(cudaMemset(c->d_phase, 0, (kPhaseWords + kTlWords) * sizeof(unsigned long long)));
             a.phase_clk = c->d_phase;
         }
         a.tb = dt;
 
         // Capture: control block reset, [document mask], pretok, merge.
-        const int pretok_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * pretok_per_sm));
+        const int pretok_blocks = std::max(1, std::min<int>(static_cast<int>((static_cast<size_t>(cap_bytes) + kPTile - 1) / kPTile), sm_count * pretok_per_sm));
         const int words_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * words_per_sm));
         const int miss_blocks = std::max(1, sm_count * miss_per_sm);
         const int asm_blocks = std::max(1, std::min<int>(static_cast<int>(c->n_tiles_cap), sm_count * asm_per_sm));
@@ -894,6 +888,17 @@ int Engine::read_phase_clocks(unsigned long long* out32, bool reset) {
     if (cudaMemcpy(out32, c->d_phase, 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     if (reset) cudaMemset(c->d_phase, 0, 32 * sizeof(unsigned long long));
     return 0;
+}
+
+int Engine::read_timeline(unsigned long long* out, uint32_t max_words) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    Ctx* c = im.staged;
+    if (!c || !c->d_phase) return -1;
+    const uint32_t words = std::min<uint32_t>(max_words, kTlWords);
+    if (cudaMemcpy(out, c->d_phase + kPhaseWords, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    cudaMemset(c->d_phase + kPhaseWords, 0, kTlWords * sizeof(unsigned long long));
+    return static_cast<int>(words);
 }
 
 // ids -> bytes on the device (the reference's TokenizerCtx::decode, src/tokenizer.cu:5499-5573).

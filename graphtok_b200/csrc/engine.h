@@ -49,6 +49,8 @@ public:
     // Device-side table block for callers inside the library (no-allocation entry point).
     // Diagnostics (contexts created with GTOK_PHASE_CLOCKS set): cycles per kernel phase, summed over blocks.
     int read_phase_clocks(unsigned long long* out32, bool reset);
+    // The block timeline of the last replay (4 kernels x 1280 blocks x 8 nanosecond stamps); cleared by the read.
+    int read_timeline(unsigned long long* out, uint32_t max_words);
     const struct DeviceTables* device_tables() const;
     int device_index() const;
 

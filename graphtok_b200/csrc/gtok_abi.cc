@@ -294,6 +294,11 @@ int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset) {
     try { return static_cast<Handle*>(handle)->engine->read_phase_clocks(reinterpret_cast<unsigned long long*>(out32), reset != 0); } catch (...) { return -1; }
 }
 
+int32_t gtok_x_timeline(void* handle, uint64_t* out, uint32_t max_words) {
+    if (!handle || !out) return -1;
+    try { return static_cast<Handle*>(handle)->engine->read_timeline(reinterpret_cast<unsigned long long*>(out), max_words); } catch (...) { return -1; }
+}
+
 int32_t gtok_x_token_bytes(void* handle, uint32_t id, uint8_t* out, uint32_t cap) {
     if (!handle) return -1;
     const gtok::HostVocab& hv = static_cast<Handle*>(handle)->engine->vocab();

@@ -175,6 +175,61 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
     out.added_ws = 0;
     for (const AddedToken& a : hv.added)
         for (unsigned char c : a.content) if (c == 0x20 || c == 0x0A || c == 0x0D) out.added_ws = 1;
+    for (int i = 0; i < 8; ++i) out.lit1_bits[i] = out.lit2_bits[i] = 0;
+    out.lit_single = 0;
+    for (const auto& a : hv.added) {
+        if (a.content.empty()) continue;
+        const unsigned char c0 = static_cast<unsigned char>(a.content[0]);
+        out.lit1_bits[c0 >> 5] |= 1u << (c0 & 31);
+        if (a.content.size() == 1) { out.lit_single = 1; continue; }
+        const unsigned char c1 = static_cast<unsigned char>(a.content[1]);
+        out.lit2_bits[c1 >> 5] |= 1u << (c1 & 31);
+    }
+    // the same literals as a hash table (see device_tables.h)
+    {
+        std::vector<uint32_t> lens;
+        for (const auto& a : hv.added) if (!a.content.empty()) lens.push_back(static_cast<uint32_t>(a.content.size()));
+        std::sort(lens.begin(), lens.end());
+        lens.erase(std::unique(lens.begin(), lens.end()), lens.end());
+        out.lit_n_lens = lens.size() <= static_cast<size_t>(kLitLens) ? static_cast<uint32_t>(lens.size()) : 0u;
+        for (int i = 0; i < kLitLens; ++i) out.lit_lens[i] = static_cast<uint32_t>(i) < out.lit_n_lens ? lens[i] : 0u;
+        out.littab.assign(16, LongSlot{0, kNoToken, 0, 0, 0});
+        out.lit_blob.assign(16, 0);
+        if (out.lit_n_lens) {
+            for (uint32_t cap = pow2_at_least(hv.added.size() * 4 + 16);; cap <<= 1) {
+                if (cap > (1u << 24)) { out.lit_n_lens = 0; out.littab.assign(16, LongSlot{0, kNoToken, 0, 0, 0}); break; }
+                out.littab.assign(cap, LongSlot{0, kNoToken, 0, 0, 0});
+                out.lit_blob.clear();
+                const uint32_t mask = cap - 1;
+                bool ok = true;
+                for (const auto& a : hv.added) {
+                    if (a.content.empty()) continue;
+                    uint64_t h = kLongHashSeed;
+                    for (unsigned char c : a.content) h = long_hash_step(h, c);
+                    h = long_hash_finish(h, static_cast<uint32_t>(a.content.size()));
+                    uint32_t at = static_cast<uint32_t>(h) & mask;
+                    int steps = 0;
+                    bool dup = false;
+                    for (;; at = (at + 1) & mask) {
+                        LongSlot& sl = out.littab[at];
+                        if (sl.id == kNoToken) break;
+                        if (sl.hash == h && sl.len == a.content.size() &&
+                            std::equal(a.content.begin(), a.content.end(), out.lit_blob.begin() + sl.off)) { dup = true; sl.id = a.id; break; }   // a repeated literal: the last id stands, as in the trie
+                        if (++steps >= 8) { ok = false; break; }
+                    }
+                    if (!ok) break;
+                    if (dup) continue;
+                    LongSlot& sl = out.littab[at];
+                    sl.hash = h; sl.id = a.id; sl.len = static_cast<uint32_t>(a.content.size());
+                    sl.off = static_cast<uint32_t>(out.lit_blob.size());
+                    out.lit_blob.insert(out.lit_blob.end(), a.content.begin(), a.content.end());
+                    while (out.lit_blob.size() % 16) out.lit_blob.push_back(0);
+                }
+                if (ok) break;
+            }
+            out.lit_blob.resize(out.lit_blob.size() + 16, 0);
+        }
+    }
     if (hv.added_max_bytes > kMaxAddedBytes) {
         err = "an added-token literal is longer than the on-device matcher supports";
         return false;

@@ -23,12 +23,34 @@ struct HostTables {
     std::vector<uint8_t> trie_blob;
     std::vector<uint16_t> trie_count;
     uint32_t added_max_bytes = 0;
+    uint32_t lit1_bits[8] = {}, lit2_bits[8] = {}, lit_single = 0;
+    std::vector<LongSlot> littab;
+    std::vector<uint8_t> lit_blob;
+    uint32_t lit_n_lens = 0, lit_lens[kLitLens] = {};
     uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0;
 };
 
 // Returns false (with a reason) when a table cannot be built within its probe
 // limit or an added-token literal is too long for the on-device matcher.
 bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err);
+
+// The scalar fields of the device view of the tables (the pointers are set by whoever owns the arrays).
+inline void fill_table_scalars(const HostTables& ht, DeviceTables& tb) {
+    tb.merge_shift = ht.merge_shift;
+    tb.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
+    tb.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
+    tb.long_max_len = ht.long_max_len;
+    tb.added_max_bytes = ht.added_max_bytes;
+    for (int i = 0; i < 8; ++i) { tb.lit1_bits[i] = ht.lit1_bits[i]; tb.lit2_bits[i] = ht.lit2_bits[i]; }
+    tb.lit_single = ht.lit_single;
+    tb.lit_mask = static_cast<uint32_t>(ht.littab.size() - 1);
+    tb.lit_n_lens = ht.lit_n_lens;
+    for (int i = 0; i < kLitLens; ++i) tb.lit_lens[i] = ht.lit_lens[i];
+    tb.family = ht.family;
+    tb.ignore_merges = ht.ignore_merges;
+    tb.monotone = ht.monotone;
+    tb.added_ws = ht.added_ws;
+}
 
 // Packs up to 15 bytes into a word-table key.
 inline void make_word_key(const uint8_t* bytes, uint32_t len, uint64_t& k0, uint64_t& k1) {

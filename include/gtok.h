@@ -87,6 +87,12 @@ int32_t gtok_x_profile(void* handle, float* ms_out6);
  * thread blocks since the last reset (slots 0-6 pre-tokenization, 8-11 words, 12-15 assemble,
  * 16-20 miss, 24-26 normalisation).  -1 if off. */
 int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset);
+/* Diagnostics, same switch: when each thread block of the last replay's four kernels started,
+ * finished, and finished its first six work items, as stamps of the GPU's nanosecond timer:
+ * out[(kernel * 1280 + block) * 8 + slot], slot 0 = start, 1 = end, 2.. = work items; kernel 0
+ * pre-tokenization, 1 words, 2 miss, 3 assemble.  Returns the words written (at most 40960),
+ * -1 if off.  The record is cleared by the call. */
+int32_t gtok_x_timeline(void* handle, uint64_t* out, uint32_t max_words);
 /* Sizes in bytes of the merge table, the whole-word table and the remaining tables. */
 void gtok_x_table_bytes(void* handle, uint64_t* out3);
 /* Kernel launches one graph replay performs (single document / batch). */

@@ -3,7 +3,8 @@ import random
 
 import numpy as np
 
-TILE = 4096
+TILE = 4096          # tile of the words / assemble kernels
+PTILE = 8000         # tile of the pre-tokenization kernel (its window of 8192 bytes less the halos)
 
 POOLS = {
     "mixed": list("ab cd\r\n1.'sXY tlrevmTLREVM\t") + ["é", "日", "ſ", " ", "2", "'ll", "'RE", "\n\n", "  ", "!!"],
@@ -33,13 +34,21 @@ def malformed_bytes(seed, count=300):
 
 
 def tile_crossers(special):
-    """Inputs whose interesting structure sits on tile edges (4096-byte tiles, 128/64-byte halos)."""
+    """Inputs whose interesting structure sits on tile edges (4096-byte and 8000-byte tiles, 128/64-byte halos)."""
     out = []
     for pad in (TILE - 70, TILE - 3, TILE - 2, TILE - 1, TILE, TILE + 1, 2 * TILE - 1):
         base = ("ab " * (pad // 3 + 1))[:pad]
         for mid in (" " * 300, "\n" * 300, " \n" * 150, "\n " * 150, "." + "\n" * 200 + " x", "7" * 500, "7" * 9000, "x" * 20, "x" * 5000,
                     "don't", "'ll", " 's", "é" * 100, "日本語" * 50, ".\r\n\r\n  \r\n y", "a" + " " * 129 + "\n" + " " * 200 + "b", "\t" * 70 + "z",
                     "=" * 200 + "\n\n\n" + "w", "1 2 3 4 5 6 7 8 9 " * 30):
+            out.append(base + mid + " tail end.")
+            if special:
+                out.append(base + special + mid + special + special + " t")
+    # the same kinds of structure on the edges of the pre-tokenization kernel's own tiles
+    for pad in (PTILE - 70, PTILE - 2, PTILE - 1, PTILE, PTILE + 1):
+        base = ("ab " * (pad // 3 + 1))[:pad]
+        for mid in (" " * 300, " \n" * 150, "." + "\n" * 200 + " x", "7" * 500, "x" * 20, "don't", "'ll", "é" * 100, "日本語" * 50, ".\r\n\r\n  \r\n y",
+                    "1 2 3 4 5 6 7 8 9 " * 30):
             out.append(base + mid + " tail end.")
             if special:
                 out.append(base + special + mid + special + special + " t")

@@ -24,6 +24,12 @@ namespace {
 
 struct CpuBlk {
     bool reverse = false;
+    // Per-thread values that live from one par() to the next: one copy per logical thread.
+    template <class T>
+    struct Local {
+        T v[gtok::kThreads];
+        T& at(int tid) { return v[tid]; }
+    };
     template <class F> void par(F f) {
         if (!reverse) for (int t = 0; t < gtok::kThreads; ++t) f(t);
         else for (int t = gtok::kThreads - 1; t >= 0; --t) f(t);
@@ -32,6 +38,12 @@ struct CpuBlk {
         uint32_t acc = 0;
         for (int i = 0; i < gtok::kThreads; ++i) { uint32_t v = arr[i]; arr[i] = acc; acc += v; }
         *total = acc;
+    }
+    void excl_scan_and_sum(uint32_t* arr, uint32_t* total, const uint32_t* other, uint32_t* other_total) {
+        uint32_t o = 0;
+        for (int i = 0; i < gtok::kThreads; ++i) o += other[i];
+        excl_scan(arr, total);
+        *other_total = o;
     }
     uint32_t lookback(unsigned long long* st, int tile, uint32_t total, uint32_t*) {
         uint32_t base = 0;
@@ -75,24 +87,25 @@ void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
     e->s2.assign(gtok_uc_stage2_init, gtok_uc_stage2_init + GTOK_UC_STAGE2_LEN);
     gtok::DeviceTables& tb = e->tb;
     const gtok::HostTables& ht = e->ht;
-    tb.merge = ht.merge.data(); tb.merge_shift = ht.merge_shift;
-    tb.word = ht.word.data(); tb.word_mask = static_cast<uint32_t>(ht.word.size() - 1);
-    tb.longtab = ht.longtab.data(); tb.long_mask = static_cast<uint32_t>(ht.longtab.size() - 1);
-    tb.long_blob = ht.long_blob.data(); tb.long_max_len = ht.long_max_len;
+    tb.merge = ht.merge.data();
+    tb.word = ht.word.data();
+    tb.longtab = ht.longtab.data();
+    tb.long_blob = ht.long_blob.data();
     tb.byte_to_id = ht.byte_to_id.data();
     tb.uc_stage1 = e->s1.data(); tb.uc_stage2 = e->s2.data();
     tb.trie_root = ht.trie_root.data(); tb.trie_first = ht.trie_first.data(); tb.trie_count = ht.trie_count.data();
     tb.trie_terminal = ht.trie_terminal.data(); tb.trie_edges = ht.trie_edges.data();
     tb.trie_skip = ht.trie_skip.data(); tb.trie_blob = ht.trie_blob.data();
-    tb.added_max_bytes = ht.added_max_bytes; tb.family = ht.family; tb.ignore_merges = ht.ignore_merges;
-    tb.monotone = ht.monotone;
-    tb.added_ws = ht.added_ws;
+    tb.littab = ht.littab.data(); tb.lit_blob = ht.lit_blob.data();
+    static_assert(GTOK_UC_STAGE2_LEN == gtok::kUcStage2Words && GTOK_UC_STAGE1_LEN >= gtok::kUcStage1Bmp, "class table sizes");
+    gtok::fill_table_scalars(ht, tb);
     return e;
 }
 
 void gtok_emul_destroy(void* h) { delete static_cast<Emul*>(h); }
 
-// force_monotone: 0 keep, 1 treat the vocabulary as non-monotone (exercises the one-merge-per-round path)
+// force_non_monotone: bit 0 treats the vocabulary as non-monotone (exercises the one-merge-per-round path),
+// bit 1 matches added-token literals by the trie walk (the path of vocabularies with too many literal lengths to hash)
 // Returns the token count, or -(error bits) when the kernels flagged an error.
 int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_t* doc_off, uint32_t n_docs,
                          uint32_t* out, uint32_t cap, uint32_t* out_doc_tok, uint32_t* bmask_out, int reverse,
@@ -129,12 +142,13 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     a.glong_cnt = glong.data() + static_cast<size_t>(n_tiles + 1) * kLongPerTile * 2;
     a.out_tokens = out; a.out_cap = cap; a.status = status;
     a.tb = e->tb;
-    if (force_non_monotone) a.tb.monotone = 0;
+    if (force_non_monotone & 1) a.tb.monotone = 0;
+    if (force_non_monotone & 2) a.tb.lit_n_lens = 0;            // added-token literals by the trie walk instead of the hashed table
     CpuBlk blk;
     blk.reverse = reverse != 0;
     {
         PretokSmem* sm = new PretokSmem();
-        for (uint32_t t = 0; t < n_tiles; ++t) { std::memset(sm, 0xCD, sizeof *sm); pretok_tile(blk, a, *sm, static_cast<int>(t)); }
+        for (uint32_t t = 0; t < (n + kPTile - 1) / kPTile; ++t) { std::memset(sm, 0xCD, sizeof *sm); pretok_block_init(blk, a, *sm); pretok_tile(blk, a, *sm, static_cast<int>(t)); }
         delete sm;
     }
     if (bmask_out) std::memcpy(bmask_out, bmask.data(), static_cast<size_t>(n_tiles) * kTileWords * 4);

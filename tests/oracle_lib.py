@@ -162,7 +162,7 @@ class Emul:
         if not self.h:
             raise RuntimeError("emul: " + err.value.decode())
 
-    def encode(self, data, offsets=None, reverse=False, non_monotone=False, want_starts=False):
+    def encode(self, data, offsets=None, reverse=False, non_monotone=False, want_starts=False, trie=False):
         data = bytes(data)
         out = np.empty(len(data) + 16, dtype=np.uint32)
         bm = np.zeros((len(data) + 4095) // 4096 * 128 + 8, dtype=np.uint32)
@@ -171,10 +171,10 @@ class Emul:
             offsets = np.ascontiguousarray(offsets, dtype=np.uint32)
             doc = np.zeros(offsets.size, dtype=np.uint32)
             n = self.lib.gtok_emul_encode(self.h, data, len(data), offsets.ctypes.data, offsets.size - 1, out.ctypes.data, out.size,
-                                          doc.ctypes.data, bm.ctypes.data, int(reverse), int(non_monotone))
+                                          doc.ctypes.data, bm.ctypes.data, int(reverse), int(non_monotone) | (2 if trie else 0))
         else:
             n = self.lib.gtok_emul_encode(self.h, data, len(data), None, 1, out.ctypes.data, out.size, None, bm.ctypes.data,
-                                          int(reverse), int(non_monotone))
+                                          int(reverse), int(non_monotone) | (2 if trie else 0))
         if n < 0:
             raise RuntimeError("emulated kernels flagged error bits %d" % -n)
         ids = out[:n].copy()

@@ -44,6 +44,19 @@ def test_emul_fuzz_ids_and_boundaries(emuls, oracles, family):
 
 
 @pytest.mark.parametrize("family", FAMILIES)
+def test_emul_added_tokens_by_trie_walk(emuls, oracles, family):
+    """Literals are matched through a hash table when they have few distinct lengths and by a trie
+    walk otherwise: the walk, forced here, gives the same ids."""
+    e, o = emuls[family], oracles[family]
+    if not SPECIAL[family]:
+        pytest.skip("vocabulary without added tokens")
+    for i, t in enumerate(cases.fuzz_strings(23, SPECIAL[family], per_pool=60)):
+        b = norm(o, t.encode())
+        if b:
+            assert np.array_equal(e.encode(b, trie=True, reverse=bool(i & 1)), o.encode_normalized(b)), repr(t[:60])
+
+
+@pytest.mark.parametrize("family", FAMILIES)
 def test_emul_malformed_utf8(emuls, oracles, family):
     e, o = emuls[family], oracles[family]
     for b in cases.malformed_bytes(31, 400):
