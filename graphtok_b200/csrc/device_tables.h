@@ -39,6 +39,11 @@ struct WordSlot { uint64_t k0, k1; uint32_t id; uint32_t pad[3]; };
 // a 64-bit hash and confirmed byte for byte against `long_blob`.
 struct LongSlot { uint64_t hash; uint32_t id, off, len, pad; };
 
+// Added-token literals by hash (lit_hash_finish of the weighted byte sum, see below);
+// id == kNoToken marks a free slot; bytes past the literal's end are zero.
+constexpr int kLitInline = 48;
+struct alignas(64) LitSlot { uint32_t hash, id, len, pad; uint8_t bytes[kLitInline]; };
+
 // Added-token (special-token) trie, path-compressed.  root[b] is the node after first byte b,
 // or kNoToken.  On arriving at node i the bytes blob[skip[i] >> 8 ...] (skip[i] & 0xFF of them)
 // must follow in the text (a chain of single-child nodes folded into one, so that the long
@@ -64,13 +69,13 @@ struct DeviceTables {
     uint32_t lit1_bits[8];               // bytes that open an added-token literal (one bit per byte value)
     uint32_t lit2_bits[8];               // bytes that come second in one
     uint32_t lit_single;                 // some literal is a single byte
-    // The literals once more as a hash table keyed by their bytes (slots as in the long-token table,
-    // spellings 16-byte aligned in lit_blob), with the distinct literal lengths in ascending order:
-    // the longest literal at a position is then found with one pass over the text bytes and one
-    // round of independent probes instead of a walk down the trie.  lit_n_lens == 0 (more than
-    // kLitLens distinct lengths): only the trie is used.
-    const LongSlot* littab;     uint32_t lit_mask;
-    const uint8_t* lit_blob;
+    // The literals once more as a hash table keyed by their bytes, each 64-byte slot holding the
+    // literal itself, with the distinct literal lengths in ascending order: the longest literal
+    // at a position is then found by hashing the text bytes once per pass and reading one slot
+    // per literal length, instead of a walk down the trie with a dependent load per step.
+    // lit_n_lens == 0 (more than kLitLens distinct lengths, or a literal too long for a slot):
+    // only the trie is used.
+    const LitSlot* littab;      uint32_t lit_mask;
     uint32_t lit_n_lens;
     uint32_t lit_lens[16];
     uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5
@@ -106,6 +111,14 @@ GTOK_HD uint32_t word_hash(uint64_t k0, uint64_t k1) {
     x ^= x >> 32; x *= 0xD6E8FEB86659FD93ULL;
     x ^= x >> 32;
     return static_cast<uint32_t>(x);
+}
+// Hash of a literal: sum of byte j times K^(j+1) (mod 2^32), folded with the length.  A sum, so that
+// the hashes of all prefixes of a text come out of one pass, or each from a thread of its own.
+constexpr uint32_t kLitHashK = 0x9E3779B1u;
+GTOK_HD uint32_t lit_hash_finish(uint32_t h, uint32_t len) {
+    uint32_t x = h ^ (len * 0x85EBCA77u);
+    x ^= x >> 15; x *= 0x85EBCA6Bu; x ^= x >> 13;
+    return x;
 }
 // FNV-1a over the bytes, folded with the length; used for the long-token table.
 GTOK_HD uint64_t long_hash_step(uint64_t h, uint8_t b) { return (h ^ b) * 1099511628211ULL; }

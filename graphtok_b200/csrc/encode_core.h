@@ -57,6 +57,7 @@ constexpr int kPChunks = 2 * kThreads;
 constexpr int kPWin = kPChunks * 16;                    // 8192 bytes staged per tile
 constexpr int kPTile = kPWin - kHaloL - kHaloR;         // 8000 bytes of text per tile
 constexpr int kPTileWords = kPTile / 32;                // 250 mask words per tile
+constexpr int kLitPlaces = 48;                          // places per tile where an added-token literal may start, looked up in parallel
 constexpr int kUcStage1Bmp = 512;        // first-stage entries of the class table that cover U+0000..U+FFFF (128 codepoints each)
 constexpr int kUcStage2Words = 1664;     // words of its second stage (unicode_class_table.h; checked where the tables are uploaded)
 
@@ -190,6 +191,13 @@ GTOK_DEV void shared_or(uint32_t* p, uint32_t v) {
     *p |= v;
 #endif
 }
+GTOK_DEV void shared_max64(unsigned long long* p, unsigned long long v) {
+#if defined(__CUDA_ARCH__)
+    atomicMax(p, v);
+#else
+    if (v > *p) *p = v;
+#endif
+}
 GTOK_DEV void global_or(uint32_t* p, uint32_t v) {
 #if defined(__CUDA_ARCH__)
     atomicOr(p, v);
@@ -319,7 +327,9 @@ GTOK_DEV uint32_t probe_long(const DeviceTables& tb, const uint8_t* text, uint32
     return kNoToken;
 }
 
-// Same lookup with the bytes at hand (shared memory).
+// Same lookup with the bytes at hand (shared memory).  The spellings in long_blob start on 4-byte
+// boundaries and are zero padded to one, so a candidate is compared a word at a time, all its
+// words requested together.
 GTOK_DEV uint32_t probe_long_bytes(const DeviceTables& tb, const uint8_t* bytes, uint32_t len) {
     if (len > tb.long_max_len) return kNoToken;
     uint64_t h = kLongHashSeed;
@@ -330,9 +340,14 @@ GTOK_DEV uint32_t probe_long_bytes(const DeviceTables& tb, const uint8_t* bytes,
         LongSlot s = tb.longtab[at];
         if (s.id == kNoToken) return kNoToken;
         if (s.hash == h && s.len == len) {
-            bool same = true;
-            for (uint32_t k = 0; k < len && same; ++k) same = ldg(tb.long_blob + s.off + k) == bytes[k];
-            if (same) return s.id;
+            uint32_t diff = 0;
+            for (uint32_t k = 0; k < len; k += 4) {
+                const uint32_t bw = ldg(reinterpret_cast<const uint32_t*>(tb.long_blob + s.off + k));
+                uint32_t tw = 0;
+                for (uint32_t b = 0; b < 4 && k + b < len; ++b) tw |= static_cast<uint32_t>(bytes[k + b]) << (8 * b);
+                diff |= bw ^ tw;
+            }
+            if (!diff) return s.id;
         }
         at = (at + 1) & tb.long_mask;
     }
@@ -400,6 +415,9 @@ struct PretokSmem {
     uint16_t cand16[kPWin / 16 + 4];          // per 16-byte chunk: bytes that open an added-token literal
     alignas(16) uint16_t ucs1[kUcStage1Bmp]; // the class table's first stage for the BMP and its whole second stage, copied once per block
     alignas(16) uint32_t ucs2[kUcStage2Words];
+    uint32_t lit_lens[kLitLens];             // the distinct added-token literal lengths (copy of the tables')
+    unsigned long long lit_best[kLitPlaces]; // per listed place: longest literal found there, length << 32 | id
+    uint16_t lit_at[kLitPlaces];             // places of the tile's window where a literal may start
     uint32_t dirty[(kPWin / 16 + 31) / 32];   // chunks whose plane entries a painted literal has made stale
     uint32_t dsw[kPWin / 32 + 2];             // document-start bits of the window
     uint16_t bnd16[2 * kPTileWords + 4], add16[2 * kPTileWords + 4], pend16[2 * kPTileWords + 4];
@@ -470,58 +488,83 @@ GTOK_DEV uint32_t match_literal(const EncodeArgs& a, int s, int n, GetByte byte_
     return best;
 }
 
-// The same answer from the hashed literal table: one pass over the text bytes keeps the running
-// hash; at every length some literal has the table is asked, and a slot whose hash and length
-// agree is confirmed against the literal's bytes, four at a time.  The longest confirmed literal
-// wins.  Everything stays in registers (no arrays: this runs with next to no L1 behind local memory).
+// The same answer from the hashed literal table (device_tables.h): the text's hash at every length
+// some literal has, one slot read per length, and a slot whose hash and length agree compared with
+// the text four bytes at a time.  The longest confirmed literal wins.  Everything stays in registers.
+struct LitView {                 // what the hashed matcher needs, by value (lens may point to shared memory)
+    const LitSlot* tab;
+    const uint32_t* lens;
+    uint32_t mask, n_lens, max_bytes;
+};
+// Is the literal of length `len` whose weighted byte sum is h (see lit_hash_finish) in the table, and
+// does it spell the text at s?  Returns its id or kNoToken.
 template <class GetByte>
-GTOK_DEV uint32_t match_literal_hashed(const EncodeArgs& a, int s, int n, GetByte byte_at, uint32_t* id_out) {
-    const DeviceTables& tb = a.tb;
-    uint32_t limit = static_cast<uint32_t>(n - s);
-    if (limit > tb.added_max_bytes) limit = tb.added_max_bytes;
-    if (a.docmask) for (uint32_t k = 1; k < limit; ++k) if (is_docstart_global(a, s + static_cast<int>(k))) { limit = k; break; }
-    uint32_t best = 0, li = 0;
-    uint64_t h = kLongHashSeed;
-    for (uint32_t len = 1; len <= limit && li < tb.lit_n_lens; ++len) {
-        h = long_hash_step(h, static_cast<uint8_t>(byte_at(s + static_cast<int>(len) - 1)));
-        if (len != tb.lit_lens[li]) continue;
-        ++li;
-        const uint64_t hf = long_hash_finish(h, len);
-        uint32_t at = static_cast<uint32_t>(hf) & tb.lit_mask;
-        for (int i = 0; i < kProbeLimit; ++i) {
-            const LongSlot& sl = tb.littab[at];
-            const uint32_t id = ldg(&sl.id);
-            if (id == kNoToken) break;
-            if (ldg(&sl.hash) == hf && ldg(&sl.len) == len) {
-                const uint32_t off = ldg(&sl.off);                 // 16-byte aligned, zero padded
-                uint32_t diff = 0;
-                for (uint32_t j = 0; j < len; j += 4) {
-                    const uint32_t lw = ldg(reinterpret_cast<const uint32_t*>(tb.lit_blob + off + j));
-                    uint32_t tw = 0;
-                    for (uint32_t b = 0; b < 4 && j + b < len; ++b) tw |= byte_at(s + static_cast<int>(j + b)) << (8 * b);
-                    diff |= lw ^ tw;
-                }
-                if (!diff) { best = len; *id_out = id; break; }
+GTOK_DEV uint32_t lit_lookup(const LitView& lv, uint32_t h, uint32_t len, int s, GetByte byte_at) {
+    const uint32_t hf = lit_hash_finish(h, len);
+    uint32_t at = hf & lv.mask;
+    for (int i = 0; i < kProbeLimit; ++i) {
+        const LitSlot* sl = lv.tab + at;
+        const uint32_t id = ldg(&sl->id);
+        if (id == kNoToken) return kNoToken;
+        if (ldg(&sl->hash) == hf && ldg(&sl->len) == len) {
+            uint32_t diff = 0;
+            for (uint32_t j = 0; j < len; j += 4) {
+                const uint32_t lw = ldg(reinterpret_cast<const uint32_t*>(sl->bytes + j));
+                uint32_t tw = 0;
+                for (uint32_t b = 0; b < 4 && j + b < len; ++b) tw |= byte_at(s + static_cast<int>(j + b)) << (8 * b);
+                diff |= lw ^ tw;
             }
-            at = (at + 1) & tb.lit_mask;
+            if (!diff) return id;
         }
+        at = (at + 1) & lv.mask;
+    }
+    return kNoToken;
+}
+// Bytes a literal at s may span: up to the end of the text, of the document, and the longest literal.
+template <class IsDoc>
+GTOK_DEV uint32_t lit_limit(const LitView& lv, bool batch, int s, int n, IsDoc is_doc) {
+    uint32_t limit = static_cast<uint32_t>(n - s);
+    if (limit > lv.max_bytes) limit = lv.max_bytes;
+    if (batch) for (uint32_t k = 1; k < limit; ++k) if (is_doc(s + static_cast<int>(k))) { limit = k; break; }
+    return limit;
+}
+// The longest literal at s, one thread: one pass over the bytes, a look-up at every literal length.
+template <class GetByte, class IsDoc>
+GTOK_DEV uint32_t match_literal_hashed(const LitView& lv, bool batch, int s, int n, GetByte byte_at, IsDoc is_doc, uint32_t* id_out) {
+    const uint32_t limit = lit_limit(lv, batch, s, n, is_doc);
+    uint32_t best = 0, li = 0, h = 0, pk = kLitHashK;
+    uint32_t next_len = lv.lens[0];
+    for (uint32_t len = 1; len <= limit; ++len) {
+        h += byte_at(s + static_cast<int>(len) - 1) * pk;
+        pk *= kLitHashK;
+        if (len != next_len) continue;
+        const uint32_t id = lit_lookup(lv, h, len, s, byte_at);
+        if (id != kNoToken) { best = len; *id_out = id; }
+        if (++li >= lv.n_lens) break;
+        next_len = lv.lens[li];
     }
     return best;
 }
 template <class GetByte>
 GTOK_DEV uint32_t longest_literal(const EncodeArgs& a, int s, int n, GetByte byte_at, uint32_t* id_out) {
-    return a.tb.lit_n_lens ? match_literal_hashed(a, s, n, byte_at, id_out) : match_literal(a, s, n, byte_at, id_out);
+    if (!a.tb.lit_n_lens) return match_literal(a, s, n, byte_at, id_out);
+    const LitView lv{a.tb.littab, a.tb.lit_lens, a.tb.lit_mask, a.tb.lit_n_lens, a.tb.added_max_bytes};
+    return match_literal_hashed(lv, a.docmask != nullptr, s, n, byte_at, [&](int q) { return is_docstart_global(a, q); }, id_out);
 }
 
 // The literal at global position s as seen from a tile's window (text bytes in shared memory from
 // global position lo on, the rest from global memory).  A function of its own, not inlined: it runs
-// for a handful of bytes per tile and must not cost the tile program registers.
-GTOK_DEV_NOINLINE uint32_t literal_in_window(const EncodeArgs& a, const uint8_t* win_txt, int lo, int s, int n, uint32_t* id_out) {
+// for a handful of bytes per tile and must not cost the tile program registers; everything it
+// needs comes as an argument, so that nothing is fetched through the kernel's parameter block
+// byte after byte.
+GTOK_DEV_NOINLINE uint32_t literal_in_window(const LitView lv, const uint8_t* win_txt, int lo, const uint8_t* text, const uint32_t* docmask,
+                                             int s, int n, uint32_t* id_out) {
     auto byte_at = [&](int q) -> uint32_t {
         const int i = q - lo;
-        return (i >= 0 && i < kPWin) ? win_txt[i] : ldg(a.text + q);
+        return (i >= 0 && i < kPWin) ? win_txt[i] : ldg(text + q);
     };
-    return longest_literal(a, s, n, byte_at, id_out);
+    auto is_doc = [&](int q) -> bool { return q == 0 || (docmask && ((ldg(docmask + (q >> 5)) >> (q & 31)) & 1u)); };
+    return match_literal_hashed(lv, docmask != nullptr, s, n, byte_at, is_doc, id_out);
 }
 
 // Class + flags of a byte, ignoring added tokens.  `byte_at(q)` must be valid for
@@ -888,6 +931,7 @@ GTOK_DEV void pretok_block_init(Blk& blk, const EncodeArgs& a, PretokSmem& sm) {
             if (tid == 0x0A || tid == 0x0D) at |= A_CRLF;
             if (tid == 0x20) at |= A_SP;
         } else at = tid < 0xC0 ? A_CONT : A_O;
+        if (tid < kLitLens) sm.lit_lens[tid] = a.tb.lit_lens[tid];
         sm.lut[tid] = at | (static_cast<uint32_t>(onehot_of(at)) << 8) | (((a.tb.lit1_bits[tid >> 5] >> (tid & 31)) & 1u) << 16);
     });
 }
@@ -927,7 +971,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     // many bytes remain in the document, anything else is a one-byte codepoint) and looked up in
     // the block's copy of the class table.
     blk.par([&](int tid) {
-        if (tid == 0) sm.misc[1] = 0;
+        if (tid == 0) { sm.misc[1] = 0; sm.misc[3] = 0; }
         if (tid < static_cast<int>(sizeof(sm.dirty) / 4)) sm.dirty[tid] = 0;
         for (int wd = tid; wd < kPWin / 32 + 2; wd += kThreads) {
             int gw = (lo >> 5) + wd;                 // lo is a multiple of 32
@@ -1071,8 +1115,26 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     };
     // ---- P2: paint added-token literals ----
     // A literal can only start at a byte that opens one and is followed by a byte that is second in
-    // one (two 256-bit sets that come with the tables), so the trie is walked at next to no false starts.
+    // one (two 256-bit sets that come with the tables).  The few such places of a tile are listed,
+    // then every (place, literal length) is looked up by a thread of its own -- a single thread
+    // going through all lengths of a thirty-byte literal would hold up the whole block for as long
+    // as the rest of the tile program takes -- and the longest hit of each place is painted.
     if (a.tb.added_max_bytes) {
+        auto paint = [&](int i, uint32_t ml, uint32_t id) {
+            const int p = lo + i;
+            // the id goes to the literal's slot at once, so that the next kernel need not match again
+            if (a.stage && p >= t0 && p < t0 + kPTile) a.stage[p] = id;
+            sm.attr[i] = static_cast<uint8_t>(A_ADDED | (sm.attr[i] & A_DOC));
+            sm.oh[i] = kOhAdded;
+            for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kPWin; ++j) {
+                sm.attr[i + j] = static_cast<uint8_t>(A_CONT | (sm.attr[i + j] & A_DOC));
+                sm.oh[i + j] = kOhC | kOhAdded;          // both bits: inside a literal
+            }
+            const int c_last = (i + static_cast<int>(ml) - 1 < kPWin ? i + static_cast<int>(ml) - 1 : kPWin - 1) >> 4;
+            for (int cc = i >> 4; cc <= c_last; ++cc) shared_or(&sm.dirty[cc >> 5], 1u << (cc & 31));
+            sm.misc[1] = 1;
+        };
+        const bool hashed = a.tb.lit_n_lens != 0;
         blk.par([&](int tid) {
             for (int c = tid; c < n_chunks; c += kThreads) {
                 uint32_t cand = sm.cand16[c];
@@ -1086,23 +1148,43 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                         const uint32_t b2 = byte_any(p + 1);
                         if (!((a.tb.lit2_bits[b2 >> 5] >> (b2 & 31)) & 1u)) continue;
                     }
-                    uint32_t id;
-                    uint32_t ml = literal_in_window(a, sm.txt, lo, p, n, &id);
-                    if (!ml) continue;
-                    // the id goes to the literal's slot at once, so that the next kernel need not walk the trie again
-                    if (a.stage && p >= t0 && p < t0 + kPTile) a.stage[p] = id;
-                    sm.attr[i] = static_cast<uint8_t>(A_ADDED | (sm.attr[i] & A_DOC));
-                    sm.oh[i] = kOhAdded;
-                    for (uint32_t j = 1; j < ml && i + static_cast<int>(j) < kPWin; ++j) {
-                        sm.attr[i + j] = static_cast<uint8_t>(A_CONT | (sm.attr[i + j] & A_DOC));
-                        sm.oh[i + j] = kOhC | kOhAdded;          // both bits: inside a literal
+                    if (hashed) {
+                        const uint32_t slot = shared_add(&sm.misc[3], 1u);
+                        if (slot < static_cast<uint32_t>(kLitPlaces)) { sm.lit_at[slot] = static_cast<uint16_t>(i); sm.lit_best[slot] = 0ull; continue; }
                     }
-                    const int c_last = (i + static_cast<int>(ml) - 1 < kPWin ? i + static_cast<int>(ml) - 1 : kPWin - 1) >> 4;
-                    for (int cc = c; cc <= c_last; ++cc) shared_or(&sm.dirty[cc >> 5], 1u << (cc & 31));
-                    sm.misc[1] = 1;
+                    // (no hashed table for this vocabulary, or more places than the list holds: one thread, start to end)
+                    uint32_t id;
+                    uint32_t ml;
+                    if (hashed) {
+                        const LitView lv{a.tb.littab, sm.lit_lens, a.tb.lit_mask, a.tb.lit_n_lens, a.tb.added_max_bytes};
+                        ml = literal_in_window(lv, sm.txt, lo, a.text, a.docmask, p, n, &id);
+                    } else ml = match_literal(a, p, n, byte_any, &id);
+                    if (ml) paint(i, ml, id);
                 }
             }
         });
+        uint32_t n_places = sm.misc[3];
+        if (n_places > static_cast<uint32_t>(kLitPlaces)) n_places = kLitPlaces;
+        if (n_places) {
+            const LitView lv{a.tb.littab, sm.lit_lens, a.tb.lit_mask, a.tb.lit_n_lens, a.tb.added_max_bytes};
+            auto is_doc = [&](int q) -> bool { return is_docstart_global(a, q); };
+            blk.par([&](int tid) {
+                for (uint32_t item = tid; item < n_places * lv.n_lens; item += kThreads) {
+                    const uint32_t place = item / lv.n_lens, len = lv.lens[item % lv.n_lens];
+                    const int i = sm.lit_at[place], p = lo + i;
+                    if (len > lit_limit(lv, a.docmask != nullptr, p, n, is_doc)) continue;
+                    uint32_t h = 0, pk = kLitHashK;
+                    for (uint32_t j = 0; j < len; ++j) { h += byte_any(p + static_cast<int>(j)) * pk; pk *= kLitHashK; }
+                    const uint32_t id = lit_lookup(lv, h, len, p, byte_any);
+                    if (id != kNoToken) shared_max64(&sm.lit_best[place], (static_cast<unsigned long long>(len) << 32) | id);
+                }
+            });
+            blk.par([&](int tid) {
+                if (static_cast<uint32_t>(tid) >= n_places) return;
+                const unsigned long long best = sm.lit_best[tid];
+                if (best) paint(sm.lit_at[tid], static_cast<uint32_t>(best >> 32), static_cast<uint32_t>(best));
+            });
+        }
         mark(2);
         if (sm.misc[1]) {
             // the planes of the chunks a literal was painted over
@@ -1952,14 +2034,34 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     mark(-1);
     uint32_t n_cand = n_take;
     if (filtered) {
-        blk.par([&](int tid) { if (tid == 0) sm.ctr[C_USED] = 0; });
+        // the entries' bytes into shared memory first (all threads, a byte each, so the loads overlap):
+        // max_len bytes apart in the arena, which nothing uses yet
+        uint8_t* stage_bytes = reinterpret_cast<uint8_t*>(sm.ws);
         blk.par([&](int tid) {
+            if (tid == 0) sm.ctr[C_USED] = 0;
+            if (static_cast<uint32_t>(tid) < n_take) sm.cand[tid] = list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];
+        });
+        blk.par([&](int tid) {
+            for (uint32_t x = tid; x < n_take * max_len; x += kThreads) {
+                const uint32_t w = x / max_len, r = x % max_len;
+                const unsigned long long wv = sm.cand[w];
+                const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
+                if (r < len) stage_bytes[x] = ldg(a.text + g + r);
+            }
+        });
+        typename Blk::template Local<unsigned long long> left;
+        blk.par([&](int tid) {
+            left.at(tid) = 0ull;
             if (static_cast<uint32_t>(tid) >= n_take) return;
-            const unsigned long long wv = list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];
+            const unsigned long long wv = sm.cand[tid];
             const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
-            const uint32_t id = probe_long(tb, a.text, g, len);
+            const uint32_t id = probe_long_bytes(tb, stage_bytes + tid * max_len, len);
             if (id != kNoToken) { put_id(a, g, 0, id); global_add(a.tile_tok + g / kTile, 1u); }
-            else sm.cand[shared_add(&sm.ctr[C_USED], 1u)] = wv;
+            else left.at(tid) = wv;
+        });
+        blk.par([&](int tid) {
+            const unsigned long long wv = left.at(tid);
+            if (wv) sm.cand[shared_add(&sm.ctr[C_USED], 1u)] = wv;
         });
         n_cand = sm.ctr[C_USED];
     }

@@ -265,7 +265,7 @@ struct Engine::Impl {
             !upload(ht.trie_first, &dt.trie_first, owned, err) || !upload(ht.trie_count, &dt.trie_count, owned, err) ||
             !upload(ht.trie_terminal, &dt.trie_terminal, owned, err) || !upload(ht.trie_edges, &dt.trie_edges, owned, err) ||
             !upload(ht.trie_skip, &dt.trie_skip, owned, err) || !upload(ht.trie_blob, &dt.trie_blob, owned, err) ||
-            !upload(ht.littab, &dt.littab, owned, err) || !upload(ht.lit_blob, &dt.lit_blob, owned, err))
+            !upload(ht.littab, &dt.littab, owned, err))
             return false;
         if (nfc) {
             NfcWords w;

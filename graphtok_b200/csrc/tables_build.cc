@@ -2,6 +2,7 @@
 #include "tables_build.h"
 
 #include <algorithm>
+#include <cstring>
 #include <map>
 #include <unordered_map>
 
@@ -157,6 +158,7 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
                         s.hash = h; s.id = e.second; s.off = static_cast<uint32_t>(out.long_blob.size());
                         s.len = static_cast<uint32_t>(e.first.size());
                         out.long_blob.insert(out.long_blob.end(), e.first.begin(), e.first.end());
+                        while (out.long_blob.size() % 4) out.long_blob.push_back(0);        // spellings start on 4-byte boundaries, zero padded
                         out.long_max_len = std::max(out.long_max_len, s.len);
                         break;
                     }
@@ -167,7 +169,7 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
             if (ok) break;
         }
     }
-    if (out.long_blob.empty()) out.long_blob.push_back(0);
+    out.long_blob.resize(out.long_blob.size() + 4, 0);
     if (out.longtab.empty()) out.longtab.assign(16, LongSlot{0, kNoToken, 0, 0, 0});
 
     // ---- added-token trie ---------------------------------------------------
@@ -188,46 +190,50 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
     // the same literals as a hash table (see device_tables.h)
     {
         std::vector<uint32_t> lens;
-        for (const auto& a : hv.added) if (!a.content.empty()) lens.push_back(static_cast<uint32_t>(a.content.size()));
+        bool fits = true;
+        for (const auto& a : hv.added) {
+            if (a.content.empty()) continue;
+            lens.push_back(static_cast<uint32_t>(a.content.size()));
+            if (a.content.size() > static_cast<size_t>(kLitInline)) fits = false;
+        }
         std::sort(lens.begin(), lens.end());
         lens.erase(std::unique(lens.begin(), lens.end()), lens.end());
-        out.lit_n_lens = lens.size() <= static_cast<size_t>(kLitLens) ? static_cast<uint32_t>(lens.size()) : 0u;
+        out.lit_n_lens = (fits && lens.size() <= static_cast<size_t>(kLitLens)) ? static_cast<uint32_t>(lens.size()) : 0u;
         for (int i = 0; i < kLitLens; ++i) out.lit_lens[i] = static_cast<uint32_t>(i) < out.lit_n_lens ? lens[i] : 0u;
-        out.littab.assign(16, LongSlot{0, kNoToken, 0, 0, 0});
-        out.lit_blob.assign(16, 0);
+        LitSlot empty;
+        std::memset(&empty, 0, sizeof empty);
+        empty.id = kNoToken;
+        out.littab.assign(16, empty);
         if (out.lit_n_lens) {
             for (uint32_t cap = pow2_at_least(hv.added.size() * 4 + 16);; cap <<= 1) {
-                if (cap > (1u << 24)) { out.lit_n_lens = 0; out.littab.assign(16, LongSlot{0, kNoToken, 0, 0, 0}); break; }
-                out.littab.assign(cap, LongSlot{0, kNoToken, 0, 0, 0});
-                out.lit_blob.clear();
+                if (cap > (1u << 22)) { out.lit_n_lens = 0; out.littab.assign(16, empty); break; }
+                out.littab.assign(cap, empty);
                 const uint32_t mask = cap - 1;
                 bool ok = true;
                 for (const auto& a : hv.added) {
                     if (a.content.empty()) continue;
-                    uint64_t h = kLongHashSeed;
-                    for (unsigned char c : a.content) h = long_hash_step(h, c);
-                    h = long_hash_finish(h, static_cast<uint32_t>(a.content.size()));
-                    uint32_t at = static_cast<uint32_t>(h) & mask;
+                    uint32_t h = 0, pk = kLitHashK;
+                    for (unsigned char c : a.content) { h += c * pk; pk *= kLitHashK; }
+                    h = lit_hash_finish(h, static_cast<uint32_t>(a.content.size()));
+                    uint32_t at = h & mask;
                     int steps = 0;
-                    bool dup = false;
                     for (;; at = (at + 1) & mask) {
-                        LongSlot& sl = out.littab[at];
-                        if (sl.id == kNoToken) break;
-                        if (sl.hash == h && sl.len == a.content.size() &&
-                            std::equal(a.content.begin(), a.content.end(), out.lit_blob.begin() + sl.off)) { dup = true; sl.id = a.id; break; }   // a repeated literal: the last id stands, as in the trie
-                        if (++steps >= 8) { ok = false; break; }
+                        LitSlot& sl = out.littab[at];
+                        if (sl.id == kNoToken) {
+                            sl.hash = h; sl.id = a.id; sl.len = static_cast<uint32_t>(a.content.size());
+                            std::memcpy(sl.bytes, a.content.data(), a.content.size());
+                            break;
+                        }
+                        if (sl.hash == h && sl.len == a.content.size() && std::memcmp(sl.bytes, a.content.data(), a.content.size()) == 0) {
+                            sl.id = a.id;                     // a repeated literal: the last id stands, as in the trie
+                            break;
+                        }
+                        if (++steps >= 4) { ok = false; break; }
                     }
                     if (!ok) break;
-                    if (dup) continue;
-                    LongSlot& sl = out.littab[at];
-                    sl.hash = h; sl.id = a.id; sl.len = static_cast<uint32_t>(a.content.size());
-                    sl.off = static_cast<uint32_t>(out.lit_blob.size());
-                    out.lit_blob.insert(out.lit_blob.end(), a.content.begin(), a.content.end());
-                    while (out.lit_blob.size() % 16) out.lit_blob.push_back(0);
                 }
                 if (ok) break;
             }
-            out.lit_blob.resize(out.lit_blob.size() + 16, 0);
         }
     }
     if (hv.added_max_bytes > kMaxAddedBytes) {

@@ -24,8 +24,7 @@ struct HostTables {
     std::vector<uint16_t> trie_count;
     uint32_t added_max_bytes = 0;
     uint32_t lit1_bits[8] = {}, lit2_bits[8] = {}, lit_single = 0;
-    std::vector<LongSlot> littab;
-    std::vector<uint8_t> lit_blob;
+    std::vector<LitSlot> littab;
     uint32_t lit_n_lens = 0, lit_lens[kLitLens] = {};
     uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0;
 };

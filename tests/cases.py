@@ -52,6 +52,10 @@ def tile_crossers(special):
             out.append(base + mid + " tail end.")
             if special:
                 out.append(base + special + mid + special + special + " t")
+    if special:
+        # more literals in one tile than are looked up in parallel, and literals cut by the end of the text
+        out.append("a" + special * 130 + " x " + special * 30 + special[:-1])
+        out.append((special + ".") * 70)
     # run walks that leave the tile window (plain whitespace right after a very long newline stretch,
     # and a very long stretch of spaces right after a newline)
     for head in ("a", ".", "1", ""):

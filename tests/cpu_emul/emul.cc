@@ -96,7 +96,7 @@ void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
     tb.trie_root = ht.trie_root.data(); tb.trie_first = ht.trie_first.data(); tb.trie_count = ht.trie_count.data();
     tb.trie_terminal = ht.trie_terminal.data(); tb.trie_edges = ht.trie_edges.data();
     tb.trie_skip = ht.trie_skip.data(); tb.trie_blob = ht.trie_blob.data();
-    tb.littab = ht.littab.data(); tb.lit_blob = ht.lit_blob.data();
+    tb.littab = ht.littab.data();
     static_assert(GTOK_UC_STAGE2_LEN == gtok::kUcStage2Words && GTOK_UC_STAGE1_LEN >= gtok::kUcStage1Bmp, "class table sizes");
     gtok::fill_table_scalars(ht, tb);
     return e;
