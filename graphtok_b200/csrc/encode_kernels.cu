@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdio>
 #include <mutex>
 #include <string>
 
@@ -342,8 +343,17 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
     static NoAllocScratch* scratch_of[64] = {};
     static int sm_of[64] = {};
     if (device < 0 || device >= 64) { err = "boundaries_noalloc: device index out of range"; return -1; }
+    // The handle's device becomes current for the duration of the call only: the caller's own
+    // current device is put back on every way out.
+    struct DeviceGuard {
+        int prev = -1;
+        ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+    } guard;
+    int was = -1;
+    if (cudaGetDevice(&was) != cudaSuccess) was = -1;
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) { err = std::string("cudaSetDevice: ") + cudaGetErrorString(e); return -1; }
+    if (was >= 0 && was != device) guard.prev = was;
     NoAllocScratch* sc;
     {
         std::lock_guard<std::mutex> lock(mu);
@@ -379,8 +389,19 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
     const int blocks = static_cast<int>(n_tiles < static_cast<uint32_t>(sm_of[device] * 4) ? n_tiles : sm_of[device] * 4);
     pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), stream>>>(a);
     e = cudaGetLastError();
+    // The kernel's error word comes back with the result (a copy into a local variable: no
+    // allocation).  A wait on an earlier tile that gave up leaves wrong bits behind, and two calls
+    // that overlapped on the shared array can end that way: both must fail, not return 0.
+    uint32_t err_bits = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&err_bits, sc->ctl + CTL_ERR, sizeof err_bits, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) { err = std::string("boundaries_noalloc: ") + cudaGetErrorString(e); return -1; }
+    if (err_bits) {
+        char buf[112];
+        std::snprintf(buf, sizeof buf, "boundaries_noalloc: the kernel reported error bits 0x%x (0x2 = a wait on an earlier tile gave up)", err_bits);
+        err = buf;
+        return -1;
+    }
     return 0;
 }
 

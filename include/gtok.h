@@ -101,26 +101,28 @@ int32_t gtok_x_launches_per_replay(void* handle, int32_t batch);
 /* Pre-token boundaries for callers that must not allocate.  No counterpart in the
  * reference.  Some hosts of this library cannot call cudaMalloc when they need an
  * answer: a serving process whose framework has claimed the whole device for its own
- * memory pool, a plug-in that was handed a fixed set of buffers, code running between
- * the begin and end of someone else's stream capture.  For them this entry point runs
- * the pre-tokenization kernel with all of its working memory taken from an array that is
- * part of the library's device image (about 0.5 MB, held on every GPU that loads the
- * library until the process exits), and calls no cudaMalloc, cudaFree or any other
- * allocating routine.  That fixed array is also the limit: inputs above 4 MiB
- * (4,194,304 bytes) are refused with -3 and a message in gtok_x_last_error.
+ * memory pool, or a plug-in that was handed a fixed set of buffers and nothing else.  For
+ * them this entry point runs the pre-tokenization kernel with all of its working memory
+ * taken from an array that is part of the library's device image (about 0.5 MB, held on
+ * every GPU that loads the library until the process exits), and calls no cudaMalloc,
+ * cudaFree or any other allocating routine.  That fixed array is also the limit: inputs
+ * above 4 MiB (4,194,304 bytes) are refused with -3 and a message in gtok_x_last_error.
  *   text_dev      device pointer, 16-byte aligned, one document of `len` bytes; the
  *                 buffer must be readable up to `len` rounded up to 16
  *   out_bits_dev  device pointer to ((len + 4095) / 4096) * 128 uint32; bit i of the
  *                 stream is set where a pre-token starts at byte i (same bits as
  *                 gtok_x_read_boundaries)
- *   cuda_stream   a cudaStream_t (NULL = default stream); the call returns after the
- *                 work on it has finished
+ *   cuda_stream   a cudaStream_t (NULL = default stream); the work is queued on it and
+ *                 the call waits for it (cudaStreamSynchronize) before it returns
  * The handle (created earlier, when allocation was still possible) supplies the
- * vocabulary tables.  The first call on a device looks up the array's device address;
- * make that first call before any stream capture begins.  All calls share the one
- * array, which keeps the previous call's contents (the parts that must start at zero
- * are cleared on the stream each time): two calls that overlap on the GPU race, so
- * serialise them.  Returns 0, -1 on error, -3 when `len` exceeds the limit. */
+ * vocabulary tables; its device is made current for the call and the caller's current
+ * device is put back before returning.  The first call on a device looks up the array's
+ * device address: make that first call before any stream capture begins.  All calls share
+ * the one array, which keeps the previous call's contents (the parts that must start at
+ * zero are cleared on the stream each time): two calls that overlap on the GPU race, so
+ * serialise them.  Returns 0; -1 on error, which includes error bits raised by the kernel
+ * itself (a wait on an earlier tile that gave up, as overlapping calls can cause); -3 when
+ * `len` exceeds the limit. */
 int32_t gtok_x_boundaries_noalloc(void* handle, const void* text_dev, uint32_t len, void* out_bits_dev, void* cuda_stream);
 
 /* Raw bytes of token `id` (the spelling the ids decode to); returns the length, -1 for an

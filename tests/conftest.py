@@ -14,6 +14,7 @@ SPECIAL = {"gpt2": None, "llama3": "<|reserved_special_token_3|>", "qwen25": "<|
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200; run with -m gpu on the GPU box")
+    config.addinivalue_line("markers", "slow: CPU tests on the full-size configurations (a minute or two in all)")
 
 
 def tiny_vocab(family):

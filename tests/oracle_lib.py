@@ -32,10 +32,20 @@ def build_oracle():
     return ORACLE_SO
 
 
+def reference_dir():
+    """Checkout of the reference project: $GTOK_REFERENCE_DIR, else a directory `reference` beside this
+    repository; None when neither holds its sources."""
+    for d in (os.environ.get("GTOK_REFERENCE_DIR"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if d and os.path.isdir(os.path.join(d, "src")):
+            return d
+    return None
+
+
 def build_ref():
     """Builds the reference host encoder when its sources are present; returns the path or None."""
-    if os.path.isdir("/root/reference/src") and _stale(REF_SO, [os.path.join(ORACLE_DIR, "ref_wrapper.cc")]):
-        subprocess.run(["make", "-C", ORACLE_DIR, "ref"], check=True, stdout=subprocess.DEVNULL)
+    ref = reference_dir()
+    if ref and _stale(REF_SO, [os.path.join(ORACLE_DIR, "ref_wrapper.cc")]):
+        subprocess.run(["make", "-C", ORACLE_DIR, "ref", "REF=" + ref], check=True, stdout=subprocess.DEVNULL)
     return REF_SO if os.path.exists(REF_SO) else None
 
 

@@ -244,32 +244,49 @@ def test_benchmark_configurations_full_size(built, config):
         del os.environ["GTOK_COPY_THREADS"]
 
 
-def test_configuration_4_prefix_and_chunk_property(built):
-    """Adversarial document: an 8 MB prefix against the oracle, and at the full 32 MB the
-    size-independent property that planned chunks concatenate to the whole."""
+def _reference_or_none(path):
+    """The reference's own host encoder (oracle/_ref, built from its sources) when it is there."""
+    if os.path.exists(oracle_lib.REF_SO):
+        return oracle_lib.Reference(path)
+    return None
+
+
+def test_configuration_4_full_size_and_chunks(built):
+    """Adversarial document at its stated 32 MB: the ids of one replay against the oracle (and the
+    reference's own encoder when it was built), and the concatenation of eight planned chunks
+    against the same ids."""
     from graphtok_b200 import GTok, synth
     path, doc = synth.config_doc(4)
-    o = oracle_lib.Oracle(path)
+    want = oracle_lib.Oracle(path).encode_normalized(doc)
+    ref = _reference_or_none(path)
+    if ref is not None:
+        assert np.array_equal(ref.encode_normalized(doc), want)
     g = GTok(path, max_bytes=len(doc) + 4096)
     try:
-        pre = doc[:8 << 20].decode("utf-8", "ignore").encode()
-        assert np.array_equal(g.encode(pre), o.encode_normalized(pre))
-        whole = g.encode(doc)
+        assert np.array_equal(g.encode(doc), want)
         cuts = g.plan_chunks(doc, 8)
         parts = [g.encode(doc[int(cuts[k]):int(cuts[k + 1])]) for k in range(8)]
-        assert np.array_equal(np.concatenate(parts), whole)
+        assert np.array_equal(np.concatenate(parts), want)
     finally:
         g.close()
 
 
-def test_configuration_2_batch(built):
+def test_configuration_2_batch_full_size(built):
+    """All 8,192 documents of the batch configuration in one call: ids and per-document offsets
+    against the oracle run document by document."""
     from graphtok_b200 import GTok, synth
-    path, blob, offs = synth.config_batch(2048)
+    path, blob, offs = synth.config_batch()
+    assert offs.size == 8193
     o = oracle_lib.Oracle(path)
+    want_ids, want_doc = o.encode_batch(blob, offs)
+    ref = _reference_or_none(path)
+    if ref is not None:
+        k = 1000                                    # the reference build on the first thousand documents
+        ref_ids = np.concatenate([ref.encode_normalized(blob[int(offs[i]):int(offs[i + 1])]) for i in range(k)])
+        assert np.array_equal(ref_ids, want_ids[:int(want_doc[k])])
     g = GTok(path, max_bytes=len(blob) + 4096)
     try:
         ids, doc = g.encode_batch(blob, offs)
-        want_ids, want_doc = o.encode_batch(blob, offs)
         assert np.array_equal(ids, want_ids) and np.array_equal(doc, want_doc)
     finally:
         g.close()

@@ -42,8 +42,9 @@ def test_oracle_matches_reference_build(oracles, family):
 
 
 def test_oracle_matches_reference_on_real_gpt2_vocab(built):
-    fx = "/root/reference/third_party/rs-gigatoken/tests/fixtures/gpt2_tokenizer.json"
-    if not os.path.exists(fx):
+    ref_dir = oracle_lib.reference_dir()
+    fx = os.path.join(ref_dir or "", "third_party", "rs-gigatoken", "tests", "fixtures", "gpt2_tokenizer.json")
+    if not ref_dir or not os.path.exists(fx):
         pytest.skip("the reference tree (and its GPT-2 fixture) is not on this machine")
     o, ref = oracle_lib.Oracle(fx), oracle_lib.Reference(fx)
     for t in cases.fuzz_strings(3, "<|endoftext|>", per_pool=150) + ["Hello, world! It's 2026"]:
@@ -67,3 +68,33 @@ def test_oracle_boundaries_match_sequential_regex(oracles, built, family):
             assert np.array_equal(got, want), repr(t[:60])
             if i > 250:
                 break
+
+
+def test_class_table_equals_the_references_table(built):
+    """The two-bit class of every codepoint from this library's table (csrc/unicode_class_table.h, own
+    two-stage layout) against the reference's generated table (generated/gbpe_class_table.h,
+    gbpe_classify), over 0 .. 0x1FFFFF: every pre-tokenization predicate rests on it."""
+    ref_dir = oracle_lib.reference_dir()
+    if not ref_dir or not os.path.exists(os.path.join(ref_dir, "generated", "gbpe_class_table.h")):
+        pytest.skip("the reference tree is not on this machine")
+    src = r'''
+#include "gbpe_class_table.h"
+#include "unicode_class_table.h"
+#include <cstdio>
+int main() {
+    long bad = 0;
+    for (uint32_t cp = 0; cp < 0x200000; ++cp) {
+        const uint32_t a = gbpe_classify(cp), b = gtok_uc_lookup(gtok_uc_stage1_init, gtok_uc_stage2_init, cp);
+        if (a != b && bad++ < 10) std::printf("U+%X: reference %u, here %u\\n", cp, a, b);
+    }
+    std::printf("differences=%ld\\n", bad);
+    return bad ? 1 : 0;
+}
+'''
+    with tempfile.TemporaryDirectory() as d:
+        cc, exe = os.path.join(d, "cmp.cc"), os.path.join(d, "cmp")
+        with open(cc, "w") as f:
+            f.write(src)
+        subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ref_dir, "generated"), "-I", oracle_lib.CSRC, "-o", exe, cc], check=True)
+        r = subprocess.run([exe], capture_output=True, text=True)
+        assert r.returncode == 0 and "differences=0" in r.stdout, r.stdout

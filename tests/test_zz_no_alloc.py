@@ -1,10 +1,10 @@
 """The allocation-free boundary entry point (gtok_x_boundaries_noalloc) against the regular
 path (stage + replay + gtok_x_read_boundaries).  It exists for hosts that cannot call
 cudaMalloc at the moment they need pre-token boundaries (a framework-owned memory pool,
-a fixed set of plug-in buffers, someone else's stream capture in progress); here torch
-plays that host and owns the text and the output buffer.  Bits are integers: the two
-results must be identical, on two calls in a row (the second reuses the library's
-built-in working memory with the first call's leftovers in it)."""
+a fixed set of plug-in buffers); here torch plays that host and owns the text and the
+output buffer.  Bits are integers: the two results must be identical, and identical to
+the pre-token starts of the CPU oracle, on two calls in a row (the second reuses the
+library's built-in working memory with the first call's leftovers in it)."""
 import ctypes
 
 import numpy as np
@@ -42,8 +42,17 @@ def test_noalloc_boundaries_match_regular_path_twice(built):
     try:
         first = synth.text(4, 21, 700000)[:650000].decode("utf-8", "ignore").encode()    # long digit runs: exercises the look-back states
         second = synth.text(1, 22, 300000)[:123457].decode("utf-8", "ignore").encode()   # shorter: leftovers from the first call remain
+        import oracle_lib
+        import torch
+        oracle = oracle_lib.Oracle(tiny_vocab("llama3"))
         for data in (first, second):
-            assert np.array_equal(_noalloc(g, data), _regular(g, data))
+            dev_before = torch.cuda.current_device()
+            got = _noalloc(g, data)
+            assert torch.cuda.current_device() == dev_before
+            assert np.array_equal(got, _regular(g, data))
+            _, starts = oracle.encode_normalized(data, want_starts=True)
+            # (a boundary bit on a stray continuation byte at the very start carries no pre-token; these texts have none)
+            assert np.array_equal(got, starts)
         # beyond the fixed working memory: refused, with a message, and nothing run
         r = g.lib.gtok_x_boundaries_noalloc(g.handle, ctypes.c_void_p(256), (4 << 20) + 1, ctypes.c_void_p(256), None)
         assert r == -3 and b"exceeds" in g.lib.gtok_x_last_error()
