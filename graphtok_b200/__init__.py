@@ -76,6 +76,12 @@ def load_lib():
     lib.gtok_x_boundaries_noalloc.argtypes = [vp, vp, u32, vp, vp]
     lib.gtok_x_phase_clocks.restype = i32
     lib.gtok_x_phase_clocks.argtypes = [vp, vp, i32]
+    lib.gtok_x_encode_batch_to_device.restype = i32
+    lib.gtok_x_encode_batch_to_device.argtypes = [vp, vp, vp, u32, vp, u32, vp]
+    lib.gtok_x_set_max_bytes.restype = u32
+    lib.gtok_x_set_max_bytes.argtypes = [vp, u32]
+    lib.gtok_x_work_stats.restype = i32
+    lib.gtok_x_work_stats.argtypes = [vp, vp]
     lib.gtok_x_timeline.restype = i32
     lib.gtok_x_timeline.argtypes = [vp, vp, u32]
     lib.gtok_x_token_bytes.restype = i32
@@ -109,6 +115,11 @@ class GTok:
         if not self.handle:
             raise GTokError("gtok_create failed: %s" % self.lib.gtok_x_last_error().decode("utf-8", "replace"))
         self.max_bytes = max(4096, int(max_bytes))
+
+    def set_max_bytes(self, max_bytes):
+        """Raises the handle's byte cap in place (tables stay; the context grows when next needed)."""
+        self.max_bytes = int(self.lib.gtok_x_set_max_bytes(self.handle, int(max_bytes)))
+        return self.max_bytes
 
     def close(self):
         if getattr(self, "handle", None):
@@ -145,6 +156,10 @@ class GTok:
         out = np.empty(len(blob) + 16, dtype=np.uint32)
         doc = np.empty(n_docs + 1, dtype=np.uint32)
         n = self.lib.gtok_encode_batch(self.handle, blob, offsets.ctypes.data, n_docs, out.ctypes.data, out.size, doc.ctypes.data)
+        if n == -2:
+            # more ids than bytes: only text that its vocabulary's NFC lengthens (at most threefold)
+            out = np.empty(3 * len(blob) + 64, dtype=np.uint32)
+            n = self.lib.gtok_encode_batch(self.handle, blob, offsets.ctypes.data, n_docs, out.ctypes.data, out.size, doc.ctypes.data)
         if n < 0:
             self._fail("gtok_encode_batch", n)
         return out[:n].copy(), doc
@@ -217,6 +232,14 @@ class GTok:
         if self.lib.gtok_x_plan_chunks(self.handle, data, len(data), n_parts, out.ctypes.data) != 0:
             raise GTokError("gtok_x_plan_chunks failed")
         return out
+
+    def work_stats(self):
+        """After a replay of the staged input: dict of what went from kernel to kernel (gtok_x_work_stats)."""
+        v = (ctypes.c_uint64 * 6)()
+        if self.lib.gtok_x_work_stats(self.handle, v) != 0:
+            raise GTokError("gtok_x_work_stats failed")
+        keys = ("pretokens", "unknown_pretokens", "unknown_bytes", "long_pretokens", "long_bytes", "ids_from_miss_kernel")
+        return dict(zip(keys, (int(x) for x in v)))
 
     def table_bytes(self):
         t = (ctypes.c_uint64 * 3)()

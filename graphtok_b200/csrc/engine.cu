@@ -803,17 +803,29 @@ int64_t Engine::encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, ui
 }
 
 int64_t Engine::encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes,
-                             uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_tok) {
+                             uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_tok, bool out_on_device) {
     Impl& im = *impl_;
     cudaSetDevice(im.device);
     const uint32_t len = doc_off[n_docs];
-    if (len == 0) { for (uint32_t d = 0; d <= n_docs; ++d) out_doc_tok[d] = 0; return 0; }
+    if (len == 0) {
+        if (out_on_device) { if (cudaMemset(out_doc_tok, 0, (static_cast<size_t>(n_docs) + 1) * 4) != cudaSuccess) return -1; }
+        else for (uint32_t d = 0; d <= n_docs; ++d) out_doc_tok[d] = 0;
+        return 0;
+    }
     Ctx* c = nullptr;
     int64_t total = im.run(c, true, bytes, len, doc_off, n_docs, cap_bytes, last_error_);
     if (total == Impl::kNoCtx) return -4;
     if (total < 0) return total;
     if (im.nfc && c->h_status[2] > cap_bytes) { last_error_ = "normalised text is longer than the handle's byte capacity"; return -3; }
     if (static_cast<uint64_t>(total) > out_cap) { last_error_ = "more token ids than the output buffer holds"; return -2; }
+    if (out_on_device) {
+        cudaError_t e = cudaSuccess;
+        if (total) e = cudaMemcpyAsync(out_tokens, c->d_out, static_cast<size_t>(total) * 4, cudaMemcpyDeviceToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(out_doc_tok, c->d_doc_tok, (static_cast<size_t>(n_docs) + 1) * 4, cudaMemcpyDeviceToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e != cudaSuccess) { last_error_ = std::string("token copy: ") + cudaGetErrorString(e); return -1; }
+        return total;
+    }
     if (!im.copy_out(c, out_tokens, static_cast<size_t>(total), out_doc_tok, static_cast<size_t>(n_docs) + 1, last_error_)) return -1;
     return total;
 }
@@ -887,6 +899,54 @@ int Engine::read_phase_clocks(unsigned long long* out32, bool reset) {
     if (!c || !c->d_phase) return -1;
     if (cudaMemcpy(out32, c->d_phase, 32 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     if (reset) cudaMemset(c->d_phase, 0, 32 * sizeof(unsigned long long));
+    return 0;
+}
+
+int Engine::read_work_stats(uint64_t* out6) {
+    Impl& im = *impl_;
+    cudaSetDevice(im.device);
+    Ctx* c = im.staged;
+    if (!c) { last_error_ = "nothing staged"; return -1; }
+    for (int i = 0; i < 6; ++i) out6[i] = 0;
+    uint32_t ctl[16];
+    if (cudaMemcpy(ctl, c->d_ctrl, sizeof ctl, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    const uint32_t text_bytes = im.nfc ? reinterpret_cast<volatile uint32_t*>(c->h_status)[2] : c->staged_len;
+    const uint32_t n_tiles = (text_bytes + kTile - 1) / kTile;
+    std::vector<uint32_t> bits(static_cast<size_t>(n_tiles) * kTileWords);
+    if (!bits.empty() && cudaMemcpy(bits.data(), c->d_bmask, bits.size() * 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    for (uint32_t w : bits) out6[0] += static_cast<uint64_t>(__builtin_popcount(w));
+    auto add_list = [&](const unsigned long long* d_list, long long dir, uint32_t count, uint64_t& n, uint64_t& bytes) -> bool {
+        if (!count) return true;
+        std::vector<unsigned long long> v(count);
+        const unsigned long long* src = dir > 0 ? d_list : d_list - (count - 1);
+        if (cudaMemcpy(v.data(), src, static_cast<size_t>(count) * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+        n += count;
+        for (unsigned long long e : v) bytes += e >> 32;
+        return true;
+    };
+    const EncodeArgs& a = c->args;
+    if (!add_list(a.gmiss, 1, ctl[CTL_NMISS], out6[1], out6[2]) || !add_list(a.gmed, 1, ctl[CTL_NMED], out6[1], out6[2]) ||
+        !add_list(a.gmed1, 1, ctl[CTL_NMED1], out6[1], out6[2]) || !add_list(a.gmed + (a.gmed_cap - 1), -1, ctl[CTL_NMED2], out6[1], out6[2]))
+        return -1;
+    const uint32_t n_long = ctl[CTL_NLONG];
+    if (n_long) {
+        std::vector<uint32_t> g(n_long), cnt(n_long);
+        if (cudaMemcpy(g.data(), a.glong_g, static_cast<size_t>(n_long) * 4, cudaMemcpyDeviceToHost) != cudaSuccess ||
+            cudaMemcpy(cnt.data(), a.glong_cnt, static_cast<size_t>(n_long) * 4, cudaMemcpyDeviceToHost) != cudaSuccess)
+            return -1;
+        out6[3] = n_long;
+        // a long pre-token ends at the next boundary bit
+        for (uint32_t i = 0; i < n_long; ++i) {
+            uint32_t p = g[i] + 1;
+            while (p < text_bytes && !((bits[p >> 5] >> (p & 31)) & 1u)) ++p;
+            out6[4] += p - g[i];
+            out6[5] += cnt[i];
+        }
+    }
+    // ids written by the miss kernel = all ids - one per pre-token the earlier kernels settled
+    const uint64_t total = reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
+    const uint64_t settled = out6[0] - out6[1] - out6[3];
+    out6[5] = total > settled ? total - settled : 0;
     return 0;
 }
 

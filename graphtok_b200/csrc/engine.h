@@ -26,8 +26,9 @@ public:
     // `text` is host memory.  When `out_on_device` the ids are copied device-to-device.
     int64_t encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, uint32_t* out, uint32_t max_out, bool out_on_device);
     // Documents are concatenated in `bytes`; `doc_off` has n_docs + 1 ascending offsets.
+    // `out_on_device`: out_tokens and out_doc_tok are device pointers, filled by device-to-device copies.
     int64_t encode_batch(const uint8_t* bytes, const uint32_t* doc_off, uint32_t n_docs, uint32_t cap_bytes,
-                         uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_tok);
+                         uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_tok, bool out_on_device = false);
 
     // ids -> the bytes they spell (host buffers).  Returns the byte count, -1 on error (an id outside
     // the vocabulary included), -2 when `max_out` is too small; `need` (optional) receives the byte
@@ -51,6 +52,12 @@ public:
     int read_phase_clocks(unsigned long long* out32, bool reset);
     // The block timeline of the last replay (4 kernels x 1280 blocks x 8 nanosecond stamps); cleared by the read.
     int read_timeline(unsigned long long* out, uint32_t max_words);
+    // What the last replay of the staged input handed from kernel to kernel:
+    //   out[0] pre-tokens (boundary bits), out[1] pre-tokens the whole-word table did not know and their
+    //   bytes out[2] (2..64 bytes, merged by a thread each), out[3] pre-tokens longer than 64 bytes and
+    //   their bytes out[4], out[5] ids the miss kernel wrote.  Counted on the host from the lists and bits
+    //   in device memory; -1 when nothing is staged.
+    int read_work_stats(uint64_t* out6);
     const struct DeviceTables* device_tables() const;
     int device_index() const;
 

@@ -71,7 +71,7 @@ int32_t do_encode(Handle* h, const uint8_t* text, uint32_t len, uint32_t* out, u
 }
 
 int32_t do_encode_batch(Handle* h, const uint8_t* concat_bytes, const uint32_t* doc_byte_offsets, uint32_t n_docs,
-                        uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets) {
+                        uint32_t* out_tokens, uint32_t out_cap, uint32_t* out_doc_offsets, bool dev = false) {
     for (uint32_t i = 0; i < n_docs; ++i)
         if (doc_byte_offsets[i + 1] < doc_byte_offsets[i]) return -1;
     const uint32_t first = doc_byte_offsets[0];
@@ -84,7 +84,7 @@ int32_t do_encode_batch(Handle* h, const uint8_t* concat_bytes, const uint32_t* 
         for (uint32_t i = 0; i <= n_docs; ++i) h->rebased[i] = doc_byte_offsets[i] - first;
         offs = h->rebased.data();
     }
-    int64_t n = h->engine->encode_batch(concat_bytes + first, offs, n_docs, h->cap_bytes, out_tokens, out_cap, out_doc_offsets);
+    int64_t n = h->engine->encode_batch(concat_bytes + first, offs, n_docs, h->cap_bytes, out_tokens, out_cap, out_doc_offsets, dev);
     if (n < 0) g_last_error = h->engine->last_error();
     return static_cast<int32_t>(n);
 }
@@ -119,6 +119,22 @@ int32_t gtok_encode_batch(void* handle, const uint8_t* concat_bytes, const uint3
     } catch (...) { return -1; }
 }
 
+int32_t gtok_x_encode_batch_to_device(void* handle, const uint8_t* concat_bytes, const uint32_t* doc_byte_offsets, uint32_t n_docs,
+                                      void* out_tokens_dev, uint32_t out_cap, void* out_doc_offsets_dev) {
+    if (!handle || !concat_bytes || !doc_byte_offsets || !out_tokens_dev || !out_doc_offsets_dev || n_docs == 0) return -1;
+    try {
+        return do_encode_batch(static_cast<Handle*>(handle), concat_bytes, doc_byte_offsets, n_docs, static_cast<uint32_t*>(out_tokens_dev), out_cap,
+                               static_cast<uint32_t*>(out_doc_offsets_dev), true);
+    } catch (...) { return -1; }
+}
+
+uint32_t gtok_x_set_max_bytes(void* handle, uint32_t max_bytes) {
+    if (!handle) return 0;
+    Handle* h = static_cast<Handle*>(handle);
+    if (max_bytes > h->cap_bytes) h->cap_bytes = max_bytes;
+    return h->cap_bytes;
+}
+
 uint32_t gtok_cpu_max_bytes(void*) { return 0u; }
 void gtok_set_cpu_max_bytes(void*, uint32_t) {}
 const char* gtok_cpu_backend(void*) { return "off"; }
@@ -141,7 +157,6 @@ int32_t gtok_dispatch_encode(void* dispatcher, const uint8_t* text, uint32_t len
         Dispatcher* d = static_cast<Dispatcher*>(dispatcher);
         Request me{text, len, out, max_out};
         std::unique_lock<std::mutex> lock(d->mu);
-        d->stats[1] += 1;
         d->queue.push_back(&me);
         for (;;) {
             if (me.done) return me.result;
@@ -176,7 +191,7 @@ int32_t gtok_dispatch_encode(void* dispatcher, const uint8_t* text, uint32_t len
                     at += batch[i]->len;
                     d->offs[i + 1] = at;
                 }
-                d->toks.resize(bytes * 2 + 64);                  // ids never outnumber (normalised) bytes
+                d->toks.resize(bytes * 3 + 64);                  // ids never outnumber normalised bytes, and NFC lengthens a text at most threefold
                 d->doc_tok.assign(batch.size() + 1, 0);
                 int32_t n = bytes ? do_encode_batch(&d->handle, d->blob.data(), d->offs.data(), static_cast<uint32_t>(batch.size()), d->toks.data(),
                                                     static_cast<uint32_t>(d->toks.size()), d->doc_tok.data())
@@ -192,8 +207,12 @@ int32_t gtok_dispatch_encode(void* dispatcher, const uint8_t* text, uint32_t len
             }
             const uint64_t ns = static_cast<uint64_t>(std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count());
             lock.lock();
-            d->stats[2] += 1;
+            // Counters as the reference keeps them (src/dispatcher.h:48-54): [0] requests answered by a CPU
+            // engine (none here: every request runs on the GPU, whatever `policy` and `cpu_workers` say),
+            // [1] requests answered from a batch replay, [2] batch replays, [3] requests too large to batch
+            // (each ran alone, counted here and not under [1]), [4] nanoseconds spent in replays.
             if (batch.size() == 1 && batch[0]->len > d->max_batch_bytes) d->stats[3] += 1;
+            else { d->stats[1] += batch.size(); d->stats[2] += 1; }
             d->stats[4] += ns;
             for (Request* r : batch) r->done = true;
             d->cv.notify_all();
@@ -292,6 +311,11 @@ int32_t gtok_x_boundaries_noalloc(void* handle, const void* text_dev, uint32_t l
 int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset) {
     if (!handle || !out32) return -1;
     try { return static_cast<Handle*>(handle)->engine->read_phase_clocks(reinterpret_cast<unsigned long long*>(out32), reset != 0); } catch (...) { return -1; }
+}
+
+int32_t gtok_x_work_stats(void* handle, uint64_t* out6) {
+    if (!handle || !out6) return -1;
+    try { return static_cast<Handle*>(handle)->engine->read_work_stats(out6); } catch (...) { return -1; }
 }
 
 int32_t gtok_x_timeline(void* handle, uint64_t* out, uint32_t max_words) {

@@ -7,8 +7,8 @@ Same class and method names, argument meaning and return types: `Tokenizer.encod
 `Dispatcher.encode_numpy` / `stats()`.  Every encode runs on the GPU: there is no CPU route,
 so `cpu_backend` is "off", `host_max_bytes` reads 0 and `last_route` is always "gpu".
 
-Use it as a drop-in with
-    import graphtok_b200.gpu_bpe_tokenizer as gpu_bpe_tokenizer
+The repository root also carries a package `gpu_bpe_tokenizer` that re-exports this module, so that
+a caller's `import gpu_bpe_tokenizer` works unchanged with the repository root on sys.path.
 """
 import ctypes
 import os
@@ -46,19 +46,18 @@ class Tokenizer:
 
     # ---- capacity ------------------------------------------------------------
     def _ensure(self, n_bytes):
-        """The C ABI answers -3 above the handle's byte cap and leaves growing to the caller."""
+        """The C ABI answers -3 above the handle's byte cap and leaves growing to the caller: the cap
+        is raised in place (gtok_x_set_max_bytes), the vocabulary and its tables stay as they are."""
         if n_bytes > self._cap:
             cap = self._cap
             while cap < n_bytes:
                 cap *= 2
-            self._g.close()
-            self._g = GTok(self._path, max_bytes=cap)
-            self._cap = cap
+            self._cap = self._g.set_max_bytes(cap)
 
     # ---- encode --------------------------------------------------------------
     def encode_numpy(self, text):
         data = _as_bytes(text)
-        self._ensure(len(data) * 2 + 16)        # NFC can lengthen the text
+        self._ensure(len(data) * 3 + 64)        # NFC lengthens a text at most threefold
         return self._g.encode(data)
 
     def encode(self, text):
@@ -73,24 +72,44 @@ class Tokenizer:
         blobs = [_as_bytes(t) for t in texts]
         offs = np.zeros(len(blobs) + 1, dtype=np.uint32)
         np.cumsum([len(b) for b in blobs], out=offs[1:])
-        self._ensure(int(offs[-1]) * 2 + 16)
+        self._ensure(int(offs[-1]) * 3 + 64)
         return self._g.encode_batch(b"".join(blobs), offs)
 
     def encode_to_device(self, text):
         """int32 torch tensor on the GPU (torch is imported only here, as in the reference :100-117)."""
         import torch
         data = _as_bytes(text)
-        self._ensure(len(data) * 2 + 16)
+        self._ensure(len(data) * 3 + 64)
         out = torch.empty(len(data) + 16, dtype=torch.int32, device="cuda")
         n = self._g.lib.gtok_encode_to_device(self._g.handle, data, len(data), ctypes.c_void_p(out.data_ptr()), out.numel())
+        if n == -2:                                 # text its vocabulary's NFC lengthens
+            out = torch.empty(3 * len(data) + 64, dtype=torch.int32, device="cuda")
+            n = self._g.lib.gtok_encode_to_device(self._g.handle, data, len(data), ctypes.c_void_p(out.data_ptr()), out.numel())
         if n < 0:
             raise RuntimeError("gtok_encode_to_device returned %d" % n)
         return out[:n]
 
     def encode_batch_to_device(self, texts):
+        """(int32 ids, int32 n+1 token offsets) as torch tensors on the GPU, copied device to device."""
         import torch
-        toks, offs = self.encode_batch(texts)
-        return torch.from_numpy(toks.astype(np.int32)).cuda(), torch.from_numpy(offs.astype(np.int32)).cuda()
+        blobs = [_as_bytes(t) for t in texts]
+        if not blobs:
+            return torch.zeros(0, dtype=torch.int32, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda")
+        offs = np.zeros(len(blobs) + 1, dtype=np.uint32)
+        np.cumsum([len(b) for b in blobs], out=offs[1:])
+        total = int(offs[-1])
+        self._ensure(total * 3 + 64)
+        blob = b"".join(blobs)
+        doc = torch.empty(len(blobs) + 1, dtype=torch.int32, device="cuda")
+        for room in (total + 16, 3 * total + 64):
+            out = torch.empty(room, dtype=torch.int32, device="cuda")
+            n = self._g.lib.gtok_x_encode_batch_to_device(self._g.handle, blob, offs.ctypes.data, len(blobs), ctypes.c_void_p(out.data_ptr()), out.numel(),
+                                                          ctypes.c_void_p(doc.data_ptr()))
+            if n != -2:
+                break
+        if n < 0:
+            raise RuntimeError("gtok_x_encode_batch_to_device returned %d" % n)
+        return out[:n], doc
 
     # ---- decode (on the device: ids -> the tokens' bytes, gtok_x_decode) ---------
     def decode_bytes(self, ids):
@@ -169,6 +188,9 @@ class Dispatcher:
         data = _as_bytes(text)
         out = np.empty(len(data) + 16, dtype=np.uint32)
         n = self._lib.gtok_dispatch_encode(self._h, data, len(data), out.ctypes.data, out.size)
+        if n == -2:                                 # text its vocabulary's NFC lengthens
+            out = np.empty(3 * len(data) + 64, dtype=np.uint32)
+            n = self._lib.gtok_dispatch_encode(self._h, data, len(data), out.ctypes.data, out.size)
         if n < 0:
             raise RuntimeError("gtok_dispatch_encode returned %d" % n)
         return out[:n].copy()

@@ -93,6 +93,21 @@ int32_t gtok_x_phase_clocks(void* handle, uint64_t* out32, int32_t reset);
  * pre-tokenization, 1 words, 2 miss, 3 assemble.  Returns the words written (at most 40960),
  * -1 if off.  The record is cleared by the call. */
 int32_t gtok_x_timeline(void* handle, uint64_t* out, uint32_t max_words);
+/* gtok_encode_batch with the ids and the n_docs + 1 token offsets left in device memory (device-to-
+ * device copies), as gtok_encode_to_device does for one document: what the reference's Python
+ * Tokenizer.encode_batch_to_device returns (src/python_bindings.cc:410-507); its C ABI has no such entry. */
+int32_t gtok_x_encode_batch_to_device(void* handle, const uint8_t* concat_bytes, const uint32_t* doc_byte_offsets, uint32_t n_docs,
+                                      void* out_tokens_dev, uint32_t out_cap, void* out_doc_offsets_dev);
+/* Raises the handle's byte cap (the limit behind return code -3) without re-creating the handle:
+ * vocabulary and tables stay, the GPU context grows at the next call that needs it.  The reference
+ * has callers re-create a bigger handle (src/gtok_shim.cc:160-202), which reloads the vocabulary.
+ * Returns the cap now in force (never lowered). */
+uint32_t gtok_x_set_max_bytes(void* handle, uint32_t max_bytes);
+/* What the last replay of the staged input handed from kernel to kernel, for byte accounting:
+ * out6 = {pre-tokens, pre-tokens of 2..64 bytes the whole-word table did not know, their bytes,
+ * pre-tokens longer than 64 bytes, their bytes, ids written by the miss kernel}.  Counted on the
+ * host from the lists and boundary bits in device memory (a debugging-speed call).  0 or -1. */
+int32_t gtok_x_work_stats(void* handle, uint64_t* out6);
 /* Sizes in bytes of the merge table, the whole-word table and the remaining tables. */
 void gtok_x_table_bytes(void* handle, uint64_t* out3);
 /* Kernel launches one graph replay performs (single document / batch). */

@@ -189,32 +189,49 @@ def test_sizes_change_between_calls_on_one_handle(gtoks, oracles):
         assert np.array_equal(g.encode(b), o.encode_normalized(b)), n
 
 
-def test_dispatcher_threads(built, oracles):
-    from graphtok_b200 import load_lib
-    lib = load_lib()
-    d = lib.gtok_dispatcher_create(os.fsencode(tiny_vocab("gpt2")), 0, 1 << 20, 64, 0)
-    assert d
-    o = oracles["gpt2"]
-    texts = [("request %d says hello %s" % (i, "again " * (i % 37))).encode() for i in range(200)]
-    want = [o.encode_normalized(t) for t in texts]
-    errors = []
+@pytest.mark.parametrize("policy", ("adaptive", "gpu", "cpu"))
+def test_dispatcher_threads(built, oracles, policy):
+    """Sixteen request threads against one dispatcher, 300 requests of 0 to 120,000 bytes, every
+    policy name the reference accepts (the shape of its tests/test_dispatcher.py:37-81): every answer
+    equals the oracle's, every request is counted once, and replays are shared (fewer batch replays
+    than requests answered from them)."""
+    import random
+    import gpu_bpe_tokenizer
+    from graphtok_b200 import synth
+    corpus = synth.text(1, 77, 300000).decode("utf-8", "ignore")
+    rng = random.Random(len(policy))
+    items = []
+    for _ in range(300):
+        size = rng.choice((0, 1, 40, 700, 3000, 9000, 30000, 120000))
+        a = rng.randrange(0, max(1, len(corpus) - size))
+        items.append(corpus[a:a + size])
+    items += ["<|reserved_special_token_3|>hi<|reserved_special_token_1|>", "\u00e9 x}\nfoo 1234567"]
+    o = oracles["llama3"]
+    d = gpu_bpe_tokenizer.Dispatcher(tiny_vocab("llama3"), cpu_workers=2, max_batch_bytes=1 << 20, max_batch_docs=64, policy=policy)
+    results = [None] * len(items)
+    idx = iter(range(len(items)))
+    lock = threading.Lock()
+    start = threading.Barrier(16)
 
-    def worker(k):
-        out = np.zeros(4096, dtype=np.uint32)
-        for i in range(k, len(texts), 8):
-            n = lib.gtok_dispatch_encode(d, texts[i], len(texts[i]), out.ctypes.data, out.size)
-            if n < 0 or not np.array_equal(out[:n], want[i]):
-                errors.append(i)
+    def worker():
+        start.wait()
+        while True:
+            with lock:
+                i = next(idx, None)
+            if i is None:
+                return
+            results[i] = d.encode_numpy(items[i])
 
-    ts = [threading.Thread(target=worker, args=(k,)) for k in range(8)]
+    ts = [threading.Thread(target=worker) for _ in range(16)]
     [t.start() for t in ts]
     [t.join() for t in ts]
-    stats = (ctypes.c_uint64 * 5)()
-    lib.gtok_dispatcher_stats(d, stats)
-    lib.gtok_dispatcher_destroy(d)
-    assert not errors
-    assert stats[1] == len(texts)          # every request counted
-    assert 1 <= stats[2] <= stats[1]       # served in at most as many batch replays
+    for i, (text, ids) in enumerate(zip(items, results)):
+        assert ids is not None and np.array_equal(ids, o.encode(text.encode("utf-8"))), "request %d (%d chars) differs" % (i, len(text))
+    s = d.stats()
+    d.close()
+    assert s["cpu_requests"] == 0                       # no CPU route in this library, whatever the policy
+    assert s["cpu_requests"] + s["gpu_requests"] + s["gpu_large"] == len(items)
+    assert s["gpu_batches"] < s["gpu_requests"]         # sixteen threads against one batcher must share replays
 
 
 @pytest.mark.parametrize("config", (0, 1, 3))
@@ -358,8 +375,9 @@ def test_decode_round_trip_full_size_configuration_1(built):
 
 def test_python_module_surface(built, oracles):
     """The reference's Python classes over this library: same calls, same return types."""
-    import graphtok_b200.gpu_bpe_tokenizer as gpu_bpe_tokenizer
+    import gpu_bpe_tokenizer                                    # the reference's module name
     tok = gpu_bpe_tokenizer.Tokenizer(tiny_vocab("llama3"), max_input_chars=4096)
+    handle_before = tok._g.handle
     o = oracles["llama3"]
     text = "Hello, world! It's 2026 <|reserved_special_token_3|> done"
     ids = tok.encode(text)
@@ -374,15 +392,18 @@ def test_python_module_surface(built, oracles):
     assert tok.decode(ids) == text and tok.decode_bytes(np.array(ids)) == text.encode()
     long_text = "grow " * 5000                                  # beyond max_input_chars: capacity grows
     assert tok.encode_numpy(long_text).tolist() == o.encode(long_text.encode()).tolist()
+    assert tok._g.handle == handle_before                       # grown in place: same handle, same tables
     assert tok.active_capacity >= len(long_text) and tok.regex_kind == "Llama3" and tok.cpu_backend == "off" and tok.last_route == "gpu"
     assert tok.vocab_size > 256 and tok.host_max_bytes == 0
     dev = tok.encode_to_device(text)
     assert dev.is_cuda and dev.cpu().numpy().astype(np.uint32).tolist() == ids
+    bt, bo = tok.encode_batch_to_device([text, "", "second doc"])
+    assert bt.is_cuda and bo.is_cuda and bt.cpu().numpy().astype(np.uint32).tolist() == toks.tolist() and bo.cpu().tolist() == offs.tolist()
     tok.bench_stage(text)
     n, ms = tok.bench_run()
     assert n == len(ids) and ms >= 0
     with pytest.raises(ValueError):
         gpu_bpe_tokenizer.Dispatcher(tiny_vocab("gpt2"), policy="sometimes")
     d = gpu_bpe_tokenizer.Dispatcher(tiny_vocab("llama3"), cpu_workers=0, policy="gpu")
-    assert d.encode_numpy(text).tolist() == ids and d.stats()["gpu_requests"] == 1 and d.cpu_backend == "off"
+    assert d.encode_numpy(text).tolist() == ids and d.stats()["gpu_requests"] == 1 and d.stats()["gpu_batches"] == 1 and d.cpu_backend == "off"
     d.close()
