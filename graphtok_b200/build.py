@@ -31,6 +31,20 @@ def _newer(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def source_hash():
+    """Short hash of the native sources (csrc/ and the C ABI header): identifies the build a
+    measurement or a profile summary was taken from."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(CSRC)):
+        if name.endswith((".h", ".cu", ".cc", ".map")):
+            with open(os.path.join(CSRC, name), "rb") as f:
+                h.update(name.encode() + b"\0" + f.read())
+    with open(os.path.join(HERE, "..", "include", "gtok.h"), "rb") as f:
+        h.update(f.read())
+    return h.hexdigest()[:16]
+
+
 def _nvcc():
     return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 

@@ -207,15 +207,38 @@ if rank == 0:
     want_ids, want_doc = o.encode_batch(blob, offs)
     assert np.array_equal(all_ids, want_ids)
     assert np.array_equal(all_doc, want_doc.astype(np.int64))
+# the other split: ONE document cut into one pre-token-aligned chunk per rank
+import ctypes
+lpath = synth.vocab_path("tiny_llama3")
+lo_ = oracle_lib.Oracle(lpath)
+e = oracle_lib.Emul(lpath)                # carries the library's planner (gtok_x_plan_chunks) without a GPU
+text = synth.text(1, 5, 200000)
+e.lib.gtok_emul_plan_chunks.restype = ctypes.c_int
+e.lib.gtok_emul_plan_chunks.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_void_p]
+cuts = np.zeros(world + 1, dtype=np.uint64)
+assert e.lib.gtok_emul_plan_chunks(e.h, text, len(text), world, cuts.ctypes.data) == 0
+part_ids = lo_.encode_normalized(text[int(cuts[rank]):int(cuts[rank + 1])])
+counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+dist.all_gather(counts, torch.tensor([len(part_ids)], dtype=torch.int64))
+offsets = np.concatenate([[0], np.cumsum([int(c) for c in counts])])
+gathered = [None] * world
+dist.all_gather_object(gathered, part_ids)
+if rank == 0:
+    whole = lo_.encode_normalized(text)
+    assert int(offsets[-1]) == len(whole) and np.array_equal(np.concatenate(gathered), whole)
+    assert 0 < int(cuts[1]) < len(text)
     print("OK")
 dist.destroy_process_group()
 """
 
 
 def test_two_rank_document_sharding_with_gloo(built):
-    """World size 2 on CPU: contiguous document ranges, all-gather of token counts, global offsets."""
+    """World size 2 on CPU, both ways the path shards: a batch by contiguous document ranges and one
+    document by pre-token-aligned chunks; all-gather of token counts, global offsets, ids concatenated."""
     from graphtok_b200 import synth
     synth.config_batch(64, seed=9)      # generated once here, read by both ranks
+    synth.vocab_path("tiny_llama3")
+    synth.text(1, 5, 200000)
     with tempfile.NamedTemporaryFile("w", suffix=".py", delete=False) as f:
         f.write(WORKER % {"root": ROOT})
     try:
