@@ -55,7 +55,8 @@ bool upload(const std::vector<T>& v, const T** dst, std::vector<void*>& owned, s
 // its copy-in, then sleep on a condition variable.
 class CopyPool {
 public:
-    explicit CopyPool(int workers) {
+    // spin_us: how long an idle worker keeps polling for the next job before it sleeps
+    CopyPool(int workers, int spin_us) : spin_us_(spin_us) {
         for (int i = 0; i < workers; ++i) threads_.emplace_back([this] { loop(); });
     }
     ~CopyPool() {
@@ -106,7 +107,7 @@ private:
                 if (stop_.load()) return;
                 if ((state_.load(std::memory_order_acquire) >> 32) != seen) break;
                 cpu_relax();
-                if ((spins & 255u) == 255u && std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(1500)) {
+                if ((spins & 255u) == 255u && std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(spin_us_)) {
                     std::unique_lock<std::mutex> lk(mu_);
                     sleepers_.fetch_add(1);
                     cv_.wait(lk, [&] { return stop_.load() || (state_.load(std::memory_order_acquire) >> 32) != seen; });
@@ -120,6 +121,7 @@ private:
             active_.fetch_sub(1, std::memory_order_acq_rel);
         }
     }
+    int spin_us_ = 1500;
     std::vector<std::thread> threads_;
     std::mutex mu_;
     std::condition_variable cv_;
@@ -525,6 +527,17 @@ struct Engine::Impl {
     // Host -> pinned -> device.  Large inputs piece by piece through the pool: finished pieces go to
     // the device while the rest is still being copied into pinned memory.
     bool host_to_device(uint8_t* d_dst, uint8_t* h_pin, const uint8_t* src, size_t len, cudaStream_t stream, std::string& err) {
+        if (len >= kCopyPart && is_pinned(src)) {
+            // the caller's buffer is page-locked: the device reads it directly, no staging copy (the tail
+            // up to the next multiple of 16 bytes may not be readable there, so it goes through the staging buffer)
+            const size_t whole = len & ~size_t(15);
+            GTOK_CUDA(cudaMemcpyAsync(d_dst, src, whole, cudaMemcpyHostToDevice, stream));
+            if (len > whole) {
+                std::memcpy(h_pin, src + whole, len - whole);
+                GTOK_CUDA(cudaMemcpyAsync(d_dst + whole, h_pin, 16, cudaMemcpyHostToDevice, stream));
+            }
+            return true;
+        }
         if (pool && len >= 2 * kCopyPart) {
             const int parts = static_cast<int>((len + kCopyPart - 1) / kCopyPart);
             if (part_done_n < parts) { part_done.reset(new std::atomic<uint8_t>[parts]); part_done_n = parts; }
@@ -771,7 +784,12 @@ Engine* Engine::create(const std::string& path, std::string& err) {
             want = std::min(want, std::max(1, share));
         }
         want = std::min(want, 16);
-        if (want > 1) im.pool.reset(new CopyPool(want - 1));
+        // Workers poll for 1.5 ms after a job, so that the copy-out of a call finds them awake after its
+        // copy-in; with several ranks on one host (torchrun exports LOCAL_WORLD_SIZE) that polling would
+        // take cores from the other ranks' copies, so they go to sleep almost at once.
+        int spin_us = 1500;
+        if (const char* lws = std::getenv("LOCAL_WORLD_SIZE")) { if (std::atoi(lws) > 1) spin_us = 40; }
+        if (want > 1) im.pool.reset(new CopyPool(want - 1, spin_us));
     }
     return e.release();
 }

@@ -249,6 +249,16 @@ def test_benchmark_configurations_full_size(built, config):
             assert np.array_equal(g.encode(doc), want)          # the raw document: the graph normalises it
     finally:
         g.close()
+    # a page-locked input buffer is read by the device directly (no staging copy): same ids
+    import torch
+    pinned = torch.frombuffer(bytearray(doc), dtype=torch.uint8).pin_memory()
+    out = np.empty(3 * len(doc) + 64, dtype=np.uint32)
+    g2 = GTok(path, max_bytes=len(b) + 4096)
+    try:
+        n = g2.lib.gtok_encode(g2.handle, ctypes.c_void_p(pinned.data_ptr()), len(doc), out.ctypes.data, out.size)
+        assert n == want.size and np.array_equal(out[:n], want)
+    finally:
+        g2.close()
     # the same with the staging copies on the calling thread alone
     os.environ["GTOK_COPY_THREADS"] = "1"
     try:
