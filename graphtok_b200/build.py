@@ -21,7 +21,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "--shared",
     "-Xlinker", "--version-script=" + os.path.join(CSRC, "gtok.map"),
 ]
-SOURCES = ["encode_kernels.cu", "engine.cu", "gtok_abi.cc", "vocab_host.cc", "tables_build.cc", "nfc_host.cc"]
+SOURCES = ["encode_kernels.cu", "tiny_kernel.cu", "engine.cu", "gtok_abi.cc", "vocab_host.cc", "tables_build.cc", "nfc_host.cc"]
 
 
 def _newer(target, deps):

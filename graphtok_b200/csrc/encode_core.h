@@ -101,6 +101,7 @@ struct EncodeArgs {
     uint32_t* bmask;              // boundary bits, 1 per byte
     uint32_t* amask;              // added-token-start bits
     uint32_t* tile_nb;            // boundaries per tile
+    uint32_t one_list;            // single-block kernel: every unknown pre-token of 2..64 bytes goes to the one list gmiss, whatever its length
     uint32_t sum_tiles;           // documents of up to this many tiles get their tile bases by direct summation (kSumTiles; tests use 0)
     uint32_t* tile_tok;           // ids per tile (by the tile where their pre-token starts): set by words, added to by miss, summed by assemble
     unsigned long long* st1;      // pretok look-back state per tile
@@ -138,14 +139,27 @@ struct EncodeArgs {
 };
 
 // ---- small portable helpers ---------------------------------------------------
+// Loads of data a kernel only reads go through the non-coherent path.  A translation unit whose
+// kernel reads what it wrote itself (the single-block kernel, which runs all tile programs one after
+// the other) defines GTOK_COHERENT_LOADS before including this header: every such load is then an
+// ordinary one, which sees the block's own earlier stores after a barrier.
 template <class T>
 GTOK_DEV T ldg(const T* p) {
-#if defined(__CUDA_ARCH__)
+#if defined(__CUDA_ARCH__) && !defined(GTOK_COHERENT_LOADS)
     return __ldg(p);
 #else
     return *p;
 #endif
 }
+#if defined(__CUDA_ARCH__)
+__device__ __forceinline__ uint4 ld128(const uint4* p) {       // text and slots: written by the same kernel in the single-block case
+#if defined(GTOK_COHERENT_LOADS)
+    return *p;
+#else
+    return __ldg(p);
+#endif
+}
+#endif
 GTOK_DEV int popc32(uint32_t x) {
 #if defined(__CUDA_ARCH__)
     return __popc(x);
@@ -696,7 +710,7 @@ GTOK_DEV bool run_of_128(const EncodeArgs& a, int q, uint32_t x, uint32_t y) {
     const uint4* p = reinterpret_cast<const uint4*>(a.text + q);
     uint4 v[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) v[k] = __ldg(p + k);
+    for (int k = 0; k < 8; ++k) v[k] = ld128(p + k);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         all_and &= v[k].x & v[k].y & v[k].z & v[k].w;
@@ -992,7 +1006,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             both[h][0] = both[h][1] = both[h][2] = both[h][3] = 0;
             if (p0 >= 0 && p0 < n) {
 #if defined(__CUDA_ARCH__)
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.text + p0));
+                const uint4 v = ld128(reinterpret_cast<const uint4*>(a.text + p0));
                 both[h][0] = v.x; both[h][1] = v.y; both[h][2] = v.z; both[h][3] = v.w;
 #else
                 for (int k = 0; k < 16; ++k) both[h][k >> 2] |= static_cast<uint32_t>(a.text[p0 + k]) << (8 * (k & 3));
@@ -1527,6 +1541,7 @@ struct MissSmem {
     unsigned long long word[kThreads]; // this batch's entries of the global list (0 = none, or done already)
     unsigned long long cand[kThreads]; // list entries left over after the whole-token look-up
     alignas(16) uint16_t lnk[kArenaSyms];   // live-symbol chain of each pre-token (prev << 8 | next)
+    alignas(16) uint32_t gmin[kArenaSyms / 4];   // lowest rank key of each group of four slots, laid out like the arena (pre-tokens of more than 16 bytes)
     uint8_t rawb[kArenaSyms];          // the pre-tokens' text bytes, max_len apart
     uint32_t ctr[8];
     unsigned long long clk_last;
@@ -1561,25 +1576,55 @@ GTOK_DEV uint32_t arena_at(uint32_t w4, uint32_t stride, uint32_t r) { return (r
 
 // ids/rk/nw/lnk are the arena's bases; the pre-token is number w4 / 4 of stride / 4; its k-th id
 // goes to the slot array by put(k, id).  Returns the number of ids.
+// For a pre-token of more than 16 bytes the search for the lowest key goes through gm, the lowest key
+// of each group of four slots (same interleaved layout, so four groups are one 128-bit load): a
+// step reads a quarter of what a pass over all slots would and then puts right the three groups the
+// merge touched.  The search is half of what a step costs beside its one memory round trip.
 template <class Put>
-GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint16_t* lnk, uint32_t w4, uint32_t stride,
+GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint16_t* lnk, uint32_t* gm, uint32_t w4, uint32_t stride,
                             uint32_t len, Put put) {
     // lnk[slot] = prev << 8 | next (slot numbers within the pre-token, 0xFF = none) keeps the
     // live symbols chained; slots past `len` in the last group hold no rank.
     const uint32_t groups = (len + 3u) >> 2;
+    const bool two_level = len > 16u;
+    auto group_min = [&](uint32_t g) -> uint32_t {
+#if defined(__CUDA_ARCH__)
+        const uint4 v = reinterpret_cast<const uint4*>(rk + w4)[g * (stride >> 2)];
+        return min(min(v.x, v.y), min(v.z, v.w));
+#else
+        uint32_t m = kNoRank;
+        for (uint32_t r = g * 4; r < g * 4 + 4; ++r) { const uint32_t v = rk[arena_at(w4, stride, r)]; if (v < m) m = v; }
+        return m;
+#endif
+    };
     for (;;) {
         uint32_t best = kNoRank;
+        if (two_level) {
+            const uint32_t quads = (groups + 3u) >> 2;
 #if defined(__CUDA_ARCH__)
-        const uint4* rp = reinterpret_cast<const uint4*>(rk + w4);
-        const uint32_t gs = stride >> 2;
+            const uint4* gp = reinterpret_cast<const uint4*>(gm + w4);
+            const uint32_t gs = stride >> 2;
 #pragma unroll 4
-        for (uint32_t g = 0; g < groups; ++g) {
-            const uint4 v = rp[g * gs];
-            best = min(best, min(min(v.x, v.y), min(v.z, v.w)));
-        }
+            for (uint32_t q = 0; q < quads; ++q) {
+                const uint4 v = gp[q * gs];
+                best = min(best, min(min(v.x, v.y), min(v.z, v.w)));
+            }
 #else
-        for (uint32_t r = 0; r < groups * 4; ++r) { const uint32_t v = rk[arena_at(w4, stride, r)]; if (v < best) best = v; }
+            for (uint32_t g = 0; g < quads * 4; ++g) { const uint32_t v = gm[arena_at(w4, stride, g)]; if (v < best) best = v; }
 #endif
+        } else {
+#if defined(__CUDA_ARCH__)
+            const uint4* rp = reinterpret_cast<const uint4*>(rk + w4);
+            const uint32_t gs = stride >> 2;
+#pragma unroll 4
+            for (uint32_t g = 0; g < groups; ++g) {
+                const uint4 v = rp[g * gs];
+                best = min(best, min(min(v.x, v.y), min(v.z, v.w)));
+            }
+#else
+            for (uint32_t r = 0; r < groups * 4; ++r) { const uint32_t v = rk[arena_at(w4, stride, r)]; if (v < best) best = v; }
+#endif
+        }
         if (best == kNoRank) break;
         const uint32_t bi = best & 63u, xb = arena_at(w4, stride, bi);
         const uint32_t l = lnk[xb];
@@ -1596,6 +1641,12 @@ GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, ui
         probe_rule2(a.tb, k != 0xFFu, merged, k != 0xFFu ? ids[xk] : 0u, &right, p != 0xFFu, p != 0xFFu ? ids[xp] : 0u, merged, &left);
         rk[xb] = rank_key(right.rank, bi); nw[xb] = right.res;
         if (p != 0xFFu) { rk[xp] = rank_key(left.rank, p); nw[xp] = left.res; }
+        if (two_level) {
+            const uint32_t gb = bi >> 2, gj = j >> 2;
+            gm[arena_at(w4, stride, gb)] = group_min(gb);
+            if (gj != gb) gm[arena_at(w4, stride, gj)] = group_min(gj);
+            if (p != 0xFFu && (p >> 2) != gb) gm[arena_at(w4, stride, p >> 2)] = group_min(p >> 2);
+        }
     }
     uint32_t c = 0;
     for (uint32_t i = 0; i != 0xFFu;) {
@@ -1807,7 +1858,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
             uint32_t* dst = reinterpret_cast<uint32_t*>(sm.txt + c * 16);
             const uint32_t* src = reinterpret_cast<const uint32_t*>(a.text + p);
 #if defined(__CUDA_ARCH__)
-            *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+            *reinterpret_cast<uint4*>(dst) = ld128(reinterpret_cast<const uint4*>(src));
 #else
             for (int k = 0; k < 4; ++k) dst[k] = src[k];
 #endif
@@ -1880,7 +1931,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                     else global_or(a.ctl + CTL_ERR, kErrInternal);
                     continue;
                 }
-                if (len > kShortWordMax) {
+                if (len > kShortWordMax && !a.one_list) {
                     if (len > static_cast<uint32_t>(kMedSplit) && len <= static_cast<uint32_t>(kMedSplit1)) {
                         sm.med1[shared_add(&sm.ctr[C_NMED1], 1u)] = o | (len << 12);
                         continue;
@@ -2114,13 +2165,25 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             nw[x] = q.res;
         }
     });
+    // lowest key of every group of four slots (pre-tokens of more than 16 bytes search through these)
+    if (max_len > 16u) {
+        blk.par([&](int tid) {
+            for (uint32_t i = tid; i < slots / 4u; i += kThreads) {
+                const uint32_t w = (i >> 2) % batch, g = ((i >> 2) / batch) * 4u + (i & 3u);
+                const uint32_t len = static_cast<uint32_t>(sm.word[w] >> 32);
+                uint32_t m = kNoRank;
+                if (g * 4u < len) for (uint32_t r = g * 4u; r < g * 4u + 4u; ++r) { const uint32_t v = rk[arena_at(4u * w, stride, r)]; if (v < m) m = v; }
+                sm.gmin[i] = m;
+            }
+        });
+    }
     mark(19);
     blk.par([&](int tid) {
         if (static_cast<uint32_t>(tid) >= n_here) return;
         const unsigned long long wv = sm.word[tid];
         const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
         if (len == 0) return;
-        const uint32_t cnt = bpe_arena(a, ids, rk, nw, sm.lnk, 4u * tid, stride, len, [&](uint32_t k, uint32_t id) { put_id(a, g, k, id); });
+        const uint32_t cnt = bpe_arena(a, ids, rk, nw, sm.lnk, sm.gmin, 4u * tid, stride, len, [&](uint32_t k, uint32_t id) { put_id(a, g, k, id); });
         global_add(a.tile_tok + g / kTile, cnt);
     });
     mark(20);
@@ -2323,7 +2386,7 @@ GTOK_DEV void assemble_tile(Blk& blk, const EncodeArgs& a, AsmSmem& sm, int tile
         const uint4* src = reinterpret_cast<const uint4*>(a.stage + t0) + tid * (kPer / 4);
 #pragma unroll
         for (int q = 0; q < kPer / 4; ++q) {
-            const uint4 w = __ldg(src + q);
+            const uint4 w = ld128(src + q);
             r.v[4 * q] = w.x; r.v[4 * q + 1] = w.y; r.v[4 * q + 2] = w.z; r.v[4 * q + 3] = w.w;
         }
 #else

@@ -29,6 +29,13 @@ void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_assemble(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_decode(const DecodeArgs& a, int blocks, cudaStream_t s);
 
+// The single-block kernel for short single documents (tiny_kernel.cu): text of up to kTinyMaxBytes
+// and {byte count, 1} in page-locked host memory the device can read; a.out_tokens and a.status may
+// be page-locked host memory as well.  a.text, a.meta and the work buffers are device memory as ever.
+constexpr uint32_t kTinyMaxBytes = 2048;
+cudaError_t configure_tiny_kernel();
+void launch_tiny(const EncodeArgs& a, const uint8_t* host_text, const uint32_t* host_meta, cudaStream_t s);
+
 
 // Largest input of boundaries_noalloc(), fixed by its statically reserved working memory.
 constexpr uint32_t kNoAllocMaxBytes = 4u << 20;

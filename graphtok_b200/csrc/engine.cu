@@ -160,6 +160,13 @@ struct Ctx {
     unsigned long long* d_phase = nullptr;
     uint8_t* h_text = nullptr;
     uint32_t* h_hdr = nullptr;
+    // short single documents: text, {length, 1} and ids in page-locked host memory the device reaches
+    // directly, and a graph of one single-block kernel (tiny_kernel.cu)
+    uint8_t* h_tiny_text = nullptr;
+    uint32_t* h_tiny_meta = nullptr;
+    uint32_t* h_tiny_out = nullptr;
+    cudaGraph_t tiny_graph = nullptr;
+    cudaGraphExec_t tiny_exec = nullptr;
     uint32_t* h_out = nullptr;
     size_t h_out_words = 0;
     cudaStream_t stream = nullptr;
@@ -176,6 +183,11 @@ struct Ctx {
     ~Ctx() {
         if (exec) cudaGraphExecDestroy(exec);
         if (graph) cudaGraphDestroy(graph);
+        if (tiny_exec) cudaGraphExecDestroy(tiny_exec);
+        if (tiny_graph) cudaGraphDestroy(tiny_graph);
+        if (h_tiny_text) cudaFreeHost(h_tiny_text);
+        if (h_tiny_meta) cudaFreeHost(h_tiny_meta);
+        if (h_tiny_out) cudaFreeHost(h_tiny_out);
         for (cudaEvent_t e : ev) if (e) cudaEventDestroy(e);
         for (cudaEvent_t e : out_ev) if (e) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
@@ -242,6 +254,7 @@ struct Engine::Impl {
     Ctx* staged = nullptr;
     int pretok_per_sm = 1, words_per_sm = 1, miss_per_sm = 1, asm_per_sm = 1, nfc_per_sm = 1;
     bool nfc = false;                    // the vocabulary declares NFC: the graph starts with the normalisation kernel
+    bool tiny = true;                    // short single documents take the one-kernel graph (GTOK_TINY=0 turns it off)
     uint32_t last_err_bits = 0;
     std::string norm;                    // host normalisation, used only after kErrNfcLong
     std::string norm_doc;
@@ -464,8 +477,53 @@ struct Engine::Impl {
         GTOK_CUDA(cudaStreamEndCapture(c->stream, &c->graph));
         GTOK_CUDA(cudaGraphInstantiate(&c->exec, c->graph, 0));
         GTOK_CUDA(cudaGetLastError());
+        if (!batch_mode && !nfc && tiny) {
+            // the one-kernel graph for short inputs: same work buffers, text and ids in mapped host memory
+            GTOK_CUDA(cudaHostAlloc(&c->h_tiny_text, kTinyMaxBytes + 64, cudaHostAllocMapped));
+            GTOK_CUDA(cudaHostAlloc(&c->h_tiny_meta, 64, cudaHostAllocMapped));
+            GTOK_CUDA(cudaHostAlloc(&c->h_tiny_out, (static_cast<size_t>(kTinyMaxBytes) + 16) * 4, cudaHostAllocMapped));
+            std::memset(c->h_tiny_text, 0, kTinyMaxBytes + 64);
+            std::memset(c->h_tiny_meta, 0, 64);
+            uint8_t* d_tt = nullptr;
+            uint32_t *d_tm = nullptr, *d_to = nullptr;
+            GTOK_CUDA(cudaHostGetDevicePointer(&d_tt, c->h_tiny_text, 0));
+            GTOK_CUDA(cudaHostGetDevicePointer(&d_tm, c->h_tiny_meta, 0));
+            GTOK_CUDA(cudaHostGetDevicePointer(&d_to, c->h_tiny_out, 0));
+            EncodeArgs ta = a;
+            ta.out_tokens = d_to;
+            ta.out_cap = kTinyMaxBytes + 16;
+            ta.one_list = 1;
+            // (with diagnostics on, the kernel stamps its stages into row 0 of timeline table 5; the per-phase cycle counters of the tile programs are shared with the four-kernel graph)
+            GTOK_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+            launch_tiny(ta, d_tt, d_tm, c->stream);
+            GTOK_CUDA(cudaStreamEndCapture(c->stream, &c->tiny_graph));
+            GTOK_CUDA(cudaGraphInstantiate(&c->tiny_exec, c->tiny_graph, 0));
+            GTOK_CUDA(cudaGetLastError());
+        }
         slot = std::move(c);
         return true;
+    }
+
+    // A short single document through the one-kernel graph.  Returns the id count, -2 when `out` is too
+    // small, or kNoCtx when the call should take the four-kernel path (the kernel gave up on something).
+    int64_t run_tiny(Ctx* c, const uint8_t* text, uint32_t len, uint32_t* out, uint32_t max_out, std::string& err) {
+        std::memcpy(c->h_tiny_text, text, len);
+        std::memset(c->h_tiny_text + len, 0, 16);
+        c->h_tiny_meta[0] = len;
+        c->h_tiny_meta[1] = 1;
+        c->h_status[0] = 0;
+        c->h_status[1] = 0;
+        c->staged_len = len;
+        c->staged_docs = 1;
+        last_err_bits = 0;
+        cudaError_t e = cudaGraphLaunch(c->tiny_exec, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e != cudaSuccess) { err = std::string("short-input graph: ") + cudaGetErrorString(e); return -1; }
+        if (reinterpret_cast<volatile uint32_t*>(c->h_status)[1]) return kNoCtx;
+        const uint32_t total = reinterpret_cast<volatile uint32_t*>(c->h_status)[0];
+        if (total > max_out) { err = "more token ids than the output buffer holds"; return -2; }
+        std::memcpy(out, c->h_tiny_out, static_cast<size_t>(total) * 4);
+        return total;
     }
 
     // Normalisation, in three launches: look for codepoints that can make the raw text non-NFC; if
@@ -771,6 +829,8 @@ Engine* Engine::create(const std::string& path, std::string& err) {
     im.asm_per_sm = assemble_blocks_per_sm();
     im.nfc_per_sm = nfc_blocks_per_sm();
     im.nfc = e->hv_.nfc;
+    if (const char* env = std::getenv("GTOK_TINY")) im.tiny = std::atoi(env) != 0;
+    if (im.tiny && configure_tiny_kernel() != cudaSuccess) { err = std::string("kernel configuration failed: ") + cudaGetErrorString(cudaGetLastError()); return nullptr; }
     if (!im.upload_tables(err)) return nullptr;
     {
         // GTOK_COPY_THREADS = host threads that share one call's staging copies (1 = the caller alone)
@@ -805,6 +865,14 @@ int64_t Engine::encode(const uint8_t* text, uint32_t len, uint32_t cap_bytes, ui
     Impl& im = *impl_;
     cudaSetDevice(im.device);
     if (len == 0) return 0;
+    if (!out_on_device && len <= kTinyMaxBytes && im.tiny && !im.nfc) {
+        Ctx* tc = im.ctx_for(false, len, 1, cap_bytes, last_error_);
+        if (!tc) return -1;
+        if (tc->tiny_exec) {
+            const int64_t r = im.run_tiny(tc, text, len, out, max_out, last_error_);
+            if (r != Impl::kNoCtx) return r;
+        }
+    }
     Ctx* c = nullptr;
     int64_t total = im.run(c, false, text, len, nullptr, 1, cap_bytes, last_error_);
     if (total == Impl::kNoCtx) return -1;

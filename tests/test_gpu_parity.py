@@ -49,6 +49,41 @@ def test_fuzz_malformed_edges_and_lengths(gtoks, oracles, family):
         assert np.array_equal(g.encode(b), o.encode_normalized(b)), repr(b[:60])
 
 
+@pytest.mark.parametrize("family", ("gpt2", "llama3"))
+def test_short_inputs_without_the_one_kernel_graph(built, oracles, family):
+    """Single documents of up to 2,048 bytes normally run as one single-block kernel; with that route
+    switched off (GTOK_TINY=0) the four-kernel graph must give the same ids on the same short inputs."""
+    from graphtok_b200 import GTok
+    o = oracles[family]
+    os.environ["GTOK_TINY"] = "0"
+    try:
+        g = GTok(tiny_vocab(family), max_bytes=1 << 20)
+    finally:
+        del os.environ["GTOK_TINY"]
+    try:
+        texts = [t.encode() for t in cases.fuzz_strings(45, SPECIAL[family], per_pool=80)] + cases.malformed_bytes(47, 100)
+        texts += [t.encode() for t in cases.length_ladder()]
+        for b in texts:
+            assert np.array_equal(g.encode(b), o.encode_normalized(b)), repr(b[:60])
+    finally:
+        g.close()
+
+
+def test_one_kernel_graph_sizes_and_return_codes(gtoks, oracles):
+    """The single-block route at and around its size limit, on a handle that alternates with long inputs,
+    and its -2 answer when the caller's buffer is too small."""
+    from graphtok_b200 import synth
+    g, o = gtoks["llama3"], oracles["llama3"]
+    doc = synth.text(1, 77, 300000)
+    for n in (1, 15, 16, 17, 2047, 2048, 2049, 4095, 4096, 4097, 8000, 8001, 12000, 3, 2048, 200000, 64):
+        b = doc[:n].decode("utf-8", "ignore").encode()
+        assert np.array_equal(g.encode(b), o.encode_normalized(b)), n
+    b = doc[:5000].decode("utf-8", "ignore").encode()
+    small = np.zeros(8, dtype=np.uint32)
+    assert g.lib.gtok_encode(g.handle, b, len(b), small.ctypes.data, small.size) == -2
+    assert np.array_equal(g.encode(b), o.encode_normalized(b))
+
+
 @pytest.mark.parametrize("family", FAMILIES)
 def test_batch_equals_per_document(gtoks, oracles, family):
     g, o = gtoks[family], oracles[family]
