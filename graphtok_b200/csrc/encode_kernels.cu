@@ -347,6 +347,8 @@ void launch_nfc_check(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_che
 void launch_nfc_copy(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_copy_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), s>>>(a); }
+const void* words_kernel_address() { return reinterpret_cast<const void*>(words_kernel); }
+const void* miss_kernel_address() { return reinterpret_cast<const void*>(miss_kernel); }
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s) { words_kernel<<<blocks, kThreads, sizeof(WordsSmem), s>>>(a); }
 void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s) { miss_kernel<<<blocks, kThreads, sizeof(MissSmem), s>>>(a); }
 void launch_decode(const DecodeArgs& a, int blocks, cudaStream_t s) { decode_kernel<<<blocks, kThreads, 0, s>>>(a); }

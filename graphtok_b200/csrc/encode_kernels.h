@@ -28,6 +28,9 @@ void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_miss(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_assemble(const EncodeArgs& a, int blocks, cudaStream_t s);
 void launch_decode(const DecodeArgs& a, int blocks, cudaStream_t s);
+// Addresses of two kernels as graph kernel nodes report them (to recognise the nodes that get an L2 access-policy window).
+const void* words_kernel_address();
+const void* miss_kernel_address();
 
 // The single-block kernel for short single documents (tiny_kernel.cu): text of up to kTinyMaxBytes
 // and {byte count, 1} in page-locked host memory the device can read; a.out_tokens and a.status may

@@ -475,6 +475,7 @@ struct Engine::Impl {
         launch_miss(a, miss_blocks, c->stream);
         launch_assemble(a, asm_blocks, c->stream);
         GTOK_CUDA(cudaStreamEndCapture(c->stream, &c->graph));
+        pin_tables_in_l2(c->graph);
         GTOK_CUDA(cudaGraphInstantiate(&c->exec, c->graph, 0));
         GTOK_CUDA(cudaGetLastError());
         if (!batch_mode && !nfc && tiny) {
@@ -524,6 +525,55 @@ struct Engine::Impl {
         if (total > max_out) { err = "more token ids than the output buffer holds"; return -2; }
         std::memcpy(out, c->h_tiny_out, static_cast<size_t>(total) * 4);
         return total;
+    }
+
+    // The two big look-up tables are kept resident in L2 (the reference's tables are "L2-resident" by
+    // being small; these are 8-32 MiB each and every replay of a large document would otherwise pull
+    // a good part of them from DRAM again): a part of L2 is set aside for persisting lines once per
+    // engine, and the graph's words kernel gets an access-policy window over the whole-word table, its
+    // miss kernel one over the merge table.  Failure of any of this is not an error: the kernels then
+    // simply run without the hint.
+    size_t l2_persist_bytes = 0;
+    void reserve_l2() {
+        int max_persist = 0, max_window = 0;
+        if (cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, device) != cudaSuccess) { cudaGetLastError(); return; }
+        if (const char* env = std::getenv("GTOK_L2_PERSIST")) { if (std::atoi(env) == 0) return; }
+        const size_t want = ht.merge.size() * sizeof(MergeSlot) + ht.word.size() * sizeof(WordSlot);
+        const size_t take = std::min<size_t>(want, static_cast<size_t>(max_persist));
+        if (!take || !max_window) return;
+        if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, take) != cudaSuccess) { cudaGetLastError(); return; }
+        l2_persist_bytes = take;
+        l2_window_max = static_cast<size_t>(max_window);
+    }
+    size_t l2_window_max = 0;
+    void pin_tables_in_l2(cudaGraph_t graph) {
+        if (!l2_persist_bytes) return;
+        size_t n = 0;
+        if (cudaGraphGetNodes(graph, nullptr, &n) != cudaSuccess || !n) { cudaGetLastError(); return; }
+        std::vector<cudaGraphNode_t> nodes(n);
+        if (cudaGraphGetNodes(graph, nodes.data(), &n) != cudaSuccess) { cudaGetLastError(); return; }
+        const size_t merge_bytes = ht.merge.size() * sizeof(MergeSlot), word_bytes = ht.word.size() * sizeof(WordSlot);
+        for (cudaGraphNode_t node : nodes) {
+            cudaGraphNodeType type;
+            if (cudaGraphNodeGetType(node, &type) != cudaSuccess || type != cudaGraphNodeTypeKernel) continue;
+            cudaKernelNodeParams kp;
+            if (cudaGraphKernelNodeGetParams(node, &kp) != cudaSuccess) { cudaGetLastError(); continue; }
+            const void* base = nullptr;
+            size_t bytes = 0;
+            if (kp.func == miss_kernel_address()) { base = dt.merge; bytes = merge_bytes; }
+            else if (kp.func == words_kernel_address()) { base = dt.word; bytes = word_bytes; }
+            if (!base) continue;
+            cudaKernelNodeAttrValue v;
+            std::memset(&v, 0, sizeof v);
+            v.accessPolicyWindow.base_ptr = const_cast<void*>(base);
+            v.accessPolicyWindow.num_bytes = std::min(bytes, l2_window_max);
+            // the share of the window that fits the set-aside part of L2 persists, the rest streams
+            v.accessPolicyWindow.hitRatio = static_cast<float>(std::min(1.0, static_cast<double>(l2_persist_bytes) / static_cast<double>(merge_bytes + word_bytes)));
+            v.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+            v.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+            if (cudaGraphKernelNodeSetAttribute(node, cudaKernelNodeAttributeAccessPolicyWindow, &v) != cudaSuccess) cudaGetLastError();
+        }
     }
 
     // Normalisation, in three launches: look for codepoints that can make the raw text non-NFC; if
@@ -832,6 +882,7 @@ Engine* Engine::create(const std::string& path, std::string& err) {
     if (const char* env = std::getenv("GTOK_TINY")) im.tiny = std::atoi(env) != 0;
     if (im.tiny && configure_tiny_kernel() != cudaSuccess) { err = std::string("kernel configuration failed: ") + cudaGetErrorString(cudaGetLastError()); return nullptr; }
     if (!im.upload_tables(err)) return nullptr;
+    im.reserve_l2();
     {
         // GTOK_COPY_THREADS = host threads that share one call's staging copies (1 = the caller alone)
         int want = 4;

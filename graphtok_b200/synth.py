@@ -48,9 +48,10 @@ def vocab_path(name):
     if os.path.exists(out):
         return out
     fam, cfg, seed, nbytes, merges, specials, flags = VOCABS[name]
-    corpus = os.path.join(DATA_DIR, name + ".corpus.tmp")
+    # (temporary names carry the process id: several ranks may generate the same file at once)
+    corpus = os.path.join(DATA_DIR, "%s.corpus.%d.tmp" % (name, os.getpid()))
     _run(["text", cfg, seed, nbytes, corpus] + flags)
-    tmp = out + ".tmp"
+    tmp = "%s.%d.tmp" % (out, os.getpid())
     _run(["train", fam, corpus, merges, specials, tmp])
     os.replace(tmp, out)
     os.remove(corpus)
@@ -63,7 +64,7 @@ def text(config, seed, nbytes, flags=()):
     key = "text_%d_%d_%d%s.bin" % (config, seed, nbytes, "".join(flags))
     out = os.path.join(DATA_DIR, key)
     if not os.path.exists(out):
-        tmp = out + ".tmp"
+        tmp = "%s.%d.tmp" % (out, os.getpid())
         _run(["text", config, seed, nbytes, tmp] + list(flags))
         os.replace(tmp, out)
     with open(out, "rb") as f:
@@ -85,9 +86,10 @@ def config_batch(n_docs=None, seed=None):
     blob_p = os.path.join(DATA_DIR, "batch_%d_%d.bin" % (seed, n_docs))
     off_p = os.path.join(DATA_DIR, "batch_%d_%d.off" % (seed, n_docs))
     if not (os.path.exists(blob_p) and os.path.exists(off_p)):
-        _run(["batch", seed, n_docs, blob_p + ".tmp", off_p + ".tmp"])
-        os.replace(blob_p + ".tmp", blob_p)
-        os.replace(off_p + ".tmp", off_p)
+        sfx = ".%d.tmp" % os.getpid()
+        _run(["batch", seed, n_docs, blob_p + sfx, off_p + sfx])
+        os.replace(off_p + sfx, off_p)
+        os.replace(blob_p + sfx, blob_p)
     with open(blob_p, "rb") as f:
         blob = f.read()
     return vocab_path(vocab), blob, np.fromfile(off_p, dtype=np.uint32)
