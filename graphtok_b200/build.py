@@ -2,6 +2,7 @@
 
   graphtok_b200/lib/libgtok.so      CUDA kernels + engine + C ABI, sm_100a only
   graphtok_b200/datagen/datagen     synthetic text / vocabulary generator (host only)
+  graphtok_b200/cli/gpu_bpe_tokenize   command-line tool over libgtok.so
 
 nvcc cross-compiles without a GPU.  Run as `python -m graphtok_b200.build`.
 """
@@ -67,12 +68,26 @@ def build_datagen(force=False):
     return DATAGEN
 
 
+CLI = os.path.join(HERE, "cli", "gpu_bpe_tokenize")
+
+
+def build_cli(force=False):
+    """The command-line tool over libgtok.so (the reference's gpu_bpe_tokenize modes and output files)."""
+    src = os.path.join(HERE, "cli", "gpu_bpe_tokenize.cc")
+    if not force and not _newer(CLI, [src, os.path.join(HERE, "..", "include", "gtok.h"), LIB]):
+        return CLI
+    subprocess.run(["g++", "-std=c++17", "-O2", "-o", CLI, src, "-L" + LIB_DIR, "-l:libgtok.so", "-Wl,-rpath," + LIB_DIR], check=True)
+    return CLI
+
+
 def main():
     force = "--force" in sys.argv
     build_lib(force=force, verbose="-v" in sys.argv)
     build_datagen(force=force)
+    build_cli(force=force)
     print(LIB)
     print(DATAGEN)
+    print(CLI)
 
 
 if __name__ == "__main__":
