@@ -17,13 +17,16 @@ constexpr int kWordKeyMax = 15;        // longest pre-token the inline-key word 
 constexpr int kLitLens = 16;           // distinct added-token literal lengths the hashed matcher takes
 constexpr int kProbeLimit = 64;        // every table is built so that no probe chain is longer
 
-// Merge rule table: two-choice (cuckoo) hashing over 16-byte slots.  A rule sits in one of
-// the two slots merge_slots() names, so a lookup is always exactly two independent 128-bit
-// loads issued together, hit or miss: one memory round trip per merge step, never a second
-// one for an unlucky lane of the warp.  At least four slots per rule.
-//   x = left id, y = right id, z = rank, w = result id;  x == kEmptyKey marks a free slot.
+// Merge rule table: buckets of two 16-byte slots, one 32-byte memory sector each.  A rule lives in
+// its first bucket (merge_buckets) unless that was full when the table was built; only then is it in
+// its second bucket, and the first bucket's flag (top bit of `result` in its slot 0, set even when
+// that slot is free) says so.  A look-up therefore reads ONE sector, hit or miss, in all but a few
+// per cent of the cases: the initial pair probes of the merge kernel are bound by L2 sector
+// bandwidth, and a merge step by the latency of its probes.  At least four slots per rule.
+//   x = left id, y = right id, z = rank, w = result id (31 bits);  x == kEmptyKey marks a free slot.
 // Replaces the reference's Slot64 / Slot128 pair (src/vocab.h:162-201): the
 // key and the value arrive in a single 128-bit load.
+constexpr uint32_t kBucketSpills = 0x80000000u;   // in slot 0's `result`: some rule of this bucket lives in its second bucket
 struct MergeSlot { uint32_t left, right, rank, result; };
 
 // Whole-word table: pre-token bytes (at most 15) -> token id, for pre-tokens whose
@@ -51,7 +54,7 @@ struct alignas(64) LitSlot { uint32_t hash, id, len, pad; uint8_t bytes[kLitInli
 // node per byte); then terminal[i] is the token id ending there or kNoToken, and the node
 // owns edges [first[i], first[i]+count[i]), sorted by byte; an edge is (next_node << 8) | byte.
 struct DeviceTables {
-    const MergeSlot* merge;     uint32_t merge_shift;     // slots = 2^(32 - merge_shift)
+    const MergeSlot* merge;     uint32_t merge_shift;     // buckets of two slots = 2^(32 - merge_shift)
     const WordSlot* word;       uint32_t word_mask;
     const LongSlot* longtab;    uint32_t long_mask;
     const uint8_t* long_blob;   uint32_t long_max_len;
@@ -98,13 +101,13 @@ struct DeviceTables {
 #define GTOK_HD inline
 #endif
 
-// 32-bit arithmetic only: this sits on the critical path of every merge step.  The two slot
-// numbers are the top bits of two different multiples of one mixed word.
-GTOK_HD void merge_slots(uint32_t l, uint32_t r, uint32_t shift, uint32_t* s1, uint32_t* s2) {
+// 32-bit arithmetic only: this sits on the critical path of every merge step.  The two bucket
+// numbers are the top bits of two different multiples of one mixed word; `shift` = 32 - log2(buckets).
+GTOK_HD void merge_buckets(uint32_t l, uint32_t r, uint32_t shift, uint32_t* b1, uint32_t* b2) {
     uint32_t x = l * 0x9E3779B1u ^ (r + 0x7F4A7C15u) * 0x85EBCA77u;
     x ^= x >> 15;
-    *s1 = (x * 0x2C1B3C6Du) >> shift;
-    *s2 = *s1 ^ (((x * 0x297A2D39u + 0x68E31DA4u) >> shift) | 1u);      // never the same slot
+    *b1 = (x * 0x2C1B3C6Du) >> shift;
+    *b2 = *b1 ^ (((x * 0x297A2D39u + 0x68E31DA4u) >> shift) | 1u);      // never the same bucket
 }
 GTOK_HD uint32_t word_hash(uint64_t k0, uint64_t k1) {
     uint64_t x = k0 * 0x9E3779B185EBCA87ULL + (k1 ^ (k1 >> 29)) * 0xC2B2AE3D27D4EB4FULL;

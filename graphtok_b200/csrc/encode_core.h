@@ -280,19 +280,30 @@ GTOK_DEV unsigned long long wait_state(const unsigned long long* st, int j, uint
 
 // ---- merge-rule probe ----------------------------------------------------------
 struct RankRes { uint32_t rank, res; };
-// A rule is in one of its two slots or nowhere: both are loaded at once.
+// A rule is in its first bucket (two slots, one 32-byte sector, read with two 128-bit loads) unless that
+// bucket's flag says some rule went to its second bucket; only then is the second bucket read as well.
 GTOK_DEV RankRes probe_rule(const DeviceTables& tb, uint32_t l, uint32_t r) {
-    uint32_t h1, h2;
-    merge_slots(l, r, tb.merge_shift, &h1, &h2);
+    uint32_t b1, b2;
+    merge_buckets(l, r, tb.merge_shift, &b1, &b2);
 #if defined(__CUDA_ARCH__)
-    const uint4 s0 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h1), s1 = __ldg(reinterpret_cast<const uint4*>(tb.merge) + h2);
-    if (s0.x == l && s0.y == r) return RankRes{s0.z, s0.w};
+    const uint4* t = reinterpret_cast<const uint4*>(tb.merge);
+    const uint4 s0 = __ldg(t + 2 * b1), s1 = __ldg(t + 2 * b1 + 1);
+    if (s0.x == l && s0.y == r) return RankRes{s0.z, s0.w & ~kBucketSpills};
     if (s1.x == l && s1.y == r) return RankRes{s1.z, s1.w};
+    if (s0.w & kBucketSpills) {
+        const uint4 u0 = __ldg(t + 2 * b2), u1 = __ldg(t + 2 * b2 + 1);
+        if (u0.x == l && u0.y == r) return RankRes{u0.z, u0.w & ~kBucketSpills};
+        if (u1.x == l && u1.y == r) return RankRes{u1.z, u1.w};
+    }
 #else
-    const MergeSlot& s0 = tb.merge[h1];
-    const MergeSlot& s1 = tb.merge[h2];
-    if (s0.left == l && s0.right == r) return RankRes{s0.rank, s0.result};
-    if (s1.left == l && s1.right == r) return RankRes{s1.rank, s1.result};
+    for (int pass = 0; pass < 2; ++pass) {
+        const uint32_t b = pass ? b2 : b1;
+        const MergeSlot& s0 = tb.merge[2 * b];
+        const MergeSlot& s1 = tb.merge[2 * b + 1];
+        if (s0.left == l && s0.right == r) return RankRes{s0.rank, s0.result & ~kBucketSpills};
+        if (s1.left == l && s1.right == r) return RankRes{s1.rank, s1.result};
+        if (pass == 0 && !(tb.merge[2 * b1].result & kBucketSpills)) break;
+    }
 #endif
     return RankRes{kNoRank, 0};
 }
@@ -368,27 +379,37 @@ GTOK_DEV uint32_t probe_long_bytes(const DeviceTables& tb, const uint8_t* bytes,
     return kNoToken;
 }
 
-// Two independent rule probes whose loads are all issued before the first compare, so that
-// the pair costs one memory round trip.
+// Two independent rule probes whose first-bucket loads are all issued before the first compare, so
+// that the pair costs one memory round trip (a second one for a probe whose bucket is flagged).
 GTOK_DEV void probe_rule2(const DeviceTables& tb, bool want1, uint32_t l1, uint32_t r1, RankRes* o1,
                           bool want2, uint32_t l2, uint32_t r2, RankRes* o2) {
     *o1 = RankRes{kNoRank, 0};
     *o2 = RankRes{kNoRank, 0};
 #if defined(__CUDA_ARCH__)
     uint32_t a1, a2, b1, b2;
-    merge_slots(l1, r1, tb.merge_shift, &a1, &a2);
-    merge_slots(l2, r2, tb.merge_shift, &b1, &b2);
+    merge_buckets(l1, r1, tb.merge_shift, &a1, &a2);
+    merge_buckets(l2, r2, tb.merge_shift, &b1, &b2);
     const uint4* t = reinterpret_cast<const uint4*>(tb.merge);
     uint4 x0 = make_uint4(kEmptyKey, 0, 0, 0), x1 = x0, y0 = x0, y1 = x0;
-    if (want1) { x0 = __ldg(t + a1); x1 = __ldg(t + a2); }
-    if (want2) { y0 = __ldg(t + b1); y1 = __ldg(t + b2); }
+    if (want1) { x0 = __ldg(t + 2 * a1); x1 = __ldg(t + 2 * a1 + 1); }
+    if (want2) { y0 = __ldg(t + 2 * b1); y1 = __ldg(t + 2 * b1 + 1); }
     if (want1) {
-        if (x0.x == l1 && x0.y == r1) *o1 = RankRes{x0.z, x0.w};
+        if (x0.x == l1 && x0.y == r1) *o1 = RankRes{x0.z, x0.w & ~kBucketSpills};
         else if (x1.x == l1 && x1.y == r1) *o1 = RankRes{x1.z, x1.w};
+        else if (x0.w & kBucketSpills) {
+            const uint4 u0 = __ldg(t + 2 * a2), u1 = __ldg(t + 2 * a2 + 1);
+            if (u0.x == l1 && u0.y == r1) *o1 = RankRes{u0.z, u0.w & ~kBucketSpills};
+            else if (u1.x == l1 && u1.y == r1) *o1 = RankRes{u1.z, u1.w};
+        }
     }
     if (want2) {
-        if (y0.x == l2 && y0.y == r2) *o2 = RankRes{y0.z, y0.w};
+        if (y0.x == l2 && y0.y == r2) *o2 = RankRes{y0.z, y0.w & ~kBucketSpills};
         else if (y1.x == l2 && y1.y == r2) *o2 = RankRes{y1.z, y1.w};
+        else if (y0.w & kBucketSpills) {
+            const uint4 u0 = __ldg(t + 2 * b2), u1 = __ldg(t + 2 * b2 + 1);
+            if (u0.x == l2 && u0.y == r2) *o2 = RankRes{u0.z, u0.w & ~kBucketSpills};
+            else if (u1.x == l2 && u1.y == r2) *o2 = RankRes{u1.z, u1.w};
+        }
     }
 #else
     if (want1) *o1 = probe_rule(tb, l1, r1);

@@ -63,34 +63,61 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
         // the reference's table too (src/vocab.cc:745-795).
         rules.m.emplace((static_cast<uint64_t>(m.left) << 32) | m.right, (static_cast<uint64_t>(k) << 32) | m.result);
     }
-    // Two-choice table, at least four slots per rule.  A rule whose two slots are taken evicts
-    // one of the occupants to that one's other slot, and so on; a walk that does not end soon
-    // means a cycle, and the table is rebuilt at twice the size.
+    // Buckets of two slots, at least four slots per rule.  A rule goes to its first bucket when that has
+    // room, else to its second; when both are full one occupant of the first bucket moves over to its own
+    // other bucket, and so on; a walk that does not end soon means a cycle, and the table is rebuilt at
+    // twice the size.  Afterwards every bucket that is the FIRST bucket of a rule living elsewhere is flagged.
     for (uint32_t bits = 4;; ++bits) {
         if (bits > 30) { err = "merge table cannot be built"; return false; }
         if ((1ull << bits) < static_cast<uint64_t>(hv.merges.size()) * 4) continue;
-        const uint32_t shift = 32 - bits;
+        const uint32_t shift = 32 - (bits - 1);                     // bits - 1 = log2(buckets)
         out.merge.assign(size_t(1) << bits, MergeSlot{kEmptyKey, kEmptyKey, kNoRank, 0});
         out.merge_shift = shift;
+        auto free_slot = [&](uint32_t b) -> int {
+            if (out.merge[2 * b].left == kEmptyKey) return 0;
+            if (out.merge[2 * b + 1].left == kEmptyKey) return 1;
+            return -1;
+        };
+        auto holds = [&](uint32_t b, uint32_t l, uint32_t r) {
+            return (out.merge[2 * b].left == l && out.merge[2 * b].right == r) || (out.merge[2 * b + 1].left == l && out.merge[2 * b + 1].right == r);
+        };
         bool ok = true;
+        uint32_t turn = 0;
         for (uint32_t k = 0; k < hv.merges.size() && ok; ++k) {
             const MergeRule& m = hv.merges[k];
-            uint32_t s1, s2;
-            merge_slots(m.left, m.right, shift, &s1, &s2);
-            // a later duplicate of a pair is unreachable: keep the first
-            if ((out.merge[s1].left == m.left && out.merge[s1].right == m.right) || (out.merge[s2].left == m.left && out.merge[s2].right == m.right)) continue;
+            uint32_t b1, b2;
+            merge_buckets(m.left, m.right, shift, &b1, &b2);
+            if (holds(b1, m.left, m.right) || holds(b2, m.left, m.right)) continue;    // a later duplicate of a pair is unreachable: keep the first
             MergeSlot cur{m.left, m.right, k, m.result};
-            uint32_t at = out.merge[s1].left == kEmptyKey ? s1 : s2;
+            uint32_t at = b1;
             ok = false;
             for (int kicks = 0; kicks < 512; ++kicks) {
-                std::swap(cur, out.merge[at]);
-                if (cur.left == kEmptyKey) { ok = true; break; }
-                // the evicted rule goes to its other slot
-                merge_slots(cur.left, cur.right, shift, &s1, &s2);
-                at = s1 == at ? s2 : s1;
+                int f = free_slot(at);
+                if (f < 0) {
+                    uint32_t c1, c2;
+                    merge_buckets(cur.left, cur.right, shift, &c1, &c2);
+                    const uint32_t other = at == c1 ? c2 : c1;
+                    f = free_slot(other);
+                    if (f >= 0) at = other;
+                }
+                if (f >= 0) { out.merge[2 * at + f] = cur; ok = true; break; }
+                // both buckets full: take a slot of `at`, its occupant moves on to its own other bucket
+                const uint32_t victim = 2 * at + (turn++ & 1u);
+                std::swap(cur, out.merge[victim]);
+                uint32_t c1, c2;
+                merge_buckets(cur.left, cur.right, shift, &c1, &c2);
+                at = at == c1 ? c2 : c1;
             }
         }
-        if (ok) break;
+        if (!ok) continue;
+        for (size_t i = 0; i < out.merge.size(); ++i) {
+            const MergeSlot& sl = out.merge[i];
+            if (sl.left == kEmptyKey) continue;
+            uint32_t b1, b2;
+            merge_buckets(sl.left, sl.right, shift, &b1, &b2);
+            if ((i >> 1) != b1) out.merge[2 * static_cast<size_t>(b1)].result |= kBucketSpills;
+        }
+        break;
     }
 
     // ---- whole-word table -------------------------------------------------
