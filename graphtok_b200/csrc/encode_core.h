@@ -67,7 +67,7 @@ constexpr int kUcStage2Words = 1664;     // words of its second stage (unicode_c
 constexpr int kPhaseWords = 32;
 constexpr int kTlBlocks = 1280;
 constexpr int kTlSlots = 8;
-constexpr int kTlWords = 6 * kTlBlocks * kTlSlots;     // tables 4 and 5: end of each pre-tokenization phase in a block's first and second tile
+constexpr int kTlWords = 6 * kTlBlocks * kTlSlots;     // table 4: end of each phase of a block's first pre-tokenization tile, then (overwritten by the later kernel) of its last miss batch; table 5: the single-block kernel's stages
 
 constexpr uint32_t kInvalidTok = 0xFFFFFFFFu;
 constexpr uint32_t kLongRef = 0x80000000u;      // tok[] entry that stands for a whole long pre-token
@@ -280,18 +280,28 @@ GTOK_DEV unsigned long long wait_state(const unsigned long long* st, int j, uint
 
 // ---- merge-rule probe ----------------------------------------------------------
 struct RankRes { uint32_t rank, res; };
-// A rule is in its first bucket (two slots, one 32-byte sector, read with two 128-bit loads) unless that
+#if defined(__CUDA_ARCH__)
+// Both slots of a bucket with one 256-bit load (sm_100): the merge kernel is bound by the number of
+// scattered load requests its threads make, and this halves them.
+__device__ __forceinline__ void load_bucket(const MergeSlot* bucket, uint4* s0, uint4* s1) {
+    asm volatile("ld.global.nc.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(s0->x), "=r"(s0->y), "=r"(s0->z), "=r"(s0->w), "=r"(s1->x), "=r"(s1->y), "=r"(s1->z), "=r"(s1->w)
+                 : "l"(bucket));
+}
+#endif
+// A rule is in its first bucket (two slots, one 32-byte sector, read with one 256-bit load) unless that
 // bucket's flag says some rule went to its second bucket; only then is the second bucket read as well.
 GTOK_DEV RankRes probe_rule(const DeviceTables& tb, uint32_t l, uint32_t r) {
     uint32_t b1, b2;
     merge_buckets(l, r, tb.merge_shift, &b1, &b2);
 #if defined(__CUDA_ARCH__)
-    const uint4* t = reinterpret_cast<const uint4*>(tb.merge);
-    const uint4 s0 = __ldg(t + 2 * b1), s1 = __ldg(t + 2 * b1 + 1);
+    uint4 s0, s1;
+    load_bucket(tb.merge + 2 * b1, &s0, &s1);
     if (s0.x == l && s0.y == r) return RankRes{s0.z, s0.w & ~kBucketSpills};
     if (s1.x == l && s1.y == r) return RankRes{s1.z, s1.w};
     if (s0.w & kBucketSpills) {
-        const uint4 u0 = __ldg(t + 2 * b2), u1 = __ldg(t + 2 * b2 + 1);
+        uint4 u0, u1;
+        load_bucket(tb.merge + 2 * b2, &u0, &u1);
         if (u0.x == l && u0.y == r) return RankRes{u0.z, u0.w & ~kBucketSpills};
         if (u1.x == l && u1.y == r) return RankRes{u1.z, u1.w};
     }
@@ -389,15 +399,15 @@ GTOK_DEV void probe_rule2(const DeviceTables& tb, bool want1, uint32_t l1, uint3
     uint32_t a1, a2, b1, b2;
     merge_buckets(l1, r1, tb.merge_shift, &a1, &a2);
     merge_buckets(l2, r2, tb.merge_shift, &b1, &b2);
-    const uint4* t = reinterpret_cast<const uint4*>(tb.merge);
     uint4 x0 = make_uint4(kEmptyKey, 0, 0, 0), x1 = x0, y0 = x0, y1 = x0;
-    if (want1) { x0 = __ldg(t + 2 * a1); x1 = __ldg(t + 2 * a1 + 1); }
-    if (want2) { y0 = __ldg(t + 2 * b1); y1 = __ldg(t + 2 * b1 + 1); }
+    if (want1) load_bucket(tb.merge + 2 * a1, &x0, &x1);
+    if (want2) load_bucket(tb.merge + 2 * b1, &y0, &y1);
     if (want1) {
         if (x0.x == l1 && x0.y == r1) *o1 = RankRes{x0.z, x0.w & ~kBucketSpills};
         else if (x1.x == l1 && x1.y == r1) *o1 = RankRes{x1.z, x1.w};
         else if (x0.w & kBucketSpills) {
-            const uint4 u0 = __ldg(t + 2 * a2), u1 = __ldg(t + 2 * a2 + 1);
+            uint4 u0, u1;
+            load_bucket(tb.merge + 2 * a2, &u0, &u1);
             if (u0.x == l1 && u0.y == r1) *o1 = RankRes{u0.z, u0.w & ~kBucketSpills};
             else if (u1.x == l1 && u1.y == r1) *o1 = RankRes{u1.z, u1.w};
         }
@@ -406,7 +416,8 @@ GTOK_DEV void probe_rule2(const DeviceTables& tb, bool want1, uint32_t l1, uint3
         if (y0.x == l2 && y0.y == r2) *o2 = RankRes{y0.z, y0.w & ~kBucketSpills};
         else if (y1.x == l2 && y1.y == r2) *o2 = RankRes{y1.z, y1.w};
         else if (y0.w & kBucketSpills) {
-            const uint4 u0 = __ldg(t + 2 * b2), u1 = __ldg(t + 2 * b2 + 1);
+            uint4 u0, u1;
+            load_bucket(tb.merge + 2 * b2, &u0, &u1);
             if (u0.x == l2 && u0.y == r2) *o2 = RankRes{u0.z, u0.w & ~kBucketSpills};
             else if (u1.x == l2 && u1.y == r2) *o2 = RankRes{u1.z, u1.w};
         }
@@ -2101,6 +2112,16 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             unsigned long long t = cycle_now();
             if (slot >= 0) add_cycles(a.phase_clk + slot, t - sm.clk_last);
             sm.clk_last = t;
+#if defined(__CUDA_ARCH__)
+            // timeline table 4, row of this block: when each phase of its (last) batch ended, and which class that was
+            if (blockIdx.x < kTlBlocks) {
+                unsigned long long ns;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+                unsigned long long* row = a.phase_clk + kPhaseWords + (static_cast<size_t>(4) * kTlBlocks + blockIdx.x) * kTlSlots;
+                row[slot < 0 ? 0 : slot - 15] = ns;                 // slots 16..20 -> 1..5
+                row[7] = max_len * 1000ull + n_take;
+            }
+#endif
         });
     };
     mark(-1);
@@ -2114,11 +2135,33 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             if (static_cast<uint32_t>(tid) < n_take) sm.cand[tid] = list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];
         });
         blk.par([&](int tid) {
-            for (uint32_t x = tid; x < n_take * max_len; x += kThreads) {
-                const uint32_t w = x / max_len, r = x % max_len;
-                const unsigned long long wv = sm.cand[w];
-                const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
-                if (r < len) stage_bytes[x] = ldg(a.text + g + r);
+            // (a word of four bytes per load where the address allows, and four loads in flight per thread:
+            // a plain byte loop waits for every byte in turn, thirty-two memory round trips in a row)
+            const uint32_t words_per = max_len / 4u;
+            for (uint32_t x0 = tid; x0 < n_take * words_per; x0 += 4 * kThreads) {
+                uint32_t v[4];
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t x = x0 + u * kThreads;
+                    v[u] = 0;
+                    if (x >= n_take * words_per) continue;
+                    const uint32_t w = x / words_per, r = (x % words_per) * 4u;
+                    const unsigned long long wv = sm.cand[w];
+                    const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
+                    if (r >= len) continue;
+                    const uint8_t* p = a.text + g + r;
+                    if (r + 4u <= len && (reinterpret_cast<uintptr_t>(p) & 3u) == 0) v[u] = ldg(reinterpret_cast<const uint32_t*>(p));
+                    else for (uint32_t b = 0; b < 4u && r + b < len; ++b) v[u] |= static_cast<uint32_t>(ldg(p + b)) << (8 * b);
+                }
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t x = x0 + u * kThreads;
+                    if (x < n_take * words_per) reinterpret_cast<uint32_t*>(stage_bytes)[x] = v[u];     // bytes past the entry's end are never read
+                }
             }
         });
         typename Blk::template Local<unsigned long long> left;
