@@ -61,7 +61,7 @@ def build_lib(force=False, verbose=False):
 
 
 def build_datagen(force=False):
-    src = [os.path.join(HERE, "datagen", f) for f in ("datagen.cc", "seqsplit.h")] + [os.path.join(CSRC, "unicode_class_table.h")]
+    src = [os.path.join(HERE, "datagen", f) for f in ("datagen.cc", "seqsplit.h")] + [os.path.join(CSRC, f) for f in ("unicode_class_table.h", "unicode_wide_table.h")]
     if not force and not _newer(DATAGEN, src):
         return DATAGEN
     subprocess.run(["g++", "-std=c++17", "-O2", "-o", DATAGEN, src[0]], check=True)

@@ -59,7 +59,7 @@ struct DeviceTables {
     const LongSlot* longtab;    uint32_t long_mask;
     const uint8_t* long_blob;   uint32_t long_max_len;
     const uint32_t* byte_to_id;          // [256]
-    const uint16_t* uc_stage1;           // unicode class table, see unicode_class_table.h
+    const uint16_t* uc_stage1;           // unicode class table, see unicode_class_table.h (unicode_wide_table.h when uc_wide)
     const uint32_t* uc_stage2;
     const uint32_t* trie_root;           // [256]
     const uint32_t* trie_first;
@@ -81,7 +81,8 @@ struct DeviceTables {
     const LitSlot* littab;      uint32_t lit_mask;
     uint32_t lit_n_lens;
     uint32_t lit_lens[16];
-    uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5
+    uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5, 3 DeepSeek-V3
+    uint32_t uc_wide;                    // the class table is the wide one (unicode_wide_table.h: four bits per codepoint)
     uint32_t ignore_merges;
     uint32_t monotone;
     uint32_t added_ws;                   // some added-token literal contains a space, CR or LF

@@ -89,9 +89,23 @@ enum : uint32_t {
 
 // Per-byte attribute (shared memory, pretok only).
 enum : uint8_t {
-    A_L = 0, A_N = 1, A_S = 2, A_O = 3, A_CONT = 4, A_ADDED = 5, A_OUT = 7, A_CLS = 7,
-    A_CRLF = 8, A_SP = 16, A_DOC = 32,
+    A_L = 0, A_N = 1, A_S = 2, A_O = 3, A_CONT = 4, A_ADDED = 5, A_P = 6, A_OUT = 7, A_CLS = 7,
+    A_CRLF = 8, A_SP = 16, A_DOC = 32, A_CJK = 64,
 };
+// A_P (\p{P} or \p{S}) and A_CJK (the three ranges of the second DeepSeek-V3 pattern) only occur with
+// the wide class table, where A_L also covers \p{M}.
+
+// Class of codepoint cp from the two-stage table: two bits per codepoint, eight words per leaf
+// (L, N, S, other), or with `wide` four bits per codepoint, sixteen words per leaf (the values of
+// A_L, A_N, A_S, A_O, A_P).
+template <class Stage1, class Stage2>
+GTOK_DEV uint32_t uc_class(Stage1 s1, Stage2 s2, uint32_t cp, bool wide) {
+    if (cp > 0x10FFFFu) return A_O;
+    const uint32_t leaf = s1(cp >> 7);
+    if (wide) return (s2(leaf * 16u + ((cp & 127u) >> 3)) >> ((cp & 7u) * 4u)) & 15u;
+    return (s2(leaf * 8u + ((cp & 127u) >> 4)) >> ((cp & 15u) * 2u)) & 3u;
+}
+GTOK_DEV bool cp_is_cjk(uint32_t cp) { return (cp >= 0x4E00u && cp <= 0x9FA5u) || (cp >= 0x3040u && cp <= 0x30FFu); }
 
 struct EncodeArgs {
     const uint8_t* text;          // padded; readable kTile + kWin bytes past the capacity
@@ -444,6 +458,7 @@ enum { PL_L = 0, PL_N, PL_S, PL_O, PL_C, PL_AD, PL_CRLF, PL_SP, PL_AP, kPlanes }
 
 GTOK_DEV uint8_t onehot_of(uint8_t at) {
     int c = at & A_CLS;
+    if (c == A_P) c = A_O;        // the planes know four classes; the wide classes are read from the attribute bytes
     uint8_t oh = c <= A_ADDED ? static_cast<uint8_t>(1u << c) : 0;
     if (at & A_CRLF) oh |= kOhCrlf;
     if (at & A_SP) oh |= kOhSp;
@@ -632,13 +647,9 @@ GTOK_DEV uint8_t plain_attr(const EncodeArgs& a, int p, int n, GetByte byte_at, 
         else if ((b & 0xF8u) == 0xF0u && avail >= 4)
             cp = ((b & 0x07u) << 18) | ((byte_at(p + 1) & 0x3Fu) << 12) | ((byte_at(p + 2) & 0x3Fu) << 6) | (byte_at(p + 3) & 0x3Fu);
     }
-    uint32_t cls;
-    if (cp > 0x10FFFFu) cls = A_O;
-    else {
-        uint32_t leaf = ldg(a.tb.uc_stage1 + (cp >> 7));
-        uint32_t w = ldg(a.tb.uc_stage2 + leaf * 8u + ((cp & 127u) >> 4));
-        cls = (w >> ((cp & 15u) * 2u)) & 3u;
-    }
+    const bool wide = a.tb.uc_wide != 0;
+    const uint32_t cls = uc_class([&](uint32_t i) { return static_cast<uint32_t>(ldg(a.tb.uc_stage1 + i)); }, [&](uint32_t i) { return ldg(a.tb.uc_stage2 + i); }, cp, wide);
+    if (wide && cp_is_cjk(cp)) flags |= A_CJK;
     if (b == 0x0Au || b == 0x0Du) flags |= A_CRLF;
     if (b == 0x20u) flags |= A_SP;
     return static_cast<uint8_t>(cls | flags);
@@ -835,10 +846,137 @@ GTOK_DEV int contraction_at(const Win& w, int k, bool ci) {
     return contraction_at(w, k, attr_at(w, k), ci);
 }
 
+// ---- DeepSeek-V3 ----
+// Three Split steps one after the other (src/vocab.cc:132-137 of the reference): numbers in
+// threes, runs inside the three CJK ranges, then the main pattern on every piece the first two
+// left, for which a piece's ends are the ends of the text.  Where the main pattern's matches
+// start follows from the codepoints next to a position (the alternatives are tried in order at
+// each place, but which one wins is settled by what a place and its neighbours are), with three
+// walks: back along ASCII letters to the punctuation mark that may have taken them along, back
+// over newlines to the punctuation whose match swallowed them, forward over whitespace to a later
+// newline.  Classes here: A_L letters and marks, A_N, A_S whitespace, A_P punctuation and symbols,
+// A_O the rest (matched by nothing unless a letter follows).
+GTOK_DEV int dcls(uint8_t a) {            // class of a neighbour, -1 for "nothing there" (an added token, outside)
+    const int c = a & A_CLS;
+    return (c <= A_O || c == A_P) ? c : -1;
+}
+GTOK_DEV bool ascii_letter(uint32_t b) { return (b >= 'a' && b <= 'z') || (b >= 'A' && b <= 'Z'); }
+GTOK_DEV bool ascii_punct(uint32_t b) { return (b >= 0x21u && b <= 0x2Fu) || (b >= 0x3Au && b <= 0x40u) || (b >= 0x5Bu && b <= 0x60u) || (b >= 0x7Bu && b <= 0x7Eu); }
+// Do the codepoints with attributes x and y (neither an added token nor outside) lie in one piece of
+// the first two steps?  Numbers are pieces of their own, and a piece is inside or outside the CJK ranges.
+GTOK_DEV bool ds_same_piece(uint8_t x, uint8_t y) {
+    if ((x & A_CLS) == A_N || (y & A_CLS) == A_N) return false;
+    return ((x ^ y) & A_CJK) == 0;
+}
+// Lead of the codepoint before / after the one at p (attribute ap) inside p's piece, or -1.
+GTOK_DEV int ds_prev(const Win& w, int p, uint8_t ap, uint8_t* aq) {
+    if (ap & A_DOC) return -1;
+    const int q = prev_lead(w, p);
+    if (q < 0) return -1;
+    *aq = attr_at(w, q);
+    if (dcls(*aq) < 0 || !ds_same_piece(*aq, ap)) return -1;
+    return q;
+}
+GTOK_DEV int ds_next(const Win& w, int p, uint8_t ap, uint8_t* ar) {
+    const int r = next_lead(w, p);
+    if (r < 0) return -1;
+    *ar = attr_at(w, r);
+    if (dcls(*ar) < 0 || !ds_same_piece(*ar, ap)) return -1;
+    return r;
+}
+// Does the first alternative (one ASCII punctuation mark, then ASCII letters) start a match at the
+// mark at m?  It does when a letter follows and the scan can be at m: the mark is not inside a run
+// of punctuation and not behind the space such a run takes along.
+GTOK_DEV bool ds_mark_takes_letters(const Win& w, int m, uint8_t am) {
+    if (!ascii_punct(text_at(w, m))) return false;
+    uint8_t ar, aq;
+    const int r = ds_next(w, m, am, &ar);
+    if (r < 0 || !ascii_letter(text_at(w, r))) return false;
+    const int q = ds_prev(w, m, am, &aq);
+    if (q < 0) return true;
+    return !((aq & A_CLS) == A_P || (aq & A_SP));
+}
+GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, bool* pending, bool* nstart) {
+    *pending = false;
+    const int cur = a0 & A_CLS;
+    if (cur == A_N) *nstart = true;
+    if (a0 & A_DOC) return true;
+    const int q = prev_lead(w, p);
+    if (q < 0) return true;
+    const uint8_t a1 = attr_at(w, q);
+    const int prev = dcls(a1);
+    if (prev < 0) return true;                               // after an added token
+    if (cur == A_N) {
+        if (prev != A_N) return true;
+        *nstart = false;
+        *pending = true;                                     // its place in the run decides (every third one starts a piece)
+        return false;
+    }
+    if (!ds_same_piece(a1, a0)) return true;                 // after a number, or into / out of the CJK ranges
+    const bool pcrlf = (a1 & A_CRLF) != 0;
+    if (cur == A_L) {
+        if (prev == A_L) {
+            // inside a run of letters: only where ASCII letters that a punctuation mark took along end
+            if (!ascii_letter(text_at(w, q)) || ascii_letter(text_at(w, p))) return false;
+            int k = q;
+            uint8_t ak = a1;
+            for (;;) {
+                uint8_t aj;
+                const int j = ds_prev(w, k, ak, &aj);
+                if (j < 0) return false;
+                if ((aj & A_CLS) == A_L && ascii_letter(text_at(w, j))) { k = j; ak = aj; continue; }
+                return ds_mark_takes_letters(w, j, aj);
+            }
+        }
+        if (prev == A_S) return pcrlf;                       // one whitespace codepoint (no newline) or one "other" leads the letters
+        if (prev == A_O) return false;
+        // prev == A_P
+        return !(ascii_letter(text_at(w, p)) && ds_mark_takes_letters(w, q, a1));
+    }
+    if (cur == A_P) return !(prev == A_P || (a1 & A_SP));
+    if (cur == A_S && (a0 & A_CRLF)) return prev == A_L || prev == A_O;     // else behind punctuation (taken along) or inside whitespace
+    if (cur == A_S) {
+        if (prev != A_S) return true;
+        if (pcrlf) {
+            // newlines before: taken along by punctuation (then whitespace starts afresh here), or part of
+            // a whitespace match that runs on through its last newline
+            int k = q;
+            uint8_t ak = a1;
+            for (;;) {
+                uint8_t aj;
+                const int j = ds_prev(w, k, ak, &aj);
+                if (j < 0) break;
+                if (aj & A_CRLF) { k = j; ak = aj; continue; }
+                if ((aj & A_CLS) == A_P) return true;
+                break;
+            }
+            k = p;
+            ak = a0;
+            for (;;) {
+                uint8_t aj;
+                const int j = ds_next(w, k, ak, &aj);
+                if (j < 0 || (aj & A_CLS) != A_S) return true;
+                if (aj & A_CRLF) return false;
+                k = j; ak = aj;
+            }
+        }
+        // inside plain whitespace: the last codepoint before a non-space stays behind for what follows
+        uint8_t ar;
+        const int r = ds_next(w, p, a0, &ar);
+        return r >= 0 && (ar & A_CLS) != A_S;
+    }
+    // cur == A_O
+    if (prev != A_O) return true;
+    uint8_t ar;
+    const int r = ds_next(w, p, a0, &ar);
+    return r >= 0 && (ar & A_CLS) == A_L;
+}
+
 // Boundary decision for the lead byte at p with attribute a0 (class L/N/S/O).
 // Sets *pending for a Llama-3 digit inside a digit run, whose answer depends on
 // its index in the run and is filled in later.
 GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool* pending, bool* nstart) {
+    if (family == 3) return is_boundary_deepseek(w, p, a0, pending, nstart);
     *pending = false;
     const int cur = a0 & A_CLS;
     const bool ci = family != 0;
@@ -961,19 +1099,21 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
 template <class Blk>
 GTOK_DEV void pretok_block_init(Blk& blk, const EncodeArgs& a, PretokSmem& sm) {
     blk.par([&](int tid) {
+        const bool wide = a.tb.uc_wide != 0;      // the wide table is larger than the block's copy: it stays in global memory
+        if (!wide) {
 #if defined(__CUDA_ARCH__)
-        // 128-bit copies (both arrays are whole multiples of 16 bytes and 16-byte aligned in device memory)
-        for (int i = tid; i < kUcStage1Bmp / 8; i += kThreads) reinterpret_cast<uint4*>(sm.ucs1)[i] = __ldg(reinterpret_cast<const uint4*>(a.tb.uc_stage1) + i);
-        for (int i = tid; i < kUcStage2Words / 4; i += kThreads) reinterpret_cast<uint4*>(sm.ucs2)[i] = __ldg(reinterpret_cast<const uint4*>(a.tb.uc_stage2) + i);
+            // 128-bit copies (both arrays are whole multiples of 16 bytes and 16-byte aligned in device memory)
+            for (int i = tid; i < kUcStage1Bmp / 8; i += kThreads) reinterpret_cast<uint4*>(sm.ucs1)[i] = __ldg(reinterpret_cast<const uint4*>(a.tb.uc_stage1) + i);
+            for (int i = tid; i < kUcStage2Words / 4; i += kThreads) reinterpret_cast<uint4*>(sm.ucs2)[i] = __ldg(reinterpret_cast<const uint4*>(a.tb.uc_stage2) + i);
 #else
-        for (int i = tid; i < kUcStage1Bmp; i += kThreads) sm.ucs1[i] = ldg(a.tb.uc_stage1 + i);
-        for (int i = tid; i < kUcStage2Words; i += kThreads) sm.ucs2[i] = ldg(a.tb.uc_stage2 + i);
+            for (int i = tid; i < kUcStage1Bmp; i += kThreads) sm.ucs1[i] = ldg(a.tb.uc_stage1 + i);
+            for (int i = tid; i < kUcStage2Words; i += kThreads) sm.ucs2[i] = ldg(a.tb.uc_stage2 + i);
 #endif
+        }
         uint8_t at;
         if (tid < 128) {
-            const uint32_t leaf = ldg(a.tb.uc_stage1);                       // codepoints 0..127 share stage-1 entry 0
-            const uint32_t wv = ldg(a.tb.uc_stage2 + leaf * 8u + (static_cast<uint32_t>(tid) >> 4));
-            at = static_cast<uint8_t>((wv >> ((tid & 15) * 2)) & 3u);
+            at = static_cast<uint8_t>(uc_class([&](uint32_t i) { return static_cast<uint32_t>(ldg(a.tb.uc_stage1 + i)); },
+                                               [&](uint32_t i) { return ldg(a.tb.uc_stage2 + i); }, static_cast<uint32_t>(tid), wide));
             if (tid == 0x0A || tid == 0x0D) at |= A_CRLF;
             if (tid == 0x20) at |= A_SP;
         } else at = tid < 0xC0 ? A_CONT : A_O;
@@ -1137,7 +1277,10 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     else if ((b & 0xF0u) == 0xE0u && avail >= 3) cp = ((b & 0x0Fu) << 12) | ((b1 & 0x3Fu) << 6) | (b2 & 0x3Fu);
                     else if ((b & 0xF8u) == 0xF0u && avail >= 4) cp = ((b & 0x07u) << 18) | ((b1 & 0x3Fu) << 12) | ((b2 & 0x3Fu) << 6) | (b3 & 0x3Fu);
                     uint32_t cls = A_O;
-                    if (cp < 0x10000u) {
+                    if (a.tb.uc_wide) {
+                        cls = uc_class([&](uint32_t k) { return static_cast<uint32_t>(ldg(a.tb.uc_stage1 + k)); }, [&](uint32_t k) { return ldg(a.tb.uc_stage2 + k); }, cp, true);
+                        if (cp_is_cjk(cp)) cls |= A_CJK;
+                    } else if (cp < 0x10000u) {
                         const uint32_t leaf = sm.ucs1[cp >> 7];
                         cls = (sm.ucs2[leaf * 8u + ((cp & 127u) >> 4)] >> ((cp & 15u) * 2u)) & 3u;
                     } else if (cp <= 0x10FFFFu) {
@@ -1145,7 +1288,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                         cls = (ldg(a.tb.uc_stage2 + leaf * 8u + ((cp & 127u) >> 4)) >> ((cp & 15u) * 2u)) & 3u;
                     }
                     sm.attr[i0 + i] = static_cast<uint8_t>(cls | (sm.attr[i0 + i] & A_DOC));
-                    sm.oh[i0 + i] = static_cast<uint8_t>(1u << cls);
+                    sm.oh[i0 + i] = onehot_of(static_cast<uint8_t>(cls & A_CLS));
                 }
                 ow[0] = ohw[0]; ow[1] = ohw[1]; ow[2] = ohw[2]; ow[3] = ohw[3];
             }
@@ -1293,7 +1436,8 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         // harmless to the algebra (the literal has no class, so its neighbours see "nothing").
         const uint64_t Cg = C & ~ADraw;
         // (a stray continuation byte right after an apostrophe is glued to it and pushes the tail letters along)
-        const bool messy = (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 || ((AP << 1) & C) != 0;
+        // (DeepSeek-V3: every codepoint is decided one by one from the attribute bytes)
+        const bool messy = family == 3 || (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 || ((AP << 1) & C) != 0;
         if (messy) unc = LEAD;
         // An apostrophe with a continuation byte within the three bytes after it: what follows is not
         // plain ASCII (U+017F counts as 's'), so this apostrophe and the three bytes after it, where a
@@ -1408,8 +1552,8 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     });
 
     mark(4);
-    // ---- P4: index of each digit in its run (Llama-3 \p{N}{1,3}) ----
-    if (family == 1) {
+    // ---- P4: index of each digit in its run (\p{N}{1,3} of Llama-3 and DeepSeek-V3) ----
+    if (family == 1 || family == 3) {
         const uint32_t* leadw = reinterpret_cast<const uint32_t*>(sm.lead16);
         const uint32_t* nleadw = reinterpret_cast<const uint32_t*>(sm.nlead16);
         const uint32_t* nstartw = reinterpret_cast<const uint32_t*>(sm.nstart16);

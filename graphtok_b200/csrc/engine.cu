@@ -19,6 +19,7 @@
 #include "nfc_host.h"
 #include "tables_build.h"
 #include "unicode_class_table.h"
+#include "unicode_wide_table.h"
 
 namespace gtok {
 
@@ -273,6 +274,10 @@ struct Engine::Impl {
     bool upload_tables(std::string& err) {
         std::vector<uint16_t> s1(gtok_uc_stage1_init, gtok_uc_stage1_init + GTOK_UC_STAGE1_LEN);
         std::vector<uint32_t> s2(gtok_uc_stage2_init, gtok_uc_stage2_init + GTOK_UC_STAGE2_LEN);
+        if (ht.family == 3) {        // DeepSeek-V3 asks for marks, punctuation and symbols too
+            s1.assign(gtok_uw_stage1_init, gtok_uw_stage1_init + GTOK_UW_STAGE1_LEN);
+            s2.assign(gtok_uw_stage2_init, gtok_uw_stage2_init + GTOK_UW_STAGE2_LEN);
+        }
         if (!upload(ht.merge, &dt.merge, owned, err) || !upload(ht.word, &dt.word, owned, err) ||
             !upload(ht.longtab, &dt.longtab, owned, err) || !upload(ht.long_blob, &dt.long_blob, owned, err) ||
             !upload(ht.byte_to_id, &dt.byte_to_id, owned, err) || !upload(s1, &dt.uc_stage1, owned, err) ||

@@ -46,6 +46,7 @@ inline void fill_table_scalars(const HostTables& ht, DeviceTables& tb) {
     tb.lit_n_lens = ht.lit_n_lens;
     for (int i = 0; i < kLitLens; ++i) tb.lit_lens[i] = ht.lit_lens[i];
     tb.family = ht.family;
+    tb.uc_wide = ht.family == 3 ? 1u : 0u;
     tb.ignore_merges = ht.ignore_merges;
     tb.monotone = ht.monotone;
     tb.added_ws = ht.added_ws;

@@ -24,6 +24,16 @@ const char* const kQwen25Pattern =
     "\\p{N}| ?[^\\s\\p{L}\\p{N}]+[\\r\\n]*|\\s*[\\r\\n]+|"
     "\\s+(?!\\S)|\\s+";
 
+// DeepSeek-V3: three Split steps (reference: src/vocab.cc:132-137).  The carriage return and the
+// line feed of the main pattern are the characters themselves, as the JSON file's \r and \n
+// escapes decode.
+const char* const kDeepSeekDigitPattern = "\\p{N}{1,3}";
+const char* const kDeepSeekCjkPattern = "[\xe4\xb8\x80-\xe9\xbe\xa5\xe3\x81\x80-\xe3\x82\x9f\xe3\x82\xa0-\xe3\x83\xbf]+";
+const char* const kDeepSeekMainPattern =
+    "[!\"#$%&'()*+,\\-./:;<=>?@\\[\\\\\\]^_`{|}~][A-Za-z]+|"
+    "[^\r\n\\p{L}\\p{P}\\p{S}]?[\\p{L}\\p{M}]+|"
+    " ?[\\p{P}\\p{S}]+[\r\n]*|\\s*[\r\n]+|\\s+(?!\\S)|\\s+";
+
 struct ByteMaps {
     uint32_t b2u[256];
     int u2b[0x200];
@@ -118,6 +128,7 @@ const char* family_name(Family f) {
         case Family::GPT2: return "GPT2";
         case Family::Llama3: return "Llama3";
         case Family::Qwen25: return "Qwen25";
+        case Family::DeepSeekV3: return "DeepSeekV3";
     }
     return "?";
 }
@@ -168,10 +179,19 @@ bool load_tokenizer_json(const std::string& path, HostVocab& out, std::string& e
                 out.nfc = true;
                 matched = true;
             }
+        } else if (seq && seq->is_array() && seq->arr.size() == 4) {
+            // an empty normalizer Sequence, three Splits, ByteLevel without its own regex (src/vocab.cc:256-262)
+            const Value* items = norm && norm->is_object() && str_is(norm, "type", "Sequence") ? norm->find("normalizers") : nullptr;
+            if (items && items->is_array() && items->arr.empty() && is_split(seq->arr[0], kDeepSeekDigitPattern) &&
+                is_split(seq->arr[1], kDeepSeekCjkPattern) && is_split(seq->arr[2], kDeepSeekMainPattern) &&
+                is_bytelevel(seq->arr[3], true, false)) {
+                out.family = Family::DeepSeekV3;
+                matched = true;
+            }
         }
     }
     if (!matched) {
-        err = "unsupported pre_tokenizer/normalizer pipeline (only the exact GPT-2, Llama-3 and Qwen2.5 shapes load)";
+        err = "unsupported pre_tokenizer/normalizer pipeline (only the exact GPT-2, Llama-3, Qwen2.5 and DeepSeek-V3 shapes load)";
         return false;
     }
     // ---- model options ---------------------------------------------------

@@ -4,7 +4,7 @@
 // Mirrors the acceptance rules of the reference loader
 // (src/vocab.cc:308-618 load_hf_tokenizer_json, :227-306 detect_regex_kind):
 // only byte-level BPE files whose normalizer / pre_tokenizer sections have
-// exactly the GPT-2, Llama-3 or Qwen2.5 shape load; everything else is a
+// exactly the GPT-2, Llama-3, Qwen2.5 or DeepSeek-V3 shape load; everything else is a
 // load failure, never a silent approximation.
 #pragma once
 #include <cstdint>
@@ -13,7 +13,7 @@
 
 namespace gtok {
 
-enum class Family : uint8_t { GPT2 = 0, Llama3 = 1, Qwen25 = 2 };
+enum class Family : uint8_t { GPT2 = 0, Llama3 = 1, Qwen25 = 2, DeepSeekV3 = 3 };
 
 struct MergeRule {
     uint32_t left, right, result;   // token ids; the rule's rank is its index

@@ -258,6 +258,7 @@ struct TextGen {
 std::string special_name(SplitFamily fam, uint32_t i) {
     char buf[64];
     if (fam == gtok_datagen::kSplitQwen25) std::snprintf(buf, sizeof buf, "<|qwen_special_%u|>", i);
+    else if (fam == gtok_datagen::kSplitDeepSeek) std::snprintf(buf, sizeof buf, "<\xef\xbd\x9cspecial\xe2\x96\x81%u\xef\xbd\x9c>", i);   // fullwidth bars, U+2581
     else std::snprintf(buf, sizeof buf, "<|reserved_special_token_%u|>", i);
     return buf;
 }
@@ -470,6 +471,12 @@ const char* kLlamaRegex =
 const char* kQwenRegex =
     "(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\\\r\\\\n\\\\p{L}\\\\p{N}]?\\\\p{L}+|\\\\p{N}| ?[^\\\\s\\\\p{L}\\\\p{N}]+[\\\\r\\\\n]*|\\\\s*[\\\\r\\\\n]+|\\\\s+(?!\\\\S)|\\\\s+";
 
+// The three DeepSeek-V3 patterns as they stand in a tokenizer.json (JSON string escapes applied).
+const char* kDeepSeekDigitRegex = "\\\\p{N}{1,3}";
+const char* kDeepSeekCjkRegex = "[\xe4\xb8\x80-\xe9\xbe\xa5\xe3\x81\x80-\xe3\x82\x9f\xe3\x82\xa0-\xe3\x83\xbf]+";
+const char* kDeepSeekMainRegex =
+    "[!\\\"#$%&'()*+,\\\\-./:;<=>?@\\\\[\\\\\\\\\\\\]^_`{|}~][A-Za-z]+|[^\\r\\n\\\\p{L}\\\\p{P}\\\\p{S}]?[\\\\p{L}\\\\p{M}]+| ?[\\\\p{P}\\\\p{S}]+[\\r\\n]*|\\\\s*[\\r\\n]+|\\\\s+(?!\\\\S)|\\\\s+";
+
 int cmd_train(SplitFamily fam, const std::string& corpus_path, size_t n_merges, uint32_t n_specials, const std::string& out_path) {
     std::string corpus = read_file(corpus_path);
     std::vector<uint32_t> starts;
@@ -502,6 +509,11 @@ int cmd_train(SplitFamily fam, const std::string& corpus_path, size_t n_merges, 
     } else if (fam == gtok_datagen::kSplitLlama3) {
         j += std::string("\"normalizer\":null,\"pre_tokenizer\":{\"type\":\"Sequence\",\"pretokenizers\":[{\"type\":\"Split\",\"pattern\":{\"Regex\":\"") +
              kLlamaRegex + "\"},\"behavior\":\"Isolated\",\"invert\":false},{\"type\":\"ByteLevel\",\"add_prefix_space\":false,\"trim_offsets\":true,\"use_regex\":false}]},";
+    } else if (fam == gtok_datagen::kSplitDeepSeek) {
+        const std::string split_a = "{\"type\":\"Split\",\"pattern\":{\"Regex\":\"", split_b = "\"},\"behavior\":\"Isolated\",\"invert\":false},";
+        j += "\"normalizer\":{\"type\":\"Sequence\",\"normalizers\":[]},\"pre_tokenizer\":{\"type\":\"Sequence\",\"pretokenizers\":[" +
+             split_a + kDeepSeekDigitRegex + split_b + split_a + kDeepSeekCjkRegex + split_b + split_a + kDeepSeekMainRegex + split_b +
+             "{\"type\":\"ByteLevel\",\"add_prefix_space\":false,\"trim_offsets\":true,\"use_regex\":false}]},";
     } else {
         j += std::string("\"normalizer\":{\"type\":\"NFC\"},\"pre_tokenizer\":{\"type\":\"Sequence\",\"pretokenizers\":[{\"type\":\"Split\",\"pattern\":{\"Regex\":\"") +
              kQwenRegex + "\"},\"behavior\":\"Isolated\",\"invert\":false},{\"type\":\"ByteLevel\",\"add_prefix_space\":false,\"trim_offsets\":false,\"use_regex\":false}]},";
@@ -537,6 +549,7 @@ SplitFamily parse_family(const char* s) {
     if (!std::strcmp(s, "gpt2")) return gtok_datagen::kSplitGPT2;
     if (!std::strcmp(s, "llama3")) return gtok_datagen::kSplitLlama3;
     if (!std::strcmp(s, "qwen25")) return gtok_datagen::kSplitQwen25;
+    if (!std::strcmp(s, "deepseek")) return gtok_datagen::kSplitDeepSeek;
     std::fprintf(stderr, "datagen: unknown family %s\n", s);
     std::exit(2);
 }

@@ -9,16 +9,23 @@
 //   Llama-3 : (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}|
 //             ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+
 //   Qwen2.5 : as Llama-3 with \p{N} in place of \p{N}{1,3}
+//   DeepSeek-V3 : three Split steps one after the other, each working on the pieces the one
+//             before left (a piece's ends are the text's ends for the next pattern):
+//             \p{N}{1,3}   then   [一-龥぀-ゟ゠-ヿ]+   then
+//             [!-/:-@\[-`{-~][A-Za-z]+|[^\r\n\p{L}\p{P}\p{S}]?[\p{L}\p{M}]+|
+//              ?[\p{P}\p{S}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+
+//             (matches and the stretches between matches are both pieces)
 #pragma once
 #include <cstdint>
 #include <string>
 #include <vector>
 
 #include "../csrc/unicode_class_table.h"
+#include "../csrc/unicode_wide_table.h"
 
 namespace gtok_datagen {
 
-enum SplitFamily { kSplitGPT2 = 0, kSplitLlama3 = 1, kSplitQwen25 = 2 };
+enum SplitFamily { kSplitGPT2 = 0, kSplitLlama3 = 1, kSplitQwen25 = 2, kSplitDeepSeek = 3 };
 
 struct Decoded {
     std::vector<uint32_t> cp;     // codepoints
@@ -117,11 +124,93 @@ inline size_t match_at(const Decoded& d, size_t i, SplitFamily fam) {
     return 1;   // unreachable for valid input: every codepoint is in one of the classes
 }
 
+// ---- DeepSeek-V3 ----
+// Wide class of a codepoint: 0 \p{L} or \p{M}, 1 \p{N}, 2 \s, 3 other, 6 \p{P} or \p{S}.
+inline int wide_class(uint32_t cp) { return static_cast<int>(gtok_uw_lookup(gtok_uw_stage1_init, gtok_uw_stage2_init, cp)); }
+inline bool ds_cjk(uint32_t cp) { return (cp >= 0x4E00 && cp <= 0x9FA5) || (cp >= 0x3040 && cp <= 0x309F) || (cp >= 0x30A0 && cp <= 0x30FF); }
+
+// Length of the main pattern's match at cursor i of the piece [i, end), 0 when no alternative matches.
+inline size_t ds_main_match(const std::vector<uint32_t>& cp, const std::vector<int>& wc, size_t i, size_t end) {
+    auto K = [&](size_t j) -> int { return j < end ? wc[j] : -1; };
+    auto P = [&](size_t j) -> uint32_t { return j < end ? cp[j] : 0xFFFFFFFFu; };
+    auto letter = [&](size_t j) { uint32_t c = P(j); return (c >= 'a' && c <= 'z') || (c >= 'A' && c <= 'Z'); };
+    auto nl = [&](size_t j) { return P(j) == '\r' || P(j) == '\n'; };
+    // punctuation of the ASCII range, then ASCII letters
+    {
+        uint32_t c = P(i);
+        const bool punct = (c >= '!' && c <= '/') || (c >= ':' && c <= '@') || (c >= '[' && c <= '`') || (c >= '{' && c <= '~');
+        if (punct && letter(i + 1)) { size_t j = i + 1; while (letter(j)) ++j; return j - i; }
+    }
+    // one optional codepoint that is no newline, letter, punctuation or symbol; then letters and marks
+    {
+        size_t j = i;
+        if (K(j) != 0 && K(j) != 6 && !nl(j) && K(j + 1) == 0) ++j;
+        if (K(j) == 0) { while (K(j) == 0) ++j; return j - i; }
+    }
+    // an optional space, punctuation and symbols, then newlines
+    {
+        size_t j = i;
+        if (P(j) == ' ' && K(j + 1) == 6) ++j;
+        if (K(j) == 6) { while (K(j) == 6) ++j; while (nl(j)) ++j; return j - i; }
+    }
+    size_t e = i;
+    while (K(e) == 2) ++e;
+    if (e == i) return 0;
+    size_t last = e;
+    while (last > i && !nl(last - 1)) --last;
+    if (last > i) return last - i;               // \s*[\r\n]+
+    if (e == end) return e - i;                  // \s+(?!\S) at the piece's end
+    if (e - i >= 2) return e - i - 1;            // \s+(?!\S) before a non-space
+    return 1;                                    // \s+
+}
+
+inline void split_deepseek(const Decoded& d, std::vector<uint32_t>& starts) {
+    const size_t n = d.cp.size();
+    std::vector<int> wc(n);
+    for (size_t i = 0; i < n; ++i) wc[i] = wide_class(d.cp[i]);
+    // the third step over one piece
+    auto step3 = [&](size_t x, size_t y) {
+        size_t i = x;
+        bool gap = false;
+        while (i < y) {
+            const size_t m = ds_main_match(d.cp, wc, i, y);
+            if (m) { starts.push_back(d.at[i]); i += m; gap = false; }
+            else { if (!gap) starts.push_back(d.at[i]); gap = true; ++i; }
+        }
+    };
+    // the second step over one piece
+    auto step2 = [&](size_t a, size_t b) {
+        size_t x = a;
+        while (x < b) {
+            size_t y = x;
+            if (ds_cjk(d.cp[x])) { while (y < b && ds_cjk(d.cp[y])) ++y; }
+            else { while (y < b && !ds_cjk(d.cp[y])) ++y; }
+            step3(x, y);
+            x = y;
+        }
+    };
+    size_t a = 0;
+    while (a < n) {
+        if (wc[a] == 1) {
+            size_t b = a;
+            while (b < n && b - a < 3 && wc[b] == 1) ++b;
+            starts.push_back(d.at[a]);           // a number piece; the later patterns match nothing in it
+            a = b;
+        } else {
+            size_t b = a;
+            while (b < n && wc[b] != 1) ++b;
+            step2(a, b);
+            a = b;
+        }
+    }
+}
+
 // Byte offsets at which pre-tokens start (no added-token handling).
 inline void split(const uint8_t* s, size_t n, SplitFamily fam, std::vector<uint32_t>& starts) {
     Decoded d;
     decode_utf8(s, n, d);
     starts.clear();
+    if (fam == kSplitDeepSeek) { split_deepseek(d, starts); return; }
     size_t i = 0;
     while (i < d.cp.size()) {
         starts.push_back(d.at[i]);

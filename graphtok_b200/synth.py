@@ -21,10 +21,12 @@ VOCABS = {
     "cfg0": ("gpt2", 0, 0, 32 << 20, 50000, 0, []),
     "cfg1": ("llama3", 1, 2, 32 << 20, 127744, 256, ["--no-specials"]),
     "cfg3": ("qwen25", 3, 5, 32 << 20, 151387, 22, ["--nfc"]),
+    "cfg5": ("deepseek", 1, 9, 32 << 20, 100000, 16, ["--no-specials"]),
     # small vocabularies for quick tests
     "tiny_gpt2": ("gpt2", 0, 100, 2 << 20, 3000, 0, []),
     "tiny_llama3": ("llama3", 1, 101, 2 << 20, 4000, 8, ["--no-specials"]),
     "tiny_qwen25": ("qwen25", 3, 102, 2 << 20, 4000, 4, ["--nfc"]),
+    "tiny_deepseek": ("deepseek", 1, 103, 2 << 20, 4000, 4, ["--no-specials"]),
 }
 
 # config id -> (vocab name, text config, seed, bytes)
@@ -33,6 +35,7 @@ DOCS = {
     1: ("cfg1", 1, 3, 4500000),
     3: ("cfg3", 3, 6, 8 << 20),
     4: ("cfg1", 4, 7, 32 << 20),
+    5: ("cfg5", 1, 10, 4 << 20),      # beyond the five benchmark configurations: a DeepSeek-V3-shaped vocabulary
 }
 BATCH = ("cfg0", 4, 8192)   # config 2: vocab, seed, documents
 
@@ -72,7 +75,7 @@ def text(config, seed, nbytes, flags=()):
 
 
 def config_doc(config):
-    """(tokenizer.json path, document bytes) for benchmark configuration 0, 1, 3 or 4."""
+    """(tokenizer.json path, document bytes) for benchmark configuration 0, 1, 3 or 4 (5: DeepSeek-V3-shaped)."""
     vocab, tcfg, seed, nbytes = DOCS[config]
     return vocab_path(vocab), text(tcfg, seed, nbytes)
 

@@ -14,6 +14,12 @@
 // (pretok_boundary.h:224-297 GPT-2, :515-671 Llama-3 / Qwen2.5); the local
 // fast paths of the reference are an optimisation and are not restated.
 //
+// DeepSeek-V3 (three Split steps one after the other, src/vocab.cc:132-137 of the reference) has
+// no host encoder in the reference (src/host_encode.cc:951-953 builds one for the other three
+// families only); its restatement here reads the three patterns literally, as a scanner that
+// tries the alternatives in order at each position, and is pinned against Hugging Face
+// `tokenizers` alone.
+//
 // Parity pinning: tests/test_oracle_pin.py checks this file against (a) the
 // reference's own HostEncoder compiled from its sources (oracle/_ref, when
 // present), and (b) golden vectors produced by Hugging Face `tokenizers`
@@ -27,11 +33,12 @@
 #include <vector>
 
 #include "../graphtok_b200/csrc/unicode_class_table.h"
+#include "../graphtok_b200/csrc/unicode_wide_table.h"
 #include "../graphtok_b200/csrc/vocab_host.h"
 
 namespace {
 
-enum : uint8_t { kL = 0, kN = 1, kS = 2, kO = 3, kAdded = 5 };
+enum : uint8_t { kL = 0, kN = 1, kS = 2, kO = 3, kAdded = 5, kP = 6 };   // kP: \p{P} or \p{S}, wide table only
 constexpr uint32_t kNone = 0xFFFFFFFFu;
 
 // Lenient UTF-8 decode, exactly the reference's rule (pretok_boundary.h:43-57):
@@ -203,6 +210,95 @@ struct Oracle {
         return !cont;
     }
 
+    // ------------------------------------------------------------ DeepSeek-V3
+    // Split(\p{N}{1,3}), then Split([一-龥぀-ゟ゠-ヿ]+), then Split(main pattern), each "Isolated":
+    // every match is a piece and so is every stretch between two matches; a later step works on
+    // each piece by itself, so a piece's two ends are the start and the end of the text for it.
+    // cls holds the wide classes here (kL = \p{L} or \p{M}, kP = \p{P} or \p{S}); cpv the codepoints.
+    std::vector<uint32_t> cpv;
+    static bool is_cjk(uint32_t cp) { return (cp >= 0x4E00u && cp <= 0x9FA5u) || (cp >= 0x3040u && cp <= 0x30FFu); }
+    static bool is_ascii_letter(uint32_t cp) { return (cp >= 'a' && cp <= 'z') || (cp >= 'A' && cp <= 'Z'); }
+    static bool is_ascii_punct(uint32_t cp) {
+        return (cp >= 0x21 && cp <= 0x2F) || (cp >= 0x3A && cp <= 0x40) || (cp >= 0x5B && cp <= 0x60) || (cp >= 0x7B && cp <= 0x7E);
+    }
+    // The main pattern over codepoints [x, y): marks the start of every match and of every
+    // stretch no alternative matches.
+    void deepseek_main(uint32_t x, uint32_t y, std::vector<uint8_t>& bnd) const {
+        auto nl = [&](uint32_t j) { return cpv[j] == 0x0D || cpv[j] == 0x0A; };
+        uint32_t i = x;
+        bool in_gap = false;
+        while (i < y) {
+            uint32_t end = 0;      // end of the match starting at i, 0 = none
+            const uint8_t c = cls[i];
+            // [!-/:-@\[-`{-~][A-Za-z]+
+            if (is_ascii_punct(cpv[i]) && i + 1 < y && is_ascii_letter(cpv[i + 1])) {
+                end = i + 2;
+                while (end < y && is_ascii_letter(cpv[end])) ++end;
+            }
+            // [^\r\n\p{L}\p{P}\p{S}]?[\p{L}\p{M}]+
+            if (!end) {
+                uint32_t k = i;
+                if (c != kL && c != kP && !nl(i) && i + 1 < y && cls[i + 1] == kL) k = i + 1;
+                if (cls[k] == kL) { end = k + 1; while (end < y && cls[end] == kL) ++end; }
+            }
+            //  ?[\p{P}\p{S}]+[\r\n]*
+            if (!end) {
+                uint32_t k = i;
+                if (cpv[i] == 0x20 && i + 1 < y && cls[i + 1] == kP) k = i + 1;
+                if (cls[k] == kP) {
+                    end = k + 1;
+                    while (end < y && cls[end] == kP) ++end;
+                    while (end < y && nl(end)) ++end;
+                }
+            }
+            if (!end && c == kS) {
+                uint32_t j = i;
+                while (j < y && cls[j] == kS) ++j;
+                // \s*[\r\n]+ : through the last newline of the run
+                for (uint32_t l = j; l > i; --l) if (nl(l - 1)) { end = l; break; }
+                // \s+(?!\S) : the whole run at the end of the piece, else all but its last codepoint
+                if (!end) { if (j == y) end = j; else if (j - i >= 2) end = j - 1; }
+                // \s+
+                if (!end) end = j;
+            }
+            if (end) { bnd[i] = 1; i = end; in_gap = false; }
+            else { if (!in_gap) bnd[i] = 1; in_gap = true; ++i; }
+        }
+    }
+    void deepseek_bounds(std::vector<uint8_t>& bnd) const {
+        bnd.assign(n, 0);
+        uint32_t s = 0;
+        while (s < n) {
+            if (cls[s] == kAdded) { bnd[s] = 1; ++s; continue; }
+            uint32_t e = s;
+            while (e < n && cls[e] != kAdded) ++e;
+            // step 1 over [s, e): runs of \p{N} in threes, the stretches between them go on
+            uint32_t a = s;
+            while (a < e) {
+                if (cls[a] == kN) {
+                    uint32_t b = a;
+                    while (b < e && cls[b] == kN) ++b;
+                    for (uint32_t j = a; j < b; j += 3) bnd[j] = 1;
+                    a = b;
+                    continue;
+                }
+                uint32_t b = a;
+                while (b < e && cls[b] != kN) ++b;
+                // step 2 over [a, b): runs inside and outside the three ranges
+                uint32_t x = a;
+                while (x < b) {
+                    const bool cj = is_cjk(cpv[x]);
+                    uint32_t y = x;
+                    while (y < b && is_cjk(cpv[y]) == cj) ++y;
+                    deepseek_main(x, y, bnd);     // step 3 (x itself is marked: a match or a gap starts there)
+                    x = y;
+                }
+                a = b;
+            }
+            s = e;
+        }
+    }
+
     // ------------------------------------------------------------------- BPE
     bool rule(uint32_t l, uint32_t r, uint32_t& rank, uint32_t& res) const {
         auto it = rules.find((static_cast<uint64_t>(l) << 32) | r);
@@ -290,7 +386,9 @@ struct Oracle {
         if (len == 0) return;
         cls.resize(len); b0.resize(len); pos.resize(len); direct.resize(len);
         n = 0;
-        const bool fold = hv.family != gtok::Family::GPT2;   // U+017F counts as 's' under (?i:)
+        const bool deepseek = hv.family == gtok::Family::DeepSeekV3;
+        if (deepseek) cpv.resize(len);
+        const bool fold = hv.family == gtok::Family::Llama3 || hv.family == gtok::Family::Qwen25;   // U+017F counts as 's' under (?i:)
         size_t i = 0;
         while (i < len) {
             uint8_t b = text[i];
@@ -300,7 +398,10 @@ struct Oracle {
             }
             if ((b & 0xC0u) == 0x80u) { ++i; continue; }   // starts no codepoint
             uint32_t cp = decode_lenient(text + i, len - i);
-            cls[n] = static_cast<uint8_t>(gtok_uc_lookup(gtok_uc_stage1_init, gtok_uc_stage2_init, cp));
+            if (deepseek) {
+                cls[n] = static_cast<uint8_t>(gtok_uw_lookup(gtok_uw_stage1_init, gtok_uw_stage2_init, cp));
+                cpv[n] = cp;
+            } else cls[n] = static_cast<uint8_t>(gtok_uc_lookup(gtok_uc_stage1_init, gtok_uc_stage2_init, cp));
             bool long_s = fold && b == 0xC5 && i + 1 < len && text[i + 1] == 0xBF;
             b0[n] = long_s ? static_cast<uint8_t>('s') : b;
             pos[n] = static_cast<uint32_t>(i);
@@ -315,11 +416,14 @@ struct Oracle {
                 do { drun[c] = s; ++c; } while (c < n && cls[c] == kN);
             }
         }
+        std::vector<uint8_t> ds_bnd;
+        if (deepseek) deepseek_bounds(ds_bnd);
         uint32_t start = 0;
         for (uint32_t c = 1; c <= n; ++c) {
             if (c < n) {
                 bool bnd;
                 switch (hv.family) {
+                    case gtok::Family::DeepSeekV3: bnd = ds_bnd[c] != 0; break;
                     case gtok::Family::GPT2: bnd = gpt2_boundary(static_cast<int>(c)); break;
                     case gtok::Family::Llama3: bnd = llamaqwen_boundary<true>(static_cast<int>(c)); break;
                     default: bnd = llamaqwen_boundary<false>(static_cast<int>(c)); break;
@@ -366,7 +470,7 @@ void* gtok_oracle_create(const char* tokenizer_json, char* err, uint32_t err_cap
 
 void gtok_oracle_destroy(void* h) { delete static_cast<Oracle*>(h); }
 
-// 0 GPT-2, 1 Llama-3, 2 Qwen2.5; bit 8 set when the vocabulary asks for NFC.
+// 0 GPT-2, 1 Llama-3, 2 Qwen2.5, 3 DeepSeek-V3; bit 8 set when the vocabulary asks for NFC.
 uint32_t gtok_oracle_family(void* h) {
     Oracle* o = static_cast<Oracle*>(h);
     return static_cast<uint32_t>(o->hv.family) | (o->hv.nfc ? 0x100u : 0u);

@@ -11,6 +11,9 @@ POOLS = {
     "space": list("a \n\r.") + [" ", " ", "　", "\t"],
     "digit": list("0123456789 a.") + ["٣", "५"],
     "apos": list("'stdmlrve ") + ["ſ", "'"],
+    # punctuation and symbols, marks, the CJK ranges and codepoints of no class: what the DeepSeek-V3 patterns tell apart
+    "wide": list("ab Z!.-$_ \n\r\t") + ["é", "\u0301", "中", "文", "の", "カ", "・", "゛", "\x00", "\x01", "\u200b", "…", "«", "€", "1", "12", "٣",
+                                       "\u00a0", "!a", " !", "a.b", "ａ"],
 }
 
 

@@ -18,6 +18,7 @@
 #include "../../graphtok_b200/csrc/shard_plan.h"
 #include "../../graphtok_b200/csrc/tables_build.h"
 #include "../../graphtok_b200/csrc/unicode_class_table.h"
+#include "../../graphtok_b200/csrc/unicode_wide_table.h"
 #include "../../graphtok_b200/csrc/vocab_host.h"
 
 namespace {
@@ -85,6 +86,10 @@ void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
     }
     e->s1.assign(gtok_uc_stage1_init, gtok_uc_stage1_init + GTOK_UC_STAGE1_LEN);
     e->s2.assign(gtok_uc_stage2_init, gtok_uc_stage2_init + GTOK_UC_STAGE2_LEN);
+    if (e->ht.family == 3) {
+        e->s1.assign(gtok_uw_stage1_init, gtok_uw_stage1_init + GTOK_UW_STAGE1_LEN);
+        e->s2.assign(gtok_uw_stage2_init, gtok_uw_stage2_init + GTOK_UW_STAGE2_LEN);
+    }
     gtok::DeviceTables& tb = e->tb;
     const gtok::HostTables& ht = e->ht;
     tb.merge = ht.merge.data();

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Regenerates the golden vectors in this directory.
 
-Vocabularies: tiny_{gpt2,llama3,qwen25}.json, written by the in-tree generator
+Vocabularies: tiny_{gpt2,llama3,qwen25,deepseek}.json, written by the in-tree generator
 (graphtok_b200.synth.vocab_path("tiny_*"): seeded corpus + greedy BPE trainer) and
 committed here because the expected ids are only meaningful for these exact files.
 
@@ -53,6 +53,20 @@ def cases(family, special):
     for pool in pools:
         for _ in range(120):
             c.append("".join(rng.choice(pool) for _ in range(rng.randint(1, 48))))
+    if family == "deepseek":
+        # the first alternative (a punctuation mark taking ASCII letters along) and what stops it; the three CJK
+        # ranges; marks; codepoints of no class; whitespace against the ends of pieces
+        c += ["!abc", "a.b.c", " !abc", "!!ab", "a!b!c", "!ab\u00e9", "!ab\u00e9cd", ".ab1cd", "x$yz", "\t!a", "\n!a", "!a\n", "_a_b", "a\u0301!b",
+              "\u4e2d\u6587abc\u4e2d\u6587", "\u4e2d\u6587 abc", "abc \u4e2d", "\u3042\u30a2\u4e00", "\u30fb\u30fc\u309b\u3099", "\u4e001\u4e00", "\u9fa5\u9fa6", "\u303f\u3040\u30ff\u3100",
+              "\u0301", "\u0301a", "a\u0301\u0302b", " \u0301", "\u0301 \u0301",
+              "\x00", "\x00\x01", "\x00a", "\x00\x01a", "a\x00b", "\x00 ", " \x00", "\u200b\u200bx", "!\x00", "\x00!", "\x00\n",
+              "a  1", "a 1", "  1", "1  a", "1 a", "12  ", "  \u4e2d", " \u4e2d", "\u4e2d  a", "a\n 1", "a \n1", "!\n\n 1", "!\n \n x", "a\n \n x", " \n \n", "\n \n  ",
+              "1234567", "12a345", "\u0663\u0664\u0665\u0666", "1\u00b22", "3.14159", "1,000,000", "\u2460\u2461\u2462\u2463",
+              " \u00a0a", "\u00a0 a", "\u3000a", "a\u2028b", "\u0085a", "\x1ca", "\x0bx \x0c y"]
+        rng2 = random.Random(20260102)
+        pool = list("ab Z!.-$_ \n\r\t") + ["\u00e9", "\u0301", "\u4e2d", "\u6587", "\u306e", "\u30ab", "\u30fb", "\u309b", "\x00", "\x01", "\u200b", "\u2026", "\u00ab", "\u20ac", "1", "12", "\u0663", "\u00a0"]
+        for _ in range(400):
+            c.append("".join(rng2.choice(pool) for _ in range(rng2.randint(1, 40))))
     if family == "qwen25":
         c += ["e\u0301", "a\u0308o\u0308u\u0308", "\u0041\u030a", "\u212b", "\u1e9b\u0323", "q\u0307\u0323", "\uac00", "\u1100\u1161\u11a8",
               "\u0958", "\u0b47\u0b56", "x\u0301\u0301\u0301", "\u0301a", "caf\u0065\u0301 na\u0069\u0308ve", "\ufb01 \u00bd \u2126",
@@ -66,7 +80,8 @@ def cases(family, special):
 
 
 def main():
-    for family, special in (("gpt2", None), ("llama3", "<|reserved_special_token_3|>"), ("qwen25", "<|qwen_special_1|>")):
+    for family, special in (("gpt2", None), ("llama3", "<|reserved_special_token_3|>"), ("qwen25", "<|qwen_special_1|>"),
+                            ("deepseek", "<\uff5cspecial\u25811\uff5c>")):
         vocab = os.path.join(HERE, "tiny_%s.json" % family)
         tok = Tokenizer.from_file(vocab)
         rows = []

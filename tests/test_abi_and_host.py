@@ -69,7 +69,7 @@ def _loads(path):
         return False
 
 
-def test_loader_accepts_the_three_shapes_only(built):
+def test_loader_accepts_the_known_shapes_only(built):
     for f in FAMILIES:
         assert _loads(tiny_vocab(f))
     bad = [
@@ -87,6 +87,15 @@ def test_loader_accepts_the_three_shapes_only(built):
         ("llama3", lambda j: j["added_tokens"][0].__setitem__("lstrip", True)),
         ("llama3", lambda j: j["added_tokens"].append({"id": 999999, "content": "a<b", "special": True})),
         ("gpt2", lambda j: j["model"].__setitem__("type", "Unigram")),
+        # DeepSeek-V3: an empty normalizer Sequence, the three exact Split patterns in their order, ByteLevel without its regex
+        ("deepseek", lambda j: j.__setitem__("normalizer", None)),
+        ("deepseek", lambda j: j["normalizer"]["normalizers"].append({"type": "NFC"})),
+        ("deepseek", lambda j: j["pre_tokenizer"]["pretokenizers"].pop(1)),
+        ("deepseek", lambda j: j["pre_tokenizer"]["pretokenizers"][0]["pattern"].__setitem__("Regex", "\\p{N}")),
+        ("deepseek", lambda j: j["pre_tokenizer"]["pretokenizers"][2]["pattern"].__setitem__("Regex", j["pre_tokenizer"]["pretokenizers"][2]["pattern"]["Regex"].replace("[A-Za-z]+", "[a-z]+"))),
+        ("deepseek", lambda j: j["pre_tokenizer"]["pretokenizers"][2].__setitem__("behavior", "Removed")),
+        ("deepseek", lambda j: j["pre_tokenizer"]["pretokenizers"][3].__setitem__("use_regex", True)),
+        ("deepseek", lambda j: j["model"].__setitem__("ignore_merges", True)),
     ]
     for fam, fn in bad:
         p = _mutate(fam, fn)

@@ -269,9 +269,9 @@ def test_dispatcher_threads(built, oracles, policy):
     assert s["gpu_batches"] < s["gpu_requests"]         # sixteen threads against one batcher must share replays
 
 
-@pytest.mark.parametrize("config", (0, 1, 3))
+@pytest.mark.parametrize("config", (0, 1, 3, 5))
 def test_benchmark_configurations_full_size(built, config):
-    """Configurations 0, 1 and 3 at their full sizes against the oracle."""
+    """Configurations 0, 1 and 3 at their full sizes against the oracle (5: the DeepSeek-V3-shaped vocabulary on 4 MiB)."""
     from graphtok_b200 import GTok, synth
     path, doc = synth.config_doc(config)
     o = oracle_lib.Oracle(path)

@@ -28,6 +28,8 @@ def test_oracle_matches_golden(oracles, family):
 
 @pytest.mark.parametrize("family", FAMILIES)
 def test_oracle_matches_reference_build(oracles, family):
+    if family == "deepseek":
+        pytest.skip("the reference has no host encoder for DeepSeek-V3 (src/host_encode.cc:951-953); Hugging Face is its pin")
     try:
         ref = oracle_lib.Reference(tiny_vocab(family))
     except FileNotFoundError:
@@ -98,3 +100,53 @@ int main() {
         subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ref_dir, "generated"), "-I", oracle_lib.CSRC, "-o", exe, cc], check=True)
         r = subprocess.run([exe], capture_output=True, text=True)
         assert r.returncode == 0 and "differences=0" in r.stdout, r.stdout
+
+
+def test_wide_class_table_equals_the_references_bits(built):
+    """The wide class of every codepoint (csrc/unicode_wide_table.h: letters and marks, numbers, whitespace,
+    punctuation and symbols, other) against the reference's property bits (generated/gbpe_class_table.h:866-871,
+    gbpe_class_bits), which must be mutually exclusive apart from nothing at all: the DeepSeek-V3 predicate
+    rests on it."""
+    ref_dir = oracle_lib.reference_dir()
+    if not ref_dir or not os.path.exists(os.path.join(ref_dir, "generated", "gbpe_class_table.h")):
+        pytest.skip("the reference tree is not on this machine")
+    src = r'''
+#include "gbpe_class_table.h"
+#include "unicode_wide_table.h"
+#include <cstdio>
+int main() {
+    long bad = 0;
+    for (uint32_t cp = 0; cp < 0x200000; ++cp) {
+        const uint32_t bits = cp <= 0x10FFFF ? gbpe_class_bits(cp) : 0u;
+        int groups = 0;
+        uint32_t want = 3;
+        if (bits & (GBPE_WB_L | GBPE_WB_M)) { want = 0; ++groups; }
+        if (bits & GBPE_WB_N) { want = 1; ++groups; }
+        if (bits & GBPE_WB_WS) { want = 2; ++groups; }
+        if (bits & (GBPE_WB_P | GBPE_WB_SY)) { want = 6; ++groups; }
+        const uint32_t got = gtok_uw_lookup(gtok_uw_stage1_init, gtok_uw_stage2_init, cp);
+        if ((groups > 1 || want != got) && bad++ < 10) std::printf("U+%X: reference bits %02x, here %u\\n", cp, bits, got);
+    }
+    std::printf("differences=%ld\\n", bad);
+    return bad ? 1 : 0;
+}
+'''
+    with tempfile.TemporaryDirectory() as d:
+        cc, exe = os.path.join(d, "cmp.cc"), os.path.join(d, "cmp")
+        with open(cc, "w") as f:
+            f.write(src)
+        subprocess.run(["g++", "-std=c++17", "-O1", "-DGBPE_HAVE_VOCAB_DEEPSEEK_V3=1", "-I", os.path.join(ref_dir, "generated"), "-I", oracle_lib.CSRC, "-o", exe, cc], check=True)
+        r = subprocess.run([exe], capture_output=True, text=True)
+        assert r.returncode == 0 and "differences=0" in r.stdout, r.stdout
+
+
+def test_deepseek_oracle_against_tokenizers_live(oracles):
+    """DeepSeek-V3 has no CPU encoder in the reference, so the oracle's reading of its three patterns is
+    checked against Hugging Face `tokenizers` itself (the reference's own test oracle) on a seeded fuzz,
+    beyond the committed golden vectors."""
+    tokenizers = pytest.importorskip("tokenizers")
+    hf = tokenizers.Tokenizer.from_file(tiny_vocab("deepseek"))
+    o = oracles["deepseek"]
+    texts = cases.fuzz_strings(21, SPECIAL["deepseek"], per_pool=400, lengths=(1, 2, 3, 5, 8, 13, 40, 120))
+    for t in texts:
+        assert o.encode(t.encode()).tolist() == hf.encode(t, add_special_tokens=False).ids, repr(t[:60])

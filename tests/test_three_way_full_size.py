@@ -24,14 +24,15 @@ def _ref(path):
     return oracle_lib.Reference(path) if oracle_lib.build_ref() else None
 
 
-@pytest.mark.parametrize("config", (0, 1, 3))
+@pytest.mark.parametrize("config", (0, 1, 3, 5))
 def test_single_document_configurations(built, config):
+    """(5 is the DeepSeek-V3-shaped vocabulary, for which the reference has no host encoder: two-way.)"""
     from graphtok_b200 import synth
     path, doc = synth.config_doc(config)
     o = oracle_lib.Oracle(path)
     want = o.encode(doc)                                   # normalises first where the vocabulary declares NFC
     assert np.array_equal(_hf_ids(_hf(path), doc), want)   # Hugging Face normalises by itself
-    ref = _ref(path)
+    ref = _ref(path) if config != 5 else None
     if ref is not None:
         assert np.array_equal(ref.encode_normalized(oracle_lib.nfc(doc) if o.needs_nfc else doc), want)
 
