@@ -490,6 +490,34 @@ struct PretokSmem {
     unsigned long long clk_last;
 };
 
+// With the wide class table (DeepSeek-V3) the block's copy of the narrow table is not used, and its
+// room holds four more planes: punctuation and symbols, ASCII letters, ASCII punctuation, and the lead
+// bytes of codepoints inside the three CJK ranges.
+enum { XP_PS = 0, XP_AL, XP_APU, XP_CJK, kXPlanes };
+constexpr int kXPlaneStride = kPWin / 16 + 8;
+static_assert(kXPlanes * kXPlaneStride * 2 <= kUcStage2Words * 4, "the extra planes fit the class-table copy");
+GTOK_DEV uint16_t* xplane(PretokSmem& sm, int k) { return reinterpret_cast<uint16_t*>(sm.ucs2) + k * kXPlaneStride; }
+GTOK_DEV const uint16_t* xplane(const PretokSmem& sm, int k) { return reinterpret_cast<const uint16_t*>(sm.ucs2) + k * kXPlaneStride; }
+// Their entries of chunk c from its attribute bytes and its text.
+GTOK_DEV void chunk_xplanes(PretokSmem& sm, int c, const uint32_t* aw, const uint32_t* tw) {
+    uint32_t ps = 0, al = 0, asc = 0, cjk = 0;
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t x = (aw[j] & 0x07070707u) ^ (A_P * 0x01010101u);            // a zero byte: class A_P
+        const uint32_t zp = ~(((x & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | x) & 0x80808080u;
+        ps |= gather_bit4(zp, 7) << (4 * j);
+        cjk |= gather_bit4(aw[j], 6) << (4 * j);
+        const uint32_t t = tw[j];
+        const uint32_t lo7 = (t | 0x20202020u) & 0x7F7F7F7Fu;                       // letters folded to lower case
+        const uint32_t ge_a = lo7 + (0x80u - 'a') * 0x01010101u, gt_z = lo7 + (0x80u - 'z' - 1u) * 0x01010101u;
+        al |= gather_bit4(ge_a & ~gt_z & ~t, 7) << (4 * j);
+        asc |= gather_bit4(~t, 7) << (4 * j);
+    }
+    xplane(sm, XP_PS)[c] = static_cast<uint16_t>(ps);
+    xplane(sm, XP_AL)[c] = static_cast<uint16_t>(al);
+    xplane(sm, XP_APU)[c] = static_cast<uint16_t>(ps & asc);
+    xplane(sm, XP_CJK)[c] = static_cast<uint16_t>(cjk);
+}
+
 // The nine plane entries of 16-byte chunk c from its one-hot bytes and its text.
 GTOK_DEV void chunk_planes(PretokSmem& sm, int c, const uint32_t* ow, const uint32_t* tw) {
     for (int k = 0; k < 8; ++k)
@@ -1199,6 +1227,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                 uint32_t* ohw = reinterpret_cast<uint32_t*>(sm.oh + i0);
                 for (int k = 0; k < 4; ++k) { txw[k] = 0; atw[k] = A_OUT * 0x01010101u; ohw[k] = 0; }
                 for (int k = 0; k < kPlanes; ++k) sm.plane[k][c] = 0;
+                if (a.tb.uc_wide) for (int k = 0; k < kXPlanes; ++k) xplane(sm, k)[c] = 0;
                 sm.cand16[c] = 0;
                 continue;
             }
@@ -1291,8 +1320,10 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     sm.oh[i0 + i] = onehot_of(static_cast<uint8_t>(cls & A_CLS));
                 }
                 ow[0] = ohw[0]; ow[1] = ohw[1]; ow[2] = ohw[2]; ow[3] = ohw[3];
+                aw[0] = atw[0]; aw[1] = atw[1]; aw[2] = atw[2]; aw[3] = atw[3];
             }
             chunk_planes(sm, c, ow, tw);
+            if (a.tb.uc_wide) chunk_xplanes(sm, c, aw, tw);
             sm.cand16[c] = static_cast<uint16_t>(cand);
         }
     });
@@ -1384,6 +1415,11 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     const uint32_t* twp = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
                     const uint32_t ow[4] = {owp[0], owp[1], owp[2], owp[3]}, tw[4] = {twp[0], twp[1], twp[2], twp[3]};
                     chunk_planes(sm, c, ow, tw);
+                    if (a.tb.uc_wide) {
+                        const uint32_t* awp = reinterpret_cast<const uint32_t*>(sm.attr + c * 16);
+                        const uint32_t aw[4] = {awp[0], awp[1], awp[2], awp[3]};
+                        chunk_xplanes(sm, c, aw, tw);
+                    }
                 }
             });
         }
@@ -1434,90 +1470,139 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         // (a continuation byte right after an apostrophe stretches a contraction past three bytes)
         // An added-token literal is its start bit plus continuation bits; those long stretches are
         // harmless to the algebra (the literal has no class, so its neighbours see "nothing").
-        const uint64_t Cg = C & ~ADraw;
-        // (a stray continuation byte right after an apostrophe is glued to it and pushes the tail letters along)
-        // (DeepSeek-V3: every codepoint is decided one by one from the attribute bytes)
-        const bool messy = family == 3 || (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 || ((AP << 1) & C) != 0;
-        if (messy) unc = LEAD;
-        // An apostrophe with a continuation byte within the three bytes after it: what follows is not
-        // plain ASCII (U+017F counts as 's'), so this apostrophe and the three bytes after it, where a
-        // contraction and the letter after it would lie, are decided one by one; the word's other
-        // apostrophes stay with the algebra.
-        const uint64_t apC = AP & ((C >> 1) | (C >> 2) | (C >> 3));
-        // Contractions: 's 't 'm 'd (tail 1) and 're 've 'll (tail 2), when the regex cursor can be
-        // at the apostrophe (anything but punctuation or a literal space before it).  The few
-        // apostrophes of a word are looked at one by one; what follows them is ASCII or the case
-        // goes to the one-by-one path.
-        uint64_t cs1 = 0, cs2 = 0;
-        if (!messy && AP) {
-            const bool ci = family != 0;
-            uint64_t aps = AP & LEAD & ~(pO | pSP) & ~apC;
-            while (aps) {
-#if defined(__CUDA_ARCH__)
-                const int bit = __ffsll(static_cast<long long>(aps)) - 1;
-#else
-                const int bit = __builtin_ctzll(aps);
-#endif
-                aps &= aps - 1;
-                const uint64_t m = 1ull << bit;
-                if (bit > 59) { unc |= m; continue; }                   // tail would leave the window
-                const int i = ww * 32 + bit - 16;
-                uint32_t x = sm.txt[i + 1], y = sm.txt[i + 2];
-                if (x >= 0x80u || ((DOC >> (bit + 1)) & 3u)) { unc |= (m | (m << 1) | (m << 2) | (m << 3) | (m << 4)) & LEAD; continue; }
-                if (ci) { if (x >= 'A' && x <= 'Z') x += 32; if (y >= 'A' && y <= 'Z') y += 32; }
-                // the second letter must be a letter of this document too (an added-token literal is not)
-                const bool y_ok = ((L >> (bit + 2)) & 1u) != 0;
-                if (!((L >> (bit + 1)) & 1u)) continue;
-                if ((x == 'r' || x == 'v') && y == 'e' && y_ok) cs2 |= m;
-                else if (x == 'l' && y == 'l' && y_ok) cs2 |= m;
-                else if (x == 's' || x == 't' || x == 'm' || x == 'd') cs1 |= m;
-            }
-        }
-        {
-            const uint64_t x = messy ? AP : apC;
-            unc |= (x | (x << 1) | (x << 2) | (x << 3)) & LEAD;
-        }
-        bnd |= AD | (DOC & C) | pNone;
-        if (family == 0) {
-            const uint64_t nNonS = nextcp(L | N | O);
-            bnd |= S & (~pS | nNonS);
-            const uint64_t rest = (L | N | O) & ~pSP;          // a literal space before leads the token
-            bnd |= rest & ((L & ~pL) | (N & ~pN) | (O & ~pO));
-        } else {
-            const uint64_t nNonS = nextcp(L | N | O);
+        if (family == 3) {
+            // DeepSeek-V3 (see is_boundary_deepseek for the rules; here the same over whole planes).
+            auto xload = [&](int k) -> uint64_t {
+                const uint32_t* pw = reinterpret_cast<const uint32_t*>(xplane(sm, k));
+                return (static_cast<uint64_t>(pw[ww - 1]) >> 16) | (static_cast<uint64_t>(pw[ww]) << 16) | (static_cast<uint64_t>(pw[ww + 1]) << 48);
+            };
+            const uint64_t PS = xload(XP_PS), AL = xload(XP_AL), APU = xload(XP_APU), CJ = xload(XP_CJK);
+            const uint64_t Op = O & ~PS;                        // the O plane holds punctuation and symbols too
+            const uint64_t Cg = C & ~ADraw;
+            const bool messy = (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0;
+            const uint64_t pPS = prevcp(PS), pOp = prevcp(Op), pCJ = prevcp(CJ), pAL = prevcp(AL), pAPU = prevcp(APU);
+            // ends of the pieces the first two patterns leave: numbers, and changes into or out of the CJK ranges
+            const uint64_t up = pNone | N | pN | ((CJ ^ pCJ) & LEAD);
+            const uint64_t in = LEAD & ~up;                     // the codepoint before is in this one's piece
+            bnd |= AD | (DOC & C) | pNone | (N & ~pN) | (~N & pN & LEAD) | ((CJ ^ pCJ) & LEAD & ~N);
+            pend = N & pN;
+            const uint64_t nIn = nextcp(in);                    // the codepoint after is in this one's piece
+            const uint64_t nL = nextcp(L & in), nNonS = nextcp((L | PS | Op) & in);
+            (void)nIn;
+            // a punctuation mark that takes the ASCII letters after it along: not inside or behind other punctuation
+            const uint64_t blocked = (pPS | pSP) & in;
+            const uint64_t takes = L & AL & in & pAPU & ~prevcp(blocked);
+            bnd |= L & in & ((pS & pCR) | (pPS & ~takes));
+            // ASCII letters that such a mark took along end where another kind of letter follows: one by one
+            unc |= L & in & pL & pAL & ~AL;
+            bnd |= PS & in & ~(pPS | pSP);
             const uint64_t Scr = S & CR, Spl = S & ~CR;
-            bnd |= Scr & (pL | pN);
-            bnd |= Spl & ~pS;
-            bnd |= Spl & pS & ~pCR & nNonS;
-            // Plain whitespace right after a newline: it opens the rest of the run when the newline
-            // stretch before it hangs off a punctuation token, or when no later newline in the run
-            // pulls it into \s*[\r\n]+.  Both are floods along a stretch of bits (carry of an
-            // addition); a stretch that leaves the window is decided one by one instead.
-            const uint64_t cand = Spl & pS & pCR;
+            bnd |= Scr & in & (pL | pOp);
+            bnd |= Spl & in & ~pS;
+            bnd |= Spl & in & pS & ~pCR & nNonS;
+            const uint64_t cand = Spl & in & pS & pCR;
             if (cand) {
-                const uint64_t Mcr = CR & ~DOC;                              // newline bytes, stretches cut at document starts
-                const uint64_t rs = CR & (~(CR << 1) | DOC);                 // first byte of each stretch
-                const uint64_t absorbed = ((Mcr + (rs & pO & Mcr)) ^ Mcr) & Mcr;
-                const uint64_t from_edge = (Mcr & 1ull) ? (((Mcr + 1ull) ^ Mcr) & Mcr) : 0ull;   // stretch whose start is not visible
+                const uint64_t Mcr = CR & ~DOC;
+                const uint64_t rs = CR & (~(CR << 1) | DOC);
+                const uint64_t absorbed = ((Mcr + (rs & pPS & in & Mcr)) ^ Mcr) & Mcr;
+                const uint64_t from_edge = (Mcr & 1ull) ? (((Mcr + 1ull) ^ Mcr) & Mcr) : 0ull;
                 const uint64_t SplF = fill(Spl) & ~DOC;
-                const uint64_t top_nl = SplF & ((CR & ~DOC) >> 1);           // whitespace byte directly before a newline
+                const uint64_t top_nl = SplF & ((CR & ~DOC) >> 1);
                 const uint64_t rM = brev64(SplF), rT = brev64(top_nl);
-                const uint64_t later_nl = brev64(((rM + rT) ^ rM) & rM);     // whitespace stretches that end in a newline
-                const uint64_t to_edge = (rM & 1ull) ? brev64(((rM + 1ull) ^ rM) & rM) : 0ull;  // stretch that reaches the window's end
+                const uint64_t later_nl = brev64(((rM + rT) ^ rM) & rM);
+                const uint64_t to_edge = (rM & 1ull) ? brev64(((rM + 1ull) ^ rM) & rM) : 0ull;
                 const uint64_t unknown = cand & ((from_edge << 1) | to_edge);
                 bnd |= cand & ~unknown & ((absorbed << 1) | ~later_nl);
                 unc |= unknown;
             }
-            const uint64_t ppOorSP = prevcp(pO | pSP);         // prev-prev is punctuation or a literal space
-            bnd |= L & ((pS & pCR) | (pO & ppOorSP) | pN);
-            if (family == 2) bnd |= N;
-            else { bnd |= N & ~pN; pend = N & pN; }
-            bnd |= O & ~pO & ~pSP;
-        }
-        {
-            const uint64_t in_tail = ((cs1 | cs2) << 1) | (cs2 << 2);
-            const uint64_t after_tail = (cs1 << 2) | (cs2 << 3);
-            bnd = (bnd & ~in_tail) | cs1 | cs2 | (after_tail & L & pL);
+            bnd |= Op & in & (~pOp | nL);
+            if (messy) unc = LEAD;
+        } else {
+            const uint64_t Cg = C & ~ADraw;
+            // (a stray continuation byte right after an apostrophe is glued to it and pushes the tail letters along)
+            // (DeepSeek-V3: every codepoint is decided one by one from the attribute bytes)
+            const bool messy = (Cg & (Cg << 1) & (Cg << 2) & (Cg << 3)) != 0 || (DOC & C) != 0 || ((AP << 1) & C) != 0;
+            if (messy) unc = LEAD;
+            // An apostrophe with a continuation byte within the three bytes after it: what follows is not
+            // plain ASCII (U+017F counts as 's'), so this apostrophe and the three bytes after it, where a
+            // contraction and the letter after it would lie, are decided one by one; the word's other
+            // apostrophes stay with the algebra.
+            const uint64_t apC = AP & ((C >> 1) | (C >> 2) | (C >> 3));
+            // Contractions: 's 't 'm 'd (tail 1) and 're 've 'll (tail 2), when the regex cursor can be
+            // at the apostrophe (anything but punctuation or a literal space before it).  The few
+            // apostrophes of a word are looked at one by one; what follows them is ASCII or the case
+            // goes to the one-by-one path.
+            uint64_t cs1 = 0, cs2 = 0;
+            if (!messy && AP) {
+                const bool ci = family != 0;
+                uint64_t aps = AP & LEAD & ~(pO | pSP) & ~apC;
+                while (aps) {
+    #if defined(__CUDA_ARCH__)
+                    const int bit = __ffsll(static_cast<long long>(aps)) - 1;
+    #else
+                    const int bit = __builtin_ctzll(aps);
+    #endif
+                    aps &= aps - 1;
+                    const uint64_t m = 1ull << bit;
+                    if (bit > 59) { unc |= m; continue; }                   // tail would leave the window
+                    const int i = ww * 32 + bit - 16;
+                    uint32_t x = sm.txt[i + 1], y = sm.txt[i + 2];
+                    if (x >= 0x80u || ((DOC >> (bit + 1)) & 3u)) { unc |= (m | (m << 1) | (m << 2) | (m << 3) | (m << 4)) & LEAD; continue; }
+                    if (ci) { if (x >= 'A' && x <= 'Z') x += 32; if (y >= 'A' && y <= 'Z') y += 32; }
+                    // the second letter must be a letter of this document too (an added-token literal is not)
+                    const bool y_ok = ((L >> (bit + 2)) & 1u) != 0;
+                    if (!((L >> (bit + 1)) & 1u)) continue;
+                    if ((x == 'r' || x == 'v') && y == 'e' && y_ok) cs2 |= m;
+                    else if (x == 'l' && y == 'l' && y_ok) cs2 |= m;
+                    else if (x == 's' || x == 't' || x == 'm' || x == 'd') cs1 |= m;
+                }
+            }
+            {
+                const uint64_t x = messy ? AP : apC;
+                unc |= (x | (x << 1) | (x << 2) | (x << 3)) & LEAD;
+            }
+            bnd |= AD | (DOC & C) | pNone;
+            if (family == 0) {
+                const uint64_t nNonS = nextcp(L | N | O);
+                bnd |= S & (~pS | nNonS);
+                const uint64_t rest = (L | N | O) & ~pSP;          // a literal space before leads the token
+                bnd |= rest & ((L & ~pL) | (N & ~pN) | (O & ~pO));
+            } else {
+                const uint64_t nNonS = nextcp(L | N | O);
+                const uint64_t Scr = S & CR, Spl = S & ~CR;
+                bnd |= Scr & (pL | pN);
+                bnd |= Spl & ~pS;
+                bnd |= Spl & pS & ~pCR & nNonS;
+                // Plain whitespace right after a newline: it opens the rest of the run when the newline
+                // stretch before it hangs off a punctuation token, or when no later newline in the run
+                // pulls it into \s*[\r\n]+.  Both are floods along a stretch of bits (carry of an
+                // addition); a stretch that leaves the window is decided one by one instead.
+                const uint64_t cand = Spl & pS & pCR;
+                if (cand) {
+                    const uint64_t Mcr = CR & ~DOC;                              // newline bytes, stretches cut at document starts
+                    const uint64_t rs = CR & (~(CR << 1) | DOC);                 // first byte of each stretch
+                    const uint64_t absorbed = ((Mcr + (rs & pO & Mcr)) ^ Mcr) & Mcr;
+                    const uint64_t from_edge = (Mcr & 1ull) ? (((Mcr + 1ull) ^ Mcr) & Mcr) : 0ull;   // stretch whose start is not visible
+                    const uint64_t SplF = fill(Spl) & ~DOC;
+                    const uint64_t top_nl = SplF & ((CR & ~DOC) >> 1);           // whitespace byte directly before a newline
+                    const uint64_t rM = brev64(SplF), rT = brev64(top_nl);
+                    const uint64_t later_nl = brev64(((rM + rT) ^ rM) & rM);     // whitespace stretches that end in a newline
+                    const uint64_t to_edge = (rM & 1ull) ? brev64(((rM + 1ull) ^ rM) & rM) : 0ull;  // stretch that reaches the window's end
+                    const uint64_t unknown = cand & ((from_edge << 1) | to_edge);
+                    bnd |= cand & ~unknown & ((absorbed << 1) | ~later_nl);
+                    unc |= unknown;
+                }
+                const uint64_t ppOorSP = prevcp(pO | pSP);         // prev-prev is punctuation or a literal space
+                bnd |= L & ((pS & pCR) | (pO & ppOorSP) | pN);
+                if (family == 2) bnd |= N;
+                else { bnd |= N & ~pN; pend = N & pN; }
+                bnd |= O & ~pO & ~pSP;
+            }
+            {
+                const uint64_t in_tail = ((cs1 | cs2) << 1) | (cs2 << 2);
+                const uint64_t after_tail = (cs1 << 2) | (cs2 << 3);
+                bnd = (bnd & ~in_tail) | cs1 | cs2 | (after_tail & L & pL);
+            }
         }
         bnd &= ~unc;
         pend &= ~unc;
