@@ -583,6 +583,37 @@ def main():
             "bytes": len(doc4), "tokens": int(off4[-1]), "device_ms": d4, "device_MBps": len(doc4) / (d4 * 1e-3) / 1e6,
             "shard_bytes": [int(x) for x in sb4], "shard_imbalance": float(sb4.max() / sb4.mean()),
             "verified": "token total only (ids at this size are compared with the oracle in tests/test_gpu_parity.py)", "tokens_expected": 14358917}
+        # beyond the five configurations: a DeepSeek-V3-shaped vocabulary (three Split patterns, 100,000 merges) on a
+        # 4 MiB multilingual document, cut into chunks like configuration 1; ids against the CPU oracle
+        path5, doc5 = synth.config_doc(5)
+        pl = GTok(path5, max_bytes=4096)
+        cuts5 = pl.plan_chunks(doc5, world) if world > 1 else np.array([0, len(doc5)], dtype=np.uint64)
+        pl.close()
+        part5 = doc5[int(cuts5[rank]):int(cuts5[rank + 1])]
+        g5 = GTok(path5, max_bytes=len(part5) + 4096)
+        ids5 = g5.encode(part5)
+        off5 = gather_counts(ids5.size)
+        ids5_all = gather_ids(ids5, off5)
+        g5.stage(part5)
+        for _ in range(3):
+            flush()
+            g5.replay()
+        barrier()
+        ms5 = []
+        for _ in range(max(5, args.steps // 5)):
+            flush()
+            ms5.append(g5.replay()[1])
+        barrier()
+        g5.close()
+        d5 = all_max([float(np.mean(ms5))])[0]
+        ok5 = None
+        if rank == 0:
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import oracle_lib
+            ok5 = bool(np.array_equal(ids5_all, oracle_lib.Oracle(path5).encode(doc5)))
+        others["deepseek_v3_shaped_4MiB"] = {
+            "bytes": len(doc5), "tokens": int(off5[-1]), "device_ms": d5, "device_MBps": len(doc5) / (d5 * 1e-3) / 1e6,
+            "ids_match_cpu_oracle": ok5}
 
     latency = decode = small = None
     if world == 1 and not args.quick:

@@ -4,7 +4,7 @@
 // document ranges of about equal byte count.  One long document is cut only at
 // positions where a pre-token provably starts whatever precedes it and no
 // run-level rule can reach across: an ASCII letter, then a single 0x20 space,
-// then an ASCII letter, with the cut in front of the space.  For all three
+// then an ASCII letter, with the cut in front of the space.  For all four
 // families the space opens the next word's pre-token there (" word"), a regular
 // expression never looks behind its match start, and cutting the text in front
 // of the space ends the left part on a letter run exactly as the space would; the

@@ -100,20 +100,20 @@ def test_emul_batch_equals_per_document(emuls, oracles, family):
 
 def test_emul_synthetic_documents(built):
     from graphtok_b200 import synth
-    for name, cfg in (("tiny_gpt2", 0), ("tiny_llama3", 1), ("tiny_qwen25", 3), ("tiny_llama3", 4)):
+    for name, cfg in (("tiny_gpt2", 0), ("tiny_llama3", 1), ("tiny_qwen25", 3), ("tiny_llama3", 4), ("tiny_deepseek", 1), ("tiny_deepseek", 4), ("tiny_deepseek", 3)):
         path = synth.vocab_path(name)
         e, o = oracle_lib.Emul(path), oracle_lib.Oracle(path)
         b = norm(o, synth.text(cfg, 77, 300000)[:260000].decode("utf-8", "ignore").encode())
         assert np.array_equal(e.encode(b), o.encode_normalized(b)), name
 
 
-@pytest.mark.parametrize("family", ("gpt2", "llama3"))
+@pytest.mark.parametrize("family", ("gpt2", "llama3", "deepseek"))
 def test_chunk_plan_concatenates(emuls, oracles, family):
     """Cutting a document at planned positions and encoding the parts gives the whole document's ids."""
     import ctypes
     from graphtok_b200 import synth
     e, o = emuls[family], oracles[family]
-    doc = synth.text(1 if family == "llama3" else 0, 5, 200000)
+    doc = synth.text(0 if family == "gpt2" else 1, 5, 200000)
     lib = e.lib
     lib.gtok_emul_plan_chunks.restype = ctypes.c_int
     lib.gtok_emul_plan_chunks.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_void_p]
