@@ -97,10 +97,10 @@ GTOK_DEV void decode_tile(Blk& blk, const DecodeArgs& a, DecodeSmem& sm, int til
     const uint32_t base = blk.lookback(a.st, tile, total, a.ctl);
     if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
         blk.par([&](int tid) {
-            if (tid == 0) a.status[0] = base + total;
+            if (tid == 0) a.status[0] = base + total < base ? 0xFFFFFFFFu : base + total;     // 0xFFFFFFFF: 4 GiB or more
         });
     }
-    if (base + total > a.out_cap || base + total < base) {
+    if (base + total > a.out_cap || base + total < base || base == 0xFFFFFFFFu) {
         blk.par([&](int tid) {
             if (tid == 0) global_or(a.ctl + CTL_ERR, kErrOutputFull);
         });

@@ -1153,6 +1153,7 @@ int64_t Engine::decode(const uint32_t* ids, uint32_t n, uint8_t* out, uint64_t m
     cudaError_t e = cudaSuccess;
     if (bits & kErrBadId) { last_error_ = "decode: an id is outside the vocabulary"; return -1; }
     if (bits & kErrWaitExpired) { last_error_ = "decode: a wait on an earlier tile gave up"; return -1; }
+    if (total == 0xFFFFFFFFu) { last_error_ = "decode: the ids spell 4 GiB or more, beyond what one call decodes"; return -1; }
     if (need) *need = total;
     if ((bits & kErrOutputFull) || total > max_out) { last_error_ = "decode: more bytes than the output buffer holds"; return -2; }
     if (bits) { last_error_ = "decode: internal error"; return -1; }

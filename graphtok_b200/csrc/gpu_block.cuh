@@ -81,7 +81,8 @@ struct GpuBlk {
         if (threadIdx.x < 32) {
             const int lane = threadIdx.x;
             if (lane == 0) store_state(st + tile, (tile == 0 ? kStFinal : kStAgg) | total);
-            uint32_t base = 0;
+            // (sums saturate at 0xFFFFFFFF instead of wrapping: a total of 4 GiB or more stays visible to every later tile)
+            unsigned long long base = 0;
             int hi = tile - 1;
             bool done = tile == 0;
             while (!done) {
@@ -95,12 +96,14 @@ struct GpuBlk {
                     if (lane > first) val = 0;
                     done = true;
                 }
-                base += __reduce_add_sync(0xFFFFFFFFu, val);
+                base += (static_cast<unsigned long long>(__reduce_add_sync(0xFFFFFFFFu, val >> 16)) << 16) + __reduce_add_sync(0xFFFFFFFFu, val & 0xFFFFu);
                 hi -= 32;
             }
+            if (base > 0xFFFFFFFFull) base = 0xFFFFFFFFull;
             if (lane == 0) {
-                if (tile > 0) store_state(st + tile, kStFinal | (base + total));
-                s_base = base;
+                const unsigned long long incl = base + total > 0xFFFFFFFFull ? 0xFFFFFFFFull : base + total;
+                if (tile > 0) store_state(st + tile, kStFinal | incl);
+                s_base = static_cast<uint32_t>(base);
             }
         }
         __syncthreads();

@@ -47,13 +47,14 @@ struct CpuBlk {
         *other_total = o;
     }
     uint32_t lookback(unsigned long long* st, int tile, uint32_t total, uint32_t*) {
-        uint32_t base = 0;
+        unsigned long long base = 0;         // saturating, like the kernels' look-back
         for (int j = tile - 1; j >= 0; --j) {
             base += static_cast<uint32_t>(st[j]);
             if ((st[j] >> 62) == 2) break;
         }
-        st[tile] = gtok::kStFinal | (base + total);
-        return base;
+        if (base > 0xFFFFFFFFull) base = 0xFFFFFFFFull;
+        st[tile] = gtok::kStFinal | (base + total > 0xFFFFFFFFull ? 0xFFFFFFFFull : base + total);
+        return static_cast<uint32_t>(base);
     }
     uint32_t reduce_min(uint32_t* arr) {
         uint32_t m = 0xFFFFFFFFu;
