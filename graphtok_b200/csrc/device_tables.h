@@ -85,7 +85,8 @@ struct DeviceTables {
     uint32_t uc_wide;                    // the class table is the wide one (unicode_wide_table.h: four bits per codepoint)
     uint32_t ignore_merges;
     uint32_t monotone;
-    uint32_t added_ws;                   // some added-token literal contains a space, CR or LF
+    uint32_t added_ws;                   // some added-token literal contains an ASCII whitespace byte (space, tab, CR, LF, VT, FF)
+    uint32_t added_alpha_end;            // some added-token literal ends with an ASCII letter
     // Normalisation data (nfc_tables.h), uploaded only for vocabularies that declare NFC.
     const uint32_t* nfc_attn_bits;       // one bit per BMP codepoint that can make a text non-NFC
     const uint32_t* nfc_attn_sup;        // (lo, hi) ranges of such codepoints above the BMP

@@ -815,21 +815,72 @@ GTOK_DEV int skip_back_newlines(const Win& w, int q) {
         --q;
     }
 }
-// r is a lead at or past the window end: first position at or after r that is not a
-// plain space of the same document, or -1 at the end of the document.
-GTOK_DEV int skip_forward_spaces(const Win& w, int r) {
+// r is a lead at or past the window end: first position at or after r that is not the byte `sp` (a
+// plain space, or another one-byte ASCII whitespace character) of the same document, or -1 at the
+// end of the document.
+GTOK_DEV int skip_forward_spaces(const Win& w, int r, uint32_t sp = 0x20u) {
     const EncodeArgs& a = *w.a;
     if (a.tb.added_ws) return r;
+    const uint32_t sp4 = sp * 0x01010101u;
     for (;;) {
         if (r >= w.n) return -1;
-        if ((r & 127) == 0 && r > 0 && r + 128 <= w.n && run_of_128(a, r, 0x20u, 0x20u)) { r += 128; continue; }
+        if ((r & 127) == 0 && r > 0 && r + 128 <= w.n && run_of_128(a, r, sp, sp)) { r += 128; continue; }
         if ((r & 15) == 0 && r + 16 <= w.n && no_docstart_in16(a, r)) {
             const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + r);
-            if (ldg(p4) == 0x20202020u && ldg(p4 + 1) == 0x20202020u && ldg(p4 + 2) == 0x20202020u && ldg(p4 + 3) == 0x20202020u) { r += 16; continue; }
+            if (ldg(p4) == sp4 && ldg(p4 + 1) == sp4 && ldg(p4 + 2) == sp4 && ldg(p4 + 3) == sp4) { r += 16; continue; }
         }
         if (is_docstart_global(a, r)) return -1;
-        if (ldg(a.text + r) != 0x20u) return r;
+        if (ldg(a.text + r) != sp) return r;
         ++r;
+    }
+}
+// q is an ASCII letter outside any added-token literal: position of the first byte before the run of
+// ASCII letters it stands in that is not one, or the letter that opens its document.  Whole words of
+// four letters are stepped over sixteen bytes at a time (a literal's bytes would read as letters too:
+// the caller asks only when no literal ends with a letter, so that a literal always shows its last,
+// other byte first).
+GTOK_DEV bool four_letters(uint32_t v) {
+    const uint32_t lo7 = (v | 0x20202020u) & 0x7F7F7F7Fu;
+    const uint32_t ge_a = lo7 + (0x80u - 'a') * 0x01010101u, gt_z = lo7 + (0x80u - 'z' - 1u) * 0x01010101u;
+    return (ge_a & ~gt_z & ~v & 0x80808080u) == 0x80808080u;
+}
+// True when the 128 bytes at q (q % 128 == 0) are all ASCII letters and none of them opens a document
+// (eight independent loads, as in run_of_128).
+GTOK_DEV bool letters_128(const EncodeArgs& a, int q) {
+    if (a.docmask) {
+        const uint32_t* dm = a.docmask + (q >> 5);
+        if (ldg(dm) | ldg(dm + 1) | ldg(dm + 2) | ldg(dm + 3)) return false;
+    }
+    bool ok = true;
+#if defined(__CUDA_ARCH__)
+    const uint4* p = reinterpret_cast<const uint4*>(a.text + q);
+    uint4 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = ld128(p + k);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ok = ok && four_letters(v[k].x) && four_letters(v[k].y) && four_letters(v[k].z) && four_letters(v[k].w);
+#else
+    for (int k = 0; k < 32; ++k) {
+        const uint8_t* t = a.text + q + 4 * k;
+        ok = ok && four_letters(static_cast<uint32_t>(t[0]) | (static_cast<uint32_t>(t[1]) << 8) | (static_cast<uint32_t>(t[2]) << 16) | (static_cast<uint32_t>(t[3]) << 24));
+    }
+#endif
+    return ok;
+}
+GTOK_DEV int skip_back_letters(const Win& w, int q) {
+    const EncodeArgs& a = *w.a;
+    for (;;) {
+        if (q < 0) return q;
+        if ((q & 127) == 127 && q >= 255 && letters_128(a, q - 127)) { q -= 128; continue; }
+        if ((q & 15) == 15 && q >= 31 && no_docstart_in16(a, q - 15)) {
+            const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + q - 15);
+            const uint32_t v0 = ldg(p4), v1 = ldg(p4 + 1), v2 = ldg(p4 + 2), v3 = ldg(p4 + 3);
+            if (four_letters(v0) && four_letters(v1) && four_letters(v2) && four_letters(v3)) { q -= 16; continue; }
+        }
+        const uint32_t b = ldg(a.text + q);
+        if (!((b >= 'a' && b <= 'z') || (b >= 'A' && b <= 'Z'))) return q;
+        if (is_docstart_global(a, q)) return q;
+        --q;
     }
 }
 
@@ -949,6 +1000,15 @@ GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, boo
             int k = q;
             uint8_t ak = a1;
             for (;;) {
+                if (k > 0 && !w.a->tb.added_alpha_end && !(ak & A_DOC) && ascii_letter(text_at(w, k - 1))) {
+                    // over raw bytes, sixteen at a time (one codepoint at a time a long run would hold its tile up)
+                    const int r = skip_back_letters(w, k - 1);
+                    if (r < k - 1) {
+                        const uint32_t br = r >= 0 ? text_at(w, r) : 0u;
+                        k = (r >= 0 && ascii_letter(br)) ? r : r + 1;        // a letter there opens its document
+                        ak = attr_at(w, k);
+                    }
+                }
                 uint8_t aj;
                 const int j = ds_prev(w, k, ak, &aj);
                 if (j < 0) return false;
@@ -971,6 +1031,15 @@ GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, boo
             int k = q;
             uint8_t ak = a1;
             for (;;) {
+                if (k > 0 && !(ak & A_DOC) && (text_at(w, k - 1) == 0x0Au || text_at(w, k - 1) == 0x0Du)) {
+                    // over raw bytes, up to 128 at a time
+                    const int r = skip_back_newlines(w, k - 1);
+                    if (r < k - 1) {
+                        const uint32_t br = r >= 0 ? text_at(w, r) : 0u;
+                        k = (r >= 0 && (br == 0x0Au || br == 0x0Du)) ? r : r + 1;        // a newline there opens its document
+                        ak = attr_at(w, k);
+                    }
+                }
                 uint8_t aj;
                 const int j = ds_prev(w, k, ak, &aj);
                 if (j < 0) break;
@@ -981,6 +1050,15 @@ GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, boo
             k = p;
             ak = a0;
             for (;;) {
+                if (k + 1 < w.n) {
+                    // runs of one ASCII whitespace byte over raw bytes
+                    const uint32_t sp = text_at(w, k + 1);
+                    if (sp == 0x20u || sp == 0x09u || sp == 0x0Bu || sp == 0x0Cu) {
+                        const int r = skip_forward_spaces(w, k + 1, sp);
+                        if (r < 0) return true;                       // whitespace to the end of the document
+                        if (r > k + 2) { k = r - 1; ak = attr_at(w, k); }
+                    }
+                }
                 uint8_t aj;
                 const int j = ds_next(w, k, ak, &aj);
                 if (j < 0 || (aj & A_CLS) != A_S) return true;
@@ -1004,7 +1082,6 @@ GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, boo
 // Sets *pending for a Llama-3 digit inside a digit run, whose answer depends on
 // its index in the run and is filled in later.
 GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool* pending, bool* nstart) {
-    if (family == 3) return is_boundary_deepseek(w, p, a0, pending, nstart);
     *pending = false;
     const int cur = a0 & A_CLS;
     const bool ci = family != 0;
@@ -1124,10 +1201,12 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
 }
 
 // Once per block, before its first tile: the byte table and the block's copy of the class table.
-template <class Blk>
+// kWide: the vocabulary is of the DeepSeek-V3 family (wide class table, its own boundary rules); a
+// template parameter so that the other families' kernel carries none of that code.
+template <bool kWide, class Blk>
 GTOK_DEV void pretok_block_init(Blk& blk, const EncodeArgs& a, PretokSmem& sm) {
     blk.par([&](int tid) {
-        const bool wide = a.tb.uc_wide != 0;      // the wide table is larger than the block's copy: it stays in global memory
+        constexpr bool wide = kWide;              // the wide table is larger than the block's copy: it stays in global memory
         if (!wide) {
 #if defined(__CUDA_ARCH__)
             // 128-bit copies (both arrays are whole multiples of 16 bytes and 16-byte aligned in device memory)
@@ -1151,7 +1230,7 @@ GTOK_DEV void pretok_block_init(Blk& blk, const EncodeArgs& a, PretokSmem& sm) {
 }
 
 // One tile of pre-tokenization.
-template <class Blk>
+template <bool kWide, class Blk>
 GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int tile) {
     const int n = static_cast<int>(ldg(a.meta));
     const int t0 = tile * kPTile;
@@ -1227,7 +1306,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                 uint32_t* ohw = reinterpret_cast<uint32_t*>(sm.oh + i0);
                 for (int k = 0; k < 4; ++k) { txw[k] = 0; atw[k] = A_OUT * 0x01010101u; ohw[k] = 0; }
                 for (int k = 0; k < kPlanes; ++k) sm.plane[k][c] = 0;
-                if (a.tb.uc_wide) for (int k = 0; k < kXPlanes; ++k) xplane(sm, k)[c] = 0;
+                if (kWide) for (int k = 0; k < kXPlanes; ++k) xplane(sm, k)[c] = 0;
                 sm.cand16[c] = 0;
                 continue;
             }
@@ -1306,7 +1385,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     else if ((b & 0xF0u) == 0xE0u && avail >= 3) cp = ((b & 0x0Fu) << 12) | ((b1 & 0x3Fu) << 6) | (b2 & 0x3Fu);
                     else if ((b & 0xF8u) == 0xF0u && avail >= 4) cp = ((b & 0x07u) << 18) | ((b1 & 0x3Fu) << 12) | ((b2 & 0x3Fu) << 6) | (b3 & 0x3Fu);
                     uint32_t cls = A_O;
-                    if (a.tb.uc_wide) {
+                    if (kWide) {
                         cls = uc_class([&](uint32_t k) { return static_cast<uint32_t>(ldg(a.tb.uc_stage1 + k)); }, [&](uint32_t k) { return ldg(a.tb.uc_stage2 + k); }, cp, true);
                         if (cp_is_cjk(cp)) cls |= A_CJK;
                     } else if (cp < 0x10000u) {
@@ -1320,10 +1399,10 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     sm.oh[i0 + i] = onehot_of(static_cast<uint8_t>(cls & A_CLS));
                 }
                 ow[0] = ohw[0]; ow[1] = ohw[1]; ow[2] = ohw[2]; ow[3] = ohw[3];
-                aw[0] = atw[0]; aw[1] = atw[1]; aw[2] = atw[2]; aw[3] = atw[3];
+                if (kWide) { aw[0] = atw[0]; aw[1] = atw[1]; aw[2] = atw[2]; aw[3] = atw[3]; }
             }
             chunk_planes(sm, c, ow, tw);
-            if (a.tb.uc_wide) chunk_xplanes(sm, c, aw, tw);
+            if (kWide) chunk_xplanes(sm, c, aw, tw);
             sm.cand16[c] = static_cast<uint16_t>(cand);
         }
     });
@@ -1415,7 +1494,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
                     const uint32_t* twp = reinterpret_cast<const uint32_t*>(sm.txt + c * 16);
                     const uint32_t ow[4] = {owp[0], owp[1], owp[2], owp[3]}, tw[4] = {twp[0], twp[1], twp[2], twp[3]};
                     chunk_planes(sm, c, ow, tw);
-                    if (a.tb.uc_wide) {
+                    if (kWide) {
                         const uint32_t* awp = reinterpret_cast<const uint32_t*>(sm.attr + c * 16);
                         const uint32_t aw[4] = {awp[0], awp[1], awp[2], awp[3]};
                         chunk_xplanes(sm, c, aw, tw);
@@ -1470,7 +1549,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         // (a continuation byte right after an apostrophe stretches a contraction past three bytes)
         // An added-token literal is its start bit plus continuation bits; those long stretches are
         // harmless to the algebra (the literal has no class, so its neighbours see "nothing").
-        if (family == 3) {
+        if (kWide) {
             // DeepSeek-V3 (see is_boundary_deepseek for the rules; here the same over whole planes).
             auto xload = [&](int k) -> uint64_t {
                 const uint32_t* pw = reinterpret_cast<const uint32_t*>(xplane(sm, k));
@@ -1621,7 +1700,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             const uint64_t m = 1ull << bit;
             if ((a0 & A_CLS) == A_ADDED) { bnd |= m; continue; }
             bool pending = false, ns = false;
-            const bool bb = is_boundary(w, p, a0, family, &pending, &ns);
+            const bool bb = kWide ? is_boundary_deepseek(w, p, a0, &pending, &ns) : is_boundary(w, p, a0, family, &pending, &ns);
             if (bb) bnd |= m; else bnd &= ~m;
             if (pending) pend |= m; else pend &= ~m;
             if ((a0 & A_CLS) == A_N) { if (ns) nstart |= m; else nstart &= ~m; }
@@ -1638,7 +1717,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 
     mark(4);
     // ---- P4: index of each digit in its run (\p{N}{1,3} of Llama-3 and DeepSeek-V3) ----
-    if (family == 1 || family == 3) {
+    if (family == 1 || kWide) {
         const uint32_t* leadw = reinterpret_cast<const uint32_t*>(sm.lead16);
         const uint32_t* nleadw = reinterpret_cast<const uint32_t*>(sm.nlead16);
         const uint32_t* nstartw = reinterpret_cast<const uint32_t*>(sm.nstart16);

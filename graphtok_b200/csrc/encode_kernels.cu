@@ -23,7 +23,8 @@ namespace gtok {
 
 namespace {
 
-__global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const __grid_constant__ EncodeArgs a) {
+template <bool kWide>
+__device__ __forceinline__ void pretok_body(const EncodeArgs& a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PretokSmem& sm = *reinterpret_cast<PretokSmem*>(smem_raw);
     __shared__ int s_tile;
@@ -31,7 +32,7 @@ __global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const __grid_consta
     const uint32_t n = a.meta[0];
     const int n_tiles = static_cast<int>((n + kPTile - 1) / kPTile);
     tl_stamp(a, 0, 0);
-    pretok_block_init(blk, a, sm);
+    pretok_block_init<kWide>(blk, a, sm);
     for (int done = 0;; ++done) {
         if (threadIdx.x == 0) s_tile = static_cast<int>(atomicAdd(a.ctl + 0, 1u));
         __syncthreads();
@@ -39,11 +40,15 @@ __global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const __grid_consta
         __syncthreads();
         if (tile >= n_tiles) break;
         if (threadIdx.x == 0) sm.misc[2] = static_cast<uint32_t>(done);      // diagnostics: which of the block's tiles this is
-        pretok_tile(blk, a, sm, tile);
+        pretok_tile<kWide>(blk, a, sm, tile);
         tl_stamp(a, 0, 2 + done);
     }
     tl_stamp(a, 0, 1);
 }
+__global__ void __launch_bounds__(kThreads, 4) pretok_kernel(const __grid_constant__ EncodeArgs a) { pretok_body<false>(a); }
+// The same for vocabularies of the DeepSeek-V3 family (wide class table, its own rules): a kernel of its own, so
+// that neither family's code weighs on the other's registers.
+__global__ void __launch_bounds__(kThreads, 4) pretok_wide_kernel(const __grid_constant__ EncodeArgs a) { pretok_body<true>(a); }
 
 // Kernel 0 (vocabularies that declare NFC): raw text -> normalised text, byte count and
 // document offsets; tiles in ticket order because a tile's place in the output is the sum of
@@ -267,7 +272,8 @@ int boundaries_noalloc(const DeviceTables& tb, int device, const void* text_dev,
     if (e != cudaSuccess) { err = std::string("cudaMemsetAsync: ") + cudaGetErrorString(e); return -1; }
     noalloc_set_meta<<<1, 1, 0, stream>>>(sc->meta, len);
     const int blocks = static_cast<int>(n_tiles < static_cast<uint32_t>(sm_of[device] * 4) ? n_tiles : sm_of[device] * 4);
-    pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), stream>>>(a);
+    if (a.tb.uc_wide) pretok_wide_kernel<<<blocks, kThreads, sizeof(PretokSmem), stream>>>(a);
+    else pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), stream>>>(a);
     e = cudaGetLastError();
     // The kernel's error word comes back with the result (a copy into a local variable: no
     // allocation).  A wait on an earlier tile that gave up leaves wrong bits behind, and two calls
@@ -289,6 +295,8 @@ cudaError_t configure_kernels() {
     cudaError_t e = cudaFuncSetAttribute(words_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(WordsSmem)));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PretokSmem)));
     if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PretokSmem)));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(pretok_wide_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(assemble_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(miss_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(MissSmem)));
     // All four kernels work out of shared memory, not L1: the largest carve-out for each, so that as
@@ -346,7 +354,10 @@ void launch_raw_docmask(const EncodeArgs& a, uint32_t* docmask, int blocks, cuda
 void launch_nfc_check(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_check_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_nfc_copy(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_copy_kernel<<<blocks, kThreads, 0, s>>>(a); }
 void launch_nfc(const EncodeArgs& a, int blocks, cudaStream_t s) { nfc_kernel<<<blocks, kThreads, 0, s>>>(a); }
-void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) { pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), s>>>(a); }
+void launch_pretok(const EncodeArgs& a, int blocks, cudaStream_t s) {
+    if (a.tb.uc_wide) pretok_wide_kernel<<<blocks, kThreads, sizeof(PretokSmem), s>>>(a);
+    else pretok_kernel<<<blocks, kThreads, sizeof(PretokSmem), s>>>(a);
+}
 const void* words_kernel_address() { return reinterpret_cast<const void*>(words_kernel); }
 const void* miss_kernel_address() { return reinterpret_cast<const void*>(miss_kernel); }
 void launch_words(const EncodeArgs& a, int blocks, cudaStream_t s) { words_kernel<<<blocks, kThreads, sizeof(WordsSmem), s>>>(a); }

@@ -202,8 +202,12 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
     // ---- added-token trie ---------------------------------------------------
     out.added_max_bytes = hv.added_max_bytes;
     out.added_ws = 0;
-    for (const AddedToken& a : hv.added)
-        for (unsigned char c : a.content) if (c == 0x20 || c == 0x0A || c == 0x0D) out.added_ws = 1;
+    out.added_alpha_end = 0;
+    for (const AddedToken& a : hv.added) {
+        for (unsigned char c : a.content) if (c == 0x20 || (c >= 0x09 && c <= 0x0D)) out.added_ws = 1;
+        const unsigned char last = a.content.empty() ? 0 : static_cast<unsigned char>(a.content.back());
+        if ((last >= 'a' && last <= 'z') || (last >= 'A' && last <= 'Z')) out.added_alpha_end = 1;
+    }
     for (int i = 0; i < 8; ++i) out.lit1_bits[i] = out.lit2_bits[i] = 0;
     out.lit_single = 0;
     for (const auto& a : hv.added) {

@@ -26,7 +26,7 @@ struct HostTables {
     uint32_t lit1_bits[8] = {}, lit2_bits[8] = {}, lit_single = 0;
     std::vector<LitSlot> littab;
     uint32_t lit_n_lens = 0, lit_lens[kLitLens] = {};
-    uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0;
+    uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0, added_alpha_end = 0;
 };
 
 // Returns false (with a reason) when a table cannot be built within its probe
@@ -50,6 +50,7 @@ inline void fill_table_scalars(const HostTables& ht, DeviceTables& tb) {
     tb.ignore_merges = ht.ignore_merges;
     tb.monotone = ht.monotone;
     tb.added_ws = ht.added_ws;
+    tb.added_alpha_end = ht.added_alpha_end;
 }
 
 // Packs up to 15 bytes into a word-table key.

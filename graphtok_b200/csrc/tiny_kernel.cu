@@ -53,10 +53,18 @@ __global__ void __launch_bounds__(kThreads, 1) tiny_kernel(const __grid_constant
     tl_stamp(a, 5, 1);
     if (n == 0) { if (tid == 0) { a.status[0] = 0; a.status[1] = host_meta[0] ? kErrInternal : 0u; } return; }
     const int p_tiles = static_cast<int>((n + kPTile - 1) / kPTile), w_tiles = static_cast<int>((n + kTile - 1) / kTile);
-    pretok_block_init(blk, a, sm.pretok);
-    for (int t = 0; t < p_tiles; ++t) {
-        if (tid == 0) sm.pretok.misc[2] = 2;            // no timeline row for this kernel
-        pretok_tile(blk, a, sm.pretok, t);
+    if (a.tb.uc_wide) {
+        pretok_block_init<true>(blk, a, sm.pretok);
+        for (int t = 0; t < p_tiles; ++t) {
+            if (tid == 0) sm.pretok.misc[2] = 2;        // no timeline row for this kernel
+            pretok_tile<true>(blk, a, sm.pretok, t);
+        }
+    } else {
+        pretok_block_init<false>(blk, a, sm.pretok);
+        for (int t = 0; t < p_tiles; ++t) {
+            if (tid == 0) sm.pretok.misc[2] = 2;
+            pretok_tile<false>(blk, a, sm.pretok, t);
+        }
     }
     __syncthreads();
     tl_stamp(a, 5, 2);

@@ -69,6 +69,15 @@ def tile_crossers(special):
     out.append("k\n" + " " * 9000 + "\n x")
     out.append("k\n" + " " * 9000)
     out.append("k\n" + " " * 5000 + "\t" + " " * 5000 + "\n\nq")
+    out.append("k\n" + "\t" * 9000 + "\nq")
+    out.append("k\n" + "\t" * 9000 + "q")
+    out.append("k!" + "\n" * 9000 + " q")
+    out.append("\n" * 9000 + " q")
+    # ASCII letters behind a punctuation mark, or not, for longer than the window, then another kind of letter
+    # (the first alternative of the DeepSeek-V3 main pattern stops there)
+    for head in ("!", " !", "!!", "", "x.", "1", "中", "\n"):
+        out.append("w " + head + "a" * 9000 + "é b")
+        out.append(head + "Zq" * 4500 + "\u0301 b")
     # long pre-tokens made of a few byte runs (run-length merge path) and of many (general path)
     out.append("w " + "a" * 3000 + "b" * 3000 + "a" * 10 + " t")
     out.append("w " + "=" * 700 + "-" * 65 + "=" * 2 + "~" * 9000 + " t")

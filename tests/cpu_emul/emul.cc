@@ -154,7 +154,11 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
     blk.reverse = reverse != 0;
     {
         PretokSmem* sm = new PretokSmem();
-        for (uint32_t t = 0; t < (n + kPTile - 1) / kPTile; ++t) { std::memset(sm, 0xCD, sizeof *sm); pretok_block_init(blk, a, *sm); pretok_tile(blk, a, *sm, static_cast<int>(t)); }
+        for (uint32_t t = 0; t < (n + kPTile - 1) / kPTile; ++t) {
+            std::memset(sm, 0xCD, sizeof *sm);
+            if (a.tb.uc_wide) { pretok_block_init<true>(blk, a, *sm); pretok_tile<true>(blk, a, *sm, static_cast<int>(t)); }
+            else { pretok_block_init<false>(blk, a, *sm); pretok_tile<false>(blk, a, *sm, static_cast<int>(t)); }
+        }
         delete sm;
     }
     if (bmask_out) std::memcpy(bmask_out, bmask.data(), static_cast<size_t>(n_tiles) * kTileWords * 4);

@@ -333,6 +333,24 @@ def test_configuration_4_full_size_and_chunks(built):
         g.close()
 
 
+def test_deepseek_vocabulary_on_the_adversarial_document(built):
+    """The 32 MB adversarial document (long runs of one whitespace character, of newlines, of digits, base64
+    blocks) under the DeepSeek-V3-shaped vocabulary: one replay and eight planned chunks against the oracle.
+    The long runs are where that family's boundary rules walk furthest."""
+    from graphtok_b200 import GTok, synth
+    path = synth.vocab_path("cfg5")
+    _, doc = synth.config_doc(4)
+    want = oracle_lib.Oracle(path).encode_normalized(doc)
+    g = GTok(path, max_bytes=len(doc) + 4096)
+    try:
+        assert np.array_equal(g.encode(doc), want)
+        cuts = g.plan_chunks(doc, 8)
+        parts = [g.encode(doc[int(cuts[k]):int(cuts[k + 1])]) for k in range(8)]
+        assert np.array_equal(np.concatenate(parts), want)
+    finally:
+        g.close()
+
+
 def test_configuration_2_batch_full_size(built):
     """All 8,192 documents of the batch configuration in one call: ids and per-document offsets
     against the oracle run document by document."""
