@@ -87,6 +87,7 @@ struct DeviceTables {
     uint32_t monotone;
     uint32_t added_ws;                   // some added-token literal contains an ASCII whitespace byte (space, tab, CR, LF, VT, FF)
     uint32_t added_alpha_end;            // some added-token literal ends with an ASCII letter
+    uint32_t lit_first, lit_first_n;     // the distinct first bytes of the literals, one per byte of lit_first when there are at most four
     // Normalisation data (nfc_tables.h), uploaded only for vocabularies that declare NFC.
     const uint32_t* nfc_attn_bits;       // one bit per BMP codepoint that can make a text non-NFC
     const uint32_t* nfc_attn_sup;        // (lo, hi) ranges of such codepoints above the BMP

@@ -689,7 +689,28 @@ GTOK_DEV_NOINLINE uint8_t attr_global(const EncodeArgs& a, int p, int n) {
     if (p < 0 || p >= n) return A_OUT;
     auto byte_at = [&](int q) -> uint32_t { return ldg(a.text + q); };
     auto is_doc = [&](int q) -> bool { return is_docstart_global(a, q); };
-    if (a.tb.added_max_bytes) {
+    bool may_be_in_literal = a.tb.added_max_bytes != 0;
+    if (may_be_in_literal && a.tb.lit_first_n <= 4u) {
+        // A literal that holds p starts at one of the few bytes a literal can start with, at most
+        // added_max_bytes - 1 before p: the words that cover that stretch are fetched together and searched for
+        // those byte values at once, so that the usual answer ("none there") costs one memory round trip.
+        int lim = p - static_cast<int>(a.tb.added_max_bytes) + 1;
+        if (lim < 0) lim = 0;
+        const int w0 = lim >> 2, w1 = p >> 2;
+        uint32_t found = 0;
+        if (w1 - w0 < 16) {
+            const uint32_t* tw = reinterpret_cast<const uint32_t*>(a.text);
+            for (int wd = w0; wd <= w1; ++wd) {
+                const uint32_t v = ldg(tw + wd);
+                for (uint32_t f = 0; f < a.tb.lit_first_n; ++f) {
+                    const uint32_t x = v ^ (((a.tb.lit_first >> (8 * f)) & 0xFFu) * 0x01010101u);
+                    found |= (x - 0x01010101u) & ~x & 0x80808080u;          // some byte of the word may be that value
+                }
+            }
+            if (!found) may_be_in_literal = false;
+        }
+    }
+    if (may_be_in_literal) {
         // Only the nearest literal-start byte at or before p can own p: a literal
         // never contains another literal's first byte past its own first position.
         int lim = p - static_cast<int>(a.tb.added_max_bytes) + 1;
@@ -721,11 +742,42 @@ GTOK_DEV uint32_t text_at(const Win& w, int p) {   // p in [0, n)
 
 // Lead position of the codepoint before the one starting at p (p itself not a
 // document start).  Returns -1 when p is the first codepoint of its document.
+// (Outside the window a long stretch of stray continuation bytes is stepped over sixteen raw bytes at a
+// time: a byte 10xxxxxx starts no codepoint whether or not an added-token literal holds it.)
+GTOK_DEV bool no_docstart_in16(const EncodeArgs& a, int q);
+GTOK_DEV bool sixteen_continuation_bytes(const EncodeArgs& a, int q) {      // q % 16 == 0; none opens a document
+    if (!no_docstart_in16(a, q)) return false;
+    const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + q);
+    const uint32_t v0 = ldg(p4), v1 = ldg(p4 + 1), v2 = ldg(p4 + 2), v3 = ldg(p4 + 3);
+    return ((v0 & v1 & v2 & v3) & 0x80808080u) == 0x80808080u && ((v0 | v1 | v2 | v3) & 0x40404040u) == 0u;
+}
+// The walks once they have left the window (q < w.vlo, q >= w.vhi): functions of their own, so that the
+// many places that step from a codepoint to its neighbour carry only the look into shared memory.
+GTOK_DEV_NOINLINE int prev_lead_far(const Win& w, int q) {
+    for (;;) {
+        if (q < 0) return -1;
+        if ((q & 15) == 15 && q >= 31 && sixteen_continuation_bytes(*w.a, q - 15)) { q -= 16; continue; }
+        const uint8_t a = attr_global(*w.a, q, w.n);
+        if ((a & A_CLS) != A_CONT) return q;
+        if (a & A_DOC) return -1;
+        --q;
+    }
+}
+GTOK_DEV_NOINLINE int next_lead_far(const Win& w, int q) {
+    for (;;) {
+        if (q >= w.n) return -1;
+        if ((q & 15) == 0 && q + 16 <= w.n && sixteen_continuation_bytes(*w.a, q)) { q += 16; continue; }
+        const uint8_t a = attr_global(*w.a, q, w.n);
+        if (a & A_DOC) return -1;
+        if ((a & A_CLS) != A_CONT) return q;
+        ++q;
+    }
+}
 GTOK_DEV int prev_lead(const Win& w, int p) {
     int q = p - 1;
     for (;;) {
-        if (q < 0) return -1;
-        uint8_t a = attr_at(w, q);
+        if (q < w.vlo || q >= w.vhi) return prev_lead_far(w, q);
+        const uint8_t a = w.sm->attr[q - w.lo];
         if ((a & A_CLS) != A_CONT) return q;
         if (a & A_DOC) return -1;     // stray continuation bytes open the document: dropped
         --q;
@@ -736,8 +788,8 @@ GTOK_DEV int prev_lead(const Win& w, int p) {
 GTOK_DEV int next_lead(const Win& w, int p) {
     int q = p + 1;
     for (;;) {
-        if (q >= w.n) return -1;
-        uint8_t a = attr_at(w, q);
+        if (q < w.vlo || q >= w.vhi) return next_lead_far(w, q);
+        const uint8_t a = w.sm->attr[q - w.lo];
         if (a & A_DOC) return -1;
         if ((a & A_CLS) != A_CONT) return q;
         ++q;
@@ -833,6 +885,44 @@ GTOK_DEV int skip_forward_spaces(const Win& w, int r, uint32_t sp = 0x20u) {
         if (ldg(a.text + r) != sp) return r;
         ++r;
     }
+}
+// r is the lead of a two- or three-byte codepoint that is not part of an added-token literal: first position
+// after the stretch in which that same codepoint is repeated within the document (r itself when it is not
+// repeated, or when its bytes could open a literal).  Raw bytes only: a literal cannot begin inside such a
+// stretch when none of the codepoint's bytes is the first byte of a literal, and one that began before it
+// would hold r too.  (A no-break space or an ideographic space repeated for kilobytes after a newline is
+// walked this way instead of one attribute at a time.)
+GTOK_DEV_NOINLINE int skip_forward_repeat(const Win& w, int r) {
+    const EncodeArgs& a = *w.a;
+    const uint32_t b0 = ldg(a.text + r);
+    const int width = b0 >= 0xE0u ? 3 : 2;
+    if (b0 < 0xC2u || b0 >= 0xF0u || r + width > w.n) return r;
+    const uint32_t b1 = ldg(a.text + r + 1), b2 = width == 3 ? ldg(a.text + r + 2) : 0u;
+    if ((b1 & 0xC0u) != 0x80u || (width == 3 && (b2 & 0xC0u) != 0x80u)) return r;
+    if (((a.tb.lit1_bits[b0 >> 5] >> (b0 & 31)) | (a.tb.lit1_bits[b1 >> 5] >> (b1 & 31)) | (width == 3 ? a.tb.lit1_bits[b2 >> 5] >> (b2 & 31) : 0u)) & 1u) return r;
+    for (int k = 1; k < width; ++k) if (is_docstart_global(a, r + k)) return r;
+    int q = r + width;
+    for (;;) {
+        if (q + width > w.n) return q;
+        if (ldg(a.text + q) != b0 || ldg(a.text + q + 1) != b1 || (width == 3 && ldg(a.text + q + 2) != b2)) return q;
+        for (int k = 0; k < width; ++k) if (is_docstart_global(a, q + k)) return q;
+        q += width;
+    }
+}
+// r is the lead of a whitespace codepoint: where to go on from when that codepoint is repeated (the last
+// of the repeats, so that the caller looks at it and steps on as usual), r itself when it is not, -1 when
+// the repeats run to the end of the document.
+GTOK_DEV_NOINLINE int skip_forward_ws_run(const Win& w, int r) {
+    const uint32_t sp = text_at(w, r);
+    if (sp == 0x20u || sp == 0x09u || sp == 0x0Bu || sp == 0x0Cu) {
+        const int e = skip_forward_spaces(w, r, sp);
+        return e < 0 ? -1 : (e > r ? e - 1 : r);
+    }
+    if (sp >= 0xC2u) {
+        const uint8_t a_r = attr_at(w, r);
+        if ((a_r & A_CLS) == A_S && !(a_r & A_CRLF)) { const int e = skip_forward_repeat(w, r); if (e > r) return e - (sp >= 0xE0u ? 3 : 2); }
+    }
+    return r;
 }
 // q is an ASCII letter outside any added-token literal: position of the first byte before the run of
 // ASCII letters it stands in that is not one, or the letter that opens its document.  Whole words of
@@ -1050,14 +1140,11 @@ GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, boo
             k = p;
             ak = a0;
             for (;;) {
-                if (k + 1 < w.n) {
-                    // runs of one ASCII whitespace byte over raw bytes
-                    const uint32_t sp = text_at(w, k + 1);
-                    if (sp == 0x20u || sp == 0x09u || sp == 0x0Bu || sp == 0x0Cu) {
-                        const int r = skip_forward_spaces(w, k + 1, sp);
-                        if (r < 0) return true;                       // whitespace to the end of the document
-                        if (r > k + 2) { k = r - 1; ak = attr_at(w, k); }
-                    }
+                {
+                    // the same whitespace codepoint again and again: over raw bytes
+                    const int e = skip_forward_ws_run(w, k);
+                    if (e < 0) return true;                           // whitespace to the end of the document
+                    if (e > k) { k = e; ak = attr_at(w, k); }
                 }
                 uint8_t aj;
                 const int j = ds_next(w, k, ak, &aj);
@@ -1169,7 +1256,7 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
                 if (ws != 0xFFFFu || ((w.sm->dsw[i >> 5] >> (i & 31)) & 0xFFFFu) != 0) break;
                 r += 16;
             }
-            if (r >= w.vhi) { r = skip_forward_spaces(w, r); if (r < 0) return true; }
+            if (r >= w.vhi) { r = skip_forward_ws_run(w, r); if (r < 0) return true; }
             uint8_t ar = attr_at(w, r);
             if ((ar & A_CLS) != A_S) return true;
             if (ar & A_CRLF) return false;

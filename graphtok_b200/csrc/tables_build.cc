@@ -218,6 +218,16 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
         const unsigned char c1 = static_cast<unsigned char>(a.content[1]);
         out.lit2_bits[c1 >> 5] |= 1u << (c1 & 31);
     }
+    // the distinct first bytes, when there are at most four of them (the usual case: '<'), packed one per byte
+    {
+        out.lit_first_n = 0;
+        out.lit_first = 0;
+        for (int b = 0; b < 256; ++b)
+            if ((out.lit1_bits[b >> 5] >> (b & 31)) & 1u) {
+                if (out.lit_first_n < 4) out.lit_first |= static_cast<uint32_t>(b) << (8 * out.lit_first_n);
+                ++out.lit_first_n;
+            }
+    }
     // the same literals as a hash table (see device_tables.h)
     {
         std::vector<uint32_t> lens;

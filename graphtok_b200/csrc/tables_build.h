@@ -26,7 +26,7 @@ struct HostTables {
     uint32_t lit1_bits[8] = {}, lit2_bits[8] = {}, lit_single = 0;
     std::vector<LitSlot> littab;
     uint32_t lit_n_lens = 0, lit_lens[kLitLens] = {};
-    uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0, added_alpha_end = 0;
+    uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0, added_alpha_end = 0, lit_first = 0, lit_first_n = 0;
 };
 
 // Returns false (with a reason) when a table cannot be built within its probe
@@ -51,6 +51,8 @@ inline void fill_table_scalars(const HostTables& ht, DeviceTables& tb) {
     tb.monotone = ht.monotone;
     tb.added_ws = ht.added_ws;
     tb.added_alpha_end = ht.added_alpha_end;
+    tb.lit_first = ht.lit_first;
+    tb.lit_first_n = ht.lit_first_n;
 }
 
 // Packs up to 15 bytes into a word-table key.

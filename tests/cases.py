@@ -33,7 +33,11 @@ def fuzz_strings(seed, special, per_pool=300, lengths=(1, 2, 3, 5, 8, 13, 40, 12
 def malformed_bytes(seed, count=300):
     rng = random.Random(seed)
     alphabet = [0x61, 0x20, 0x80, 0xBF, 0xC3, 0xE4, 0xF0, 0xA9, 0x0A, 0x27, 0x73, 0x31, 0xFF, 0xC5, 0x2E]
-    return [bytes(rng.choice(alphabet) for _ in range(rng.randint(1, 60))) for _ in range(count)]
+    out = [bytes(rng.choice(alphabet) for _ in range(rng.randint(1, 60))) for _ in range(count)]
+    # stray continuation bytes for longer than the pre-tokenization window, before and after other text
+    out += [b"a" + b"\x80" * 9000 + b"b c", b"\xbf" * 9000 + b"'s", b"a \xe4" + b"\x80\xbf" * 4500 + b" 12", b"x\n" + b"\x80" * 9000 + b"\n y",
+            b"a" + b"\x80" * 17 + b"b" + b"\xa9" * 8200 + b"1234"]
+    return out
 
 
 def tile_crossers(special):
@@ -71,6 +75,8 @@ def tile_crossers(special):
     out.append("k\n" + " " * 5000 + "\t" + " " * 5000 + "\n\nq")
     out.append("k\n" + "\t" * 9000 + "\nq")
     out.append("k\n" + "\t" * 9000 + "q")
+    out.append("k\n" + "\u00a0" * 5000 + "q")
+    out.append("k\n" + "\u3000\t " * 3000 + "\nq")
     out.append("k!" + "\n" * 9000 + " q")
     out.append("\n" * 9000 + " q")
     # ASCII letters behind a punctuation mark, or not, for longer than the window, then another kind of letter
