@@ -2007,9 +2007,15 @@ GTOK_DEV uint32_t arena_at(uint32_t w4, uint32_t stride, uint32_t r) { return (r
 // of each group of four slots (same interleaved layout, so four groups are one 128-bit load): a
 // step reads a quarter of what a pass over all slots would and then puts right the three groups the
 // merge touched.  The search is half of what a step costs beside its one memory round trip.
-template <class Put>
+// `hist` is told whenever the pre-token's first or last symbol changes (the new symbol and the rank of
+// the merge that made it): what pieces_word needs to know about a piece's two ends.
+struct NoEdgeHistory {
+    GTOK_DEV void first(uint32_t, uint32_t) {}
+    GTOK_DEV void last(uint32_t, uint32_t) {}
+};
+template <class Put, class Hist = NoEdgeHistory>
 GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint16_t* lnk, uint32_t* gm, uint32_t w4, uint32_t stride,
-                            uint32_t len, Put put) {
+                            uint32_t len, Put put, Hist hist = Hist()) {
     // lnk[slot] = prev << 8 | next (slot numbers within the pre-token, 0xFF = none) keeps the
     // live symbols chained; slots past `len` in the last group hold no rank.
     const uint32_t groups = (len + 3u) >> 2;
@@ -2060,6 +2066,8 @@ GTOK_DEV uint32_t bpe_arena(const EncodeArgs& a, uint32_t* ids, uint32_t* rk, ui
         const uint32_t k = lnk[xj] & 0xFFu;
         const uint32_t merged = nw[xb];
         ids[xb] = merged;
+        if (p == 0xFFu) hist.first(merged, best >> 6);
+        if (k == 0xFFu) hist.last(merged, best >> 6);
         rk[xj] = kNoRank;
         lnk[xb] = static_cast<uint16_t>((p << 8) | k);
         const uint32_t xk = arena_at(w4, stride, k & 63u), xp = arena_at(w4, stride, p & 63u);
@@ -2480,6 +2488,55 @@ GTOK_DEV void put_id(const EncodeArgs& a, uint32_t g, uint32_t k, uint32_t id) {
     else a.ovf[static_cast<size_t>(tile) * kTokExtra + (g + k - t1)] = id;
 }
 
+// The first two phases of a batch over the block's arena (sm.word holds the batch's entries, position |
+// length << 32, 0 = none): all threads fetch the bytes, a slot each, so that the loads overlap ...
+constexpr uint32_t kPendingRank = 0xFFFFFFFDu;
+template <class Blk>
+GTOK_DEV void arena_fill(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t* ids, uint32_t* rk, uint32_t batch, uint32_t max_len) {
+    const uint32_t slots = batch * max_len;
+    blk.par([&](int tid) {
+        for (uint32_t x = tid; x < slots; x += kThreads) {
+            const uint32_t w = (x >> 2) % batch, r = ((x >> 2) / batch) * 4u + (x & 3u);
+            const unsigned long long wv = sm.word[w];
+            const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
+            if (r >= ((len + 3u) & ~3u)) continue;                  // beyond the pre-token's last group: never read
+            if (r >= len) { rk[x] = kNoRank; continue; }            // padding of the last group
+            const uint32_t bt = ldg(a.text + g + r);
+            sm.rawb[w * max_len + r] = static_cast<uint8_t>(bt);
+            ids[x] = sm.b2i[bt];
+            rk[x] = (r + 1 < len) ? kPendingRank : kNoRank;
+            sm.lnk[x] = static_cast<uint16_t>(((r ? r - 1 : 0xFFu) << 8) | (r + 1 < len ? r + 1 : 0xFFu));
+        }
+    });
+}
+// ... and probe all adjacent pairs, a slot each; then the lowest key of every group of four slots
+// (pre-tokens of more than 16 bytes search through these).
+template <class Blk>
+GTOK_DEV void arena_pairs(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t* ids, uint32_t* rk, uint32_t* nw, uint32_t batch, uint32_t max_len) {
+    const uint32_t slots = batch * max_len, stride = batch * 4u;
+    blk.par([&](int tid) {
+        for (uint32_t x = tid; x < slots; x += kThreads) {
+            const uint32_t w = (x >> 2) % batch, r = ((x >> 2) / batch) * 4u + (x & 3u);
+            const uint32_t len = static_cast<uint32_t>(sm.word[w] >> 32);
+            if (r + 1 >= len || rk[x] != kPendingRank) continue;
+            RankRes q = probe_rule(a.tb, ids[x], ids[arena_at(4u * w, stride, r + 1)]);
+            rk[x] = rank_key(q.rank, r);
+            nw[x] = q.res;
+        }
+    });
+    if (max_len > 16u) {
+        blk.par([&](int tid) {
+            for (uint32_t i = tid; i < slots / 4u; i += kThreads) {
+                const uint32_t w = (i >> 2) % batch, g = ((i >> 2) / batch) * 4u + (i & 3u);
+                const uint32_t len = static_cast<uint32_t>(sm.word[w] >> 32);
+                uint32_t m = kNoRank;
+                if (g * 4u < len) for (uint32_t r = g * 4u; r < g * 4u + 4u; ++r) { const uint32_t v = rk[arena_at(4u * w, stride, r)]; if (v < m) m = v; }
+                sm.gmin[i] = m;
+            }
+        });
+    }
+}
+
 // ---- kernel 3a: one batch of unknown pre-tokens (2..64 bytes), one per thread ----------
 // All threads fetch the batch's bytes into the block's arena and probe the initial pairs, a
 // slot each; then the thread that owns a pre-token merges it (lowest rank first) and stores
@@ -2489,7 +2546,6 @@ template <class Blk>
 GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss,
                          uint32_t batch, uint32_t max_len, uint32_t take) {
     const DeviceTables& tb = a.tb;
-    constexpr uint32_t kPending = 0xFFFFFFFDu;
     uint32_t* ids = sm.ws;
     uint32_t* rk = sm.ws + kArenaSyms;
     uint32_t* nw = sm.ws + 2 * kArenaSyms;
@@ -2499,7 +2555,6 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     const uint32_t n_take = n_miss - first < take ? n_miss - first : take;
     const bool filtered = take > batch;
     const uint32_t stride = batch * 4u;                 // arena elements from one group of a pre-token to its next
-    const uint32_t slots = batch * max_len;
     auto mark = [&](int slot) {
         if (!a.phase_clk) return;
         blk.par([&](int tid) {
@@ -2583,21 +2638,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
                            : list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];   // dir = -1: a list that grows downwards
     });
     mark(16);
-    // all threads: fetch the bytes, one slot each, so the loads overlap
-    blk.par([&](int tid) {
-        for (uint32_t x = tid; x < slots; x += kThreads) {
-            const uint32_t w = (x >> 2) % batch, r = ((x >> 2) / batch) * 4u + (x & 3u);
-            const unsigned long long wv = sm.word[w];
-            const uint32_t g = static_cast<uint32_t>(wv), len = static_cast<uint32_t>(wv >> 32);
-            if (r >= ((len + 3u) & ~3u)) continue;                  // beyond the pre-token's last group: never read
-            if (r >= len) { rk[x] = kNoRank; continue; }            // padding of the last group
-            const uint32_t bt = ldg(a.text + g + r);
-            sm.rawb[w * max_len + r] = static_cast<uint8_t>(bt);
-            ids[x] = sm.b2i[bt];
-            rk[x] = (r + 1 < len) ? kPending : kNoRank;
-            sm.lnk[x] = static_cast<uint16_t>(((r ? r - 1 : 0xFFu) << 8) | (r + 1 < len ? r + 1 : 0xFFu));
-        }
-    });
+    arena_fill(blk, a, sm, ids, rk, batch, max_len);
     mark(17);
     // owner: a pre-token of 16 bytes or more that is itself in the vocabulary (ignore_merges)
     if (!filtered && tb.ignore_merges && max_len > static_cast<uint32_t>(kWordKeyMax)) {
@@ -2614,28 +2655,7 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
         });
     }
     mark(18);
-    blk.par([&](int tid) {
-        for (uint32_t x = tid; x < slots; x += kThreads) {
-            const uint32_t w = (x >> 2) % batch, r = ((x >> 2) / batch) * 4u + (x & 3u);
-            const uint32_t len = static_cast<uint32_t>(sm.word[w] >> 32);
-            if (r + 1 >= len || rk[x] != kPending) continue;
-            RankRes q = probe_rule(tb, ids[x], ids[arena_at(4u * w, stride, r + 1)]);
-            rk[x] = rank_key(q.rank, r);
-            nw[x] = q.res;
-        }
-    });
-    // lowest key of every group of four slots (pre-tokens of more than 16 bytes search through these)
-    if (max_len > 16u) {
-        blk.par([&](int tid) {
-            for (uint32_t i = tid; i < slots / 4u; i += kThreads) {
-                const uint32_t w = (i >> 2) % batch, g = ((i >> 2) / batch) * 4u + (i & 3u);
-                const uint32_t len = static_cast<uint32_t>(sm.word[w] >> 32);
-                uint32_t m = kNoRank;
-                if (g * 4u < len) for (uint32_t r = g * 4u; r < g * 4u + 4u; ++r) { const uint32_t v = rk[arena_at(4u * w, stride, r)]; if (v < m) m = v; }
-                sm.gmin[i] = m;
-            }
-        });
-    }
+    arena_pairs(blk, a, sm, ids, rk, nw, batch, max_len);
     mark(19);
     blk.par([&](int tid) {
         if (static_cast<uint32_t>(tid) >= n_here) return;
@@ -2765,6 +2785,161 @@ GTOK_DEV bool rle_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li,
 }
 
 // ---- kernel 3b: one pre-token longer than 64 bytes, by the whole block ------------------
+// ---- long pre-tokens in pieces ---------------------------------------------------------------
+// A pre-token of thousands of symbols that is no handful of runs is cut into pieces of at most 64 bytes
+// that are merged like ordinary unknown pre-tokens, a thread each, 48 to a batch -- instead of rounds over
+// all of its symbols, one round per rank that occurs.  What makes that exact: with a monotone vocabulary
+// the greedy loop applies its merges in order of rank, so a cut is a token boundary of the whole pre-token
+// if and only if the pair across it never gets its turn: at every moment, the rule joining the symbol left
+// of the cut to the symbol right of it (if there is one) has a rank at or above the rank at which the left
+// symbol next merges leftwards, or above the rank at which the right symbol next merges rightwards.  Both
+// symbols' histories come out of merging the two pieces independently (each piece's two edges are recorded
+// as it is merged), and if every cut passes, the pieces' ids one after the other are the pre-token's ids.
+//   pass 0   windows of 64 bytes around every 40th byte are merged; the token boundary nearest the middle
+//            of each (at most 12 bytes away) becomes a cut -- a true boundary almost always, far from the
+//            window's own ends as it is
+//   pass 1   the pieces between the cuts are merged, ids and edge histories to the pre-token's workspace
+//   check    every cut, a thread each; a cut that fails, a piece that comes out too long, a history that
+//            outgrows its room: nothing has been written that matters, the caller takes the general path
+//   commit   piece totals summed, ids moved together, counts published
+// Workspace (the three per-byte arrays of the pre-token, relative to its start): gwork_rk holds the cuts and,
+// behind them, 32 words per piece {id count, changes of the first symbol, changes of the last symbol, then up
+// to seven (id, rank) pairs for each}; gwork_nw holds piece k's ids at its own bytes; gstage the result.
+constexpr uint32_t kPieceStep = 40, kPieceHalf = 32, kPieceDev = 12, kPieceMax = 64, kPieceHist = 7, kPieceRec = 32;
+constexpr uint32_t kPieceMinLen = 512;         // shorter long pre-tokens stay with the general path
+
+struct PieceHistory {
+    uint32_t* rec;          // the piece's 32-word record
+    GTOK_DEV void first(uint32_t id, uint32_t rank) {
+        const uint32_t k = rec[1];
+        if (k < kPieceHist) { rec[3 + 2 * k] = id; rec[4 + 2 * k] = rank; }
+        rec[1] = k + 1;
+    }
+    GTOK_DEV void last(uint32_t id, uint32_t rank) {
+        const uint32_t k = rec[2];
+        if (k < kPieceHist) { rec[3 + 2 * kPieceHist + 2 * k] = id; rec[4 + 2 * kPieceHist + 2 * k] = rank; }
+        rec[2] = k + 1;
+    }
+};
+
+template <class Blk>
+GTOK_DEV bool pieces_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li, uint32_t g, uint32_t len) {
+    const DeviceTables& tb = a.tb;
+    // cuts 1..K at about every kPieceStep bytes; cut 0 = 0, cut K + 1 = len
+    const uint32_t K = (len - 12u) / kPieceStep;                      // the last piece stays within kPieceMax however its cut falls
+    uint32_t* cuts = a.gwork_rk + g;
+    const uint32_t rec0 = (K + 2u + 3u) & ~3u;
+    if (rec0 + (K + 1u) * kPieceRec > len) return false;              // (only for pre-tokens far shorter than kPieceMinLen)
+    uint32_t* recs = a.gwork_rk + g + rec0;
+    uint32_t* piece_ids = a.gwork_nw + g;
+    uint32_t* ids = sm.ws;
+    uint32_t* rk = sm.ws + kArenaSyms;
+    uint32_t* nw = sm.ws + 2 * kArenaSyms;
+    constexpr uint32_t batch = kMedBatchA, max_len = kMedWordMax, stride = batch * 4u;
+    static_assert(kPieceMax <= static_cast<uint32_t>(kMedWordMax) && 2 * kPieceHalf <= kPieceMax, "a piece is one arena pre-token");
+    blk.par([&](int tid) { if (tid == 0) { sm.ctr[C_TMP2] = 0; cuts[0] = 0; cuts[K + 1] = len; } });
+    // ---- pass 0: a cut near every kPieceStep-th byte ----
+    for (uint32_t first = 0; first < K; first += batch) {
+        const uint32_t n_here = K - first < batch ? K - first : batch;
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= batch) return;
+            unsigned long long wv = 0ull;
+            if (static_cast<uint32_t>(tid) < n_here) {
+                const uint32_t c = kPieceStep * (first + tid + 1u);
+                const uint32_t lo = c - kPieceHalf, hi = c + kPieceHalf < len ? c + kPieceHalf : len;      // c >= kPieceStep > kPieceHalf
+                wv = static_cast<unsigned long long>(g + lo) | (static_cast<unsigned long long>(hi - lo) << 32);
+            }
+            sm.word[tid] = wv;
+        });
+        arena_fill(blk, a, sm, ids, rk, batch, max_len);
+        arena_pairs(blk, a, sm, ids, rk, nw, batch, max_len);
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= n_here) return;
+            const uint32_t wlen = static_cast<uint32_t>(sm.word[tid] >> 32);
+            bpe_arena(a, ids, rk, nw, sm.lnk, sm.gmin, 4u * tid, stride, wlen, [](uint32_t, uint32_t) {});
+            // the symbols left are the window's tokens; their first slots are the byte offsets where tokens begin
+            uint32_t best = 0, best_dev = 0xFFFFFFFFu;
+            for (uint32_t i = sm.lnk[arena_at(4u * tid, stride, 0)] & 0xFFu; i != 0xFFu; i = sm.lnk[arena_at(4u * tid, stride, i)] & 0xFFu) {
+                const uint32_t dev = i > kPieceHalf ? i - kPieceHalf : kPieceHalf - i;
+                if (dev < best_dev) { best_dev = dev; best = i; }
+            }
+            if (best_dev > kPieceDev) { sm.ctr[C_TMP2] = 1; return; }
+            cuts[first + tid + 1u] = kPieceStep * (first + tid + 1u) - kPieceHalf + best;
+        });
+        if (sm.ctr[C_TMP2]) return false;
+    }
+    // ---- pass 1: the pieces ----
+    for (uint32_t first = 0; first <= K; first += batch) {
+        const uint32_t n_here = K + 1u - first < batch ? K + 1u - first : batch;
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= batch) return;
+            unsigned long long wv = 0ull;
+            if (static_cast<uint32_t>(tid) < n_here) {
+                const uint32_t lo = cuts[first + tid], hi = cuts[first + tid + 1u];
+                if (hi <= lo || hi - lo > kPieceMax) sm.ctr[C_TMP2] = 1;
+                else wv = static_cast<unsigned long long>(g + lo) | (static_cast<unsigned long long>(hi - lo) << 32);
+            }
+            sm.word[tid] = wv;
+        });
+        if (sm.ctr[C_TMP2]) return false;
+        arena_fill(blk, a, sm, ids, rk, batch, max_len);
+        arena_pairs(blk, a, sm, ids, rk, nw, batch, max_len);
+        blk.par([&](int tid) {
+            if (static_cast<uint32_t>(tid) >= n_here) return;
+            const unsigned long long wv = sm.word[tid];
+            const uint32_t lo = static_cast<uint32_t>(wv) - g, plen = static_cast<uint32_t>(wv >> 32);
+            uint32_t* rec = recs + static_cast<size_t>(first + tid) * kPieceRec;
+            rec[1] = 0; rec[2] = 0;
+            PieceHistory hist{rec};
+            rec[0] = bpe_arena(a, ids, rk, nw, sm.lnk, sm.gmin, 4u * tid, stride, plen, [&](uint32_t k, uint32_t id) { piece_ids[lo + k] = id; }, hist);
+            if (rec[1] > kPieceHist || rec[2] > kPieceHist) sm.ctr[C_TMP2] = 1;
+        });
+        if (sm.ctr[C_TMP2]) return false;
+    }
+    // ---- check every cut ----
+    blk.par([&](int tid) {
+        for (uint32_t k = 1u + tid; k <= K; k += kThreads) {
+            const uint32_t* L = recs + static_cast<size_t>(k - 1u) * kPieceRec;      // the piece left of cut k: its last symbol
+            const uint32_t* R = recs + static_cast<size_t>(k) * kPieceRec;           // the piece right of it: its first symbol
+            const uint32_t nl = L[2], nr = R[1];
+            uint32_t sl = sm.b2i[ldg(a.text + g + cuts[k] - 1u)], sr = sm.b2i[ldg(a.text + g + cuts[k])];
+            uint32_t i = 0, j = 0;
+            for (;;) {
+                const uint32_t tl = i < nl ? L[4 + 2 * kPieceHist + 2 * i] : 0xFFFFFFFFu;      // rank at which the left symbol next changes
+                const uint32_t tr = j < nr ? R[4 + 2 * j] : 0xFFFFFFFFu;
+                const RankRes q = probe_rule(tb, sl, sr);
+                if (q.rank != kNoRank && q.rank < tl && q.rank <= tr) { sm.ctr[C_TMP2] = 1; break; }   // the pair across the cut would merge
+                if (i >= nl && j >= nr) break;
+                // the side that changes first (on equal ranks the left one: its pair lies further left)
+                if (tl <= tr) { sl = L[3 + 2 * kPieceHist + 2 * i]; ++i; }
+                else { sr = R[3 + 2 * j]; ++j; }
+            }
+        }
+    });
+    if (sm.ctr[C_TMP2]) return false;
+    // ---- commit: where each piece's ids go, the ids, the counts ----
+    // (piece totals replaced by their running sum, 256 pieces at a time)
+    uint32_t total = 0;
+    uint32_t* scan = sm.ws;                     // (the arena is free again)
+    for (uint32_t base = 0; base <= K; base += kThreads) {
+        blk.par([&](int tid) { const uint32_t k = base + tid; scan[tid] = k <= K ? recs[static_cast<size_t>(k) * kPieceRec] : 0u; });
+        uint32_t sum = 0;
+        blk.excl_scan(scan, &sum);
+        blk.par([&](int tid) { const uint32_t k = base + tid; if (k <= K) recs[static_cast<size_t>(k) * kPieceRec + 1] = total + scan[tid]; });
+        total += sum;
+    }
+    blk.par([&](int tid) {
+        // a thread per piece copies its few ids
+        for (uint32_t k = tid; k <= K; k += kThreads) {
+            const uint32_t* rec = recs + static_cast<size_t>(k) * kPieceRec;
+            const uint32_t cnt = rec[0], to = rec[1], from = cuts[k];
+            for (uint32_t i = 0; i < cnt; ++i) a.gstage[g + to + i] = piece_ids[from + i];
+        }
+    });
+    blk.par([&](int tid) { if (tid == 0) { a.glong_cnt[li] = total; global_add(a.tile_tok + g / kTile, total); } });
+    return true;
+}
+
 template <class Blk>
 GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li) {
     const uint32_t n = ldg(a.meta);
@@ -2786,6 +2961,7 @@ GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li
         return;
     }
     if (tb.monotone && rle_word(blk, a, sm, li, g, len)) return;
+    if (tb.monotone && len >= kPieceMinLen && pieces_word(blk, a, sm, li, g, len)) return;
     // Workspace: shared memory when the pre-token fits beside the team's own scratch,
     // else the per-byte global arrays (disjoint per pre-token).
     constexpr uint32_t kScratch = 6 * kThreads + 16;                 // team scratch + keep buffer

@@ -89,6 +89,14 @@ def tile_crossers(special):
     out.append("w " + "=" * 700 + "-" * 65 + "=" * 2 + "~" * 9000 + " t")
     out.append("w" + (" " * 70 + "\t" * 70) * 3 + "t")
     out.append("w " + "ab" * 40 + " " + "abc" * 2000 + " t")
+    # long pre-tokens that are no handful of runs: merged in pieces of at most 64 bytes whose cuts are checked
+    # (random text over small and large alphabets), or by the general path when a cut fails (periodic text)
+    rng = random.Random(4242)
+    for alphabet, length in (("abcdefghijklmnopqrstuvwxyz", 20000), ("ACGT", 9000), ("etaoinshr", 3000), ("ab", 700), ("theinandofto", 5000),
+                             ("中文日本語的一是不了人我在有他这为之大来以个", 2500), ("éèêàùç", 900), ("!@#$%^&*()-=+", 4000)):
+        out.append("p " + "".join(rng.choice(alphabet) for _ in range(length)) + " q")
+    out.append("p " + "the" * 600 + "in" * 500 + " q")
+    out.append("p " + "thequickbrownfox" * 200 + " q")
     out.append("é" * 3000 + "日" * 2000 + "\U0001F600" * 500)
     out.append("z" * (3 * TILE + 17))
     out.append("9" * (2 * TILE + 5) + " " + "8" * 100)
