@@ -2806,7 +2806,7 @@ GTOK_DEV bool rle_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li,
 // behind them, 32 words per piece {id count, changes of the first symbol, changes of the last symbol, then up
 // to seven (id, rank) pairs for each}; gwork_nw holds piece k's ids at its own bytes; gstage the result.
 constexpr uint32_t kPieceStep = 40, kPieceHalf = 32, kPieceDev = 12, kPieceMax = 64, kPieceHist = 7, kPieceRec = 32;
-constexpr uint32_t kPieceMinLen = 512;         // shorter long pre-tokens stay with the general path
+constexpr uint32_t kPieceMinLen = 256;         // shorter long pre-tokens stay with the general path
 
 struct PieceHistory {
     uint32_t* rec;          // the piece's 32-word record
