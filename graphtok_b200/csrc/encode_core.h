@@ -448,6 +448,18 @@ GTOK_DEV bool is_docstart_global(const EncodeArgs& a, int p) {
     if (!a.docmask) return false;
     return (ldg(a.docmask + (p >> 5)) >> (p & 31)) & 1u;
 }
+// The two pointers the raw-byte walks need, by value: a walk that runs in a function of its own would otherwise
+// fetch them through the argument block's address at every step.
+struct RawText {
+    const uint8_t* text;
+    const uint32_t* docmask;
+};
+GTOK_DEV RawText raw_text(const EncodeArgs& a) { return RawText{a.text, a.docmask}; }
+GTOK_DEV bool raw_docstart(RawText t, int p) {
+    if (p == 0) return true;
+    if (!t.docmask) return false;
+    return (ldg(t.docmask + (p >> 5)) >> (p & 31)) & 1u;
+}
 
 // ==================================================================================
 //                                   PRE-TOKENIZATION
@@ -471,7 +483,7 @@ struct PretokSmem {
     alignas(16) uint8_t txt[kPWin + 16];
     alignas(16) uint8_t attr[kPWin + 16];
     alignas(16) uint8_t oh[kPWin + 16];       // one-hot class + flags per byte (see kOh*)
-    alignas(4) uint16_t plane[kPlanes][kPWin / 16 + 4];   // bit planes of the window, 16 bytes per entry
+    alignas(8) uint16_t plane[kPlanes][kPWin / 16 + 4];   // bit planes of the window, 16 bytes per entry
     uint32_t lut[256];                       // byte -> attr | one-hot << 8 | (opens an added-token literal) << 16: ASCII as classified, continuation bytes, lead bytes as "other" until decoded
     uint16_t cand16[kPWin / 16 + 4];          // per 16-byte chunk: bytes that open an added-token literal
     alignas(16) uint16_t ucs1[kUcStage1Bmp]; // the class table's first stage for the BMP and its whole second stage, copied once per block
@@ -487,6 +499,7 @@ struct PretokSmem {
     uint32_t sum_has[32], sum_cnt[32], lane_last[32], lane_firstn[32];
     uint32_t scan[kThreads];
     uint32_t misc[8];
+    int far_run[4];                          // runs that leave the window, found by the whole block before the rules are applied: {position the forward walk starts at, its answer, position the backward walk starts at, its answer}
     unsigned long long clk_last;
 };
 
@@ -744,19 +757,20 @@ GTOK_DEV uint32_t text_at(const Win& w, int p) {   // p in [0, n)
 // document start).  Returns -1 when p is the first codepoint of its document.
 // (Outside the window a long stretch of stray continuation bytes is stepped over sixteen raw bytes at a
 // time: a byte 10xxxxxx starts no codepoint whether or not an added-token literal holds it.)
-GTOK_DEV bool no_docstart_in16(const EncodeArgs& a, int q);
-GTOK_DEV bool sixteen_continuation_bytes(const EncodeArgs& a, int q) {      // q % 16 == 0; none opens a document
-    if (!no_docstart_in16(a, q)) return false;
-    const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + q);
+GTOK_DEV bool no_docstart_in16(RawText t, int q);
+GTOK_DEV bool sixteen_continuation_bytes(RawText t, int q) {      // q % 16 == 0; none opens a document
+    if (!no_docstart_in16(t, q)) return false;
+    const uint32_t* p4 = reinterpret_cast<const uint32_t*>(t.text + q);
     const uint32_t v0 = ldg(p4), v1 = ldg(p4 + 1), v2 = ldg(p4 + 2), v3 = ldg(p4 + 3);
     return ((v0 & v1 & v2 & v3) & 0x80808080u) == 0x80808080u && ((v0 | v1 | v2 | v3) & 0x40404040u) == 0u;
 }
 // The walks once they have left the window (q < w.vlo, q >= w.vhi): functions of their own, so that the
 // many places that step from a codepoint to its neighbour carry only the look into shared memory.
 GTOK_DEV_NOINLINE int prev_lead_far(const Win& w, int q) {
+    const RawText t = raw_text(*w.a);
     for (;;) {
         if (q < 0) return -1;
-        if ((q & 15) == 15 && q >= 31 && sixteen_continuation_bytes(*w.a, q - 15)) { q -= 16; continue; }
+        if ((q & 15) == 15 && q >= 31 && sixteen_continuation_bytes(t, q - 15)) { q -= 16; continue; }
         const uint8_t a = attr_global(*w.a, q, w.n);
         if ((a & A_CLS) != A_CONT) return q;
         if (a & A_DOC) return -1;
@@ -764,9 +778,11 @@ GTOK_DEV_NOINLINE int prev_lead_far(const Win& w, int q) {
     }
 }
 GTOK_DEV_NOINLINE int next_lead_far(const Win& w, int q) {
+    const RawText t = raw_text(*w.a);
+    const int n = w.n;
     for (;;) {
-        if (q >= w.n) return -1;
-        if ((q & 15) == 0 && q + 16 <= w.n && sixteen_continuation_bytes(*w.a, q)) { q += 16; continue; }
+        if (q >= n) return -1;
+        if ((q & 15) == 0 && q + 16 <= n && sixteen_continuation_bytes(t, q)) { q += 16; continue; }
         const uint8_t a = attr_global(*w.a, q, w.n);
         if (a & A_DOC) return -1;
         if ((a & A_CLS) != A_CONT) return q;
@@ -813,17 +829,18 @@ GTOK_DEV bool all_bytes_in(uint32_t v, uint32_t x, uint32_t y) {   // every byte
     for (int k = 0; k < 4; ++k) { uint32_t b = (v >> (8 * k)) & 0xFFu; if (b != x && b != y) return false; }
     return true;
 }
-GTOK_DEV bool no_docstart_in16(const EncodeArgs& a, int q) {    // q..q+15 within one mask word (q % 16 == 0)
+GTOK_DEV bool no_docstart_in16(RawText t, int q) {    // q..q+15 within one mask word (q % 16 == 0)
     if (q == 0) return false;
-    if (!a.docmask) return true;
-    return ((ldg(a.docmask + (q >> 5)) >> (q & 31)) & 0xFFFFu) == 0;
+    if (!t.docmask) return true;
+    return ((ldg(t.docmask + (q >> 5)) >> (q & 31)) & 0xFFFFu) == 0;
 }
+GTOK_DEV bool no_docstart_in16(const EncodeArgs& a, int q) { return no_docstart_in16(raw_text(a), q); }
 // True when the 128 bytes at q (q % 128 == 0) repeat one 4-byte pattern whose bytes are all x
 // or y (CR/LF stretches: x = 0x0A, y = 0x0D; spaces: x = y = 0x20) and none of them opens a
 // document.  The eight loads are independent and the test is two operations per word, so a long
 // run is walked at about one memory round trip per 128 bytes.  (A stretch that mixes its two
 // bytes irregularly is not recognised here and is walked 16 bytes at a time.)
-GTOK_DEV bool run_of_128(const EncodeArgs& a, int q, uint32_t x, uint32_t y) {
+GTOK_DEV bool run_of_128(RawText a, int q, uint32_t x, uint32_t y) {
     if (a.docmask) {
         const uint32_t* dm = a.docmask + (q >> 5);
         if (ldg(dm) | ldg(dm + 1) | ldg(dm + 2) | ldg(dm + 3)) return false;
@@ -851,19 +868,22 @@ GTOK_DEV bool run_of_128(const EncodeArgs& a, int q, uint32_t x, uint32_t y) {
     return all_bytes_in(all_and, x, y);
 }
 GTOK_DEV int skip_back_newlines(const Win& w, int q) {
-    const EncodeArgs& a = *w.a;
-    if (a.tb.added_ws) return q;
+    if (w.a->tb.added_ws) return q;
+    const RawText a = raw_text(*w.a);
+    const int far = w.sm->far_run[2];              // from here on the whole block has looked already (far_runs); -2: nowhere
     for (;;) {
         if (q < 0) return q;
-        if ((q & 127) == 127 && q >= 255 && run_of_128(a, q - 127, 0x0Au, 0x0Du)) { q -= 128; continue; }
-        if ((q & 15) == 15 && q >= 31 && no_docstart_in16(a, q - 15)) {
+        if (q == far) return w.sm->far_run[3];
+        const bool over128 = q > far && q - 128 < far, over16 = q > far && q - 16 < far;      // never step over that place
+        if ((q & 127) == 127 && q >= 255 && !over128 && run_of_128(a, q - 127, 0x0Au, 0x0Du)) { q -= 128; continue; }
+        if ((q & 15) == 15 && q >= 31 && !over16 && no_docstart_in16(a, q - 15)) {
             const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + q - 15);
             uint32_t v0 = ldg(p4), v1 = ldg(p4 + 1), v2 = ldg(p4 + 2), v3 = ldg(p4 + 3);
             if (all_bytes_in(v0, 0x0Au, 0x0Du) && all_bytes_in(v1, 0x0Au, 0x0Du) && all_bytes_in(v2, 0x0Au, 0x0Du) && all_bytes_in(v3, 0x0Au, 0x0Du)) { q -= 16; continue; }
         }
         uint32_t b = ldg(a.text + q);
         if (b != 0x0Au && b != 0x0Du) return q;
-        if (is_docstart_global(a, q)) return q;
+        if (raw_docstart(a, q)) return q;
         --q;
     }
 }
@@ -871,17 +891,21 @@ GTOK_DEV int skip_back_newlines(const Win& w, int q) {
 // plain space, or another one-byte ASCII whitespace character) of the same document, or -1 at the
 // end of the document.
 GTOK_DEV int skip_forward_spaces(const Win& w, int r, uint32_t sp = 0x20u) {
-    const EncodeArgs& a = *w.a;
-    if (a.tb.added_ws) return r;
+    if (w.a->tb.added_ws) return r;
+    const RawText a = raw_text(*w.a);
+    const int n = w.n;
     const uint32_t sp4 = sp * 0x01010101u;
+    const int far = w.sm->far_run[0];              // from here on the whole block has looked already (far_runs); -2: nowhere
     for (;;) {
-        if (r >= w.n) return -1;
-        if ((r & 127) == 0 && r > 0 && r + 128 <= w.n && run_of_128(a, r, sp, sp)) { r += 128; continue; }
-        if ((r & 15) == 0 && r + 16 <= w.n && no_docstart_in16(a, r)) {
+        if (r >= n) return -1;
+        if (r == far) return w.sm->far_run[1];
+        const bool over128 = r < far && r + 128 > far, over16 = r < far && r + 16 > far;          // never step over that place
+        if ((r & 127) == 0 && r > 0 && r + 128 <= n && !over128 && run_of_128(a, r, sp, sp)) { r += 128; continue; }
+        if ((r & 15) == 0 && r + 16 <= n && !over16 && no_docstart_in16(a, r)) {
             const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + r);
             if (ldg(p4) == sp4 && ldg(p4 + 1) == sp4 && ldg(p4 + 2) == sp4 && ldg(p4 + 3) == sp4) { r += 16; continue; }
         }
-        if (is_docstart_global(a, r)) return -1;
+        if (raw_docstart(a, r)) return -1;
         if (ldg(a.text + r) != sp) return r;
         ++r;
     }
@@ -893,19 +917,21 @@ GTOK_DEV int skip_forward_spaces(const Win& w, int r, uint32_t sp = 0x20u) {
 // would hold r too.  (A no-break space or an ideographic space repeated for kilobytes after a newline is
 // walked this way instead of one attribute at a time.)
 GTOK_DEV_NOINLINE int skip_forward_repeat(const Win& w, int r) {
-    const EncodeArgs& a = *w.a;
+    const EncodeArgs& args = *w.a;
+    const RawText a = raw_text(args);
+    const int n = w.n;
     const uint32_t b0 = ldg(a.text + r);
     const int width = b0 >= 0xE0u ? 3 : 2;
-    if (b0 < 0xC2u || b0 >= 0xF0u || r + width > w.n) return r;
+    if (b0 < 0xC2u || b0 >= 0xF0u || r + width > n) return r;
     const uint32_t b1 = ldg(a.text + r + 1), b2 = width == 3 ? ldg(a.text + r + 2) : 0u;
     if ((b1 & 0xC0u) != 0x80u || (width == 3 && (b2 & 0xC0u) != 0x80u)) return r;
-    if (((a.tb.lit1_bits[b0 >> 5] >> (b0 & 31)) | (a.tb.lit1_bits[b1 >> 5] >> (b1 & 31)) | (width == 3 ? a.tb.lit1_bits[b2 >> 5] >> (b2 & 31) : 0u)) & 1u) return r;
-    for (int k = 1; k < width; ++k) if (is_docstart_global(a, r + k)) return r;
+    if (((args.tb.lit1_bits[b0 >> 5] >> (b0 & 31)) | (args.tb.lit1_bits[b1 >> 5] >> (b1 & 31)) | (width == 3 ? args.tb.lit1_bits[b2 >> 5] >> (b2 & 31) : 0u)) & 1u) return r;
+    for (int k = 1; k < width; ++k) if (raw_docstart(a, r + k)) return r;
     int q = r + width;
     for (;;) {
-        if (q + width > w.n) return q;
+        if (q + width > n) return q;
         if (ldg(a.text + q) != b0 || ldg(a.text + q + 1) != b1 || (width == 3 && ldg(a.text + q + 2) != b2)) return q;
-        for (int k = 0; k < width; ++k) if (is_docstart_global(a, q + k)) return q;
+        for (int k = 0; k < width; ++k) if (raw_docstart(a, q + k)) return q;
         q += width;
     }
 }
@@ -915,7 +941,7 @@ GTOK_DEV_NOINLINE int skip_forward_repeat(const Win& w, int r) {
 GTOK_DEV_NOINLINE int skip_forward_ws_run(const Win& w, int r) {
     const uint32_t sp = text_at(w, r);
     if (sp == 0x20u || sp == 0x09u || sp == 0x0Bu || sp == 0x0Cu) {
-        const int e = skip_forward_spaces(w, r, sp);
+        const int e = sp == 0x20u ? skip_forward_spaces(w, r, 0x20u) : skip_forward_spaces(w, r, sp);     // (the usual byte as a constant)
         return e < 0 ? -1 : (e > r ? e - 1 : r);
     }
     if (sp >= 0xC2u) {
@@ -936,7 +962,7 @@ GTOK_DEV bool four_letters(uint32_t v) {
 }
 // True when the 128 bytes at q (q % 128 == 0) are all ASCII letters and none of them opens a document
 // (eight independent loads, as in run_of_128).
-GTOK_DEV bool letters_128(const EncodeArgs& a, int q) {
+GTOK_DEV bool letters_128(RawText a, int q) {
     if (a.docmask) {
         const uint32_t* dm = a.docmask + (q >> 5);
         if (ldg(dm) | ldg(dm + 1) | ldg(dm + 2) | ldg(dm + 3)) return false;
@@ -958,7 +984,7 @@ GTOK_DEV bool letters_128(const EncodeArgs& a, int q) {
     return ok;
 }
 GTOK_DEV int skip_back_letters(const Win& w, int q) {
-    const EncodeArgs& a = *w.a;
+    const RawText a = raw_text(*w.a);
     for (;;) {
         if (q < 0) return q;
         if ((q & 127) == 127 && q >= 255 && letters_128(a, q - 127)) { q -= 128; continue; }
@@ -969,7 +995,7 @@ GTOK_DEV int skip_back_letters(const Win& w, int q) {
         }
         const uint32_t b = ldg(a.text + q);
         if (!((b >= 'a' && b <= 'z') || (b >= 'A' && b <= 'Z'))) return q;
-        if (is_docstart_global(a, q)) return q;
+        if (raw_docstart(a, q)) return q;
         --q;
     }
 }
@@ -1231,8 +1257,12 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
             if (q < w.vlo) q = skip_back_newlines(w, q);      // long runs: raw bytes, 128 or 16 at a time
             if (q < 0) break;
             {
-                // inside the window: a 16-byte chunk of nothing but newline bytes of this document, from the bit planes
+                // inside the window: 64 bytes, then 16, of nothing but newline bytes of this document, from the bit planes
                 const int i = q - w.lo;
+                if ((i & 63) == 63 && q - 63 >= w.vlo && q < w.vhi) {
+                    const uint64_t cr = *reinterpret_cast<const uint64_t*>(&w.sm->plane[PL_CRLF][(i - 63) >> 4]);
+                    if (cr == ~0ull && (w.sm->dsw[(i - 63) >> 5] | w.sm->dsw[((i - 63) >> 5) + 1]) == 0) { q -= 64; continue; }
+                }
                 if ((i & 15) == 15 && q - 15 >= w.vlo && q < w.vhi && w.sm->plane[PL_CRLF][i >> 4] == 0xFFFFu &&
                     ((w.sm->dsw[(i - 15) >> 5] >> ((i - 15) & 31)) & 0xFFFFu) == 0) { q -= 16; continue; }
             }
@@ -1249,8 +1279,12 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
             r = next_lead(w, r);
             if (r < 0) return true;
             for (;;) {
-                // inside the window: 16-byte chunks of plain (non-newline) one-byte whitespace of this document
+                // inside the window: 64 bytes, then 16, of plain (non-newline) one-byte whitespace of this document
                 const int i = r - w.lo;
+                if ((i & 63) == 0 && r >= w.vlo && r + 64 <= w.vhi && r + 64 < w.n) {
+                    const uint64_t ws = *reinterpret_cast<const uint64_t*>(&w.sm->plane[PL_S][i >> 4]), cr = *reinterpret_cast<const uint64_t*>(&w.sm->plane[PL_CRLF][i >> 4]);
+                    if (ws == ~0ull && cr == 0ull && (w.sm->dsw[i >> 5] | w.sm->dsw[(i >> 5) + 1]) == 0) { r += 64; continue; }
+                }
                 if ((i & 15) != 0 || r < w.vlo || r + 16 > w.vhi || r + 16 >= w.n) break;
                 const uint32_t ws = w.sm->plane[PL_S][i >> 4] & ~static_cast<uint32_t>(w.sm->plane[PL_CRLF][i >> 4]);
                 if (ws != 0xFFFFu || ((w.sm->dsw[i >> 5] >> (i & 31)) & 0xFFFFu) != 0) break;
@@ -1316,6 +1350,104 @@ GTOK_DEV void pretok_block_init(Blk& blk, const EncodeArgs& a, PretokSmem& sm) {
     });
 }
 
+// Runs that leave the tile's window, found by the whole block.  A walk along a run of newlines or of one
+// whitespace byte is one thread's work, 128 bytes a step, while the rest of the block waits: a 36 KB run of
+// spaces after a newline is 280 steps, longer than everything else the tile does.  So before the rules are
+// applied, when the window ends inside a run of one ASCII whitespace byte, all threads look for that run's
+// end together, 4 KB a step; likewise backwards from the window's start inside a stretch of newlines.  The
+// walks (skip_forward_ws_run, skip_back_newlines) take the answer when they arrive at the window's edge.
+template <class Blk>
+GTOK_DEV void far_runs(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int lo, int vlo, int vhi, int n) {
+    blk.par([&](int tid) {
+        if (tid != 0) return;
+        if (vhi < n && vhi - 1 >= vlo) {
+            const uint32_t sp = sm.txt[vhi - 1 - lo];
+            if ((sp == 0x20u || sp == 0x09u || sp == 0x0Bu || sp == 0x0Cu) && ldg(a.text + vhi) == sp && !is_docstart_global(a, vhi)) sm.far_run[0] = vhi;
+        }
+        if (vlo >= 2 && vlo < vhi) {
+            const uint32_t b0 = sm.txt[vlo - lo], b1 = ldg(a.text + vlo - 1);
+            if ((b0 == 0x0Au || b0 == 0x0Du) && (b1 == 0x0Au || b1 == 0x0Du) && !is_docstart_global(a, vlo)) sm.far_run[2] = vlo - 1;
+        }
+    });
+    if (sm.far_run[0] >= 0) {
+        // what skip_forward_spaces(vhi) returns: the first position that is not that byte, or -1 when the document ends first
+        const uint32_t sp = sm.txt[vhi - 1 - lo];
+        int answer = -1;
+        for (int base = vhi;; base += 64 * kThreads) {
+            blk.par([&](int tid) {
+                // sixty-four bytes a thread, sixteen at a time (the window's end is a multiple of 16)
+                uint32_t first = 0xFFFFFFFFu;
+                const uint32_t sp4 = sp * 0x01010101u;
+                for (int c = 0; c < 4 && first == 0xFFFFFFFFu; ++c) {
+                    const int q0 = base + 64 * tid + 16 * c;
+                    if (q0 + 16 <= n && no_docstart_in16(a, q0)) {
+                        const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + q0);
+                        if (ldg(p4) == sp4 && ldg(p4 + 1) == sp4 && ldg(p4 + 2) == sp4 && ldg(p4 + 3) == sp4) continue;
+                    }
+                    for (int k = 0; k < 16 && first == 0xFFFFFFFFu; ++k) {
+                        const int q = q0 + k;
+                        if (q >= n || is_docstart_global(a, q) || ldg(a.text + q) != sp) first = static_cast<uint32_t>(q);
+                    }
+                }
+                sm.scan[tid] = first;
+            });
+            const uint32_t m = blk.reduce_min(sm.scan);
+            if (m != 0xFFFFFFFFu) {
+                const int q = static_cast<int>(m);
+                answer = (q >= n || is_docstart_global(a, q)) ? -1 : q;
+                break;
+            }
+        }
+        blk.par([&](int tid) { if (tid == 0) sm.far_run[1] = answer; });
+    }
+    if (sm.far_run[2] >= 0) {
+        // what skip_back_newlines(vlo - 1) returns: the first position going back that holds no newline byte, or a
+        // newline that opens its document, or -1
+        int answer = -1;
+        // (the bytes from the last 16-byte line below the window's start up to that start first, by one thread's loop below)
+        const int top = vlo & ~15;                                // 16-byte lines from here down
+        bool found = false;
+        {
+            blk.par([&](int tid) {
+                uint32_t key = 0xFFFFFFFFu;
+                if (tid == 0)
+                    for (int q = vlo - 1; q >= top && key == 0xFFFFFFFFu; --q) {
+                        const uint32_t b = ldg(a.text + q);
+                        if ((b != 0x0Au && b != 0x0Du) || is_docstart_global(a, q)) key = 0x7FFFFFFEu - static_cast<uint32_t>(q);
+                    }
+                sm.scan[tid] = key;
+            });
+            const uint32_t m = blk.reduce_min(sm.scan);
+            if (m != 0xFFFFFFFFu) { answer = static_cast<int>(0x7FFFFFFEu - m); found = true; }
+        }
+        for (int base = top; !found; base -= 64 * kThreads) {
+            if (base <= 0) { answer = -1; break; }
+            blk.par([&](int tid) {
+                // sixty-four bytes a thread, a 16-byte line at a time, downwards
+                uint32_t key = 0xFFFFFFFFu;                        // smallest key = highest position that ends the walk
+                for (int c = 0; c < 4 && key == 0xFFFFFFFFu; ++c) {
+                    const int hi = base - 64 * tid - 16 * c;       // the line is [hi - 16, hi)
+                    if (hi <= 0) { key = 0x7FFFFFFFu; break; }    // (position -1)
+                    if (hi >= 32 && no_docstart_in16(a, hi - 16)) {
+                        const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + hi - 16);
+                        const uint32_t v0 = ldg(p4), v1 = ldg(p4 + 1), v2 = ldg(p4 + 2), v3 = ldg(p4 + 3);
+                        if (all_bytes_in(v0, 0x0Au, 0x0Du) && all_bytes_in(v1, 0x0Au, 0x0Du) && all_bytes_in(v2, 0x0Au, 0x0Du) && all_bytes_in(v3, 0x0Au, 0x0Du)) continue;
+                    }
+                    for (int q = hi - 1; q >= hi - 16 && key == 0xFFFFFFFFu; --q) {
+                        if (q < 0) { key = 0x7FFFFFFFu; break; }
+                        const uint32_t b = ldg(a.text + q);
+                        if ((b != 0x0Au && b != 0x0Du) || is_docstart_global(a, q)) key = 0x7FFFFFFEu - static_cast<uint32_t>(q);
+                    }
+                }
+                sm.scan[tid] = key;
+            });
+            const uint32_t m = blk.reduce_min(sm.scan);
+            if (m != 0xFFFFFFFFu) { answer = m == 0x7FFFFFFFu ? -1 : static_cast<int>(0x7FFFFFFEu - m); break; }
+        }
+        blk.par([&](int tid) { if (tid == 0) sm.far_run[3] = answer; });
+    }
+}
+
 // One tile of pre-tokenization.
 template <bool kWide, class Blk>
 GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int tile) {
@@ -1351,7 +1483,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     // many bytes remain in the document, anything else is a one-byte codepoint) and looked up in
     // the block's copy of the class table.
     blk.par([&](int tid) {
-        if (tid == 0) { sm.misc[1] = 0; sm.misc[3] = 0; }
+        if (tid == 0) { sm.misc[1] = 0; sm.misc[3] = 0; sm.far_run[0] = -2; sm.far_run[2] = -2; }
         if (tid < static_cast<int>(sizeof(sm.dirty) / 4)) sm.dirty[tid] = 0;
         for (int wd = tid; wd < kPWin / 32 + 2; wd += kThreads) {
             int gw = (lo >> 5) + wd;                 // lo is a multiple of 32
@@ -1596,6 +1728,13 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
     w.sm = &sm; w.a = &a; w.lo = lo; w.n = n;
     w.vlo = lo < 0 ? 0 : lo + static_cast<int>(a.tb.added_max_bytes);
     w.vhi = lo + kPWin < n ? lo + kPWin : n;
+    {
+        // (only when the window ends in whitespace or begins with newlines: every thread sees that without a barrier)
+        const uint32_t last_b = w.vhi - 1 >= w.vlo ? sm.txt[w.vhi - 1 - lo] : 0u, first_b = w.vlo < w.vhi ? sm.txt[w.vlo - lo] : 0u;
+        const bool fwd = w.vhi < n && (last_b == 0x20u || last_b == 0x09u || last_b == 0x0Bu || last_b == 0x0Cu);
+        const bool back = w.vlo >= 2 && (first_b == 0x0Au || first_b == 0x0Du);
+        if (!a.tb.added_ws && (fwd || back)) far_runs(blk, a, sm, lo, w.vlo, w.vhi, n);
+    }
 
     // ---- P3: boundary bits, 32 bytes per thread as 64-bit planes with 16-bit margins ----
     // Bit i of a plane is byte i; "<< 1" moves a fact from a byte to the byte after it.
