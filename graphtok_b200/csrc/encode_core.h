@@ -2833,24 +2833,45 @@ GTOK_DEV bool rle_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li,
     uint32_t* r_next = t_self + (kRleMax + 2);
     uint32_t* t_next = r_next + (kRleMax + 2);
     uint32_t* offs = t_next + (kRleMax + 2);
-    const uint32_t per = (len + kThreads - 1) / kThreads;
+    // Each thread takes a stretch of whole 16-byte lines of the text (the first and the last thread also the ragged ends).
     // ---- byte runs ----
+    // A line whose sixteen bytes all equal the byte before it opens no run: such lines, nearly all of a
+    // long run, cost one 128-bit load and a few compares; the others are looked at byte by byte.
+    uint32_t head = (16u - (g & 15u)) & 15u;                          // bytes before the first whole line
+    if (head > len) head = len;
+    const uint32_t lines = (len - head) / 16u;
+    const uint32_t per = (lines + kThreads - 1) / kThreads;            // lines per thread
+    auto scan_stretch = [&](int tid, auto&& on_start) {
+        // thread t: lines [t * per, (t + 1) * per) of the pre-token; thread 0 also the head, the last thread the tail
+        const uint32_t l0 = static_cast<uint32_t>(tid) * per < lines ? static_cast<uint32_t>(tid) * per : lines;
+        const uint32_t l1 = (static_cast<uint32_t>(tid) + 1u) * per < lines ? (static_cast<uint32_t>(tid) + 1u) * per : lines;
+        const uint32_t lo = tid == 0 ? 0u : head + 16u * l0;
+        const uint32_t hi = tid == kThreads - 1 ? len : head + 16u * l1;
+        uint32_t i = lo;
+        uint32_t prev = i ? ldg(a.text + g + i - 1) : 0x100u;
+        while (i < hi) {
+            if (((g + i) & 15u) == 0 && i + 16u <= hi && prev < 0x100u) {
+                const uint32_t* p4 = reinterpret_cast<const uint32_t*>(a.text + g + i);
+                const uint32_t pat = prev * 0x01010101u;
+                if (ldg(p4) == pat && ldg(p4 + 1) == pat && ldg(p4 + 2) == pat && ldg(p4 + 3) == pat) { i += 16u; continue; }
+            }
+            const uint32_t b = ldg(a.text + g + i);
+            if (b != prev) on_start(i, b);
+            prev = b;
+            ++i;
+        }
+    };
     blk.par([&](int tid) {
-        const uint32_t lo = tid * per, hi = lo + per < len ? lo + per : len;
         uint32_t c = 0;
-        for (uint32_t i = lo; i < hi; ++i) c += (i == 0 || ldg(a.text + g + i) != ldg(a.text + g + i - 1)) ? 1u : 0u;
+        scan_stretch(tid, [&](uint32_t, uint32_t) { ++c; });
         s_cnt[tid] = c;
     });
     uint32_t n_runs = 0;
     blk.excl_scan(s_cnt, &n_runs);
     if (n_runs > static_cast<uint32_t>(kRleMax)) return false;
     blk.par([&](int tid) {
-        const uint32_t lo = tid * per, hi = lo + per < len ? lo + per : len;
         uint32_t at = s_cnt[tid];
-        for (uint32_t i = lo; i < hi; ++i) {
-            const uint32_t b = ldg(a.text + g + i);
-            if (i == 0 || b != ldg(a.text + g + i - 1)) { sym[at] = sm.b2i[b]; offs[at] = i; ++at; }
-        }
+        scan_stretch(tid, [&](uint32_t i, uint32_t b) { sym[at] = sm.b2i[b]; offs[at] = i; ++at; });
     });
     blk.par([&](int tid) {
         if (static_cast<uint32_t>(tid) < n_runs) cnt[tid] = (static_cast<uint32_t>(tid) + 1 < n_runs ? offs[tid + 1] : len) - offs[tid];
