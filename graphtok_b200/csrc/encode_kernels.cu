@@ -127,7 +127,16 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const __grid_constant
     tl_stamp(a, 2, 0);
     sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
     __syncthreads();
-    // longest pre-tokens first: their merge chains decide when the kernel ends
+    // the pre-tokens of more than 64 bytes first, a block each (the longest of them take longer than a block's share of
+    // the batches), then the batches, longest class first: their merge chains decide when the kernel ends
+    for (;;) {
+        if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);
+        __syncthreads();
+        const uint32_t li = s_pick;
+        __syncthreads();
+        if (li >= n_long) break;
+        long_word(blk, a, sm, li);
+    }
     for (int done = 0;; ++done) {
         if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_BATCH, 1u);
         __syncthreads();
@@ -144,14 +153,6 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const __grid_constant
         }
         miss_batch(blk, a, sm, list, dir, first, count, batch, max_len, take);
         tl_stamp(a, 2, 2 + done);
-    }
-    for (;;) {
-        if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_LONG, 1u);
-        __syncthreads();
-        const uint32_t li = s_pick;
-        __syncthreads();
-        if (li >= n_long) break;
-        long_word(blk, a, sm, li);
     }
     tl_stamp(a, 2, 1);
 }
