@@ -2375,20 +2375,30 @@ GTOK_DEV uint32_t team_bpe(Team& tm, const EncodeArgs& a, uint32_t* ids, uint32_
 
 // End (exclusive, global byte position) of the pre-token starting at g, found by
 // scanning the boundary bits; tiles without any boundary are skipped in one step.
-GTOK_DEV uint32_t find_word_end(const EncodeArgs& a, uint32_t g, uint32_t n) {
+// Where the pre-token that starts at g ends (the next boundary bit, or the end of the text), by the whole
+// block: 256 mask words (8 KB of text) a step.  One thread going through the mask a word at a time took
+// longer over a 36 KB pre-token than the block then took to merge it.  `scratch`: kThreads words.
+template <class Blk>
+GTOK_DEV uint32_t find_word_end(Blk& blk, const EncodeArgs& a, uint32_t* scratch, uint32_t g, uint32_t n) {
+    const uint32_t n_words = ((n + kTile - 1) / kTile) * kTileWords;
     uint32_t wi = g >> 5;
-    uint32_t n_words = ((n + kTile - 1) / kTile) * kTileWords;
-    uint32_t bits = ldg(a.bmask + wi) & ~((2u << (g & 31)) - 1u);
-    if ((g & 31) == 31) bits = 0;
-    for (;;) {
-        if (bits) { uint32_t e = wi * 32 + ffs32(bits); return e < n ? e : n; }
-        ++wi;
-        if (wi >= n_words) return n;
-        if ((wi % kPTileWords) == 0) {       // tile_nb counts per pre-tokenization tile
-            while (wi < n_words && ldg(a.tile_nb + wi / kPTileWords) == 0) wi += kPTileWords;
-            if (wi >= n_words) return n;
-        }
-        bits = ldg(a.bmask + wi);
+    {
+        uint32_t bits = ldg(a.bmask + wi) & ~((2u << (g & 31)) - 1u);
+        if ((g & 31) == 31) bits = 0;
+        if (bits) { const uint32_t e = wi * 32 + ffs32(bits); return e < n ? e : n; }
+    }
+    for (uint32_t base = wi + 1;; base += kThreads) {
+        if (base >= n_words) return n;
+        blk.par([&](int tid) {
+            const uint32_t w = base + static_cast<uint32_t>(tid);
+            scratch[tid] = (w >= n_words || ldg(a.bmask + w)) ? static_cast<uint32_t>(tid) : 0xFFFFFFFFu;
+        });
+        const uint32_t m = blk.reduce_min(scratch);
+        if (m == 0xFFFFFFFFu) continue;
+        const uint32_t w = base + m;
+        if (w >= n_words) return n;
+        const uint32_t e = w * 32 + ffs32(ldg(a.bmask + w));
+        return e < n ? e : n;
     }
 }
 
@@ -3105,16 +3115,14 @@ GTOK_DEV void long_word(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t li
     const uint32_t n = ldg(a.meta);
     const DeviceTables& tb = a.tb;
     const uint32_t g = ldg(a.glong_g + li);
+    uint32_t len = ldg(a.glong_len + li);
+    if (len == 0) len = find_word_end(blk, a, sm.ws, g, n) - g;
     blk.par([&](int tid) {
         if (tid != 0) return;
-        uint32_t len = ldg(a.glong_len + li);
-        if (len == 0) len = find_word_end(a, g, n) - g;
         uint32_t id = kNoToken;
         if (tb.ignore_merges) id = probe_long(tb, a.text, g, len);
-        sm.ctr[C_TMP] = len;
         sm.ctr[C_TMP2] = id;
     });
-    const uint32_t len = sm.ctr[C_TMP];
     const uint32_t hit = sm.ctr[C_TMP2];
     if (hit != kNoToken) {
         blk.par([&](int tid) { if (tid == 0) { a.gstage[g] = hit; a.glong_cnt[li] = 1; global_add(a.tile_tok + g / kTile, 1u); } });
