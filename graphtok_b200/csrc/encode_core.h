@@ -292,6 +292,32 @@ GTOK_DEV unsigned long long wait_state(const unsigned long long* st, int j, uint
     return kStFinal;
 }
 
+// Counts one more finished producer, after everything this block wrote before (the caller has
+// passed a block barrier since).
+GTOK_DEV void release_add(uint32_t* p, uint32_t v) {
+#if defined(__CUDA_ARCH__)
+    __threadfence();
+    atomicAdd(p, v);
+#else
+    *p += v;
+#endif
+}
+// Waits until the counter reaches `want`; false (and the error bit) when the limit runs out.
+GTOK_DEV bool wait_count(const uint32_t* p, uint32_t want, uint32_t* ctl) {
+    for (int it = 0; it < kWaitLimit; ++it) {
+#if defined(__CUDA_ARCH__)
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+#else
+        const uint32_t v = *p;
+#endif
+        if (v >= want) return true;
+        backoff(); backoff(); backoff(); backoff();       // many blocks poll this one word
+    }
+    global_or(ctl + 2, kErrWaitExpired);
+    return false;
+}
+
 // ---- merge-rule probe ----------------------------------------------------------
 struct RankRes { uint32_t rank, res; };
 #if defined(__CUDA_ARCH__)
@@ -2074,7 +2100,10 @@ constexpr int kMissBatch = kThreads / 2;       // unknown pre-tokens per batch o
 constexpr int kArenaSyms = 3072;               // symbols of one batch (ids, ranks, results: 36 KB)
 constexpr int kSumTiles = 16384;               // documents up to this many tiles (64 MiB): tile bases by direct summation
 constexpr int kLongPerTile = 64;               // a tile holds fewer than 4096 / 65 pre-tokens longer than 64 bytes
-enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10, CTL_NMED1 = 11, CTL_NFCFLAG = 12 };
+enum { CTL_PRETOK = 0, CTL_ASM = 1, CTL_ERR = 2, CTL_EXIT = 3, CTL_NMISS = 4, CTL_NLONG = 5, CTL_BATCH = 6, CTL_LONG = 7, CTL_NMED = 8, CTL_NFC = 9, CTL_NMED2 = 10, CTL_NMED1 = 11, CTL_NFCFLAG = 12,
+       CTL_FILTERED = 13,   // calls of the 17..32-byte class that are through their whole-token lookups (surplus handed back)
+       CTL_SURPLUS = 14,    // ticket for the chunks of that surplus
+       CTL_NSURPLUS = 15 }; // entries handed back in all
 constexpr int kShortWordMax = 16;              // unknown pre-tokens up to this length and the longer ones are batched apart
 // A batch lasts as long as its longest merge chain, so pre-tokens are batched by length class and
 // the classes are handed out longest first: 49..64 bytes, 33..48, 17..32, then the short ones.
@@ -2691,9 +2720,13 @@ GTOK_DEV void arena_pairs(Blk& blk, const EncodeArgs& a, MissSmem& sm, uint32_t*
 // slot each; then the thread that owns a pre-token merges it (lowest rank first) and stores
 // the ids.  `max_len` is the longest pre-token of the batch's length class: batch * max_len
 // slots fit the arena.
-template <class Blk>
+// kMode 1 (`share`): a call with take > batch hands back what it cannot merge in one arena; kMode 2
+// (`surplus`): the entries are such handed-back ones.  (Template values, so that the plain call's code is
+// what it was without them.)
+template <class Blk, int kMode = 0>
 GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss,
                          uint32_t batch, uint32_t max_len, uint32_t take) {
+    constexpr bool share = kMode == 1, surplus = kMode == 2;
     const DeviceTables& tb = a.tb;
     uint32_t* ids = sm.ws;
     uint32_t* rk = sm.ws + kArenaSyms;
@@ -2778,19 +2811,38 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
             if (wv) sm.cand[shared_add(&sm.ctr[C_USED], 1u)] = wv;
         });
         n_cand = sm.ctr[C_USED];
+        if (share) {
+            // What does not fit one arena goes back to the head of this call's stretch of the list, its
+            // count in front of it, for whichever block is free first (miss_surplus): a text whose long
+            // pre-tokens are not in the vocabulary would otherwise keep this block for three arenas in a row.
+            const uint32_t extra = n_cand > batch ? n_cand - batch : 0u;
+            unsigned long long* wlist = const_cast<unsigned long long*>(list);
+            blk.par([&](int tid) {
+                if (tid == 0) store_state(wlist + static_cast<long long>(dir) * static_cast<long long>(first), extra);
+                if (static_cast<uint32_t>(tid) < extra)
+                    store_state(wlist + static_cast<long long>(dir) * static_cast<long long>(first + 1u + tid), sm.cand[batch + tid]);
+            });
+            blk.par([&](int tid) {
+                if (tid != 0) return;
+                if (extra) global_add(a.ctl + CTL_NSURPLUS, extra);
+                release_add(a.ctl + CTL_FILTERED, 1u);
+            });
+            if (n_cand > batch) n_cand = batch;
+        }
     }
     for (uint32_t done = 0; done < n_cand; done += batch) {
     const uint32_t n_here = n_cand - done < batch ? n_cand - done : batch;
     blk.par([&](int tid) {
         if (static_cast<uint32_t>(tid) < batch)
             sm.word[tid] = static_cast<uint32_t>(tid) >= n_here ? 0ull : filtered ? sm.cand[done + tid]
+                           : surplus ? load_state(list + static_cast<long long>(dir) * static_cast<long long>(first + tid))   // written by another block
                            : list[static_cast<long long>(dir) * static_cast<long long>(first + tid)];   // dir = -1: a list that grows downwards
     });
     mark(16);
     arena_fill(blk, a, sm, ids, rk, batch, max_len);
     mark(17);
     // owner: a pre-token of 16 bytes or more that is itself in the vocabulary (ignore_merges)
-    if (!filtered && tb.ignore_merges && max_len > static_cast<uint32_t>(kWordKeyMax)) {
+    if (!filtered && !surplus && tb.ignore_merges && max_len > static_cast<uint32_t>(kWordKeyMax)) {
         blk.par([&](int tid) {
             if (static_cast<uint32_t>(tid) >= n_here) return;
             const unsigned long long wv = sm.word[tid];
@@ -2816,6 +2868,28 @@ GTOK_DEV void miss_batch(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsi
     });
     mark(20);
     }
+}
+
+// The two rare modes as functions of their own: inlined into the kernel beside the plain call they cost
+// every text a few percent of the kernel (registers and code size), used or not.
+template <class Blk>
+GTOK_DEV_NOINLINE void miss_batch_sharing(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss,
+                                          uint32_t batch, uint32_t max_len, uint32_t take) {
+    miss_batch<Blk, 1>(blk, a, sm, list, dir, first, n_miss, batch, max_len, take);
+}
+template <class Blk>
+GTOK_DEV_NOINLINE void miss_batch_surplus(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t n_miss) {
+    miss_batch<Blk, 2>(blk, a, sm, list, dir, first, n_miss, kMedBatchB, kMedSplit, kMedBatchB);
+}
+
+// What a call of the 17..32-byte class with `share` left behind: chunk `chunk` of the surplus of the
+// call that began at list entry `first`.  The entries are known not to be vocabulary tokens.
+constexpr uint32_t kSurplusChunks = (kMedTakeB - kMedBatchB + kMedBatchB - 1) / kMedBatchB;
+template <class Blk>
+GTOK_DEV void miss_surplus(Blk& blk, const EncodeArgs& a, MissSmem& sm, const unsigned long long* list, int dir, uint32_t first, uint32_t chunk) {
+    const uint32_t extra = static_cast<uint32_t>(load_state(list + static_cast<long long>(dir) * static_cast<long long>(first)));
+    if (chunk * kMedBatchB >= extra) return;
+    miss_batch_surplus(blk, a, sm, list, dir, first + 1u + chunk * kMedBatchB, first + 1u + extra);
 }
 
 // ---- run-length path for long pre-tokens made of a few byte runs ------------------------

@@ -124,6 +124,10 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const __grid_constant
     const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med1_batches = (n_med1 + kMedBatchA1 - 1) / kMedBatchA1;
     const uint32_t med2_batches = (n_med2 + take_b - 1) / take_b;
     const uint32_t short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
+    // A call of the 17..32-byte class under ignore_merges looks 256 entries up as whole tokens but merges at most 96
+    // of them at a time.  With fewer calls than blocks (a prompt rather than a corpus) it hands the rest back for the
+    // blocks that got no call; otherwise it works through the rest itself, which keeps the blocks evenly loaded.
+    const bool share = take_b > kMedBatchB && med2_batches != 0 && med_batches + med1_batches + med2_batches + short_batches + n_long < gridDim.x;
     tl_stamp(a, 2, 0);
     sm.b2i[threadIdx.x] = a.tb.byte_to_id[threadIdx.x];
     __syncthreads();
@@ -151,8 +155,27 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const __grid_constant
         else if (t < med_batches + med1_batches + med2_batches) {
             list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches - med1_batches) * take_b; count = n_med2; batch = kMedBatchB; max_len = kMedSplit; take = take_b;
         }
-        miss_batch(blk, a, sm, list, dir, first, count, batch, max_len, take);
+        if (share && take > batch) miss_batch_sharing(blk, a, sm, list, dir, first, count, batch, max_len, take);
+        else miss_batch(blk, a, sm, list, dir, first, count, batch, max_len, take);
         tl_stamp(a, 2, 2 + done);
+    }
+    // What the calls of the 17..32-byte class handed back: wait until every such call is through its lookups, then
+    // take the chunks in turn.  The wait is for blocks that are running (a call is only ever held by a block that
+    // took its ticket).
+    if (share) {
+        if (threadIdx.x == 0)
+            s_pick = wait_count(a.ctl + CTL_FILTERED, med2_batches, a.ctl) && *reinterpret_cast<volatile uint32_t*>(a.ctl + CTL_NSURPLUS) ? 1u : 0u;   // usually nothing
+        __syncthreads();
+        const bool ready = s_pick != 0;
+        __syncthreads();
+        while (ready) {
+            if (threadIdx.x == 0) s_pick = atomicAdd(a.ctl + CTL_SURPLUS, 1u);
+            __syncthreads();
+            const uint32_t u = s_pick;
+            __syncthreads();
+            if (u >= med2_batches * kSurplusChunks) break;
+            miss_surplus(blk, a, sm, a.gmed + (a.gmed_cap - 1), -1, (u / kSurplusChunks) * take_b, u % kSurplusChunks);
+        }
     }
     tl_stamp(a, 2, 1);
 }

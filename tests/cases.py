@@ -95,6 +95,13 @@ def tile_crossers(special):
     for alphabet, length in (("abcdefghijklmnopqrstuvwxyz", 20000), ("ACGT", 9000), ("etaoinshr", 3000), ("ab", 700), ("theinandofto", 5000),
                              ("中文日本語的一是不了人我在有他这为之大来以个", 2500), ("éèêàùç", 900), ("!@#$%^&*()-=+", 4000)):
         out.append("p " + "".join(rng.choice(alphabet) for _ in range(length)) + " q")
+    # many pre-tokens of 17 to 32 bytes that are no vocabulary tokens (what one block does not merge itself it hands back),
+    # alone and among ones that may be
+    b64 = "ABCDEFGHIJKLMNOPQRSTUVWXYZabcdefghijklmnopqrstuvwxyz0123456789+/"
+    out.append(" ".join("".join(rng.choice(b64[:52]) for _ in range(rng.randint(17, 32))) for _ in range(900)))
+    out.append(" ".join(("".join(rng.choice(b64[:52]) for _ in range(rng.randint(14, 34))) if rng.random() < 0.6 else
+                         rng.choice(("international", "responsibilities", "internationalization", "characteristically", "telecommunications")))
+                        for _ in range(1500)))
     out.append("p " + "the" * 600 + "in" * 500 + " q")
     out.append("p " + "thequickbrownfox" * 200 + " q")
     out.append("é" * 3000 + "日" * 2000 + "\U0001F600" * 500)

@@ -176,7 +176,13 @@ int64_t gtok_emul_encode(void* h, const uint8_t* text, uint32_t n, const uint32_
         for (uint32_t first = 0; first < n_med; first += kMedBatchA) miss_batch(blk, a, *sm, a.gmed, 1, first, n_med, kMedBatchA, kMedWordMax, kMedBatchA);
         for (uint32_t first = 0; first < n_med1; first += kMedBatchA1) miss_batch(blk, a, *sm, a.gmed1, 1, first, n_med1, kMedBatchA1, kMedSplit1, kMedBatchA1);
         const uint32_t take_b = a.tb.ignore_merges ? kMedTakeB : kMedBatchB;
-        for (uint32_t first = 0; first < n_med2; first += take_b) miss_batch(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, n_med2, kMedBatchB, kMedSplit, take_b);
+        for (uint32_t first = 0; first < n_med2; first += take_b) {
+            if (take_b > kMedBatchB) miss_batch_sharing(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, n_med2, kMedBatchB, kMedSplit, take_b);
+            else miss_batch(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, n_med2, kMedBatchB, kMedSplit, take_b);
+        }
+        if (take_b > kMedBatchB)
+            for (uint32_t first = 0; first < n_med2; first += take_b)
+                for (uint32_t c = 0; c < kSurplusChunks; ++c) miss_surplus(blk, a, *sm, a.gmed + (a.gmed_cap - 1), -1, first, c);
         for (uint32_t first = 0; first < n_miss; first += kMissBatch) miss_batch(blk, a, *sm, a.gmiss, 1, first, n_miss, kMissBatch, kShortWordMax, kMissBatch);
         for (uint32_t li = 0; li < n_long; ++li) long_word(blk, a, *sm, li);
         delete sm;
