@@ -893,6 +893,60 @@ GTOK_DEV bool run_of_128(RawText a, int q, uint32_t x, uint32_t y) {
     if (all_and != all_or) return false;               // the 32 words are not all the same
     return all_bytes_in(all_and, x, y);
 }
+// Inside the window, from the bit planes (16 bytes per entry, eight-byte aligned rows) and the window's
+// document-start bits.  First window index in [i, i_end) whose byte is not a plain (non-newline) one-byte
+// whitespace character of the running document, i_end when there is none: 64 bytes a step, 256 while whole
+// groups of four are clean.  Pointers and bounds by value, in a function of its own: the loop then keeps
+// everything in registers (a newline followed by a window full of spaces is 125 steps of 64, and one
+// codepoint at a time through the attribute bytes costs a hundred times that).
+GTOK_DEV int low_bit(uint64_t x) {
+#if defined(__CUDA_ARCH__)
+    return __ffsll(static_cast<long long>(x)) - 1;
+#else
+    return __builtin_ctzll(x);
+#endif
+}
+GTOK_DEV int high_bit(uint64_t x) {
+#if defined(__CUDA_ARCH__)
+    return 63 - __clzll(static_cast<long long>(x));
+#else
+    return 63 - __builtin_clzll(x);
+#endif
+}
+GTOK_DEV_NOINLINE int plain_ws_end(const uint16_t* ps, const uint16_t* pcr, const uint32_t* dsw, int i, int i_end) {
+    if (i >= i_end) return i_end;
+    const uint64_t* S = reinterpret_cast<const uint64_t*>(ps);
+    const uint64_t* C = reinterpret_cast<const uint64_t*>(pcr);
+    int g = i >> 6;
+    uint64_t bad = (~S[g] | C[g] | dsw[2 * g] | (static_cast<uint64_t>(dsw[2 * g + 1]) << 32)) & (~0ull << (i & 63));
+    for (;;) {
+        if (bad) { const int j = g * 64 + low_bit(bad); return j < i_end ? j : i_end; }
+        ++g;
+        while (g * 64 + 256 <= i_end) {
+            const uint64_t s_all = S[g] & S[g + 1] & S[g + 2] & S[g + 3], c_any = C[g] | C[g + 1] | C[g + 2] | C[g + 3];
+            const uint32_t* d = dsw + 2 * g;
+            const uint32_t d_any = d[0] | d[1] | d[2] | d[3] | d[4] | d[5] | d[6] | d[7];
+            if (s_all != ~0ull || c_any != 0ull || d_any != 0u) break;
+            g += 4;
+        }
+        if (g * 64 >= i_end) return i_end;
+        bad = ~S[g] | C[g] | dsw[2 * g] | (static_cast<uint64_t>(dsw[2 * g + 1]) << 32);
+    }
+}
+// The same going back over newline bytes: the lowest window index j in [i_begin, i] such that j..i are all
+// newline bytes none of which opens a document (i + 1 when the byte at i is not such a one).
+GTOK_DEV_NOINLINE int newline_run_begin(const uint16_t* pcr, const uint32_t* dsw, int i, int i_begin) {
+    if (i < i_begin) return i + 1;
+    const uint64_t* C = reinterpret_cast<const uint64_t*>(pcr);
+    int g = i >> 6;
+    uint64_t bad = (~C[g] | dsw[2 * g] | (static_cast<uint64_t>(dsw[2 * g + 1]) << 32)) & (~0ull >> (63 - (i & 63)));
+    for (;;) {
+        if (bad) { const int j = g * 64 + high_bit(bad) + 1; return j > i_begin ? j : i_begin; }
+        if (g * 64 <= i_begin) return i_begin;
+        --g;
+        bad = ~C[g] | dsw[2 * g] | (static_cast<uint64_t>(dsw[2 * g + 1]) << 32);
+    }
+}
 GTOK_DEV int skip_back_newlines(const Win& w, int q) {
     if (w.a->tb.added_ws) return q;
     const RawText a = raw_text(*w.a);
@@ -1282,15 +1336,10 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
         for (;;) {
             if (q < w.vlo) q = skip_back_newlines(w, q);      // long runs: raw bytes, 128 or 16 at a time
             if (q < 0) break;
-            {
-                // inside the window: 64 bytes, then 16, of nothing but newline bytes of this document, from the bit planes
-                const int i = q - w.lo;
-                if ((i & 63) == 63 && q - 63 >= w.vlo && q < w.vhi) {
-                    const uint64_t cr = *reinterpret_cast<const uint64_t*>(&w.sm->plane[PL_CRLF][(i - 63) >> 4]);
-                    if (cr == ~0ull && (w.sm->dsw[(i - 63) >> 5] | w.sm->dsw[((i - 63) >> 5) + 1]) == 0) { q -= 64; continue; }
-                }
-                if ((i & 15) == 15 && q - 15 >= w.vlo && q < w.vhi && w.sm->plane[PL_CRLF][i >> 4] == 0xFFFFu &&
-                    ((w.sm->dsw[(i - 15) >> 5] >> ((i - 15) & 31)) & 0xFFFFu) == 0) { q -= 16; continue; }
+            if (q >= w.vlo && q < w.vhi) {
+                // inside the window: down to the first of the newline bytes that end at q, from the bit planes
+                const int i2 = newline_run_begin(w.sm->plane[PL_CRLF], w.sm->dsw, q - w.lo, w.vlo - w.lo);
+                if (w.lo + i2 < q) q = w.lo + i2;
             }
             uint8_t aq = attr_at(w, q);
             if (!((aq & A_CLS) == A_S && (aq & A_CRLF))) { if ((aq & A_CLS) == A_O) return true; break; }
@@ -1302,21 +1351,29 @@ GTOK_DEV bool is_boundary(const Win& w, int p, uint8_t a0, uint32_t family, bool
         // only if no later newline in the run pulls it into \s*[\r\n]+.
         int r = p;
         for (;;) {
+            if (r + 1 >= w.vlo && r + 1 < w.vhi) {
+                // inside the window: on to the last byte before the first one that is not plain one-byte whitespace, from the bit planes
+                const int j = plain_ws_end(w.sm->plane[PL_S], w.sm->plane[PL_CRLF], w.sm->dsw, r + 1 - w.lo, w.vhi - w.lo);
+                if (w.lo + j - 1 > r) r = w.lo + j - 1;
+            }
             r = next_lead(w, r);
             if (r < 0) return true;
-            for (;;) {
-                // inside the window: 64 bytes, then 16, of plain (non-newline) one-byte whitespace of this document
-                const int i = r - w.lo;
-                if ((i & 63) == 0 && r >= w.vlo && r + 64 <= w.vhi && r + 64 < w.n) {
-                    const uint64_t ws = *reinterpret_cast<const uint64_t*>(&w.sm->plane[PL_S][i >> 4]), cr = *reinterpret_cast<const uint64_t*>(&w.sm->plane[PL_CRLF][i >> 4]);
-                    if (ws == ~0ull && cr == 0ull && (w.sm->dsw[i >> 5] | w.sm->dsw[(i >> 5) + 1]) == 0) { r += 64; continue; }
+            if (r >= w.vhi) {
+                const int r2 = skip_forward_ws_run(w, r);
+                if (r2 < 0) return true;
+                if (r2 > r) {
+                    // r2 is the last of the repeats (plain whitespace, as r is).  The usual byte after it settles the
+                    // question without classifying anything: an ASCII newline, or ASCII that is no whitespace.
+                    r = r2;
+                    if (r + 1 < w.n) {
+                        const uint32_t b = ldg(w.a->text + r + 1);
+                        const bool other_doc = is_docstart_global(*w.a, r + 1);
+                        if (!other_doc && (b == 0x0Au || b == 0x0Du)) return false;
+                        if (other_doc || (b > 0x20u && b < 0x80u)) return true;
+                    }
+                    continue;
                 }
-                if ((i & 15) != 0 || r < w.vlo || r + 16 > w.vhi || r + 16 >= w.n) break;
-                const uint32_t ws = w.sm->plane[PL_S][i >> 4] & ~static_cast<uint32_t>(w.sm->plane[PL_CRLF][i >> 4]);
-                if (ws != 0xFFFFu || ((w.sm->dsw[i >> 5] >> (i & 31)) & 0xFFFFu) != 0) break;
-                r += 16;
             }
-            if (r >= w.vhi) { r = skip_forward_ws_run(w, r); if (r < 0) return true; }
             uint8_t ar = attr_at(w, r);
             if ((ar & A_CLS) != A_S) return true;
             if (ar & A_CRLF) return false;
