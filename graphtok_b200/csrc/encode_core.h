@@ -1227,6 +1227,11 @@ GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, boo
             int k = q;
             uint8_t ak = a1;
             for (;;) {
+                if (k - 1 >= w.vlo && k - 1 < w.vhi && !(ak & A_DOC)) {
+                    // inside the window: down to the first of the newline bytes that end before k, from the bit planes
+                    const int i2 = newline_run_begin(w.sm->plane[PL_CRLF], w.sm->dsw, k - 1 - w.lo, w.vlo - w.lo);
+                    if (w.lo + i2 < k - 1) { k = w.lo + i2; ak = attr_at(w, k); }
+                }
                 if (k > 0 && !(ak & A_DOC) && (text_at(w, k - 1) == 0x0Au || text_at(w, k - 1) == 0x0Du)) {
                     // over raw bytes, up to 128 at a time
                     const int r = skip_back_newlines(w, k - 1);
@@ -1246,6 +1251,11 @@ GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, boo
             k = p;
             ak = a0;
             for (;;) {
+                if (k + 1 >= w.vlo && k + 1 < w.vhi) {
+                    // inside the window: on to the last byte before the first one that is not plain one-byte whitespace, from the bit planes
+                    const int j = plain_ws_end(w.sm->plane[PL_S], w.sm->plane[PL_CRLF], w.sm->dsw, k + 1 - w.lo, w.vhi - w.lo);
+                    if (w.lo + j - 1 > k) { k = w.lo + j - 1; ak = attr_at(w, k); }
+                }
                 {
                     // the same whitespace codepoint again and again: over raw bytes
                     const int e = skip_forward_ws_run(w, k);
