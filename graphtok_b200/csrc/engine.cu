@@ -292,12 +292,14 @@ struct Engine::Impl {
             nfc_table_words(w);
             if (!upload(w.attn_bits, &dt.nfc_attn_bits, owned, err) || !upload(w.attn_sup, &dt.nfc_attn_sup, owned, err) ||
                 !upload(w.ccc, &dt.nfc_ccc, owned, err) || !upload(w.decomp, &dt.nfc_decomp, owned, err) ||
-                !upload(w.comp, &dt.nfc_comp, owned, err))
+                !upload(w.comp, &dt.nfc_comp, owned, err) || !upload(w.comp_hash, &dt.nfc_comp_hash, owned, err))
                 return false;
+            dt.nfc_comp_hash_mask = static_cast<uint32_t>(w.comp_hash.size() / 4 - 1);
             dt.nfc_attn_sup_n = static_cast<uint32_t>(w.attn_sup.size() / 2);
             dt.nfc_ccc_n = static_cast<uint32_t>(w.ccc.size() / 2);
             dt.nfc_decomp_n = static_cast<uint32_t>(w.decomp.size() / 6);
             dt.nfc_comp_n = static_cast<uint32_t>(w.comp.size() / 3);
+            for (int i = 0; i < 8; ++i) dt.nfc_lead_quiet[i] = w.lead_quiet[i];
         }
         static_assert(GTOK_UC_STAGE2_LEN == kUcStage2Words && GTOK_UC_STAGE1_LEN >= kUcStage1Bmp, "class table sizes the kernels copy to shared memory");
         fill_table_scalars(ht, dt);

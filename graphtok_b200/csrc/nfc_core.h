@@ -26,7 +26,11 @@ namespace gtok {
 
 constexpr int kNfcMaxCps = 96;       // decomposed codepoints of one stretch; longer ones are flagged (kErrNfcLong)
 
+constexpr int kNfcStage = kTile + 528;      // bytes of a tile's output put together in shared memory before they go out
 struct NfcSmem {
+    alignas(16) uint8_t outb[kNfcStage];
+    uint8_t sres[kThreads][12];      // the normalised form of the one stretch a chunk owns, kept from sizing to writing
+    uint8_t slen[kThreads];          // its length; 0: not kept (no stretch, several, or longer than that)
     uint32_t scan[kThreads];
     uint16_t attl[kThreads + 2];     // per 16-byte chunk, one before and one after the tile: attention lead bytes
     uint16_t attf[kThreads + 2];     // ... and every byte of an attention codepoint
@@ -92,13 +96,17 @@ GTOK_DEV uint32_t nfc_compose(const DeviceTables& tb, uint32_t x, uint32_t y) { 
     constexpr uint32_t SB = 0xAC00, LB = 0x1100, VB = 0x1161, TB = 0x11A7, LC = 19, VC = 21, TC = 28;
     if (x >= LB && x < LB + LC && y >= VB && y < VB + VC) return SB + ((x - LB) * VC + (y - VB)) * TC;
     if (x >= SB && x < SB + LC * VC * TC && (x - SB) % TC == 0 && y > TB && y < TB + TC) return x + (y - TB);
-    uint32_t lo = 0, hi = tb.nfc_comp_n;
-    while (lo < hi) {
-        uint32_t mid = (lo + hi) >> 1;
-        const uint32_t f = ldg(tb.nfc_comp + 3 * mid), s = ldg(tb.nfc_comp + 3 * mid + 1);
-        if (f < x || (f == x && s < y)) lo = mid + 1; else hi = mid;
+    // (hashed: a binary search of the thousand pairs was ten dependent loads, most of a stretch's time)
+    for (uint32_t at = nfc_comp_hash(x, y) & tb.nfc_comp_hash_mask;; at = (at + 1) & tb.nfc_comp_hash_mask) {
+#if defined(__CUDA_ARCH__)
+        const uint4 s = __ldg(reinterpret_cast<const uint4*>(tb.nfc_comp_hash) + at);
+        const uint32_t f = s.x, sec = s.y, comp = s.z;
+#else
+        const uint32_t f = tb.nfc_comp_hash[4 * at], sec = tb.nfc_comp_hash[4 * at + 1], comp = tb.nfc_comp_hash[4 * at + 2];
+#endif
+        if (f == 0xFFFFFFFFu) break;
+        if (f == x && sec == y) return comp;
     }
-    if (lo < tb.nfc_comp_n && ldg(tb.nfc_comp + 3 * lo) == x && ldg(tb.nfc_comp + 3 * lo + 1) == y) return ldg(tb.nfc_comp + 3 * lo + 2);
     return 0;
 }
 
@@ -266,7 +274,7 @@ GTOK_DEV void nfc_chunk_masks(const EncodeArgs& a, long long c0s, uint32_t n, ui
             const int i = 4 * (k - 1) + (bit >> 3);        // byte offset from c0, -3 .. 15
             const uint32_t word = k == 0 ? before : w[k - 1];
             const uint32_t b = (word >> (bit - 7)) & 0xFFu;
-            if ((b >= 0xE4 && b <= 0xE9) || b > 0xF4) continue;   // no attention codepoint begins with these bytes
+            if (b > 0xF4 || ((a.tb.nfc_lead_quiet[b >> 5] >> (b & 31)) & 1u)) continue;   // no attention codepoint begins with this byte
             const uint32_t pos = c0 + i;                   // i >= -3 and c0 >= 16 whenever i < 0
             if (pos >= n) continue;
             uint32_t cp;
@@ -312,6 +320,7 @@ GTOK_DEV void nfc_tile(Blk& blk, const EncodeArgs& a, NfcSmem& sm, int tile) {
             sm.attf[tid == 0 ? 0 : kThreads + 1] = static_cast<uint16_t>(f);
         }
     });
+    mark(27);
     // ---- N2: stretches; bytes each thread will emit ----
     blk.par([&](int tid) {
         const uint32_t c0 = t0 + tid * kPer;
@@ -322,7 +331,7 @@ GTOK_DEV void nfc_tile(Blk& blk, const EncodeArgs& a, NfcSmem& sm, int tile) {
                                       (static_cast<unsigned long long>(sm.attl[tid + 2]) << 32);
         const unsigned long long wf = static_cast<unsigned long long>(sm.attf[tid]) | (static_cast<unsigned long long>(sm.attf[tid + 1]) << 16) |
                                       (static_cast<unsigned long long>(sm.attf[tid + 2]) << 32);
-        uint32_t drop = sm.attf[tid + 1], own = 0, extra = 0;
+        uint32_t drop = sm.attf[tid + 1], own = 0, extra = 0, kept = 0;
         // run starts at c0 .. c0 + 19: the codepoint before such a run may lie in this chunk
         unsigned long long rs = wl & ~(wf << 1);
         if (a.raw_docmask && (wl >> 16)) {
@@ -350,9 +359,15 @@ GTOK_DEV void nfc_tile(Blk& blk, const EncodeArgs& a, NfcSmem& sm, int tile) {
             if (a0 >= c0 && a0 < c0 + kPer) {
                 own |= 1u << (a0 - c0);
                 drop |= 1u << (a0 - c0);
-                extra += nfc_stretch(a, a0, p, n, nullptr, 0, 0);
+                // (the first one's bytes are kept for the write phase when they fit: working a stretch out is one thread's
+                // job while its warp waits, and most of what this kernel costs)
+                const bool keep = own == (1u << (a0 - c0));
+                const uint32_t len = nfc_stretch(a, a0, p, n, keep ? sm.sres[tid] : nullptr, 0, keep ? 12u : 0u);
+                kept = keep && len <= 12u ? len : 0u;
+                extra += len;
             }
         }
+        sm.slen[tid] = static_cast<uint8_t>(popc32(own) == 1 ? kept : 0u);
         sm.drop[tid] = static_cast<uint16_t>(drop);
         sm.own[tid] = static_cast<uint16_t>(own);
         sm.scan[tid] = static_cast<uint32_t>(popc32(valid & ~drop)) + extra;
@@ -364,6 +379,12 @@ GTOK_DEV void nfc_tile(Blk& blk, const EncodeArgs& a, NfcSmem& sm, int tile) {
     const uint32_t base = blk.lookback(a.st0, tile, total, a.ctl);
     mark(25);
     // ---- N4: write ----
+    // Once a document has changed length its bytes no longer land on the 16-byte lines they came from.  The
+    // tile's output is therefore put together in shared memory, shifted so that shared-memory lines are
+    // output lines, and goes out line by line (the ragged first and last line byte by byte: the neighbouring
+    // tiles write the rest of those).  A tile that grows beyond the buffer writes its bytes one by one.
+    const uint32_t shift = base & 15u;
+    const bool staged = shift + total <= static_cast<uint32_t>(kNfcStage);
     blk.par([&](int tid) {
         const uint32_t c0 = t0 + tid * kPer;
         if (c0 >= n) return;
@@ -374,6 +395,38 @@ GTOK_DEV void nfc_tile(Blk& blk, const EncodeArgs& a, NfcSmem& sm, int tile) {
         if (a.raw_docmask) docbits = (ldg(a.raw_docmask + (c0 >> 5)) >> (c0 & 31)) & 0xFFFFu;
         uint32_t w[4];
         load16(a.raw + c0, w);
+        if (staged) {
+            // same walk as below, into the buffer: position `at` of the output is byte at - base + shift there
+            uint32_t la = shift + sm.scan[tid];
+            if (drop == 0 && docbits == 0 && cnt == kPer) {
+                if ((la & 3u) == 0) { uint32_t* d = reinterpret_cast<uint32_t*>(sm.outb + la); d[0] = w[0]; d[1] = w[1]; d[2] = w[2]; d[3] = w[3]; }
+                else for (int i = 0; i < kPer; ++i) sm.outb[la + i] = static_cast<uint8_t>(w[i >> 2] >> (8 * (i & 3)));
+                return;
+            }
+            for (uint32_t i = 0; i < cnt; ++i) {
+                if ((docbits >> i) & 1u) {
+                    const uint32_t r = c0 + i;
+                    uint32_t lo = 0, hi = n_docs + 1;
+                    while (lo < hi) { uint32_t mid = (lo + hi) >> 1; if (ldg(a.raw_doc_off + mid) < r) lo = mid + 1; else hi = mid; }
+                    for (uint32_t d = lo; d <= n_docs && ldg(a.raw_doc_off + d) == r; ++d) a.norm_doc_off[d] = base + (la - shift);
+                }
+                if ((own >> i) & 1u) {
+                    const uint32_t a0 = c0 + i;
+                    uint32_t p = a0;
+                    if (!((sm.attl[tid + 1] >> i) & 1u)) {
+                        uint32_t cp;
+                        p = a0 + static_cast<uint32_t>(nfc_decode(a, a0, n, &cp));
+                    }
+                    const uint32_t kept = sm.slen[tid];
+                    if (kept) { for (uint32_t t = 0; t < kept; ++t) sm.outb[la + t] = sm.sres[tid][t]; la += kept; }
+                    else la += nfc_stretch(a, a0, p, n, sm.outb, la, kNfcStage);
+                } else if (!((drop >> i) & 1u)) {
+                    sm.outb[la] = static_cast<uint8_t>(w[i >> 2] >> (8 * (i & 3)));
+                    ++la;
+                }
+            }
+            return;
+        }
         if (drop == 0 && docbits == 0 && cnt == kPer && (at & 15u) == 0 && at + kPer <= cap) {
 #if defined(__CUDA_ARCH__)
             *reinterpret_cast<uint4*>(a.norm_text + at) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -404,6 +457,25 @@ GTOK_DEV void nfc_tile(Blk& blk, const EncodeArgs& a, NfcSmem& sm, int tile) {
             }
         }
     });
+    if (staged && total) {
+        blk.par([&](int tid) {
+            const uint32_t line0 = base - shift, lines = (shift + total + 15u) / 16u;
+            for (uint32_t l = tid; l < lines; l += kThreads) {
+                const uint32_t lo_b = l == 0 ? shift : 0u;                                      // first and one-past-last byte of the line that are this tile's
+                const uint32_t hi_b = (l + 1) * 16u <= shift + total ? 16u : shift + total - l * 16u;
+                const uint32_t g0 = line0 + l * 16u;
+                if (lo_b == 0 && hi_b == 16u && g0 + 16u <= cap) {
+#if defined(__CUDA_ARCH__)
+                    *reinterpret_cast<uint4*>(a.norm_text + g0) = *reinterpret_cast<const uint4*>(sm.outb + l * 16u);
+#else
+                    for (int i = 0; i < 16; ++i) a.norm_text[g0 + i] = sm.outb[l * 16u + i];
+#endif
+                    continue;
+                }
+                for (uint32_t i = lo_b; i < hi_b; ++i) if (g0 + i < cap) a.norm_text[g0 + i] = sm.outb[l * 16u + i];
+            }
+        });
+    }
     if (static_cast<uint32_t>(tile) + 1 == n_tiles) {
         blk.par([&](int tid) {
             const uint32_t new_n = base + total;

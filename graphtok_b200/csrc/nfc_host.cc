@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <vector>
 
+#include "device_tables.h"
 #include "nfc_tables.h"
 
 namespace gtok {
@@ -141,6 +142,13 @@ void nfc_table_words(NfcWords& out) {
             out.attn_sup.push_back(gtok_nfc_attn[r].hi);
         }
     }
+    // lead bytes under which no such codepoint lies (all of Cyrillic's D0 and D1, the CJK ideographs' E4..E9, ...)
+    for (uint32_t& w : out.lead_quiet) w = 0xFFFFFFFFu;
+    for (uint32_t r = 0; r < GTOK_NFC_ATTN_LEN; ++r)
+        for (uint32_t cp = gtok_nfc_attn[r].lo; cp <= gtok_nfc_attn[r].hi; ++cp) {
+            const uint32_t lead = cp < 0x80 ? cp : cp < 0x800 ? 0xC0u | (cp >> 6) : cp < 0x10000 ? 0xE0u | (cp >> 12) : 0xF0u | (cp >> 18);
+            out.lead_quiet[lead >> 5] &= ~(1u << (lead & 31));
+        }
     out.ccc.clear();
     for (uint32_t i = 0; i < GTOK_NFC_CCC_LEN; ++i) { out.ccc.push_back(gtok_nfc_ccc[i].cp); out.ccc.push_back(gtok_nfc_ccc[i].ccc); }
     out.decomp.clear();
@@ -152,6 +160,15 @@ void nfc_table_words(NfcWords& out) {
     out.comp.clear();
     for (uint32_t i = 0; i < GTOK_NFC_COMP_LEN; ++i) {
         out.comp.push_back(gtok_nfc_comp[i].first); out.comp.push_back(gtok_nfc_comp[i].second); out.comp.push_back(gtok_nfc_comp[i].composite);
+    }
+    uint32_t slots = 1024;
+    while (slots < 4 * GTOK_NFC_COMP_LEN) slots <<= 1;
+    out.comp_hash.assign(static_cast<size_t>(slots) * 4, 0xFFFFFFFFu);
+    for (uint32_t i = 0; i < GTOK_NFC_COMP_LEN; ++i) {
+        uint32_t at = nfc_comp_hash(gtok_nfc_comp[i].first, gtok_nfc_comp[i].second) & (slots - 1);
+        while (out.comp_hash[4 * at] != 0xFFFFFFFFu) at = (at + 1) & (slots - 1);
+        out.comp_hash[4 * at] = gtok_nfc_comp[i].first; out.comp_hash[4 * at + 1] = gtok_nfc_comp[i].second;
+        out.comp_hash[4 * at + 2] = gtok_nfc_comp[i].composite; out.comp_hash[4 * at + 3] = 0;
     }
 }
 
