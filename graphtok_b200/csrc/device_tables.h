@@ -96,6 +96,8 @@ struct DeviceTables {
     const uint32_t* nfc_comp;            // (first, second, composite) primary composites, ascending
     uint32_t nfc_attn_sup_n, nfc_ccc_n, nfc_decomp_n, nfc_comp_n;
     uint32_t nfc_lead_quiet[8];          // bit b: no codepoint of nfc_attn_* begins with byte b in UTF-8
+    const uint32_t* nfc_cp_hash;         // codepoint -> combining class | (index into nfc_decomp + 1) << 8: (codepoint, that) per slot, codepoint = 0xFFFFFFFF: empty
+    uint32_t nfc_cp_hash_mask;
     const uint32_t* nfc_comp_hash;       // nfc_comp as an open-addressed table: (first, second, composite, 0) per slot, first = 0xFFFFFFFF: empty
     uint32_t nfc_comp_hash_mask;
 };
@@ -130,6 +132,7 @@ GTOK_HD uint32_t lit_hash_finish(uint32_t h, uint32_t len) {
     return x;
 }
 // FNV-1a over the bytes, folded with the length; used for the long-token table.
+GTOK_HD uint32_t nfc_cp_hash(uint32_t cp) { return (cp * 0x9E3779B1u) >> 12; }
 GTOK_HD uint32_t nfc_comp_hash(uint32_t first, uint32_t second) { return (first * 0x9E3779B1u) ^ (second * 0x85EBCA6Bu) ^ ((first * 0x9E3779B1u) >> 15); }
 GTOK_HD uint64_t long_hash_step(uint64_t h, uint8_t b) { return (h ^ b) * 1099511628211ULL; }
 constexpr uint64_t kLongHashSeed = 1469598103934665603ULL;

@@ -292,8 +292,10 @@ struct Engine::Impl {
             nfc_table_words(w);
             if (!upload(w.attn_bits, &dt.nfc_attn_bits, owned, err) || !upload(w.attn_sup, &dt.nfc_attn_sup, owned, err) ||
                 !upload(w.ccc, &dt.nfc_ccc, owned, err) || !upload(w.decomp, &dt.nfc_decomp, owned, err) ||
-                !upload(w.comp, &dt.nfc_comp, owned, err) || !upload(w.comp_hash, &dt.nfc_comp_hash, owned, err))
+                !upload(w.comp, &dt.nfc_comp, owned, err) || !upload(w.comp_hash, &dt.nfc_comp_hash, owned, err) ||
+                !upload(w.cp_hash, &dt.nfc_cp_hash, owned, err))
                 return false;
+            dt.nfc_cp_hash_mask = static_cast<uint32_t>(w.cp_hash.size() / 2 - 1);
             dt.nfc_comp_hash_mask = static_cast<uint32_t>(w.comp_hash.size() / 4 - 1);
             dt.nfc_attn_sup_n = static_cast<uint32_t>(w.attn_sup.size() / 2);
             dt.nfc_ccc_n = static_cast<uint32_t>(w.ccc.size() / 2);

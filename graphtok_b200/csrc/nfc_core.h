@@ -85,11 +85,18 @@ GTOK_DEV bool nfc_attention(const DeviceTables& tb, uint32_t cp) {
     return lo > 0 && cp <= ldg(tb.nfc_attn_sup + 2 * (lo - 1) + 1);
 }
 
+// Combining class (low byte) and index + 1 into nfc_decomp (from bit 8) of cp, 0 for a codepoint that has
+// neither: one hashed look-up (a binary search of each list was ten dependent loads per codepoint of a stretch).
+GTOK_DEV uint32_t nfc_cp_info(const DeviceTables& tb, uint32_t cp) {
+    for (uint32_t at = nfc_cp_hash(cp) & tb.nfc_cp_hash_mask;; at = (at + 1) & tb.nfc_cp_hash_mask) {
+        const uint32_t k = ldg(tb.nfc_cp_hash + 2 * at);
+        if (k == cp) return ldg(tb.nfc_cp_hash + 2 * at + 1);
+        if (k == 0xFFFFFFFFu) return 0;
+    }
+}
 GTOK_DEV uint32_t nfc_ccc(const DeviceTables& tb, uint32_t cp) {
     if (cp < 0x300) return 0;
-    uint32_t lo = 0, hi = tb.nfc_ccc_n;
-    while (lo < hi) { uint32_t mid = (lo + hi) >> 1; if (ldg(tb.nfc_ccc + 2 * mid) < cp) lo = mid + 1; else hi = mid; }
-    return (lo < tb.nfc_ccc_n && ldg(tb.nfc_ccc + 2 * lo) == cp) ? ldg(tb.nfc_ccc + 2 * lo + 1) : 0u;
+    return nfc_cp_info(tb, cp) & 0xFFu;
 }
 
 GTOK_DEV uint32_t nfc_compose(const DeviceTables& tb, uint32_t x, uint32_t y) {   // 0 when the pair does not compose
@@ -134,13 +141,18 @@ GTOK_DEV void nfc_push(const DeviceTables& tb, NfcBuf& b, uint32_t cp) {
         return;
     }
     if (cp >= 0xC0) {
-        uint32_t lo = 0, hi = tb.nfc_decomp_n;
-        while (lo < hi) { uint32_t mid = (lo + hi) >> 1; if (ldg(tb.nfc_decomp + 6 * mid) < cp) lo = mid + 1; else hi = mid; }
-        if (lo < tb.nfc_decomp_n && ldg(tb.nfc_decomp + 6 * lo) == cp) {
+        const uint32_t info = nfc_cp_info(tb, cp);
+        if (info >> 8) {
+            const uint32_t lo = (info >> 8) - 1u;
             const uint32_t k = ldg(tb.nfc_decomp + 6 * lo + 1);
             for (uint32_t i = 0; i < k && i < 4; ++i) nfc_push1(tb, b, ldg(tb.nfc_decomp + 6 * lo + 2 + i));
             return;
         }
+        if (b.n >= kNfcMaxCps) { b.over = true; return; }
+        b.cp[b.n] = cp;
+        b.cc[b.n] = static_cast<uint8_t>(info & 0xFFu);
+        ++b.n;
+        return;
     }
     nfc_push1(tb, b, cp);
 }
@@ -457,6 +469,7 @@ GTOK_DEV void nfc_tile(Blk& blk, const EncodeArgs& a, NfcSmem& sm, int tile) {
             }
         }
     });
+    mark(28);
     if (staged && total) {
         blk.par([&](int tid) {
             const uint32_t line0 = base - shift, lines = (shift + total + 15u) / 16u;

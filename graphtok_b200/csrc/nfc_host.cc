@@ -161,6 +161,20 @@ void nfc_table_words(NfcWords& out) {
     for (uint32_t i = 0; i < GTOK_NFC_COMP_LEN; ++i) {
         out.comp.push_back(gtok_nfc_comp[i].first); out.comp.push_back(gtok_nfc_comp[i].second); out.comp.push_back(gtok_nfc_comp[i].composite);
     }
+    {
+        // combining class and decomposition of a codepoint behind one hashed look-up (a codepoint in neither list has no slot)
+        uint32_t n_slots = 1024;
+        while (n_slots < 4 * (GTOK_NFC_CCC_LEN + GTOK_NFC_DECOMP_LEN)) n_slots <<= 1;
+        out.cp_hash.assign(static_cast<size_t>(n_slots) * 2, 0xFFFFFFFFu);
+        auto slot_of = [&](uint32_t cp) -> uint32_t {
+            uint32_t at = nfc_cp_hash(cp) & (n_slots - 1);
+            while (out.cp_hash[2 * at] != 0xFFFFFFFFu && out.cp_hash[2 * at] != cp) at = (at + 1) & (n_slots - 1);
+            if (out.cp_hash[2 * at] == 0xFFFFFFFFu) { out.cp_hash[2 * at] = cp; out.cp_hash[2 * at + 1] = 0; }
+            return at;
+        };
+        for (uint32_t i = 0; i < GTOK_NFC_CCC_LEN; ++i) out.cp_hash[2 * slot_of(gtok_nfc_ccc[i].cp) + 1] |= gtok_nfc_ccc[i].ccc & 0xFFu;
+        for (uint32_t i = 0; i < GTOK_NFC_DECOMP_LEN; ++i) out.cp_hash[2 * slot_of(gtok_nfc_decomp[i].cp) + 1] |= (i + 1) << 8;
+    }
     uint32_t slots = 1024;
     while (slots < 4 * GTOK_NFC_COMP_LEN) slots <<= 1;
     out.comp_hash.assign(static_cast<size_t>(slots) * 4, 0xFFFFFFFFu);

@@ -21,6 +21,7 @@ bool nfc_normalize(const uint8_t* text, size_t len, std::string& out);
 struct NfcWords {
     std::vector<uint32_t> attn_bits, attn_sup, ccc, decomp, comp;
     uint32_t lead_quiet[8];      // bit b: no such codepoint's UTF-8 form begins with byte b
+    std::vector<uint32_t> cp_hash;     // codepoint -> (combining class, index into decomp + 1 or 0): open-addressed (codepoint, class | index << 8) slots, codepoint = 0xFFFFFFFF: empty
     std::vector<uint32_t> comp_hash;   // the composites again as an open-addressed table of (first, second, composite, 0) slots; first = 0xFFFFFFFF: empty
 };
 void nfc_table_words(NfcWords& out);

@@ -239,6 +239,7 @@ int64_t gtok_emul_nfc_device(const uint8_t* text, uint32_t n, const uint32_t* do
     a.tb.nfc_decomp = words.decomp.data(); a.tb.nfc_decomp_n = static_cast<uint32_t>(words.decomp.size() / 6);
     a.tb.nfc_comp = words.comp.data(); a.tb.nfc_comp_n = static_cast<uint32_t>(words.comp.size() / 3);
     for (int i = 0; i < 8; ++i) a.tb.nfc_lead_quiet[i] = words.lead_quiet[i];
+    a.tb.nfc_cp_hash = words.cp_hash.data(); a.tb.nfc_cp_hash_mask = static_cast<uint32_t>(words.cp_hash.size() / 2 - 1);
     a.tb.nfc_comp_hash = words.comp_hash.data(); a.tb.nfc_comp_hash_mask = static_cast<uint32_t>(words.comp_hash.size() / 4 - 1);
     CpuBlk blk;
     blk.reverse = reverse != 0;
