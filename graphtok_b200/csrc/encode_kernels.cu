@@ -121,9 +121,17 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const __grid_constant
     GpuBlk blk;
     const uint32_t n_miss = a.ctl[CTL_NMISS], n_med = a.ctl[CTL_NMED], n_med1 = a.ctl[CTL_NMED1], n_med2 = a.ctl[CTL_NMED2], n_long = a.ctl[CTL_NLONG];
     const uint32_t take_b = a.tb.ignore_merges ? kMedTakeB : kMedBatchB;      // list entries per call of the 17..32-byte class
-    const uint32_t med_batches = (n_med + kMedBatchA - 1) / kMedBatchA, med1_batches = (n_med1 + kMedBatchA1 - 1) / kMedBatchA1;
     const uint32_t med2_batches = (n_med2 + take_b - 1) / take_b;
     const uint32_t short_batches = (n_miss + kMissBatch - 1) / kMissBatch;
+    // Pre-tokens per call of the two longest classes: an arena's worth, unless that leaves most blocks without a call (a
+    // prompt, a shard of a document): then a quarter, so that a call's fetch and pair phases, which the merge chains wait for,
+    // are a quarter as long.
+    uint32_t batch_a = kMedBatchA, batch_a1 = kMedBatchA1;
+    if (2u * ((n_med + kMedBatchA / 4 - 1) / (kMedBatchA / 4) + (n_med1 + kMedBatchA1 / 4 - 1) / (kMedBatchA1 / 4) + med2_batches + short_batches + n_long) < gridDim.x) {
+        batch_a = kMedBatchA / 4;
+        batch_a1 = kMedBatchA1 / 4;
+    }
+    const uint32_t med_batches = (n_med + batch_a - 1) / batch_a, med1_batches = (n_med1 + batch_a1 - 1) / batch_a1;
     // A call of the 17..32-byte class under ignore_merges looks 256 entries up as whole tokens but merges at most 96
     // of them at a time.  With fewer calls than blocks (a prompt rather than a corpus) it hands the rest back for the
     // blocks that got no call; otherwise it works through the rest itself, which keeps the blocks evenly loaded.
@@ -150,8 +158,8 @@ __global__ void __launch_bounds__(kThreads, 4) miss_kernel(const __grid_constant
         const unsigned long long* list = a.gmiss;
         int dir = 1;
         uint32_t first = (t - med_batches - med1_batches - med2_batches) * kMissBatch, count = n_miss, batch = kMissBatch, max_len = kShortWordMax, take = kMissBatch;
-        if (t < med_batches) { list = a.gmed; first = t * kMedBatchA; count = n_med; batch = kMedBatchA; max_len = kMedWordMax; take = kMedBatchA; }
-        else if (t < med_batches + med1_batches) { list = a.gmed1; first = (t - med_batches) * kMedBatchA1; count = n_med1; batch = kMedBatchA1; max_len = kMedSplit1; take = kMedBatchA1; }
+        if (t < med_batches) { list = a.gmed; first = t * batch_a; count = n_med; batch = batch_a; max_len = kMedWordMax; take = batch_a; }
+        else if (t < med_batches + med1_batches) { list = a.gmed1; first = (t - med_batches) * batch_a1; count = n_med1; batch = batch_a1; max_len = kMedSplit1; take = batch_a1; }
         else if (t < med_batches + med1_batches + med2_batches) {
             list = a.gmed + (a.gmed_cap - 1); dir = -1; first = (t - med_batches - med1_batches) * take_b; count = n_med2; batch = kMedBatchB; max_len = kMedSplit; take = take_b;
         }
