@@ -91,6 +91,8 @@ __global__ void __launch_bounds__(kThreads, 1) tiny_kernel(const __grid_constant
         if (longest > static_cast<uint32_t>(kMedSplit1)) { batch = kMedBatchA; max_len = kMedWordMax; }
         else if (longest > static_cast<uint32_t>(kMedSplit)) { batch = kMedBatchA1; max_len = kMedSplit1; }
         else if (longest > static_cast<uint32_t>(kShortWordMax)) { batch = kMedBatchB; max_len = kMedSplit; }
+        // (no more arena than there are entries: the fetch and pair phases pass over batch * max_len slots)
+        if (n_miss < batch) batch = n_miss ? (n_miss + 3u) & ~3u : 4u;
         for (uint32_t first = 0; first < n_miss; first += batch) miss_batch(blk, a, ms, a.gmiss, 1, first, n_miss, batch, max_len, batch);
         for (uint32_t li = 0; li < n_long; ++li) long_word(blk, a, ms, li);
     }
