@@ -305,6 +305,15 @@ int64_t gtok_emul_decode(void* h, const uint32_t* ids, uint32_t n, uint8_t* out,
     return total;
 }
 
+// The bit scans the whitespace and newline walks use inside a tile's window, on planes the caller makes up:
+// s, cr: one bit per byte (16 bits per entry, entries in eight-byte aligned rows), doc: 32 bits per word.
+int gtok_emul_plain_ws_end(const uint16_t* s, const uint16_t* cr, const uint32_t* doc, int i, int i_end) {
+    return gtok::plain_ws_end(s, cr, doc, i, i_end);
+}
+int gtok_emul_newline_run_begin(const uint16_t* cr, const uint32_t* doc, int i, int i_begin) {
+    return gtok::newline_run_begin(cr, doc, i, i_begin);
+}
+
 int gtok_emul_plan_chunks(void* h, const uint8_t* text, uint64_t len, uint32_t n_parts, uint64_t* out) {
     std::vector<uint64_t> cuts;
     gtok::plan_chunks(static_cast<Emul*>(h)->hv, text, len, n_parts, cuts);

@@ -245,3 +245,51 @@ def test_emul_decode_errors(emuls):
     assert bits & 64                                                # an id outside the vocabulary
     got, total, bits = e.decode(np.zeros(0, dtype=np.uint32))
     assert total == 0 and bits == 0
+
+
+def test_window_bit_scans_against_plain_loops(built):
+    """plain_ws_end / newline_run_begin (csrc/encode_core.h): the first byte at or after i that is not plain one-byte
+    whitespace of the running document, and the first of the newline bytes that end at i, from the bit planes --
+    against byte-by-byte loops over the same bits, on random planes with long clean stretches, from every kind of
+    start position and bound."""
+    import ctypes, random
+    lib = ctypes.CDLL(oracle_lib.build_emul())
+    lib.gtok_emul_plain_ws_end.restype = ctypes.c_int
+    lib.gtok_emul_plain_ws_end.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int]
+    lib.gtok_emul_newline_run_begin.restype = ctypes.c_int
+    lib.gtok_emul_newline_run_begin.argtypes = [ctypes.c_void_p] * 2 + [ctypes.c_int, ctypes.c_int]
+    rng = random.Random(77)
+    n = 8192
+    for trial in range(60):
+        # whitespace / newline / document-start bits per byte: mostly long clean stretches with a few breaks
+        density = rng.choice((0.0, 0.0005, 0.003, 0.02, 0.3))
+        ws = np.ones(n, dtype=bool)
+        cr = np.zeros(n, dtype=bool)
+        doc = np.zeros(n, dtype=bool)
+        for arr, val in ((ws, False), (cr, True), (doc, True)):
+            for _ in range(int(n * density) + rng.randint(0, 2)):
+                arr[rng.randrange(n)] = val
+        if trial % 3 == 0:
+            cr[:] = ~cr                                           # newline stretches for the backward scan
+        pack16 = lambda b: np.packbits(b.reshape(-1, 16), axis=1, bitorder="little").view(np.uint16).reshape(-1)
+        pack32 = lambda b: np.packbits(b.reshape(-1, 32), axis=1, bitorder="little").view(np.uint32).reshape(-1)
+        s16 = np.concatenate([pack16(ws), np.zeros(8, np.uint16)])
+        c16 = np.concatenate([pack16(cr), np.zeros(8, np.uint16)])
+        d32 = np.concatenate([pack32(doc), np.zeros(4, np.uint32)])
+        good_f = ws & ~cr & ~doc
+        good_b = cr & ~doc
+        for _ in range(200):
+            i = rng.choice((rng.randrange(n), rng.randrange(n) & ~63, (rng.randrange(n) & ~63) | 63, 0, n - 1))
+            i_end = rng.choice((n, rng.randrange(n + 1), min(n, i + rng.randrange(600))))
+            want = i_end
+            if i < i_end:
+                bad = np.flatnonzero(~good_f[i:i_end])
+                if bad.size: want = i + int(bad[0])
+            assert lib.gtok_emul_plain_ws_end(s16.ctypes.data, c16.ctypes.data, d32.ctypes.data, i, i_end) == want, (trial, i, i_end)
+            i_begin = rng.choice((0, rng.randrange(n), max(0, i - rng.randrange(600))))
+            if i < i_begin:
+                want_b = i + 1
+            else:
+                bad = np.flatnonzero(~good_b[i_begin:i + 1])
+                want_b = i_begin if not bad.size else i_begin + int(bad[-1]) + 1
+            assert lib.gtok_emul_newline_run_begin(c16.ctypes.data, d32.ctypes.data, i, i_begin) == want_b, (trial, i, i_begin)
