@@ -305,6 +305,31 @@ int64_t gtok_emul_decode(void* h, const uint32_t* ids, uint32_t n, uint8_t* out,
     return total;
 }
 
+// The normalisation kernel's table look-ups (hashed on the device side), one codepoint or pair at a time.
+static gtok::DeviceTables nfc_lookup_tables(gtok::NfcWords& words) {
+    gtok::nfc_table_words(words);
+    gtok::DeviceTables tb;
+    std::memset(&tb, 0, sizeof tb);
+    tb.nfc_cp_hash = words.cp_hash.data(); tb.nfc_cp_hash_mask = static_cast<uint32_t>(words.cp_hash.size() / 2 - 1);
+    tb.nfc_comp_hash = words.comp_hash.data(); tb.nfc_comp_hash_mask = static_cast<uint32_t>(words.comp_hash.size() / 4 - 1);
+    tb.nfc_decomp = words.decomp.data(); tb.nfc_decomp_n = static_cast<uint32_t>(words.decomp.size() / 6);
+    return tb;
+}
+// out[cp] = combining class | (number of codepoints in the full canonical decomposition, 0 = none) << 8, for cp < n
+void gtok_emul_nfc_cp_info(uint32_t* out, uint32_t n) {
+    gtok::NfcWords words;
+    const gtok::DeviceTables tb = nfc_lookup_tables(words);
+    for (uint32_t cp = 0; cp < n; ++cp) {
+        const uint32_t info = cp >= 0xC0 ? gtok::nfc_cp_info(tb, cp) : 0u;
+        out[cp] = gtok::nfc_ccc(tb, cp) | ((info >> 8) ? tb.nfc_decomp[6 * ((info >> 8) - 1) + 1] << 8 : 0u);
+    }
+}
+void gtok_emul_nfc_compose(const uint32_t* first, const uint32_t* second, uint32_t* out, uint32_t n) {
+    gtok::NfcWords words;
+    const gtok::DeviceTables tb = nfc_lookup_tables(words);
+    for (uint32_t i = 0; i < n; ++i) out[i] = gtok::nfc_compose(tb, first[i], second[i]);
+}
+
 // The bit scans the whitespace and newline walks use inside a tile's window, on planes the caller makes up:
 // s, cr: one bit per byte (16 bits per entry, entries in eight-byte aligned rows), doc: 32 bits per word.
 int gtok_emul_plain_ws_end(const uint16_t* s, const uint16_t* cr, const uint32_t* doc, int i, int i_end) {

@@ -293,3 +293,41 @@ def test_window_bit_scans_against_plain_loops(built):
                 bad = np.flatnonzero(~good_b[i_begin:i + 1])
                 want_b = i_begin if not bad.size else i_begin + int(bad[-1]) + 1
             assert lib.gtok_emul_newline_run_begin(c16.ctypes.data, d32.ctypes.data, i, i_begin) == want_b, (trial, i, i_begin)
+
+
+def test_normaliser_table_lookups_cover_every_codepoint_and_pair(built):
+    """The device side finds a codepoint's combining class and decomposition, and a pair's composite, in hashed
+    tables (csrc/nfc_core.h: nfc_cp_info, nfc_compose).  Every codepoint and every composing pair against
+    Python's unicodedata, and pairs that do not compose."""
+    import ctypes, random, unicodedata
+    lib = ctypes.CDLL(oracle_lib.build_emul())
+    n = 0x110000
+    info = np.zeros(n, dtype=np.uint32)
+    lib.gtok_emul_nfc_cp_info(ctypes.c_void_p(info.ctypes.data), ctypes.c_uint32(n))
+    firsts, seconds, wants = [], [], []
+    for cp in range(n):
+        if 0xD800 <= cp <= 0xDFFF:
+            continue
+        ch = chr(cp)
+        assert (info[cp] & 0xFF) == unicodedata.combining(ch), hex(cp)
+        hangul = 0xAC00 <= cp < 0xAC00 + 11172
+        full = unicodedata.normalize("NFD", ch)
+        if not hangul:                                            # Hangul syllables are decomposed by arithmetic, not from the table
+            assert (info[cp] >> 8) == (len(full) if full != ch else 0), hex(cp)
+        dec = unicodedata.decomposition(ch)
+        if dec and not dec.startswith("<") and len(dec.split()) == 2:
+            a, b = (int(x, 16) for x in dec.split())
+            back = unicodedata.normalize("NFC", chr(a) + chr(b))
+            firsts.append(a); seconds.append(b); wants.append(ord(back) if len(back) == 1 else 0)
+    rng = random.Random(5)
+    pool = sorted(set(firsts) | set(seconds))
+    for _ in range(20000):                                        # other pairs of the same codepoints: whatever NFC says
+        a, b = rng.choice(pool), rng.choice(pool)
+        back = unicodedata.normalize("NFC", chr(a) + chr(b))
+        if unicodedata.normalize("NFD", chr(a)) != chr(a) or unicodedata.normalize("NFD", chr(b)) != chr(b):
+            continue                                              # (the kernel composes decomposed input only)
+        firsts.append(a); seconds.append(b); wants.append(ord(back) if len(back) == 1 else 0)
+    f = np.array(firsts, dtype=np.uint32); s2 = np.array(seconds, dtype=np.uint32); out = np.zeros(len(firsts), dtype=np.uint32)
+    lib.gtok_emul_nfc_compose(ctypes.c_void_p(f.ctypes.data), ctypes.c_void_p(s2.ctypes.data), ctypes.c_void_p(out.ctypes.data), ctypes.c_uint32(len(firsts)))
+    bad = np.flatnonzero(out != np.array(wants, dtype=np.uint32))
+    assert bad.size == 0, [(hex(firsts[i]), hex(seconds[i]), hex(int(out[i])), hex(wants[i])) for i in bad[:5]]
