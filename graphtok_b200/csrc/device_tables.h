@@ -81,7 +81,7 @@ struct DeviceTables {
     const LitSlot* littab;      uint32_t lit_mask;
     uint32_t lit_n_lens;
     uint32_t lit_lens[16];
-    uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5, 3 DeepSeek-V3
+    uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5, 3 DeepSeek-V3, 4 Gemma-3
     uint32_t uc_wide;                    // the class table is the wide one (unicode_wide_table.h: four bits per codepoint)
     uint32_t ignore_merges;
     uint32_t monotone;

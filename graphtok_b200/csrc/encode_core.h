@@ -1171,6 +1171,66 @@ GTOK_DEV bool ds_mark_takes_letters(const Win& w, int m, uint8_t am) {
     if (q < 0) return true;
     return !((aq & A_CLS) == A_P || (aq & A_SP));
 }
+// ---- Gemma-3 shape ----
+// The model merges the characters of the whole text, so any cut must be one that no rule can reach across.  Two
+// kinds are taken.  A byte that is not part of a whole character of the vocabulary (a character the vocabulary lacks,
+// malformed UTF-8, a character cut by a document's end) stands alone: the model spells it as its "<0xNN>" token,
+// which no rule mentions, and keeping such bytes apart is also what keeps the loader's byte-to-character rules from
+// ever seeing them.  And a space (U+0020, which the normaliser writes as U+2581, or that character itself) opens a
+// pre-token unless some rule's left side ends with the character before it while its right side begins with U+2581
+// (class 6 in the vocabulary's class table; 0 any other character of the vocabulary, 3 everything else).
+// Every byte of the tile is decided here, by strict decoding of the bytes around it.
+GTOK_DEV bool sp_docstart_at(const Win& w, int p) {
+    const int i = p - w.lo;
+    if (i >= 0 && i < kPWin) return (w.sm->dsw[i >> 5] >> (i & 31)) & 1u;
+    return is_docstart_global(*w.a, p);
+}
+// The whole character that holds byte p, inside p's document: its first byte in *start, its codepoint in *cp; 0 when
+// there is none, else its width.
+GTOK_DEV int sp_char_at(const Win& w, int p, int* start, uint32_t* cp) {
+    int s = p;
+    for (int k = 0; (text_at(w, s) & 0xC0u) == 0x80u; ++k) {
+        if (k == 3 || s == 0 || sp_docstart_at(w, s)) return 0;
+        --s;
+    }
+    const uint32_t b0 = text_at(w, s);
+    int width;
+    if (b0 < 0x80u) width = 1;
+    else if (b0 >= 0xC2u && b0 <= 0xDFu) width = 2;
+    else if (b0 >= 0xE0u && b0 <= 0xEFu) width = 3;
+    else if (b0 >= 0xF0u && b0 <= 0xF4u) width = 4;
+    else return 0;
+    if (s + width > w.n || p >= s + width) return 0;
+    uint32_t v = width == 1 ? b0 : width == 2 ? (b0 & 0x1Fu) : width == 3 ? (b0 & 0x0Fu) : (b0 & 0x07u);
+    for (int k = 1; k < width; ++k) {
+        const uint32_t b = text_at(w, s + k);
+        if ((b & 0xC0u) != 0x80u || sp_docstart_at(w, s + k)) return 0;
+        v = (v << 6) | (b & 0x3Fu);
+    }
+    if ((width == 3 && (v < 0x800u || (v >= 0xD800u && v <= 0xDFFFu))) || (width == 4 && (v < 0x10000u || v > 0x10FFFFu))) return 0;
+    *start = s;
+    *cp = v;
+    return width;
+}
+GTOK_DEV uint32_t sp_class(const EncodeArgs& a, uint32_t cp) {
+    return uc_class([&](uint32_t i) { return static_cast<uint32_t>(ldg(a.tb.uc_stage1 + i)); }, [&](uint32_t i) { return ldg(a.tb.uc_stage2 + i); }, cp, true);
+}
+GTOK_DEV_NOINLINE bool is_boundary_sp(const Win& w, int p) {
+    if (p == 0 || sp_docstart_at(w, p)) return true;
+    int s = 0, s1 = 0;
+    uint32_t cp = 0, c1 = 0;
+    if (!sp_char_at(w, p, &s, &cp) || sp_class(*w.a, cp) == 3u) return true;       // on its own, byte by byte
+    if (s != p) return false;                                                         // inside a character
+    // what ends right before p: an added token, a byte on its own, or a character
+    const int q = prev_lead(w, p);
+    if (q < 0 || (attr_at(w, q) & A_CLS) == A_ADDED) return true;
+    if (!sp_char_at(w, p - 1, &s1, &c1)) return true;
+    const uint32_t k1 = sp_class(*w.a, c1);
+    if (k1 == 3u) return true;
+    if (cp == 0x20u || cp == 0x2581u) return k1 != 6u;
+    return false;
+}
+
 GTOK_DEV_NOINLINE bool is_boundary_deepseek(const Win& w, int p, uint8_t a0, bool* pending, bool* nstart) {
     *pending = false;
     const int cur = a0 & A_CLS;
@@ -1868,7 +1928,14 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
         // (a continuation byte right after an apostrophe stretches a contraction past three bytes)
         // An added-token literal is its start bit plus continuation bits; those long stretches are
         // harmless to the algebra (the literal has no class, so its neighbours see "nothing").
-        if (kWide) {
+        if (kWide && family == 4) {
+            // Gemma-3 shape: every byte outside an added-token literal is decided one by one (is_boundary_sp)
+            unc = ~(ADraw & C);
+            for (int bit = 16; bit < 48; ++bit) {
+                const int p = lo + ww * 32 + bit - 16;
+                if (p < 0 || p >= n) unc &= ~(1ull << bit);
+            }
+        } else if (kWide) {
             // DeepSeek-V3 (see is_boundary_deepseek for the rules; here the same over whole planes).
             auto xload = [&](int k) -> uint64_t {
                 const uint32_t* pw = reinterpret_cast<const uint32_t*>(xplane(sm, k));
@@ -2019,7 +2086,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             const uint64_t m = 1ull << bit;
             if ((a0 & A_CLS) == A_ADDED) { bnd |= m; continue; }
             bool pending = false, ns = false;
-            const bool bb = kWide ? is_boundary_deepseek(w, p, a0, &pending, &ns) : is_boundary(w, p, a0, family, &pending, &ns);
+            const bool bb = kWide ? (family == 4 ? is_boundary_sp(w, p) : is_boundary_deepseek(w, p, a0, &pending, &ns)) : is_boundary(w, p, a0, family, &pending, &ns);
             if (bb) bnd |= m; else bnd &= ~m;
             if (pending) pend |= m; else pend &= ~m;
             if ((a0 & A_CLS) == A_N) { if (ns) nstart |= m; else nstart &= ~m; }
@@ -2036,7 +2103,7 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
 
     mark(4);
     // ---- P4: index of each digit in its run (\p{N}{1,3} of Llama-3 and DeepSeek-V3) ----
-    if (family == 1 || kWide) {
+    if (family == 1 || (kWide && family == 3)) {
         const uint32_t* leadw = reinterpret_cast<const uint32_t*>(sm.lead16);
         const uint32_t* nleadw = reinterpret_cast<const uint32_t*>(sm.nlead16);
         const uint32_t* nstartw = reinterpret_cast<const uint32_t*>(sm.nstart16);
@@ -2599,7 +2666,7 @@ GTOK_DEV void words_tile(Blk& blk, const EncodeArgs& a, WordsSmem& sm, int tile)
                 if (e != 0xFFFFu) len = e - o;
                 else if (t0 + kTile + 64 >= n) len = n - g;
                 if (len && g + len > n) len = n - g;
-                if ((sm.txt[o] & 0xC0u) == 0x80u) continue;      // stray continuation bytes opening a document
+                if ((sm.txt[o] & 0xC0u) == 0x80u && tb.family != 4u) continue;      // stray continuation bytes opening a document (the Gemma-3 shape spells every byte)
                 if ((sm.am[o >> 5] >> (o & 31)) & 1u) {
                     sm.tok[o] = a.stage[g];                 // an added token: its id was left here when the literal was matched
                     ++known;

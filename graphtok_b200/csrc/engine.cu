@@ -278,6 +278,7 @@ struct Engine::Impl {
             s1.assign(gtok_uw_stage1_init, gtok_uw_stage1_init + GTOK_UW_STAGE1_LEN);
             s2.assign(gtok_uw_stage2_init, gtok_uw_stage2_init + GTOK_UW_STAGE2_LEN);
         }
+        if (ht.family == 4) { s1 = ht.sp_stage1; s2 = ht.sp_stage2; }      // Gemma-3 shape: the vocabulary's own characters
         if (!upload(ht.merge, &dt.merge, owned, err) || !upload(ht.word, &dt.word, owned, err) ||
             !upload(ht.longtab, &dt.longtab, owned, err) || !upload(ht.long_blob, &dt.long_blob, owned, err) ||
             !upload(ht.byte_to_id, &dt.byte_to_id, owned, err) || !upload(s1, &dt.uc_stage1, owned, err) ||

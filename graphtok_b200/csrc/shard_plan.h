@@ -15,6 +15,7 @@
 #pragma once
 #include <cstdint>
 #include <string>
+#include <algorithm>
 #include <vector>
 
 #include "vocab_host.h"
@@ -27,6 +28,13 @@ inline bool ascii_letter(uint8_t b) { return (b >= 'a' && b <= 'z') || (b >= 'A'
 inline bool safe_cut(const HostVocab& hv, const uint8_t* text, uint64_t len, uint64_t p) {
     if (p == 0 || p + 1 >= len) return false;
     if (!(ascii_letter(text[p - 1]) && text[p] == 0x20 && ascii_letter(text[p + 1]))) return false;
+    // (Gemma-3 shape: the space is the character U+2581 of a model that merges across everything; the cut holds
+    // when no rule can join the letter before it to a U+2581 after it and the vocabulary has that letter)
+    if (hv.family == Family::Gemma3) {
+        if (std::binary_search(hv.sp_before_bar.begin(), hv.sp_before_bar.end(), static_cast<uint32_t>(text[p - 1]))) return false;
+        auto it = std::lower_bound(hv.sp_chars.begin(), hv.sp_chars.end(), std::make_pair(static_cast<uint32_t>(text[p - 1]), 0u));
+        if (it == hv.sp_chars.end() || it->first != text[p - 1]) return true;      // a byte on its own: a cut on either side of it
+    }
     // No added-token literal occurrence may overlap the three bytes.
     if (hv.added_max_bytes) {
         uint64_t lo = p + 2 > hv.added_max_bytes ? p + 2 - hv.added_max_bytes : 0;

@@ -120,11 +120,41 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
         break;
     }
 
+    // ---- Gemma-3 shape: the vocabulary's characters as a class table ------------
+    out.sp_stage1.clear();
+    out.sp_stage2.clear();
+    if (hv.family == Family::Gemma3) {
+        std::map<std::vector<uint32_t>, uint16_t> leaves;      // sixteen words of 4-bit classes -> leaf number
+        out.sp_stage1.assign(0x110000 / 128, 0);
+        size_t ci = 0, bi = 0;
+        for (uint32_t block = 0; block < 0x110000 / 128; ++block) {
+            std::vector<uint32_t> leaf(16, 0x33333333u);
+            const uint32_t lo = block * 128, hi = lo + 128;
+            while (ci < hv.sp_chars.size() && hv.sp_chars[ci].first < lo) ++ci;
+            while (bi < hv.sp_before_bar.size() && hv.sp_before_bar[bi] < lo) ++bi;
+            for (size_t k = ci; k < hv.sp_chars.size() && hv.sp_chars[k].first < hi; ++k) {
+                const uint32_t o = hv.sp_chars[k].first - lo;
+                leaf[o >> 3] &= ~(15u << ((o & 7) * 4));
+            }
+            for (size_t k = bi; k < hv.sp_before_bar.size() && hv.sp_before_bar[k] < hi; ++k) {
+                const uint32_t o = hv.sp_before_bar[k] - lo;
+                if (((leaf[o >> 3] >> ((o & 7) * 4)) & 15u) == 0) leaf[o >> 3] |= 6u << ((o & 7) * 4);
+            }
+            auto it = leaves.find(leaf);
+            if (it == leaves.end()) {
+                if (leaves.size() >= 0xFFFF) { err = "too many distinct blocks of characters"; return false; }
+                it = leaves.emplace(leaf, static_cast<uint16_t>(leaves.size())).first;
+                out.sp_stage2.insert(out.sp_stage2.end(), leaf.begin(), leaf.end());
+            }
+            out.sp_stage1[block] = it->second;
+        }
+    }
+
     // ---- whole-word table -------------------------------------------------
     std::vector<std::pair<std::string, uint32_t>> entries;   // (bytes, id)
     {
         std::map<std::string, uint32_t> lowest;   // the lowest id wins for a repeated spelling
-        for (uint32_t id = 0; id < hv.token_bytes.size(); ++id) {
+        for (uint32_t id = 0; id < hv.token_bytes.size() && id < hv.vocab_size; ++id) {     // (ids beyond: partly assembled characters of a Gemma-3 vocabulary)
             const std::string& b = hv.token_bytes[id];
             if (b.empty()) continue;
             if (!hv.ignore_merges) {

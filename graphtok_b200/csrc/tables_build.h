@@ -26,6 +26,10 @@ struct HostTables {
     uint32_t lit1_bits[8] = {}, lit2_bits[8] = {}, lit_single = 0;
     std::vector<LitSlot> littab;
     uint32_t lit_n_lens = 0, lit_lens[kLitLens] = {};
+    // Gemma-3 shape: a class per codepoint in the layout of the wide class table (uc_class(..., wide)), made from the
+    // vocabulary: 0 a character of the vocabulary, 6 one that a rule may join to a U+2581 after it, 3 any other codepoint
+    std::vector<uint16_t> sp_stage1;
+    std::vector<uint32_t> sp_stage2;
     uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0, added_alpha_end = 0, lit_first = 0, lit_first_n = 0;
 };
 
@@ -46,7 +50,7 @@ inline void fill_table_scalars(const HostTables& ht, DeviceTables& tb) {
     tb.lit_n_lens = ht.lit_n_lens;
     for (int i = 0; i < kLitLens; ++i) tb.lit_lens[i] = ht.lit_lens[i];
     tb.family = ht.family;
-    tb.uc_wide = ht.family == 3 ? 1u : 0u;
+    tb.uc_wide = ht.family == 3 || ht.family == 4 ? 1u : 0u;
     tb.ignore_merges = ht.ignore_merges;
     tb.monotone = ht.monotone;
     tb.added_ws = ht.added_ws;

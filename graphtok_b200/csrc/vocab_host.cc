@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <fstream>
+#include <map>
 #include <sstream>
 #include <unordered_map>
 
@@ -110,11 +111,53 @@ std::string decode_token(const std::string& s) {
     return out;
 }
 
+// Strict decode of one UTF-8 character at s[i]; 0 when there is none.
+size_t utf8_char(const std::string& s, size_t i, uint32_t* cp) {
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(s.data());
+    const size_t n = s.size();
+    if (i >= n) return 0;
+    const unsigned char c = p[i];
+    if (c < 0x80) { *cp = c; return 1; }
+    auto cont = [&](size_t k) { return i + k < n && (p[i + k] & 0xC0) == 0x80; };
+    if (c >= 0xC2 && c <= 0xDF && cont(1)) { *cp = ((c & 0x1Fu) << 6) | (p[i + 1] & 0x3Fu); return 2; }
+    if ((c & 0xF0) == 0xE0 && cont(1) && cont(2)) {
+        *cp = ((c & 0x0Fu) << 12) | ((p[i + 1] & 0x3Fu) << 6) | (p[i + 2] & 0x3Fu);
+        return (*cp >= 0x800 && !(*cp >= 0xD800 && *cp <= 0xDFFF)) ? 3 : 0;
+    }
+    if (c >= 0xF0 && c <= 0xF4 && cont(1) && cont(2) && cont(3)) {
+        *cp = ((c & 0x07u) << 18) | ((p[i + 1] & 0x3Fu) << 12) | ((p[i + 2] & 0x3Fu) << 6) | (p[i + 3] & 0x3Fu);
+        return (*cp >= 0x10000 && *cp <= 0x10FFFF) ? 4 : 0;
+    }
+    return 0;
+}
+const char* const kBar = "\xe2\x96\x81";      // U+2581, what the Gemma-3 normaliser writes for a space
+
+// Gemma-3 shape: a token string is raw UTF-8.  What it decodes to: U+2581 as a space, "<0xNN>" as that byte.
+// fallback_byte: 0..255 for a "<0xNN>" token, else -1.
+std::string decode_sp_token(const std::string& s, int* fallback_byte) {
+    *fallback_byte = -1;
+    if (s.size() == 6 && s[0] == '<' && s[1] == '0' && s[2] == 'x' && s[5] == '>') {
+        auto hex = [](char c) { return c >= '0' && c <= '9' ? c - '0' : c >= 'A' && c <= 'F' ? c - 'A' + 10 : -1; };
+        const int h = hex(s[3]), l = hex(s[4]);
+        if (h >= 0 && l >= 0) { *fallback_byte = h * 16 + l; return std::string(1, static_cast<char>(h * 16 + l)); }
+    }
+    std::string out;
+    for (size_t i = 0; i < s.size();) {
+        if (s.compare(i, 3, kBar) == 0) { out.push_back(' '); i += 3; }
+        else out.push_back(s[i++]);
+    }
+    return out;
+}
+
 std::string utf8_of(uint32_t cp) {
     std::string s;
     if (cp < 0x80) s.push_back(static_cast<char>(cp));
     else if (cp < 0x800) { s.push_back(static_cast<char>(0xC0 | (cp >> 6))); s.push_back(static_cast<char>(0x80 | (cp & 0x3F))); }
-    else { s.push_back(static_cast<char>(0xE0 | (cp >> 12))); s.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F))); s.push_back(static_cast<char>(0x80 | (cp & 0x3F))); }
+    else if (cp < 0x10000) { s.push_back(static_cast<char>(0xE0 | (cp >> 12))); s.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F))); s.push_back(static_cast<char>(0x80 | (cp & 0x3F))); }
+    else {
+        s.push_back(static_cast<char>(0xF0 | (cp >> 18))); s.push_back(static_cast<char>(0x80 | ((cp >> 12) & 0x3F)));
+        s.push_back(static_cast<char>(0x80 | ((cp >> 6) & 0x3F))); s.push_back(static_cast<char>(0x80 | (cp & 0x3F)));
+    }
     return s;
 }
 
@@ -129,6 +172,7 @@ const char* family_name(Family f) {
         case Family::Llama3: return "Llama3";
         case Family::Qwen25: return "Qwen25";
         case Family::DeepSeekV3: return "DeepSeekV3";
+        case Family::Gemma3: return "Gemma3";
     }
     return "?";
 }
@@ -190,20 +234,33 @@ bool load_tokenizer_json(const std::string& path, HostVocab& out, std::string& e
             }
         }
     }
+    if (!matched && norm && norm->is_object() && str_is(norm, "type", "Replace") && str_is(norm, "content", kBar) && pt && pt->is_object()) {
+        // Gemma-3: every space becomes U+2581, then a Split on the (now absent) space (src/vocab.cc:267-281)
+        const Value* npat = norm->find("pattern");
+        const Value* ppat = pt->find("pattern");
+        if (npat && npat->is_object() && str_is(npat, "String", " ") && str_is(pt, "type", "Split") && ppat && ppat->is_object() &&
+            str_is(ppat, "String", " ") && str_is(pt, "behavior", "MergedWithPrevious") && bool_is(pt, "invert", false, false)) {
+            out.family = Family::Gemma3;
+            matched = true;
+        }
+    }
     if (!matched) {
-        err = "unsupported pre_tokenizer/normalizer pipeline (only the exact GPT-2, Llama-3, Qwen2.5 and DeepSeek-V3 shapes load)";
+        err = "unsupported pre_tokenizer/normalizer pipeline (only the exact GPT-2, Llama-3, Qwen2.5, DeepSeek-V3 and Gemma-3 shapes load)";
         return false;
     }
     // ---- model options ---------------------------------------------------
-    const bool llama = out.family == Family::Llama3;
+    const bool llama = out.family == Family::Llama3, gemma = out.family == Family::Gemma3;
     if (!null_or_absent(model, "dropout") || !empty_or_absent(model, "continuing_subword_prefix") ||
-        !empty_or_absent(model, "end_of_word_suffix") || !bool_is(model, "byte_fallback", false, false) ||
-        !bool_is(model, "fuse_unk", false, false) || !bool_is(model, "ignore_merges", llama, false) ||
-        !null_or_absent(model, "unk_token")) {
+        !empty_or_absent(model, "end_of_word_suffix") || !bool_is(model, "byte_fallback", gemma, false) ||
+        !bool_is(model, "fuse_unk", gemma, false) || !bool_is(model, "ignore_merges", llama, false) ||
+        (gemma ? !str_is(model, "unk_token", "<unk>") : !null_or_absent(model, "unk_token"))) {
         err = "unsupported BPE model options for this family";
         return false;
     }
     out.ignore_merges = llama;
+    out.sp_synthetic = 0;
+    out.sp_chars.clear();
+    out.sp_before_bar.clear();
 
     // ---- vocab -----------------------------------------------------------
     std::unordered_map<std::string, uint32_t> id_of;
@@ -220,10 +277,64 @@ bool load_tokenizer_json(const std::string& path, HostVocab& out, std::string& e
             if (id > (1u << 24)) { err = "vocab id too large"; return false; }
             out.token_bytes.resize(id + 1);
         }
-        out.token_bytes[id] = decode_token(m.first);
+        if (gemma) {
+            int fb = -1;
+            // (a token with a literal space in it can never be matched: the normaliser leaves no space in the text)
+            out.token_bytes[id] = m.first.find(' ') == std::string::npos ? decode_sp_token(m.first, &fb) : std::string();
+            if (fb >= 0) out.sp_fallback[fb] = id + 1;          // + 1: 0 = not seen yet
+            uint32_t cp = 0;
+            if (fb < 0 && utf8_char(m.first, 0, &cp) == m.first.size() && cp != ' ') out.sp_chars.emplace_back(cp, id);
+        } else {
+            out.token_bytes[id] = decode_token(m.first);
+        }
         id_of[m.first] = id;    // a repeated key keeps its last id, like a JSON object
     }
-    for (int b = 0; b < 256; ++b) {
+    std::vector<MergeRule> synthetic;
+    if (gemma) {
+        // (the ids made up below must lie beyond every id of the file, those of its added tokens included)
+        if (const Value* at = root.find("added_tokens"); at && at->is_array())
+            for (const Value& t : at->arr) {
+                const Value* idv = t.is_object() ? t.find("id") : nullptr;
+                if (idv && idv->is_number() && idv->inum >= 0 && idv->inum <= (1 << 24) && static_cast<size_t>(idv->inum) >= out.token_bytes.size())
+                    out.token_bytes.resize(static_cast<size_t>(idv->inum) + 1);
+            }
+        for (int b = 0; b < 256; ++b) {
+            if (!out.sp_fallback[b]) {
+                char buf[64];
+                std::snprintf(buf, sizeof buf, "missing byte-fallback token <0x%02X>", b);
+                err = buf;
+                return false;
+            }
+            --out.sp_fallback[b];
+        }
+        std::sort(out.sp_chars.begin(), out.sp_chars.end());
+        uint32_t bar_id = 0xFFFFFFFFu;
+        for (const auto& c : out.sp_chars) if (c.first == 0x2581u) bar_id = c.second;
+        if (bar_id == 0xFFFFFFFFu) { err = "the vocabulary has no token for U+2581"; return false; }
+        out.sp_chars.emplace_back(0x20u, bar_id);
+        std::sort(out.sp_chars.begin(), out.sp_chars.end());
+        for (int b = 0; b < 256; ++b) out.byte_to_id[b] = out.sp_fallback[b];
+        // every character of the vocabulary from its bytes: (b0, b1) -> partial, (partial, b2) -> ... -> the character's id
+        std::map<std::pair<uint32_t, uint32_t>, uint32_t> made;
+        for (const auto& c : out.sp_chars) {
+            if (c.first < 0x80) { out.byte_to_id[c.first] = c.second; continue; }
+            const std::string bytes = utf8_of(c.first);
+            uint32_t cur = out.sp_fallback[static_cast<unsigned char>(bytes[0])];
+            for (size_t k = 1; k < bytes.size(); ++k) {
+                const uint32_t nxt = out.sp_fallback[static_cast<unsigned char>(bytes[k])];
+                const bool last = k + 1 == bytes.size();
+                auto it = made.find({cur, nxt});
+                if (it == made.end()) {
+                    uint32_t res = c.second;
+                    if (!last) { res = static_cast<uint32_t>(out.token_bytes.size()); out.token_bytes.push_back(bytes.substr(0, k + 1)); }
+                    synthetic.push_back({cur, nxt, res});
+                    it = made.emplace(std::make_pair(cur, nxt), res).first;
+                }
+                cur = it->second;
+            }
+        }
+    }
+    for (int b = 0; b < 256 && !gemma; ++b) {
         auto it = id_of.find(utf8_of(byte_to_unicode()[b]));
         if (it == id_of.end()) {
             char buf[64];
@@ -257,6 +368,20 @@ bool load_tokenizer_json(const std::string& path, HostVocab& out, std::string& e
         auto ci = id_of.find(l + r);
         if (ci == id_of.end()) { err = "merge product missing from vocab"; return false; }
         out.merges.push_back({li->second, ri->second, ci->second});
+        if (gemma && r.compare(0, 3, kBar) == 0) {
+            // the character this rule's left side ends with may be joined to a U+2581 after it: no cut there
+            size_t i = l.size();
+            while (i > 0 && (static_cast<unsigned char>(l[i - 1]) & 0xC0) == 0x80) --i;
+            uint32_t cp = 0;
+            if (i > 0 && utf8_char(l, i - 1, &cp)) out.sp_before_bar.push_back(cp == 0x2581u ? 0x20u : cp), out.sp_before_bar.push_back(cp);
+        }
+    }
+    if (gemma) {
+        std::sort(out.sp_before_bar.begin(), out.sp_before_bar.end());
+        out.sp_before_bar.erase(std::unique(out.sp_before_bar.begin(), out.sp_before_bar.end()), out.sp_before_bar.end());
+        out.sp_synthetic = static_cast<uint32_t>(synthetic.size());
+        if (synthetic.size() + out.merges.size() >= (1u << 26)) { err = "more than 2^26 merges"; return false; }
+        out.merges.insert(out.merges.begin(), synthetic.begin(), synthetic.end());
     }
 
     // ---- added tokens ----------------------------------------------------
@@ -318,10 +443,17 @@ bool load_tokenizer_json(const std::string& path, HostVocab& out, std::string& e
                 }
     }
     out.vocab_size = static_cast<uint32_t>(out.token_bytes.size());
+    if (gemma) {
+        // the ids beyond the file's own (partly assembled characters) are not part of the vocabulary
+        uint32_t top = 0;
+        for (const json::Member& m : vocab->obj) top = std::max(top, static_cast<uint32_t>(m.second.inum) + 1);
+        for (const AddedToken& a : out.added) top = std::max(top, a.id + 1);
+        out.vocab_size = top;
+    }
 
     // ---- rank monotonicity ------------------------------------------------
     {
-        std::vector<uint32_t> last_made(out.vocab_size, 0);   // 1 + highest rank producing the id
+        std::vector<uint32_t> last_made(out.token_bytes.size(), 0);   // 1 + highest rank producing the id
         out.monotone = true;
         for (uint32_t k = 0; k < out.merges.size(); ++k)
             last_made[out.merges[k].result] = k + 1;

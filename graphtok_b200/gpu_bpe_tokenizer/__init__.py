@@ -19,7 +19,7 @@ from .. import GTok, GTokError, load_lib
 
 __all__ = ["Tokenizer", "Dispatcher"]
 
-_KINDS = {0: "GPT2", 1: "Llama3", 2: "Qwen25", 3: "DeepSeekV3"}
+_KINDS = {0: "GPT2", 1: "Llama3", 2: "Qwen25", 3: "DeepSeekV3", 4: "Gemma3"}
 _POLICIES = {"adaptive": 0, "gpu": 1, "cpu": 2}
 _BACKENDS = ("", "auto", "off", "host", "gigatoken")
 

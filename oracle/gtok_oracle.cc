@@ -380,10 +380,101 @@ struct Oracle {
         return best;
     }
 
+    // ---------------------------------------------------------------- Gemma-3 shape
+    // What Hugging Face does with such a file: every space becomes U+2581, the Split on " " then finds nothing to
+    // split, and the BPE model merges the characters of the whole text (between added tokens), lowest rank first,
+    // leftmost among equals; a character the vocabulary lacks is spelt as its "<0xNN>" byte tokens, which no rule
+    // mentions.  Done here on the characters themselves, with the file's own rules only (the loader's byte-level
+    // rewriting is the product's business), one priority queue over the whole stretch.
+    std::unordered_map<uint64_t, uint64_t, PairHash> sp_rules;      // the file's rules only, ranks from 0
+    static size_t sp_char(const uint8_t* p, size_t avail, uint32_t* cp) {   // strict UTF-8, 0 = not a character
+        const uint8_t c = p[0];
+        if (c < 0x80) { *cp = c; return 1; }
+        auto cont = [&](size_t k) { return k < avail && (p[k] & 0xC0) == 0x80; };
+        if (c >= 0xC2 && c <= 0xDF && cont(1)) { *cp = ((c & 0x1Fu) << 6) | (p[1] & 0x3Fu); return 2; }
+        if ((c & 0xF0) == 0xE0 && cont(1) && cont(2)) {
+            *cp = ((c & 0x0Fu) << 12) | ((p[1] & 0x3Fu) << 6) | (p[2] & 0x3Fu);
+            return (*cp >= 0x800 && !(*cp >= 0xD800 && *cp <= 0xDFFF)) ? 3 : 0;
+        }
+        if (c >= 0xF0 && c <= 0xF4 && cont(1) && cont(2) && cont(3)) {
+            *cp = ((c & 0x07u) << 18) | ((p[1] & 0x3Fu) << 12) | ((p[2] & 0x3Fu) << 6) | (p[3] & 0x3Fu);
+            return (*cp >= 0x10000 && *cp <= 0x10FFFF) ? 4 : 0;
+        }
+        return 0;
+    }
+    bool sp_id_of(uint32_t cp, uint32_t* id) const {
+        auto it = std::lower_bound(hv.sp_chars.begin(), hv.sp_chars.end(), std::make_pair(cp, 0u));
+        if (it == hv.sp_chars.end() || it->first != cp) return false;
+        *id = it->second;
+        return true;
+    }
+    void sp_segment(const uint8_t* text, size_t len, size_t base, std::vector<uint32_t>& out, std::vector<uint32_t>* starts) {
+        std::vector<uint32_t> sym, cps;
+        std::vector<uint32_t> at;                       // byte offset of each symbol
+        std::vector<uint8_t> known;
+        for (size_t i = 0; i < len;) {
+            uint32_t cp = 0, id = 0;
+            const size_t w = sp_char(text + i, len - i, &cp);
+            if (w && sp_id_of(cp, &id)) { sym.push_back(id); cps.push_back(cp); known.push_back(1); at.push_back(static_cast<uint32_t>(base + i)); i += w; }
+            else { sym.push_back(hv.sp_fallback[text[i]]); cps.push_back(0); known.push_back(0); at.push_back(static_cast<uint32_t>(base + i)); i += 1; }
+        }
+        const size_t m = sym.size();
+        if (starts) {
+            // where the product may cut (and does): around every byte that is not part of a character of the vocabulary,
+            // and in front of a space unless a rule could join it to the character before
+            for (size_t k = 0; k < m; ++k) {
+                bool cut = k == 0 || !known[k] || !known[k - 1];
+                if (!cut && (cps[k] == 0x20 || cps[k] == 0x2581)) cut = !std::binary_search(hv.sp_before_bar.begin(), hv.sp_before_bar.end(), cps[k - 1]);
+                if (cut) starts->push_back(at[k]);
+            }
+        }
+        std::vector<int> prev(m), next(m);
+        std::vector<uint8_t> dead(m, 0);
+        for (size_t k = 0; k < m; ++k) { prev[k] = static_cast<int>(k) - 1; next[k] = k + 1 < m ? static_cast<int>(k + 1) : -1; }
+        struct Cand { uint32_t rank; uint32_t pos; uint32_t l, r, res; };
+        auto worse = [](const Cand& a, const Cand& b) { return a.rank != b.rank ? a.rank > b.rank : a.pos > b.pos; };
+        std::priority_queue<Cand, std::vector<Cand>, decltype(worse)> heap(worse);
+        auto push = [&](int k) {
+            if (k < 0 || next[k] < 0) return;
+            auto it = sp_rules.find((static_cast<uint64_t>(sym[k]) << 32) | sym[next[k]]);
+            if (it != sp_rules.end()) heap.push({static_cast<uint32_t>(it->second >> 32), static_cast<uint32_t>(k), sym[k], sym[next[k]], static_cast<uint32_t>(it->second)});
+        };
+        for (size_t k = 0; k < m; ++k) push(static_cast<int>(k));
+        while (!heap.empty()) {
+            const Cand c = heap.top();
+            heap.pop();
+            const int k = static_cast<int>(c.pos);
+            if (dead[k] || next[k] < 0 || sym[k] != c.l || sym[next[k]] != c.r) continue;     // stale
+            const int r = next[k];
+            sym[k] = c.res;
+            dead[r] = 1;
+            next[k] = next[r];
+            if (next[r] >= 0) prev[next[r]] = k;
+            push(prev[k]);
+            push(k);
+        }
+        for (int k = m ? 0 : -1; k >= 0; k = next[k]) out.push_back(sym[k]);
+    }
+    void encode_sp(const uint8_t* text, size_t len, std::vector<uint32_t>& out, std::vector<uint32_t>* starts) {
+        size_t seg = 0;
+        for (size_t i = 0; i < len;) {
+            uint32_t id = 0;
+            const uint32_t al = (hv.added_max_bytes && root_byte[text[i]]) ? match_literal(text, len, i, &id) : 0u;
+            if (!al) { ++i; continue; }
+            if (i > seg) sp_segment(text + seg, i - seg, seg, out, starts);
+            if (starts) starts->push_back(static_cast<uint32_t>(i));
+            out.push_back(id);
+            i += al;
+            seg = i;
+        }
+        if (len > seg) sp_segment(text + seg, len - seg, seg, out, starts);
+    }
+
     // Stage 1-3 of the encoder.  Fills `starts` with the byte offset of every
     // pre-token (added-token literals included) when `starts` is non-null.
     void encode(const uint8_t* text, size_t len, std::vector<uint32_t>& out, std::vector<uint32_t>* starts) {
         if (len == 0) return;
+        if (hv.family == gtok::Family::Gemma3) { encode_sp(text, len, out, starts); return; }
         cls.resize(len); b0.resize(len); pos.resize(len); direct.resize(len);
         n = 0;
         const bool deepseek = hv.family == gtok::Family::DeepSeekV3;
@@ -458,6 +549,10 @@ void* gtok_oracle_create(const char* tokenizer_json, char* err, uint32_t err_cap
         const gtok::MergeRule& m = o->hv.merges[k];
         o->rules.emplace((static_cast<uint64_t>(m.left) << 32) | m.right, (static_cast<uint64_t>(k) << 32) | m.result);
     }
+    for (uint32_t k = o->hv.sp_synthetic; k < o->hv.merges.size() && o->hv.family == gtok::Family::Gemma3; ++k) {
+        const gtok::MergeRule& m = o->hv.merges[k];
+        o->sp_rules.emplace((static_cast<uint64_t>(m.left) << 32) | m.right, (static_cast<uint64_t>(k - o->hv.sp_synthetic) << 32) | m.result);
+    }
     if (o->hv.ignore_merges)
         for (uint32_t id = 0; id < o->hv.token_bytes.size(); ++id)
             if (!o->hv.token_bytes[id].empty()) o->whole.emplace(o->hv.token_bytes[id], id);
@@ -470,7 +565,7 @@ void* gtok_oracle_create(const char* tokenizer_json, char* err, uint32_t err_cap
 
 void gtok_oracle_destroy(void* h) { delete static_cast<Oracle*>(h); }
 
-// 0 GPT-2, 1 Llama-3, 2 Qwen2.5, 3 DeepSeek-V3; bit 8 set when the vocabulary asks for NFC.
+// 0 GPT-2, 1 Llama-3, 2 Qwen2.5, 3 DeepSeek-V3, 4 Gemma-3; bit 8 set when the vocabulary asks for NFC.
 uint32_t gtok_oracle_family(void* h) {
     Oracle* o = static_cast<Oracle*>(h);
     return static_cast<uint32_t>(o->hv.family) | (o->hv.nfc ? 0x100u : 0u);

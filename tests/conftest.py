@@ -8,8 +8,8 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-FAMILIES = ("gpt2", "llama3", "qwen25", "deepseek")
-SPECIAL = {"gpt2": None, "llama3": "<|reserved_special_token_3|>", "qwen25": "<|qwen_special_1|>", "deepseek": "<\uff5cspecial\u25811\uff5c>"}
+FAMILIES = ("gpt2", "llama3", "qwen25", "deepseek", "gemma")
+SPECIAL = {"gpt2": None, "llama3": "<|reserved_special_token_3|>", "qwen25": "<|qwen_special_1|>", "deepseek": "<\uff5cspecial\u25811\uff5c>", "gemma": "<bos>"}
 
 
 def pytest_configure(config):

@@ -91,6 +91,7 @@ void* gtok_emul_create(const char* path, char* err, uint32_t err_cap) {
         e->s1.assign(gtok_uw_stage1_init, gtok_uw_stage1_init + GTOK_UW_STAGE1_LEN);
         e->s2.assign(gtok_uw_stage2_init, gtok_uw_stage2_init + GTOK_UW_STAGE2_LEN);
     }
+    if (e->ht.family == 4) { e->s1 = e->ht.sp_stage1; e->s2 = e->ht.sp_stage2; }
     gtok::DeviceTables& tb = e->tb;
     const gtok::HostTables& ht = e->ht;
     tb.merge = ht.merge.data();

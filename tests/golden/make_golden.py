@@ -4,6 +4,9 @@
 Vocabularies: tiny_{gpt2,llama3,qwen25,deepseek}.json, written by the in-tree generator
 (graphtok_b200.synth.vocab_path("tiny_*"): seeded corpus + greedy BPE trainer) and
 committed here because the expected ids are only meaningful for these exact files.
+tiny_gemma.json (the Gemma-3 shape: characters merged by a SentencePiece-style BPE, spaces
+written as U+2581, byte fallback) is made by make_tiny_gemma() below with the `tokenizers`
+trainer on the in-tree synthetic text; `--vocab` rewrites it, else the committed file is used.
 
 Expected ids: Hugging Face `tokenizers` (the reference's own test oracle,
 tests/test_encode_batch.py:69-84 there) on every case string:
@@ -67,6 +70,14 @@ def cases(family, special):
         pool = list("ab Z!.-$_ \n\r\t") + ["\u00e9", "\u0301", "\u4e2d", "\u6587", "\u306e", "\u30ab", "\u30fb", "\u309b", "\x00", "\x01", "\u200b", "\u2026", "\u00ab", "\u20ac", "1", "12", "\u0663", "\u00a0"]
         for _ in range(400):
             c.append("".join(rng2.choice(pool) for _ in range(rng2.randint(1, 40))))
+    if family == "gemma":
+        # spaces against U+2581 itself, characters the vocabulary lacks (byte fallback), runs of spaces
+        c += ["\u2581", " \u2581 ", "a\u2581b c", "\u2581\u2581x", "x \u2581", "\u4e2d\u6587 \u6587\u4e2d", "\U0001F600 \U0001F600", "a\u0301 b\u0301",
+              "\x00 \x01", "\x7f", "word<eos>word", "<bos> x", "x <bos>", "<bo s>", " <pad>"]
+        rng3 = random.Random(20260103)
+        pool = list("ab cd\n\t.,XY12\u2581") + ["\u00e9", "\u4e2d", "\u6587", "\U0001F600", "\u0301", "<bos>", "<eos>", "  ", "   "]
+        for _ in range(500):
+            c.append("".join(rng3.choice(pool) for _ in range(rng3.randint(1, 40))))
     if family == "qwen25":
         c += ["e\u0301", "a\u0308o\u0308u\u0308", "\u0041\u030a", "\u212b", "\u1e9b\u0323", "q\u0307\u0323", "\uac00", "\u1100\u1161\u11a8",
               "\u0958", "\u0b47\u0b56", "x\u0301\u0301\u0301", "\u0301a", "caf\u0065\u0301 na\u0069\u0308ve", "\ufb01 \u00bd \u2126",
@@ -79,9 +90,42 @@ def cases(family, special):
     return out
 
 
+def make_tiny_gemma(path):
+    """A small vocabulary of the Gemma-3 shape: trained on pieces that do not cross a space (as SentencePiece does),
+    then given the file's real sections (Replace normaliser, the Split on " ", byte-fallback tokens, the decoder)."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from tokenizers import Regex, models, normalizers, pre_tokenizers, trainers
+    from graphtok_b200 import synth
+    text = synth.text(1, 4242, 600000).decode("utf-8", "ignore")
+    tok = Tokenizer(models.BPE(unk_token="<unk>", byte_fallback=True, fuse_unk=True))
+    tok.normalizer = normalizers.Replace(" ", "\u2581")
+    tok.pre_tokenizer = pre_tokenizers.Split(Regex("\u2581"), behavior="merged_with_next")
+    specials = ["<pad>", "<eos>", "<bos>", "<unk>"]
+    tok.train_from_iterator([l for l in text.split("\n") if l],
+                            trainers.BpeTrainer(vocab_size=3000, special_tokens=specials, show_progress=False, limit_alphabet=400))
+    j = json.loads(tok.to_str())
+    vocab = j["model"]["vocab"]
+    nid = max(vocab.values()) + 1
+    for b in range(256):
+        vocab["<0x%02X>" % b] = nid + b
+    j["normalizer"] = {"type": "Replace", "pattern": {"String": " "}, "content": "\u2581"}
+    j["pre_tokenizer"] = {"type": "Split", "pattern": {"String": " "}, "behavior": "MergedWithPrevious", "invert": False}
+    j["decoder"] = {"type": "Sequence", "decoders": [{"type": "Replace", "pattern": {"String": "\u2581"}, "content": " "},
+                                                     {"type": "ByteFallback"}, {"type": "Fuse"}]}
+    j["post_processor"] = None
+    j["added_tokens"] = [{"id": vocab[s], "content": s, "single_word": False, "lstrip": False, "rstrip": False, "normalized": False,
+                          "special": True} for s in specials]
+    with open(path, "w") as f:
+        json.dump(j, f, ensure_ascii=False)
+
+
 def main():
+    import sys
+    if "--vocab" in sys.argv:
+        make_tiny_gemma(os.path.join(HERE, "tiny_gemma.json"))
     for family, special in (("gpt2", None), ("llama3", "<|reserved_special_token_3|>"), ("qwen25", "<|qwen_special_1|>"),
-                            ("deepseek", "<\uff5cspecial\u25811\uff5c>")):
+                            ("deepseek", "<\uff5cspecial\u25811\uff5c>"), ("gemma", "<bos>")):
         vocab = os.path.join(HERE, "tiny_%s.json" % family)
         tok = Tokenizer.from_file(vocab)
         rows = []

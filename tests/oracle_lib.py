@@ -227,6 +227,15 @@ def token_spellings(tokenizer_json):
             extra += 1
     j = json.load(open(tokenizer_json, encoding="utf-8"))
     table = {}
+    if j["model"].get("byte_fallback"):
+        # the Gemma-3 shape: raw strings, U+2581 for a space, "<0xNN>" for a byte (its decoder section says the same)
+        import re
+        for tok, tid in j["model"]["vocab"].items():
+            m = re.fullmatch(r"<0x([0-9A-F]{2})>", tok)
+            table[tid] = bytes([int(m.group(1), 16)]) if m else tok.replace("\u2581", " ").encode("utf-8")
+        for at in j.get("added_tokens", []):
+            table[at["id"]] = at["content"].encode("utf-8")
+        return table
     for tok, tid in j["model"]["vocab"].items():
         table[tid] = bytes(back[ch] for ch in tok)
     for at in j.get("added_tokens", []):

@@ -96,6 +96,19 @@ def test_loader_accepts_the_known_shapes_only(built):
         ("deepseek", lambda j: j["pre_tokenizer"]["pretokenizers"][2].__setitem__("behavior", "Removed")),
         ("deepseek", lambda j: j["pre_tokenizer"]["pretokenizers"][3].__setitem__("use_regex", True)),
         ("deepseek", lambda j: j["model"].__setitem__("ignore_merges", True)),
+        # Gemma-3: Replace " " by U+2581, the Split on " " merged with the previous piece, byte fallback with every "<0xNN>" token
+        ("gemma", lambda j: j["normalizer"].__setitem__("content", "_")),
+        ("gemma", lambda j: j["normalizer"]["pattern"].__setitem__("String", "  ")),
+        ("gemma", lambda j: j.__setitem__("normalizer", None)),
+        ("gemma", lambda j: j["pre_tokenizer"].__setitem__("behavior", "Isolated")),
+        ("gemma", lambda j: j["pre_tokenizer"].__setitem__("invert", True)),
+        ("gemma", lambda j: j["pre_tokenizer"]["pattern"].__setitem__("String", "\u2581")),
+        ("gemma", lambda j: j["model"].__setitem__("byte_fallback", False)),
+        ("gemma", lambda j: j["model"].__setitem__("fuse_unk", False)),
+        ("gemma", lambda j: j["model"].__setitem__("unk_token", None)),
+        ("gemma", lambda j: j["model"].__setitem__("ignore_merges", True)),
+        ("gemma", lambda j: j["model"]["vocab"].pop("<0x7F>")),
+        ("gemma", lambda j: j["model"]["vocab"].pop("\u2581")),
     ]
     for fam, fn in bad:
         p = _mutate(fam, fn)

@@ -372,6 +372,12 @@ def test_configuration_2_batch_full_size(built):
         g.close()
 
 
+def decoded(family, b):
+    """What ids decode to when they were made from the bytes b: b itself, but for the Gemma-3 shape, whose U+2581 and
+    space are one character of the vocabulary that decodes to a space."""
+    return b.replace("\u2581".encode(), b" ") if family == "gemma" else b
+
+
 @pytest.mark.parametrize("family", FAMILIES)
 def test_decode_on_the_device(gtoks, oracles, family):
     """gtok_x_decode: random ids against the spellings read from the tokenizer.json, the golden
@@ -385,11 +391,11 @@ def test_decode_on_the_device(gtoks, oracles, family):
         assert g.decode(ids) == b"".join(table[int(t)] for t in ids), n
     data = json.load(open(os.path.join(GOLDEN, "golden_%s.json" % family)))
     for row in data["cases"]:
-        assert g.decode(row["ids"]) == norm(o, row["text"].encode("utf-8")), repr(row["text"][:40])
+        assert g.decode(row["ids"]) == decoded(family, norm(o, row["text"].encode("utf-8"))), repr(row["text"][:40])
     for t in cases.fuzz_strings(78, SPECIAL[family], per_pool=40):
         b = norm(o, t.encode())
         if b:
-            assert g.decode(g.encode(b)) == b, repr(t[:40])
+            assert g.decode(g.encode(b)) == decoded(family, b), repr(t[:40])
     assert g.decode(np.zeros(0, dtype=np.uint32)) == b""
     longest = max(table, key=lambda t: len(table[t]))
     assert g.decode(np.full(50000, longest, dtype=np.uint32)) == table[longest] * 50000

@@ -16,8 +16,17 @@ def norm(o, b):
     return oracle_lib.nfc(b) if o.needs_nfc else b
 
 
-def starts_without_dropped(starts, data):
-    """Boundary bits on stray continuation bytes (dropped text at a document start) carry no pre-token."""
+def decoded(family, b):
+    """What ids decode to when they were made from the bytes b: b itself, but for the Gemma-3 shape, whose U+2581 and
+    space are one character of the vocabulary that decodes to a space."""
+    return b.replace("\u2581".encode(), b" ") if family == "gemma" else b
+
+
+def starts_without_dropped(starts, data, family=None):
+    """Boundary bits on stray continuation bytes (dropped text at a document start) carry no pre-token -- except for the
+    Gemma-3 shape, which spells every byte of the text."""
+    if family == "gemma":
+        return np.array(starts, dtype=np.uint32)
     return np.array([s for s in starts if (data[s] & 0xC0) != 0x80], dtype=np.uint32)
 
 
@@ -40,7 +49,7 @@ def test_emul_fuzz_ids_and_boundaries(emuls, oracles, family):
         ids, st = e.encode(b, reverse=bool(i & 1), want_starts=True)
         want, wst = o.encode_normalized(b, want_starts=True)
         assert np.array_equal(ids, want), repr(t[:60])
-        assert np.array_equal(starts_without_dropped(st, b), wst), repr(t[:60])
+        assert np.array_equal(starts_without_dropped(st, b, family), wst), repr(t[:60])
 
 
 @pytest.mark.parametrize("family", FAMILIES)
@@ -218,12 +227,12 @@ def test_emul_decode_against_the_vocabulary_file_and_round_trip(emuls, oracles, 
     data = json.load(open(os.path.join(GOLDEN, "golden_%s.json" % family)))
     for row in data["cases"]:
         got, _, bits = e.decode(row["ids"])
-        assert bits == 0 and got == norm(o, row["text"].encode("utf-8")), repr(row["text"][:40])
+        assert bits == 0 and got == decoded(family, norm(o, row["text"].encode("utf-8"))), repr(row["text"][:40])
     for t in list(cases.fuzz_strings(77, SPECIAL[family], per_pool=25)) + [("naïve café — 日本語 " * 900)]:
         b = norm(o, t.encode())
         ids = o.encode_normalized(b)
         got, _, bits = e.decode(ids)
-        assert bits == 0 and got == b, repr(t[:40])
+        assert bits == 0 and got == decoded(family, b), repr(t[:40])
     # one long token repeated: several rounds of the staging buffer per tile
     longest = max(table, key=lambda t: len(table[t]))
     ids = np.full(6000, longest, dtype=np.uint32)
