@@ -82,6 +82,8 @@ struct DeviceTables {
     uint32_t lit_n_lens;
     uint32_t lit_lens[16];
     uint32_t family;                     // 0 GPT-2, 1 Llama-3, 2 Qwen2.5, 3 DeepSeek-V3, 4 Gemma-3
+    uint32_t sp_ascii_known[4];          // Gemma-3: bit c = the ASCII character c is a token of the vocabulary (the space stands for U+2581)
+    uint32_t sp_ascii_before_bar[4];     // ... and a rule may join it to a U+2581 after it
     uint32_t uc_wide;                    // the class table is the wide one (unicode_wide_table.h: four bits per codepoint)
     uint32_t ignore_merges;
     uint32_t monotone;

@@ -2085,6 +2085,17 @@ GTOK_DEV void pretok_tile(Blk& blk, const EncodeArgs& a, PretokSmem& sm, int til
             const uint8_t a0 = sm.attr[i];
             const uint64_t m = 1ull << bit;
             if ((a0 & A_CLS) == A_ADDED) { bnd |= m; continue; }
+            if (kWide && family == 4 && i >= 1) {
+                // Gemma-3 shape, an ASCII character after an ASCII character of the same document, no added token before it: settled
+                // from two bit sets of the vocabulary's ASCII characters (is_boundary_sp says the same, by the long way)
+                const uint32_t c = sm.txt[i], c1 = sm.txt[i - 1];
+                if (c < 0x80u && c1 < 0x80u && p >= 1 && !((DOC >> bit) & 1ull) && !((ADraw >> (bit - 1)) & 1ull)) {
+                    const bool known = (a.tb.sp_ascii_known[c >> 5] >> (c & 31)) & 1u, known1 = (a.tb.sp_ascii_known[c1 >> 5] >> (c1 & 31)) & 1u;
+                    const bool cut = !known || !known1 || (c == 0x20u && !((a.tb.sp_ascii_before_bar[c1 >> 5] >> (c1 & 31)) & 1u));
+                    if (cut) bnd |= m; else bnd &= ~m;
+                    continue;
+                }
+            }
             bool pending = false, ns = false;
             const bool bb = kWide ? (family == 4 ? is_boundary_sp(w, p) : is_boundary_deepseek(w, p, a0, &pending, &ns)) : is_boundary(w, p, a0, family, &pending, &ns);
             if (bb) bnd |= m; else bnd &= ~m;

@@ -123,7 +123,10 @@ bool build_host_tables(const HostVocab& hv, HostTables& out, std::string& err) {
     // ---- Gemma-3 shape: the vocabulary's characters as a class table ------------
     out.sp_stage1.clear();
     out.sp_stage2.clear();
+    for (int i = 0; i < 4; ++i) out.sp_ascii_known[i] = out.sp_ascii_before_bar[i] = 0;
     if (hv.family == Family::Gemma3) {
+        for (const auto& c : hv.sp_chars) if (c.first < 128) out.sp_ascii_known[c.first >> 5] |= 1u << (c.first & 31);
+        for (uint32_t c : hv.sp_before_bar) if (c < 128) out.sp_ascii_before_bar[c >> 5] |= 1u << (c & 31);
         std::map<std::vector<uint32_t>, uint16_t> leaves;      // sixteen words of 4-bit classes -> leaf number
         out.sp_stage1.assign(0x110000 / 128, 0);
         size_t ci = 0, bi = 0;

@@ -30,6 +30,7 @@ struct HostTables {
     // vocabulary: 0 a character of the vocabulary, 6 one that a rule may join to a U+2581 after it, 3 any other codepoint
     std::vector<uint16_t> sp_stage1;
     std::vector<uint32_t> sp_stage2;
+    uint32_t sp_ascii_known[4] = {}, sp_ascii_before_bar[4] = {};
     uint32_t family = 0, ignore_merges = 0, monotone = 1, added_ws = 0, added_alpha_end = 0, lit_first = 0, lit_first_n = 0;
 };
 
@@ -50,6 +51,7 @@ inline void fill_table_scalars(const HostTables& ht, DeviceTables& tb) {
     tb.lit_n_lens = ht.lit_n_lens;
     for (int i = 0; i < kLitLens; ++i) tb.lit_lens[i] = ht.lit_lens[i];
     tb.family = ht.family;
+    for (int i = 0; i < 4; ++i) { tb.sp_ascii_known[i] = ht.sp_ascii_known[i]; tb.sp_ascii_before_bar[i] = ht.sp_ascii_before_bar[i]; }
     tb.uc_wide = ht.family == 3 || ht.family == 4 ? 1u : 0u;
     tb.ignore_merges = ht.ignore_merges;
     tb.monotone = ht.monotone;
