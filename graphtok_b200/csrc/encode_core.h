@@ -1212,20 +1212,27 @@ GTOK_DEV int sp_char_at(const Win& w, int p, int* start, uint32_t* cp) {
     *cp = v;
     return width;
 }
-GTOK_DEV uint32_t sp_class(const EncodeArgs& a, uint32_t cp) {
+// Class of the whole character cp that begins at s.  Inside the window the classification phase has looked it up already
+// (a well-formed sequence decodes there to the same codepoint); outside, from the table in global memory.
+GTOK_DEV uint32_t sp_class(const Win& w, int s, uint32_t cp) {
+    if (s >= w.vlo && s < w.vhi) {
+        const uint32_t k = w.sm->attr[s - w.lo] & A_CLS;
+        if (k == 0u || k == 3u || k == 6u) return k;              // (an added token's bytes carry another class: the long way then)
+    }
+    const EncodeArgs& a = *w.a;
     return uc_class([&](uint32_t i) { return static_cast<uint32_t>(ldg(a.tb.uc_stage1 + i)); }, [&](uint32_t i) { return ldg(a.tb.uc_stage2 + i); }, cp, true);
 }
 GTOK_DEV_NOINLINE bool is_boundary_sp(const Win& w, int p) {
     if (p == 0 || sp_docstart_at(w, p)) return true;
     int s = 0, s1 = 0;
     uint32_t cp = 0, c1 = 0;
-    if (!sp_char_at(w, p, &s, &cp) || sp_class(*w.a, cp) == 3u) return true;       // on its own, byte by byte
+    if (!sp_char_at(w, p, &s, &cp) || sp_class(w, s, cp) == 3u) return true;       // on its own, byte by byte
     if (s != p) return false;                                                         // inside a character
     // what ends right before p: an added token, a byte on its own, or a character
     const int q = prev_lead(w, p);
     if (q < 0 || (attr_at(w, q) & A_CLS) == A_ADDED) return true;
     if (!sp_char_at(w, p - 1, &s1, &c1)) return true;
-    const uint32_t k1 = sp_class(*w.a, c1);
+    const uint32_t k1 = sp_class(w, s1, c1);
     if (k1 == 3u) return true;
     if (cp == 0x20u || cp == 0x2581u) return k1 != 6u;
     return false;
