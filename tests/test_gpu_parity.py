@@ -351,6 +351,27 @@ def test_deepseek_vocabulary_on_the_adversarial_document(built):
         g.close()
 
 
+def test_gemma_vocabulary_on_large_documents(built):
+    """The Gemma-3-shaped vocabulary on 4 MB of the multilingual text (a third of its characters are not in the
+    3,000-token vocabulary and come out as byte tokens) and on 2 MB of the adversarial document (its long runs are long
+    pre-tokens here): one replay and four planned chunks against the oracle, which merges each whole text without cutting it,
+    and the ids decoded back."""
+    from graphtok_b200 import GTok, synth
+    path = tiny_vocab("gemma")
+    o = oracle_lib.Oracle(path)
+    for doc in (synth.text(1, 7, 4 << 20), synth.config_doc(4)[1][:2 << 20].decode("utf-8", "ignore").encode()):
+        want = o.encode_normalized(doc)
+        g = GTok(path, max_bytes=len(doc) + 4096)
+        try:
+            ids = g.encode(doc)
+            assert np.array_equal(ids, want)
+            cuts = g.plan_chunks(doc, 4)
+            assert np.array_equal(np.concatenate([g.encode(doc[int(cuts[k]):int(cuts[k + 1])]) for k in range(4) if cuts[k + 1] > cuts[k]]), want)
+            assert g.decode(ids) == decoded("gemma", doc)
+        finally:
+            g.close()
+
+
 def test_configuration_2_batch_full_size(built):
     """All 8,192 documents of the batch configuration in one call: ids and per-document offsets
     against the oracle run document by document."""
